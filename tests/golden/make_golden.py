@@ -1,0 +1,250 @@
+"""Generate the golden vectors in this folder by RUNNING THE REFERENCE.
+
+Run where the reference checkout and its compiled CPU extension exist:
+
+    python oracle/build_ref.py            # compiles oracle/_ref/philtorch_ref_C.so
+    python tests/golden/make_golden.py    # writes tests/golden/*.npz
+
+The reference Python package is imported from its checkout (nothing is copied): its
+compiled module ``philtorch._C`` is replaced by the extension built from its own C++
+sources, and its third-party dependency ``torchlpc`` (not installed here, not used by
+any call below) by a stub that raises.
+
+Every case stores inputs, outputs and gradients produced by the reference's public
+API and autograd Functions; names of the callables are recorded in each file's
+``case`` entry.
+"""
+from __future__ import annotations
+
+import os
+import sys
+import types
+import warnings
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+
+from oracle import build_ref  # noqa: E402
+
+
+def import_reference():
+    so = build_ref.build_reference_ext()
+    ref_dir = build_ref.reference_dir()
+    assert so and ref_dir, "reference checkout not found"
+    torch.ops.load_library(so)
+    sys.modules["philtorch._C"] = types.ModuleType("philtorch._C")
+    stub = types.ModuleType("torchlpc")
+
+    def _missing(*a, **k):
+        raise RuntimeError("torchlpc is not installed")
+
+    stub.sample_wise_lpc = _missing
+    sys.modules["torchlpc"] = stub
+    sys.path.insert(0, ref_dir)
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        import philtorch  # noqa: F401
+        import philtorch.lti
+        import philtorch.lpv
+    assert philtorch.EXTENSION_LOADED
+    return philtorch
+
+
+def _np(t):
+    return None if t is None else t.detach().cpu().numpy()
+
+
+def save(name, **arrays):
+    arrays = {k: v for k, v in arrays.items() if v is not None}
+    np.savez_compressed(os.path.join(HERE, name + ".npz"), **arrays)
+    print(name, {k: getattr(v, "shape", None) for k, v in arrays.items()})
+
+
+def grads(out, gy, *inputs):
+    gs = torch.autograd.grad(out, inputs, gy, allow_unused=True)
+    return [_np(g) for g in gs]
+
+
+def main():
+    pt = import_reference()
+    from philtorch.lti.recur import LTIRecurrence
+    from philtorch.lti.ssm import LTIMatrixRecurrence
+    from philtorch.lpv.ssm import MatrixRecurrence
+    from philtorch.mat import companion
+
+    torch.manual_seed(20240607)
+
+    # ---- first-order LTI: LTIRecurrence (op lti_recur) ------------------------------
+    for dt, tag in ((torch.float64, "f64"), (torch.float32, "f32")):
+        for mode in ("batched", "shared1", "scalar"):
+            B, T = 3, 101
+            a = (torch.rand(B if mode == "batched" else 1, dtype=dt) * 2 - 1)
+            if mode == "scalar":
+                a = a[0]
+            a = a.clone().requires_grad_()
+            zi = torch.randn(B, dtype=dt, requires_grad=True)
+            x = torch.randn(B, T, dtype=dt, requires_grad=True)
+            gy = torch.randn(B, T, dtype=dt)
+            y = LTIRecurrence.apply(a, zi, x)
+            ga, gzi, gx = grads(y, gy, a, zi, x)
+            save(f"lti_recur_{mode}_{tag}", a=_np(a), zi=_np(zi), x=_np(x), gy=_np(gy), y=_np(y),
+                 grad_a=ga, grad_zi=gzi, grad_x=gx)
+
+    # ---- first-order LPV through recurN with N = 1 and the pure-Python loop ----------
+    for dt, tag in ((torch.float64, "f64"), (torch.float32, "f32")):
+        for mode in ("batched", "shared"):
+            B, T = 3, 257
+            a = (torch.rand(*((B, T) if mode == "batched" else (T,)), dtype=dt) * 1.98 - 0.99)
+            a.requires_grad_()
+            zi = torch.randn(B, dtype=dt, requires_grad=True)
+            x = torch.randn(B, T, dtype=dt, requires_grad=True)
+            gy = torch.randn(B, T, dtype=dt)
+            y = MatrixRecurrence.apply(a[..., None, None], zi[:, None], x[..., None])[..., 0]
+            ga, gzi, gx = grads(y, gy, a, zi, x)
+            y_loop = pt.lpv.linear_recurrence(a.detach(), zi.detach(), x.detach())
+            y_unrolled = pt.lpv.linear_recurrence(a.detach(), zi.detach(), x.detach(), unroll_factor=8)
+            save(f"lpv_recur1_{mode}_{tag}", a=_np(a), zi=_np(zi), x=_np(x), gy=_np(gy), y=_np(y),
+                 y_python_loop=_np(y_loop), y_python_unrolled=_np(y_unrolled),
+                 grad_a=ga, grad_zi=gzi, grad_x=gx)
+
+    # ---- 2x2 LTI: LTIMatrixRecurrence (op lti_recur2) -------------------------------
+    def rand_stable_a(n):
+        r = 0.5 + 0.49 * torch.rand(n, dtype=torch.float64)
+        th = np.pi * torch.rand(n, dtype=torch.float64)
+        return torch.stack([-2 * r * torch.cos(th), r * r], -1)
+
+    for dt, tag in ((torch.float64, "f64"), (torch.float32, "f32")):
+        for mode in ("batched", "shared"):
+            B, T = 3, 101
+            A = companion(rand_stable_a(B if mode == "batched" else 1)).to(dt)
+            if mode == "shared":
+                A = A[0]
+            A = A.clone().requires_grad_()
+            zi = torch.randn(B, 2, dtype=dt, requires_grad=True)
+            x = torch.randn(B, T, 2, dtype=dt, requires_grad=True)
+            gy = torch.randn(B, T, 2, dtype=dt)
+            y = LTIMatrixRecurrence.apply(A, zi, x)
+            gA, gzi, gx = grads(y, gy, A, zi, x)
+            save(f"lti_recur2_{mode}_{tag}", A=_np(A), zi=_np(zi), x=_np(x), gy=_np(gy), y=_np(y),
+                 grad_A=gA, grad_zi=gzi, grad_x=gx)
+
+    # ---- 2x2 LPV: MatrixRecurrence (op recur2) --------------------------------------
+    for dt, tag in ((torch.float64, "f64"), (torch.float32, "f32")):
+        for mode in ("batched", "shared"):
+            B, T = 3, 77
+            n = (B, T) if mode == "batched" else (T,)
+            r = 0.6 + 0.38 * torch.rand(*n, dtype=torch.float64)
+            th = np.pi * torch.rand(*n, dtype=torch.float64)
+            A = companion(torch.stack([-2 * r * torch.cos(th), r * r], -1)).to(dt)
+            A = (A + 0.05 * torch.randn_like(A)).requires_grad_()   # general, not only companion
+            zi = torch.randn(B, 2, dtype=dt, requires_grad=True)
+            x = torch.randn(B, T, 2, dtype=dt, requires_grad=True)
+            gy = torch.randn(B, T, 2, dtype=dt)
+            y = MatrixRecurrence.apply(A, zi, x)
+            gA, gzi, gx = grads(y, gy, A, zi, x)
+            y_loop = pt.lpv.state_space_recursion(A.detach(), zi.detach(), x.detach())
+            y_loop_idx = pt.lpv.state_space_recursion(A.detach(), zi.detach(), x.detach()[..., 0], out_idx=1)
+            save(f"lpv_recur2_{mode}_{tag}", A=_np(A), zi=_np(zi), x=_np(x), gy=_np(gy), y=_np(y),
+                 y_python_loop=_np(y_loop), y_python_loop_x2d_idx1=_np(y_loop_idx),
+                 grad_A=gA, grad_zi=gzi, grad_x=gx)
+
+    # ---- public scalar API: lti.linear_recurrence ------------------------------------
+    B, T = 4, 130
+    a = torch.rand(B, dtype=torch.float64) * 1.8 - 0.9
+    zi = torch.randn(B, dtype=torch.float64)
+    x = torch.randn(B, T, dtype=torch.float64)
+    save("lti_linear_recurrence_f64", a=_np(a), zi=_np(zi), x=_np(x),
+         y=_np(pt.lti.linear_recurrence(a, zi, x)),
+         y_unrolled=_np(pt.lti.linear_recurrence(a, zi, x, unroll_factor=7)),
+         y_scalar_a=_np(pt.lti.linear_recurrence(a[0], zi[0], x)))
+
+    # ---- public matrix API: lti.state_space_recursion --------------------------------
+    A = companion(rand_stable_a(B))
+    zi2 = torch.randn(B, 2, dtype=torch.float64)
+    x2 = torch.randn(B, T, 2, dtype=torch.float64)
+    save("lti_state_space_recursion_f64", A=_np(A), zi=_np(zi2), x=_np(x2),
+         y=_np(pt.lti.state_space_recursion(A, zi2, x2)),
+         y_shared=_np(pt.lti.state_space_recursion(A[0], zi2, x2)),
+         y_x2d_idx0=_np(pt.lti.state_space_recursion(A, zi2, x2[..., 0], out_idx=0)),
+         y_unrolled=_np(pt.lti.state_space_recursion(A, zi2, x2, unroll_factor=5)))
+
+    # ---- lfilter / filtfilt through the extension route (unroll_factor=1) -------------
+    for dt, tag in ((torch.float64, "f64"), (torch.float32, "f32")):
+        for order in (1, 2):
+            for mode in ("batched", "shared"):
+                B, T = 4, 300
+                nb = B if mode == "batched" else 1
+                if order == 2:
+                    a = rand_stable_a(nb)
+                else:
+                    a = (torch.rand(nb, 1, dtype=torch.float64) * 1.8 - 0.9)
+                b = torch.randn(nb, order + 1, dtype=torch.float64)
+                if mode == "shared":
+                    a, b = a[0], b[0]
+                a = a.to(dt).requires_grad_()
+                b = b.to(dt).requires_grad_()
+                x = torch.randn(B, T, dtype=dt, requires_grad=True)
+                zi = torch.randn(B, order, dtype=dt, requires_grad=True)
+                gy = torch.randn(B, T, dtype=dt)
+                gzf = torch.randn(B, order, dtype=dt)
+                out = {}
+                for form in ("tdf2", "df2"):
+                    y = pt.lti.lfilter(b, a, x, form=form, unroll_factor=1)
+                    gb, ga, gx = grads(y, gy, b, a, x)
+                    y_zi, zf = pt.lti.lfilter(b, a, x, zi=zi, form=form, unroll_factor=1)
+                    gs = torch.autograd.grad([y_zi, zf], [b, a, x, zi], [gy, gzf])
+                    out.update({f"{form}_y": _np(y), f"{form}_grad_b": gb, f"{form}_grad_a": ga,
+                                f"{form}_grad_x": gx, f"{form}_y_zi": _np(y_zi), f"{form}_zf": _np(zf),
+                                f"{form}_zi_grad_b": _np(gs[0]), f"{form}_zi_grad_a": _np(gs[1]),
+                                f"{form}_zi_grad_x": _np(gs[2]), f"{form}_zi_grad_zi": _np(gs[3])})
+                ff = pt.lti.filtfilt(b.detach(), a.detach(), x.detach(), unroll_factor=1)
+                ffg = pt.lti.filtfilt(b, a, x, unroll_factor=1)
+                gb, ga, gx = grads(ffg, gy, b, a, x)
+                save(f"lfilter_order{order}_{mode}_{tag}", b=_np(b), a=_np(a), x=_np(x), zi=_np(zi),
+                     gy=_np(gy), gzf=_np(gzf), filtfilt_y=_np(ff), filtfilt_grad_b=gb,
+                     filtfilt_grad_a=ga, filtfilt_grad_x=gx, **out)
+
+    # ---- the five benchmark configurations at reduced size ----------------------------
+    from philtorch_b200 import workloads as W
+
+    w = W.lti_first_order(B=8, T=4096)
+    a, zi, x = (w[k].clone().requires_grad_() for k in ("a", "zi", "x"))
+    y = LTIRecurrence.apply(a, zi, x)
+    ga, gzi, gx = grads(y, w["gy"], a, zi, x)
+    save("config1_small", y=_np(y), grad_a=ga, grad_x=gx, B=8, T=4096)
+
+    w = W.lpv_first_order(B=4, T=8192)
+    a, zi, x = (w[k].clone().requires_grad_() for k in ("a", "zi", "x"))
+    y = MatrixRecurrence.apply(a[..., None, None], zi[:, None], x[..., None])[..., 0]
+    ga, gzi, gx = grads(y, w["gy"], a, zi, x)
+    save("config2_small", y=_np(y), grad_a=ga, grad_zi=gzi, grad_x=gx, B=4, T=8192)
+
+    w = W.sos_cascade(B=4, T=4096, sections=6)
+    b, a, x = (w[k].clone().requires_grad_() for k in ("b", "a", "x"))
+    u = x
+    for k in range(6):
+        u = pt.lti.lfilter(b[k], a[k], u, form="tdf2", unroll_factor=1)
+    gb, ga, gx = grads(u, w["gy"], b, a, x)
+    save("config3_small", y=_np(u), grad_b=gb, grad_a=ga, grad_x=gx, B=4, T=4096)
+
+    for dt, tag in ((torch.float32, "f32"), (torch.float64, "f64")):
+        w = W.lpv_second_order(B=2, T=4096, dtype=dt)
+        A, x = (w[k].clone().requires_grad_() for k in ("A", "x"))
+        xp = torch.stack([x, torch.zeros_like(x)], -1)
+        y = MatrixRecurrence.apply(A, w["zi"], xp)
+        gA, gx = grads(y, w["gy"], A, x)
+        save(f"config4_small_{tag}", y=_np(y), grad_A=gA, grad_x=gx, B=2, T=4096)
+
+    w = W.long_first_order(B=2, T=16384)
+    a, zi, x = (w[k].clone().requires_grad_() for k in ("a", "zi", "x"))
+    y = MatrixRecurrence.apply(a[..., None, None], zi[:, None], x[..., None])[..., 0]
+    ga, gzi, gx = grads(y, w["gy"], a, zi, x)
+    save("config5_small", y=_np(y), grad_a=ga, grad_x=gx, B=2, T=16384)
+
+
+if __name__ == "__main__":
+    main()

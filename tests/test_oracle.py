@@ -1,0 +1,124 @@
+"""Pins the CPU oracle (oracle/recur_oracle.c) against the reference: the golden vectors
+made by running the reference, and -- when it was compiled into oracle/_ref -- the
+reference CPU extension itself on fresh seeded inputs."""
+import pytest
+import torch
+
+from conftest import load_golden, rel_err, tol
+from oracle import cport, refext
+
+DT = {"f32": torch.float32, "f64": torch.float64}
+
+
+@pytest.mark.parametrize("tag", ["f32", "f64"])
+@pytest.mark.parametrize("mode", ["batched", "shared1", "scalar"])
+def test_lti_recur_golden(tag, mode):
+    g = load_golden(f"lti_recur_{mode}_{tag}")
+    t = tol(DT[tag])
+    y = cport.lti_recur(g["a"], g["zi"], g["x"])
+    assert rel_err(y, g["y"]) <= t
+    ga, gzi, gx = cport.lti_recur_bwd(g["a"], g["zi"], g["y"], g["gy"])
+    assert rel_err(ga, g["grad_a"]) <= t
+    assert rel_err(gzi, g["grad_zi"]) <= t
+    assert rel_err(gx, g["grad_x"]) <= t
+
+
+@pytest.mark.parametrize("tag", ["f32", "f64"])
+@pytest.mark.parametrize("mode", ["batched", "shared"])
+def test_recur1_golden(tag, mode):
+    g = load_golden(f"lpv_recur1_{mode}_{tag}")
+    t = tol(DT[tag])
+    y = cport.recur1(g["a"], g["zi"], g["x"])
+    assert rel_err(y, g["y"]) <= t
+    assert rel_err(y, g["y_python_loop"]) <= t
+    assert rel_err(y, g["y_python_unrolled"]) <= (1e-4 if tag == "f32" else 1e-9)
+    ga, gzi, gx = cport.recur1_bwd(g["a"], g["zi"], g["y"], g["gy"])
+    assert rel_err(ga, g["grad_a"]) <= t
+    assert rel_err(gzi, g["grad_zi"]) <= t
+    assert rel_err(gx, g["grad_x"]) <= t
+
+
+@pytest.mark.parametrize("tag", ["f32", "f64"])
+@pytest.mark.parametrize("mode", ["batched", "shared"])
+@pytest.mark.parametrize("kind", ["lti", "lpv"])
+def test_recur2_golden(tag, mode, kind):
+    g = load_golden(f"{kind}_recur2_{mode}_{tag}")
+    t = tol(DT[tag])
+    fwd = cport.lti_recur2 if kind == "lti" else cport.recur2
+    bwd = cport.lti_recur2_bwd if kind == "lti" else cport.recur2_bwd
+    y = fwd(g["A"], g["zi"], g["x"])
+    assert rel_err(y, g["y"]) <= t
+    if kind == "lpv":
+        assert rel_err(y, g["y_python_loop"]) <= t
+    gA, gzi, gx = bwd(g["A"], g["zi"], g["y"], g["gy"])
+    assert rel_err(gA, g["grad_A"]) <= t
+    assert rel_err(gzi, g["grad_zi"]) <= t
+    assert rel_err(gx, g["grad_x"]) <= t
+
+
+@pytest.mark.parametrize("tag", ["f32", "f64"])
+@pytest.mark.parametrize("mode", ["batched", "shared"])
+def test_biquad_golden(tag, mode):
+    g = load_golden(f"lfilter_order2_{mode}_{tag}")
+    t = tol(DT[tag])
+    y, _ = cport.biquad_tdf2(g["b"], g["a"], None, g["x"])
+    assert rel_err(y, g["tdf2_y"]) <= t
+    y, zf = cport.biquad_tdf2(g["b"], g["a"], g["zi"], g["x"])
+    assert rel_err(y, g["tdf2_y_zi"]) <= t
+    assert rel_err(zf, g["tdf2_zf"]) <= t
+
+
+def test_g_in_chains_adjoint():
+    """An adjoint state entering from the right equals running the adjoint on the
+    concatenated sequence (used when a long sequence is split along time)."""
+    torch.manual_seed(0)
+    B, T = 3, 64
+    a = torch.rand(B, T, dtype=torch.float64) * 1.9 - 0.95
+    zi = torch.randn(B, dtype=torch.float64)
+    x = torch.randn(B, T, dtype=torch.float64)
+    gy = torch.randn(B, T, dtype=torch.float64)
+    y = cport.recur1(a, zi, x)
+    ga, gzi, gx = cport.recur1_bwd(a, zi, y, gy)
+    h = T // 2
+    ga2, gzi2, gx2 = cport.recur1_bwd(a[:, h:], y[:, h - 1], y[:, h:], gy[:, h:])
+    ga1, gzi1, gx1 = cport.recur1_bwd(a[:, :h], zi, y[:, :h], gy[:, :h], g_in=gzi2)
+    assert rel_err(torch.cat([gx1, gx2], 1), gx) <= 1e-12
+    assert rel_err(torch.cat([ga1, ga2], 1), ga) <= 1e-12
+    assert rel_err(gzi1, gzi) <= 1e-12
+
+
+needs_ref = pytest.mark.skipif(not refext.available(), reason="reference extension not built")
+
+
+@needs_ref
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+def test_against_reference_extension(dtype):
+    torch.manual_seed(1)
+    B, T = 5, 333
+    t = tol(dtype)
+    zi = torch.randn(B, dtype=dtype)
+    x = torch.randn(B, T, dtype=dtype)
+    gy = torch.randn(B, T, dtype=dtype)
+    for a in (torch.rand(B, dtype=dtype) * 1.8 - 0.9, torch.rand(1, dtype=dtype) * 1.8 - 0.9):
+        y = cport.lti_recur(a, zi, x)
+        assert rel_err(y, refext.lti_recur(a, zi, x)) <= t
+        for o, r in zip(cport.lti_recur_bwd(a, zi, y, gy), refext.lti_recur_bwd(a, zi, y, gy)):
+            assert rel_err(o, r) <= t
+    for a in (torch.rand(B, T, dtype=dtype) * 1.9 - 0.95, torch.rand(T, dtype=dtype) * 1.9 - 0.95):
+        y = cport.recur1(a, zi, x)
+        assert rel_err(y, refext.recur1(a, zi, x)) <= t
+        for o, r in zip(cport.recur1_bwd(a, zi, y, gy), refext.recur1_bwd(a, zi, y, gy)):
+            assert rel_err(o, r) <= t
+    zi2 = torch.randn(B, 2, dtype=dtype)
+    x2 = torch.randn(B, T, 2, dtype=dtype)
+    gy2 = torch.randn(B, T, 2, dtype=dtype)
+    for A in (torch.randn(B, 2, 2, dtype=dtype) * 0.4, torch.randn(2, 2, dtype=dtype) * 0.4):
+        y = cport.lti_recur2(A, zi2, x2)
+        assert rel_err(y, refext.lti_recur2(A, zi2, x2)) <= t
+        for o, r in zip(cport.lti_recur2_bwd(A, zi2, y, gy2), refext.lti_recur2_bwd(A, zi2, y, gy2)):
+            assert rel_err(o, r) <= t
+    for A in (torch.randn(B, T, 2, 2, dtype=dtype) * 0.4, torch.randn(T, 2, 2, dtype=dtype) * 0.4):
+        y = cport.recur2(A, zi2, x2)
+        assert rel_err(y, refext.recur2(A, zi2, x2)) <= t
+        for o, r in zip(cport.recur2_bwd(A, zi2, y, gy2), refext.recur2_bwd(A, zi2, y, gy2)):
+            assert rel_err(o, r) <= t
