@@ -1,0 +1,95 @@
+/*
+ * philtorch_b200 -- C ABI of the B200 (sm_100a) linear-recurrence kernels.
+ *
+ * Drop-in boundary for the differentiable linear-recurrence path of the reference project
+ * (philtorch): the functions below are what a binding of that path's native ops would call.
+ * Plain pointers and sizes only; no torch types.  All data pointers are DEVICE pointers to
+ * dense row-major arrays; every call is asynchronous on `stream`, allocates nothing and
+ * synchronises nothing.
+ *
+ * Common conventions
+ *   dtype        PTB_F32 or PTB_F64; all arrays of a call share it.
+ *   recurrence   y[-1] := zi, y[t] = A[t] * y[t-1] + x[t], t = 0..T-1: the coefficient with time
+ *                index t multiplies the PREVIOUS state (philtorch/csrc/host_recurN.cpp:254-255).
+ *   *_batched    1: the array has a leading batch axis of length B; 0: one copy shared by all rows.
+ *   workspace    scratch of at least ptb_workspace_bytes(B, T) bytes, 256-byte aligned, private to
+ *                the call until it completes (tile tickets, look-back flags, per-tile carries).
+ *   status       device uint32, sticky error bits OR-ed in by the kernels when a bounded device
+ *                wait expires (never cleared by the library); read it with ptb_read_status.
+ *                May be NULL.
+ *   return       PTB_OK or a PTB_ERR_* code; nothing was launched on error.
+ */
+#ifndef PHILTORCH_B200_H
+#define PHILTORCH_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* ptb_stream_t; /* a cudaStream_t */
+
+enum { PTB_F32 = 0, PTB_F64 = 1 };
+enum {
+  PTB_OK = 0,
+  PTB_ERR_ARG = 1,       /* null pointer, negative size, unknown dtype */
+  PTB_ERR_WORKSPACE = 2, /* workspace missing, misaligned or too small */
+  PTB_ERR_CUDA = 3,      /* a CUDA runtime call failed (see ptb_last_cuda_error) */
+  PTB_ERR_TOO_LARGE = 4  /* more than 2^32-2 tiles */
+};
+
+const char* ptb_version(void);
+const char* ptb_error_string(int code);
+/* cudaError_t of the last failing runtime call made by this library on the calling thread. */
+int ptb_last_cuda_error(void);
+
+/* Upper bound of the scratch any entry point needs for B rows of T samples. */
+int64_t ptb_workspace_bytes(int64_t B, int64_t T);
+
+/* Copies *status to the host after synchronising `stream` (the only blocking call). */
+int ptb_read_status(const uint32_t* status, ptb_stream_t stream, uint32_t* host_out);
+
+/* ---- first-order, time-invariant ------------------------------------------------------------
+ * Replaces op philtorch::lti_recur(a, zi, x) -> y
+ *   (philtorch/csrc/host_recur2.cpp:170, CPU kernel philtorch/csrc/host_lti_recur.cpp:42-80,
+ *    CUDA philtorch/csrc/lti_recur.cu:113-158).
+ * a: (B,) if a_batched else (1,); zi: (B,) if zi_batched else (1,); x, y: (B,T);
+ * zf: optional (B,), receives y[:, T-1]. */
+int ptb_lti_recur_fwd(int dtype, int64_t B, int64_t T, const void* a, int a_batched, const void* zi,
+                      int zi_batched, const void* x, void* y, void* zf, void* workspace,
+                      int64_t workspace_bytes, uint32_t* status, ptb_stream_t stream);
+
+/* Fused adjoint of the above; replaces LTIRecurrence.backward (philtorch/lti/recur.py:25-59) and
+ * _lti_recur_backward (philtorch/__init__.py:115-148), which run the forward op on flipped copies.
+ *   g[t] = a*g[t+1] + gy[t];  grad_x = g;  grad_zi = a*g[0];
+ *   grad_a = sum_t y[t-1]*g[t] per row, summed over rows as well when !a_batched.
+ * y: forward output (B,T); gy: (B,T); g_in: optional (B,), an adjoint state a*g[T] entering from the
+ * right (rows that continue on another device); grad_x: (B,T); grad_a: optional, (B,) or (1,);
+ * grad_zi: optional (B,). */
+int ptb_lti_recur_bwd(int dtype, int64_t B, int64_t T, const void* a, int a_batched, const void* zi,
+                      int zi_batched, const void* y, const void* gy, const void* g_in, void* grad_x,
+                      void* grad_a, void* grad_zi, void* workspace, int64_t workspace_bytes,
+                      uint32_t* status, ptb_stream_t stream);
+
+/* ---- first-order, per-sample coefficients ---------------------------------------------------
+ * Replaces philtorch.lpv.linear_recurrence (philtorch/lpv/recur.py:20-101, pure PyTorch in the
+ * reference) and the N = 1 case of op philtorch::recurN (philtorch/csrc/host_recurN.cpp:236-281).
+ * a: (B,T) if a_batched else (T,). */
+int ptb_lpv_recur_fwd(int dtype, int64_t B, int64_t T, const void* a, int a_batched, const void* zi,
+                      int zi_batched, const void* x, void* y, void* zf, void* workspace,
+                      int64_t workspace_bytes, uint32_t* status, ptb_stream_t stream);
+
+/* Fused adjoint; replaces MatrixRecurrence.backward with M = 1 (philtorch/lpv/ssm.py:64-99),
+ * which materialises transposed, rolled and flipped copies of the coefficients.
+ *   g[t] = a[t+1]*g[t+1] + gy[t];  grad_x = g;  grad_a[b,t] = g[t]*y[t-1];  grad_zi = a[0]*g[0].
+ * grad_a: optional, always (B,T) (per row; a caller with shared coefficients sums over rows). */
+int ptb_lpv_recur_bwd(int dtype, int64_t B, int64_t T, const void* a, int a_batched, const void* zi,
+                      int zi_batched, const void* y, const void* gy, const void* g_in, void* grad_x,
+                      void* grad_a, void* grad_zi, void* workspace, int64_t workspace_bytes,
+                      uint32_t* status, ptb_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PHILTORCH_B200_H */

@@ -1,0 +1,122 @@
+"""ctypes binding of ``libphiltorch_b200.so`` (the C ABI declared in include/philtorch_b200.h).
+
+There is no CPU fallback: if the library is missing the import fails, and every wrapper
+raises for non-CUDA tensors.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libphiltorch_b200.so")
+
+PTB_F32, PTB_F64 = 0, 1
+_DTYPES = {torch.float32: PTB_F32, torch.float64: PTB_F64}
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(
+        f"{LIB_PATH} is missing: build it with `python -m philtorch_b200.build` "
+        "(needs nvcc; philtorch_b200 has no CPU or pure-PyTorch fallback)")
+
+lib = ctypes.CDLL(LIB_PATH)
+
+_vp, _i64, _i32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int
+_tail = [_vp, _i64, _vp, _vp]  # workspace, workspace_bytes, status, stream
+
+lib.ptb_version.restype = ctypes.c_char_p
+lib.ptb_error_string.restype = ctypes.c_char_p
+lib.ptb_error_string.argtypes = [_i32]
+lib.ptb_last_cuda_error.restype = _i32
+lib.ptb_workspace_bytes.restype = _i64
+lib.ptb_workspace_bytes.argtypes = [_i64, _i64]
+lib.ptb_read_status.argtypes = [_vp, _vp, ctypes.POINTER(ctypes.c_uint32)]
+
+_fo_fwd = [_i32, _i64, _i64, _vp, _i32, _vp, _i32, _vp, _vp, _vp] + _tail
+_fo_bwd = [_i32, _i64, _i64, _vp, _i32, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp] + _tail
+for _n in ("ptb_lti_recur_fwd", "ptb_lpv_recur_fwd"):
+    getattr(lib, _n).argtypes = _fo_fwd
+    getattr(lib, _n).restype = _i32
+for _n in ("ptb_lti_recur_bwd", "ptb_lpv_recur_bwd"):
+    getattr(lib, _n).argtypes = _fo_bwd
+    getattr(lib, _n).restype = _i32
+
+_status: dict[int, torch.Tensor] = {}
+
+ERROR_BITS = {1: "look-back wait expired", 2: "tile load wait expired", 4: "tile drain wait expired"}
+
+
+def dtype_code(t: torch.Tensor) -> int:
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        raise RuntimeError(f"philtorch_b200 kernels support float32 and float64, got {t.dtype}") from None
+
+
+def require_cuda(*tensors: torch.Tensor) -> torch.device:
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise RuntimeError("philtorch_b200 runs on CUDA tensors only (there is no CPU path); "
+                               f"got a tensor on {t.device}")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise RuntimeError(f"all tensors must be on the same device, got {dev} and {t.device}")
+    return dev
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    s = _status.get(idx)
+    if s is None:
+        s = torch.zeros(1, dtype=torch.int32, device=device)
+        _status[idx] = s
+    return s
+
+
+def workspace(B: int, T: int, device: torch.device) -> torch.Tensor:
+    return torch.empty(lib.ptb_workspace_bytes(B, T), dtype=torch.uint8, device=device)
+
+
+def ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        msg = lib.ptb_error_string(rc).decode()
+        if rc == 3:
+            msg += f" (cudaError {lib.ptb_last_cuda_error()})"
+        raise RuntimeError(f"{what}: {msg}")
+
+
+def call(fn, device: torch.device, B: int, T: int, *args) -> None:
+    """Runs ``fn(*args, workspace, bytes, status, stream)`` on ``device``'s current stream."""
+    ws = workspace(B, T, device)
+    st = status_word(device)
+    if device.index is not None and device.index != torch.cuda.current_device():
+        with torch.cuda.device(device):
+            rc = fn(*args, ws.data_ptr(), ws.numel(), st.data_ptr(),
+                    torch.cuda.current_stream(device).cuda_stream)
+    else:
+        rc = fn(*args, ws.data_ptr(), ws.numel(), st.data_ptr(),
+                torch.cuda.current_stream(device).cuda_stream)
+    check(rc, fn.__name__)
+
+
+def check_errors(device=None) -> None:
+    """Synchronises and raises if a kernel reported an expired device-side wait since the
+    last check (results of such a launch are invalid)."""
+    for idx, st in list(_status.items()):
+        if device is not None and torch.device(device).index not in (None, idx):
+            continue
+        v = int(st.item())
+        if v:
+            st.zero_()
+            names = [n for b, n in ERROR_BITS.items() if v & b]
+            raise RuntimeError(f"philtorch_b200 kernel error on cuda:{idx}: {', '.join(names)}")

@@ -1,0 +1,288 @@
+// Scan-engine policies for the scalar first-order recurrence
+//     y[t] = a[t] * y[t-1] + x[t],   y[-1] = zi
+// and its adjoint
+//     g[t] = gy[t] + c[t+1],  c[t] = a[t] * g[t],  c[T] = g_in (0 unless the row continues to the right)
+//     grad_x = g,  grad_a[t] = g[t] * y[t-1],  grad_zi = c[0].
+// LPV = true : a is per sample, (B,T) or (T,) (row stride 0)
+// LPV = false: a is per row, (B,) or a single value (row stride 0); grad_a is a sum over time,
+//              emitted as one partial per tile and reduced by reduce_partials_kernel.
+#pragma once
+#include "scan_engine.cuh"
+
+namespace ptb {
+
+template <class S, int N_>
+struct Pod {
+  static constexpr int N = N_;
+  S v[N_];
+};
+
+template <class S> struct Vec16;
+template <> struct Vec16<float> { using type = float4; static constexpr int V = 4; };
+template <> struct Vec16<double> { using type = double2; static constexpr int V = 2; };
+
+template <class S, int V> struct VecIO;
+template <> struct VecIO<float, 4> {
+  static __device__ __forceinline__ void ld(const unsigned char* p, float* r) {
+    const float4 q = *reinterpret_cast<const float4*>(p);
+    r[0] = q.x; r[1] = q.y; r[2] = q.z; r[3] = q.w;
+  }
+  static __device__ __forceinline__ void st(unsigned char* p, const float* r) {
+    *reinterpret_cast<float4*>(p) = make_float4(r[0], r[1], r[2], r[3]);
+  }
+};
+template <> struct VecIO<double, 2> {
+  static __device__ __forceinline__ void ld(const unsigned char* p, double* r) {
+    const double2 q = *reinterpret_cast<const double2*>(p);
+    r[0] = q.x; r[1] = q.y;
+  }
+  static __device__ __forceinline__ void st(unsigned char* p, const double* r) {
+    *reinterpret_cast<double2*>(p) = make_double2(r[0], r[1]);
+  }
+};
+
+// Algebra of scalar affine maps m(h) = P*h + s, stored as v = {P, s}.
+template <class S>
+struct ScalarAffine {
+  using Map = Pod<S, 2>;
+  using State = Pod<S, 1>;
+  static __device__ __forceinline__ Map identity() { Map m; m.v[0] = S(1); m.v[1] = S(0); return m; }
+  static __device__ __forceinline__ State zero_state() { State s; s.v[0] = S(0); return s; }
+  static __device__ __forceinline__ Map const_map(const State& s) { Map m; m.v[0] = S(0); m.v[1] = s.v[0]; return m; }
+  // apply `first`, then `second`
+  static __device__ __forceinline__ Map compose(const Map& first, const Map& second) {
+    Map m;
+    m.v[0] = second.v[0] * first.v[0];
+    m.v[1] = second.v[0] * first.v[1] + second.v[1];
+    return m;
+  }
+  static __device__ __forceinline__ State apply(const Map& m, const State& s) {
+    State r; r.v[0] = m.v[0] * s.v[0] + m.v[1]; return r;
+  }
+};
+
+// ------------------------------------------------------------------------------------ forward
+template <class S>
+struct FoFwdParams {
+  const S* a; int64_t a_row_stride;   // LPV: T or 0; LTI: 1 or 0
+  const S* zi; int64_t zi_stride;     // 1, or 0 when one value is shared by all rows
+  const S* x;
+  S* y;
+  S* zf;                              // optional (B,) final state
+  int64_t T;
+};
+
+template <class S, int CH, int STAGES_, int MIN_CTAS_, bool LPV>
+struct FoFwd : ScalarAffine<S> {
+  using Alg = ScalarAffine<S>;
+  using typename Alg::Map;
+  using typename Alg::State;
+  using Partial = Pod<S, 1>;
+  using Params = FoFwdParams<S>;
+  using Scalar = S;
+  static constexpr int V = Vec16<S>::V;
+  static constexpr int NT = 256;
+  static constexpr int SPT = V * CH;
+  static constexpr int TILE = NT * SPT;
+  static constexpr int STAGES = STAGES_;
+  static constexpr int MIN_CTAS = MIN_CTAS_;
+  static constexpr bool REVERSE = false;
+  static constexpr bool HAS_PARTIAL = false;
+  static constexpr int SLOT = TILE * (int)sizeof(S);
+  static constexpr int X_OFF = 0;
+  static constexpr int A_OFF = SLOT;
+  static constexpr int STAGE_BYTES = LPV ? 2 * SLOT : SLOT;
+  // bytes per sample that must be 16-byte granular for the bulk path
+  static constexpr int ALIGN_ELEMS = V;
+
+  static __device__ __forceinline__ void plan(const Params& p, bool, int64_t row, int64_t t0, int nvalid,
+                                              IoPlan& io) {
+    const uint32_t bytes = (uint32_t)nvalid * sizeof(S);
+    io.load(X_OFF, p.x + row * p.T + t0, bytes);
+    if (LPV) io.load(A_OFF, p.a + row * p.a_row_stride + t0, bytes);
+    io.store(X_OFF, p.y + row * p.T + t0, bytes);
+  }
+  static __device__ __forceinline__ State row_init(const Params& p, int64_t row) {
+    State s; s.v[0] = __ldg(p.zi + row * p.zi_stride); return s;
+  }
+  static __device__ __forceinline__ void row_final(const Params& p, int64_t row, const State& s) {
+    if (p.zf) p.zf[row] = s.v[0];
+  }
+
+  struct Thread {
+    S x[SPT];
+    S a[LPV ? SPT : 1];
+    int nv;
+    __device__ __forceinline__ S coef(int j) const { return LPV ? a[j] : (j < nv ? a[0] : S(1)); }
+    __device__ __forceinline__ void load(const Params& p, const unsigned char* stage, int tpos, int64_t row,
+                                         int64_t, int nvalid) {
+      const int p0 = tpos * SPT;
+      nv = nvalid - p0;
+      nv = nv < 0 ? 0 : (nv > SPT ? SPT : nv);
+      const unsigned char* px = stage + X_OFF + (size_t)p0 * sizeof(S);
+#pragma unroll
+      for (int c = 0; c < CH; ++c) VecIO<S, V>::ld(px + 16 * c, &x[c * V]);
+      if (LPV) {
+        const unsigned char* pa = stage + A_OFF + (size_t)p0 * sizeof(S);
+#pragma unroll
+        for (int c = 0; c < CH; ++c) VecIO<S, V>::ld(pa + 16 * c, &a[c * V]);
+      } else {
+        a[0] = __ldg(p.a + row * p.a_row_stride);
+      }
+      if (nv < SPT) {
+#pragma unroll
+        for (int j = 0; j < SPT; ++j)
+          if (j >= nv) { x[j] = S(0); if (LPV) a[j] = S(1); }
+      }
+    }
+    __device__ __forceinline__ Map aggregate() const {
+      S P = S(1), s = S(0);
+#pragma unroll
+      for (int j = 0; j < SPT; ++j) { const S aj = coef(j); s = aj * s + x[j]; P *= aj; }
+      Map m; m.v[0] = P; m.v[1] = s; return m;
+    }
+    __device__ __forceinline__ Partial finish(const Params&, const State& in, unsigned char* stage, int tpos, int) {
+      S h = in.v[0];
+#pragma unroll
+      for (int j = 0; j < SPT; ++j) { h = coef(j) * h + x[j]; x[j] = h; }
+      unsigned char* px = stage + X_OFF + (size_t)tpos * SPT * sizeof(S);
+#pragma unroll
+      for (int c = 0; c < CH; ++c) VecIO<S, V>::st(px + 16 * c, &x[c * V]);
+      Partial r; r.v[0] = S(0); return r;
+    }
+  };
+};
+
+// ------------------------------------------------------------------------------------ adjoint
+template <class S>
+struct FoBwdParams {
+  const S* a; int64_t a_row_stride;
+  const S* zi; int64_t zi_stride;
+  const S* y;        // forward output, needed only when grad_a is wanted
+  const S* gy;       // upstream gradient
+  const S* g_in;     // optional (B,): adjoint state entering from the right of the last sample
+  S* grad_x;
+  S* grad_a;         // LPV: (B,T) per-sample; LTI: unused here (partials go to the workspace)
+  S* grad_zi;        // optional (B,)
+  int64_t T;
+  int want_ga;
+};
+
+template <class S, int CH, int STAGES_, int MIN_CTAS_, bool LPV>
+struct FoBwd : ScalarAffine<S> {
+  using Alg = ScalarAffine<S>;
+  using typename Alg::Map;
+  using typename Alg::State;
+  using Partial = Pod<S, 1>;
+  using Params = FoBwdParams<S>;
+  using Scalar = S;
+  static constexpr int V = Vec16<S>::V;
+  static constexpr int NT = 256;
+  static constexpr int SPT = V * CH;
+  static constexpr int TILE = NT * SPT;
+  static constexpr int STAGES = STAGES_;
+  static constexpr int MIN_CTAS = MIN_CTAS_;
+  static constexpr bool REVERSE = true;
+  static constexpr bool HAS_PARTIAL = !LPV;
+  static constexpr int SLOT = TILE * (int)sizeof(S);
+  static constexpr int G_OFF = 0;                       // gy in, grad_x out
+  static constexpr int Y_OFF = SLOT;                    // y in, grad_a out (LPV)
+  static constexpr int HALO_OFF = 2 * SLOT;             // 16 bytes ending with y[t0-1]
+  static constexpr int A_OFF = 2 * SLOT + 128;          // a in (LPV)
+  static constexpr int STAGE_BYTES = (LPV ? 3 * SLOT : 2 * SLOT) + 128;
+  static constexpr int ALIGN_ELEMS = V;
+
+  static __device__ __forceinline__ void plan(const Params& p, bool bulk, int64_t row, int64_t t0, int nvalid,
+                                              IoPlan& io) {
+    const uint32_t bytes = (uint32_t)nvalid * sizeof(S);
+    io.load(G_OFF, p.gy + row * p.T + t0, bytes);
+    if (LPV) io.load(A_OFF, p.a + row * p.a_row_stride + t0, bytes);
+    if (p.want_ga) {
+      io.load(Y_OFF, p.y + row * p.T + t0, bytes);
+      if (t0 > 0) {
+        if (bulk) io.load(HALO_OFF, p.y + row * p.T + t0 - V, 16);
+        else io.load(HALO_OFF + 16 - (int)sizeof(S), p.y + row * p.T + t0 - 1, sizeof(S));
+      }
+    }
+    io.store(G_OFF, p.grad_x + row * p.T + t0, bytes);
+    if (LPV && p.want_ga) io.store(Y_OFF, p.grad_a + row * p.T + t0, bytes);
+  }
+  static __device__ __forceinline__ State row_init(const Params& p, int64_t row) {
+    State s; s.v[0] = p.g_in ? __ldg(p.g_in + row) : S(0); return s;
+  }
+  static __device__ __forceinline__ void row_final(const Params& p, int64_t row, const State& s) {
+    if (p.grad_zi) p.grad_zi[row] = s.v[0];
+  }
+
+  struct Thread {
+    S g[SPT];
+    S a[LPV ? SPT : 1];
+    S y[SPT];
+    S yprev;
+    int nv;
+    __device__ __forceinline__ S coef(int j) const { return LPV ? a[j] : (j < nv ? a[0] : S(1)); }
+    __device__ __forceinline__ void load(const Params& p, const unsigned char* stage, int tpos, int64_t row,
+                                         int64_t t0, int nvalid) {
+      const int p0 = tpos * SPT;
+      nv = nvalid - p0;
+      nv = nv < 0 ? 0 : (nv > SPT ? SPT : nv);
+      const unsigned char* pg = stage + G_OFF + (size_t)p0 * sizeof(S);
+#pragma unroll
+      for (int c = 0; c < CH; ++c) VecIO<S, V>::ld(pg + 16 * c, &g[c * V]);
+      if (LPV) {
+        const unsigned char* pa = stage + A_OFF + (size_t)p0 * sizeof(S);
+#pragma unroll
+        for (int c = 0; c < CH; ++c) VecIO<S, V>::ld(pa + 16 * c, &a[c * V]);
+      } else {
+        a[0] = __ldg(p.a + row * p.a_row_stride);
+      }
+      yprev = S(0);
+      if (p.want_ga) {
+        const unsigned char* py = stage + Y_OFF + (size_t)p0 * sizeof(S);
+#pragma unroll
+        for (int c = 0; c < CH; ++c) VecIO<S, V>::ld(py + 16 * c, &y[c * V]);
+        if (tpos > 0) yprev = *reinterpret_cast<const S*>(py - sizeof(S));
+        else if (t0 > 0) yprev = *reinterpret_cast<const S*>(stage + HALO_OFF + 16 - sizeof(S));
+        else yprev = __ldg(p.zi + row * p.zi_stride);
+      }
+      if (nv < SPT) {
+#pragma unroll
+        for (int j = 0; j < SPT; ++j)
+          if (j >= nv) { g[j] = S(0); y[j] = S(0); if (LPV) a[j] = S(1); }
+      }
+    }
+    // map over c (time descending): c_out = a_j * (gy_j + c_in)
+    __device__ __forceinline__ Map aggregate() const {
+      S P = S(1), s = S(0);
+#pragma unroll
+      for (int j = SPT - 1; j >= 0; --j) { const S aj = coef(j); s = aj * (s + g[j]); P *= aj; }
+      Map m; m.v[0] = P; m.v[1] = s; return m;
+    }
+    __device__ __forceinline__ Partial finish(const Params& p, const State& in, unsigned char* stage, int tpos, int) {
+      S c = in.v[0];
+      S acc = S(0);
+#pragma unroll
+      for (int j = SPT - 1; j >= 0; --j) {
+        const S gj = g[j] + c;
+        g[j] = gj;
+        c = coef(j) * gj;
+        if (p.want_ga) {
+          const S yp = j > 0 ? y[j - 1] : yprev;
+          if (LPV) y[j] = gj * yp;
+          else if (j < nv) acc += gj * yp;
+        }
+      }
+      unsigned char* pg = stage + G_OFF + (size_t)tpos * SPT * sizeof(S);
+#pragma unroll
+      for (int c2 = 0; c2 < CH; ++c2) VecIO<S, V>::st(pg + 16 * c2, &g[c2 * V]);
+      if (LPV && p.want_ga) {
+        unsigned char* py = stage + Y_OFF + (size_t)tpos * SPT * sizeof(S);
+#pragma unroll
+        for (int c2 = 0; c2 < CH; ++c2) VecIO<S, V>::st(py + 16 * c2, &y[c2 * V]);
+      }
+      Partial r; r.v[0] = acc; return r;
+    }
+  };
+};
+
+}  // namespace ptb

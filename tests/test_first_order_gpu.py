@@ -1,0 +1,183 @@
+"""GPU parity of the first-order kernels (through the torch ops -> ctypes -> C ABI) against the
+CPU oracle and the golden vectors made by the reference.  Tolerance: max|out-ref|/max|ref|
+<= 1e-4 (fp32), <= 1e-10 (fp64)."""
+import pytest
+import torch
+
+import philtorch_b200 as ptb
+from philtorch_b200 import workloads
+from philtorch_b200.autograd import LPVRecurrence, LTIRecurrence
+from conftest import load_golden, rel_err, tol
+from oracle import cport
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+DT = {"f32": torch.float32, "f64": torch.float64}
+
+# tile sizes are 3072 (fp32) / 1536 (fp64) samples: cover below / at / above one and several tiles,
+# and lengths that are not a multiple of 16 bytes (plain-load path)
+LENGTHS = [1, 2, 3, 4, 5, 31, 32, 33, 101, 1535, 1536, 1537, 3071, 3072, 3073, 4096, 6148, 9216, 12289, 40000]
+
+
+def _cuda(*ts):
+    return [t.to(DEV) for t in ts]
+
+
+def _run_fo(kind, a, zi, x, gy):
+    fn = LTIRecurrence if kind == "lti" else LPVRecurrence
+    a_, zi_, x_ = (t.to(DEV).requires_grad_() for t in (a, zi, x))
+    y = fn.apply(a_, zi_, x_)
+    ga, gzi, gx = torch.autograd.grad(y, (a_, zi_, x_), gy.to(DEV))
+    ptb.check_errors()
+    return y, ga, gzi, gx
+
+
+def _check_fo(kind, a, zi, x, gy, dtype):
+    t = tol(dtype)
+    y, ga, gzi, gx = _run_fo(kind, a, zi, x, gy)
+    if kind == "lti":
+        y_ref = cport.lti_recur(a, zi, x)
+        ga_ref, gzi_ref, gx_ref = cport.lti_recur_bwd(a, zi, y_ref, gy)
+    else:
+        y_ref = cport.recur1(a, zi, x)
+        ga_ref, gzi_ref, gx_ref = cport.recur1_bwd(a, zi, y_ref, gy)
+    assert rel_err(y, y_ref) <= t
+    assert rel_err(gx, gx_ref) <= t
+    assert rel_err(gzi, gzi_ref) <= t
+    assert rel_err(ga, ga_ref.reshape(ga.shape)) <= t
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+@pytest.mark.parametrize("T", LENGTHS)
+@pytest.mark.parametrize("B", [1, 3])
+def test_lpv_lengths(dtype, T, B):
+    g = torch.Generator().manual_seed(T * 7 + B)
+    a = (torch.rand(B, T, generator=g, dtype=torch.float64) * 1.98 - 0.99).to(dtype)
+    zi = torch.randn(B, generator=g, dtype=torch.float64).to(dtype)
+    x = torch.randn(B, T, generator=g, dtype=torch.float64).to(dtype)
+    gy = torch.randn(B, T, generator=g, dtype=torch.float64).to(dtype)
+    _check_fo("lpv", a, zi, x, gy, dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+@pytest.mark.parametrize("T", LENGTHS)
+@pytest.mark.parametrize("mode", ["batched", "shared1", "scalar"])
+def test_lti_lengths(dtype, T, mode):
+    B = 3
+    g = torch.Generator().manual_seed(T * 11 + len(mode))
+    a = (torch.rand(B if mode == "batched" else 1, generator=g, dtype=torch.float64) * 1.9 - 0.95).to(dtype)
+    if mode == "scalar":
+        a = a[0]
+    zi = torch.randn(B, generator=g, dtype=torch.float64).to(dtype)
+    x = torch.randn(B, T, generator=g, dtype=torch.float64).to(dtype)
+    gy = torch.randn(B, T, generator=g, dtype=torch.float64).to(dtype)
+    _check_fo("lti", a, zi, x, gy, dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+def test_lpv_shared_coefficients(dtype):
+    B, T = 5, 7000
+    g = torch.Generator().manual_seed(3)
+    a = (torch.rand(T, generator=g, dtype=torch.float64) * 1.98 - 0.99).to(dtype)
+    zi = torch.randn(B, generator=g, dtype=torch.float64).to(dtype)
+    x = torch.randn(B, T, generator=g, dtype=torch.float64).to(dtype)
+    gy = torch.randn(B, T, generator=g, dtype=torch.float64).to(dtype)
+    _check_fo("lpv", a, zi, x, gy, dtype)
+
+
+@pytest.mark.parametrize("tag", ["f32", "f64"])
+@pytest.mark.parametrize("mode", ["batched", "shared1", "scalar"])
+def test_lti_golden(tag, mode):
+    g = load_golden(f"lti_recur_{mode}_{tag}")
+    t = tol(DT[tag])
+    y, ga, gzi, gx = _run_fo("lti", g["a"], g["zi"], g["x"], g["gy"])
+    assert rel_err(y, g["y"]) <= t
+    assert rel_err(ga, g["grad_a"]) <= t
+    assert rel_err(gzi, g["grad_zi"]) <= t
+    assert rel_err(gx, g["grad_x"]) <= t
+
+
+@pytest.mark.parametrize("tag", ["f32", "f64"])
+@pytest.mark.parametrize("mode", ["batched", "shared"])
+def test_lpv_golden(tag, mode):
+    g = load_golden(f"lpv_recur1_{mode}_{tag}")
+    t = tol(DT[tag])
+    y, ga, gzi, gx = _run_fo("lpv", g["a"], g["zi"], g["x"], g["gy"])
+    assert rel_err(y, g["y"]) <= t
+    assert rel_err(y, g["y_python_loop"]) <= t
+    assert rel_err(ga, g["grad_a"]) <= t
+    assert rel_err(gzi, g["grad_zi"]) <= t
+    assert rel_err(gx, g["grad_x"]) <= t
+
+
+def test_config_goldens():
+    g = load_golden("config1_small")
+    w = workloads.lti_first_order(B=8, T=4096)
+    y, ga, _, gx = _run_fo("lti", w["a"], w["zi"], w["x"], w["gy"])
+    assert rel_err(y, g["y"]) <= 1e-4 and rel_err(ga, g["grad_a"]) <= 1e-4 and rel_err(gx, g["grad_x"]) <= 1e-4
+    g = load_golden("config2_small")
+    w = workloads.lpv_first_order(B=4, T=8192)
+    y, ga, gzi, gx = _run_fo("lpv", w["a"], w["zi"], w["x"], w["gy"])
+    assert rel_err(y, g["y"]) <= 1e-4 and rel_err(ga, g["grad_a"]) <= 1e-4
+    assert rel_err(gzi, g["grad_zi"]) <= 1e-4 and rel_err(gx, g["grad_x"]) <= 1e-4
+    g = load_golden("config5_small")
+    w = workloads.long_first_order(B=2, T=16384)
+    y, ga, _, gx = _run_fo("lpv", w["a"], w["zi"], w["x"], w["gy"])
+    assert rel_err(y, g["y"]) <= 1e-4 and rel_err(ga, g["grad_a"]) <= 1e-4 and rel_err(gx, g["grad_x"]) <= 1e-4
+
+
+@pytest.mark.parametrize("kind,B,T", [("lpv", 64, 1 << 16), ("lti", 64, 1 << 16), ("lpv", 2, 1 << 21),
+                                      ("lti", 1, 1 << 21), ("lpv", 300, 9000)])
+def test_many_tiles(kind, B, T):
+    """Enough tiles to keep every SM busy and make the look-back span several predecessors."""
+    dtype = torch.float32
+    w = workloads.lpv_first_order(B=B, T=T) if kind == "lpv" else workloads.lti_first_order(B=B, T=T)
+    zi = torch.randn(B, generator=torch.Generator().manual_seed(5))
+    _check_fo(kind, w["a"], zi, w["x"], w["gy"], dtype)
+
+
+def test_slowly_decaying_long_row():
+    """a close to 1 (config-5 distribution): carries travel far, in fp32 and fp64."""
+    for dtype in (torch.float32, torch.float64):
+        w = workloads.long_first_order(B=2, T=1 << 20, dtype=dtype)
+        _check_fo("lpv", w["a"], w["zi"], w["x"], w["gy"], dtype)
+
+
+def test_public_api_and_errors():
+    g = load_golden("lti_linear_recurrence_f64")
+    a, zi, x = _cuda(g["a"], g["zi"], g["x"])
+    assert rel_err(ptb.lti.linear_recurrence(a, zi, x), g["y"]) <= 1e-10
+    assert rel_err(ptb.lti.linear_recurrence(a, zi, x, unroll_factor=7), g["y_unrolled"]) <= 1e-10
+    assert rel_err(ptb.lti.linear_recurrence(a[0], zi[0], x), g["y_scalar_a"]) <= 1e-10
+    with pytest.raises(ValueError):
+        ptb.lti.linear_recurrence(a[:2], zi, x)
+    with pytest.raises(ValueError):
+        ptb.lti.linear_recurrence(a, zi, x, unroll_factor=0)
+    with pytest.raises(RuntimeError):
+        ptb.lti.linear_recurrence(a.float(), zi, x)          # dtype mismatch
+    with pytest.raises(RuntimeError):
+        ptb.lti.linear_recurrence(a.cpu(), zi.cpu(), x.cpu())  # no CPU path
+    with pytest.raises(RuntimeError):
+        ptb.lti.linear_recurrence(a.half(), zi.half(), x.half())
+    # empty inputs
+    assert ptb.lti.linear_recurrence(a, zi, x[:, :0]).shape == (4, 0)
+    assert ptb.lpv.linear_recurrence(x[:0], zi[:0], x[:0]).shape == (0, 130)
+
+
+def test_non_contiguous_inputs():
+    g = torch.Generator().manual_seed(9)
+    B, T = 4, 5000
+    a = (torch.rand(T, B, generator=g) * 1.9 - 0.95).t()       # (B,T) view, column-major
+    x = torch.randn(B, 2 * T, generator=g)[:, ::2]
+    zi = torch.randn(2 * B, generator=g)[::2]
+    y = ptb.lpv.linear_recurrence(a.to(DEV), zi.to(DEV), x.to(DEV))
+    assert rel_err(y, cport.recur1(a, zi, x)) <= 1e-4
+
+
+def test_repeatable():
+    w = workloads.lpv_first_order(B=32, T=1 << 16)
+    a, zi, x = _cuda(w["a"], w["zi"], w["x"])
+    y1 = ptb.lpv.linear_recurrence(a, zi, x)
+    y2 = ptb.lpv.linear_recurrence(a, zi, x)
+    assert rel_err(y1, y2) <= 1e-6   # look-back association may differ in the last bits only
+    ptb.check_errors()
