@@ -11,7 +11,8 @@ import os
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libphiltorch_b200.so")
+# PHILTORCH_B200_LIB: load another build of the same library (kernel tuning experiments)
+LIB_PATH = os.environ.get("PHILTORCH_B200_LIB") or os.path.join(_HERE, "libphiltorch_b200.so")
 
 PTB_F32, PTB_F64 = 0, 1
 _DTYPES = {torch.float32: PTB_F32, torch.float64: PTB_F64}

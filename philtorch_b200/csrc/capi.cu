@@ -9,7 +9,7 @@
 namespace ptb {
 
 constexpr int kMinTile = 512;        // every policy's TILE is at least this (workspace bound)
-constexpr int kTileRecordBytes = 128;   // flag + Map + State + Partial, generous upper bound
+constexpr int kTileRecordBytes = 160;   // look-back record + Partial, generous upper bound
 constexpr int kHeaderBytes = 256;
 constexpr int kMaxDevices = 64;
 
@@ -28,14 +28,12 @@ static inline int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * 
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 struct WsLayout {
-  int64_t flags_off, agg_off, incl_off, part_off, total;
+  int64_t slots_off, part_off, total;
 };
-static WsLayout ws_layout(int64_t ntiles, int map_bytes, int state_bytes, int part_bytes) {
+static WsLayout ws_layout(int64_t ntiles, int slot_words, int part_bytes) {
   WsLayout l;
-  l.flags_off = kHeaderBytes;
-  l.agg_off = l.flags_off + align_up(4 * ntiles, 256);
-  l.incl_off = l.agg_off + align_up((int64_t)map_bytes * ntiles, 256);
-  l.part_off = l.incl_off + align_up((int64_t)state_bytes * ntiles, 256);
+  l.slots_off = kHeaderBytes;
+  l.part_off = l.slots_off + align_up((int64_t)slot_words * 8 * ntiles, 256);
   l.total = l.part_off + align_up((int64_t)part_bytes * ntiles, 256);
   return l;
 }
@@ -52,25 +50,21 @@ static int launch_scan(const typename P::Params& prm, int64_t B, int64_t T, bool
                        int64_t workspace_bytes, uint32_t* status, cudaStream_t st, void** partial_out,
                        int64_t* nchunks_out) {
   static_assert(P::TILE >= kMinTile, "workspace bound assumes TILE >= kMinTile");
-  static_assert(sizeof(typename P::Map) + sizeof(typename P::State) + sizeof(typename P::Partial) + 4 <=
-                    kTileRecordBytes,
+  static_assert(P::SLOT_WORDS * 8 + sizeof(typename P::Partial) <= kTileRecordBytes,
                 "per-tile record too large");
   static_assert(P::STAGE_BYTES % 128 == 0, "stages must stay 128-byte aligned");
   const int64_t nchunks = (T + P::TILE - 1) / P::TILE;
   const int64_t ntiles = B * nchunks;
   if (ntiles >= 0xFFFFFFFEll || B >= 0xFFFFFFFFll) return PTB_ERR_TOO_LARGE;
-  const WsLayout l = ws_layout(ntiles, sizeof(typename P::Map), sizeof(typename P::State),
-                               sizeof(typename P::Partial));
+  const WsLayout l = ws_layout(ntiles, P::SLOT_WORDS, sizeof(typename P::Partial));
   if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255u) || workspace_bytes < l.total)
     return PTB_ERR_WORKSPACE;
   char* w = static_cast<char*>(workspace);
-  PTB_CUDA(cudaMemsetAsync(w, 0, (size_t)l.agg_off, st));   // header + flags
+  PTB_CUDA(cudaMemsetAsync(w, 0, (size_t)l.part_off, st));   // header + look-back records
   Workspace ws;
   ws.ticket = reinterpret_cast<uint32_t*>(w);
   ws.error = status ? status : reinterpret_cast<uint32_t*>(w + 4);
-  ws.flags = reinterpret_cast<uint32_t*>(w + l.flags_off);
-  ws.agg = w + l.agg_off;
-  ws.incl = w + l.incl_off;
+  ws.slots = reinterpret_cast<uint64_t*>(w + l.slots_off);
   ws.partial = w + l.part_off;
   if (partial_out) *partial_out = ws.partial;
   if (nchunks_out) *nchunks_out = nchunks;
@@ -83,7 +77,7 @@ static int launch_scan(const typename P::Params& prm, int64_t B, int64_t T, bool
   if (!cache.ready[dev]) {
     PTB_CUDA(cudaFuncSetAttribute(scan_kernel<P>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     int occ = 0;
-    PTB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, scan_kernel<P>, P::NT + 32, smem));
+    PTB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, scan_kernel<P>, P::NT + 32 * (P::STAGES + 1), smem));
     int sms = 0;
     PTB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     cache.ctas_per_sm[dev] = std::max(occ, 1);
@@ -92,7 +86,7 @@ static int launch_scan(const typename P::Params& prm, int64_t B, int64_t T, bool
   }
   const int64_t resident = (int64_t)cache.sms[dev] * cache.ctas_per_sm[dev];
   const unsigned grid = (unsigned)std::min<int64_t>(ntiles, resident);
-  scan_kernel<P><<<grid, P::NT + 32, smem, st>>>(prm, ws, (uint32_t)B, T, (uint32_t)nchunks, (uint32_t)ntiles,
+  scan_kernel<P><<<grid, P::NT + 32 * (P::STAGES + 1), smem, st>>>(prm, ws, (uint32_t)B, T, (uint32_t)nchunks, (uint32_t)ntiles,
                                                 bulk ? 1 : 0);
   PTB_CUDA(cudaGetLastError());
   return PTB_OK;
@@ -159,8 +153,19 @@ static int launch_reduce(const void* part, void* out, int64_t B, int64_t nchunks
 
 // ---------------------------------------------------------------------------- first order
 // Tile geometry: 3 x 16 bytes per thread and array (odd => bank-conflict-free strided access).
-template <class S, bool LPV> using FoFwdP = FoFwd<S, 3, 3, 3, LPV>;
-template <class S, bool LPV> using FoBwdP = FoBwd<S, 3, 3, 2, LPV>;
+// (16-byte units per thread and array, stages, CTAs per SM); overridable for tuning experiments
+#ifndef PTB_FO_FWD_CH
+#define PTB_FO_FWD_CH 3
+#define PTB_FO_FWD_STAGES 3
+#define PTB_FO_FWD_CTAS 3
+#endif
+#ifndef PTB_FO_BWD_CH
+#define PTB_FO_BWD_CH 3
+#define PTB_FO_BWD_STAGES 3
+#define PTB_FO_BWD_CTAS 2
+#endif
+template <class S, bool LPV> using FoFwdP = FoFwd<S, PTB_FO_FWD_CH, PTB_FO_FWD_STAGES, PTB_FO_FWD_CTAS, LPV>;
+template <class S, bool LPV> using FoBwdP = FoBwd<S, PTB_FO_BWD_CH, PTB_FO_BWD_STAGES, PTB_FO_BWD_CTAS, LPV>;
 
 template <class S, bool LPV>
 static int fo_fwd(int64_t B, int64_t T, const void* a, int a_batched, const void* zi, int zi_batched,
@@ -232,7 +237,7 @@ int ptb_last_cuda_error(void) { return g_last_cuda_error; }
 int64_t ptb_workspace_bytes(int64_t B, int64_t T) {
   if (B <= 0 || T <= 0) return kHeaderBytes;
   const int64_t ntiles = B * ((T + kMinTile - 1) / kMinTile);
-  return kHeaderBytes + align_up(4 * ntiles, 256) + 3 * 256 + (int64_t)kTileRecordBytes * ntiles;
+  return kHeaderBytes + 2 * 256 + (int64_t)kTileRecordBytes * ntiles;
 }
 
 int ptb_read_status(const uint32_t* status, ptb_stream_t stream, uint32_t* host_out) {

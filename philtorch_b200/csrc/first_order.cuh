@@ -88,12 +88,11 @@ struct FoFwd : ScalarAffine<S> {
   static constexpr int MIN_CTAS = MIN_CTAS_;
   static constexpr bool REVERSE = false;
   static constexpr bool HAS_PARTIAL = false;
+  static constexpr int SLOT_WORDS = Words<Map>::W;
   static constexpr int SLOT = TILE * (int)sizeof(S);
   static constexpr int X_OFF = 0;
   static constexpr int A_OFF = SLOT;
   static constexpr int STAGE_BYTES = LPV ? 2 * SLOT : SLOT;
-  // bytes per sample that must be 16-byte granular for the bulk path
-  static constexpr int ALIGN_ELEMS = V;
 
   static __device__ __forceinline__ void plan(const Params& p, bool, int64_t row, int64_t t0, int nvalid,
                                               IoPlan& io) {
@@ -109,13 +108,13 @@ struct FoFwd : ScalarAffine<S> {
     if (p.zf) p.zf[row] = s.v[0];
   }
 
-  struct Thread {
+  struct Regs {
     S x[SPT];
     S a[LPV ? SPT : 1];
     int nv;
     __device__ __forceinline__ S coef(int j) const { return LPV ? a[j] : (j < nv ? a[0] : S(1)); }
     __device__ __forceinline__ void load(const Params& p, const unsigned char* stage, int tpos, int64_t row,
-                                         int64_t, int nvalid) {
+                                         int nvalid) {
       const int p0 = tpos * SPT;
       nv = nvalid - p0;
       nv = nv < 0 ? 0 : (nv > SPT ? SPT : nv);
@@ -135,22 +134,29 @@ struct FoFwd : ScalarAffine<S> {
           if (j >= nv) { x[j] = S(0); if (LPV) a[j] = S(1); }
       }
     }
-    __device__ __forceinline__ Map aggregate() const {
-      S P = S(1), s = S(0);
-#pragma unroll
-      for (int j = 0; j < SPT; ++j) { const S aj = coef(j); s = aj * s + x[j]; P *= aj; }
-      Map m; m.v[0] = P; m.v[1] = s; return m;
-    }
-    __device__ __forceinline__ Partial finish(const Params&, const State& in, unsigned char* stage, int tpos, int) {
-      S h = in.v[0];
-#pragma unroll
-      for (int j = 0; j < SPT; ++j) { h = coef(j) * h + x[j]; x[j] = h; }
-      unsigned char* px = stage + X_OFF + (size_t)tpos * SPT * sizeof(S);
-#pragma unroll
-      for (int c = 0; c < CH; ++c) VecIO<S, V>::st(px + 16 * c, &x[c * V]);
-      Partial r; r.v[0] = S(0); return r;
-    }
   };
+
+  static __device__ __forceinline__ Map aggregate(const Params& p, const unsigned char* stage, int tpos,
+                                                  int64_t row, int64_t, int nvalid) {
+    Regs r;
+    r.load(p, stage, tpos, row, nvalid);
+    S P = S(1), s = S(0);
+#pragma unroll
+    for (int j = 0; j < SPT; ++j) { const S aj = r.coef(j); s = aj * s + r.x[j]; P *= aj; }
+    Map m; m.v[0] = P; m.v[1] = s; return m;
+  }
+  static __device__ __forceinline__ Partial finish(const Params& p, const State& in, unsigned char* stage,
+                                                   int tpos, int64_t row, int64_t, int nvalid) {
+    Regs r;
+    r.load(p, stage, tpos, row, nvalid);
+    S h = in.v[0];
+#pragma unroll
+    for (int j = 0; j < SPT; ++j) { h = r.coef(j) * h + r.x[j]; r.x[j] = h; }
+    unsigned char* px = stage + X_OFF + (size_t)tpos * SPT * sizeof(S);
+#pragma unroll
+    for (int c = 0; c < CH; ++c) VecIO<S, V>::st(px + 16 * c, &r.x[c * V]);
+    Partial out; out.v[0] = S(0); return out;
+  }
 };
 
 // ------------------------------------------------------------------------------------ adjoint
@@ -184,13 +190,13 @@ struct FoBwd : ScalarAffine<S> {
   static constexpr int MIN_CTAS = MIN_CTAS_;
   static constexpr bool REVERSE = true;
   static constexpr bool HAS_PARTIAL = !LPV;
+  static constexpr int SLOT_WORDS = Words<Map>::W;
   static constexpr int SLOT = TILE * (int)sizeof(S);
   static constexpr int G_OFF = 0;                       // gy in, grad_x out
-  static constexpr int Y_OFF = SLOT;                    // y in, grad_a out (LPV)
+  static constexpr int Y_OFF = SLOT;                    // y in (read-only)
   static constexpr int HALO_OFF = 2 * SLOT;             // 16 bytes ending with y[t0-1]
-  static constexpr int A_OFF = 2 * SLOT + 128;          // a in (LPV)
+  static constexpr int A_OFF = 2 * SLOT + 128;          // a in, grad_a out (LPV)
   static constexpr int STAGE_BYTES = (LPV ? 3 * SLOT : 2 * SLOT) + 128;
-  static constexpr int ALIGN_ELEMS = V;
 
   static __device__ __forceinline__ void plan(const Params& p, bool bulk, int64_t row, int64_t t0, int nvalid,
                                               IoPlan& io) {
@@ -205,7 +211,7 @@ struct FoBwd : ScalarAffine<S> {
       }
     }
     io.store(G_OFF, p.grad_x + row * p.T + t0, bytes);
-    if (LPV && p.want_ga) io.store(Y_OFF, p.grad_a + row * p.T + t0, bytes);
+    if (LPV && p.want_ga) io.store(A_OFF, p.grad_a + row * p.T + t0, bytes);
   }
   static __device__ __forceinline__ State row_init(const Params& p, int64_t row) {
     State s; s.v[0] = p.g_in ? __ldg(p.g_in + row) : S(0); return s;
@@ -214,15 +220,13 @@ struct FoBwd : ScalarAffine<S> {
     if (p.grad_zi) p.grad_zi[row] = s.v[0];
   }
 
-  struct Thread {
+  struct Regs {
     S g[SPT];
     S a[LPV ? SPT : 1];
-    S y[SPT];
-    S yprev;
     int nv;
     __device__ __forceinline__ S coef(int j) const { return LPV ? a[j] : (j < nv ? a[0] : S(1)); }
     __device__ __forceinline__ void load(const Params& p, const unsigned char* stage, int tpos, int64_t row,
-                                         int64_t t0, int nvalid) {
+                                         int nvalid) {
       const int p0 = tpos * SPT;
       nv = nvalid - p0;
       nv = nv < 0 ? 0 : (nv > SPT ? SPT : nv);
@@ -236,53 +240,64 @@ struct FoBwd : ScalarAffine<S> {
       } else {
         a[0] = __ldg(p.a + row * p.a_row_stride);
       }
-      yprev = S(0);
-      if (p.want_ga) {
-        const unsigned char* py = stage + Y_OFF + (size_t)p0 * sizeof(S);
-#pragma unroll
-        for (int c = 0; c < CH; ++c) VecIO<S, V>::ld(py + 16 * c, &y[c * V]);
-        if (tpos > 0) yprev = *reinterpret_cast<const S*>(py - sizeof(S));
-        else if (t0 > 0) yprev = *reinterpret_cast<const S*>(stage + HALO_OFF + 16 - sizeof(S));
-        else yprev = __ldg(p.zi + row * p.zi_stride);
-      }
       if (nv < SPT) {
 #pragma unroll
         for (int j = 0; j < SPT; ++j)
-          if (j >= nv) { g[j] = S(0); y[j] = S(0); if (LPV) a[j] = S(1); }
+          if (j >= nv) { g[j] = S(0); if (LPV) a[j] = S(1); }
       }
-    }
-    // map over c (time descending): c_out = a_j * (gy_j + c_in)
-    __device__ __forceinline__ Map aggregate() const {
-      S P = S(1), s = S(0);
-#pragma unroll
-      for (int j = SPT - 1; j >= 0; --j) { const S aj = coef(j); s = aj * (s + g[j]); P *= aj; }
-      Map m; m.v[0] = P; m.v[1] = s; return m;
-    }
-    __device__ __forceinline__ Partial finish(const Params& p, const State& in, unsigned char* stage, int tpos, int) {
-      S c = in.v[0];
-      S acc = S(0);
-#pragma unroll
-      for (int j = SPT - 1; j >= 0; --j) {
-        const S gj = g[j] + c;
-        g[j] = gj;
-        c = coef(j) * gj;
-        if (p.want_ga) {
-          const S yp = j > 0 ? y[j - 1] : yprev;
-          if (LPV) y[j] = gj * yp;
-          else if (j < nv) acc += gj * yp;
-        }
-      }
-      unsigned char* pg = stage + G_OFF + (size_t)tpos * SPT * sizeof(S);
-#pragma unroll
-      for (int c2 = 0; c2 < CH; ++c2) VecIO<S, V>::st(pg + 16 * c2, &g[c2 * V]);
-      if (LPV && p.want_ga) {
-        unsigned char* py = stage + Y_OFF + (size_t)tpos * SPT * sizeof(S);
-#pragma unroll
-        for (int c2 = 0; c2 < CH; ++c2) VecIO<S, V>::st(py + 16 * c2, &y[c2 * V]);
-      }
-      Partial r; r.v[0] = acc; return r;
     }
   };
+
+  // map over c (time descending): c_out = a_j * (gy_j + c_in)
+  static __device__ __forceinline__ Map aggregate(const Params& p, const unsigned char* stage, int tpos,
+                                                  int64_t row, int64_t, int nvalid) {
+    Regs r;
+    r.load(p, stage, tpos, row, nvalid);
+    S P = S(1), s = S(0);
+#pragma unroll
+    for (int j = SPT - 1; j >= 0; --j) { const S aj = r.coef(j); s = aj * (s + r.g[j]); P *= aj; }
+    Map m; m.v[0] = P; m.v[1] = s; return m;
+  }
+  static __device__ __forceinline__ Partial finish(const Params& p, const State& in, unsigned char* stage,
+                                                   int tpos, int64_t row, int64_t t0, int nvalid) {
+    Regs r;
+    r.load(p, stage, tpos, row, nvalid);
+    S y[SPT];
+    S yprev = S(0);
+    const int p0 = tpos * SPT;
+    unsigned char* py = stage + Y_OFF + (size_t)p0 * sizeof(S);
+    if (p.want_ga) {
+#pragma unroll
+      for (int c = 0; c < CH; ++c) VecIO<S, V>::ld(py + 16 * c, &y[c * V]);
+      if (tpos > 0) yprev = *reinterpret_cast<const S*>(py - sizeof(S));
+      else if (t0 > 0) yprev = *reinterpret_cast<const S*>(stage + HALO_OFF + 16 - sizeof(S));
+      else yprev = __ldg(p.zi + row * p.zi_stride);
+    }
+    S c = in.v[0];
+    S acc = S(0);
+#pragma unroll
+    for (int j = SPT - 1; j >= 0; --j) {
+      const S gj = r.g[j] + c;
+      r.g[j] = gj;
+      c = r.coef(j) * gj;
+      if (p.want_ga) {
+        const S yp = j > 0 ? y[j - 1] : yprev;
+        if (LPV) y[j] = gj * yp;
+        else if (j < r.nv) acc += gj * yp;
+      }
+    }
+    unsigned char* pg = stage + G_OFF + (size_t)p0 * sizeof(S);
+#pragma unroll
+    for (int c2 = 0; c2 < CH; ++c2) VecIO<S, V>::st(pg + 16 * c2, &r.g[c2 * V]);
+    if (LPV && p.want_ga) {
+      // grad_a goes over this thread's own coefficients: the y slot stays read-only, because the
+      // neighbouring thread reads its previous sample from it at an unsynchronised time
+      unsigned char* pa = stage + A_OFF + (size_t)p0 * sizeof(S);
+#pragma unroll
+      for (int c2 = 0; c2 < CH; ++c2) VecIO<S, V>::st(pa + 16 * c2, &y[c2 * V]);
+    }
+    Partial out; out.v[0] = acc; return out;
+  }
 };
 
 }  // namespace ptb

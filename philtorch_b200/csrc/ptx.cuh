@@ -2,7 +2,6 @@
 //   * mbarrier (shared-memory transaction barriers) with BOUNDED waits
 //   * 1-D bulk asynchronous copies (TMA, cp.async.bulk) global<->shared, no multicast
 //   * gpu-scope acquire/release accesses for the inter-CTA look-back
-//   * named barriers for the compute warps
 #pragma once
 #include <cstdint>
 #include <cuda_runtime.h>
@@ -41,13 +40,36 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: returns false when `limit` polls went by without the phase completing.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint32_t limit) {
-  for (uint32_t i = 0; i < limit; ++i) {
+// Non-blocking probe (try_wait may suspend the thread for a system-dependent time).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Wait bounded in TIME: returns false when `limit_ns` went by without the phase completing
+// (try_wait itself may suspend the thread for a system-dependent while, so polls are not counted).
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint64_t limit_ns) {
+  if (mbar_test_wait(bar, parity)) return true;
+#pragma unroll 1
+  for (int i = 0; i < 32; ++i)
     if (mbar_try_wait(bar, parity)) return true;
-    if (i > 64) __nanosleep(64);
+  const uint64_t t0 = globaltimer_ns();
+#pragma unroll 1
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (globaltimer_ns() - t0 > limit_ns) return false;
   }
-  return false;
 }
 
 // ----------------------------------------------------------------------------- bulk copies (TMA, 1-D)
@@ -87,9 +109,14 @@ __device__ __forceinline__ void st_release_u32(uint32_t* p, uint32_t v) {
   asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-// ----------------------------------------------------------------------------- named barrier
-__device__ __forceinline__ void bar_sync(int id, int nthreads) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+// single-copy-atomic 64-bit accesses that bypass L1: {flag, payload word} records of the look-back
+__device__ __forceinline__ uint64_t ld_relaxed_u64(const uint64_t* p) {
+  uint64_t v;
+  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_relaxed_u64(uint64_t* p, uint64_t v) {
+  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
 
 }  // namespace ptb

@@ -8,21 +8,32 @@
 //     predecessor of a tile (same row, previous chunk) is B tickets older and has normally
 //     published its end state before the tile asks for it; a CTA only ever waits on OLDER
 //     tickets, which are held by running CTAs, so the look-back cannot deadlock.
-//   * One CTA = P::NT compute threads + one DMA warp.  Lane 0 of the DMA warp owns the ticket
-//     counter, issues the 1-D bulk (TMA) loads of a tile's operands into a ring of P::STAGES
-//     shared-memory stages (mbarrier transaction counts signal arrival) and, once the compute
-//     warps have written the tile's results back into the same stage, issues the bulk stores.
-//   * Compute thread i owns P::SPT consecutive samples of the tile.  P::SPT is chosen so that the
-//     per-thread footprint of every staged array is an ODD number of 16-byte (or 8-byte) units,
-//     which makes the strided 128-bit / 64-bit shared-memory accesses bank-conflict free without
-//     swizzling.  Each thread folds its samples into one affine map, maps are scanned with warp
-//     shuffles, warp totals are scanned by warp 0, the tile aggregate is published
-//     (flag 1) and warp 0 looks back over predecessor tiles -- 32 at a time -- until it meets
-//     an end state (flag 2).  The tile's end state is published (flag 2) and every thread
-//     replays its samples from its own incoming state.
+//   * One CTA = P::NT compute threads + one look-back warp + one DMA warp, decoupled by
+//     shared-memory mbarriers (no CTA-wide barrier on the bulk path):
+//       DMA warp (lane 0)   owns the ticket counter, issues the 1-D bulk (TMA) loads of a tile's
+//                           operands into a ring of P::STAGES shared-memory stages and, once the
+//                           compute warps have written the tile's results back into the stage,
+//                           the bulk stores.
+//       compute warps       phase 1 of tile n+1: every thread folds its P::SPT consecutive samples
+//                           into one affine map, maps are scanned with warp shuffles, warp totals
+//                           go to shared memory.  Phase 2 of tile n: with the tile's incoming
+//                           state known, every thread replays its samples from its own incoming
+//                           state and writes the results into the stage.  Phase 1 of the next
+//                           tile runs BEFORE phase 2 of the current one, which hides the
+//                           look-back latency.
+//       look-back warp      scans the warp totals, publishes the tile aggregate (flag 1), looks
+//                           back over predecessor tiles -- 32 at a time -- until it meets an end
+//                           state (flag 2), publishes the tile's end state and hands the
+//                           incoming state to the compute warps.
+//   * P::SPT is chosen so that the per-thread footprint of every staged array is an ODD number of
+//     16-byte (or 8-byte) units: the strided 128-bit / 64-bit shared-memory accesses are then
+//     bank-conflict free without swizzling.
+//   * Published records need no fences: every 32-bit payload word travels in its own 64-bit word
+//     next to the flag, written and read with single relaxed 64-bit accesses; a reader accepts a
+//     record only when all its words carry the same flag.
 //
-// All waits are bounded; on expiry an error bit is set in the workspace and the kernel runs to
-// completion (results are then invalid, the host reports the error).
+// All waits are bounded; on expiry an error bit is set and the kernel runs to completion
+// (results are then invalid, the host reports the error).
 //
 // The association order of the look-back depends on which predecessors had already published
 // an end state, so floating-point results can differ in the last bits from run to run, as with
@@ -36,16 +47,45 @@ constexpr uint32_t kNoTile = 0xFFFFFFFFu;
 constexpr uint32_t kErrLookbackTimeout = 1u;
 constexpr uint32_t kErrLoadTimeout = 2u;
 constexpr uint32_t kErrDrainTimeout = 4u;
-constexpr uint32_t kSpinLimit = 1u << 22;   // polls (each >= 64 ns once backed off): a few tenths of a second
-constexpr uint32_t kSpinLimitAfterError = 1u << 8;
+constexpr uint32_t kErrPipeTimeout = 8u;
+constexpr uint64_t kWaitNs = 2000000000ull;        // any single device-side wait gives up after 2 s
+constexpr uint64_t kWaitNsAfterError = 1000000ull;   // ... or after 1 ms once this CTA has seen an error
+
+// Optional role-level timing (compile with -DPTB_PROFILE): cycles each role spends waiting,
+// summed over CTAs into 64-bit counters that follow the workspace header.
+#ifdef PTB_PROFILE
+#define PTB_PROF_DECL(name) long long name = 0
+#define PTB_PROF_BEGIN(t) const long long t = clock64()
+#define PTB_PROF_END(name, t) name += clock64() - t
+#define PTB_PROF_FLUSH(idx, name) atomicAdd(reinterpret_cast<unsigned long long*>(ws.ticket) + 8 + (idx), (unsigned long long)(name))
+#else
+#define PTB_PROF_DECL(name)
+#define PTB_PROF_BEGIN(t)
+#define PTB_PROF_END(name, t)
+#define PTB_PROF_FLUSH(idx, name)
+#endif
+
+// Optional event trace of CTA 0 (compile with -DPTB_TRACE): {clock:48 | tile:12 | event:4} words
+// written over the (otherwise unused) partial area of the workspace.
+#ifdef PTB_TRACE
+#define PTB_EV(type, n)                                                                         \
+  do {                                                                                          \
+    if (blockIdx.x == 0) {                                                                      \
+      const unsigned ei_ = atomicAdd(sm_trace_cnt, 1u);                                         \
+      if (ei_ < 8000u)                                                                          \
+        reinterpret_cast<unsigned long long*>(ws.partial)[ei_] =                                \
+            ((unsigned long long)clock64() << 16) | (((unsigned long long)(n) & 0xfffu) << 4) | (type); \
+    }                                                                                           \
+  } while (0)
+#else
+#define PTB_EV(type, n)
+#endif
 
 struct Workspace {
   uint32_t* ticket;   // [1]   zeroed before launch
   uint32_t* error;    // [1]   sticky error bits
-  uint32_t* flags;    // [ntiles] zeroed before launch: 0 empty, 1 aggregate ready, 2 end state ready
-  void* agg;          // [ntiles] Map
-  void* incl;         // [ntiles] State
-  void* partial;      // [ntiles] P::Partial (policy specific), may be null
+  uint64_t* slots;    // [ntiles][P::SLOT_WORDS] zeroed before launch: {flag:32 | payload word:32}
+  void* partial;      // [ntiles] P::Partial (policy specific)
 };
 
 constexpr int kMaxIo = 4;
@@ -88,17 +128,42 @@ __device__ __forceinline__ T shfl_pod(const T& x, int src) {
   for (int i = 0; i < T::N; ++i) r.v[i] = __shfl_sync(0xffffffffu, x.v[i], src);
   return r;
 }
+
+// ---- published records --------------------------------------------------------------------------
 template <class T>
-__device__ __forceinline__ void st_cg_pod(T* p, const T& x) {
+struct Words {
+  static constexpr int W = (int)(sizeof(T) / 4);
+  union U { T t; uint32_t w[W]; };
+};
+template <class T>
+__device__ __forceinline__ void slot_store(uint64_t* slot, const T& v, uint32_t flag) {
+  typename Words<T>::U u;
+  u.t = v;
 #pragma unroll
-  for (int i = 0; i < T::N; ++i) __stcg(&p->v[i], x.v[i]);
+  for (int i = 0; i < Words<T>::W; ++i) st_relaxed_u64(slot + i, ((uint64_t)flag << 32) | u.w[i]);
 }
-template <class T>
-__device__ __forceinline__ T ld_cg_pod(const T* p) {
-  T r;
+// fetch the raw words of a record (all loads in flight together) ...
+template <class Map>
+__device__ __forceinline__ void slot_fetch(const uint64_t* slot, uint64_t* r) {
 #pragma unroll
-  for (int i = 0; i < T::N; ++i) r.v[i] = __ldcg(&p->v[i]);
-  return r;
+  for (int i = 0; i < Words<Map>::W; ++i) r[i] = ld_relaxed_u64(slot + i);
+}
+// ... and decode them.  0: nothing usable yet, 1: aggregate in `m`, 2: end state in `st`
+template <class Map, class State>
+__device__ __forceinline__ uint32_t slot_decode(const uint64_t* r, Map& m, State& st) {
+  constexpr int WM = Words<Map>::W, WS = Words<State>::W;
+  static_assert(WS <= WM, "end states are stored in the first words of the aggregate's slot");
+  const uint32_t f0 = (uint32_t)(r[0] >> 32);
+  bool ok2 = true, ok1 = true;
+  typename Words<State>::U us;
+  typename Words<Map>::U um;
+#pragma unroll
+  for (int i = 0; i < WS; ++i) { ok2 = ok2 && ((uint32_t)(r[i] >> 32) == 2u); us.w[i] = (uint32_t)r[i]; }
+#pragma unroll
+  for (int i = 0; i < WM; ++i) { ok1 = ok1 && ((uint32_t)(r[i] >> 32) == 1u); um.w[i] = (uint32_t)r[i]; }
+  st = us.t;
+  m = um.t;
+  return (f0 == 2u && ok2) ? 2u : ((f0 == 1u && ok1) ? 1u : 0u);
 }
 
 template <class P>
@@ -111,17 +176,40 @@ __device__ __forceinline__ typename P::Map warp_scan_inclusive(typename P::Map m
   return m;
 }
 
-// Look-back executed by all 32 lanes of compute warp 0.  Returns (in every lane) the state
-// entering the tile.
+// Look-back executed by all 32 lanes of a look-back warp; returns (in every lane) the state
+// entering the tile.  It may start before the tile's own operands have landed, so it first
+// polls, with one lane only, the nearest predecessor until that tile has published anything:
+// this keeps the polling traffic in L2 negligible.  In the usual case the record found is an end
+// state and the look-back is over; otherwise windows of 32 predecessors (one per lane, all
+// loads in flight together) are folded until one contains an end state.
 template <class P>
 __device__ __forceinline__ typename P::State lookback(const Workspace& ws, uint32_t ticket,
                                                       uint32_t chunk, uint32_t B, int lane,
                                                       uint32_t& failed) {
   using Map = typename P::Map;
   using State = typename P::State;
-  const Map* aggs = static_cast<const Map*>(ws.agg);
-  const State* incls = static_cast<const State*>(ws.incl);
-  Map acc = P::identity();   // meaningful in lane 0: maps nearer to the tile than the window
+  {
+    uint32_t f = 0;
+    State st0 = P::zero_state();
+    if (lane == 0) {
+      Map m0;
+      const uint64_t* slot = ws.slots + ((size_t)ticket - B) * P::SLOT_WORDS;
+      const uint64_t limit = failed ? kWaitNsAfterError : kWaitNs;
+      uint64_t t0 = 0;
+      for (uint32_t it = 0;; ++it) {
+        uint64_t raw[Words<Map>::W];
+        slot_fetch<Map>(slot, raw);
+        f = slot_decode<Map, State>(raw, m0, st0);
+        if (f != 0) break;
+        __nanosleep(it > 64 ? 256 : 64);
+        if (it == 64) t0 = globaltimer_ns();
+        if (it > 64 && globaltimer_ns() - t0 > limit) break;
+      }
+    }
+    f = __shfl_sync(0xffffffffu, f, 0);
+    if (f == 2u) return shfl_pod(st0, 0);
+  }
+  Map acc = P::identity();
   uint32_t base = 1;
   State result;
   while (true) {
@@ -129,12 +217,20 @@ __device__ __forceinline__ typename P::State lookback(const Workspace& ws, uint3
     const bool valid = k <= chunk;
     const size_t idx = valid ? (size_t)ticket - (size_t)k * B : 0;
     uint32_t flag = 0;
+    Map m = P::identity();
+    State st = P::zero_state();
     if (valid) {
-      const uint32_t limit = failed ? kSpinLimitAfterError : kSpinLimit;
-      for (uint32_t it = 0; it < limit; ++it) {
-        flag = ld_acquire_u32(ws.flags + idx);
+      const uint64_t* slot = ws.slots + idx * P::SLOT_WORDS;
+      const uint64_t limit = failed ? kWaitNsAfterError : kWaitNs;
+      uint64_t t0 = 0;
+      for (uint32_t it = 0;; ++it) {
+        uint64_t raw[Words<Map>::W];
+        slot_fetch<Map>(slot, raw);
+        flag = slot_decode<Map, State>(raw, m, st);
         if (flag != 0) break;
         if (it > 16) __nanosleep(it > 256 ? 256 : 32);
+        if (it == 64) t0 = globaltimer_ns();
+        if (it > 64 && globaltimer_ns() - t0 > limit) break;
       }
     }
     const bool timed_out = valid && flag == 0;
@@ -143,33 +239,24 @@ __device__ __forceinline__ typename P::State lookback(const Workspace& ws, uint3
       if (lane == 0) atomicOr(ws.error, kErrLookbackTimeout);
     }
     const uint32_t m2 = __ballot_sync(0xffffffffu, (valid && flag == 2) || timed_out || !valid);
-    if (m2 & 1u) {   // common case: the immediate predecessor already has its end state
-      State s = P::zero_state();
-      if (lane == 0 && valid && flag == 2) s = ld_cg_pod(incls + idx);
-      s = shfl_pod(s, 0);
-      // fold with the nearer maps gathered so far (identity on the first window)
-      Map a0 = shfl_pod(acc, 0);
+    if (m2 & 1u) {
+      const State s = shfl_pod(st, 0);
+      const Map a0 = shfl_pod(acc, 0);
       result = P::apply(a0, s);
       break;
     }
     const int j = m2 ? (__ffs(m2) - 1) : 32;
-    Map m = P::identity();
-    if (lane < j) {
-      m = ld_cg_pod(aggs + idx);
-    } else if (lane == j) {
-      State s = P::zero_state();
-      if (valid && flag == 2) s = ld_cg_pod(incls + idx);
-      m = P::const_map(s);
-    }
+    if (lane == j) m = P::const_map((valid && flag == 2) ? st : P::zero_state());
+    else if (lane > j) m = P::identity();
 #pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {   // ordered reduction: higher lane = earlier in the sequence
+    for (int d = 1; d < 32; d <<= 1) {
       Map o = shfl_down_pod(m, d);
       if (lane + d < 32) m = P::compose(o, m);
     }
-    acc = P::compose(m, acc);   // window first, then the nearer maps
+    acc = P::compose(m, acc);
     if (m2) {
-      Map a0 = shfl_pod(acc, 0);
-      result = P::apply(a0, P::zero_state());   // acc ends in a constant map: its offset is the state
+      const Map a0 = shfl_pod(acc, 0);
+      result = P::apply(a0, P::zero_state());
       break;
     }
     base += 32;
@@ -179,44 +266,62 @@ __device__ __forceinline__ typename P::State lookback(const Workspace& ws, uint3
 
 // --------------------------------------------------------------------------------------------------
 // Policy requirements (see first_order.cuh for a worked example):
-//   types   S, Map{S v[N]}, State{S v[N]}, Partial{S v[N]}, Params, Thread
+//   types   S, Map{S v[N]}, State{S v[N]}, Partial{S v[N]}, Params
 //   consts  NT (compute threads, multiple of 32), SPT, TILE = NT*SPT, STAGES, STAGE_BYTES,
-//           MIN_CTAS, REVERSE (process time descending), HAS_PARTIAL
+//           MIN_CTAS, REVERSE (process time descending), HAS_PARTIAL, SLOT_WORDS
 //   static  identity(), zero_state(), const_map(State), compose(first, second), apply(Map, State),
-//           plan(prm, bulk, row, t0, nvalid, IoPlan&), row_init(prm, row), row_final(prm, row, State)
-//   Thread  load(prm, stage, tpos, row, t0, nvalid), aggregate() -> Map,
-//           finish(prm, State in, stage, tpos, nvalid) -> Partial
+//           plan(prm, bulk, row, t0, nvalid, IoPlan&), row_init(prm, row), row_final(prm, row, State),
+//           aggregate(prm, stage, tpos, row, t0, nvalid) -> Map          (phase 1, reads the stage)
+//           finish(prm, State in, stage, tpos, row, t0, nvalid) -> Partial (phase 2, reads and
+//                                                                          overwrites the stage)
 // --------------------------------------------------------------------------------------------------
 template <class P>
 struct EngineSmem {
-  static constexpr int kStagesBytes = P::STAGES * P::STAGE_BYTES;
+  static constexpr int D = P::STAGES;
+  static constexpr int kStagesBytes = D * P::STAGE_BYTES;
   static constexpr int kNW = P::NT / 32;
-  // after the stages:
-  static constexpr int kFullOff = kStagesBytes;                       // u64 full[STAGES]
-  static constexpr int kDoneOff = kFullOff + 8 * P::STAGES;           // u64 done[STAGES]
-  static constexpr int kTicketOff = kDoneOff + 8 * P::STAGES;         // u32 tile_ticket[STAGES]
-  static constexpr int kScratchOff = ((kTicketOff + 4 * P::STAGES + 15) / 16) * 16;
-  static constexpr int kWtotOff = kScratchOff;                                          // Map wtot[NW]
-  static constexpr int kWpreOff = kWtotOff + (int)sizeof(typename P::Map) * kNW;        // Map wpre[NW]
-  static constexpr int kHinOff = kWpreOff + (int)sizeof(typename P::Map) * kNW;         // State hin
-  static constexpr int kPartOff = ((kHinOff + (int)sizeof(typename P::State) + 15) / 16) * 16;  // Partial[NW]
+  static constexpr int kMapB = (int)sizeof(typename P::Map);
+  static constexpr int kStateB = (int)sizeof(typename P::State);
+  static constexpr int kFullOff = kStagesBytes;            // u64 full[D]      operands landed
+  static constexpr int kDoneOff = kFullOff + 8 * D;        // u64 done[D]      results written to the stage
+  static constexpr int kAggOff = kDoneOff + 8 * D;         // u64 agg_ready[D] tile aggregate known
+  static constexpr int kLbOff = kAggOff + 8 * D;           // u64 lb_done[D]   incoming state known
+  static constexpr int kIssuedOff = kLbOff + 8 * D;        // u64 issued[D]    ticket of the stage known
+  static constexpr int kSyncOff = kIssuedOff + 8 * D;      // u64 sync_bar[3]  barriers among the compute threads
+  static constexpr int kTicketOff = kSyncOff + 8 * 3;      // u32 tile_ticket[D]
+  static constexpr int kCntOff = kTicketOff + 4 * D;       // u32 arrived[D]
+  static constexpr int kAbortOff = kCntOff + 4 * D;        // u32 abort, u32 trace counter
+  static constexpr int kWtotOff = ((kAbortOff + 8 + 15) / 16) * 16;   // Map wtot[D][NW]
+  static constexpr int kWpreOff = kWtotOff + D * kMapB * kNW;         // Map wpre[D][NW]
+  static constexpr int kTaggOff = kWpreOff + D * kMapB * kNW;         // Map tile_agg[D]
+  static constexpr int kHinOff = kTaggOff + D * kMapB;                // State hin[D]
+  static constexpr int kPartOff = ((kHinOff + D * kStateB + 15) / 16) * 16;   // Partial[NW]
   static constexpr int kTotal = kPartOff + (int)sizeof(typename P::Partial) * kNW + 16;
 };
 
-template <class P>
-__device__ __forceinline__ void tile_coords(const typename P::Params& prm, uint32_t ticket, uint32_t B,
-                                            uint32_t nchunks, int64_t T, uint32_t& chunk, uint32_t& row,
-                                            int64_t& t0, int& nvalid) {
-  chunk = ticket / B;
-  row = ticket - chunk * B;
-  const uint32_t tc = P::REVERSE ? (nchunks - 1 - chunk) : chunk;
-  t0 = (int64_t)tc * P::TILE;
-  const int64_t rem = T - t0;
-  nvalid = rem < (int64_t)P::TILE ? (int)rem : P::TILE;
-}
+struct TileCoords {
+  uint32_t ticket, chunk, row;
+  int64_t t0;
+  int nvalid;
+};
 
 template <class P>
-__global__ void __launch_bounds__(P::NT + 32, P::MIN_CTAS)
+__device__ __forceinline__ TileCoords tile_coords(uint32_t ticket, uint32_t B, uint32_t nchunks, int64_t T) {
+  TileCoords c;
+  c.ticket = ticket;
+  c.chunk = ticket / B;
+  c.row = ticket - c.chunk * B;
+  const uint32_t tc = P::REVERSE ? (nchunks - 1 - c.chunk) : c.chunk;
+  c.t0 = (int64_t)tc * P::TILE;
+  const int64_t rem = T - c.t0;
+  c.nvalid = rem < (int64_t)P::TILE ? (int)rem : P::TILE;
+  return c;
+}
+
+template <int I> struct StageTag { static constexpr int value = I; };
+
+template <class P>
+__global__ void __launch_bounds__(P::NT + 32 * (P::STAGES + 1), P::MIN_CTAS)
 scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, const int64_t T,
             const uint32_t nchunks, const uint32_t ntiles, const int bulk) {
   using Map = typename P::Map;
@@ -226,9 +331,20 @@ scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, 
   extern __shared__ __align__(128) unsigned char smem[];
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::kFullOff);
   uint64_t* done = reinterpret_cast<uint64_t*>(smem + L::kDoneOff);
+  uint64_t* agg_ready = reinterpret_cast<uint64_t*>(smem + L::kAggOff);
+  uint64_t* lb_done = reinterpret_cast<uint64_t*>(smem + L::kLbOff);
+  uint64_t* issued = reinterpret_cast<uint64_t*>(smem + L::kIssuedOff);
+  uint64_t* sync_bar = reinterpret_cast<uint64_t*>(smem + L::kSyncOff);
   volatile uint32_t* tile_ticket = reinterpret_cast<volatile uint32_t*>(smem + L::kTicketOff);
+  uint32_t* sm_cnt = reinterpret_cast<uint32_t*>(smem + L::kCntOff);
+  volatile uint32_t* sm_abort = reinterpret_cast<volatile uint32_t*>(smem + L::kAbortOff);
+#ifdef PTB_TRACE
+  uint32_t* sm_trace_cnt = reinterpret_cast<uint32_t*>(smem + L::kAbortOff + 4);
+  if (threadIdx.x == 0) *sm_trace_cnt = 0;
+#endif
   Map* wtot = reinterpret_cast<Map*>(smem + L::kWtotOff);
   Map* wpre = reinterpret_cast<Map*>(smem + L::kWpreOff);
+  Map* sm_tagg = reinterpret_cast<Map*>(smem + L::kTaggOff);
   State* sm_hin = reinterpret_cast<State*>(smem + L::kHinOff);
   Partial* sm_part = reinterpret_cast<Partial*>(smem + L::kPartOff);
 
@@ -238,142 +354,241 @@ scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, 
   constexpr int NT = P::NT;
   constexpr int NW = NT / 32;
   constexpr int D = P::STAGES;
+  static_assert(D >= 2 && D <= 4, "the compute warps keep one prefix per stage in registers");
 
   if (tid == 0) {
     for (int s = 0; s < D; ++s) {
       mbar_init(&full[s], 1);
-      mbar_init(&done[s], NT);
+      mbar_init(&done[s], NT + 1);   // compute threads + the stage's look-back warp
+      mbar_init(&agg_ready[s], 1);
+      mbar_init(&lb_done[s], 1);
+      mbar_init(&issued[s], 1);
+      sm_cnt[s] = 0;
     }
+    for (int i = 0; i < 3; ++i) mbar_init(&sync_bar[i], NT);
+    *sm_abort = 0;
     fence_mbar_init();
   }
   __syncthreads();
 
-  if (warp == NW) {
+  if (warp == NW + D) {
     // ======================================================================= DMA warp
     if (lane != 0) return;
     uint32_t failed = 0;
     uint32_t next = atomicAdd(ws.ticket, 1u);
     uint32_t n = 0;
+    PTB_PROF_DECL(t_wait_done); PTB_PROF_DECL(t_wait_read); PTB_PROF_DECL(t_dma_total);
+    PTB_PROF_BEGIN(tdma0);
     auto drain = [&](uint32_t j) {   // results of the j-th tile of this CTA are in its stage
       const int s = j % D;
-      const uint32_t limit = failed ? kSpinLimitAfterError : kSpinLimit;
+      const uint64_t limit = (failed || *sm_abort) ? kWaitNsAfterError : kWaitNs;
+      PTB_PROF_BEGIN(tw0);
       if (!mbar_wait_bounded(&done[s], (j / D) & 1u, limit)) {
         failed = 1;
         atomicOr(ws.error, kErrDrainTimeout);
+        return;   // the stage was not completed: nothing to store
       }
+      PTB_PROF_END(t_wait_done, tw0);
+      PTB_EV(8, j);
       if (bulk) {
-        uint32_t chunk, row; int64_t t0; int nvalid;
-        tile_coords<P>(prm, tile_ticket[s], B, nchunks, T, chunk, row, t0, nvalid);
+        const TileCoords c = tile_coords<P>(tile_ticket[s], B, nchunks, T);
         IoPlan io; io.nld = 0; io.nst = 0;
-        P::plan(prm, true, row, t0, nvalid, io);
+        P::plan(prm, true, c.row, c.t0, c.nvalid, io);
         unsigned char* stage = smem + s * P::STAGE_BYTES;
-        for (int i = 0; i < io.nst; ++i)
-          if (io.st_bytes[i]) bulk_s2g(io.st_g[i], stage + io.st_soff[i], io.st_bytes[i]);
+#pragma unroll
+        for (int i = 0; i < kMaxIo; ++i)
+          if (i < io.nst && io.st_bytes[i]) bulk_s2g(io.st_g[i], stage + io.st_soff[i], io.st_bytes[i]);
         bulk_commit();
+        PTB_PROF_BEGIN(tr0);
         bulk_wait_read_all();   // the stage may be overwritten from here on
+        PTB_PROF_END(t_wait_read, tr0);
+        PTB_EV(9, j);
       }
     };
     for (;; ++n) {
       const int s = n % D;
       if (n >= (uint32_t)D) drain(n - D);
-      const uint32_t ticket = next;
-      if (ticket >= ntiles) {
-        tile_ticket[s] = kNoTile;
-        mbar_arrive(&full[s]);
-        break;
-      }
+      const uint32_t ticket = (failed || *sm_abort) ? ntiles : next;   // stop handing out work after an error
+      if (ticket >= ntiles) break;
       next = atomicAdd(ws.ticket, 1u);
       tile_ticket[s] = ticket;
+      PTB_EV(1, n);
+      mbar_arrive(&issued[s]);   // the stage's look-back warp may start right away
       if (bulk) {
-        uint32_t chunk, row; int64_t t0; int nvalid;
-        tile_coords<P>(prm, ticket, B, nchunks, T, chunk, row, t0, nvalid);
+        const TileCoords c = tile_coords<P>(ticket, B, nchunks, T);
         IoPlan io; io.nld = 0; io.nst = 0;
-        P::plan(prm, true, row, t0, nvalid, io);
+        P::plan(prm, true, c.row, c.t0, c.nvalid, io);
         uint32_t total = 0;
-        for (int i = 0; i < io.nld; ++i) total += io.ld_bytes[i];
+#pragma unroll
+        for (int i = 0; i < kMaxIo; ++i)
+          if (i < io.nld) total += io.ld_bytes[i];
         mbar_arrive_expect_tx(&full[s], total);
         unsigned char* stage = smem + s * P::STAGE_BYTES;
-        for (int i = 0; i < io.nld; ++i)
-          if (io.ld_bytes[i]) bulk_g2s(stage + io.ld_soff[i], io.ld_g[i], io.ld_bytes[i], &full[s]);
+#pragma unroll
+        for (int i = 0; i < kMaxIo; ++i)
+          if (i < io.nld && io.ld_bytes[i]) bulk_g2s(stage + io.ld_soff[i], io.ld_g[i], io.ld_bytes[i], &full[s]);
       } else {
         mbar_arrive(&full[s]);
       }
     }
-    // n = index of the terminal slot; tiles n-D+1 .. n-1 are still in their stages
-    for (uint32_t j = (n >= (uint32_t)D ? n - D + 1 : 0); j < n; ++j) drain(j);
+    // n = first index without a tile: put the end marker into every stage (each look-back warp
+    // watches its own), draining the tiles still held by the stages on the way
+    for (uint32_t k = 0; k < (uint32_t)D; ++k) {
+      const uint32_t m = n + k;
+      const int s = m % D;
+      if (k > 0 && m >= (uint32_t)D) drain(m - D);
+      tile_ticket[s] = kNoTile;
+      mbar_arrive(&issued[s]);
+      mbar_arrive(&full[s]);
+    }
+    if (failed || *sm_abort) {
+      // make sure no bulk load of this CTA is still writing shared memory when the CTA exits
+      for (uint32_t j = (n >= (uint32_t)D ? n - D : 0); j < n; ++j)
+        mbar_wait_bounded(&full[j % D], (j / D) & 1u, kWaitNs);
+    }
     if (bulk) bulk_wait_all();
+    PTB_PROF_END(t_dma_total, tdma0);
+    PTB_PROF_FLUSH(0, t_wait_done); PTB_PROF_FLUSH(1, t_wait_read); PTB_PROF_FLUSH(2, t_dma_total);
+    PTB_PROF_FLUSH(3, (long long)n);
+    return;
+  }
+
+  if (warp >= NW) {
+    // ======================================================================= look-back warps
+    // One per stage.  The look-back of a tile needs nothing from the tile itself, so it starts as
+    // soon as the DMA warp has assigned the ticket and overlaps the tile's own load.
+    const int s = warp - NW;
+    uint32_t failed = 0;
+    PTB_PROF_DECL(t_lb_wait_issue); PTB_PROF_DECL(t_lb_wait_agg); PTB_PROF_DECL(t_lb_look); PTB_PROF_DECL(t_lb_total);
+    PTB_PROF_BEGIN(tlb0);
+    for (uint32_t par = 0;; par ^= 1u) {
+      uint64_t limit = (failed || *sm_abort) ? kWaitNsAfterError : kWaitNs;
+      PTB_PROF_BEGIN(tf0);
+      if (!mbar_wait_bounded(&issued[s], par, limit)) {
+        if (lane == 0) { atomicOr(ws.error, kErrLoadTimeout); *sm_abort = 1; }
+        break;
+      }
+      PTB_PROF_END(t_lb_wait_issue, tf0);
+      const uint32_t ticket = tile_ticket[s];
+      if (ticket == kNoTile) break;
+      const TileCoords c = tile_coords<P>(ticket, B, nchunks, T);
+      PTB_PROF_BEGIN(tl0);
+      if (lane == 0) PTB_EV(4, (par ? 1 : 0));
+      State hin;
+      if (c.chunk == 0) hin = P::row_init(prm, c.row);   // its end state is published in phase 1
+      else hin = lookback<P>(ws, ticket, c.chunk, B, lane, failed);
+      if (lane == 0) {
+        sm_hin[s] = hin;
+        mbar_arrive(&lb_done[s]);
+        PTB_EV(5, s);
+      }
+      PTB_PROF_END(t_lb_look, tl0);
+      limit = (failed || *sm_abort) ? kWaitNsAfterError : kWaitNs;
+      PTB_PROF_BEGIN(ta0);
+      if (!mbar_wait_bounded(&agg_ready[s], par, limit)) {
+        if (lane == 0) { atomicOr(ws.error, kErrPipeTimeout); *sm_abort = 1; }
+        break;
+      }
+      PTB_PROF_END(t_lb_wait_agg, ta0);
+      if (lane == 0) {
+        if (c.chunk > 0 || nchunks == 1) {
+          const State hend = P::apply(sm_tagg[s], hin);
+          if (c.chunk + 1 < nchunks) slot_store(ws.slots + (size_t)ticket * P::SLOT_WORDS, hend, 2u);
+          else P::row_final(prm, c.row, hend);
+        }
+        mbar_arrive(&done[s]);   // this warp is through with the stage's scratch
+      }
+      __syncwarp();
+    }
+    PTB_PROF_END(t_lb_total, tlb0);
+    if (lane == 0 && s == 0) {
+      PTB_PROF_FLUSH(4, t_lb_wait_issue); PTB_PROF_FLUSH(5, t_lb_wait_agg); PTB_PROF_FLUSH(6, t_lb_look);
+      PTB_PROF_FLUSH(7, t_lb_total);
+    }
     return;
   }
 
   // ========================================================================= compute warps
-  uint32_t failed = 0;
-  for (uint32_t n = 0;; ++n) {
-    const int s = n % D;
-    {
-      const uint32_t limit = failed ? kSpinLimitAfterError : kSpinLimit;
-      if (!mbar_wait_bounded(&full[s], (n / D) & 1u, limit)) {
-        failed = 1;
-        if (lane == 0) atomicOr(ws.error, kErrLoadTimeout);
-      }
+  // Event loop per warp: finish (phase 2) the oldest aggregated tile as soon as its incoming state
+  // is known; otherwise aggregate (phase 1) the next tile as soon as its operands have landed.
+  // Every landed tile therefore publishes its aggregate without waiting for older look-backs.
+  const int tpos = P::REVERSE ? (NT - 1 - tid) : tid;
+  Map exc[D];          // this thread's exclusive prefix inside the tile held by each stage
+  uint32_t p1 = 0, p2 = 0;   // tiles aggregated / finished so far by this warp
+  uint32_t sync_par0 = 0, sync_par1 = 0, sync_par2 = 0;
+  // barrier among the compute threads, bounded like every other wait of the kernel
+  auto cta_sync = [&](int id, uint32_t& par) {
+    mbar_arrive(&sync_bar[id]);
+    if (!mbar_wait_bounded(&sync_bar[id], par, (*sm_abort) ? kWaitNsAfterError : kWaitNs)) {
+      if (lane == 0) { atomicOr(ws.error, kErrPipeTimeout); *sm_abort = 1; }
     }
-    const uint32_t ticket = tile_ticket[s];
-    if (ticket == kNoTile) break;
-    uint32_t chunk, row; int64_t t0; int nvalid;
-    tile_coords<P>(prm, ticket, B, nchunks, T, chunk, row, t0, nvalid);
-    unsigned char* stage = smem + s * P::STAGE_BYTES;
+    par ^= 1u;
+  };
+  PTB_PROF_DECL(t_c_idle); PTB_PROF_DECL(t_c_total);
+  PTB_PROF_BEGIN(tc0);
 
+  auto phase1 = [&](auto tag, uint32_t ticket) {
+    constexpr int s = decltype(tag)::value;
+    const TileCoords c = tile_coords<P>(ticket, B, nchunks, T);
+    unsigned char* stage = smem + s * P::STAGE_BYTES;
+    if (tid == 0) PTB_EV(2, p1);
     if (!bulk) {   // operands that are not 16-byte aligned: cooperative word copies
       IoPlan io; io.nld = 0; io.nst = 0;
-      P::plan(prm, false, row, t0, nvalid, io);
-      for (int i = 0; i < io.nld; ++i) {
-        const uint32_t* g = reinterpret_cast<const uint32_t*>(io.ld_g[i]);
-        uint32_t* d = reinterpret_cast<uint32_t*>(stage + io.ld_soff[i]);
-        const uint32_t nw = io.ld_bytes[i] >> 2;
-        for (uint32_t w = tid; w < nw; w += NT) d[w] = __ldg(g + w);
+      P::plan(prm, false, c.row, c.t0, c.nvalid, io);
+#pragma unroll
+      for (int i = 0; i < kMaxIo; ++i) {
+        if (i < io.nld) {
+          const uint32_t* g = reinterpret_cast<const uint32_t*>(io.ld_g[i]);
+          uint32_t* d = reinterpret_cast<uint32_t*>(stage + io.ld_soff[i]);
+          const uint32_t nw = io.ld_bytes[i] >> 2;
+          for (uint32_t w = tid; w < nw; w += NT) d[w] = __ldg(g + w);
+        }
       }
-      bar_sync(1, NT);
+      cta_sync(0, sync_par0);
     }
-
-    const int tpos = P::REVERSE ? (NT - 1 - tid) : tid;
-    typename P::Thread th;
-    th.load(prm, stage, tpos, row, t0, nvalid);
-    const Map mine = th.aggregate();
+    const Map mine = P::aggregate(prm, stage, tpos, c.row, c.t0, c.nvalid);
     const Map inc = warp_scan_inclusive<P>(mine, lane);
-    if (lane == 31) wtot[warp] = inc;
-    Map exc = shfl_up_pod(inc, 1);
-    if (lane == 0) exc = P::identity();
-    bar_sync(1, NT);   // (A) warp totals visible, every thread holds its operands in registers
-
-    if (warp == 0) {
-      Map w = lane < NW ? wtot[lane] : P::identity();
+    uint32_t order = 0;
+    if (lane == 31) {
+      wtot[s * NW + warp] = inc;
+      __threadfence_block();
+      order = atomicAdd(&sm_cnt[s], 1u);
+    }
+    order = __shfl_sync(0xffffffffu, order, 31);
+    Map e = shfl_up_pod(inc, 1);
+    if (lane == 0) e = P::identity();
+    exc[s] = e;
+    if (order == (uint32_t)(NW - 1)) {
+      // last warp of the tile: scan the warp totals and publish the tile's record right away
+      __threadfence_block();
+      const Map w = lane < NW ? wtot[s * NW + lane] : P::identity();
       const Map winc = warp_scan_inclusive<P>(w, lane);
       Map wexc = shfl_up_pod(winc, 1);
       if (lane == 0) wexc = P::identity();
-      if (lane < NW) wpre[lane] = wexc;
-      const Map tile_agg = shfl_pod(winc, NW - 1);
-      State hin;
-      if (chunk == 0) {
-        hin = P::row_init(prm, row);
-      } else {
-        if (lane == 0) {
-          st_cg_pod(static_cast<Map*>(ws.agg) + ticket, tile_agg);
-          st_release_u32(ws.flags + ticket, 1u);
+      if (lane < NW) wpre[s * NW + lane] = wexc;
+      if (lane == NW - 1) {
+        sm_tagg[s] = winc;
+        sm_cnt[s] = 0;
+        uint64_t* slot = ws.slots + (size_t)c.ticket * P::SLOT_WORDS;
+        if (c.chunk > 0) {
+          slot_store(slot, winc, 1u);
+        } else if (nchunks > 1) {
+          slot_store(slot, P::apply(winc, P::row_init(prm, c.row)), 2u);
         }
-        hin = lookback<P>(ws, ticket, chunk, B, lane, failed);
       }
-      if (lane == 0) {
-        const State hend = P::apply(tile_agg, hin);
-        st_cg_pod(static_cast<State*>(ws.incl) + ticket, hend);
-        st_release_u32(ws.flags + ticket, 2u);
-        *sm_hin = hin;
-        if (chunk == nchunks - 1) P::row_final(prm, row, hend);
-      }
+      __syncwarp();
+      if (lane == NW - 1) { mbar_arrive(&agg_ready[s]); PTB_EV(3, p1); }
     }
-    bar_sync(1, NT);   // (B) incoming state and warp prefixes visible
+  };
 
-    const State hin = *sm_hin;
-    const Map pre = P::compose(wpre[warp], exc);
-    Partial part = th.finish(prm, P::apply(pre, hin), stage, tpos, nvalid);
+  auto phase2 = [&](auto tag) {
+    constexpr int s = decltype(tag)::value;
+    const TileCoords c = tile_coords<P>(tile_ticket[s], B, nchunks, T);
+    unsigned char* stage = smem + s * P::STAGE_BYTES;
+    const State hin = sm_hin[s];
+    if (tid == 0) PTB_EV(6, p2);
+    const Map pre = P::compose(wpre[s * NW + warp], exc[s]);
+    Partial part = P::finish(prm, P::apply(pre, hin), stage, tpos, c.row, c.t0, c.nvalid);
 
     if (P::HAS_PARTIAL) {
 #pragma unroll
@@ -384,39 +599,99 @@ scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, 
       }
       if (lane == 0) sm_part[warp] = part;
     }
-
     if (bulk) {
       fence_proxy_async_smem();
       mbar_arrive(&done[s]);
-      if (P::HAS_PARTIAL) {
-        bar_sync(1, NT);
-        if (tid == 0) {
-          Partial tot = sm_part[0];
-          for (int w2 = 1; w2 < NW; ++w2)
+      if (tid == 0) PTB_EV(7, p2);
+      if (P::HAS_PARTIAL) cta_sync(1, sync_par1);
+    } else {
+      cta_sync(1, sync_par1);
+      IoPlan io; io.nld = 0; io.nst = 0;
+      P::plan(prm, false, c.row, c.t0, c.nvalid, io);
 #pragma unroll
-            for (int i = 0; i < Partial::N; ++i) tot.v[i] += sm_part[w2].v[i];
-          static_cast<Partial*>(ws.partial)[(size_t)row * nchunks + chunk] = tot;
+      for (int i = 0; i < kMaxIo; ++i) {
+        if (i < io.nst) {
+          uint32_t* g = reinterpret_cast<uint32_t*>(io.st_g[i]);
+          const uint32_t* d = reinterpret_cast<const uint32_t*>(stage + io.st_soff[i]);
+          const uint32_t nw = io.st_bytes[i] >> 2;
+          for (uint32_t w = tid; w < nw; w += NT) g[w] = d[w];
         }
       }
-    } else {
-      bar_sync(1, NT);
-      if (P::HAS_PARTIAL && tid == 0) {
+      mbar_arrive(&done[s]);
+    }
+    if (P::HAS_PARTIAL) {
+      if (tid == 0) {
         Partial tot = sm_part[0];
         for (int w2 = 1; w2 < NW; ++w2)
 #pragma unroll
           for (int i = 0; i < Partial::N; ++i) tot.v[i] += sm_part[w2].v[i];
-        static_cast<Partial*>(ws.partial)[(size_t)row * nchunks + chunk] = tot;
+        static_cast<Partial*>(ws.partial)[(size_t)c.row * nchunks + c.chunk] = tot;
       }
-      IoPlan io; io.nld = 0; io.nst = 0;
-      P::plan(prm, false, row, t0, nvalid, io);
-      for (int i = 0; i < io.nst; ++i) {
-        uint32_t* g = reinterpret_cast<uint32_t*>(io.st_g[i]);
-        const uint32_t* d = reinterpret_cast<const uint32_t*>(stage + io.st_soff[i]);
-        const uint32_t nw = io.st_bytes[i] >> 2;
-        for (uint32_t w = tid; w < nw; w += NT) g[w] = d[w];
-      }
-      mbar_arrive(&done[s]);
+      cta_sync(2, sync_par2);   // sm_part may be rewritten by the next tile
     }
+  };
+
+  bool ended = false;
+  uint32_t idle = 0;
+  uint64_t idle_t0 = 0;
+  // On the plain-load path both phases contain barriers among the compute threads, so all warps
+  // must take the phases in one fixed order: a tile is aggregated only when nothing is pending.
+  const uint32_t ahead = bulk ? (uint32_t)D : 1u;
+  while (true) {
+    bool progressed = false;
+    if (p2 < p1) {
+      const int s2 = p2 % D;
+      // the warp prefixes need every warp's phase 1 (agg_ready), the incoming state the look-back
+      if (__all_sync(0xffffffffu, mbar_test_wait(&agg_ready[s2], (p2 / D) & 1u) &&
+                                      mbar_test_wait(&lb_done[s2], (p2 / D) & 1u))) {
+        switch (s2) {
+          case 0: phase2(StageTag<0>{}); break;
+          case 1: phase2(StageTag<1>{}); break;
+          case 2: if (D > 2) phase2(StageTag<(D > 2 ? 2 : 0)>{}); break;
+          default: if (D > 3) phase2(StageTag<(D > 3 ? 3 : 0)>{}); break;
+        }
+        ++p2;
+        progressed = true;
+      }
+    }
+    if (!progressed && !ended && p1 < p2 + ahead) {
+      const int s1 = p1 % D;
+      if (__all_sync(0xffffffffu, mbar_test_wait(&full[s1], (p1 / D) & 1u))) {
+        const uint32_t ticket = tile_ticket[s1];
+        if (ticket == kNoTile) {
+          ended = true;
+        } else {
+          switch (s1) {
+            case 0: phase1(StageTag<0>{}, ticket); break;
+            case 1: phase1(StageTag<1>{}, ticket); break;
+            case 2: if (D > 2) phase1(StageTag<(D > 2 ? 2 : 0)>{}, ticket); break;
+            default: if (D > 3) phase1(StageTag<(D > 3 ? 3 : 0)>{}, ticket); break;
+          }
+          ++p1;
+        }
+        progressed = true;
+      }
+    }
+    if (ended && p2 == p1) break;
+    if (progressed) {
+      idle = 0;
+    } else {
+      ++idle;
+      if (idle > 8) __nanosleep(idle > 64 ? 128 : 32);
+      if (idle == 256) idle_t0 = globaltimer_ns();
+      if (idle > 256 && (idle & 63u) == 0 &&
+          globaltimer_ns() - idle_t0 > ((*sm_abort) ? kWaitNsAfterError : kWaitNs)) {
+        if (lane == 0) { atomicOr(ws.error, kErrPipeTimeout); *sm_abort = 1; }
+        break;
+      }
+#ifdef PTB_PROFILE
+      t_c_idle += 1;
+#endif
+    }
+  }
+  PTB_PROF_END(t_c_total, tc0);
+  if (tid == 0) {
+    PTB_PROF_FLUSH(8, t_c_idle); PTB_PROF_FLUSH(10, t_c_total);
   }
 }
 
