@@ -89,6 +89,63 @@ int ptb_lpv_recur_bwd(int dtype, int64_t B, int64_t T, const void* a, int a_batc
                       void* grad_a, void* grad_zi, void* workspace, int64_t workspace_bytes,
                       uint32_t* status, ptb_stream_t stream);
 
+/* ---- 2x2, time-invariant ---------------------------------------------------------------------
+ * Replaces op philtorch::lti_recur2(A, zi, x) -> y (philtorch/csrc/host_recur2.cpp:166, CPU kernel
+ * philtorch/csrc/host_lti_recurN.cpp:63-108, CUDA philtorch/csrc/lti_recur2.cu:66-113).
+ * A: (B,2,2) if A_batched else (2,2), row-major; zi: (B,2); y: (B,T,2); zf: optional (B,2).
+ * x: (B,T,2), or (B,T) when x_scalar (the sequence feeds state 0 only, as
+ * philtorch/lti/ssm.py:187-191 does by zero-padding). */
+int ptb_lti_recur2_fwd(int dtype, int64_t B, int64_t T, const void* A, int A_batched, const void* zi,
+                       const void* x, int x_scalar, void* y, void* zf, void* workspace,
+                       int64_t workspace_bytes, uint32_t* status, ptb_stream_t stream);
+
+/* Fused adjoint; replaces LTIMatrixRecurrence.backward (philtorch/lti/ssm.py:67-96) and
+ * _lti_recurN_backward (philtorch/__init__.py:76-112).
+ *   g[t] = A^T g[t+1] + gy[t];  grad_x = g (state 0 only when x_scalar, then (B,T));
+ *   grad_zi = A^T g[0];  grad_A = sum_t g[t] (x) y[t-1], also summed over rows when !A_batched.
+ * grad_A: optional, (B,2,2) or (2,2); g_in: optional (B,2); grad_zi: optional (B,2). */
+int ptb_lti_recur2_bwd(int dtype, int64_t B, int64_t T, const void* A, int A_batched, const void* zi,
+                       const void* y, const void* gy, const void* g_in, int x_scalar, void* grad_x,
+                       void* grad_A, void* grad_zi, void* workspace, int64_t workspace_bytes,
+                       uint32_t* status, ptb_stream_t stream);
+
+/* ---- 2x2, per-sample coefficients --------------------------------------------------------------
+ * Replaces op philtorch::recur2(A, zi, x) -> y (philtorch/csrc/host_recur2.cpp:164, CPU kernel
+ * philtorch/csrc/host_recurN.cpp:236-281, CUDA philtorch/csrc/recur2.cu:69-117).
+ * A: (B,T,2,2) if A_batched else (T,2,2). */
+int ptb_lpv_recur2_fwd(int dtype, int64_t B, int64_t T, const void* A, int A_batched, const void* zi,
+                       const void* x, int x_scalar, void* y, void* zf, void* workspace,
+                       int64_t workspace_bytes, uint32_t* status, ptb_stream_t stream);
+
+/* Fused adjoint; replaces MatrixRecurrence.backward (philtorch/lpv/ssm.py:64-99) and
+ * _recurN_backward (philtorch/__init__.py:34-73).
+ *   g[t] = A[t+1]^T g[t+1] + gy[t];  grad_A[b,t] = g[t] (x) y[t-1];  grad_zi = A[0]^T g[0].
+ * grad_A: optional, always (B,T,2,2) (per row; a caller with shared coefficients sums over rows). */
+int ptb_lpv_recur2_bwd(int dtype, int64_t B, int64_t T, const void* A, int A_batched, const void* zi,
+                       const void* y, const void* gy, const void* g_in, int x_scalar, void* grad_x,
+                       void* grad_A, void* grad_zi, void* workspace, int64_t workspace_bytes,
+                       uint32_t* status, ptb_stream_t stream);
+
+/* ---- one second-order section, transposed direct form II, scalar in / scalar out --------------
+ * Replaces the whole lfilter(b, a, x, zi, form="tdf2") call stack for order <= 2
+ * (philtorch/lti/filtering.py:211-333 -> philtorch/lti/ssm.py:386-510 -> op lti_recur2), a0 = 1:
+ *   y[t] = h0[t-1] + b0 x[t];  h0[t] = -a1 h0[t-1] + h1[t-1] + (b1-b0 a1) x[t];
+ *   h1[t] = -a2 h0[t-1] + (b2-b0 a2) x[t].
+ * b: (B,3) / (3,), a: (B,2) / (2,) (coef_batched applies to both); zi: optional (B,2), zero if
+ * NULL; x, y: (B,T); zf: optional (B,2) final state. */
+int ptb_biquad_tdf2_fwd(int dtype, int64_t B, int64_t T, const void* b, const void* a, int coef_batched,
+                        const void* zi, const void* x, void* y, void* zf, void* workspace,
+                        int64_t workspace_bytes, uint32_t* status, ptb_stream_t stream);
+
+/* Adjoint of the section above (what autograd derives in the reference through the state-space
+ * glue).  Reads gy, x and the forward OUTPUT y only; no state sequence is stored.
+ * g_zf: optional (B,2) gradient w.r.t. zf; grad_x: (B,T); grad_b: optional (B,3)/(3,);
+ * grad_a: optional (B,2)/(2,); grad_zi: optional (B,2). */
+int ptb_biquad_tdf2_bwd(int dtype, int64_t B, int64_t T, const void* b, const void* a, int coef_batched,
+                        const void* x, const void* y, const void* gy, const void* g_zf, void* grad_x,
+                        void* grad_b, void* grad_a, void* grad_zi, void* workspace, int64_t workspace_bytes,
+                        uint32_t* status, ptb_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -44,9 +44,23 @@ for _n in ("ptb_lti_recur_bwd", "ptb_lpv_recur_bwd"):
     getattr(lib, _n).argtypes = _fo_bwd
     getattr(lib, _n).restype = _i32
 
+_so_fwd = [_i32, _i64, _i64, _vp, _i32, _vp, _vp, _i32, _vp, _vp] + _tail
+_so_bwd = [_i32, _i64, _i64, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp] + _tail
+for _n in ("ptb_lti_recur2_fwd", "ptb_lpv_recur2_fwd"):
+    getattr(lib, _n).argtypes = _so_fwd
+    getattr(lib, _n).restype = _i32
+for _n in ("ptb_lti_recur2_bwd", "ptb_lpv_recur2_bwd"):
+    getattr(lib, _n).argtypes = _so_bwd
+    getattr(lib, _n).restype = _i32
+lib.ptb_biquad_tdf2_fwd.argtypes = [_i32, _i64, _i64, _vp, _vp, _i32, _vp, _vp, _vp, _vp] + _tail
+lib.ptb_biquad_tdf2_fwd.restype = _i32
+lib.ptb_biquad_tdf2_bwd.argtypes = [_i32, _i64, _i64, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp] + _tail
+lib.ptb_biquad_tdf2_bwd.restype = _i32
+
 _status: dict[int, torch.Tensor] = {}
 
-ERROR_BITS = {1: "look-back wait expired", 2: "tile load wait expired", 4: "tile drain wait expired"}
+ERROR_BITS = {1: "look-back wait expired", 2: "tile load wait expired", 4: "tile drain wait expired",
+              8: "pipeline wait expired"}
 
 
 def dtype_code(t: torch.Tensor) -> int:

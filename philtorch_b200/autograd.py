@@ -118,3 +118,194 @@ class LPVRecurrence(Function):
         if grad_a is not None:
             fwd_x = fwd_x + _prev_states(init, out) * grad_a
         return LPVRecurrence.apply(a, fwd_init, fwd_x)
+
+
+def _prev_states2(zi: Tensor, y: Tensor) -> Tensor:
+    return torch.cat([zi.unsqueeze(1), y[:, :-1]], dim=1)
+
+
+def _pad_state0(x: Tensor) -> Tensor:
+    """(B,T) -> (B,T,2) with the sequence in state 0 (philtorch/lti/ssm.py:187-191)."""
+    return torch.stack([x, torch.zeros_like(x)], dim=-1)
+
+
+class LTIMatrixRecurrence(Function):
+    """h[t] = A h[t-1] + x[t] with A of shape (2,2) or (B,2,2), zi (B,2), x (B,T,2)."""
+
+    @staticmethod
+    def forward(A: Tensor, zi: Tensor, x: Tensor) -> Tensor:
+        if x.size(-1) != 2:
+            raise NotImplementedError("philtorch_b200 implements state dimensions 1 and 2 only")
+        return _ops.lti_recur2(A, zi, x)
+
+    @staticmethod
+    def setup_context(ctx: Any, inputs, output) -> None:
+        A, zi, _ = inputs
+        ctx.save_for_backward(A, zi, output)
+        ctx.save_for_forward(A, zi, output)
+
+    @staticmethod
+    def backward(ctx: Any, grad_y: Tensor):
+        A, zi, y = ctx.saved_tensors
+        need_A, need_zi, need_x = ctx.needs_input_grad
+        if not torch.is_grad_enabled():
+            gA, gzi, gx = _ops.lti_recur2_bwd(A, zi, y, grad_y, None, False, need_A, need_zi)
+            return _none_if_empty(gA, need_A), _none_if_empty(gzi, need_zi), _none_if_empty(gx, need_x)
+        AmT = A.mT
+        g = LTIMatrixRecurrence.apply(AmT, torch.zeros_like(zi), grad_y.flip(1)).flip(1)
+        grad_A = grad_zi = grad_x = None
+        if need_zi:
+            grad_zi = (AmT @ g[:, 0, :, None]).squeeze(-1)
+        if need_x:
+            grad_x = g
+        if need_A:
+            prev = _prev_states2(zi, y)
+            grad_A = g.flatten(0, 1).T @ prev.flatten(0, 1) if A.dim() == 2 else g.mT @ prev
+        return grad_A, grad_zi, grad_x
+
+    @staticmethod
+    def jvp(ctx: Any, grad_A, grad_zi, grad_x) -> Tensor:
+        A, zi, y = ctx.saved_tensors
+        fwd_zi = grad_zi if grad_zi is not None else torch.zeros_like(zi)
+        fwd_x = grad_x if grad_x is not None else torch.zeros_like(y)
+        if grad_A is not None:
+            prev = _prev_states2(zi, y)
+            dA = grad_A if grad_A.dim() == 2 else grad_A.unsqueeze(-3)
+            fwd_x = fwd_x + (dA @ prev.unsqueeze(-1)).squeeze(-1)
+        return LTIMatrixRecurrence.apply(A, fwd_zi, fwd_x)
+
+
+class MatrixRecurrence(Function):
+    """h[t] = A[t] h[t-1] + x[t] with A of shape (T,2,2) or (B,T,2,2), zi (B,2), x (B,T,2)."""
+
+    @staticmethod
+    def forward(A: Tensor, zi: Tensor, x: Tensor) -> Tensor:
+        if x.size(-1) != 2:
+            raise NotImplementedError("philtorch_b200 implements state dimensions 1 and 2 only")
+        return _ops.recur2(A, zi, x)
+
+    @staticmethod
+    def setup_context(ctx: Any, inputs, output) -> None:
+        A, zi, _ = inputs
+        ctx.save_for_backward(A, zi, output)
+        ctx.save_for_forward(A, zi, output)
+
+    @staticmethod
+    def backward(ctx: Any, grad_y: Tensor):
+        A, zi, y = ctx.saved_tensors
+        need_A, need_zi, need_x = ctx.needs_input_grad
+        if not torch.is_grad_enabled():
+            gA, gzi, gx = _ops.recur2_bwd(A, zi, y, grad_y, None, False, need_A, need_zi)
+            return _none_if_empty(gA, need_A), _none_if_empty(gzi, need_zi), _none_if_empty(gx, need_x)
+        AmT = A.mT
+        A_rev = torch.roll(AmT, shifts=-1, dims=-3).flip(-3)
+        g = MatrixRecurrence.apply(A_rev, torch.zeros_like(zi), grad_y.flip(1)).flip(1)
+        grad_A = grad_zi = grad_x = None
+        if need_zi:
+            grad_zi = (AmT[..., 0, :, :] @ g[:, 0, :, None]).squeeze(-1)
+        if need_x:
+            grad_x = g
+        if need_A:
+            prev = _prev_states2(zi, y)
+            grad_A = g.unsqueeze(-1) * prev.unsqueeze(-2)
+            if A.dim() == 3:
+                grad_A = grad_A.sum(0)
+        return grad_A, grad_zi, grad_x
+
+    @staticmethod
+    def jvp(ctx: Any, grad_A, grad_zi, grad_x) -> Tensor:
+        A, zi, y = ctx.saved_tensors
+        fwd_zi = grad_zi if grad_zi is not None else torch.zeros_like(zi)
+        fwd_x = grad_x if grad_x is not None else torch.zeros_like(y)
+        if grad_A is not None:
+            prev = _prev_states2(zi, y)
+            fwd_x = fwd_x + (grad_A @ prev.unsqueeze(-1)).squeeze(-1)
+        return MatrixRecurrence.apply(A, fwd_zi, fwd_x)
+
+
+class _ScalarInputMatrixRecurrence(Function):
+    """2x2 recurrence driven by a scalar sequence x (B,T) into state 0; ``lpv`` selects per-sample
+    coefficients.  Same result as zero-padding x to (B,T,2) (philtorch/lti/ssm.py:187-191,
+    philtorch/lpv/ssm.py:197-201) without materialising the padded tensor or its gradient."""
+
+    @staticmethod
+    def forward(A: Tensor, zi: Tensor, x: Tensor, lpv: bool) -> Tensor:
+        return _ops.recur2_sx(A, zi, x) if lpv else _ops.lti_recur2_sx(A, zi, x)
+
+    @staticmethod
+    def setup_context(ctx: Any, inputs, output) -> None:
+        A, zi, _, lpv = inputs
+        ctx.lpv = lpv
+        ctx.save_for_backward(A, zi, output)
+
+    @staticmethod
+    def backward(ctx: Any, grad_y: Tensor):
+        A, zi, y = ctx.saved_tensors
+        need_A, need_zi, need_x, _ = ctx.needs_input_grad
+        if not torch.is_grad_enabled():
+            op = _ops.recur2_bwd if ctx.lpv else _ops.lti_recur2_bwd
+            gA, gzi, gx = op(A, zi, y, grad_y, None, True, need_A, need_zi)
+            return _none_if_empty(gA, need_A), _none_if_empty(gzi, need_zi), _none_if_empty(gx, need_x), None
+        raise RuntimeError("double backward through the scalar-input fast path is not supported; "
+                           "pass x with shape (B, T, 2)")
+
+
+def matrix_recurrence_scalar_input(A: Tensor, zi: Tensor, x: Tensor, lpv: bool) -> Tensor:
+    """2x2 recurrence fed by a scalar sequence (B,T) through the fused scalar-input kernels."""
+    return _ScalarInputMatrixRecurrence.apply(A, zi, x, lpv)
+
+
+class BiquadTDF2(Function):
+    """One transposed-direct-form-II second-order section, (b, a, zi, x) -> (y, zf)."""
+
+    @staticmethod
+    def forward(b: Tensor, a: Tensor, zi: Optional[Tensor], x: Tensor):
+        return _ops.biquad_tdf2(b, a, zi, x)
+
+    @staticmethod
+    def setup_context(ctx: Any, inputs, output) -> None:
+        b, a, zi, x = inputs
+        y, _ = output
+        ctx.has_zi = zi is not None
+        ctx.save_for_backward(b, a, x, y, *([zi] if zi is not None else []))
+
+    @staticmethod
+    def backward(ctx: Any, grad_y: Tensor, grad_zf: Tensor):
+        b, a, x, y, *rest = ctx.saved_tensors
+        need_b, need_a, need_zi, need_x = ctx.needs_input_grad
+        need_zi = need_zi and ctx.has_zi
+        if torch.is_grad_enabled():
+            # higher-order graph: recompute through the differentiable state-space form
+            zi = rest[0] if rest else None
+            with torch.enable_grad():
+                y2, zf2 = _biquad_reference_form(b, a, zi, x)
+                ins = [t for t, n in ((b, need_b), (a, need_a), (zi, need_zi), (x, need_x)) if n]
+                gs = list(torch.autograd.grad([y2, zf2], ins, [grad_y, grad_zf], create_graph=True,
+                                              allow_unused=True))
+            out = []
+            for n in (need_b, need_a, need_zi, need_x):
+                out.append(gs.pop(0) if n else None)
+            return tuple(out)
+        if grad_y is None:
+            grad_y = torch.zeros_like(x)
+        gb, ga, gzi, gx = _ops.biquad_tdf2_bwd(b, a, x, y, grad_y, grad_zf, need_b or need_a, need_zi)
+        return (_none_if_empty(gb, need_b), _none_if_empty(ga, need_a), _none_if_empty(gzi, need_zi),
+                _none_if_empty(gx, need_x))
+
+
+def _biquad_reference_form(b: Tensor, a: Tensor, zi: Optional[Tensor], x: Tensor):
+    """The same section written with differentiable pieces (2x2 recurrence + elementwise glue),
+    following philtorch/lti/filtering.py:304-317 and philtorch/lti/ssm.py:466-504."""
+    B = x.shape[0]
+    a1, a2 = a[..., 0], a[..., 1]
+    zero, one = torch.zeros_like(a1), torch.ones_like(a1)
+    At = torch.stack([torch.stack([-a1, one], -1), torch.stack([-a2, zero], -1)], -2)
+    Bv = b[..., 1:] - b[..., :1] * a
+    if zi is None:
+        zi = x.new_zeros(B, 2)
+    Bx = x.unsqueeze(-1) * (Bv if Bv.dim() == 1 else Bv.unsqueeze(1))
+    h = LTIMatrixRecurrence.apply(At, zi, Bx)
+    h0 = torch.cat([zi[:, None, 0], h[:, :-1, 0]], dim=1)
+    b0 = b[..., 0]
+    y = h0 + (b0 if b0.dim() == 0 else b0.unsqueeze(1)) * x
+    return y, h[:, -1, :]

@@ -1,0 +1,262 @@
+// Scan-engine policies for ONE second-order section in transposed direct form II, scalar in and
+// scalar out, with the state-space glue of the reference folded into the kernel:
+//     y[t]  = h0[t-1] + b0 x[t]
+//     h0[t] = -a1 h0[t-1] + h1[t-1] + (b1 - b0 a1) x[t]
+//     h1[t] = -a2 h0[t-1]           + (b2 - b0 a2) x[t]
+// (philtorch/lti/filtering.py:304-317 builds A^T = [[-a1,1],[-a2,0]], B = b[1:] - b0 a, D = b0 and
+// philtorch/lti/ssm.py:466-504 materialises B x, runs the 2x2 recurrence, delays it by one sample
+// and adds D x: five extra passes over (B,T,2) tensors that never leave the chip here.)
+//
+// Adjoint (lam[t] = dL/dh[t], M = A^T):
+//     lam[t-1] = M^T lam[t] + e0 gy[t],   lam[T-1] = grad of the final state (0 if unused)
+//     grad_x[t] = b0 gy[t] + B . lam[t]
+//     grad_b0 = sum gy x - a1 sum x lam0 - a2 sum x lam1,  grad_b1 = sum x lam0,  grad_b2 = sum x lam1
+//     grad_a1 = -sum y lam0,  grad_a2 = -sum y lam1        (y[t] = h0[t-1] + b0 x[t] absorbs both paths)
+//     grad_zi = lam[-1]
+// so the backward pass reads gy, x and y only: no state is stored or recomputed.
+#pragma once
+#include "second_order.cuh"
+
+namespace ptb {
+
+template <class S>
+struct BqCoef {
+  S b0, B0, B1, na1, na2;
+  __device__ __forceinline__ void load(const S* b, int64_t bs, const S* a, int64_t as, int64_t row) {
+    const S* pb = b + row * bs;
+    const S* pa = a + row * as;
+    b0 = __ldg(pb);
+    const S b1 = __ldg(pb + 1), b2 = __ldg(pb + 2), a1 = __ldg(pa), a2 = __ldg(pa + 1);
+    B0 = b1 - b0 * a1;
+    B1 = b2 - b0 * a2;
+    na1 = -a1;
+    na2 = -a2;
+  }
+};
+
+template <class S>
+struct BqFwdParams {
+  const S* b; int64_t b_stride;   // 3 or 0
+  const S* a; int64_t a_stride;   // 2 or 0
+  const S* zi;                    // optional (B,2)
+  const S* x;
+  S* y;
+  S* zf;                          // optional (B,2)
+  int64_t T;
+};
+
+template <class S, int CH, int STAGES_, int MIN_CTAS_, int LBW_>
+struct BqFwd : MatAffine<S> {
+  using Alg = MatAffine<S>;
+  using typename Alg::Map;
+  using typename Alg::State;
+  using Partial = Pod<S, 1>;
+  using Params = BqFwdParams<S>;
+  static constexpr int V = Vec16<S>::V;
+  static constexpr int NT = 256;
+  static constexpr int SPT = V * CH;
+  static constexpr int TILE = NT * SPT;
+  static constexpr int STAGES = STAGES_;
+  static constexpr int MIN_CTAS = MIN_CTAS_;
+  static constexpr int LBW = LBW_;
+  static constexpr bool REVERSE = false;
+  static constexpr bool HAS_PARTIAL = false;
+  static constexpr int SLOT_WORDS = Words<Map>::W;
+  static constexpr int X_OFF = 0;
+  static constexpr int STAGE_BYTES = TILE * (int)sizeof(S);
+
+  static __device__ __forceinline__ void plan(const Params& p, bool, int64_t row, int64_t t0, int nvalid,
+                                              IoPlan& io) {
+    const uint32_t bytes = (uint32_t)nvalid * sizeof(S);
+    io.load(X_OFF, p.x + row * p.T + t0, bytes);
+    io.store(X_OFF, p.y + row * p.T + t0, bytes);
+  }
+  static __device__ __forceinline__ State row_init(const Params& p, int64_t row) {
+    State s = Alg::zero_state();
+    if (p.zi) { s.v[0] = __ldg(p.zi + row * 2); s.v[1] = __ldg(p.zi + row * 2 + 1); }
+    return s;
+  }
+  static __device__ __forceinline__ void row_final(const Params& p, int64_t row, const State& s) {
+    if (p.zf) { p.zf[row * 2] = s.v[0]; p.zf[row * 2 + 1] = s.v[1]; }
+  }
+  static __device__ __forceinline__ int load_x(const unsigned char* stage, int tpos, int nvalid, S* x) {
+    const int p0 = tpos * SPT;
+    int nv = nvalid - p0;
+    nv = nv < 0 ? 0 : (nv > SPT ? SPT : nv);
+    const unsigned char* px = stage + X_OFF + (size_t)p0 * sizeof(S);
+#pragma unroll
+    for (int c = 0; c < CH; ++c) VecIO<S, V>::ld(px + 16 * c, &x[c * V]);
+    return nv;
+  }
+  static __device__ __forceinline__ Map aggregate(const Params& p, const unsigned char* stage, int tpos,
+                                                  int64_t row, int64_t, int nvalid) {
+    BqCoef<S> k;
+    k.load(p.b, p.b_stride, p.a, p.a_stride, row);
+    S x[SPT];
+    const int nv = load_x(stage, tpos, nvalid, x);
+    Map m = Alg::identity();
+#pragma unroll
+    for (int j = 0; j < SPT; ++j) {
+      if (j < nv) {
+        Map n;   // M = [na1 1; na2 0]
+        n.v[0] = k.na1 * m.v[0] + m.v[2];
+        n.v[1] = k.na1 * m.v[1] + m.v[3];
+        n.v[2] = k.na2 * m.v[0];
+        n.v[3] = k.na2 * m.v[1];
+        n.v[4] = k.na1 * m.v[4] + m.v[5] + k.B0 * x[j];
+        n.v[5] = k.na2 * m.v[4] + k.B1 * x[j];
+        m = n;
+      }
+    }
+    return m;
+  }
+  static __device__ __forceinline__ Partial finish(const Params& p, const State& in, unsigned char* stage,
+                                                   int tpos, int64_t row, int64_t, int nvalid) {
+    BqCoef<S> k;
+    k.load(p.b, p.b_stride, p.a, p.a_stride, row);
+    S x[SPT];
+    const int nv = load_x(stage, tpos, nvalid, x);
+    S h0 = in.v[0], h1 = in.v[1];
+#pragma unroll
+    for (int j = 0; j < SPT; ++j) {
+      if (j < nv) {
+        const S xj = x[j];
+        x[j] = h0 + k.b0 * xj;
+        const S n0 = k.na1 * h0 + h1 + k.B0 * xj;
+        h1 = k.na2 * h0 + k.B1 * xj;
+        h0 = n0;
+      }
+    }
+    unsigned char* px = stage + X_OFF + (size_t)tpos * SPT * sizeof(S);
+#pragma unroll
+    for (int c = 0; c < CH; ++c) VecIO<S, V>::st(px + 16 * c, &x[c * V]);
+    Partial r; r.v[0] = S(0); return r;
+  }
+};
+
+template <class S>
+struct BqBwdParams {
+  const S* b; int64_t b_stride;
+  const S* a; int64_t a_stride;
+  const S* x;
+  const S* y;        // forward output; needed only when coefficient gradients are wanted
+  const S* gy;
+  const S* g_in;     // optional (B,2): gradient w.r.t. the final state
+  S* grad_x;
+  S* grad_zi;        // optional (B,2)
+  int64_t T;
+  int want_coef;
+};
+
+template <class S, int CH, int STAGES_, int MIN_CTAS_, int LBW_>
+struct BqBwd : MatAffine<S> {
+  using Alg = MatAffine<S>;
+  using typename Alg::Map;
+  using typename Alg::State;
+  using Partial = Pod<S, 5>;   // sum gy x, sum x lam0, sum x lam1, sum y lam0, sum y lam1
+  using Params = BqBwdParams<S>;
+  static constexpr int V = Vec16<S>::V;
+  static constexpr int NT = 256;
+  static constexpr int SPT = V * CH;
+  static constexpr int TILE = NT * SPT;
+  static constexpr int STAGES = STAGES_;
+  static constexpr int MIN_CTAS = MIN_CTAS_;
+  static constexpr int LBW = LBW_;
+  static constexpr bool REVERSE = true;
+  static constexpr bool HAS_PARTIAL = true;
+  static constexpr int SLOT_WORDS = Words<Map>::W;
+  static constexpr int SLOT = TILE * (int)sizeof(S);
+  static constexpr int G_OFF = 0;          // gy in, grad_x out
+  static constexpr int X_OFF = SLOT;       // x in
+  static constexpr int Y_OFF = 2 * SLOT;   // y in
+  static constexpr int STAGE_BYTES = 3 * SLOT;
+
+  static __device__ __forceinline__ void plan(const Params& p, bool, int64_t row, int64_t t0, int nvalid,
+                                              IoPlan& io) {
+    const uint32_t bytes = (uint32_t)nvalid * sizeof(S);
+    io.load(G_OFF, p.gy + row * p.T + t0, bytes);
+    if (p.want_coef) {
+      io.load(X_OFF, p.x + row * p.T + t0, bytes);
+      io.load(Y_OFF, p.y + row * p.T + t0, bytes);
+    }
+    io.store(G_OFF, p.grad_x + row * p.T + t0, bytes);
+  }
+  static __device__ __forceinline__ State row_init(const Params& p, int64_t row) {
+    State s = Alg::zero_state();
+    if (p.g_in) { s.v[0] = __ldg(p.g_in + row * 2); s.v[1] = __ldg(p.g_in + row * 2 + 1); }
+    return s;
+  }
+  static __device__ __forceinline__ void row_final(const Params& p, int64_t row, const State& s) {
+    if (p.grad_zi) { p.grad_zi[row * 2] = s.v[0]; p.grad_zi[row * 2 + 1] = s.v[1]; }
+  }
+  static __device__ __forceinline__ int load_slot(const unsigned char* stage, int off, int tpos, int nvalid, S* r) {
+    const int p0 = tpos * SPT;
+    int nv = nvalid - p0;
+    nv = nv < 0 ? 0 : (nv > SPT ? SPT : nv);
+    const unsigned char* q = stage + off + (size_t)p0 * sizeof(S);
+#pragma unroll
+    for (int c = 0; c < CH; ++c) VecIO<S, V>::ld(q + 16 * c, &r[c * V]);
+    return nv;
+  }
+  // map over lam (time descending): lam' = M^T lam + e0 gy,  M^T = [na1 na2; 1 0]
+  static __device__ __forceinline__ Map aggregate(const Params& p, const unsigned char* stage, int tpos,
+                                                  int64_t row, int64_t, int nvalid) {
+    BqCoef<S> k;
+    k.load(p.b, p.b_stride, p.a, p.a_stride, row);
+    S g[SPT];
+    const int nv = load_slot(stage, G_OFF, tpos, nvalid, g);
+    Map m = Alg::identity();
+#pragma unroll
+    for (int j = SPT - 1; j >= 0; --j) {
+      if (j < nv) {
+        Map n;
+        n.v[0] = k.na1 * m.v[0] + k.na2 * m.v[2];
+        n.v[1] = k.na1 * m.v[1] + k.na2 * m.v[3];
+        n.v[2] = m.v[0];
+        n.v[3] = m.v[1];
+        n.v[4] = k.na1 * m.v[4] + k.na2 * m.v[5] + g[j];
+        n.v[5] = m.v[4];
+        m = n;
+      }
+    }
+    return m;
+  }
+  static __device__ __forceinline__ Partial finish(const Params& p, const State& in, unsigned char* stage,
+                                                   int tpos, int64_t row, int64_t, int nvalid) {
+    BqCoef<S> k;
+    k.load(p.b, p.b_stride, p.a, p.a_stride, row);
+    S g[SPT], x[SPT], y[SPT];
+    const int nv = load_slot(stage, G_OFF, tpos, nvalid, g);
+    if (p.want_coef) {
+      load_slot(stage, X_OFF, tpos, nvalid, x);
+      load_slot(stage, Y_OFF, tpos, nvalid, y);
+    }
+    S l0 = in.v[0], l1 = in.v[1];
+    Partial acc;
+#pragma unroll
+    for (int i = 0; i < 5; ++i) acc.v[i] = S(0);
+#pragma unroll
+    for (int j = SPT - 1; j >= 0; --j) {
+      if (j < nv) {
+        const S gj = g[j];
+        g[j] = k.b0 * gj + k.B0 * l0 + k.B1 * l1;
+        if (p.want_coef) {
+          acc.v[0] += gj * x[j];
+          acc.v[1] += x[j] * l0;
+          acc.v[2] += x[j] * l1;
+          acc.v[3] += y[j] * l0;
+          acc.v[4] += y[j] * l1;
+        }
+        const S n0 = k.na1 * l0 + k.na2 * l1 + gj;
+        l1 = l0;
+        l0 = n0;
+      }
+    }
+    unsigned char* pg = stage + G_OFF + (size_t)tpos * SPT * sizeof(S);
+#pragma unroll
+    for (int c = 0; c < CH; ++c) VecIO<S, V>::st(pg + 16 * c, &g[c * V]);
+    return acc;
+  }
+};
+
+}  // namespace ptb

@@ -2,7 +2,7 @@
 // See include/philtorch_b200.h for the contract of every entry point.
 #include "../../include/philtorch_b200.h"
 
-#include "first_order.cuh"
+#include "biquad.cuh"
 
 #include <algorithm>
 
@@ -77,7 +77,7 @@ static int launch_scan(const typename P::Params& prm, int64_t B, int64_t T, bool
   if (!cache.ready[dev]) {
     PTB_CUDA(cudaFuncSetAttribute(scan_kernel<P>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     int occ = 0;
-    PTB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, scan_kernel<P>, P::NT + 32 * (P::STAGES + 1), smem));
+    PTB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, scan_kernel<P>, P::NT + 32 * (P::LBW + 1), smem));
     int sms = 0;
     PTB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     cache.ctas_per_sm[dev] = std::max(occ, 1);
@@ -86,38 +86,61 @@ static int launch_scan(const typename P::Params& prm, int64_t B, int64_t T, bool
   }
   const int64_t resident = (int64_t)cache.sms[dev] * cache.ctas_per_sm[dev];
   const unsigned grid = (unsigned)std::min<int64_t>(ntiles, resident);
-  scan_kernel<P><<<grid, P::NT + 32 * (P::STAGES + 1), smem, st>>>(prm, ws, (uint32_t)B, T, (uint32_t)nchunks, (uint32_t)ntiles,
+  scan_kernel<P><<<grid, P::NT + 32 * (P::LBW + 1), smem, st>>>(prm, ws, (uint32_t)B, T, (uint32_t)nchunks, (uint32_t)ntiles,
                                                 bulk ? 1 : 0);
   PTB_CUDA(cudaGetLastError());
   return PTB_OK;
 }
 
-// Sums per-tile partials: part[row][chunk][N] -> out[row][N] (batched) or out[N] (all rows).
+// Sums per-tile partials part[row][chunk][N] per row (batched) or over all rows, in double, and
+// hands the N sums to an epilogue that writes the result.
 template <class S, int N>
-__global__ void reduce_partials_kernel(const S* __restrict__ part, S* __restrict__ out, int64_t B,
-                                       int64_t nchunks, int batched) {
+struct StoreSums {
+  S* out;
+  __device__ void operator()(int64_t row, const double* acc) const {
+    for (int i = 0; i < N; ++i) out[row * N + i] = (S)acc[i];
+  }
+};
+// sums {gy x, x lam0, x lam1, y lam0, y lam1} -> grad_b (3), grad_a (2) of a TDF-II section
+template <class S>
+struct BiquadCoefGrads {
+  const S* a; int64_t a_stride;
+  S* grad_b; S* grad_a;
+  __device__ void operator()(int64_t row, const double* acc) const {
+    const double a1 = (double)a[row * a_stride], a2 = (double)a[row * a_stride + 1];
+    if (grad_b) {
+      grad_b[row * 3 + 0] = (S)(acc[0] - a1 * acc[1] - a2 * acc[2]);
+      grad_b[row * 3 + 1] = (S)acc[1];
+      grad_b[row * 3 + 2] = (S)acc[2];
+    }
+    if (grad_a) {
+      grad_a[row * 2 + 0] = (S)(-acc[3]);
+      grad_a[row * 2 + 1] = (S)(-acc[4]);
+    }
+  }
+};
+
+template <class S, int N, class Epi>
+__global__ void reduce_partials_kernel(const S* __restrict__ part, int64_t B, int64_t nchunks, int batched,
+                                       Epi epi) {
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
+  double acc[N];
+#pragma unroll
+  for (int i = 0; i < N; ++i) acc[i] = 0.0;
   if (batched) {
     const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + warp;
     if (row >= B) return;
-    double acc[N];
-#pragma unroll
-    for (int i = 0; i < N; ++i) acc[i] = 0.0;
     for (int64_t c = lane; c < nchunks; c += 32)
 #pragma unroll
       for (int i = 0; i < N; ++i) acc[i] += (double)part[(row * nchunks + c) * N + i];
 #pragma unroll
-    for (int i = 0; i < N; ++i) {
+    for (int i = 0; i < N; ++i)
 #pragma unroll
       for (int d = 16; d > 0; d >>= 1) acc[i] += __shfl_down_sync(0xffffffffu, acc[i], d);
-      if (lane == 0) out[row * N + i] = (S)acc[i];
-    }
+    if (lane == 0) epi(row, acc);
   } else {
     __shared__ double sm[32][N];
-    double acc[N];
-#pragma unroll
-    for (int i = 0; i < N; ++i) acc[i] = 0.0;
     const int64_t total = B * nchunks;
     for (int64_t c = threadIdx.x; c < total; c += blockDim.x)
 #pragma unroll
@@ -129,23 +152,25 @@ __global__ void reduce_partials_kernel(const S* __restrict__ part, S* __restrict
       if (lane == 0) sm[warp][i] = acc[i];
     }
     __syncthreads();
-    if (threadIdx.x < N) {
-      double t = 0.0;
-      for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += sm[w][threadIdx.x];
-      out[threadIdx.x] = (S)t;
+    if (threadIdx.x == 0) {
+      double t[N];
+      for (int i = 0; i < N; ++i) {
+        t[i] = 0.0;
+        for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t[i] += sm[w][i];
+      }
+      epi(0, t);
     }
   }
 }
 
-template <class S, int N>
-static int launch_reduce(const void* part, void* out, int64_t B, int64_t nchunks, int batched, cudaStream_t st) {
+template <class S, int N, class Epi>
+static int launch_reduce(const void* part, int64_t B, int64_t nchunks, int batched, Epi epi, cudaStream_t st) {
   if (batched) {
     const int wpb = 4;
-    reduce_partials_kernel<S, N><<<(unsigned)((B + wpb - 1) / wpb), wpb * 32, 0, st>>>(
-        static_cast<const S*>(part), static_cast<S*>(out), B, nchunks, 1);
+    reduce_partials_kernel<S, N, Epi><<<(unsigned)((B + wpb - 1) / wpb), wpb * 32, 0, st>>>(
+        static_cast<const S*>(part), B, nchunks, 1, epi);
   } else {
-    reduce_partials_kernel<S, N><<<1, 1024, 0, st>>>(static_cast<const S*>(part), static_cast<S*>(out), B,
-                                                    nchunks, 0);
+    reduce_partials_kernel<S, N, Epi><<<1, 1024, 0, st>>>(static_cast<const S*>(part), B, nchunks, 0, epi);
   }
   PTB_CUDA(cudaGetLastError());
   return PTB_OK;
@@ -159,13 +184,16 @@ static int launch_reduce(const void* part, void* out, int64_t B, int64_t nchunks
 #define PTB_FO_FWD_STAGES 3
 #define PTB_FO_FWD_CTAS 3
 #endif
+#ifndef PTB_FO_LBW
+#define PTB_FO_LBW 1   // look-back warps per CTA: 1, or one per stage
+#endif
 #ifndef PTB_FO_BWD_CH
 #define PTB_FO_BWD_CH 3
 #define PTB_FO_BWD_STAGES 3
 #define PTB_FO_BWD_CTAS 2
 #endif
-template <class S, bool LPV> using FoFwdP = FoFwd<S, PTB_FO_FWD_CH, PTB_FO_FWD_STAGES, PTB_FO_FWD_CTAS, LPV>;
-template <class S, bool LPV> using FoBwdP = FoBwd<S, PTB_FO_BWD_CH, PTB_FO_BWD_STAGES, PTB_FO_BWD_CTAS, LPV>;
+template <class S, bool LPV> using FoFwdP = FoFwd<S, PTB_FO_FWD_CH, PTB_FO_FWD_STAGES, PTB_FO_FWD_CTAS, (PTB_FO_LBW == 1 ? 1 : PTB_FO_FWD_STAGES), LPV>;
+template <class S, bool LPV> using FoBwdP = FoBwd<S, PTB_FO_BWD_CH, PTB_FO_BWD_STAGES, PTB_FO_BWD_CTAS, (PTB_FO_LBW == 1 ? 1 : PTB_FO_BWD_STAGES), LPV>;
 
 template <class S, bool LPV>
 static int fo_fwd(int64_t B, int64_t T, const void* a, int a_batched, const void* zi, int zi_batched,
@@ -209,7 +237,114 @@ static int fo_bwd(int64_t B, int64_t T, const void* a, int a_batched, const void
   int64_t nchunks = 0;
   int rc = launch_scan<P>(p, B, T, bulk, ws, wsb, status, st, &partial, &nchunks);
   if (rc != PTB_OK) return rc;
-  if (!LPV && grad_a) rc = launch_reduce<S, 1>(partial, grad_a, B, nchunks, a_batched, st);
+  if (!LPV && grad_a)
+    rc = launch_reduce<S, 1>(partial, B, nchunks, a_batched, StoreSums<S, 1>{static_cast<S*>(grad_a)}, st);
+  return rc;
+}
+
+// ---------------------------------------------------------------------------- 2x2
+// samples per thread (odd), stages, CTAs per SM
+template <class S> struct SoCfg;
+template <> struct SoCfg<float> { static constexpr int FWD_NS = 7, BWD_NS = 5; };
+template <> struct SoCfg<double> { static constexpr int FWD_NS = 3, BWD_NS = 3; };
+template <class S, bool LPV, bool XS> using SoFwdP = SoFwd<S, SoCfg<S>::FWD_NS, 2, 2, 1, LPV, XS>;
+template <class S, bool LPV, bool XS> using SoBwdP = SoBwd<S, SoCfg<S>::BWD_NS, 2, 2, 1, LPV, XS>;
+
+template <class S, bool LPV, bool XS>
+static int so_fwd(int64_t B, int64_t T, const void* A, int A_batched, const void* zi, const void* x, void* y,
+                  void* zf, void* ws, int64_t wsb, uint32_t* status, cudaStream_t st) {
+  using P = SoFwdP<S, LPV, XS>;
+  typename P::Params p;
+  p.A = static_cast<const S*>(A);
+  p.a_row_stride = A_batched ? (LPV ? 4 * T : 4) : 0;
+  p.zi = static_cast<const S*>(zi);
+  p.zi_stride = 2;
+  p.x = static_cast<const S*>(x);
+  p.y = static_cast<S*>(y);
+  p.zf = static_cast<S*>(zf);
+  p.T = T;
+  const bool bulk = aligned16(x) && aligned16(y) && (!LPV || aligned16(A)) &&
+                    (T * (XS ? 1 : 2) * sizeof(S)) % 16 == 0;
+  return launch_scan<P>(p, B, T, bulk, ws, wsb, status, st, nullptr, nullptr);
+}
+
+template <class S, bool LPV, bool XS>
+static int so_bwd(int64_t B, int64_t T, const void* A, int A_batched, const void* zi, const void* y,
+                  const void* gy, const void* g_in, void* grad_x, void* grad_A, void* grad_zi, void* ws,
+                  int64_t wsb, uint32_t* status, cudaStream_t st) {
+  using P = SoBwdP<S, LPV, XS>;
+  typename P::Params p;
+  p.A = static_cast<const S*>(A);
+  p.a_row_stride = A_batched ? (LPV ? 4 * T : 4) : 0;
+  p.zi = static_cast<const S*>(zi);
+  p.zi_stride = 2;
+  p.y = static_cast<const S*>(y);
+  p.gy = static_cast<const S*>(gy);
+  p.g_in = static_cast<const S*>(g_in);
+  p.grad_x = static_cast<S*>(grad_x);
+  p.grad_A = LPV ? static_cast<S*>(grad_A) : nullptr;
+  p.grad_zi = static_cast<S*>(grad_zi);
+  p.T = T;
+  p.want_gA = grad_A != nullptr;
+  const bool bulk = aligned16(gy) && aligned16(grad_x) && (!LPV || aligned16(A)) &&
+                    (!p.want_gA || (aligned16(y) && (!LPV || aligned16(grad_A)))) &&
+                    (T * (XS ? 1 : 2) * sizeof(S)) % 16 == 0;
+  void* partial = nullptr;
+  int64_t nchunks = 0;
+  int rc = launch_scan<P>(p, B, T, bulk, ws, wsb, status, st, &partial, &nchunks);
+  if (rc != PTB_OK) return rc;
+  if (!LPV && grad_A)
+    rc = launch_reduce<S, 4>(partial, B, nchunks, A_batched, StoreSums<S, 4>{static_cast<S*>(grad_A)}, st);
+  return rc;
+}
+
+// ---------------------------------------------------------------------------- TDF-II section
+template <class S> using BqFwdP = BqFwd<S, 3, 4, 2, 1>;
+template <class S> using BqBwdP = BqBwd<S, 3, 3, 2, 1>;
+
+template <class S>
+static int bq_fwd(int64_t B, int64_t T, const void* b, const void* a, int batched, const void* zi, const void* x,
+                  void* y, void* zf, void* ws, int64_t wsb, uint32_t* status, cudaStream_t st) {
+  using P = BqFwdP<S>;
+  typename P::Params p;
+  p.b = static_cast<const S*>(b); p.b_stride = batched ? 3 : 0;
+  p.a = static_cast<const S*>(a); p.a_stride = batched ? 2 : 0;
+  p.zi = static_cast<const S*>(zi);
+  p.x = static_cast<const S*>(x);
+  p.y = static_cast<S*>(y);
+  p.zf = static_cast<S*>(zf);
+  p.T = T;
+  const bool bulk = aligned16(x) && aligned16(y) && (T * sizeof(S)) % 16 == 0;
+  return launch_scan<P>(p, B, T, bulk, ws, wsb, status, st, nullptr, nullptr);
+}
+
+template <class S>
+static int bq_bwd(int64_t B, int64_t T, const void* b, const void* a, int batched, const void* x, const void* y,
+                  const void* gy, const void* g_zf, void* grad_x, void* grad_b, void* grad_a, void* grad_zi,
+                  void* ws, int64_t wsb, uint32_t* status, cudaStream_t st) {
+  using P = BqBwdP<S>;
+  typename P::Params p;
+  p.b = static_cast<const S*>(b); p.b_stride = batched ? 3 : 0;
+  p.a = static_cast<const S*>(a); p.a_stride = batched ? 2 : 0;
+  p.x = static_cast<const S*>(x);
+  p.y = static_cast<const S*>(y);
+  p.gy = static_cast<const S*>(gy);
+  p.g_in = static_cast<const S*>(g_zf);
+  p.grad_x = static_cast<S*>(grad_x);
+  p.grad_zi = static_cast<S*>(grad_zi);
+  p.T = T;
+  p.want_coef = (grad_b != nullptr) || (grad_a != nullptr);
+  const bool bulk = aligned16(gy) && aligned16(grad_x) && (!p.want_coef || (aligned16(x) && aligned16(y))) &&
+                    (T * sizeof(S)) % 16 == 0;
+  void* partial = nullptr;
+  int64_t nchunks = 0;
+  int rc = launch_scan<P>(p, B, T, bulk, ws, wsb, status, st, &partial, &nchunks);
+  if (rc != PTB_OK) return rc;
+  if (p.want_coef) {
+    BiquadCoefGrads<S> epi{static_cast<const S*>(a), batched ? 2 : 0, static_cast<S*>(grad_b),
+                           static_cast<S*>(grad_a)};
+    rc = launch_reduce<S, 5>(partial, B, nchunks, batched, epi, st);
+  }
   return rc;
 }
 
@@ -294,6 +429,80 @@ int ptb_lpv_recur_bwd(int dtype, int64_t B, int64_t T, const void* a, int a_batc
   if (!a || !gy || !grad_x || (grad_a && (!y || !zi))) return PTB_ERR_ARG;
   PTB_DISPATCH(dtype, (fo_bwd<S, true>(B, T, a, a_batched, zi, zi_batched, y, gy, g_in, grad_x, grad_a,
                                        grad_zi, workspace, workspace_bytes, status, (cudaStream_t)stream)));
+}
+
+#define PTB_SO_DISPATCH(dtype, FN, ...)                                                      \
+  switch (dtype) {                                                                          \
+    case PTB_F32: return x_scalar ? FN<float, kLpv, true>(__VA_ARGS__) : FN<float, kLpv, false>(__VA_ARGS__);   \
+    case PTB_F64: return x_scalar ? FN<double, kLpv, true>(__VA_ARGS__) : FN<double, kLpv, false>(__VA_ARGS__); \
+    default: return PTB_ERR_ARG;                                                            \
+  }
+
+int ptb_lti_recur2_fwd(int dtype, int64_t B, int64_t T, const void* A, int A_batched, const void* zi,
+                       const void* x, int x_scalar, void* y, void* zf, void* workspace,
+                       int64_t workspace_bytes, uint32_t* status, ptb_stream_t stream) {
+  if (B < 0 || T < 0) return PTB_ERR_ARG;
+  if (B == 0 || T == 0) return PTB_OK;
+  if (!A || !zi || !x || !y) return PTB_ERR_ARG;
+  constexpr bool kLpv = false;
+  PTB_SO_DISPATCH(dtype, so_fwd, B, T, A, A_batched, zi, x, y, zf, workspace, workspace_bytes, status,
+                  (cudaStream_t)stream);
+}
+
+int ptb_lpv_recur2_fwd(int dtype, int64_t B, int64_t T, const void* A, int A_batched, const void* zi,
+                       const void* x, int x_scalar, void* y, void* zf, void* workspace,
+                       int64_t workspace_bytes, uint32_t* status, ptb_stream_t stream) {
+  if (B < 0 || T < 0) return PTB_ERR_ARG;
+  if (B == 0 || T == 0) return PTB_OK;
+  if (!A || !zi || !x || !y) return PTB_ERR_ARG;
+  constexpr bool kLpv = true;
+  PTB_SO_DISPATCH(dtype, so_fwd, B, T, A, A_batched, zi, x, y, zf, workspace, workspace_bytes, status,
+                  (cudaStream_t)stream);
+}
+
+int ptb_lti_recur2_bwd(int dtype, int64_t B, int64_t T, const void* A, int A_batched, const void* zi,
+                       const void* y, const void* gy, const void* g_in, int x_scalar, void* grad_x,
+                       void* grad_A, void* grad_zi, void* workspace, int64_t workspace_bytes,
+                       uint32_t* status, ptb_stream_t stream) {
+  if (B < 0 || T < 0) return PTB_ERR_ARG;
+  if (B == 0 || T == 0) return PTB_OK;
+  if (!A || !gy || !grad_x || (grad_A && (!y || !zi))) return PTB_ERR_ARG;
+  constexpr bool kLpv = false;
+  PTB_SO_DISPATCH(dtype, so_bwd, B, T, A, A_batched, zi, y, gy, g_in, grad_x, grad_A, grad_zi, workspace,
+                  workspace_bytes, status, (cudaStream_t)stream);
+}
+
+int ptb_lpv_recur2_bwd(int dtype, int64_t B, int64_t T, const void* A, int A_batched, const void* zi,
+                       const void* y, const void* gy, const void* g_in, int x_scalar, void* grad_x,
+                       void* grad_A, void* grad_zi, void* workspace, int64_t workspace_bytes,
+                       uint32_t* status, ptb_stream_t stream) {
+  if (B < 0 || T < 0) return PTB_ERR_ARG;
+  if (B == 0 || T == 0) return PTB_OK;
+  if (!A || !gy || !grad_x || (grad_A && (!y || !zi))) return PTB_ERR_ARG;
+  constexpr bool kLpv = true;
+  PTB_SO_DISPATCH(dtype, so_bwd, B, T, A, A_batched, zi, y, gy, g_in, grad_x, grad_A, grad_zi, workspace,
+                  workspace_bytes, status, (cudaStream_t)stream);
+}
+
+int ptb_biquad_tdf2_fwd(int dtype, int64_t B, int64_t T, const void* b, const void* a, int coef_batched,
+                        const void* zi, const void* x, void* y, void* zf, void* workspace,
+                        int64_t workspace_bytes, uint32_t* status, ptb_stream_t stream) {
+  if (B < 0 || T < 0) return PTB_ERR_ARG;
+  if (B == 0 || T == 0) return PTB_OK;
+  if (!b || !a || !x || !y) return PTB_ERR_ARG;
+  PTB_DISPATCH(dtype, (bq_fwd<S>(B, T, b, a, coef_batched, zi, x, y, zf, workspace, workspace_bytes, status,
+                                 (cudaStream_t)stream)));
+}
+
+int ptb_biquad_tdf2_bwd(int dtype, int64_t B, int64_t T, const void* b, const void* a, int coef_batched,
+                        const void* x, const void* y, const void* gy, const void* g_zf, void* grad_x,
+                        void* grad_b, void* grad_a, void* grad_zi, void* workspace, int64_t workspace_bytes,
+                        uint32_t* status, ptb_stream_t stream) {
+  if (B < 0 || T < 0) return PTB_ERR_ARG;
+  if (B == 0 || T == 0) return PTB_OK;
+  if (!b || !a || !gy || !grad_x || ((grad_b || grad_a) && (!x || !y))) return PTB_ERR_ARG;
+  PTB_DISPATCH(dtype, (bq_bwd<S>(B, T, b, a, coef_batched, x, y, gy, g_zf, grad_x, grad_b, grad_a, grad_zi,
+                                 workspace, workspace_bytes, status, (cudaStream_t)stream)));
 }
 
 }  // extern "C"

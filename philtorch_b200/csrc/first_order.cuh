@@ -72,7 +72,7 @@ struct FoFwdParams {
   int64_t T;
 };
 
-template <class S, int CH, int STAGES_, int MIN_CTAS_, bool LPV>
+template <class S, int CH, int STAGES_, int MIN_CTAS_, int LBW_, bool LPV>
 struct FoFwd : ScalarAffine<S> {
   using Alg = ScalarAffine<S>;
   using typename Alg::Map;
@@ -86,6 +86,7 @@ struct FoFwd : ScalarAffine<S> {
   static constexpr int TILE = NT * SPT;
   static constexpr int STAGES = STAGES_;
   static constexpr int MIN_CTAS = MIN_CTAS_;
+  static constexpr int LBW = LBW_;
   static constexpr bool REVERSE = false;
   static constexpr bool HAS_PARTIAL = false;
   static constexpr int SLOT_WORDS = Words<Map>::W;
@@ -174,7 +175,7 @@ struct FoBwdParams {
   int want_ga;
 };
 
-template <class S, int CH, int STAGES_, int MIN_CTAS_, bool LPV>
+template <class S, int CH, int STAGES_, int MIN_CTAS_, int LBW_, bool LPV>
 struct FoBwd : ScalarAffine<S> {
   using Alg = ScalarAffine<S>;
   using typename Alg::Map;
@@ -188,6 +189,7 @@ struct FoBwd : ScalarAffine<S> {
   static constexpr int TILE = NT * SPT;
   static constexpr int STAGES = STAGES_;
   static constexpr int MIN_CTAS = MIN_CTAS_;
+  static constexpr int LBW = LBW_;
   static constexpr bool REVERSE = true;
   static constexpr bool HAS_PARTIAL = !LPV;
   static constexpr int SLOT_WORDS = Words<Map>::W;

@@ -8,23 +8,22 @@
 //     predecessor of a tile (same row, previous chunk) is B tickets older and has normally
 //     published its end state before the tile asks for it; a CTA only ever waits on OLDER
 //     tickets, which are held by running CTAs, so the look-back cannot deadlock.
-//   * One CTA = P::NT compute threads + one look-back warp + one DMA warp, decoupled by
+//   * One CTA = P::NT compute threads + P::LBW look-back warps + one DMA warp, decoupled by
 //     shared-memory mbarriers (no CTA-wide barrier on the bulk path):
 //       DMA warp (lane 0)   owns the ticket counter, issues the 1-D bulk (TMA) loads of a tile's
 //                           operands into a ring of P::STAGES shared-memory stages and, once the
 //                           compute warps have written the tile's results back into the stage,
 //                           the bulk stores.
-//       compute warps       phase 1 of tile n+1: every thread folds its P::SPT consecutive samples
-//                           into one affine map, maps are scanned with warp shuffles, warp totals
-//                           go to shared memory.  Phase 2 of tile n: with the tile's incoming
-//                           state known, every thread replays its samples from its own incoming
-//                           state and writes the results into the stage.  Phase 1 of the next
-//                           tile runs BEFORE phase 2 of the current one, which hides the
-//                           look-back latency.
-//       look-back warp      scans the warp totals, publishes the tile aggregate (flag 1), looks
-//                           back over predecessor tiles -- 32 at a time -- until it meets an end
-//                           state (flag 2), publishes the tile's end state and hands the
-//                           incoming state to the compute warps.
+//       compute warps       event loop.  Phase 1 (as soon as a tile's operands have landed): every
+//                           thread folds its P::SPT consecutive samples into one affine map, maps
+//                           are scanned with warp shuffles, the last warp to arrive scans the warp
+//                           totals and PUBLISHES the tile aggregate (flag 1) at once, so successors
+//                           never wait for this CTA's look-back.  Phase 2 (as soon as the tile's
+//                           incoming state is known): every thread replays its samples from its
+//                           own incoming state and writes the results into the stage.
+//       look-back warps     look back over predecessor tiles -- 32 at a time, one per lane --
+//                           until they meet an end state (flag 2), hand the incoming state to
+//                           the compute warps and publish the tile's end state.
 //   * P::SPT is chosen so that the per-thread footprint of every staged array is an ODD number of
 //     16-byte (or 8-byte) units: the strided 128-bit / 64-bit shared-memory accesses are then
 //     bank-conflict free without swizzling.
@@ -177,38 +176,14 @@ __device__ __forceinline__ typename P::Map warp_scan_inclusive(typename P::Map m
 }
 
 // Look-back executed by all 32 lanes of a look-back warp; returns (in every lane) the state
-// entering the tile.  It may start before the tile's own operands have landed, so it first
-// polls, with one lane only, the nearest predecessor until that tile has published anything:
-// this keeps the polling traffic in L2 negligible.  In the usual case the record found is an end
-// state and the look-back is over; otherwise windows of 32 predecessors (one per lane, all
-// loads in flight together) are folded until one contains an end state.
+// entering the tile.  Windows of 32 predecessors (one per lane, all loads in flight together)
+// are folded until one contains an end state; in the usual case that is the nearest one.
 template <class P>
 __device__ __forceinline__ typename P::State lookback(const Workspace& ws, uint32_t ticket,
                                                       uint32_t chunk, uint32_t B, int lane,
                                                       uint32_t& failed) {
   using Map = typename P::Map;
   using State = typename P::State;
-  {
-    uint32_t f = 0;
-    State st0 = P::zero_state();
-    if (lane == 0) {
-      Map m0;
-      const uint64_t* slot = ws.slots + ((size_t)ticket - B) * P::SLOT_WORDS;
-      const uint64_t limit = failed ? kWaitNsAfterError : kWaitNs;
-      uint64_t t0 = 0;
-      for (uint32_t it = 0;; ++it) {
-        uint64_t raw[Words<Map>::W];
-        slot_fetch<Map>(slot, raw);
-        f = slot_decode<Map, State>(raw, m0, st0);
-        if (f != 0) break;
-        __nanosleep(it > 64 ? 256 : 64);
-        if (it == 64) t0 = globaltimer_ns();
-        if (it > 64 && globaltimer_ns() - t0 > limit) break;
-      }
-    }
-    f = __shfl_sync(0xffffffffu, f, 0);
-    if (f == 2u) return shfl_pod(st0, 0);
-  }
   Map acc = P::identity();
   uint32_t base = 1;
   State result;
@@ -286,8 +261,7 @@ struct EngineSmem {
   static constexpr int kDoneOff = kFullOff + 8 * D;        // u64 done[D]      results written to the stage
   static constexpr int kAggOff = kDoneOff + 8 * D;         // u64 agg_ready[D] tile aggregate known
   static constexpr int kLbOff = kAggOff + 8 * D;           // u64 lb_done[D]   incoming state known
-  static constexpr int kIssuedOff = kLbOff + 8 * D;        // u64 issued[D]    ticket of the stage known
-  static constexpr int kSyncOff = kIssuedOff + 8 * D;      // u64 sync_bar[3]  barriers among the compute threads
+  static constexpr int kSyncOff = kLbOff + 8 * D;          // u64 sync_bar[3]  barriers among the compute threads
   static constexpr int kTicketOff = kSyncOff + 8 * 3;      // u32 tile_ticket[D]
   static constexpr int kCntOff = kTicketOff + 4 * D;       // u32 arrived[D]
   static constexpr int kAbortOff = kCntOff + 4 * D;        // u32 abort, u32 trace counter
@@ -318,10 +292,8 @@ __device__ __forceinline__ TileCoords tile_coords(uint32_t ticket, uint32_t B, u
   return c;
 }
 
-template <int I> struct StageTag { static constexpr int value = I; };
-
 template <class P>
-__global__ void __launch_bounds__(P::NT + 32 * (P::STAGES + 1), P::MIN_CTAS)
+__global__ void __launch_bounds__(P::NT + 32 * (P::LBW + 1), P::MIN_CTAS)
 scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, const int64_t T,
             const uint32_t nchunks, const uint32_t ntiles, const int bulk) {
   using Map = typename P::Map;
@@ -333,7 +305,6 @@ scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, 
   uint64_t* done = reinterpret_cast<uint64_t*>(smem + L::kDoneOff);
   uint64_t* agg_ready = reinterpret_cast<uint64_t*>(smem + L::kAggOff);
   uint64_t* lb_done = reinterpret_cast<uint64_t*>(smem + L::kLbOff);
-  uint64_t* issued = reinterpret_cast<uint64_t*>(smem + L::kIssuedOff);
   uint64_t* sync_bar = reinterpret_cast<uint64_t*>(smem + L::kSyncOff);
   volatile uint32_t* tile_ticket = reinterpret_cast<volatile uint32_t*>(smem + L::kTicketOff);
   uint32_t* sm_cnt = reinterpret_cast<uint32_t*>(smem + L::kCntOff);
@@ -354,7 +325,7 @@ scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, 
   constexpr int NT = P::NT;
   constexpr int NW = NT / 32;
   constexpr int D = P::STAGES;
-  static_assert(D >= 2 && D <= 4, "the compute warps keep one prefix per stage in registers");
+  static_assert(D >= 2, "at least two stages");
 
   if (tid == 0) {
     for (int s = 0; s < D; ++s) {
@@ -362,7 +333,6 @@ scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, 
       mbar_init(&done[s], NT + 1);   // compute threads + the stage's look-back warp
       mbar_init(&agg_ready[s], 1);
       mbar_init(&lb_done[s], 1);
-      mbar_init(&issued[s], 1);
       sm_cnt[s] = 0;
     }
     for (int i = 0; i < 3; ++i) mbar_init(&sync_bar[i], NT);
@@ -371,7 +341,9 @@ scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, 
   }
   __syncthreads();
 
-  if (warp == NW + D) {
+  constexpr int LBW = P::LBW;
+  static_assert(LBW == 1 || LBW == D, "one look-back warp, or one per stage");
+  if (warp == NW + LBW) {
     // ======================================================================= DMA warp
     if (lane != 0) return;
     uint32_t failed = 0;
@@ -413,7 +385,6 @@ scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, 
       next = atomicAdd(ws.ticket, 1u);
       tile_ticket[s] = ticket;
       PTB_EV(1, n);
-      mbar_arrive(&issued[s]);   // the stage's look-back warp may start right away
       if (bulk) {
         const TileCoords c = tile_coords<P>(ticket, B, nchunks, T);
         IoPlan io; io.nld = 0; io.nst = 0;
@@ -431,14 +402,13 @@ scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, 
         mbar_arrive(&full[s]);
       }
     }
-    // n = first index without a tile: put the end marker into every stage (each look-back warp
-    // watches its own), draining the tiles still held by the stages on the way
+    // n = first index without a tile: put the end marker into every stage (with one look-back
+    // warp per stage each watches its own), draining the tiles still held by the stages on the way
     for (uint32_t k = 0; k < (uint32_t)D; ++k) {
       const uint32_t m = n + k;
       const int s = m % D;
       if (k > 0 && m >= (uint32_t)D) drain(m - D);
       tile_ticket[s] = kNoTile;
-      mbar_arrive(&issued[s]);
       mbar_arrive(&full[s]);
     }
     if (failed || *sm_abort) {
@@ -455,32 +425,33 @@ scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, 
 
   if (warp >= NW) {
     // ======================================================================= look-back warps
-    // One per stage.  The look-back of a tile needs nothing from the tile itself, so it starts as
-    // soon as the DMA warp has assigned the ticket and overlaps the tile's own load.
-    const int s = warp - NW;
+    // Warp w handles the CTA's tiles w, w + LBW, w + 2 LBW, ...: all of them with LBW == 1, those of
+    // stage w with LBW == D (the look-backs of the stages then overlap one another).
     uint32_t failed = 0;
-    PTB_PROF_DECL(t_lb_wait_issue); PTB_PROF_DECL(t_lb_wait_agg); PTB_PROF_DECL(t_lb_look); PTB_PROF_DECL(t_lb_total);
+    PTB_PROF_DECL(t_lb_wait_full); PTB_PROF_DECL(t_lb_wait_agg); PTB_PROF_DECL(t_lb_look); PTB_PROF_DECL(t_lb_total);
     PTB_PROF_BEGIN(tlb0);
-    for (uint32_t par = 0;; par ^= 1u) {
+    for (uint32_t n = warp - NW;; n += LBW) {
+      const int s = n % D;
+      const uint32_t par = (n / D) & 1u;
       uint64_t limit = (failed || *sm_abort) ? kWaitNsAfterError : kWaitNs;
       PTB_PROF_BEGIN(tf0);
-      if (!mbar_wait_bounded(&issued[s], par, limit)) {
+      if (!mbar_wait_bounded(&full[s], par, limit)) {
         if (lane == 0) { atomicOr(ws.error, kErrLoadTimeout); *sm_abort = 1; }
         break;
       }
-      PTB_PROF_END(t_lb_wait_issue, tf0);
+      PTB_PROF_END(t_lb_wait_full, tf0);
       const uint32_t ticket = tile_ticket[s];
       if (ticket == kNoTile) break;
       const TileCoords c = tile_coords<P>(ticket, B, nchunks, T);
       PTB_PROF_BEGIN(tl0);
-      if (lane == 0) PTB_EV(4, (par ? 1 : 0));
+      if (lane == 0) PTB_EV(4, n);
       State hin;
       if (c.chunk == 0) hin = P::row_init(prm, c.row);   // its end state is published in phase 1
       else hin = lookback<P>(ws, ticket, c.chunk, B, lane, failed);
       if (lane == 0) {
         sm_hin[s] = hin;
         mbar_arrive(&lb_done[s]);
-        PTB_EV(5, s);
+        PTB_EV(5, n);
       }
       PTB_PROF_END(t_lb_look, tl0);
       limit = (failed || *sm_abort) ? kWaitNsAfterError : kWaitNs;
@@ -501,8 +472,8 @@ scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, 
       __syncwarp();
     }
     PTB_PROF_END(t_lb_total, tlb0);
-    if (lane == 0 && s == 0) {
-      PTB_PROF_FLUSH(4, t_lb_wait_issue); PTB_PROF_FLUSH(5, t_lb_wait_agg); PTB_PROF_FLUSH(6, t_lb_look);
+    if (lane == 0 && warp == NW) {
+      PTB_PROF_FLUSH(4, t_lb_wait_full); PTB_PROF_FLUSH(5, t_lb_wait_agg); PTB_PROF_FLUSH(6, t_lb_look);
       PTB_PROF_FLUSH(7, t_lb_total);
     }
     return;
@@ -513,7 +484,7 @@ scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, 
   // is known; otherwise aggregate (phase 1) the next tile as soon as its operands have landed.
   // Every landed tile therefore publishes its aggregate without waiting for older look-backs.
   const int tpos = P::REVERSE ? (NT - 1 - tid) : tid;
-  Map exc[D];          // this thread's exclusive prefix inside the tile held by each stage
+  Map exc[D];                // this thread's exclusive prefix inside the tile held by each stage
   uint32_t p1 = 0, p2 = 0;   // tiles aggregated / finished so far by this warp
   uint32_t sync_par0 = 0, sync_par1 = 0, sync_par2 = 0;
   // barrier among the compute threads, bounded like every other wait of the kernel
@@ -527,8 +498,7 @@ scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, 
   PTB_PROF_DECL(t_c_idle); PTB_PROF_DECL(t_c_total);
   PTB_PROF_BEGIN(tc0);
 
-  auto phase1 = [&](auto tag, uint32_t ticket) {
-    constexpr int s = decltype(tag)::value;
+  auto phase1 = [&](const int s, uint32_t ticket) {
     const TileCoords c = tile_coords<P>(ticket, B, nchunks, T);
     unsigned char* stage = smem + s * P::STAGE_BYTES;
     if (tid == 0) PTB_EV(2, p1);
@@ -557,7 +527,11 @@ scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, 
     order = __shfl_sync(0xffffffffu, order, 31);
     Map e = shfl_up_pod(inc, 1);
     if (lane == 0) e = P::identity();
-    exc[s] = e;
+    // this thread's exclusive prefix inside its warp, kept for phase 2 (select chain: the stage
+    // index is dynamic, the register array must be indexed statically)
+#pragma unroll
+    for (int i = 0; i < D; ++i)
+      if (i == s) exc[i] = e;
     if (order == (uint32_t)(NW - 1)) {
       // last warp of the tile: scan the warp totals and publish the tile's record right away
       __threadfence_block();
@@ -581,13 +555,16 @@ scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, 
     }
   };
 
-  auto phase2 = [&](auto tag) {
-    constexpr int s = decltype(tag)::value;
+  auto phase2 = [&](const int s) {
     const TileCoords c = tile_coords<P>(tile_ticket[s], B, nchunks, T);
     unsigned char* stage = smem + s * P::STAGE_BYTES;
     const State hin = sm_hin[s];
     if (tid == 0) PTB_EV(6, p2);
-    const Map pre = P::compose(wpre[s * NW + warp], exc[s]);
+    Map e = exc[0];
+#pragma unroll
+    for (int i = 1; i < D; ++i)
+      if (i == s) e = exc[i];
+    const Map pre = P::compose(wpre[s * NW + warp], e);
     Partial part = P::finish(prm, P::apply(pre, hin), stage, tpos, c.row, c.t0, c.nvalid);
 
     if (P::HAS_PARTIAL) {
@@ -644,12 +621,7 @@ scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, 
       // the warp prefixes need every warp's phase 1 (agg_ready), the incoming state the look-back
       if (__all_sync(0xffffffffu, mbar_test_wait(&agg_ready[s2], (p2 / D) & 1u) &&
                                       mbar_test_wait(&lb_done[s2], (p2 / D) & 1u))) {
-        switch (s2) {
-          case 0: phase2(StageTag<0>{}); break;
-          case 1: phase2(StageTag<1>{}); break;
-          case 2: if (D > 2) phase2(StageTag<(D > 2 ? 2 : 0)>{}); break;
-          default: if (D > 3) phase2(StageTag<(D > 3 ? 3 : 0)>{}); break;
-        }
+        phase2(s2);
         ++p2;
         progressed = true;
       }
@@ -661,12 +633,7 @@ scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, 
         if (ticket == kNoTile) {
           ended = true;
         } else {
-          switch (s1) {
-            case 0: phase1(StageTag<0>{}, ticket); break;
-            case 1: phase1(StageTag<1>{}, ticket); break;
-            case 2: if (D > 2) phase1(StageTag<(D > 2 ? 2 : 0)>{}, ticket); break;
-            default: if (D > 3) phase1(StageTag<(D > 3 ? 3 : 0)>{}, ticket); break;
-          }
+          phase1(s1, ticket);
           ++p1;
         }
         progressed = true;
@@ -677,7 +644,7 @@ scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, 
       idle = 0;
     } else {
       ++idle;
-      if (idle > 8) __nanosleep(idle > 64 ? 128 : 32);
+      if (idle > 32) __nanosleep(idle > 256 ? 100 : 20);
       if (idle == 256) idle_t0 = globaltimer_ns();
       if (idle > 256 && (idle & 63u) == 0 &&
           globaltimer_ns() - idle_t0 > ((*sm_abort) ? kWaitNsAfterError : kWaitNs)) {

@@ -1,3 +1,4 @@
 from .recur import LPVRecurrence, linear_recurrence
+from .ssm import MatrixRecurrence, state_space_recursion
 
-__all__ = ["LPVRecurrence", "linear_recurrence"]
+__all__ = ["LPVRecurrence", "MatrixRecurrence", "linear_recurrence", "state_space_recursion"]

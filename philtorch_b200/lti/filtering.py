@@ -1,0 +1,159 @@
+"""Time-invariant IIR filtering (orders 1 and 2) on the GPU kernels.
+
+``lfilter`` / ``filtfilt`` / ``lfilter_zi`` keep the signatures of philtorch/lti/filtering.py.
+The default transposed-direct-form-II path runs ONE fused kernel per direction for a section
+(scalar in, scalar out); ``form="df2"`` goes through the 2x2 state-space kernels.  The FIR-based
+forms (``df1`` / ``tdf1``), orders above two and the ``diag_ssm`` backend are outside this package.
+"""
+from __future__ import annotations
+
+from typing import Optional, Union
+
+import torch
+import torch.nn.functional as F
+from torch import Tensor
+
+from ..autograd import BiquadTDF2
+from ..mat import companion
+from .ssm import state_space
+
+__all__ = ["lfilter", "filtfilt", "lfilter_zi"]
+
+
+def _pad_to_order2(b: Tensor, a: Tensor):
+    """Coefficient vectors of a section of order <= 2 padded to b: (...,3), a: (...,2)."""
+    order = max(b.size(-1) - 1, a.size(-1))
+    if order > 2:
+        raise NotImplementedError(f"filter order {order}: philtorch_b200 implements first- and second-order "
+                                  "sections only (cascade them for higher orders)")
+    if order < 1:
+        raise ValueError("the filter needs at least one recursive or delayed coefficient")
+    if b.size(-1) < 3:
+        b = F.pad(b, (0, 3 - b.size(-1)))
+    if a.size(-1) < 2:
+        a = F.pad(a, (0, 2 - a.size(-1)))
+    return b, a, order
+
+
+def _tdf2_section(b: Tensor, a: Tensor, x: Tensor, zi: Optional[Tensor]):
+    b2, a2, order = _pad_to_order2(b, a)
+    if b2.dim() != a2.dim():   # one batched, one shared
+        B = x.size(0)
+        b2 = b2.expand(B, -1) if b2.dim() == 1 else b2
+        a2 = a2.expand(B, -1) if a2.dim() == 1 else a2
+    zi2 = None
+    if zi is not None:
+        if zi.dim() == 1:
+            zi = zi.unsqueeze(0).expand(x.size(0), -1)
+        zi2 = F.pad(zi, (0, 2 - zi.size(-1))) if zi.size(-1) < 2 else zi
+    y, zf = BiquadTDF2.apply(b2, a2, zi2, x)
+    if zi is None:
+        return y
+    return y, zf[:, :order]
+
+
+def _ssm_lfilter(b: Tensor, a: Tensor, x: Tensor, zi: Optional[Tensor] = None, form: str = "tdf2", **kwargs):
+    kwargs.pop("unroll_factor", None)   # block size of the reference's Python scan; meaningless here
+    if kwargs:
+        raise TypeError(f"unexpected keyword arguments: {sorted(kwargs)}")
+    if form == "tdf2":
+        return _tdf2_section(b, a, x, zi)
+    if form == "df2":
+        if b.size(-1) < a.size(-1) + 1:
+            b = F.pad(b, (0, a.size(-1) + 1 - b.size(-1)))
+        elif b.size(-1) > a.size(-1) + 1:
+            a = F.pad(a, (0, b.size(-1) - a.size(-1) - 1))
+        if a.size(-1) > 2:
+            raise NotImplementedError("philtorch_b200 implements first- and second-order sections only")
+        b0 = b[..., :1]
+        return state_space(companion(a), x, B=None, C=b[..., 1:] - b0 * a, D=b[..., 0], zi=zi, out_idx=None)
+    if form in ("df1", "tdf1"):
+        raise NotImplementedError(f"form={form!r} is built on an FIR convolution, which is outside this package; "
+                                  "use 'tdf2' or 'df2'")
+    raise ValueError(f"Unknown filter form: {form}")
+
+
+def lfilter(b: Tensor, a: Tensor, x: Tensor, zi: Optional[Tensor] = None, form: str = "tdf2",
+            backend: str = "ssm", **kwargs) -> Union[Tensor, tuple[Tensor, Tensor]]:
+    """Apply a batch of time-invariant IIR filters (``a0 = 1`` implicit, ``a`` excludes it).
+
+    Args:
+        b: numerator, (B, Mb+1) or (Mb+1,).
+        a: denominator without a0, (B, Ma) or (Ma,); max(Mb, Ma) <= 2.
+        x: input, (B, N) or (N,), CUDA, float32 or float64.
+        zi: initial state, (B, max(Mb, Ma)) or (max(Mb, Ma),); when given, ``(y, zf)`` is returned.
+        form: 'tdf2' (default, fused kernel) or 'df2'.
+        backend: only 'ssm'.
+        **kwargs: ``unroll_factor`` is accepted for compatibility and ignored.
+    """
+    squeeze_first = (x.dim() == 1) & (b.dim() == 1) & (a.dim() == 1) & ((zi is None) or (zi.dim() == 1))
+    if x.dim() == 1:
+        x = x.unsqueeze(0)
+    elif x.dim() > 2:
+        raise ValueError("Input signal x must be 1D or 2D.")
+    assert b.dim() in (1, 2), "Numerator coefficients b must be 1D or 2D."
+    assert a.dim() in (1, 2), "Denominator coefficients a must be 1D or 2D."
+    if backend != "ssm":
+        if backend == "diag_ssm":
+            raise NotImplementedError("backend='diag_ssm' (complex eigen-domain filtering) is outside this package")
+        raise ValueError(f"Unknown backend: {backend}")
+    y = _ssm_lfilter(b, a, x, zi, form=form, **kwargs)
+    if isinstance(y, tuple):
+        y, zf = y
+        if squeeze_first:
+            y, zf = y.squeeze(0), zf.squeeze(0)
+        return y, zf
+    return y.squeeze(0) if squeeze_first else y
+
+
+def lfilter_zi(a: Tensor, b: Optional[Tensor] = None, transpose: bool = True) -> Tensor:
+    """Initial state for which a constant unit input gives a constant output (step steady state),
+    as philtorch/lti/filtering.py:107-142: solves (I - A) zi = B for the chosen structure."""
+    assert a.dim() >= 1, "Denominator coefficients a must be at least 1D."
+    if not transpose:
+        n = a.size(-1) + 1
+        A = companion(a)
+        Bv = a.new_zeros(n - 1)
+        Bv[0] = 1.0
+    elif b is not None:
+        assert b.dim() >= 1, "Numerator coefficients b must be at least 1D."
+        n = max(b.size(-1), a.size(-1) + 1)
+        if b.size(-1) < n:
+            b = F.pad(b, (0, n - b.size(-1)))
+        if a.size(-1) < n - 1:
+            a = F.pad(a, (0, n - 1 - a.size(-1)))
+        A = companion(a).mT
+        Bv = b[..., 1:] - b[..., :1] * a
+    else:
+        raise ValueError("Numerator coefficients b must be provided for transpose=True.")
+    IminusA = torch.eye(n - 1, device=a.device, dtype=a.dtype) - A
+    if IminusA.dim() == 2 and Bv.dim() > 1:
+        IminusA = IminusA.expand(*Bv.shape[:-1], -1, -1)
+    return torch.linalg.solve(IminusA, Bv)
+
+
+def filtfilt(b: Tensor, a: Tensor, x: Tensor, padmode: Optional[str] = "replicate", padlen: Optional[int] = None,
+             method: str = "pad", irlen: Optional[int] = None, form: str = "tdf2", **kwargs) -> Tensor:
+    """Zero-phase filtering: forward pass, time reversal, second pass (philtorch/lti/filtering.py:413-484).
+    Edges are padded by ``padlen`` (default 3 x taps) samples in ``padmode`` and both passes start
+    from the step steady state scaled by the first sample."""
+    assert method in ("pad", "gust"), "Method must be either 'pad' or 'gust'."
+    if method == "gust":
+        raise NotImplementedError("Gustafsson's method is not implemented yet.")
+    if padmode is None:
+        padlen = 0
+    ntaps = max(b.size(-1), a.size(-1) + 1)
+    edge = 3 * ntaps if padlen is None else padlen
+    assert x.size(-1) > edge, f"Input signal length {x.size(-1)} must be greater than pad length {edge}."
+    if edge > 0 and padmode is not None:
+        ext = F.pad(x.view(-1, x.size(-1)), (edge, edge), mode=padmode)
+        if x.dim() == 1:
+            ext = ext.squeeze(0)
+    else:
+        ext = x
+    zi = lfilter_zi(a, b, transpose=(form == "tdf2"))
+    y, _ = lfilter(b, a, ext, zi=zi * ext[..., :1], form=form, **kwargs)
+    y, _ = lfilter(b, a, y.flip(-1), zi=zi * y[..., -1:], form=form, **kwargs)
+    if edge > 0:
+        y = y[..., edge:-edge]
+    return y.flip(-1)

@@ -159,6 +159,172 @@ def _(a, zi, y, gy, g_in, need_a, need_zi):
             torch.empty_like(y, memory_format=torch.contiguous_format))
 
 
+# =============================================================================== 2x2
+# x is (B,T,2), or (B,T) for the *_sx ops (scalar sequence feeding state 0 only).
+for _n in ("lti_recur2", "lti_recur2_sx", "recur2", "recur2_sx"):
+    _LIB.define(f"{_n}(Tensor A, Tensor zi, Tensor x) -> Tensor", tags=_TAGS)
+for _n in ("lti_recur2_bwd", "recur2_bwd"):
+    _LIB.define(f"{_n}(Tensor A, Tensor zi, Tensor y, Tensor gy, Tensor? g_in, bool x_scalar, bool need_A, "
+                "bool need_zi) -> (Tensor, Tensor, Tensor)", tags=_TAGS)
+
+
+def _check_recur2(A: Tensor, zi: Tensor, x: Tensor, lpv: bool, sx: bool) -> None:
+    torch._check(A.dim() >= 2 and A.shape[-1] == 2 and A.shape[-2] == 2, lambda: "A must be square.")
+    if lpv:
+        torch._check(A.dim() in (3, 4), lambda: "A must be 3D or 4D.")
+    else:
+        torch._check(A.dim() in (2, 3), lambda: "A must be 2D or 3D.")
+    torch._check(zi.dim() == 2 and zi.shape[1] == 2, lambda: "zi must have last dimension of size 2.")
+    if sx:
+        torch._check(x.dim() == 2, lambda: "x must be 2D (batch, time).")
+    else:
+        torch._check(x.dim() == 3 and x.shape[2] == 2, lambda: "x must have last dimension of size 2.")
+    torch._check(x.shape[0] == zi.shape[0], lambda: "x and zi must have the same batch size.")
+    if lpv:
+        torch._check(x.shape[1] == A.shape[-3], lambda: "x's second dimension must match A's last-3 dimension.")
+    if A.dim() == (4 if lpv else 3):
+        torch._check(A.shape[0] == x.shape[0], lambda: "A's first dimension must match x's batch size.")
+
+
+def _make_recur2(lpv: bool, sx: bool):
+    fn = lib.ptb_lpv_recur2_fwd if lpv else lib.ptb_lti_recur2_fwd
+
+    def impl(A: Tensor, zi: Tensor, x: Tensor) -> Tensor:
+        _check_recur2(A, zi, x, lpv, sx)
+        dev = _lib.require_cuda(A, zi, x)
+        _same_dtype(A, zi, x)
+        B, T = x.shape[0], x.shape[1]
+        A_c, zi_c, x_c = A.contiguous(), zi.contiguous(), x.contiguous()
+        y = x.new_empty(B, T, 2)
+        if B and T:
+            _lib.call(fn, dev, B, T, _lib.dtype_code(x), B, T, ptr(A_c), int(A.dim() == (4 if lpv else 3)),
+                      ptr(zi_c), ptr(x_c), int(sx), ptr(y), None)
+        return y
+
+    def fake(A, zi, x):
+        _check_recur2(A, zi, x, lpv, sx)
+        return x.new_empty(x.shape[0], x.shape[1], 2)
+
+    return impl, fake
+
+
+def _make_recur2_bwd(lpv: bool):
+    fn = lib.ptb_lpv_recur2_bwd if lpv else lib.ptb_lti_recur2_bwd
+
+    def impl(A, zi, y, gy, g_in, x_scalar, need_A, need_zi):
+        dev = _lib.require_cuda(A, zi, y, gy, g_in)
+        B, T = y.shape[0], y.shape[1]
+        A_c, zi_c, y_c, gy_c, gin_c = A.contiguous(), zi.contiguous(), y.contiguous(), gy.contiguous(), _opt(g_in)
+        gx = y.new_empty((B, T) if x_scalar else (B, T, 2))
+        batched = A.dim() == (4 if lpv else 3)
+        if not need_A:
+            gA = A.new_empty(0)
+        elif lpv:
+            gA = y.new_empty(B, T, 2, 2)            # per row
+        else:
+            gA = torch.zeros_like(A_c)
+        gzi = torch.empty_like(zi_c) if need_zi else zi.new_empty(0)
+        if B and T:
+            _lib.call(fn, dev, B, T, _lib.dtype_code(y), B, T, ptr(A_c), int(batched), ptr(zi_c), ptr(y_c),
+                      ptr(gy_c), ptr(gin_c), int(x_scalar), ptr(gx), ptr(gA) if need_A else None,
+                      ptr(gzi) if need_zi else None)
+        elif need_zi:
+            gzi.zero_()
+        if need_A and lpv and not batched:
+            gA = gA.sum(0)   # coefficients shared by the batch: philtorch/__init__.py:62-65
+        return gA, gzi, gx
+
+    def fake(A, zi, y, gy, g_in, x_scalar, need_A, need_zi):
+        B, T = y.shape[0], y.shape[1]
+        return (torch.empty_like(A) if need_A else A.new_empty(0),
+                torch.empty_like(zi) if need_zi else zi.new_empty(0),
+                y.new_empty((B, T) if x_scalar else (B, T, 2)))
+
+    return impl, fake
+
+
+for _n, _lpv, _sx in (("lti_recur2", False, False), ("lti_recur2_sx", False, True),
+                      ("recur2", True, False), ("recur2_sx", True, True)):
+    _impl, _fake = _make_recur2(_lpv, _sx)
+    _LIB.impl(_n, _impl, "CUDA")
+    torch.library.register_fake(f"philtorch_b200::{_n}")(_fake)
+for _n, _lpv in (("lti_recur2_bwd", False), ("recur2_bwd", True)):
+    _impl, _fake = _make_recur2_bwd(_lpv)
+    _LIB.impl(_n, _impl, "CUDA")
+    torch.library.register_fake(f"philtorch_b200::{_n}")(_fake)
+
+
+# =============================================================================== TDF-II section
+_LIB.define("biquad_tdf2(Tensor b, Tensor a, Tensor? zi, Tensor x) -> (Tensor, Tensor)", tags=_TAGS)
+_LIB.define("biquad_tdf2_bwd(Tensor b, Tensor a, Tensor x, Tensor y, Tensor gy, Tensor? gzf, bool need_coef, "
+            "bool need_zi) -> (Tensor, Tensor, Tensor, Tensor)", tags=_TAGS)
+
+
+def _check_biquad(b: Tensor, a: Tensor, zi: Optional[Tensor], x: Tensor) -> None:
+    torch._check(x.dim() == 2, lambda: "x must be 2D (batch, time).")
+    torch._check(b.dim() in (1, 2) and b.shape[-1] == 3, lambda: "b must be (3,) or (B,3).")
+    torch._check(a.dim() == b.dim() and a.shape[-1] == 2, lambda: "a must be (2,) or (B,2), like b.")
+    if b.dim() == 2:
+        torch._check(b.shape[0] == x.shape[0] and a.shape[0] == x.shape[0],
+                     lambda: "batched coefficients must match x's batch size.")
+    if zi is not None:
+        torch._check(zi.dim() == 2 and zi.shape[0] == x.shape[0] and zi.shape[1] == 2, lambda: "zi must be (B,2).")
+
+
+def _biquad_tdf2(b, a, zi, x):
+    _check_biquad(b, a, zi, x)
+    dev = _lib.require_cuda(b, a, zi, x)
+    if b.dtype != x.dtype or a.dtype != x.dtype or (zi is not None and zi.dtype != x.dtype):
+        raise RuntimeError("b, a and zi must have the same scalar type as input")
+    B, T = x.shape
+    b_c, a_c, zi_c, x_c = b.contiguous(), a.contiguous(), _opt(zi), x.contiguous()
+    y = torch.empty_like(x_c)
+    zf = x.new_empty(B, 2)
+    if B and T:
+        _lib.call(lib.ptb_biquad_tdf2_fwd, dev, B, T, _lib.dtype_code(x), B, T, ptr(b_c), ptr(a_c),
+                  int(b.dim() == 2), ptr(zi_c), ptr(x_c), ptr(y), ptr(zf))
+    elif B:
+        zf.copy_(zi_c) if zi_c is not None else zf.zero_()
+    return y, zf
+
+
+def _biquad_tdf2_bwd(b, a, x, y, gy, gzf, need_coef, need_zi):
+    dev = _lib.require_cuda(b, a, x, y, gy, gzf)
+    B, T = x.shape
+    b_c, a_c, x_c, y_c, gy_c, gzf_c = b.contiguous(), a.contiguous(), x.contiguous(), y.contiguous(), \
+        gy.contiguous(), _opt(gzf)
+    gx = torch.empty_like(x_c)
+    gb = torch.zeros_like(b_c) if need_coef else b.new_empty(0)
+    ga = torch.zeros_like(a_c) if need_coef else a.new_empty(0)
+    gzi = x.new_empty(B, 2) if need_zi else x.new_empty(0)
+    if B and T:
+        _lib.call(lib.ptb_biquad_tdf2_bwd, dev, B, T, _lib.dtype_code(x), B, T, ptr(b_c), ptr(a_c),
+                  int(b.dim() == 2), ptr(x_c), ptr(y_c), ptr(gy_c), ptr(gzf_c), ptr(gx),
+                  ptr(gb) if need_coef else None, ptr(ga) if need_coef else None,
+                  ptr(gzi) if need_zi else None)
+    elif need_zi:
+        gzi.copy_(gzf_c) if gzf_c is not None else gzi.zero_()
+    return gb, ga, gzi, gx
+
+
+_LIB.impl("biquad_tdf2", _biquad_tdf2, "CUDA")
+_LIB.impl("biquad_tdf2_bwd", _biquad_tdf2_bwd, "CUDA")
+
+
+@torch.library.register_fake("philtorch_b200::biquad_tdf2")
+def _(b, a, zi, x):
+    _check_biquad(b, a, zi, x)
+    return torch.empty_like(x, memory_format=torch.contiguous_format), x.new_empty(x.shape[0], 2)
+
+
+@torch.library.register_fake("philtorch_b200::biquad_tdf2_bwd")
+def _(b, a, x, y, gy, gzf, need_coef, need_zi):
+    return (torch.empty_like(b) if need_coef else b.new_empty(0),
+            torch.empty_like(a) if need_coef else a.new_empty(0),
+            x.new_empty(x.shape[0], 2) if need_zi else x.new_empty(0),
+            torch.empty_like(x, memory_format=torch.contiguous_format))
+
+
 # CPU (and any other backend) tensors: fail loudly instead of "no kernel registered" noise.
 def _no_backend(name):
     def fn(*args, **kwargs):
@@ -166,5 +332,6 @@ def _no_backend(name):
     return fn
 
 
-for _name in ("lti_recur", "lti_recur_bwd", "lpv_recur", "lpv_recur_bwd"):
+for _name in ("lti_recur", "lti_recur_bwd", "lpv_recur", "lpv_recur_bwd", "lti_recur2", "lti_recur2_sx", "recur2",
+              "recur2_sx", "lti_recur2_bwd", "recur2_bwd", "biquad_tdf2", "biquad_tdf2_bwd"):
     _LIB.impl(_name, _no_backend(_name), "CPU")
