@@ -1,0 +1,289 @@
+#!/usr/bin/env python
+"""Benchmark of the linear-recurrence hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+A step = one forward + one backward pass of the first-order recurrence with per-sample
+coefficients (B = 256 channels, T = 2^20 samples, fp32; gradients w.r.t. x, a and the initial
+state) over one batch of seeded synthetic input.  One JSON line is printed by rank 0.
+
+* ``value``        samples/s of the whole job (all ranks), inputs resident in HBM, timed with CUDA
+                   events between a barrier + synchronize on both sides, max over ranks.
+* ``e2e``          the same metric through the host-buffer entry point: every step uploads the
+                   inputs from pinned host memory and downloads all results.
+* ``roofline``     algorithmic bytes of the backward launch / its mean duration (CUDA events on the
+                   launching stream inside the timed region) against the measured copy bandwidth.
+* ``cpu_baseline`` the reference project's own CPU extension (compiled into oracle/_ref), forward
+                   + backward on a bounded sample of the same workload, on this machine's cores.
+
+Multi-GPU (launched by torchrun): the batch axis is sharded, every rank runs the full per-GPU
+workload on its own rows (weak scaling, no data-path collective).
+
+``--impl reference`` times only the reference CPU extension (rank 0; other ranks exit).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "fwd+bwd filter samples/s"
+UNIT = "samples/s"
+B, T = 256, 1 << 20
+WORKLOAD = "LPV first-order linear_recurrence fwd+bwd (grads x, a, zi), fp32, B=256, T=2^20"
+BYTES_FWD, BYTES_BWD = 12, 20          # algorithmic bytes per sample: r a,x w y | r gy,a,y w gx,ga
+FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one backward launch at the bench size, scaled
+# from the ncu capture summarised in profiles/first_order_lpv_fwd_bwd_ncu.md.
+NCU_TRAFFIC_BWD_BYTES = 4 * 1299106304   # 64-row capture x 4 (traffic is proportional to rows)
+
+
+def measured_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.proc = None
+        self.gpu = gpu_index
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        sm, mx, reasons = [], [], set()
+        for line in out.splitlines():
+            f = [s.strip() for s in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        # samples under load = the upper half of the clock readings
+        sm_sorted = sorted(sm)
+        load = sm_sorted[len(sm_sorted) // 2:] if sm_sorted else []
+        return {"sm_mhz": statistics.median(load) if load else None,
+                "sm_max_mhz": max(mx) if mx else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------------------------ CPU reference
+def cpu_reference_run(steps: int, warmup: int, sample_T: int):
+    """Forward + backward of the same op on the host cores with the reference's own CPU extension
+    (oracle/_ref, compiled from its sources) or, if that binary is absent, the C oracle port."""
+    import torch
+    from philtorch_b200 import workloads
+    from oracle import cport, refext
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    w = workloads.lpv_first_order(B=B, T=sample_T)
+    a, zi, x, gy = w["a"], w["zi"], w["x"], w["gy"]
+    if refext.available():
+        kind = "reference"
+
+        def step():
+            y = refext.recur1(a, zi, x)
+            return refext.recur1_bwd(a, zi, y, gy)
+    else:
+        kind = "port"
+
+        def step():
+            y = cport.recur1(a, zi, x)
+            return cport.recur1_bwd(a, zi, y, gy)
+    for _ in range(max(1, warmup)):
+        step()
+    ts = []
+    for _ in range(max(1, steps)):
+        t0 = time.perf_counter()
+        step()
+        ts.append(time.perf_counter() - t0)
+    t = statistics.median(ts)
+    return {"value": B * sample_T / t, "unit": UNIT, "cores": min(cores, B), "kind": kind,
+            "sample": f"B={B}, T={sample_T} (1/{T // sample_T} of the workload's time axis), "
+                      f"median of {len(ts)} fwd+bwd passes, {1e3 * t:.1f} ms each"}, t
+
+
+def run_reference_arm(args, rank: int):
+    if rank != 0:
+        return
+    steps = max(1, args.steps)
+    base, t = cpu_reference_run(steps, args.warmup, sample_T=1 << 16)
+    line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
+            "steps": steps, "warmup": args.warmup, "ms_per_step": 1e3 * t, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic (seeded)",
+            "config": {"workload": WORKLOAD, "note": "each step is a bounded sample: " + base["sample"]},
+            "cpu_baseline": base,
+            "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------ GPU arm
+def run_ours(args, rank: int, world: int, local_rank: int):
+    import torch
+    import torch.distributed as dist
+
+    import philtorch_b200 as ptb
+    from philtorch_b200 import workloads
+    from philtorch_b200.host import HostPipeline
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    ops = torch.ops.philtorch_b200
+
+    B = args.rows
+    w = workloads.lpv_first_order(B=B, T=T, device=dev)   # this rank's rows (batch-sharded job)
+    a, zi, x, gy = w["a"], w["zi"], w["x"], w["gy"]
+
+    def step(ev=None):
+        if ev:
+            ev[0].record()
+        y = ops.lpv_recur(a, zi, x)
+        if ev:
+            ev[1].record()
+        out = ops.lpv_recur_bwd(a, zi, y, gy, None, True, True)
+        if ev:
+            ev[2].record()
+        return y, out
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t_start.record()
+    for k in range(args.steps):
+        step(evs[k])
+    t_end.record()
+    barrier()
+    ms_total = t_start.elapsed_time(t_end)
+    clocks = sampler.stop() if sampler else None
+    ptb.check_errors(dev)
+    fwd_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in evs)
+    bwd_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in evs)
+
+    if args.kernels_only:
+        if rank == 0:
+            print(json.dumps({"profile_case": True, "rows": B, "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
+                              "fwd_gbs": BYTES_FWD * B * T / fwd_ms / 1e6, "bwd_gbs": BYTES_BWD * B * T / bwd_ms / 1e6}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    # ---- end to end through the host-buffer entry point (pinned host memory in and out)
+    e2e_steps = max(1, min(args.steps, 3))
+    host = {k: v.cpu().pin_memory() for k, v in (("a", a), ("zi", zi), ("x", x), ("gy", gy))}
+    out = {"y": torch.empty_like(host["x"]).pin_memory(), "grad_a": torch.empty_like(host["x"]).pin_memory(),
+           "grad_x": torch.empty_like(host["x"]).pin_memory(), "grad_zi": torch.empty_like(host["zi"]).pin_memory()}
+    pipe = HostPipeline(B, T, torch.float32, dev)
+    pipe.run(host["a"], host["zi"], host["x"], host["gy"], out)   # warm-up
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(e2e_steps):
+        pipe.run(host["a"], host["zi"], host["x"], host["gy"], out)
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+    ptb.check_errors(dev)
+
+    times = torch.tensor([ms_total, e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms_total, e2e_ms = times.tolist()
+
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        nsamp = B * T
+        achieved = BYTES_BWD * nsamp / (bwd_ms * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": world * nsamp * args.steps / (ms_total * 1e-3), "unit": UNIT,
+            "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+            "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic (seeded, generated on device)",
+            "config": {"workload": WORKLOAD if B == 256 else WORKLOAD.replace("B=256", f"B={B}"), "rows_per_gpu": B, "sharding": "batch axis, no collective",
+                       "l2": "inputs (1 GiB per array) exceed the 126 MB L2, no flush needed"},
+            "roofline": {"bound": "hbm", "kernel": "scan_kernel<FoBwd<float,LPV>> (adjoint scan)",
+                         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_source": f"{peak_kind} copy bandwidth", "traffic": NCU_TRAFFIC_BWD_BYTES,
+                         "algorithmic_bytes_per_launch": BYTES_BWD * nsamp, "launch_ms": bwd_ms,
+                         "forward": {"achieved": BYTES_FWD * nsamp / (fwd_ms * 1e-3) / 1e9, "launch_ms": fwd_ms,
+                                     "frac": BYTES_FWD * nsamp / (fwd_ms * 1e-3) / 1e9 / peak},
+                         "fwd_plus_bwd_frac": (BYTES_FWD + BYTES_BWD) * nsamp / ((fwd_ms + bwd_ms) * 1e-3) / 1e9 / peak},
+            "e2e": {"value": world * nsamp * e2e_steps / (e2e_ms * 1e-3), "unit": UNIT,
+                    "h2d_bytes_per_step": pipe.h2d_bytes, "d2h_bytes_per_step": pipe.d2h_bytes,
+                    "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps,
+                    "api": "philtorch_b200.host.HostPipeline.run (pinned host buffers in and out)"},
+            "gpu_launches": 2 * args.steps,
+            "clocks": clocks,
+        }
+        if world == 1:
+            base, _ = cpu_reference_run(steps=3, warmup=1, sample_T=1 << 18)
+            line["cpu_baseline"] = base
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    # reduced cases for profiler captures (never a bench value): fewer rows, device-resident loop only
+    ap.add_argument("--rows", type=int, default=B, help="rows per GPU (default: the benchmark's 256)")
+    ap.add_argument("--kernels-only", action="store_true", help="skip the host-buffer and CPU legs")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference_arm(args, rank)
+        return
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -63,12 +63,14 @@ def test_against_scipy(order):
     a = torch.tensor(aa[1:] / aa[0], device=DEV)
     xt = torch.tensor(x, device=DEV)
     assert rel_err(ptb.lti.lfilter(b, a, xt), torch.from_numpy(signal.lfilter(bb, aa, x))) <= 1e-10
-    zi = np.ascontiguousarray(signal.lfilter_zi(bb, aa))
+    zi = np.array(signal.lfilter_zi(bb, aa), copy=True).reshape(-1).copy()
     assert rel_err(ptb.lti.lfilter_zi(a, b), torch.from_numpy(zi)) <= 1e-10
     y_ref, zf_ref = signal.lfilter(bb, aa, x, zi=zi[None, :] * x[:, :1])
     y, zf = ptb.lti.lfilter(b, a, xt, zi=torch.tensor(zi, device=DEV) * xt[:, :1])
     assert rel_err(y, torch.from_numpy(y_ref)) <= 1e-10 and rel_err(zf, torch.from_numpy(zf_ref)) <= 1e-10
-    assert rel_err(ptb.lti.filtfilt(b, a, xt), torch.from_numpy(signal.filtfilt(bb, aa, x).copy())) <= 1e-8
+    assert rel_err(ptb.lti.filtfilt(b, a, xt), torch.from_numpy(signal.filtfilt(bb, aa, x, padtype="constant").copy())) <= 1e-8
+    assert rel_err(ptb.lti.filtfilt(b, a, xt, padmode="reflect", padlen=21),
+                   torch.from_numpy(signal.filtfilt(bb, aa, x, padtype="even", padlen=21).copy())) <= 1e-8
     # 1-D signal with 1-D coefficients keeps its rank
     assert ptb.lti.lfilter(b, a, xt[0]).shape == (T,)
 
