@@ -36,7 +36,8 @@ enum {
   PTB_ERR_ARG = 1,       /* null pointer, negative size, unknown dtype */
   PTB_ERR_WORKSPACE = 2, /* workspace missing, misaligned or too small */
   PTB_ERR_CUDA = 3,      /* a CUDA runtime call failed (see ptb_last_cuda_error) */
-  PTB_ERR_TOO_LARGE = 4  /* more than 2^32-2 tiles */
+  PTB_ERR_TOO_LARGE = 4, /* more than 2^32-2 tiles */
+  PTB_ERR_SCRATCH_LIMIT = 5 /* ptb_lpv_recur_fwd_static: problem larger than its built-in scratch */
 };
 
 const char* ptb_version(void);
@@ -88,6 +89,27 @@ int ptb_lpv_recur_bwd(int dtype, int64_t B, int64_t T, const void* a, int a_batc
                       int zi_batched, const void* y, const void* gy, const void* g_in, void* grad_x,
                       void* grad_a, void* grad_zi, void* workspace, int64_t workspace_bytes,
                       uint32_t* status, ptb_stream_t stream);
+
+/* ---- first-order forward without any caller-side or library-side allocation -----------------
+ * No counterpart in the reference.  Same computation and arguments as ptb_lpv_recur_fwd, minus the
+ * workspace: the look-back scratch is a fixed 2 MiB array inside the library image (every GPU
+ * that loads the library holds it until the process exits).  It is for callers whose processing
+ * call is not allowed to allocate device memory -- a real-time audio or DSP callback, where
+ * cudaMalloc may stall the whole device for an unbounded time, or a host application that has
+ * handed all device memory to its own pool -- and that have no workspace to pass either.
+ *   - Limit: B * ceil(T / tile) <= ptb_lpv_recur_fwd_static_max_tiles(dtype), the tile being 3072
+ *     samples (fp32) or 1536 (fp64): about 3.2e8 fp32 samples.  Larger problems return
+ *     PTB_ERR_SCRATCH_LIMIT and launch nothing.
+ *   - The first call on each device looks up the array's device address (that device must be
+ *     current, as for every entry point); make that first call before any stream capture.
+ *   - All calls on a device share the one array; the part a call uses is cleared on `stream`
+ *     before its kernel runs, and it keeps the last call's records afterwards.  Two calls that may
+ *     overlap on the GPU (different streams without an ordering between them) race: serialise them.
+ *   - It calls no cudaMalloc / cudaFree and no allocating library routine. */
+int64_t ptb_lpv_recur_fwd_static_max_tiles(int dtype);
+int ptb_lpv_recur_fwd_static(int dtype, int64_t B, int64_t T, const void* a, int a_batched, const void* zi,
+                             int zi_batched, const void* x, void* y, void* zf, uint32_t* status,
+                             ptb_stream_t stream);
 
 /* ---- 2x2, time-invariant ---------------------------------------------------------------------
  * Replaces op philtorch::lti_recur2(A, zi, x) -> y (philtorch/csrc/host_recur2.cpp:166, CPU kernel

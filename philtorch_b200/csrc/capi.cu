@@ -348,6 +348,41 @@ static int bq_bwd(int64_t B, int64_t T, const void* b, const void* a, int batche
   return rc;
 }
 
+// ---------------------------------------------------------------------------- no-allocation variant
+// Scratch that lives in the library image instead of being passed in: one array per GPU that loads
+// the library, held until the process exits.  On the host the symbol below is only a stand-in;
+// the device address is fetched once per device with cudaGetSymbolAddress.
+constexpr int64_t kStaticScratchBytes = 2ll << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+static void* g_static_scratch_addr[kMaxDevices] = {};
+
+static int static_scratch(void** out) {
+  int dev = 0;
+  PTB_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return PTB_ERR_ARG;
+  if (!g_static_scratch_addr[dev]) {
+    void* p = nullptr;
+    PTB_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));   // device `dev` is current
+    g_static_scratch_addr[dev] = p;
+  }
+  *out = g_static_scratch_addr[dev];
+  return PTB_OK;
+}
+
+template <class S>
+static int fo_fwd_lpv_static(int64_t B, int64_t T, const void* a, int a_batched, const void* zi, int zi_batched,
+                             const void* x, void* y, void* zf, uint32_t* status, cudaStream_t st) {
+  using P = FoFwdP<S, true>;
+  const int64_t ntiles = B * ((T + P::TILE - 1) / P::TILE);
+  if (ws_layout(ntiles, P::SLOT_WORDS, sizeof(typename P::Partial)).total > kStaticScratchBytes)
+    return PTB_ERR_SCRATCH_LIMIT;
+  void* scratch = nullptr;
+  const int rc = static_scratch(&scratch);
+  if (rc != PTB_OK) return rc;
+  // launch_scan clears the ticket and the look-back records of this call with cudaMemsetAsync
+  return fo_fwd<S, true>(B, T, a, a_batched, zi, zi_batched, x, y, zf, scratch, kStaticScratchBytes, status, st);
+}
+
 }  // namespace ptb
 
 using namespace ptb;
@@ -363,6 +398,9 @@ const char* ptb_error_string(int code) {
     case PTB_ERR_WORKSPACE: return "workspace missing, not 256-byte aligned or smaller than ptb_workspace_bytes";
     case PTB_ERR_CUDA: return "CUDA runtime call failed";
     case PTB_ERR_TOO_LARGE: return "problem needs more than 2^32-2 tiles";
+    case PTB_ERR_SCRATCH_LIMIT:
+      return "problem exceeds the built-in scratch of the no-allocation entry point "
+             "(see ptb_lpv_recur_fwd_static_max_tiles); use the entry point that takes a workspace";
     default: return "unknown error";
   }
 }
@@ -407,6 +445,22 @@ int ptb_lpv_recur_fwd(int dtype, int64_t B, int64_t T, const void* a, int a_batc
   if (!a || !zi || !x || !y) return PTB_ERR_ARG;
   PTB_DISPATCH(dtype, (fo_fwd<S, true>(B, T, a, a_batched, zi, zi_batched, x, y, zf, workspace,
                                        workspace_bytes, status, (cudaStream_t)stream)));
+}
+
+int64_t ptb_lpv_recur_fwd_static_max_tiles(int dtype) {
+  // header + one look-back record and one (unused) partial slot per tile
+  const int64_t per_tile = dtype == PTB_F64 ? (4 * 8 + 8) : (2 * 8 + 4);
+  return (kStaticScratchBytes - kHeaderBytes - 2 * 256) / per_tile;
+}
+
+int ptb_lpv_recur_fwd_static(int dtype, int64_t B, int64_t T, const void* a, int a_batched, const void* zi,
+                             int zi_batched, const void* x, void* y, void* zf, uint32_t* status,
+                             ptb_stream_t stream) {
+  if (B < 0 || T < 0) return PTB_ERR_ARG;
+  if (B == 0 || T == 0) return PTB_OK;
+  if (!a || !zi || !x || !y) return PTB_ERR_ARG;
+  PTB_DISPATCH(dtype, (fo_fwd_lpv_static<S>(B, T, a, a_batched, zi, zi_batched, x, y, zf, status,
+                                            (cudaStream_t)stream)));
 }
 
 int ptb_lti_recur_bwd(int dtype, int64_t B, int64_t T, const void* a, int a_batched, const void* zi,
