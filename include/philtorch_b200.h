@@ -90,6 +90,17 @@ int ptb_lpv_recur_bwd(int dtype, int64_t B, int64_t T, const void* a, int a_batc
                       void* grad_a, void* grad_zi, void* workspace, int64_t workspace_bytes,
                       uint32_t* status, ptb_stream_t stream);
 
+/* ---- carry pass of a first-order scan whose time axis is split across devices --------------------
+ * New with the time-sharded mode (the reference has no multi-device code).  Reads a shard's
+ * coefficients and inputs once and returns, per row, the shard's total affine map
+ *   carry[b] = { prod_t a[b,t],  end state of the shard started from zero }
+ * without writing the sequence.  reverse = 0: the forward recurrence (x = inputs);
+ * reverse = 1: the adjoint recurrence c[t] = a[t] (gy[t] + c[t+1]) run from the shard's end
+ * (x = gy).  a: (B,T) if a_batched else (T,); carry: (B,2). */
+int ptb_lpv_recur_carry(int dtype, int64_t B, int64_t T, const void* a, int a_batched, const void* x,
+                        int reverse, void* carry, void* workspace, int64_t workspace_bytes, uint32_t* status,
+                        ptb_stream_t stream);
+
 /* ---- first-order forward without any caller-side or library-side allocation -----------------
  * No counterpart in the reference.  Same computation and arguments as ptb_lpv_recur_fwd, minus the
  * workspace: the look-back scratch is a fixed 2 MiB array inside the library image (every GPU

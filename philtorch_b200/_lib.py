@@ -57,6 +57,9 @@ lib.ptb_biquad_tdf2_fwd.restype = _i32
 lib.ptb_biquad_tdf2_bwd.argtypes = [_i32, _i64, _i64, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp] + _tail
 lib.ptb_biquad_tdf2_bwd.restype = _i32
 
+lib.ptb_lpv_recur_carry.argtypes = [_i32, _i64, _i64, _vp, _i32, _vp, _i32, _vp] + _tail
+lib.ptb_lpv_recur_carry.restype = _i32
+
 _status: dict[int, torch.Tensor] = {}
 
 ERROR_BITS = {1: "look-back wait expired", 2: "tile load wait expired", 4: "tile drain wait expired",

@@ -303,3 +303,99 @@ struct FoBwd : ScalarAffine<S> {
 };
 
 }  // namespace ptb
+
+namespace ptb {
+
+// ------------------------------------------------------------------------------------ carry pass
+// Total affine map of every row, (product of a, end state from a zero start), without writing
+// the sequence: the first pass of a scan whose time axis is split across devices.  The carried
+// "state" is itself a map S = (P, s); a tile acts on it by composition, S -> m o S.  Operators on
+// maps are kept as three numbers (alpha, beta, gamma): S -> (alpha S.P + beta, alpha S.s + gamma),
+// which also represents the constant operators the look-back needs.
+// REVERSE_ = false: maps of the forward recurrence, offsets x.
+// REVERSE_ = true : maps of the adjoint recurrence over c, offsets a*gy, time descending.
+template <class S>
+struct FoCarryParams {
+  const S* a; int64_t a_row_stride;
+  const S* x;        // x (forward) or gy (adjoint)
+  S* carry;          // (B,2): {product of a over the row, end state from a zero start}
+  int64_t T;
+};
+
+template <class S, int CH, int STAGES_, int MIN_CTAS_, bool REVERSE_>
+struct FoCarry {
+  using Map = Pod<S, 3>;
+  using State = Pod<S, 2>;
+  using Partial = Pod<S, 1>;
+  using Params = FoCarryParams<S>;
+  static constexpr int V = Vec16<S>::V;
+  static constexpr int NT = 256;
+  static constexpr int SPT = V * CH;
+  static constexpr int TILE = NT * SPT;
+  static constexpr int STAGES = STAGES_;
+  static constexpr int MIN_CTAS = MIN_CTAS_;
+  static constexpr int LBW = 1;
+  static constexpr bool REVERSE = REVERSE_;
+  static constexpr bool HAS_PARTIAL = false;
+  static constexpr int SLOT_WORDS = Words<Map>::W;
+  static constexpr int SLOT = TILE * (int)sizeof(S);
+  static constexpr int X_OFF = 0;
+  static constexpr int A_OFF = SLOT;
+  static constexpr int STAGE_BYTES = 2 * SLOT;
+
+  static __device__ __forceinline__ Map identity() { Map m; m.v[0] = S(1); m.v[1] = S(0); m.v[2] = S(0); return m; }
+  static __device__ __forceinline__ State zero_state() { State s; s.v[0] = S(1); s.v[1] = S(0); return s; }
+  static __device__ __forceinline__ Map const_map(const State& s) {
+    Map m; m.v[0] = S(0); m.v[1] = s.v[0]; m.v[2] = s.v[1]; return m;
+  }
+  static __device__ __forceinline__ Map compose(const Map& f, const Map& g) {   // f first, then g
+    Map m;
+    m.v[0] = g.v[0] * f.v[0];
+    m.v[1] = g.v[0] * f.v[1] + g.v[1];
+    m.v[2] = g.v[0] * f.v[2] + g.v[2];
+    return m;
+  }
+  static __device__ __forceinline__ State apply(const Map& m, const State& s) {
+    State r; r.v[0] = m.v[0] * s.v[0] + m.v[1]; r.v[1] = m.v[0] * s.v[1] + m.v[2]; return r;
+  }
+  static __device__ __forceinline__ void plan(const Params& p, bool, int64_t row, int64_t t0, int nvalid,
+                                              IoPlan& io) {
+    const uint32_t bytes = (uint32_t)nvalid * sizeof(S);
+    io.load(X_OFF, p.x + row * p.T + t0, bytes);
+    io.load(A_OFF, p.a + row * p.a_row_stride + t0, bytes);
+  }
+  static __device__ __forceinline__ State row_init(const Params&, int64_t) { return zero_state(); }
+  static __device__ __forceinline__ void row_final(const Params& p, int64_t row, const State& s) {
+    p.carry[row * 2] = s.v[0];
+    p.carry[row * 2 + 1] = s.v[1];
+  }
+  static __device__ __forceinline__ Map aggregate(const Params&, const unsigned char* stage, int tpos, int64_t,
+                                                  int64_t, int nvalid) {
+    const int p0 = tpos * SPT;
+    int nv = nvalid - p0;
+    nv = nv < 0 ? 0 : (nv > SPT ? SPT : nv);
+    S x[SPT], a[SPT];
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      VecIO<S, V>::ld(stage + X_OFF + (size_t)p0 * sizeof(S) + 16 * c, &x[c * V]);
+      VecIO<S, V>::ld(stage + A_OFF + (size_t)p0 * sizeof(S) + 16 * c, &a[c * V]);
+    }
+    S P = S(1), s = S(0);
+    if (!REVERSE) {
+#pragma unroll
+      for (int j = 0; j < SPT; ++j)
+        if (j < nv) { s = a[j] * s + x[j]; P *= a[j]; }
+    } else {
+#pragma unroll
+      for (int j = SPT - 1; j >= 0; --j)
+        if (j < nv) { s = a[j] * (s + x[j]); P *= a[j]; }
+    }
+    Map m; m.v[0] = P; m.v[1] = S(0); m.v[2] = s; return m;   // S -> (P S.P, P S.s + s)
+  }
+  static __device__ __forceinline__ Partial finish(const Params&, const State&, unsigned char*, int, int64_t,
+                                                   int64_t, int) {
+    Partial r; r.v[0] = S(0); return r;
+  }
+};
+
+}  // namespace ptb

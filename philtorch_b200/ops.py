@@ -159,6 +159,36 @@ def _(a, zi, y, gy, g_in, need_a, need_zi):
             torch.empty_like(y, memory_format=torch.contiguous_format))
 
 
+# carry pass of a time-sharded first-order scan: (product of a, end state from zero) per row
+_LIB.define("lpv_recur_carry(Tensor a, Tensor x, bool reverse) -> Tensor", tags=_TAGS)
+
+
+def _lpv_recur_carry(a: Tensor, x: Tensor, reverse: bool) -> Tensor:
+    torch._check(x.dim() == 2 and a.dim() in (1, 2) and a.shape[-1] == x.shape[1],
+                 lambda: "a must be (T,) or (B,T) and x (B,T)")
+    dev = _lib.require_cuda(a, x)
+    if a.dtype != x.dtype:
+        raise RuntimeError("a must have the same scalar type as input")
+    B, T = x.shape
+    a_c, x_c = a.contiguous(), x.contiguous()
+    carry = x.new_empty(B, 2)
+    if B and T:
+        _lib.call(lib.ptb_lpv_recur_carry, dev, B, T, _lib.dtype_code(x), B, T, ptr(a_c), int(a.dim() == 2),
+                  ptr(x_c), int(reverse), ptr(carry))
+    elif B:
+        carry[:, 0] = 1
+        carry[:, 1] = 0
+    return carry
+
+
+_LIB.impl("lpv_recur_carry", _lpv_recur_carry, "CUDA")
+
+
+@torch.library.register_fake("philtorch_b200::lpv_recur_carry")
+def _(a, x, reverse):
+    return x.new_empty(x.shape[0], 2)
+
+
 # =============================================================================== 2x2
 # x is (B,T,2), or (B,T) for the *_sx ops (scalar sequence feeding state 0 only).
 for _n in ("lti_recur2", "lti_recur2_sx", "recur2", "recur2_sx"):
@@ -333,5 +363,5 @@ def _no_backend(name):
 
 
 for _name in ("lti_recur", "lti_recur_bwd", "lpv_recur", "lpv_recur_bwd", "lti_recur2", "lti_recur2_sx", "recur2",
-              "recur2_sx", "lti_recur2_bwd", "recur2_bwd", "biquad_tdf2", "biquad_tdf2_bwd"):
+              "recur2_sx", "lti_recur2_bwd", "recur2_bwd", "biquad_tdf2", "biquad_tdf2_bwd", "lpv_recur_carry"):
     _LIB.impl(_name, _no_backend(_name), "CPU")
