@@ -192,8 +192,23 @@ static int launch_reduce(const void* part, int64_t B, int64_t nchunks, int batch
 #define PTB_FO_BWD_STAGES 3
 #define PTB_FO_BWD_CTAS 2
 #endif
-template <class S, bool LPV> using FoFwdP = FoFwd<S, PTB_FO_FWD_CH, PTB_FO_FWD_STAGES, PTB_FO_FWD_CTAS, (PTB_FO_LBW == 1 ? 1 : PTB_FO_FWD_STAGES), LPV>;
-template <class S, bool LPV> using FoBwdP = FoBwd<S, PTB_FO_BWD_CH, PTB_FO_BWD_STAGES, PTB_FO_BWD_CTAS, (PTB_FO_LBW == 1 ? 1 : PTB_FO_BWD_STAGES), LPV>;
+// time-invariant variants stage fewer arrays per tile: larger tiles / more stages fill shared memory
+#ifndef PTB_FOLTI_FWD_CH
+#define PTB_FOLTI_FWD_CH 7
+#define PTB_FOLTI_FWD_STAGES 4
+#define PTB_FOLTI_FWD_CTAS 2
+#endif
+#ifndef PTB_FOLTI_BWD_CH
+#define PTB_FOLTI_BWD_CH 5
+#define PTB_FOLTI_BWD_STAGES 2
+#define PTB_FOLTI_BWD_CTAS 2
+#endif
+template <class S, bool LPV> struct FoFwdSel { using type = FoFwd<S, PTB_FO_FWD_CH, PTB_FO_FWD_STAGES, PTB_FO_FWD_CTAS, 1, true>; };
+template <class S> struct FoFwdSel<S, false> { using type = FoFwd<S, PTB_FOLTI_FWD_CH, PTB_FOLTI_FWD_STAGES, PTB_FOLTI_FWD_CTAS, 1, false>; };
+template <class S, bool LPV> struct FoBwdSel { using type = FoBwd<S, PTB_FO_BWD_CH, PTB_FO_BWD_STAGES, PTB_FO_BWD_CTAS, 1, true>; };
+template <class S> struct FoBwdSel<S, false> { using type = FoBwd<S, PTB_FOLTI_BWD_CH, PTB_FOLTI_BWD_STAGES, PTB_FOLTI_BWD_CTAS, 1, false>; };
+template <class S, bool LPV> using FoFwdP = typename FoFwdSel<S, LPV>::type;
+template <class S, bool LPV> using FoBwdP = typename FoBwdSel<S, LPV>::type;
 
 template <class S, bool LPV>
 static int fo_fwd(int64_t B, int64_t T, const void* a, int a_batched, const void* zi, int zi_batched,
@@ -259,10 +274,22 @@ static int fo_carry(int64_t B, int64_t T, const void* a, int a_batched, const vo
 // ---------------------------------------------------------------------------- 2x2
 // samples per thread (odd), stages, CTAs per SM
 template <class S> struct SoCfg;
-template <> struct SoCfg<float> { static constexpr int FWD_NS = 7, BWD_NS = 5; };
+#ifndef PTB_SO_F32_FWD_NS
+#define PTB_SO_F32_FWD_NS 7
+#define PTB_SO_F32_BWD_NS 5
+#endif
+template <> struct SoCfg<float> { static constexpr int FWD_NS = PTB_SO_F32_FWD_NS, BWD_NS = PTB_SO_F32_BWD_NS; };
 template <> struct SoCfg<double> { static constexpr int FWD_NS = 3, BWD_NS = 3; };
-template <class S, bool LPV, bool XS> using SoFwdP = SoFwd<S, SoCfg<S>::FWD_NS, 2, 2, 1, LPV, XS>;
-template <class S, bool LPV, bool XS> using SoBwdP = SoBwd<S, SoCfg<S>::BWD_NS, 2, 2, 1, LPV, XS>;
+#ifndef PTB_SO_FWD_STAGES
+#define PTB_SO_FWD_STAGES 2
+#define PTB_SO_FWD_CTAS 2
+#endif
+#ifndef PTB_SO_BWD_STAGES
+#define PTB_SO_BWD_STAGES 2
+#define PTB_SO_BWD_CTAS 2
+#endif
+template <class S, bool LPV, bool XS> using SoFwdP = SoFwd<S, SoCfg<S>::FWD_NS, PTB_SO_FWD_STAGES, PTB_SO_FWD_CTAS, 1, LPV, XS>;
+template <class S, bool LPV, bool XS> using SoBwdP = SoBwd<S, SoCfg<S>::BWD_NS, PTB_SO_BWD_STAGES, PTB_SO_BWD_CTAS, 1, LPV, XS>;
 
 template <class S, bool LPV, bool XS>
 static int so_fwd(int64_t B, int64_t T, const void* A, int A_batched, const void* zi, const void* x, void* y,
@@ -313,8 +340,18 @@ static int so_bwd(int64_t B, int64_t T, const void* A, int A_batched, const void
 }
 
 // ---------------------------------------------------------------------------- TDF-II section
-template <class S> using BqFwdP = BqFwd<S, 3, 4, 2, 1>;
-template <class S> using BqBwdP = BqBwd<S, 3, 3, 2, 1>;
+#ifndef PTB_BQ_FWD_CH
+#define PTB_BQ_FWD_CH 7
+#define PTB_BQ_FWD_STAGES 3
+#define PTB_BQ_FWD_CTAS 2
+#endif
+#ifndef PTB_BQ_BWD_CH
+#define PTB_BQ_BWD_CH 3
+#define PTB_BQ_BWD_STAGES 3
+#define PTB_BQ_BWD_CTAS 2
+#endif
+template <class S> using BqFwdP = BqFwd<S, PTB_BQ_FWD_CH, PTB_BQ_FWD_STAGES, PTB_BQ_FWD_CTAS, 1>;
+template <class S> using BqBwdP = BqBwd<S, PTB_BQ_BWD_CH, PTB_BQ_BWD_STAGES, PTB_BQ_BWD_CTAS, 1>;
 
 template <class S>
 static int bq_fwd(int64_t B, int64_t T, const void* b, const void* a, int batched, const void* zi, const void* x,

@@ -176,8 +176,11 @@ __device__ __forceinline__ typename P::Map warp_scan_inclusive(typename P::Map m
 }
 
 // Look-back executed by all 32 lanes of a look-back warp; returns (in every lane) the state
-// entering the tile.  Windows of 32 predecessors (one per lane, all loads in flight together)
-// are folded until one contains an end state; in the usual case that is the nearest one.
+// entering the tile.  Windows of predecessors (one per lane, all loads in flight together) are
+// folded until one contains an end state.  The look-back starts as soon as the tile's ticket is
+// known, usually before the predecessors have published anything, so the first window is only 8
+// lanes wide and polls with a back-off: that keeps the polling traffic in L2 small.  Later
+// windows are 32 wide.
 template <class P>
 __device__ __forceinline__ typename P::State lookback(const Workspace& ws, uint32_t ticket,
                                                       uint32_t chunk, uint32_t B, int lane,
@@ -186,10 +189,12 @@ __device__ __forceinline__ typename P::State lookback(const Workspace& ws, uint3
   using State = typename P::State;
   Map acc = P::identity();
   uint32_t base = 1;
+  int wsize = 8;
   State result;
   while (true) {
     const uint32_t k = base + lane;
-    const bool valid = k <= chunk;
+    const bool active = lane < wsize;
+    const bool valid = active && k <= chunk;
     const size_t idx = valid ? (size_t)ticket - (size_t)k * B : 0;
     uint32_t flag = 0;
     Map m = P::identity();
@@ -203,7 +208,7 @@ __device__ __forceinline__ typename P::State lookback(const Workspace& ws, uint3
         slot_fetch<Map>(slot, raw);
         flag = slot_decode<Map, State>(raw, m, st);
         if (flag != 0) break;
-        if (it > 16) __nanosleep(it > 256 ? 256 : 32);
+        if (it > 1) __nanosleep(it > 64 ? 400 : 100);
         if (it == 64) t0 = globaltimer_ns();
         if (it > 64 && globaltimer_ns() - t0 > limit) break;
       }
@@ -213,7 +218,8 @@ __device__ __forceinline__ typename P::State lookback(const Workspace& ws, uint3
       failed = 1;
       if (lane == 0) atomicOr(ws.error, kErrLookbackTimeout);
     }
-    const uint32_t m2 = __ballot_sync(0xffffffffu, (valid && flag == 2) || timed_out || !valid);
+    // lanes of the window that end the walk: an end state, a wait that expired, the row start
+    const uint32_t m2 = __ballot_sync(0xffffffffu, active && ((valid && flag == 2) || timed_out || !valid));
     if (m2 & 1u) {
       const State s = shfl_pod(st, 0);
       const Map a0 = shfl_pod(acc, 0);
@@ -222,7 +228,7 @@ __device__ __forceinline__ typename P::State lookback(const Workspace& ws, uint3
     }
     const int j = m2 ? (__ffs(m2) - 1) : 32;
     if (lane == j) m = P::const_map((valid && flag == 2) ? st : P::zero_state());
-    else if (lane > j) m = P::identity();
+    else if (lane > j || !active) m = P::identity();
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
       Map o = shfl_down_pod(m, d);
@@ -234,7 +240,8 @@ __device__ __forceinline__ typename P::State lookback(const Workspace& ws, uint3
       result = P::apply(a0, P::zero_state());
       break;
     }
-    base += 32;
+    base += wsize;
+    wsize = 32;
   }
   return result;
 }
@@ -261,7 +268,8 @@ struct EngineSmem {
   static constexpr int kDoneOff = kFullOff + 8 * D;        // u64 done[D]      results written to the stage
   static constexpr int kAggOff = kDoneOff + 8 * D;         // u64 agg_ready[D] tile aggregate known
   static constexpr int kLbOff = kAggOff + 8 * D;           // u64 lb_done[D]   incoming state known
-  static constexpr int kSyncOff = kLbOff + 8 * D;          // u64 sync_bar[3]  barriers among the compute threads
+  static constexpr int kIssuedOff = kLbOff + 8 * D;        // u64 issued[D]    ticket of the stage known
+  static constexpr int kSyncOff = kIssuedOff + 8 * D;      // u64 sync_bar[3]  barriers among the compute threads
   static constexpr int kTicketOff = kSyncOff + 8 * 3;      // u32 tile_ticket[D]
   static constexpr int kCntOff = kTicketOff + 4 * D;       // u32 arrived[D]
   static constexpr int kAbortOff = kCntOff + 4 * D;        // u32 abort, u32 trace counter
@@ -269,8 +277,9 @@ struct EngineSmem {
   static constexpr int kWpreOff = kWtotOff + D * kMapB * kNW;         // Map wpre[D][NW]
   static constexpr int kTaggOff = kWpreOff + D * kMapB * kNW;         // Map tile_agg[D]
   static constexpr int kHinOff = kTaggOff + D * kMapB;                // State hin[D]
-  static constexpr int kPartOff = ((kHinOff + D * kStateB + 15) / 16) * 16;   // Partial[NW]
-  static constexpr int kTotal = kPartOff + (int)sizeof(typename P::Partial) * kNW + 16;
+  static constexpr int kPcntOff = kHinOff + D * kStateB;              // u32 partial arrivals[D]
+  static constexpr int kPartOff = ((kPcntOff + 4 * D + 15) / 16) * 16;   // Partial[D][NW]
+  static constexpr int kTotal = kPartOff + (int)sizeof(typename P::Partial) * kNW * D + 16;
 };
 
 struct TileCoords {
@@ -305,6 +314,7 @@ scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, 
   uint64_t* done = reinterpret_cast<uint64_t*>(smem + L::kDoneOff);
   uint64_t* agg_ready = reinterpret_cast<uint64_t*>(smem + L::kAggOff);
   uint64_t* lb_done = reinterpret_cast<uint64_t*>(smem + L::kLbOff);
+  uint64_t* issued = reinterpret_cast<uint64_t*>(smem + L::kIssuedOff);
   uint64_t* sync_bar = reinterpret_cast<uint64_t*>(smem + L::kSyncOff);
   volatile uint32_t* tile_ticket = reinterpret_cast<volatile uint32_t*>(smem + L::kTicketOff);
   uint32_t* sm_cnt = reinterpret_cast<uint32_t*>(smem + L::kCntOff);
@@ -318,6 +328,7 @@ scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, 
   Map* sm_tagg = reinterpret_cast<Map*>(smem + L::kTaggOff);
   State* sm_hin = reinterpret_cast<State*>(smem + L::kHinOff);
   Partial* sm_part = reinterpret_cast<Partial*>(smem + L::kPartOff);
+  uint32_t* sm_pcnt = reinterpret_cast<uint32_t*>(smem + L::kPcntOff);
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -333,7 +344,9 @@ scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, 
       mbar_init(&done[s], NT + 1);   // compute threads + the stage's look-back warp
       mbar_init(&agg_ready[s], 1);
       mbar_init(&lb_done[s], 1);
+      mbar_init(&issued[s], 1);
       sm_cnt[s] = 0;
+      sm_pcnt[s] = 0;
     }
     for (int i = 0; i < 3; ++i) mbar_init(&sync_bar[i], NT);
     *sm_abort = 0;
@@ -385,6 +398,7 @@ scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, 
       next = atomicAdd(ws.ticket, 1u);
       tile_ticket[s] = ticket;
       PTB_EV(1, n);
+      mbar_arrive(&issued[s]);   // the look-back of this tile may start: it needs nothing from the tile
       if (bulk) {
         const TileCoords c = tile_coords<P>(ticket, B, nchunks, T);
         IoPlan io; io.nld = 0; io.nst = 0;
@@ -409,6 +423,7 @@ scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, 
       const int s = m % D;
       if (k > 0 && m >= (uint32_t)D) drain(m - D);
       tile_ticket[s] = kNoTile;
+      mbar_arrive(&issued[s]);
       mbar_arrive(&full[s]);
     }
     if (failed || *sm_abort) {
@@ -435,7 +450,7 @@ scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, 
       const uint32_t par = (n / D) & 1u;
       uint64_t limit = (failed || *sm_abort) ? kWaitNsAfterError : kWaitNs;
       PTB_PROF_BEGIN(tf0);
-      if (!mbar_wait_bounded(&full[s], par, limit)) {
+      if (!mbar_wait_bounded(&issued[s], par, limit)) {
         if (lane == 0) { atomicOr(ws.error, kErrLoadTimeout); *sm_abort = 1; }
         break;
       }
@@ -486,7 +501,7 @@ scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, 
   const int tpos = P::REVERSE ? (NT - 1 - tid) : tid;
   Map exc[D];                // this thread's exclusive prefix inside the tile held by each stage
   uint32_t p1 = 0, p2 = 0;   // tiles aggregated / finished so far by this warp
-  uint32_t sync_par0 = 0, sync_par1 = 0, sync_par2 = 0;
+  uint32_t sync_par0 = 0, sync_par1 = 0;
   // barrier among the compute threads, bounded like every other wait of the kernel
   auto cta_sync = [&](int id, uint32_t& par) {
     mbar_arrive(&sync_bar[id]);
@@ -568,19 +583,37 @@ scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, 
     Partial part = P::finish(prm, P::apply(pre, hin), stage, tpos, c.row, c.t0, c.nvalid);
 
     if (P::HAS_PARTIAL) {
+      // per-tile sum for time-invariant gradients: warp shuffle, then the last warp to arrive adds
+      // the warp sums in a fixed order (deterministic) and writes the tile's partial.  This is done
+      // before the stage is released, so the per-stage scratch cannot be overwritten meanwhile.
 #pragma unroll
       for (int d = 16; d > 0; d >>= 1) {
         Partial o = shfl_down_pod(part, d);
 #pragma unroll
         for (int i = 0; i < Partial::N; ++i) part.v[i] += o.v[i];
       }
-      if (lane == 0) sm_part[warp] = part;
+      uint32_t order = 0;
+      if (lane == 0) {
+        sm_part[s * NW + warp] = part;
+        __threadfence_block();
+        order = atomicAdd(&sm_pcnt[s], 1u);
+      }
+      order = __shfl_sync(0xffffffffu, order, 0);
+      if (order == (uint32_t)(NW - 1) && lane == 0) {
+        __threadfence_block();
+        Partial tot = sm_part[s * NW];
+        for (int w2 = 1; w2 < NW; ++w2)
+#pragma unroll
+          for (int i = 0; i < Partial::N; ++i) tot.v[i] += sm_part[s * NW + w2].v[i];
+        static_cast<Partial*>(ws.partial)[(size_t)c.row * nchunks + c.chunk] = tot;
+        sm_pcnt[s] = 0;
+      }
+      __syncwarp();
     }
     if (bulk) {
       fence_proxy_async_smem();
       mbar_arrive(&done[s]);
       if (tid == 0) PTB_EV(7, p2);
-      if (P::HAS_PARTIAL) cta_sync(1, sync_par1);
     } else {
       cta_sync(1, sync_par1);
       IoPlan io; io.nld = 0; io.nst = 0;
@@ -595,16 +628,6 @@ scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, 
         }
       }
       mbar_arrive(&done[s]);
-    }
-    if (P::HAS_PARTIAL) {
-      if (tid == 0) {
-        Partial tot = sm_part[0];
-        for (int w2 = 1; w2 < NW; ++w2)
-#pragma unroll
-          for (int i = 0; i < Partial::N; ++i) tot.v[i] += sm_part[w2].v[i];
-        static_cast<Partial*>(ws.partial)[(size_t)c.row * nchunks + c.chunk] = tot;
-      }
-      cta_sync(2, sync_par2);   // sm_part may be rewritten by the next tile
     }
   };
 
