@@ -108,8 +108,8 @@ int ptb_lpv_recur_carry(int dtype, int64_t B, int64_t T, const void* a, int a_ba
  * call is not allowed to allocate device memory -- a real-time audio or DSP callback, where
  * cudaMalloc may stall the whole device for an unbounded time, or a host application that has
  * handed all device memory to its own pool -- and that have no workspace to pass either.
- *   - Limit: B * ceil(T / tile) <= ptb_lpv_recur_fwd_static_max_tiles(dtype), the tile being 3072
- *     samples (fp32) or 1536 (fp64): about 3.2e8 fp32 samples.  Larger problems return
+ *   - Limit: B * ceil(T / tile) <= ptb_lpv_recur_fwd_static_max_tiles(dtype), the tile being 9216
+ *     samples (fp32) or 4608 (fp64): about 9.6e8 fp32 samples of long rows.  Larger problems return
  *     PTB_ERR_SCRATCH_LIMIT and launch nothing.
  *   - The first call on each device looks up the array's device address (that device must be
  *     current, as for every entry point); make that first call before any stream capture.

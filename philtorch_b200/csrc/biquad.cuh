@@ -34,6 +34,30 @@ struct BqCoef {
   }
 };
 
+// M^n for a 2x2 matrix by binary powering (n a compile-time constant): the linear part of the map
+// of a thread that owns n samples of a time-invariant section.
+template <class S, int N>
+__device__ __forceinline__ void mat2_power(const S* m, S* out) {
+  S r[4] = {S(1), S(0), S(0), S(1)};
+  S b[4] = {m[0], m[1], m[2], m[3]};
+  bool first = true;
+#pragma unroll
+  for (int bit = 0; (1 << bit) <= N; ++bit) {
+    if (N & (1 << bit)) {
+      if (first) { r[0] = b[0]; r[1] = b[1]; r[2] = b[2]; r[3] = b[3]; first = false; }
+      else {
+        const S t0 = b[0] * r[0] + b[1] * r[2], t1 = b[0] * r[1] + b[1] * r[3];
+        const S t2 = b[2] * r[0] + b[3] * r[2], t3 = b[2] * r[1] + b[3] * r[3];
+        r[0] = t0; r[1] = t1; r[2] = t2; r[3] = t3;
+      }
+    }
+    const S q0 = b[0] * b[0] + b[1] * b[2], q1 = b[0] * b[1] + b[1] * b[3];
+    const S q2 = b[2] * b[0] + b[3] * b[2], q3 = b[2] * b[1] + b[3] * b[3];
+    b[0] = q0; b[1] = q1; b[2] = q2; b[3] = q3;
+  }
+  out[0] = r[0]; out[1] = r[1]; out[2] = r[2]; out[3] = r[3];
+}
+
 template <class S>
 struct BqFwdParams {
   const S* b; int64_t b_stride;   // 3 or 0
@@ -45,7 +69,7 @@ struct BqFwdParams {
   int64_t T;
 };
 
-template <class S, int CH, int STAGES_, int MIN_CTAS_, int LBW_>
+template <class S, int CH, int STAGES_, int MIN_CTAS_, int NT_>
 struct BqFwd : MatAffine<S> {
   using Alg = MatAffine<S>;
   using typename Alg::Map;
@@ -53,12 +77,12 @@ struct BqFwd : MatAffine<S> {
   using Partial = Pod<S, 1>;
   using Params = BqFwdParams<S>;
   static constexpr int V = Vec16<S>::V;
-  static constexpr int NT = 256;
+  static constexpr int NT = NT_;
   static constexpr int SPT = V * CH;
   static constexpr int TILE = NT * SPT;
   static constexpr int STAGES = STAGES_;
   static constexpr int MIN_CTAS = MIN_CTAS_;
-  static constexpr int LBW = LBW_;
+  static constexpr int LBW = 1;
   static constexpr bool REVERSE = false;
   static constexpr bool HAS_PARTIAL = false;
   static constexpr int SLOT_WORDS = Words<Map>::W;
@@ -95,6 +119,20 @@ struct BqFwd : MatAffine<S> {
     S x[SPT];
     const int nv = load_x(stage, tpos, nvalid, x);
     Map m = Alg::identity();
+    if (nv == SPT) {
+      // full thread: offsets by the recurrence, linear part M^SPT by binary powering
+      S s0 = S(0), s1 = S(0);
+#pragma unroll
+      for (int j = 0; j < SPT; ++j) {
+        const S n0 = k.na1 * s0 + s1 + k.B0 * x[j];
+        s1 = k.na2 * s0 + k.B1 * x[j];
+        s0 = n0;
+      }
+      const S M[4] = {k.na1, S(1), k.na2, S(0)};
+      mat2_power<S, SPT>(M, m.v);
+      m.v[4] = s0; m.v[5] = s1;
+      return m;
+    }
 #pragma unroll
     for (int j = 0; j < SPT; ++j) {
       if (j < nv) {
@@ -148,7 +186,7 @@ struct BqBwdParams {
   int want_coef;
 };
 
-template <class S, int CH, int STAGES_, int MIN_CTAS_, int LBW_>
+template <class S, int CH, int STAGES_, int MIN_CTAS_, int NT_>
 struct BqBwd : MatAffine<S> {
   using Alg = MatAffine<S>;
   using typename Alg::Map;
@@ -156,12 +194,12 @@ struct BqBwd : MatAffine<S> {
   using Partial = Pod<S, 5>;   // sum gy x, sum x lam0, sum x lam1, sum y lam0, sum y lam1
   using Params = BqBwdParams<S>;
   static constexpr int V = Vec16<S>::V;
-  static constexpr int NT = 256;
+  static constexpr int NT = NT_;
   static constexpr int SPT = V * CH;
   static constexpr int TILE = NT * SPT;
   static constexpr int STAGES = STAGES_;
   static constexpr int MIN_CTAS = MIN_CTAS_;
-  static constexpr int LBW = LBW_;
+  static constexpr int LBW = 1;
   static constexpr bool REVERSE = true;
   static constexpr bool HAS_PARTIAL = true;
   static constexpr int SLOT_WORDS = Words<Map>::W;
@@ -206,6 +244,19 @@ struct BqBwd : MatAffine<S> {
     S g[SPT];
     const int nv = load_slot(stage, G_OFF, tpos, nvalid, g);
     Map m = Alg::identity();
+    if (nv == SPT) {
+      S s0 = S(0), s1 = S(0);
+#pragma unroll
+      for (int j = SPT - 1; j >= 0; --j) {
+        const S n0 = k.na1 * s0 + k.na2 * s1 + g[j];
+        s1 = s0;
+        s0 = n0;
+      }
+      const S Mt[4] = {k.na1, k.na2, S(1), S(0)};
+      mat2_power<S, SPT>(Mt, m.v);
+      m.v[4] = s0; m.v[5] = s1;
+      return m;
+    }
 #pragma unroll
     for (int j = SPT - 1; j >= 0; --j) {
       if (j < nv) {

@@ -53,6 +53,7 @@ static int launch_scan(const typename P::Params& prm, int64_t B, int64_t T, bool
   static_assert(P::SLOT_WORDS * 8 + sizeof(typename P::Partial) <= kTileRecordBytes,
                 "per-tile record too large");
   static_assert(P::STAGE_BYTES % 128 == 0, "stages must stay 128-byte aligned");
+  static_assert(EngineSmem<P>::kTotal <= 227 * 1024, "stage ring exceeds the shared memory of an SM");
   const int64_t nchunks = (T + P::TILE - 1) / P::TILE;
   const int64_t ntiles = B * nchunks;
   if (ntiles >= 0xFFFFFFFEll || B >= 0xFFFFFFFFll) return PTB_ERR_TOO_LARGE;
@@ -177,31 +178,33 @@ static int launch_reduce(const void* part, int64_t B, int64_t nchunks, int batch
 }
 
 // ---------------------------------------------------------------------------- first order
-// Tile geometry: 3 x 16 bytes per thread and array (odd => bank-conflict-free strided access).
+// Tile geometry: an ODD number of 16-byte units per thread and array (bank-conflict-free strided
+// access), large tiles (tens of KB per bulk copy are the most DRAM-efficient), one CTA per SM with
+// 2-4 stages filling its shared memory.
 // (16-byte units per thread and array, stages, CTAs per SM); overridable for tuning experiments
 #ifndef PTB_FO_FWD_CH
-#define PTB_FO_FWD_CH 3
+#define PTB_FO_FWD_CH 9
 #define PTB_FO_FWD_STAGES 3
-#define PTB_FO_FWD_CTAS 3
+#define PTB_FO_FWD_CTAS 1
 #endif
 #ifndef PTB_FO_LBW
 #define PTB_FO_LBW 1   // look-back warps per CTA: 1, or one per stage
 #endif
 #ifndef PTB_FO_BWD_CH
-#define PTB_FO_BWD_CH 3
+#define PTB_FO_BWD_CH 5
 #define PTB_FO_BWD_STAGES 3
-#define PTB_FO_BWD_CTAS 2
+#define PTB_FO_BWD_CTAS 1
 #endif
 // time-invariant variants stage fewer arrays per tile: larger tiles / more stages fill shared memory
 #ifndef PTB_FOLTI_FWD_CH
-#define PTB_FOLTI_FWD_CH 7
+#define PTB_FOLTI_FWD_CH 13
 #define PTB_FOLTI_FWD_STAGES 4
-#define PTB_FOLTI_FWD_CTAS 2
+#define PTB_FOLTI_FWD_CTAS 1
 #endif
 #ifndef PTB_FOLTI_BWD_CH
-#define PTB_FOLTI_BWD_CH 5
-#define PTB_FOLTI_BWD_STAGES 2
-#define PTB_FOLTI_BWD_CTAS 2
+#define PTB_FOLTI_BWD_CH 9
+#define PTB_FOLTI_BWD_STAGES 3
+#define PTB_FOLTI_BWD_CTAS 1
 #endif
 template <class S, bool LPV> struct FoFwdSel { using type = FoFwd<S, PTB_FO_FWD_CH, PTB_FO_FWD_STAGES, PTB_FO_FWD_CTAS, 1, true>; };
 template <class S> struct FoFwdSel<S, false> { using type = FoFwd<S, PTB_FOLTI_FWD_CH, PTB_FOLTI_FWD_STAGES, PTB_FOLTI_FWD_CTAS, 1, false>; };
@@ -260,7 +263,7 @@ static int fo_bwd(int64_t B, int64_t T, const void* a, int a_batched, const void
 template <class S, bool REV>
 static int fo_carry(int64_t B, int64_t T, const void* a, int a_batched, const void* x, void* carry, void* ws,
                     int64_t wsb, uint32_t* status, cudaStream_t st) {
-  using P = FoCarry<S, 3, 3, 3, REV>;
+  using P = FoCarry<S, PTB_FO_FWD_CH, PTB_FO_FWD_STAGES, PTB_FO_FWD_CTAS, REV>;
   typename P::Params p;
   p.a = static_cast<const S*>(a);
   p.a_row_stride = a_batched ? T : 0;
@@ -274,22 +277,41 @@ static int fo_carry(int64_t B, int64_t T, const void* a, int a_batched, const vo
 // ---------------------------------------------------------------------------- 2x2
 // samples per thread (odd), stages, CTAs per SM
 template <class S> struct SoCfg;
+// samples per thread (odd) and stages, per precision; one CTA per SM
 #ifndef PTB_SO_F32_FWD_NS
-#define PTB_SO_F32_FWD_NS 7
-#define PTB_SO_F32_BWD_NS 5
+#define PTB_SO_F32_FWD_NS 15
+#define PTB_SO_F32_FWD_STAGES 2
 #endif
-template <> struct SoCfg<float> { static constexpr int FWD_NS = PTB_SO_F32_FWD_NS, BWD_NS = PTB_SO_F32_BWD_NS; };
-template <> struct SoCfg<double> { static constexpr int FWD_NS = 3, BWD_NS = 3; };
-#ifndef PTB_SO_FWD_STAGES
-#define PTB_SO_FWD_STAGES 2
-#define PTB_SO_FWD_CTAS 2
+#ifndef PTB_SO_F32_BWD_NS
+#define PTB_SO_F32_BWD_NS 11
+#define PTB_SO_F32_BWD_STAGES 2
 #endif
-#ifndef PTB_SO_BWD_STAGES
-#define PTB_SO_BWD_STAGES 2
-#define PTB_SO_BWD_CTAS 2
+#ifndef PTB_SO_F64_FWD_NS
+#define PTB_SO_F64_FWD_NS 7
+#define PTB_SO_F64_FWD_STAGES 2
 #endif
-template <class S, bool LPV, bool XS> using SoFwdP = SoFwd<S, SoCfg<S>::FWD_NS, PTB_SO_FWD_STAGES, PTB_SO_FWD_CTAS, 1, LPV, XS>;
-template <class S, bool LPV, bool XS> using SoBwdP = SoBwd<S, SoCfg<S>::BWD_NS, PTB_SO_BWD_STAGES, PTB_SO_BWD_CTAS, 1, LPV, XS>;
+#ifndef PTB_SO_F64_BWD_NS
+#define PTB_SO_F64_BWD_NS 5
+#define PTB_SO_F64_BWD_STAGES 2
+#endif
+#ifndef PTB_SO_CTAS
+#define PTB_SO_CTAS 1
+#endif
+#ifndef PTB_SO_NT
+#define PTB_SO_NT 256   // compute threads per CTA
+#endif
+template <> struct SoCfg<float> {
+  static constexpr int FWD_NS = PTB_SO_F32_FWD_NS, FWD_ST = PTB_SO_F32_FWD_STAGES;
+  static constexpr int BWD_NS = PTB_SO_F32_BWD_NS, BWD_ST = PTB_SO_F32_BWD_STAGES;
+};
+template <> struct SoCfg<double> {
+  static constexpr int FWD_NS = PTB_SO_F64_FWD_NS, FWD_ST = PTB_SO_F64_FWD_STAGES;
+  static constexpr int BWD_NS = PTB_SO_F64_BWD_NS, BWD_ST = PTB_SO_F64_BWD_STAGES;
+};
+template <class S, bool LPV, bool XS>
+using SoFwdP = SoFwd<S, SoCfg<S>::FWD_NS, SoCfg<S>::FWD_ST, PTB_SO_CTAS, PTB_SO_NT, LPV, XS>;
+template <class S, bool LPV, bool XS>
+using SoBwdP = SoBwd<S, SoCfg<S>::BWD_NS, SoCfg<S>::BWD_ST, PTB_SO_CTAS, PTB_SO_NT, LPV, XS>;
 
 template <class S, bool LPV, bool XS>
 static int so_fwd(int64_t B, int64_t T, const void* A, int A_batched, const void* zi, const void* x, void* y,
@@ -341,17 +363,20 @@ static int so_bwd(int64_t B, int64_t T, const void* A, int A_batched, const void
 
 // ---------------------------------------------------------------------------- TDF-II section
 #ifndef PTB_BQ_FWD_CH
-#define PTB_BQ_FWD_CH 7
+#define PTB_BQ_FWD_CH 15
 #define PTB_BQ_FWD_STAGES 3
-#define PTB_BQ_FWD_CTAS 2
+#define PTB_BQ_FWD_CTAS 1
 #endif
 #ifndef PTB_BQ_BWD_CH
-#define PTB_BQ_BWD_CH 3
-#define PTB_BQ_BWD_STAGES 3
-#define PTB_BQ_BWD_CTAS 2
+#define PTB_BQ_BWD_CH 7
+#define PTB_BQ_BWD_STAGES 2
+#define PTB_BQ_BWD_CTAS 1
 #endif
-template <class S> using BqFwdP = BqFwd<S, PTB_BQ_FWD_CH, PTB_BQ_FWD_STAGES, PTB_BQ_FWD_CTAS, 1>;
-template <class S> using BqBwdP = BqBwd<S, PTB_BQ_BWD_CH, PTB_BQ_BWD_STAGES, PTB_BQ_BWD_CTAS, 1>;
+#ifndef PTB_BQ_NT
+#define PTB_BQ_NT 256
+#endif
+template <class S> using BqFwdP = BqFwd<S, PTB_BQ_FWD_CH, PTB_BQ_FWD_STAGES, PTB_BQ_FWD_CTAS, PTB_BQ_NT>;
+template <class S> using BqBwdP = BqBwd<S, PTB_BQ_BWD_CH, PTB_BQ_BWD_STAGES, PTB_BQ_BWD_CTAS, PTB_BQ_NT>;
 
 template <class S>
 static int bq_fwd(int64_t B, int64_t T, const void* b, const void* a, int batched, const void* zi, const void* x,

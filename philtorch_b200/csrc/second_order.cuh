@@ -102,19 +102,19 @@ struct SoFwdParams {
   int64_t T;
 };
 
-template <class S, int NS, int STAGES_, int MIN_CTAS_, int LBW_, bool LPV, bool XS>
+template <class S, int NS, int STAGES_, int MIN_CTAS_, int NT_, bool LPV, bool XS>
 struct SoFwd : MatAffine<S> {
   using Alg = MatAffine<S>;
   using typename Alg::Map;
   using typename Alg::State;
   using Partial = Pod<S, 1>;
   using Params = SoFwdParams<S>;
-  static constexpr int NT = 256;
+  static constexpr int NT = NT_;
   static constexpr int SPT = NS;
   static constexpr int TILE = NT * NS;
   static constexpr int STAGES = STAGES_;
   static constexpr int MIN_CTAS = MIN_CTAS_;
-  static constexpr int LBW = LBW_;
+  static constexpr int LBW = 1;
   static constexpr bool REVERSE = false;
   static constexpr bool HAS_PARTIAL = false;
   static constexpr int SLOT_WORDS = Words<Map>::W;
@@ -216,19 +216,19 @@ struct SoBwdParams {
   int want_gA;
 };
 
-template <class S, int NS, int STAGES_, int MIN_CTAS_, int LBW_, bool LPV, bool XS>
+template <class S, int NS, int STAGES_, int MIN_CTAS_, int NT_, bool LPV, bool XS>
 struct SoBwd : MatAffine<S> {
   using Alg = MatAffine<S>;
   using typename Alg::Map;
   using typename Alg::State;
   using Partial = Pod<S, 4>;
   using Params = SoBwdParams<S>;
-  static constexpr int NT = 256;
+  static constexpr int NT = NT_;
   static constexpr int SPT = NS;
   static constexpr int TILE = NT * NS;
   static constexpr int STAGES = STAGES_;
   static constexpr int MIN_CTAS = MIN_CTAS_;
-  static constexpr int LBW = LBW_;
+  static constexpr int LBW = 1;
   static constexpr bool REVERSE = true;
   static constexpr bool HAS_PARTIAL = !LPV;
   static constexpr int SLOT_WORDS = Words<Map>::W;

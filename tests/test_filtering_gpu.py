@@ -76,7 +76,7 @@ def test_against_scipy(order):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
-@pytest.mark.parametrize("T", [1, 2, 5, 100, 3071, 3072, 3073, 1535, 1536, 1537, 20001])
+@pytest.mark.parametrize("T", [1, 2, 5, 100, 3072, 3073, 3584, 3585, 7167, 7168, 7169, 7680, 15359, 15360, 15361, 40001])
 def test_biquad_lengths(dtype, T):
     B = 3
     w = workloads.sos_cascade(B=B, T=T, sections=1, dtype=dtype)

@@ -14,9 +14,11 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 DT = {"f32": torch.float32, "f64": torch.float64}
 
-# tile sizes are 3072 (fp32) / 1536 (fp64) samples: cover below / at / above one and several tiles,
-# and lengths that are not a multiple of 16 bytes (plain-load path)
-LENGTHS = [1, 2, 3, 4, 5, 31, 32, 33, 101, 1535, 1536, 1537, 3071, 3072, 3073, 4096, 6148, 9216, 12289, 40000]
+# tile sizes are a few thousand samples (e.g. 9216 forward / 5120 backward in fp32, half that in
+# fp64): cover below / at / above one and several tiles, and lengths that are not a multiple of
+# 16 bytes (plain-load path)
+LENGTHS = [1, 2, 3, 4, 5, 31, 32, 33, 101, 1535, 1536, 1537, 2560, 2561, 3072, 3073, 4608, 4609, 5119, 5120,
+           5121, 9215, 9216, 9217, 12289, 18432, 40000]
 
 
 def _cuda(*ts):

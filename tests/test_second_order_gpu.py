@@ -15,8 +15,8 @@ from oracle import cport
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
 DT = {"f32": torch.float32, "f64": torch.float64}
-# tiles: fwd 1792 (fp32) / 768 (fp64) samples, bwd 1280 / 768
-LENGTHS = [1, 2, 3, 7, 33, 101, 767, 768, 769, 1279, 1280, 1281, 1792, 1793, 4000, 9001]
+# tiles are a few thousand samples (e.g. 3840 forward / 2816 backward in fp32, 1792 / 1280 in fp64)
+LENGTHS = [1, 2, 3, 7, 33, 101, 768, 769, 1279, 1280, 1281, 1792, 1793, 2816, 2817, 3839, 3840, 3841, 9001, 16000]
 
 
 def _stable_A(shape, g, dtype):
