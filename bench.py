@@ -266,6 +266,59 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         dist.destroy_process_group()
 
 
+def run_time_sharded(args, rank: int, world: int, local_rank: int):
+    """Secondary line (not the headline metric): the long-sequence configuration, B = 8 rows of
+    T = 2^28 samples split along TIME over the ranks (strong scaling): per rank a carry pass, one
+    all-gather of (B,2) carries per direction, the seeded scan and the adjoint with its incoming state."""
+    import torch
+    import torch.distributed as dist
+
+    import philtorch_b200 as ptb
+    from philtorch_b200 import workloads
+    from philtorch_b200.sharded import time_sharded_linear_recurrence
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist.init_process_group("nccl", device_id=dev)
+    Bl, Ttot = 8, 1 << args.log2_T
+    Tl = Ttot // world
+    w = workloads.long_first_order(B=Bl, T=Tl, device=dev)   # this rank's time range (seeded per rank)
+    a, x, gy = w["a"].requires_grad_(), w["x"].requires_grad_(), w["gy"]
+    zi = torch.zeros(Bl, device=dev, requires_grad=True)
+
+    def step():
+        y = time_sharded_linear_recurrence(a, zi, x)
+        return torch.autograd.grad(y, (a, zi, x), gy)
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    dist.barrier(); torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    dist.barrier(); torch.cuda.synchronize(dev)
+    ptb.check_errors(dev)
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        ms = t.item() / args.steps
+        peak, kind = measured_peak()
+        print(json.dumps({"metric": METRIC, "value": Bl * Ttot / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
+                          "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms,
+                          "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+                          "data": "synthetic (seeded, generated on device)",
+                          "config": {"workload": f"time-sharded LPV first-order fwd+bwd, fp32, B=8, T=2^{args.log2_T}",
+                                     "sharding": "time axis, one (B,2) all-gather per direction"},
+                          "roofline": {"bound": "hbm", "achieved": 32 * Bl * Ttot / world / (ms * 1e-3) / 1e9,
+                                       "peak": peak, "unit": "GB/s", "peak_source": f"{kind} copy bandwidth",
+                                       "frac": 32 * Bl * Ttot / world / (ms * 1e-3) / 1e9 / peak,
+                                       "note": "algorithmic 32 B/sample per GPU; the carry passes are overhead"}}),
+              flush=True)
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -275,12 +328,22 @@ def main():
     # reduced cases for profiler captures (never a bench value): fewer rows, device-resident loop only
     ap.add_argument("--rows", type=int, default=B, help="rows per GPU (default: the benchmark's 256)")
     ap.add_argument("--kernels-only", action="store_true", help="skip the host-buffer and CPU legs")
+    ap.add_argument("--time-sharded", action="store_true",
+                    help="secondary workload: B=8 long rows split along time over the ranks")
+    ap.add_argument("--log2-T", type=int, default=28, dest="log2_T", help="total row length of --time-sharded")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference_arm(args, rank)
+        return
+    if args.time_sharded:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29512")
+        os.environ.setdefault("RANK", "0")
+        os.environ.setdefault("WORLD_SIZE", "1")
+        run_time_sharded(args, rank, world, local_rank)
         return
     run_ours(args, rank, world, local_rank)
 

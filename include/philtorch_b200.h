@@ -101,6 +101,14 @@ int ptb_lpv_recur_carry(int dtype, int64_t B, int64_t T, const void* a, int a_ba
                         int reverse, void* carry, void* workspace, int64_t workspace_bytes, uint32_t* status,
                         ptb_stream_t stream);
 
+/* Local scan of a time shard and its total map in ONE pass: y = the recurrence started from a ZERO
+ * state, carry[b] = { prod_t a[b,t], y[b,T-1] }.  With the true incoming state s of the shard,
+ * y_true[t] = y[t] + (prod_{u<=t} a[u]) s; the correction dies out where the running product
+ * underflows, so it is applied to a prefix only (philtorch_b200/sharded.py). */
+int ptb_lpv_recur_fwd_carry(int dtype, int64_t B, int64_t T, const void* a, int a_batched, const void* x, void* y,
+                            void* carry, void* workspace, int64_t workspace_bytes, uint32_t* status,
+                            ptb_stream_t stream);
+
 /* ---- first-order forward without any caller-side or library-side allocation -----------------
  * No counterpart in the reference.  Same computation and arguments as ptb_lpv_recur_fwd, minus the
  * workspace: the look-back scratch is a fixed 2 MiB array inside the library image (every GPU

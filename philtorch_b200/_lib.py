@@ -19,7 +19,7 @@ _DTYPES = {torch.float32: PTB_F32, torch.float64: PTB_F64}
 
 if not os.path.exists(LIB_PATH):
     raise ImportError(
-        f"{LIB_PATH} is missing: build it with `python -m philtorch_b200.build` "
+        f"{LIB_PATH} is missing: build it with `python philtorch_b200/build.py` "
         "(needs nvcc; philtorch_b200 has no CPU or pure-PyTorch fallback)")
 
 lib = ctypes.CDLL(LIB_PATH)
@@ -59,6 +59,8 @@ lib.ptb_biquad_tdf2_bwd.restype = _i32
 
 lib.ptb_lpv_recur_carry.argtypes = [_i32, _i64, _i64, _vp, _i32, _vp, _i32, _vp] + _tail
 lib.ptb_lpv_recur_carry.restype = _i32
+lib.ptb_lpv_recur_fwd_carry.argtypes = [_i32, _i64, _i64, _vp, _i32, _vp, _vp, _vp] + _tail
+lib.ptb_lpv_recur_fwd_carry.restype = _i32
 
 _status: dict[int, torch.Tensor] = {}
 

@@ -1,6 +1,6 @@
 """Builds ``libphiltorch_b200.so`` (the C-ABI CUDA library) in-tree with nvcc for sm_100a.
 
-    python -m philtorch_b200.build [-v]
+    python philtorch_b200/build.py [-v]      (by path: works even when the built library is stale)
 
 The library has no torch dependency; it links the CUDA runtime only.
 """

@@ -260,17 +260,18 @@ static int fo_bwd(int64_t B, int64_t T, const void* a, int a_batched, const void
   return rc;
 }
 
-template <class S, bool REV>
-static int fo_carry(int64_t B, int64_t T, const void* a, int a_batched, const void* x, void* carry, void* ws,
-                    int64_t wsb, uint32_t* status, cudaStream_t st) {
-  using P = FoCarry<S, PTB_FO_FWD_CH, PTB_FO_FWD_STAGES, PTB_FO_FWD_CTAS, REV>;
+template <class S, bool REV, bool WRITE = false>
+static int fo_carry(int64_t B, int64_t T, const void* a, int a_batched, const void* x, void* y, void* carry,
+                    void* ws, int64_t wsb, uint32_t* status, cudaStream_t st) {
+  using P = FoCarry<S, PTB_FO_FWD_CH, PTB_FO_FWD_STAGES, PTB_FO_FWD_CTAS, REV, WRITE>;
   typename P::Params p;
   p.a = static_cast<const S*>(a);
   p.a_row_stride = a_batched ? T : 0;
   p.x = static_cast<const S*>(x);
+  p.y = static_cast<S*>(y);
   p.carry = static_cast<S*>(carry);
   p.T = T;
-  const bool bulk = aligned16(x) && aligned16(a) && (T * sizeof(S)) % 16 == 0;
+  const bool bulk = aligned16(x) && aligned16(a) && (!WRITE || aligned16(y)) && (T * sizeof(S)) % 16 == 0;
   return launch_scan<P>(p, B, T, bulk, ws, wsb, status, st, nullptr, nullptr);
 }
 
@@ -531,17 +532,27 @@ int ptb_lpv_recur_carry(int dtype, int64_t B, int64_t T, const void* a, int a_ba
   if (T == 0 || !a || !x || !carry) return PTB_ERR_ARG;
   switch (dtype) {
     case PTB_F32:
-      return reverse ? fo_carry<float, true>(B, T, a, a_batched, x, carry, workspace, workspace_bytes, status,
+      return reverse ? fo_carry<float, true>(B, T, a, a_batched, x, nullptr, carry, workspace, workspace_bytes, status,
                                              (cudaStream_t)stream)
-                     : fo_carry<float, false>(B, T, a, a_batched, x, carry, workspace, workspace_bytes, status,
+                     : fo_carry<float, false>(B, T, a, a_batched, x, nullptr, carry, workspace, workspace_bytes, status,
                                               (cudaStream_t)stream);
     case PTB_F64:
-      return reverse ? fo_carry<double, true>(B, T, a, a_batched, x, carry, workspace, workspace_bytes, status,
+      return reverse ? fo_carry<double, true>(B, T, a, a_batched, x, nullptr, carry, workspace, workspace_bytes, status,
                                               (cudaStream_t)stream)
-                     : fo_carry<double, false>(B, T, a, a_batched, x, carry, workspace, workspace_bytes, status,
+                     : fo_carry<double, false>(B, T, a, a_batched, x, nullptr, carry, workspace, workspace_bytes, status,
                                                (cudaStream_t)stream);
     default: return PTB_ERR_ARG;
   }
+}
+
+int ptb_lpv_recur_fwd_carry(int dtype, int64_t B, int64_t T, const void* a, int a_batched, const void* x, void* y,
+                            void* carry, void* workspace, int64_t workspace_bytes, uint32_t* status,
+                            ptb_stream_t stream) {
+  if (B < 0 || T < 0) return PTB_ERR_ARG;
+  if (B == 0) return PTB_OK;
+  if (T == 0 || !a || !x || !y || !carry) return PTB_ERR_ARG;
+  PTB_DISPATCH(dtype, (fo_carry<S, false, true>(B, T, a, a_batched, x, y, carry, workspace, workspace_bytes,
+                                                 status, (cudaStream_t)stream)));
 }
 
 int64_t ptb_lpv_recur_fwd_static_max_tiles(int dtype) {

@@ -314,16 +314,20 @@ namespace ptb {
 // which also represents the constant operators the look-back needs.
 // REVERSE_ = false: maps of the forward recurrence, offsets x.
 // REVERSE_ = true : maps of the adjoint recurrence over c, offsets a*gy, time descending.
+// WRITE_   = true : (forward only) additionally writes the sequence y started from a ZERO state,
+//                   i.e. the local scan of a time shard and its total map in one pass.
 template <class S>
 struct FoCarryParams {
   const S* a; int64_t a_row_stride;
   const S* x;        // x (forward) or gy (adjoint)
+  S* y;              // WRITE_ only: (B,T) zero-start outputs
   S* carry;          // (B,2): {product of a over the row, end state from a zero start}
   int64_t T;
 };
 
-template <class S, int CH, int STAGES_, int MIN_CTAS_, bool REVERSE_>
+template <class S, int CH, int STAGES_, int MIN_CTAS_, bool REVERSE_, bool WRITE_ = false>
 struct FoCarry {
+  static_assert(!(REVERSE_ && WRITE_), "the writing variant is forward only");
   using Map = Pod<S, 3>;
   using State = Pod<S, 2>;
   using Partial = Pod<S, 1>;
@@ -363,6 +367,7 @@ struct FoCarry {
     const uint32_t bytes = (uint32_t)nvalid * sizeof(S);
     io.load(X_OFF, p.x + row * p.T + t0, bytes);
     io.load(A_OFF, p.a + row * p.a_row_stride + t0, bytes);
+    if (WRITE_) io.store(X_OFF, p.y + row * p.T + t0, bytes);
   }
   static __device__ __forceinline__ State row_init(const Params&, int64_t) { return zero_state(); }
   static __device__ __forceinline__ void row_final(const Params& p, int64_t row, const State& s) {
@@ -392,8 +397,25 @@ struct FoCarry {
     }
     Map m; m.v[0] = P; m.v[1] = S(0); m.v[2] = s; return m;   // S -> (P S.P, P S.s + s)
   }
-  static __device__ __forceinline__ Partial finish(const Params&, const State&, unsigned char*, int, int64_t,
-                                                   int64_t, int) {
+  static __device__ __forceinline__ Partial finish(const Params&, const State& in, unsigned char* stage, int tpos,
+                                                   int64_t, int64_t, int nvalid) {
+    if (WRITE_) {
+      const int p0 = tpos * SPT;
+      int nv = nvalid - p0;
+      nv = nv < 0 ? 0 : (nv > SPT ? SPT : nv);
+      S x[SPT], a[SPT];
+#pragma unroll
+      for (int c = 0; c < CH; ++c) {
+        VecIO<S, V>::ld(stage + X_OFF + (size_t)p0 * sizeof(S) + 16 * c, &x[c * V]);
+        VecIO<S, V>::ld(stage + A_OFF + (size_t)p0 * sizeof(S) + 16 * c, &a[c * V]);
+      }
+      S h = in.v[1];   // the state reached from a zero start
+#pragma unroll
+      for (int j = 0; j < SPT; ++j)
+        if (j < nv) { h = a[j] * h + x[j]; x[j] = h; }
+#pragma unroll
+      for (int c = 0; c < CH; ++c) VecIO<S, V>::st(stage + X_OFF + (size_t)p0 * sizeof(S) + 16 * c, &x[c * V]);
+    }
     Partial r; r.v[0] = S(0); return r;
   }
 };

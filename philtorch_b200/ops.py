@@ -183,6 +183,34 @@ def _lpv_recur_carry(a: Tensor, x: Tensor, reverse: bool) -> Tensor:
 
 _LIB.impl("lpv_recur_carry", _lpv_recur_carry, "CUDA")
 
+# local scan of a time shard from a zero state, plus the shard's total map, in one pass
+_LIB.define("lpv_recur_zero_carry(Tensor a, Tensor x) -> (Tensor, Tensor)", tags=_TAGS)
+
+
+def _lpv_recur_zero_carry(a: Tensor, x: Tensor):
+    torch._check(x.dim() == 2 and a.dim() in (1, 2) and a.shape[-1] == x.shape[1] and x.shape[1] > 0,
+                 lambda: "a must be (T,) or (B,T) and x (B,T), T > 0")
+    dev = _lib.require_cuda(a, x)
+    if a.dtype != x.dtype:
+        raise RuntimeError("a must have the same scalar type as input")
+    B, T = x.shape
+    a_c, x_c = a.contiguous(), x.contiguous()
+    y = torch.empty_like(x_c)
+    carry = x.new_empty(B, 2)
+    if B:
+        _lib.call(lib.ptb_lpv_recur_fwd_carry, dev, B, T, _lib.dtype_code(x), B, T, ptr(a_c), int(a.dim() == 2),
+                  ptr(x_c), ptr(y), ptr(carry))
+    return y, carry
+
+
+_LIB.impl("lpv_recur_zero_carry", _lpv_recur_zero_carry, "CUDA")
+
+
+@torch.library.register_fake("philtorch_b200::lpv_recur_zero_carry")
+def _(a, x):
+    return torch.empty_like(x, memory_format=torch.contiguous_format), x.new_empty(x.shape[0], 2)
+
+
 
 @torch.library.register_fake("philtorch_b200::lpv_recur_carry")
 def _(a, x, reverse):
@@ -363,5 +391,5 @@ def _no_backend(name):
 
 
 for _name in ("lti_recur", "lti_recur_bwd", "lpv_recur", "lpv_recur_bwd", "lti_recur2", "lti_recur2_sx", "recur2",
-              "recur2_sx", "lti_recur2_bwd", "recur2_bwd", "biquad_tdf2", "biquad_tdf2_bwd", "lpv_recur_carry"):
+              "recur2_sx", "lti_recur2_bwd", "recur2_bwd", "biquad_tdf2", "biquad_tdf2_bwd", "lpv_recur_carry", "lpv_recur_zero_carry"):
     _LIB.impl(_name, _no_backend(_name), "CPU")

@@ -3,14 +3,21 @@
 The reference has no multi-device code; this mode exists for rows too long for one GPU
 (e.g. B = 8, T = 2^28).  Rank r of W owns the contiguous samples [r T/W, (r+1) T/W) of every row.
 
-Forward, per rank:  (1) carry pass over the shard -> per row (P_r, e_r) = (product of a, end state
-from a zero start);  (2) ONE all-gather of the (B, 2) carries;  (3) every rank folds the carries
-of the ranks before it into its true incoming state s_r = P_{r-1} s_{r-1} + e_{r-1} (s_0 = zi);
-(4) the ordinary forward scan started from s_r.
-Backward mirrors it with the adjoint recurrence run from the right: carries flow from rank W-1
-down, the incoming adjoint state enters the local adjoint kernel as ``g_in``.
+Forward, per rank
+  (1) ONE pass over the shard: the scan started from a zero state, y0, together with the shard's
+      total affine map (P_r, e_r) = (product of a, y0's last sample);
+  (2) ONE all-gather of the (B, 2) maps; every rank folds the maps of the ranks before it into its
+      true incoming state  s_r = P_{r-1} s_{r-1} + e_{r-1}  (s_0 = zi);
+  (3) fix-up  y[t] = y0[t] + (prod_{u<=t} a[u]) s_r.  The running product normally underflows to
+      exactly zero after a few thousand samples (|a| < 1), from where the correction is exactly
+      zero: it is applied block by block from the shard's start and stops at the first block that
+      ends with an all-zero correction (one tiny device->host read per block).  If the products
+      never vanish the blocks double until the whole shard has been corrected: still exact.
+Backward mirrors it from the right: the local adjoint scan with a zero incoming state, one
+all-gather of (P_r, adjoint end state), and a fix-up of grad_x / grad_a over a suffix.
 
-The collective is tiny (W x B x 2 scalars) and latency-bound; everything else is local.
+The collectives are tiny (W x B x 2 scalars) and latency-bound; everything else is local, so a
+rank moves the same 12 + 20 bytes per sample as an unsharded run.
 """
 from __future__ import annotations
 
@@ -21,14 +28,17 @@ import torch.distributed as dist
 from torch import Tensor
 from torch.autograd import Function
 
+FIXUP_BLOCK = 1 << 16   # first fix-up block (samples); later blocks double
+
 
 class _GpuKernels:
     """The compiled kernels (default).  Tests substitute a CPU stand-in with the same methods to
     exercise the rank logic without a GPU."""
 
     @staticmethod
-    def carry(a: Tensor, x: Tensor, reverse: bool) -> Tensor:
-        return torch.ops.philtorch_b200.lpv_recur_carry(a, x, reverse)
+    def scan_zero(a: Tensor, x: Tensor):
+        """(y from a zero state, carry (B,2) = {prod a, y[:, -1]})"""
+        return torch.ops.philtorch_b200.lpv_recur_zero_carry(a, x)
 
     @staticmethod
     def forward(a: Tensor, zi: Tensor, x: Tensor) -> Tensor:
@@ -63,17 +73,57 @@ def fold_carries_backward(carries: Tensor, rank: int) -> Tensor:
     return c
 
 
+def _rows(a: Tensor, lo: int, hi: int) -> Tensor:
+    return a[..., lo:hi].contiguous()
+
+
+def fixup_forward(k, a: Tensor, y: Tensor, s: Tensor) -> None:
+    """In place: y[t] += (prod_{u<=t} a[u]) s, block by block until the correction has died out."""
+    T = y.shape[1]
+    lo, blk = 0, FIXUP_BLOCK
+    while lo < T:
+        hi = min(T, lo + blk)
+        z = k.forward(_rows(a, lo, hi), s.contiguous(), torch.zeros_like(y[:, lo:hi]))
+        y[:, lo:hi] += z
+        s = z[:, -1]
+        if not bool((s != 0).any()):
+            break
+        lo, blk = hi, blk * 2
+
+
+def fixup_backward(k, a: Tensor, s_in: Tensor, y: Tensor, c: Tensor, gx: Tensor, ga: Optional[Tensor]) -> None:
+    """In place: adds to grad_x (and grad_a) the adjoint driven by the state ``c`` entering the shard
+    from the right, suffix block by suffix block until it has died out."""
+    T = y.shape[1]
+    hi, blk = T, FIXUP_BLOCK
+    while hi > 0:
+        lo = max(0, hi - blk)
+        y_prev = s_in if lo == 0 else y[:, lo - 1]
+        ga_b, c, gx_b = k.backward(_rows(a, lo, hi), y_prev.contiguous(), y[:, lo:hi].contiguous(),
+                                   torch.zeros_like(y[:, lo:hi]), c.contiguous(), ga is not None)
+        gx[:, lo:hi] += gx_b
+        if ga is not None:
+            ga[..., lo:hi] += ga_b   # (B,T) per row, or (T,) when the coefficients are shared
+        if not bool((c != 0).any()):
+            break
+        hi, blk = lo, blk * 2
+
+
 class TimeShardedLPVRecurrence(Function):
     @staticmethod
     def forward(ctx: Any, a: Tensor, zi: Tensor, x: Tensor, group, kernels) -> Tensor:
         k = kernels or _GpuKernels
         rank, world = dist.get_rank(group), dist.get_world_size(group)
         if world > 1:
-            carries = _all_gather(k.carry(a, x, False), group)
-            s = fold_carries_forward(carries, zi, rank)
+            y, carry = k.scan_zero(a, x)
+            carries = _all_gather(carry, group)
+            s = fold_carries_forward(carries, zi, rank).contiguous()
+            fixup_forward(k, a, y, s)
+            ctx.P = carry[:, 0].contiguous()
         else:
-            s = zi
-        y = k.forward(a, s.contiguous(), x)
+            s = zi.contiguous()
+            y = k.forward(a, s, x)
+            ctx.P = None
         ctx.group, ctx.kernels, ctx.rank, ctx.world = group, k, rank, world
         ctx.save_for_backward(a, s, y)
         return y
@@ -84,12 +134,14 @@ class TimeShardedLPVRecurrence(Function):
         k = ctx.kernels
         need_a, need_zi, need_x = ctx.needs_input_grad[:3]
         gy = gy.contiguous()
-        g_in: Optional[Tensor] = None
+        ga, gs, gx = k.backward(a, s, y, gy, None, need_a)   # adjoint with nothing entering from the right
         if ctx.world > 1:
-            carries = _all_gather(k.carry(a, gy, True), ctx.group)
-            g_in = fold_carries_backward(carries, ctx.rank).contiguous()
-        ga, gs, gx = k.backward(a, s, y, gy, g_in, need_a)
-        # gs = adjoint state leaving this shard on the left; only rank 0's is the gradient of zi
+            carries = _all_gather(torch.stack([ctx.P, gs], dim=1), ctx.group)
+            c = fold_carries_backward(carries, ctx.rank)
+            if ctx.rank < ctx.world - 1:
+                fixup_backward(k, a, s, y, c, gx, ga if need_a else None)
+            gs = ctx.P * c + gs   # adjoint state leaving this shard on the left
+        # only rank 0's is the gradient of zi (sum over ranks = the gradient)
         gzi = gs if ctx.rank == 0 else torch.zeros_like(gs)
         return (ga if need_a else None, gzi if need_zi else None, gx if need_x else None, None, None)
 

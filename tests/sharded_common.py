@@ -20,6 +20,12 @@ class OracleKernels:
         return torch.stack([P, e], dim=1)
 
     @staticmethod
+    def scan_zero(a, x):
+        y = cport.recur1(a, torch.zeros(x.shape[0], dtype=x.dtype), x)
+        ab = a if a.dim() == 2 else a.expand(x.shape[0], -1)
+        return y, torch.stack([ab.prod(dim=1), y[:, -1]], dim=1)
+
+    @staticmethod
     def forward(a, zi, x):
         return cport.recur1(a, zi, x)
 

@@ -13,18 +13,22 @@ from conftest import rel_err
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _worker(rank, world, port, B, T, q):
+def _worker(rank, world, port, B, T, q, slow_decay):
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
+        from philtorch_b200 import sharded
         from philtorch_b200.sharded import time_sharded_linear_recurrence
         from sharded_common import OracleKernels
 
+        sharded.FIXUP_BLOCK = 16   # several (doubling) fix-up blocks inside a 96-sample shard
         g = torch.Generator().manual_seed(7)
         a = torch.rand(B, T, generator=g, dtype=torch.float64) * 1.9 - 0.95
+        if slow_decay:
+            a = 0.98 + 0.04 * a   # products never vanish: the fix-up must cover the whole shard
         zi = torch.randn(B, generator=g, dtype=torch.float64)
         x = torch.randn(B, T, generator=g, dtype=torch.float64)
         gy = torch.randn(B, T, generator=g, dtype=torch.float64)
@@ -40,15 +44,15 @@ def _worker(rank, world, port, B, T, q):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2, 3])
-def test_two_rank_gloo(world):
+@pytest.mark.parametrize("world,slow_decay", [(2, False), (3, False), (2, True)])
+def test_two_rank_gloo(world, slow_decay):
     from sharded_common import full_reference
 
     B, T = 3, 96 * world
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29500 + os.getpid() % 2000 + world
-    procs = [ctx.Process(target=_worker, args=(r, world, port, B, T, q)) for r in range(world)]
+    port = 29500 + os.getpid() % 2000 + world + 10 * int(slow_decay)
+    procs = [ctx.Process(target=_worker, args=(r, world, port, B, T, q, slow_decay)) for r in range(world)]
     for p in procs:
         p.start()
     res = sorted([q.get(timeout=60) for _ in range(world)], key=lambda t: t[0])
@@ -57,6 +61,8 @@ def test_two_rank_gloo(world):
         assert p.exitcode == 0
     g = torch.Generator().manual_seed(7)
     a = torch.rand(B, T, generator=g, dtype=torch.float64) * 1.9 - 0.95
+    if slow_decay:
+        a = 0.98 + 0.04 * a
     zi = torch.randn(B, generator=g, dtype=torch.float64)
     x = torch.randn(B, T, generator=g, dtype=torch.float64)
     gy = torch.randn(B, T, generator=g, dtype=torch.float64)

@@ -36,6 +36,21 @@ def test_carry_kernel(dtype, T, reverse):
     ptb.check_errors()
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+@pytest.mark.parametrize("T", [7, 4608, 9217, 50000])
+def test_zero_start_scan_with_carry(dtype, T):
+    B = 4
+    g = torch.Generator().manual_seed(T)
+    a = (0.7 + 0.2999 * torch.rand(B, T, generator=g, dtype=torch.float64)).to(dtype)
+    x = torch.randn(B, T, generator=g, dtype=torch.float64).to(dtype)
+    y, carry = ops.lpv_recur_zero_carry(a.to(DEV), x.to(DEV))
+    y_ref, carry_ref = OracleKernels.scan_zero(a, x)
+    t = tol(dtype)
+    assert rel_err(y, y_ref) <= t and rel_err(carry[:, 1], carry_ref[:, 1]) <= t
+    assert ((carry[:, 0].cpu().double() - carry_ref[:, 0].double()).abs() <= t * carry_ref[:, 0].double().abs() + 1e-300).all()
+    ptb.check_errors()
+
+
 @pytest.mark.parametrize("world", [2, 8])
 def test_shards_emulated_on_one_gpu(world):
     """Config-5 distribution (a ~ U(0.9, 0.999)), B = 8, shards of 2^17 samples."""
