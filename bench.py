@@ -43,7 +43,7 @@ BYTES_FWD, BYTES_BWD = 12, 20          # algorithmic bytes per sample: r a,x w y
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one backward launch at the bench size, scaled
 # from the ncu capture summarised in profiles/first_order_lpv_fwd_bwd_ncu.md.
-NCU_TRAFFIC_BWD_BYTES = 4 * 1299106304   # 64-row capture x 4 (traffic is proportional to rows)
+NCU_TRAFFIC_BWD_BYTES = 4 * 1300032256   # 64-row capture x 4 (traffic is proportional to rows)
 
 
 def measured_peak():

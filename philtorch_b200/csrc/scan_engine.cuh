@@ -21,9 +21,14 @@
 //                           never wait for this CTA's look-back.  Phase 2 (as soon as the tile's
 //                           incoming state is known): every thread replays its samples from its
 //                           own incoming state and writes the results into the stage.
-//       look-back warps     look back over predecessor tiles -- 32 at a time, one per lane --
-//                           until they meet an end state (flag 2), hand the incoming state to
-//                           the compute warps and publish the tile's end state.
+//       look-back warp      starts as soon as the tile's ticket is known (it needs nothing from the
+//                           tile's own operands, so it overlaps their load): looks back over
+//                           predecessor tiles, one per lane, until it meets an end state (flag 2),
+//                           hands the incoming state to the compute warps and, once the tile
+//                           aggregate is known, publishes the tile's end state.
+//   * Tiles are large (tens of KB per array and bulk copy) and there is one CTA per SM: large
+//     contiguous requests are what the memory system serves fastest; 2-4 stages fill the SM's
+//     shared memory.
 //   * P::SPT is chosen so that the per-thread footprint of every staged array is an ODD number of
 //     16-byte (or 8-byte) units: the strided 128-bit / 64-bit shared-memory accesses are then
 //     bank-conflict free without swizzling.
