@@ -148,16 +148,12 @@ struct BqFwd : MatAffine<S> {
     }
     return m;
   }
-  static __device__ __forceinline__ Partial finish(const Params& p, const State& in, unsigned char* stage,
-                                                   int tpos, int64_t row, int64_t, int nvalid) {
-    BqCoef<S> k;
-    k.load(p.b, p.b_stride, p.a, p.a_stride, row);
-    S x[SPT];
-    const int nv = load_x(stage, tpos, nvalid, x);
-    S h0 = in.v[0], h1 = in.v[1];
+  // FULL: every sample of the thread is valid, so the per-sample guards compile away
+  template <bool FULL>
+  static __device__ __forceinline__ void replay(const BqCoef<S>& k, S h0, S h1, int nv, S* x) {
 #pragma unroll
     for (int j = 0; j < SPT; ++j) {
-      if (j < nv) {
+      if (FULL || j < nv) {
         const S xj = x[j];
         x[j] = h0 + k.b0 * xj;
         const S n0 = k.na1 * h0 + h1 + k.B0 * xj;
@@ -165,6 +161,15 @@ struct BqFwd : MatAffine<S> {
         h0 = n0;
       }
     }
+  }
+  static __device__ __forceinline__ Partial finish(const Params& p, const State& in, unsigned char* stage,
+                                                   int tpos, int64_t row, int64_t, int nvalid) {
+    BqCoef<S> k;
+    k.load(p.b, p.b_stride, p.a, p.a_stride, row);
+    S x[SPT];
+    const int nv = load_x(stage, tpos, nvalid, x);
+    if (nv == SPT) replay<true>(k, in.v[0], in.v[1], nv, x);
+    else replay<false>(k, in.v[0], in.v[1], nv, x);
     unsigned char* px = stage + X_OFF + (size_t)tpos * SPT * sizeof(S);
 #pragma unroll
     for (int c = 0; c < CH; ++c) VecIO<S, V>::st(px + 16 * c, &x[c * V]);
@@ -272,26 +277,18 @@ struct BqBwd : MatAffine<S> {
     }
     return m;
   }
-  static __device__ __forceinline__ Partial finish(const Params& p, const State& in, unsigned char* stage,
-                                                   int tpos, int64_t row, int64_t, int nvalid) {
-    BqCoef<S> k;
-    k.load(p.b, p.b_stride, p.a, p.a_stride, row);
-    S g[SPT], x[SPT], y[SPT];
-    const int nv = load_slot(stage, G_OFF, tpos, nvalid, g);
-    if (p.want_coef) {
-      load_slot(stage, X_OFF, tpos, nvalid, x);
-      load_slot(stage, Y_OFF, tpos, nvalid, y);
-    }
-    S l0 = in.v[0], l1 = in.v[1];
+  template <bool FULL, bool COEF>
+  static __device__ __forceinline__ Partial replay(const BqCoef<S>& k, S l0, S l1, int nv, S* g, const S* x,
+                                                   const S* y) {
     Partial acc;
 #pragma unroll
     for (int i = 0; i < 5; ++i) acc.v[i] = S(0);
 #pragma unroll
     for (int j = SPT - 1; j >= 0; --j) {
-      if (j < nv) {
+      if (FULL || j < nv) {
         const S gj = g[j];
         g[j] = k.b0 * gj + k.B0 * l0 + k.B1 * l1;
-        if (p.want_coef) {
+        if (COEF) {
           acc.v[0] += gj * x[j];
           acc.v[1] += x[j] * l0;
           acc.v[2] += x[j] * l1;
@@ -302,6 +299,24 @@ struct BqBwd : MatAffine<S> {
         l1 = l0;
         l0 = n0;
       }
+    }
+    return acc;
+  }
+  static __device__ __forceinline__ Partial finish(const Params& p, const State& in, unsigned char* stage,
+                                                   int tpos, int64_t row, int64_t, int nvalid) {
+    BqCoef<S> k;
+    k.load(p.b, p.b_stride, p.a, p.a_stride, row);
+    S g[SPT], x[SPT], y[SPT];
+    const int nv = load_slot(stage, G_OFF, tpos, nvalid, g);
+    Partial acc;
+    if (p.want_coef) {
+      load_slot(stage, X_OFF, tpos, nvalid, x);
+      load_slot(stage, Y_OFF, tpos, nvalid, y);
+      acc = nv == SPT ? replay<true, true>(k, in.v[0], in.v[1], nv, g, x, y)
+                      : replay<false, true>(k, in.v[0], in.v[1], nv, g, x, y);
+    } else {
+      acc = nv == SPT ? replay<true, false>(k, in.v[0], in.v[1], nv, g, x, y)
+                      : replay<false, false>(k, in.v[0], in.v[1], nv, g, x, y);
     }
     unsigned char* pg = stage + G_OFF + (size_t)tpos * SPT * sizeof(S);
 #pragma unroll

@@ -113,7 +113,8 @@ struct FoFwd : ScalarAffine<S> {
     S x[SPT];
     S a[LPV ? SPT : 1];
     int nv;
-    __device__ __forceinline__ S coef(int j) const { return LPV ? a[j] : (j < nv ? a[0] : S(1)); }
+    // time-invariant: the row's coefficient, 1 for masked samples (only tail threads have any)
+    __device__ __forceinline__ S coef(int j) const { return LPV ? a[j] : ((nv == SPT || j < nv) ? a[0] : S(1)); }
     __device__ __forceinline__ void load(const Params& p, const unsigned char* stage, int tpos, int64_t row,
                                          int nvalid) {
       const int p0 = tpos * SPT;
@@ -226,7 +227,8 @@ struct FoBwd : ScalarAffine<S> {
     S g[SPT];
     S a[LPV ? SPT : 1];
     int nv;
-    __device__ __forceinline__ S coef(int j) const { return LPV ? a[j] : (j < nv ? a[0] : S(1)); }
+    // time-invariant: the row's coefficient, 1 for masked samples (only tail threads have any)
+    __device__ __forceinline__ S coef(int j) const { return LPV ? a[j] : ((nv == SPT || j < nv) ? a[0] : S(1)); }
     __device__ __forceinline__ void load(const Params& p, const unsigned char* stage, int tpos, int64_t row,
                                          int nvalid) {
       const int p0 = tpos * SPT;

@@ -139,9 +139,11 @@ struct SoFwd : MatAffine<S> {
   }
 
   // operands of sample j of this thread; masked samples are the identity map
+  // (FULL: the whole thread is inside the row, the per-sample test compiles away)
+  template <bool FULL>
   static __device__ __forceinline__ void sample(const Params& p, const unsigned char* stage, int pos, int nvalid,
                                                 int swap, const S* arow, S* a, S* x) {
-    if (pos < nvalid) {
+    if (FULL || pos < nvalid) {
       if (LPV) SoIO<S>::ld_mat(stage + A_OFF, pos, swap, a);
       else { a[0] = arow[0]; a[1] = arow[1]; a[2] = arow[2]; a[3] = arow[3]; }
       if (XS) { x[0] = *reinterpret_cast<const S*>(stage + XS_OFF + (size_t)pos * SZ); x[1] = S(0); }
@@ -159,6 +161,17 @@ struct SoFwd : MatAffine<S> {
 
   static __device__ __forceinline__ Map aggregate(const Params& p, const unsigned char* stage, int tpos,
                                                   int64_t row, int64_t, int nvalid) {
+    return (tpos + 1) * NS <= nvalid ? aggregate_t<true>(p, stage, tpos, row, nvalid)
+                                     : aggregate_t<false>(p, stage, tpos, row, nvalid);
+  }
+  static __device__ __forceinline__ Partial finish(const Params& p, const State& in, unsigned char* stage,
+                                                   int tpos, int64_t row, int64_t, int nvalid) {
+    return (tpos + 1) * NS <= nvalid ? finish_t<true>(p, in, stage, tpos, row, nvalid)
+                                     : finish_t<false>(p, in, stage, tpos, row, nvalid);
+  }
+  template <bool FULL>
+  static __device__ __forceinline__ Map aggregate_t(const Params& p, const unsigned char* stage, int tpos,
+                                                    int64_t row, int nvalid) {
     S arow[4];
     row_matrix(p, row, arow);
     const int swap = (tpos >> 2) & 1;
@@ -166,7 +179,7 @@ struct SoFwd : MatAffine<S> {
 #pragma unroll
     for (int j = 0; j < NS; ++j) {
       S a[4], x[2];
-      sample(p, stage, tpos * NS + j, nvalid, swap, arow, a, x);
+      sample<FULL>(p, stage, tpos * NS + j, nvalid, swap, arow, a, x);
       Map n;
       n.v[0] = a[0] * m.v[0] + a[1] * m.v[2];
       n.v[1] = a[0] * m.v[1] + a[1] * m.v[3];
@@ -178,8 +191,9 @@ struct SoFwd : MatAffine<S> {
     }
     return m;
   }
-  static __device__ __forceinline__ Partial finish(const Params& p, const State& in, unsigned char* stage,
-                                                   int tpos, int64_t row, int64_t, int nvalid) {
+  template <bool FULL>
+  static __device__ __forceinline__ Partial finish_t(const Params& p, const State& in, unsigned char* stage,
+                                                     int tpos, int64_t row, int nvalid) {
     S arow[4];
     row_matrix(p, row, arow);
     const int swap = (tpos >> 2) & 1;
@@ -188,7 +202,7 @@ struct SoFwd : MatAffine<S> {
 #pragma unroll
     for (int j = 0; j < NS; ++j) {
       S a[4], x[2];
-      sample(p, stage, tpos * NS + j, nvalid, swap, arow, a, x);
+      sample<FULL>(p, stage, tpos * NS + j, nvalid, swap, arow, a, x);
       const S n0 = a[0] * h0 + a[1] * h1 + x[0];
       const S n1 = a[2] * h0 + a[3] * h1 + x[1];
       h0 = n0; h1 = n1;
@@ -269,9 +283,10 @@ struct SoBwd : MatAffine<S> {
       arow[0] = __ldg(q); arow[1] = __ldg(q + 1); arow[2] = __ldg(q + 2); arow[3] = __ldg(q + 3);
     }
   }
+  template <bool FULL>
   static __device__ __forceinline__ void sample(const unsigned char* stage, int pos, int nvalid, int swap,
                                                 const S* arow, S* a, S* g) {
-    if (pos < nvalid) {
+    if (FULL || pos < nvalid) {
       if (LPV) SoIO<S>::ld_mat(stage + A_OFF, pos, swap, a);
       else { a[0] = arow[0]; a[1] = arow[1]; a[2] = arow[2]; a[3] = arow[3]; }
       SoIO<S>::ld_vec(stage + G_OFF, pos, g);
@@ -280,9 +295,20 @@ struct SoBwd : MatAffine<S> {
     }
   }
 
-  // map over c (time descending): c_out = A_j^T (gy_j + c_in)
   static __device__ __forceinline__ Map aggregate(const Params& p, const unsigned char* stage, int tpos,
                                                   int64_t row, int64_t, int nvalid) {
+    return (tpos + 1) * NS <= nvalid ? aggregate_t<true>(p, stage, tpos, row, nvalid)
+                                     : aggregate_t<false>(p, stage, tpos, row, nvalid);
+  }
+  static __device__ __forceinline__ Partial finish(const Params& p, const State& in, unsigned char* stage,
+                                                   int tpos, int64_t row, int64_t t0, int nvalid) {
+    return (tpos + 1) * NS <= nvalid ? finish_t<true>(p, in, stage, tpos, row, t0, nvalid)
+                                     : finish_t<false>(p, in, stage, tpos, row, t0, nvalid);
+  }
+  // map over c (time descending): c_out = A_j^T (gy_j + c_in)
+  template <bool FULL>
+  static __device__ __forceinline__ Map aggregate_t(const Params& p, const unsigned char* stage, int tpos,
+                                                    int64_t row, int nvalid) {
     S arow[4];
     row_matrix(p, row, arow);
     const int swap = (tpos >> 2) & 1;
@@ -290,7 +316,7 @@ struct SoBwd : MatAffine<S> {
 #pragma unroll
     for (int j = NS - 1; j >= 0; --j) {
       S a[4], g[2];
-      sample(stage, tpos * NS + j, nvalid, swap, arow, a, g);
+      sample<FULL>(stage, tpos * NS + j, nvalid, swap, arow, a, g);
       const S u0 = m.v[4] + g[0], u1 = m.v[5] + g[1];
       Map n;   // A^T = [a0 a2; a1 a3]
       n.v[0] = a[0] * m.v[0] + a[2] * m.v[2];
@@ -303,8 +329,9 @@ struct SoBwd : MatAffine<S> {
     }
     return m;
   }
-  static __device__ __forceinline__ Partial finish(const Params& p, const State& in, unsigned char* stage,
-                                                   int tpos, int64_t row, int64_t t0, int nvalid) {
+  template <bool FULL>
+  static __device__ __forceinline__ Partial finish_t(const Params& p, const State& in, unsigned char* stage,
+                                                     int tpos, int64_t row, int64_t t0, int nvalid) {
     S arow[4];
     row_matrix(p, row, arow);
     const int swap = (tpos >> 2) & 1;
@@ -314,7 +341,7 @@ struct SoBwd : MatAffine<S> {
     if (p.want_gA) {
 #pragma unroll
       for (int j = 0; j < NS; ++j) {
-        if (p0 + j < nvalid) SoIO<S>::ld_vec(stage + Y_OFF, p0 + j, yv[j]);
+        if (FULL || p0 + j < nvalid) SoIO<S>::ld_vec(stage + Y_OFF, p0 + j, yv[j]);
         else { yv[j][0] = S(0); yv[j][1] = S(0); }
       }
       if (tpos > 0) SoIO<S>::ld_vec(stage + Y_OFF, p0 - 1, yprev);
@@ -332,7 +359,7 @@ struct SoBwd : MatAffine<S> {
 #pragma unroll
     for (int j = NS - 1; j >= 0; --j) {
       S a[4], g[2];
-      sample(stage, p0 + j, nvalid, swap, arow, a, g);
+      sample<FULL>(stage, p0 + j, nvalid, swap, arow, a, g);
       const S g0 = g[0] + c0, g1 = g[1] + c1;
       if (XS) {
         *reinterpret_cast<S*>(stage + GX_OFF + (size_t)(p0 + j) * SZ) = g0;
@@ -346,7 +373,7 @@ struct SoBwd : MatAffine<S> {
         if (LPV) {
           const S ga[4] = {g0 * y0, g0 * y1, g1 * y0, g1 * y1};
           SoIO<S>::st_mat(stage + A_OFF, p0 + j, swap, ga);   // over this thread's own coefficients
-        } else if (p0 + j < nvalid) {
+        } else if (FULL || p0 + j < nvalid) {
           acc.v[0] += g0 * y0; acc.v[1] += g0 * y1; acc.v[2] += g1 * y0; acc.v[3] += g1 * y1;
         }
       }
