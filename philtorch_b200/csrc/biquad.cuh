@@ -19,18 +19,21 @@
 
 namespace ptb {
 
+// Derived constants of a row's section {b0, b1 - b0 a1, b2 - b0 a2, -a1, -a2}: computed once per tile
+// by the DMA warp (row_constants) and read from the stage by every thread.
 template <class S>
 struct BqCoef {
   S b0, B0, B1, na1, na2;
-  __device__ __forceinline__ void load(const S* b, int64_t bs, const S* a, int64_t as, int64_t row) {
+  static __device__ __forceinline__ void derive(const S* b, int64_t bs, const S* a, int64_t as, int64_t row,
+                                                S* out) {
     const S* pb = b + row * bs;
     const S* pa = a + row * as;
-    b0 = __ldg(pb);
-    const S b1 = __ldg(pb + 1), b2 = __ldg(pb + 2), a1 = __ldg(pa), a2 = __ldg(pa + 1);
-    B0 = b1 - b0 * a1;
-    B1 = b2 - b0 * a2;
-    na1 = -a1;
-    na2 = -a2;
+    const S b0 = __ldg(pb), b1 = __ldg(pb + 1), b2 = __ldg(pb + 2), a1 = __ldg(pa), a2 = __ldg(pa + 1);
+    out[0] = b0; out[1] = b1 - b0 * a1; out[2] = b2 - b0 * a2; out[3] = -a1; out[4] = -a2;
+  }
+  __device__ __forceinline__ void load(const unsigned char* rowc) {
+    const S* q = reinterpret_cast<const S*>(rowc);
+    b0 = q[0]; B0 = q[1]; B1 = q[2]; na1 = q[3]; na2 = q[4];
   }
 };
 
@@ -87,7 +90,13 @@ struct BqFwd : MatAffine<S> {
   static constexpr bool HAS_PARTIAL = false;
   static constexpr int SLOT_WORDS = Words<Map>::W;
   static constexpr int X_OFF = 0;
-  static constexpr int STAGE_BYTES = TILE * (int)sizeof(S);
+  using Scalar = S;
+  static constexpr int NROWC = 5;
+  static constexpr int ROWC_OFF = TILE * (int)sizeof(S);
+  static constexpr int STAGE_BYTES = ROWC_OFF + 128;
+  static __device__ __forceinline__ void row_constants(const Params& p, int64_t row, S* out) {
+    BqCoef<S>::derive(p.b, p.b_stride, p.a, p.a_stride, row, out);
+  }
 
   static __device__ __forceinline__ void plan(const Params& p, bool, int64_t row, int64_t t0, int nvalid,
                                               IoPlan& io) {
@@ -115,7 +124,7 @@ struct BqFwd : MatAffine<S> {
   static __device__ __forceinline__ Map aggregate(const Params& p, const unsigned char* stage, int tpos,
                                                   int64_t row, int64_t, int nvalid) {
     BqCoef<S> k;
-    k.load(p.b, p.b_stride, p.a, p.a_stride, row);
+    k.load(stage + ROWC_OFF);
     S x[SPT];
     const int nv = load_x(stage, tpos, nvalid, x);
     Map m = Alg::identity();
@@ -165,7 +174,7 @@ struct BqFwd : MatAffine<S> {
   static __device__ __forceinline__ Partial finish(const Params& p, const State& in, unsigned char* stage,
                                                    int tpos, int64_t row, int64_t, int nvalid) {
     BqCoef<S> k;
-    k.load(p.b, p.b_stride, p.a, p.a_stride, row);
+    k.load(stage + ROWC_OFF);
     S x[SPT];
     const int nv = load_x(stage, tpos, nvalid, x);
     if (nv == SPT) replay<true>(k, in.v[0], in.v[1], nv, x);
@@ -212,7 +221,13 @@ struct BqBwd : MatAffine<S> {
   static constexpr int G_OFF = 0;          // gy in, grad_x out
   static constexpr int X_OFF = SLOT;       // x in
   static constexpr int Y_OFF = 2 * SLOT;   // y in
-  static constexpr int STAGE_BYTES = 3 * SLOT;
+  using Scalar = S;
+  static constexpr int NROWC = 5;
+  static constexpr int ROWC_OFF = 3 * SLOT;
+  static constexpr int STAGE_BYTES = ROWC_OFF + 128;
+  static __device__ __forceinline__ void row_constants(const Params& p, int64_t row, S* out) {
+    BqCoef<S>::derive(p.b, p.b_stride, p.a, p.a_stride, row, out);
+  }
 
   static __device__ __forceinline__ void plan(const Params& p, bool, int64_t row, int64_t t0, int nvalid,
                                               IoPlan& io) {
@@ -245,7 +260,7 @@ struct BqBwd : MatAffine<S> {
   static __device__ __forceinline__ Map aggregate(const Params& p, const unsigned char* stage, int tpos,
                                                   int64_t row, int64_t, int nvalid) {
     BqCoef<S> k;
-    k.load(p.b, p.b_stride, p.a, p.a_stride, row);
+    k.load(stage + ROWC_OFF);
     S g[SPT];
     const int nv = load_slot(stage, G_OFF, tpos, nvalid, g);
     Map m = Alg::identity();
@@ -305,7 +320,7 @@ struct BqBwd : MatAffine<S> {
   static __device__ __forceinline__ Partial finish(const Params& p, const State& in, unsigned char* stage,
                                                    int tpos, int64_t row, int64_t, int nvalid) {
     BqCoef<S> k;
-    k.load(p.b, p.b_stride, p.a, p.a_stride, row);
+    k.load(stage + ROWC_OFF);
     S g[SPT], x[SPT], y[SPT];
     const int nv = load_slot(stage, G_OFF, tpos, nvalid, g);
     Partial acc;

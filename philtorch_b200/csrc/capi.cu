@@ -364,9 +364,9 @@ static int so_bwd(int64_t B, int64_t T, const void* A, int A_batched, const void
 
 // ---------------------------------------------------------------------------- TDF-II section
 #ifndef PTB_BQ_FWD_CH
-#define PTB_BQ_FWD_CH 15
-#define PTB_BQ_FWD_STAGES 3
-#define PTB_BQ_FWD_CTAS 1
+#define PTB_BQ_FWD_CH 13
+#define PTB_BQ_FWD_STAGES 2
+#define PTB_BQ_FWD_CTAS 2
 #endif
 #ifndef PTB_BQ_BWD_CH
 #define PTB_BQ_BWD_CH 7

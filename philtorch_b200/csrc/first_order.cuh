@@ -93,7 +93,12 @@ struct FoFwd : ScalarAffine<S> {
   static constexpr int SLOT = TILE * (int)sizeof(S);
   static constexpr int X_OFF = 0;
   static constexpr int A_OFF = SLOT;
-  static constexpr int STAGE_BYTES = LPV ? 2 * SLOT : SLOT;
+  static constexpr int NROWC = LPV ? 0 : 1;                 // time-invariant: the row's coefficient
+  static constexpr int ROWC_OFF = LPV ? 2 * SLOT : SLOT;
+  static constexpr int STAGE_BYTES = ROWC_OFF + (LPV ? 0 : 128);
+  static __device__ __forceinline__ void row_constants(const Params& p, int64_t row, S* out) {
+    out[0] = __ldg(p.a + row * p.a_row_stride);
+  }
 
   static __device__ __forceinline__ void plan(const Params& p, bool, int64_t row, int64_t t0, int nvalid,
                                               IoPlan& io) {
@@ -128,7 +133,7 @@ struct FoFwd : ScalarAffine<S> {
 #pragma unroll
         for (int c = 0; c < CH; ++c) VecIO<S, V>::ld(pa + 16 * c, &a[c * V]);
       } else {
-        a[0] = __ldg(p.a + row * p.a_row_stride);
+        a[0] = *reinterpret_cast<const S*>(stage + ROWC_OFF);
       }
       if (nv < SPT) {
 #pragma unroll
@@ -199,7 +204,12 @@ struct FoBwd : ScalarAffine<S> {
   static constexpr int Y_OFF = SLOT;                    // y in (read-only)
   static constexpr int HALO_OFF = 2 * SLOT;             // 16 bytes ending with y[t0-1]
   static constexpr int A_OFF = 2 * SLOT + 128;          // a in, grad_a out (LPV)
+  static constexpr int NROWC = LPV ? 0 : 1;
+  static constexpr int ROWC_OFF = HALO_OFF + 64;         // second half of the halo line
   static constexpr int STAGE_BYTES = (LPV ? 3 * SLOT : 2 * SLOT) + 128;
+  static __device__ __forceinline__ void row_constants(const Params& p, int64_t row, S* out) {
+    out[0] = __ldg(p.a + row * p.a_row_stride);
+  }
 
   static __device__ __forceinline__ void plan(const Params& p, bool bulk, int64_t row, int64_t t0, int nvalid,
                                               IoPlan& io) {
@@ -242,7 +252,7 @@ struct FoBwd : ScalarAffine<S> {
 #pragma unroll
         for (int c = 0; c < CH; ++c) VecIO<S, V>::ld(pa + 16 * c, &a[c * V]);
       } else {
-        a[0] = __ldg(p.a + row * p.a_row_stride);
+        a[0] = *reinterpret_cast<const S*>(stage + ROWC_OFF);
       }
       if (nv < SPT) {
 #pragma unroll
@@ -348,6 +358,10 @@ struct FoCarry {
   static constexpr int X_OFF = 0;
   static constexpr int A_OFF = SLOT;
   static constexpr int STAGE_BYTES = 2 * SLOT;
+  using Scalar = S;
+  static constexpr int NROWC = 0;
+  static constexpr int ROWC_OFF = 0;
+  static __device__ __forceinline__ void row_constants(const Params&, int64_t, S*) {}
 
   static __device__ __forceinline__ Map identity() { Map m; m.v[0] = S(1); m.v[1] = S(0); m.v[2] = S(0); return m; }
   static __device__ __forceinline__ State zero_state() { State s; s.v[0] = S(1); s.v[1] = S(0); return s; }

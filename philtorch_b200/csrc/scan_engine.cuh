@@ -255,7 +255,9 @@ __device__ __forceinline__ typename P::State lookback(const Workspace& ws, uint3
 // Policy requirements (see first_order.cuh for a worked example):
 //   types   S, Map{S v[N]}, State{S v[N]}, Partial{S v[N]}, Params
 //   consts  NT (compute threads, multiple of 32), SPT, TILE = NT*SPT, STAGES, STAGE_BYTES,
-//           MIN_CTAS, REVERSE (process time descending), HAS_PARTIAL, SLOT_WORDS
+//           MIN_CTAS, REVERSE (process time descending), HAS_PARTIAL, SLOT_WORDS,
+//           NROWC / ROWC_OFF / row_constants(prm, row, Scalar*): per-row constants the DMA warp
+//           places at ROWC_OFF of the stage (0 = none)
 //   static  identity(), zero_state(), const_map(State), compose(first, second), apply(Map, State),
 //           plan(prm, bulk, row, t0, nvalid, IoPlan&), row_init(prm, row), row_final(prm, row, State),
 //           aggregate(prm, stage, tpos, row, t0, nvalid) -> Map          (phase 1, reads the stage)
@@ -367,6 +369,11 @@ scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, 
     uint32_t failed = 0;
     uint32_t next = atomicAdd(ws.ticket, 1u);
     uint32_t n = 0;
+    // per-row constants (time-invariant coefficients) of the NEXT tile, fetched one iteration ahead
+    // so that their latency hides behind the drain of an older tile; they travel with the stage
+    constexpr int NR = P::NROWC;
+    typename P::Scalar rc[NR > 0 ? NR : 1];
+    if (NR > 0 && next < ntiles) P::row_constants(prm, (int64_t)(next % B), rc);
     PTB_PROF_DECL(t_wait_done); PTB_PROF_DECL(t_wait_read); PTB_PROF_DECL(t_dma_total);
     PTB_PROF_BEGIN(tdma0);
     auto drain = [&](uint32_t j) {   // results of the j-th tile of this CTA are in its stage
@@ -402,6 +409,12 @@ scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, 
       if (ticket >= ntiles) break;
       next = atomicAdd(ws.ticket, 1u);
       tile_ticket[s] = ticket;
+      if (NR > 0) {
+        typename P::Scalar* dst = reinterpret_cast<typename P::Scalar*>(smem + s * P::STAGE_BYTES + P::ROWC_OFF);
+#pragma unroll
+        for (int i = 0; i < NR; ++i) dst[i] = rc[i];
+        if (next < ntiles) P::row_constants(prm, (int64_t)(next % B), rc);
+      }
       PTB_EV(1, n);
       mbar_arrive(&issued[s]);   // the look-back of this tile may start: it needs nothing from the tile
       if (bulk) {
@@ -537,7 +550,9 @@ scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, 
       cta_sync(0, sync_par0);
     }
     const Map mine = P::aggregate(prm, stage, tpos, c.row, c.t0, c.nvalid);
+    if (tid == 0) PTB_EV(10, p1);
     const Map inc = warp_scan_inclusive<P>(mine, lane);
+    if (tid == 0) PTB_EV(11, p1);
     uint32_t order = 0;
     if (lane == 31) {
       wtot[s * NW + warp] = inc;

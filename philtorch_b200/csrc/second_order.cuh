@@ -122,7 +122,14 @@ struct SoFwd : MatAffine<S> {
   static constexpr int Y_OFF = 0;                                       // y out (x in when !XS)
   static constexpr int XS_OFF = align128(TILE * 2 * SZ);                // scalar x in (XS only)
   static constexpr int A_OFF = XS_OFF + (XS ? align128(TILE * SZ) : 0); // A in (LPV only)
-  static constexpr int STAGE_BYTES = A_OFF + (LPV ? align128(TILE * 4 * SZ) : 0);
+  using Scalar = S;
+  static constexpr int NROWC = LPV ? 0 : 4;                             // time-invariant: the row's matrix
+  static constexpr int ROWC_OFF = A_OFF;
+  static constexpr int STAGE_BYTES = A_OFF + (LPV ? align128(TILE * 4 * SZ) : 128);
+  static __device__ __forceinline__ void row_constants(const Params& p, int64_t row, S* out) {
+    const S* q = p.A + row * p.a_row_stride;
+    out[0] = __ldg(q); out[1] = __ldg(q + 1); out[2] = __ldg(q + 2); out[3] = __ldg(q + 3);
+  }
 
   static __device__ __forceinline__ void plan(const Params& p, bool, int64_t row, int64_t t0, int nvalid,
                                               IoPlan& io) {
@@ -152,10 +159,10 @@ struct SoFwd : MatAffine<S> {
       a[0] = S(1); a[1] = S(0); a[2] = S(0); a[3] = S(1); x[0] = S(0); x[1] = S(0);
     }
   }
-  static __device__ __forceinline__ void row_matrix(const Params& p, int64_t row, S* arow) {
+  static __device__ __forceinline__ void row_matrix(const unsigned char* stage, S* arow) {
     if (!LPV) {
-      const S* q = p.A + row * p.a_row_stride;
-      arow[0] = __ldg(q); arow[1] = __ldg(q + 1); arow[2] = __ldg(q + 2); arow[3] = __ldg(q + 3);
+      const S* q = reinterpret_cast<const S*>(stage + ROWC_OFF);
+      arow[0] = q[0]; arow[1] = q[1]; arow[2] = q[2]; arow[3] = q[3];
     }
   }
 
@@ -173,7 +180,7 @@ struct SoFwd : MatAffine<S> {
   static __device__ __forceinline__ Map aggregate_t(const Params& p, const unsigned char* stage, int tpos,
                                                     int64_t row, int nvalid) {
     S arow[4];
-    row_matrix(p, row, arow);
+    row_matrix(stage, arow);
     const int swap = (tpos >> 2) & 1;
     Map m = Alg::identity();
 #pragma unroll
@@ -195,7 +202,7 @@ struct SoFwd : MatAffine<S> {
   static __device__ __forceinline__ Partial finish_t(const Params& p, const State& in, unsigned char* stage,
                                                      int tpos, int64_t row, int nvalid) {
     S arow[4];
-    row_matrix(p, row, arow);
+    row_matrix(stage, arow);
     const int swap = (tpos >> 2) & 1;
     S h0 = in.v[0], h1 = in.v[1];
     S out[NS][2];
@@ -252,7 +259,14 @@ struct SoBwd : MatAffine<S> {
   static constexpr int HALO_OFF = Y_OFF + align128(TILE * 2 * SZ);           // 16 bytes ending with y[t0-1]
   static constexpr int GX_OFF = HALO_OFF + 128;                              // scalar grad_x out (XS only)
   static constexpr int A_OFF = GX_OFF + (XS ? align128(TILE * SZ) : 0);      // A in, grad_A out (LPV only)
-  static constexpr int STAGE_BYTES = A_OFF + (LPV ? align128(TILE * 4 * SZ) : 0);
+  using Scalar = S;
+  static constexpr int NROWC = LPV ? 0 : 4;
+  static constexpr int ROWC_OFF = A_OFF;
+  static constexpr int STAGE_BYTES = A_OFF + (LPV ? align128(TILE * 4 * SZ) : 128);
+  static __device__ __forceinline__ void row_constants(const Params& p, int64_t row, S* out) {
+    const S* q = p.A + row * p.a_row_stride;
+    out[0] = __ldg(q); out[1] = __ldg(q + 1); out[2] = __ldg(q + 2); out[3] = __ldg(q + 3);
+  }
 
   static __device__ __forceinline__ void plan(const Params& p, bool bulk, int64_t row, int64_t t0, int nvalid,
                                               IoPlan& io) {
@@ -277,10 +291,10 @@ struct SoBwd : MatAffine<S> {
   static __device__ __forceinline__ void row_final(const Params& p, int64_t row, const State& s) {
     if (p.grad_zi) { p.grad_zi[row * 2] = s.v[0]; p.grad_zi[row * 2 + 1] = s.v[1]; }
   }
-  static __device__ __forceinline__ void row_matrix(const Params& p, int64_t row, S* arow) {
+  static __device__ __forceinline__ void row_matrix(const unsigned char* stage, S* arow) {
     if (!LPV) {
-      const S* q = p.A + row * p.a_row_stride;
-      arow[0] = __ldg(q); arow[1] = __ldg(q + 1); arow[2] = __ldg(q + 2); arow[3] = __ldg(q + 3);
+      const S* q = reinterpret_cast<const S*>(stage + ROWC_OFF);
+      arow[0] = q[0]; arow[1] = q[1]; arow[2] = q[2]; arow[3] = q[3];
     }
   }
   template <bool FULL>
@@ -310,7 +324,7 @@ struct SoBwd : MatAffine<S> {
   static __device__ __forceinline__ Map aggregate_t(const Params& p, const unsigned char* stage, int tpos,
                                                     int64_t row, int nvalid) {
     S arow[4];
-    row_matrix(p, row, arow);
+    row_matrix(stage, arow);
     const int swap = (tpos >> 2) & 1;
     Map m = Alg::identity();
 #pragma unroll
@@ -333,7 +347,7 @@ struct SoBwd : MatAffine<S> {
   static __device__ __forceinline__ Partial finish_t(const Params& p, const State& in, unsigned char* stage,
                                                      int tpos, int64_t row, int64_t t0, int nvalid) {
     S arow[4];
-    row_matrix(p, row, arow);
+    row_matrix(stage, arow);
     const int swap = (tpos >> 2) & 1;
     const int p0 = tpos * NS;
     S yv[NS][2];
