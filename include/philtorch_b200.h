@@ -51,6 +51,21 @@ int64_t ptb_workspace_bytes(int64_t B, int64_t T);
 /* Copies *status to the host after synchronising `stream` (the only blocking call). */
 int ptb_read_status(const uint32_t* status, ptb_stream_t stream, uint32_t* host_out);
 
+/* ---- failure detection ----------------------------------------------------------------------
+ * Every device-side wait of the kernels (look-back records of other CTAs, shared-memory barriers)
+ * is bounded in time; when a bound expires the kernel sets a bit in `status`, finishes its copies
+ * and runs to completion, so the context stays usable.  The bound is 2000 ms by default. */
+int ptb_set_wait_limit_ms(int64_t ms);
+/* Self-test of that path without faulting anything: runs the first-order forward kernel on two
+ * tiles of which the FIRST IS NEVER PROCESSED, so the second one's look-back waits for a record
+ * that nothing writes, gives up after the wait limit and reports kErrLookbackTimeout (bit 0) in
+ * `status`.  buf: device scratch of at least ptb_selftest_wait_expiry_elems() floats (contents
+ * irrelevant, 16-byte aligned); workspace as for the other entry points with B = 1,
+ * T = that many samples. */
+int64_t ptb_selftest_wait_expiry_elems(void);
+int ptb_selftest_wait_expiry(void* workspace, int64_t workspace_bytes, void* buf, int64_t buf_elems,
+                             uint32_t* status, ptb_stream_t stream);
+
 /* ---- first-order, time-invariant ------------------------------------------------------------
  * Replaces op philtorch::lti_recur(a, zi, x) -> y
  *   (philtorch/csrc/host_recur2.cpp:170, CPU kernel philtorch/csrc/host_lti_recur.cpp:42-80,

@@ -14,6 +14,7 @@ constexpr int kHeaderBytes = 256;
 constexpr int kMaxDevices = 64;
 
 static thread_local int g_last_cuda_error = 0;
+static uint64_t g_wait_ns = kDefaultWaitNs;   // bound of every device-side wait (ptb_set_wait_limit_ms)
 
 #define PTB_CUDA(expr)                                   \
   do {                                                   \
@@ -48,7 +49,7 @@ struct KernelCache {
 template <class P>
 static int launch_scan(const typename P::Params& prm, int64_t B, int64_t T, bool bulk, void* workspace,
                        int64_t workspace_bytes, uint32_t* status, cudaStream_t st, void** partial_out,
-                       int64_t* nchunks_out) {
+                       int64_t* nchunks_out, bool skip_first_chunk = false) {
   static_assert(P::TILE >= kMinTile, "workspace bound assumes TILE >= kMinTile");
   static_assert(P::SLOT_WORDS * 8 + sizeof(typename P::Partial) <= kTileRecordBytes,
                 "per-tile record too large");
@@ -62,6 +63,9 @@ static int launch_scan(const typename P::Params& prm, int64_t B, int64_t T, bool
     return PTB_ERR_WORKSPACE;
   char* w = static_cast<char*>(workspace);
   PTB_CUDA(cudaMemsetAsync(w, 0, (size_t)l.part_off, st));   // header + look-back records
+  // self-test only: start the ticket counter at 1, so the first tile is never processed and its
+  // successor's look-back waits for a record that nothing writes
+  if (skip_first_chunk) PTB_CUDA(cudaMemsetAsync(w, 1, 1, st));
   Workspace ws;
   ws.ticket = reinterpret_cast<uint32_t*>(w);
   ws.error = status ? status : reinterpret_cast<uint32_t*>(w + 4);
@@ -87,8 +91,11 @@ static int launch_scan(const typename P::Params& prm, int64_t B, int64_t T, bool
   }
   const int64_t resident = (int64_t)cache.sms[dev] * cache.ctas_per_sm[dev];
   const unsigned grid = (unsigned)std::min<int64_t>(ntiles, resident);
+  // tiles of one row that are in flight together: the depth the look-back usually has to cover
+  const int64_t depth = resident * P::STAGES / B;
+  const int lb_first = depth > 6 ? 32 : 8;
   scan_kernel<P><<<grid, P::NT + 32 * (P::LBW + 1), smem, st>>>(prm, ws, (uint32_t)B, T, (uint32_t)nchunks, (uint32_t)ntiles,
-                                                bulk ? 1 : 0);
+                                                bulk ? 1 : 0, lb_first, g_wait_ns);
   PTB_CUDA(cudaGetLastError());
   return PTB_OK;
 }
@@ -553,6 +560,31 @@ int ptb_lpv_recur_fwd_carry(int dtype, int64_t B, int64_t T, const void* a, int 
   if (T == 0 || !a || !x || !y || !carry) return PTB_ERR_ARG;
   PTB_DISPATCH(dtype, (fo_carry<S, false, true>(B, T, a, a_batched, x, y, carry, workspace, workspace_bytes,
                                                  status, (cudaStream_t)stream)));
+}
+
+int ptb_set_wait_limit_ms(int64_t ms) {
+  if (ms < 1 || ms > 600000) return PTB_ERR_ARG;
+  g_wait_ns = (uint64_t)ms * 1000000ull;
+  return PTB_OK;
+}
+
+int64_t ptb_selftest_wait_expiry_elems(void) { return 3 * 2 * (int64_t)FoFwdP<float, true>::TILE + 16; }
+
+int ptb_selftest_wait_expiry(void* workspace, int64_t workspace_bytes, void* buf, int64_t buf_elems,
+                             uint32_t* status, ptb_stream_t stream) {
+  using P = FoFwdP<float, true>;
+  const int64_t T = 2 * (int64_t)P::TILE;
+  if (!workspace || !buf || !status || buf_elems < 3 * T + 16) return PTB_ERR_ARG;
+  float* f = static_cast<float*>(buf);
+  typename P::Params p;
+  p.a = f; p.a_row_stride = T;
+  p.x = f + T;
+  p.y = f + 2 * T;
+  p.zi = f + 3 * T; p.zi_stride = 1;
+  p.zf = nullptr;
+  p.T = T;
+  return launch_scan<P>(p, 1, T, true, workspace, workspace_bytes, status, (cudaStream_t)stream, nullptr, nullptr,
+                        /*skip_first_chunk=*/true);
 }
 
 int64_t ptb_lpv_recur_fwd_static_max_tiles(int dtype) {

@@ -52,7 +52,7 @@ constexpr uint32_t kErrLookbackTimeout = 1u;
 constexpr uint32_t kErrLoadTimeout = 2u;
 constexpr uint32_t kErrDrainTimeout = 4u;
 constexpr uint32_t kErrPipeTimeout = 8u;
-constexpr uint64_t kWaitNs = 2000000000ull;        // any single device-side wait gives up after 2 s
+constexpr uint64_t kDefaultWaitNs = 2000000000ull;  // any single device-side wait gives up after 2 s (default)
 constexpr uint64_t kWaitNsAfterError = 1000000ull;   // ... or after 1 ms once this CTA has seen an error
 
 // Optional role-level timing (compile with -DPTB_PROFILE): cycles each role spends waiting,
@@ -183,18 +183,19 @@ __device__ __forceinline__ typename P::Map warp_scan_inclusive(typename P::Map m
 // Look-back executed by all 32 lanes of a look-back warp; returns (in every lane) the state
 // entering the tile.  Windows of predecessors (one per lane, all loads in flight together) are
 // folded until one contains an end state.  The look-back starts as soon as the tile's ticket is
-// known, usually before the predecessors have published anything, so the first window is only 8
-// lanes wide and polls with a back-off: that keeps the polling traffic in L2 small.  Later
-// windows are 32 wide.
+// known, usually before the predecessors have published anything, so the first window is only
+// `first_window` lanes wide (8 when the batch is large enough that a row has few tiles in flight,
+// 32 for a handful of long rows) and polls with a back-off: that keeps the polling traffic in L2
+// small.  Later windows are 32 wide.
 template <class P>
 __device__ __forceinline__ typename P::State lookback(const Workspace& ws, uint32_t ticket,
                                                       uint32_t chunk, uint32_t B, int lane,
-                                                      uint32_t& failed) {
+                                                      uint32_t& failed, int first_window, uint64_t kWaitNs) {
   using Map = typename P::Map;
   using State = typename P::State;
   Map acc = P::identity();
   uint32_t base = 1;
-  int wsize = 8;
+  int wsize = first_window;
   State result;
   while (true) {
     const uint32_t k = base + lane;
@@ -311,7 +312,7 @@ __device__ __forceinline__ TileCoords tile_coords(uint32_t ticket, uint32_t B, u
 template <class P>
 __global__ void __launch_bounds__(P::NT + 32 * (P::LBW + 1), P::MIN_CTAS)
 scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, const int64_t T,
-            const uint32_t nchunks, const uint32_t ntiles, const int bulk) {
+            const uint32_t nchunks, const uint32_t ntiles, const int bulk, const int lb_first, const uint64_t kWaitNs) {
   using Map = typename P::Map;
   using State = typename P::State;
   using Partial = typename P::Partial;
@@ -480,7 +481,7 @@ scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, 
       if (lane == 0) PTB_EV(4, n);
       State hin;
       if (c.chunk == 0) hin = P::row_init(prm, c.row);   // its end state is published in phase 1
-      else hin = lookback<P>(ws, ticket, c.chunk, B, lane, failed);
+      else hin = lookback<P>(ws, ticket, c.chunk, B, lane, failed, lb_first, kWaitNs);
       if (lane == 0) {
         sm_hin[s] = hin;
         mbar_arrive(&lb_done[s]);
