@@ -202,6 +202,29 @@ int ptb_biquad_tdf2_bwd(int dtype, int64_t B, int64_t T, const void* b, const vo
                         void* grad_b, void* grad_a, void* grad_zi, void* workspace, int64_t workspace_bytes,
                         uint32_t* status, ptb_stream_t stream);
 
+/* ---- cascade of K second-order sections, fused -------------------------------------------------
+ * All K sections of a cascade in ONE pass over the signal per direction.  The reference runs a
+ * cascade as K chained lfilter(b_k, a_k, ., form="tdf2") calls (philtorch/lti/filtering.py:304-317,
+ * philtorch/lti/ssm.py:466-504); results equal that chain's up to floating-point re-association.
+ *   K            number of sections: 2, 4, 6 or 8 (callers pad an odd cascade with the identity
+ *                section b = {1,0,0}, a = {0,0} and split longer ones)
+ *   b, a         (K,B,3), (K,B,2) when coef_batched, else (K,3), (K,2); a0 = 1 implicit
+ *   zi / zf      optional (K,B,2) states of every section before the first / after the last sample
+ *   x, y         (B,T)
+ *   mid          optional (K-1,B,T): outputs of sections 0..K-2, needed by the backward pass for
+ *                coefficient gradients
+ * Backward: gy (B,T), g_zf optional (K,B,2) -> grad_x (B,T), grad_b / grad_a shaped like b / a
+ * (optional, both or none; need x, mid, y), grad_zi optional (K,B,2).
+ * Workspace: ptb_sos_cascade_workspace_bytes (holds the per-row table of matrix powers too). */
+int64_t ptb_sos_cascade_workspace_bytes(int dtype, int K, int64_t B, int64_t T);
+int ptb_sos_cascade_fwd(int dtype, int K, int64_t B, int64_t T, const void* b, const void* a, int coef_batched,
+                        const void* zi, const void* x, void* y, void* mid, void* zf, void* workspace,
+                        int64_t workspace_bytes, uint32_t* status, ptb_stream_t stream);
+int ptb_sos_cascade_bwd(int dtype, int K, int64_t B, int64_t T, const void* b, const void* a, int coef_batched,
+                        const void* x, const void* mid, const void* y, const void* gy, const void* g_zf,
+                        void* grad_x, void* grad_b, void* grad_a, void* grad_zi, void* workspace,
+                        int64_t workspace_bytes, uint32_t* status, ptb_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

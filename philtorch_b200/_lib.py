@@ -68,6 +68,13 @@ lib.ptb_selftest_wait_expiry_elems.restype = _i64
 lib.ptb_selftest_wait_expiry.argtypes = [_vp, _i64, _vp, _i64, _vp, _vp]
 lib.ptb_selftest_wait_expiry.restype = _i32
 
+lib.ptb_sos_cascade_workspace_bytes.argtypes = [_i32, _i32, _i64, _i64]
+lib.ptb_sos_cascade_workspace_bytes.restype = _i64
+lib.ptb_sos_cascade_fwd.argtypes = [_i32, _i32, _i64, _i64, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp] + _tail
+lib.ptb_sos_cascade_fwd.restype = _i32
+lib.ptb_sos_cascade_bwd.argtypes = [_i32, _i32, _i64, _i64, _vp, _vp, _i32] + [_vp] * 9 + _tail
+lib.ptb_sos_cascade_bwd.restype = _i32
+
 _status: dict[int, torch.Tensor] = {}
 
 ERROR_BITS = {1: "look-back wait expired", 2: "tile load wait expired", 4: "tile drain wait expired",
@@ -121,9 +128,9 @@ def check(rc: int, what: str) -> None:
         raise RuntimeError(f"{what}: {msg}")
 
 
-def call(fn, device: torch.device, B: int, T: int, *args) -> None:
+def call(fn, device: torch.device, B: int, T: int, *args, ws_bytes: int = -1) -> None:
     """Runs ``fn(*args, workspace, bytes, status, stream)`` on ``device``'s current stream."""
-    ws = workspace(B, T, device)
+    ws = workspace(B, T, device) if ws_bytes < 0 else torch.empty(ws_bytes, dtype=torch.uint8, device=device)
     st = status_word(device)
     if device.index is not None and device.index != torch.cuda.current_device():
         with torch.cuda.device(device):

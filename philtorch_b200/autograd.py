@@ -293,6 +293,46 @@ class BiquadTDF2(Function):
                 _none_if_empty(gx, need_x))
 
 
+class SOSCascade(Function):
+    """K second-order sections (TDF-II) in one fused pass, (b, a, zi, x) -> (y, zf) with b (K,3) or
+    (K,B,3), a (K,2) or (K,B,2), zi/zf (K,B,2).  Same results as K chained ``BiquadTDF2`` calls
+    (the reference chains ``lfilter`` calls, philtorch/lti/filtering.py:304-317)."""
+
+    @staticmethod
+    def forward(ctx: Any, b: Tensor, a: Tensor, zi: Optional[Tensor], x: Tensor):
+        need_coef = ctx.needs_input_grad[0] or ctx.needs_input_grad[1]
+        y, mid, zf = _ops.sos_cascade(b, a, zi, x, need_coef)
+        ctx.has_zi = zi is not None
+        ctx.save_for_backward(b, a, x, mid, y, *([zi] if zi is not None else []))
+        return y, zf
+
+    @staticmethod
+    def backward(ctx: Any, grad_y: Tensor, grad_zf: Tensor):
+        b, a, x, mid, y, *rest = ctx.saved_tensors
+        need_b, need_a, need_zi, need_x = ctx.needs_input_grad
+        need_zi = need_zi and ctx.has_zi
+        if torch.is_grad_enabled():
+            # higher-order graph: recompute as a chain of differentiable single sections
+            zi = rest[0] if rest else None
+            with torch.enable_grad():
+                u, zfs = x, []
+                for k in range(b.shape[0]):
+                    u, zf_k = BiquadTDF2.apply(b[k], a[k], None if zi is None else zi[k], u)
+                    zfs.append(zf_k)
+                ins = [t for t, n in ((b, need_b), (a, need_a), (zi, need_zi), (x, need_x)) if n]
+                gs = list(torch.autograd.grad([u, torch.stack(zfs)], ins, [grad_y, grad_zf], create_graph=True,
+                                              allow_unused=True))
+            out = []
+            for n in (need_b, need_a, need_zi, need_x):
+                out.append(gs.pop(0) if n else None)
+            return tuple(out)
+        if grad_y is None:
+            grad_y = torch.zeros_like(x)
+        gb, ga, gzi, gx = _ops.sos_cascade_bwd(b, a, x, mid, y, grad_y, grad_zf, need_b or need_a, need_zi)
+        return (_none_if_empty(gb, need_b), _none_if_empty(ga, need_a), _none_if_empty(gzi, need_zi),
+                _none_if_empty(gx, need_x))
+
+
 def _biquad_reference_form(b: Tensor, a: Tensor, zi: Optional[Tensor], x: Tensor):
     """The same section written with differentiable pieces (2x2 recurrence + elementwise glue),
     following philtorch/lti/filtering.py:304-317 and philtorch/lti/ssm.py:466-504."""

@@ -18,7 +18,7 @@ ROOT_INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-    "-shared", "-Xcompiler", "-fPIC", "-cudart", "shared",
+    "-shared", "-Xcompiler", "-fPIC", "-cudart", "shared", "--threads", "0",
 ]
 
 

@@ -133,9 +133,9 @@ struct BqFwd : MatAffine<S> {
       S s0 = S(0), s1 = S(0);
 #pragma unroll
       for (int j = 0; j < SPT; ++j) {
-        const S n0 = k.na1 * s0 + s1 + k.B0 * x[j];
+        const S t = s1 + k.B0 * x[j];   // off the chain through s0
         s1 = k.na2 * s0 + k.B1 * x[j];
-        s0 = n0;
+        s0 = k.na1 * s0 + t;
       }
       const S M[4] = {k.na1, S(1), k.na2, S(0)};
       mat2_power<S, SPT>(M, m.v);
@@ -165,9 +165,9 @@ struct BqFwd : MatAffine<S> {
       if (FULL || j < nv) {
         const S xj = x[j];
         x[j] = h0 + k.b0 * xj;
-        const S n0 = k.na1 * h0 + h1 + k.B0 * xj;
+        const S t = h1 + k.B0 * xj;   // off the chain through h0
         h1 = k.na2 * h0 + k.B1 * xj;
-        h0 = n0;
+        h0 = k.na1 * h0 + t;
       }
     }
   }
@@ -268,9 +268,9 @@ struct BqBwd : MatAffine<S> {
       S s0 = S(0), s1 = S(0);
 #pragma unroll
       for (int j = SPT - 1; j >= 0; --j) {
-        const S n0 = k.na1 * s0 + k.na2 * s1 + g[j];
+        const S t = k.na2 * s1 + g[j];   // off the chain through s0
         s1 = s0;
-        s0 = n0;
+        s0 = k.na1 * s0 + t;
       }
       const S Mt[4] = {k.na1, k.na2, S(1), S(0)};
       mat2_power<S, SPT>(Mt, m.v);
@@ -310,9 +310,9 @@ struct BqBwd : MatAffine<S> {
           acc.v[3] += y[j] * l0;
           acc.v[4] += y[j] * l1;
         }
-        const S n0 = k.na1 * l0 + k.na2 * l1 + gj;
+        const S t = k.na2 * l1 + gj;   // off the chain through l0
         l1 = l0;
-        l0 = n0;
+        l0 = k.na1 * l0 + t;
       }
     }
     return acc;

@@ -1,0 +1,224 @@
+// C ABI of the fused second-order-section cascade (see include/philtorch_b200.h).
+#include "launch.cuh"
+
+#include "sos_cascade.cuh"
+
+namespace ptb {
+
+// (16-byte units per thread and array, stages)
+#ifndef PTB_SOS_FWD_CH
+#define PTB_SOS_FWD_CH 9
+#define PTB_SOS_FWD_STAGES 3
+#define PTB_SOS_FWD_NT 256
+#define PTB_SOS_FWD_CTAS 1
+#endif
+#ifndef PTB_SOS_BWD_CH
+#define PTB_SOS_BWD_CH 9
+#define PTB_SOS_BWD_STAGES 2
+#define PTB_SOS_BWD_NT 256
+#define PTB_SOS_BWD_CTAS 1
+#endif
+template <class S, int K> using SosFwdP = SosFwd<S, K, PTB_SOS_FWD_CH, PTB_SOS_FWD_STAGES, PTB_SOS_FWD_NT, PTB_SOS_FWD_CTAS>;
+template <class S, int K> using SosBwdP = SosBwd<S, K, PTB_SOS_BWD_CH, PTB_SOS_BWD_STAGES, PTB_SOS_BWD_NT, PTB_SOS_BWD_CTAS>;
+
+template <class S, int K>
+static int64_t table_bytes(int64_t rows) { return align_up(rows * SosDims<K>::ROWTAB * (int64_t)sizeof(S), 256); }
+
+template <class P>
+static int64_t scan_ws_bytes(int64_t B, int64_t T) {
+  const int64_t ntiles = B * ((T + P::TILE - 1) / P::TILE);
+  return ws_layout(ntiles, P::SLOT_WORDS, sizeof(typename P::Partial)).total;
+}
+
+template <class S, int K>
+static int64_t sos_ws_bytes(int64_t B, int64_t T) {
+  return std::max(table_bytes<S, K>(B) + std::max(scan_ws_bytes<SosFwdP<S, K>>(B, T), scan_ws_bytes<SosBwdP<S, K>>(B, T)),
+                  ptb_workspace_bytes(B, T));
+}
+
+template <class S, int K, bool ADJ>
+static int build_table(const void* b, const void* a, int coef_batched, int64_t B, void* tab, int spt,
+                       cudaStream_t st) {
+  const int64_t rows = coef_batched ? B : 1;
+  const int threads = std::max(32, SosDims<K>::NS * SosDims<K>::NS);
+  sos_setup_kernel<S, K, ADJ><<<(unsigned)rows, threads, 0, st>>>(
+      static_cast<const S*>(b), rows * 3, coef_batched ? 3 : 0, static_cast<const S*>(a), rows * 2,
+      coef_batched ? 2 : 0, static_cast<S*>(tab), spt);
+  PTB_CUDA(cudaGetLastError());
+  return PTB_OK;
+}
+
+template <class S, int K>
+static int sos_fwd(int64_t B, int64_t T, const void* b, const void* a, int coef_batched, const void* zi,
+                   const void* x, void* y, void* zf, void* ws, int64_t wsb, uint32_t* status, cudaStream_t st) {
+  using P = SosFwdP<S, K>;
+  const int64_t rows = coef_batched ? B : 1;
+  const int64_t tb = table_bytes<S, K>(rows);
+  if (!ws || (reinterpret_cast<uintptr_t>(ws) & 255u) || wsb < tb) return PTB_ERR_WORKSPACE;
+  int rc = build_table<S, K, false>(b, a, coef_batched, B, ws, P::SPT, st);
+  if (rc != PTB_OK) return rc;
+  typename P::Params p;
+  p.tab = static_cast<const S*>(ws);
+  p.tab_stride = coef_batched ? SosDims<K>::ROWTAB : 0;
+  p.zi = static_cast<const S*>(zi);
+  p.x = static_cast<const S*>(x);
+  p.y = static_cast<S*>(y);
+  p.zf = static_cast<S*>(zf);
+  p.T = T;
+  p.B = B;
+  const bool bulk = aligned16(x) && aligned16(y) && (T * sizeof(S)) % 16 == 0;
+  return launch_scan<P, false>(p, B, T, bulk, static_cast<char*>(ws) + tb, wsb - tb, status, st, nullptr, nullptr);
+}
+
+// With the outputs of the inner sections wanted, the sections run one by one through the
+// single-section kernel: each of those passes moves 8 bytes per sample at close to the memory
+// bandwidth, and together they write exactly the arrays the fused backward pass reads.
+template <class S>
+static int sos_fwd_chain(int dtype, int K, int64_t B, int64_t T, const S* b, const S* a, int coef_batched,
+                         const S* zi, const S* x, S* y, S* mid, S* zf, void* ws, int64_t wsb, uint32_t* status,
+                         ptb_stream_t st) {
+  const int64_t rows = coef_batched ? B : 1;
+  for (int k = 0; k < K; ++k) {
+    const S* in = k == 0 ? x : mid + (int64_t)(k - 1) * B * T;
+    S* out = k == K - 1 ? y : mid + (int64_t)k * B * T;
+    const int rc = ptb_biquad_tdf2_fwd(dtype, B, T, b + (int64_t)k * rows * 3, a + (int64_t)k * rows * 2, coef_batched,
+                                       zi ? zi + (int64_t)k * B * 2 : nullptr, in, out,
+                                       zf ? zf + (int64_t)k * B * 2 : nullptr, ws, wsb, status, st);
+    if (rc != PTB_OK) return rc;
+  }
+  return PTB_OK;
+}
+
+template <class S, int K>
+struct SosCoefGrads {
+  const S* a; int64_t a_sec, a_row;
+  S* grad_b; S* grad_a;
+  int64_t rows;
+  __device__ void operator()(int64_t row, const double* acc) const {
+    for (int k = 0; k < K; ++k) {
+      const double a1 = (double)a[k * a_sec + row * a_row], a2 = (double)a[k * a_sec + row * a_row + 1];
+      const double* q = acc + 5 * k;
+      if (grad_b) {
+        S* gb = grad_b + (k * rows + row) * 3;
+        gb[0] = (S)(q[0] - a1 * q[1] - a2 * q[2]);
+        gb[1] = (S)q[1];
+        gb[2] = (S)q[2];
+      }
+      if (grad_a) {
+        S* ga = grad_a + (k * rows + row) * 2;
+        ga[0] = (S)(-q[3]);
+        ga[1] = (S)(-q[4]);
+      }
+    }
+  }
+};
+
+template <class S, int K>
+static int sos_bwd(int64_t B, int64_t T, const void* b, const void* a, int coef_batched, const void* x,
+                   const void* mid, const void* y, const void* gy, const void* g_zf, void* grad_x, void* grad_b,
+                   void* grad_a, void* grad_zi, void* ws, int64_t wsb, uint32_t* status, cudaStream_t st) {
+  using P = SosBwdP<S, K>;
+  const int64_t rows = coef_batched ? B : 1;
+  const int64_t tb = table_bytes<S, K>(rows);
+  if (!ws || (reinterpret_cast<uintptr_t>(ws) & 255u) || wsb < tb + kHeaderBytes) return PTB_ERR_WORKSPACE;
+  const bool want_coef = grad_b != nullptr || grad_a != nullptr;
+  if (want_coef && (!x || !mid || !y)) return PTB_ERR_ARG;
+  int rc = build_table<S, K, true>(b, a, coef_batched, B, ws, P::SPT, st);
+  if (rc != PTB_OK) return rc;
+  char* scan_ws = static_cast<char*>(ws) + tb;
+  typename P::Params p;
+  p.tab = static_cast<const S*>(ws);
+  p.tab_stride = coef_batched ? SosDims<K>::ROWTAB : 0;
+  p.gy = static_cast<const S*>(gy);
+  p.x = static_cast<const S*>(x);
+  p.mid = static_cast<const S*>(mid);
+  p.y = static_cast<const S*>(y);
+  p.g_in = static_cast<const S*>(g_zf);
+  p.grad_x = static_cast<S*>(grad_x);
+  p.grad_zi = static_cast<S*>(grad_zi);
+  p.err = status ? status : reinterpret_cast<uint32_t*>(scan_ws + 4);
+  p.T = T;
+  p.B = B;
+  p.want_coef = want_coef ? 1 : 0;
+  const bool bulk = aligned16(gy) && aligned16(grad_x) &&
+                    (!want_coef || (aligned16(x) && aligned16(mid) && aligned16(y))) && (T * sizeof(S)) % 16 == 0;
+  p.bulk = bulk ? 1 : 0;
+  void* partial = nullptr;
+  int64_t nchunks = 0;
+  rc = launch_scan<P, false>(p, B, T, bulk, scan_ws, wsb - tb, status, st, &partial, &nchunks);
+  if (rc != PTB_OK || !want_coef) return rc;
+  SosCoefGrads<S, K> epi{static_cast<const S*>(a), rows * 2, coef_batched ? 2 : 0, static_cast<S*>(grad_b),
+                         static_cast<S*>(grad_a), rows};
+  return launch_reduce<S, 5 * K>(partial, B, nchunks, coef_batched, epi, st);
+}
+
+}  // namespace ptb
+
+using namespace ptb;
+
+#ifdef PTB_SOS_MINIMAL   // tuning builds: only the six-section float kernels
+#define PTB_SOS_DISPATCH(FN, ...)                                            \
+  do {                                                                       \
+    if (dtype == PTB_F32 && K == 6) return FN<float, 6>(__VA_ARGS__);        \
+  } while (0)
+#else
+#define PTB_SOS_DISPATCH(FN, ...)                                            \
+  do {                                                                       \
+    if (dtype == PTB_F32) {                                                  \
+      switch (K) {                                                           \
+        case 2: return FN<float, 2>(__VA_ARGS__);                            \
+        case 4: return FN<float, 4>(__VA_ARGS__);                            \
+        case 6: return FN<float, 6>(__VA_ARGS__);                            \
+        case 8: return FN<float, 8>(__VA_ARGS__);                            \
+      }                                                                      \
+    } else if (dtype == PTB_F64) {                                           \
+      switch (K) {                                                           \
+        case 2: return FN<double, 2>(__VA_ARGS__);                           \
+        case 4: return FN<double, 4>(__VA_ARGS__);                           \
+        case 6: return FN<double, 6>(__VA_ARGS__);                           \
+        case 8: return FN<double, 8>(__VA_ARGS__);                           \
+      }                                                                      \
+    }                                                                        \
+  } while (0)
+#endif
+
+extern "C" {
+
+int64_t ptb_sos_cascade_workspace_bytes(int dtype, int K, int64_t B, int64_t T) {
+  if (B <= 0 || T <= 0) return 0;
+  PTB_SOS_DISPATCH(sos_ws_bytes, B, T);   // includes the bound of the single-section passes
+  return 0;
+}
+
+int ptb_sos_cascade_fwd(int dtype, int K, int64_t B, int64_t T, const void* b, const void* a, int coef_batched,
+                        const void* zi, const void* x, void* y, void* mid, void* zf, void* workspace,
+                        int64_t workspace_bytes, uint32_t* status, ptb_stream_t stream) {
+  if (B <= 0 || T <= 0 || !b || !a || !x || !y) return PTB_ERR_ARG;
+  if (mid != nullptr) {
+    if (K < 2 || K > 8) return PTB_ERR_ARG;
+    if (dtype == PTB_F32)
+      return sos_fwd_chain<float>(dtype, K, B, T, (const float*)b, (const float*)a, coef_batched, (const float*)zi,
+                                  (const float*)x, (float*)y, (float*)mid, (float*)zf, workspace, workspace_bytes,
+                                  status, stream);
+    if (dtype == PTB_F64)
+      return sos_fwd_chain<double>(dtype, K, B, T, (const double*)b, (const double*)a, coef_batched,
+                                   (const double*)zi, (const double*)x, (double*)y, (double*)mid, (double*)zf,
+                                   workspace, workspace_bytes, status, stream);
+    return PTB_ERR_ARG;
+  }
+  PTB_SOS_DISPATCH(sos_fwd, B, T, b, a, coef_batched, zi, x, y, zf, workspace, workspace_bytes, status,
+                   (cudaStream_t)stream);
+  return PTB_ERR_ARG;
+}
+
+int ptb_sos_cascade_bwd(int dtype, int K, int64_t B, int64_t T, const void* b, const void* a, int coef_batched,
+                        const void* x, const void* mid, const void* y, const void* gy, const void* g_zf,
+                        void* grad_x, void* grad_b, void* grad_a, void* grad_zi, void* workspace,
+                        int64_t workspace_bytes, uint32_t* status, ptb_stream_t stream) {
+  if (B <= 0 || T <= 0 || !b || !a || !gy || !grad_x) return PTB_ERR_ARG;
+  PTB_SOS_DISPATCH(sos_bwd, B, T, b, a, coef_batched, x, mid, y, gy, g_zf, grad_x, grad_b, grad_a, grad_zi, workspace,
+                   workspace_bytes, status, (cudaStream_t)stream);
+  return PTB_ERR_ARG;
+}
+
+}  // extern "C"

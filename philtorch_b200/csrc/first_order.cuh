@@ -59,6 +59,7 @@ struct ScalarAffine {
   static __device__ __forceinline__ State apply(const Map& m, const State& s) {
     State r; r.v[0] = m.v[0] * s.v[0] + m.v[1]; return r;
   }
+  PTB_NO_CTX
 };
 
 // ------------------------------------------------------------------------------------ forward
@@ -378,6 +379,7 @@ struct FoCarry {
   static __device__ __forceinline__ State apply(const Map& m, const State& s) {
     State r; r.v[0] = m.v[0] * s.v[0] + m.v[1]; r.v[1] = m.v[0] * s.v[1] + m.v[2]; return r;
   }
+  PTB_NO_CTX
   static __device__ __forceinline__ void plan(const Params& p, bool, int64_t row, int64_t t0, int nvalid,
                                               IoPlan& io) {
     const uint32_t bytes = (uint32_t)nvalid * sizeof(S);

@@ -45,7 +45,40 @@
 #pragma once
 #include "ptx.cuh"
 
+#include <type_traits>
+
 namespace ptb {
+
+// Policies whose maps are self-contained (they carry their own linear part) need no context:
+// this macro, expanded inside the algebra struct after compose/apply, supplies the context-taking
+// forms the engine calls.  Policies whose linear part is implicit (a per-row table of matrix
+// powers, see sos_cascade.cuh) define Ctx, ctx_stage, ctx_row and the three functions themselves.
+#define PTB_NO_CTX                                                                                       \
+  using Ctx = int;                                                                                       \
+  static __device__ __forceinline__ Ctx ctx_stage(const unsigned char*) { return 0; }                    \
+  template <class Pr_>                                                                                   \
+  static __device__ __forceinline__ Ctx ctx_row(const Pr_&, int64_t) { return 0; }                       \
+  static __device__ __forceinline__ Map compose(Ctx, const Map& a, const Map& b) { return compose(a, b); } \
+  static __device__ __forceinline__ State apply(Ctx, const Map& m, const State& s) { return apply(m, s); } \
+  static __device__ __forceinline__ State thread_state(Ctx, const Map& wp, const Map& e, const State& hin, \
+                                                       int) {                                            \
+    return apply(compose(wp, e), hin);                                                                   \
+  }                                                                                                      \
+  /* inclusive scan over the lanes of a warp (level 0: threads of a warp, 1: warps of a tile) */         \
+  static __device__ __forceinline__ Map warp_scan(Ctx, Map m, int lane, int) {                           \
+    _Pragma("unroll") for (int d = 1; d < 32; d <<= 1) {                                                 \
+      Map o = shfl_up_pod(m, d);                                                                         \
+      if (lane >= d) m = compose(o, m);                                                                  \
+    }                                                                                                    \
+    return m;                                                                                            \
+  }
+
+// Optional policy members: EXTRA_SMEM bytes of policy-owned shared memory behind the engine's
+// (with init_extra / prefetch / finish_x hooks, see scan_kernel).
+template <class P, class = void>
+struct ExtraSmemOf { static constexpr int value = 0; };
+template <class P>
+struct ExtraSmemOf<P, std::void_t<decltype(P::EXTRA_SMEM)>> { static constexpr int value = P::EXTRA_SMEM; };
 
 constexpr uint32_t kNoTile = 0xFFFFFFFFu;
 constexpr uint32_t kErrLookbackTimeout = 1u;
@@ -170,16 +203,6 @@ __device__ __forceinline__ uint32_t slot_decode(const uint64_t* r, Map& m, State
   return (f0 == 2u && ok2) ? 2u : ((f0 == 1u && ok1) ? 1u : 0u);
 }
 
-template <class P>
-__device__ __forceinline__ typename P::Map warp_scan_inclusive(typename P::Map m, int lane) {
-#pragma unroll
-  for (int d = 1; d < 32; d <<= 1) {
-    typename P::Map o = shfl_up_pod(m, d);
-    if (lane >= d) m = P::compose(o, m);
-  }
-  return m;
-}
-
 // Look-back executed by all 32 lanes of a look-back warp; returns (in every lane) the state
 // entering the tile.  Windows of predecessors (one per lane, all loads in flight together) are
 // folded until one contains an end state.  The look-back starts as soon as the tile's ticket is
@@ -188,7 +211,7 @@ __device__ __forceinline__ typename P::Map warp_scan_inclusive(typename P::Map m
 // 32 for a handful of long rows) and polls with a back-off: that keeps the polling traffic in L2
 // small.  Later windows are 32 wide.
 template <class P>
-__device__ __forceinline__ typename P::State lookback(const Workspace& ws, uint32_t ticket,
+__device__ __forceinline__ typename P::State lookback(const typename P::Ctx& ctx, const Workspace& ws, uint32_t ticket,
                                                       uint32_t chunk, uint32_t B, int lane,
                                                       uint32_t& failed, int first_window, uint64_t kWaitNs) {
   using Map = typename P::Map;
@@ -229,7 +252,7 @@ __device__ __forceinline__ typename P::State lookback(const Workspace& ws, uint3
     if (m2 & 1u) {
       const State s = shfl_pod(st, 0);
       const Map a0 = shfl_pod(acc, 0);
-      result = P::apply(a0, s);
+      result = P::apply(ctx, a0, s);
       break;
     }
     const int j = m2 ? (__ffs(m2) - 1) : 32;
@@ -238,12 +261,12 @@ __device__ __forceinline__ typename P::State lookback(const Workspace& ws, uint3
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
       Map o = shfl_down_pod(m, d);
-      if (lane + d < 32) m = P::compose(o, m);
+      if (lane + d < 32) m = P::compose(ctx, o, m);
     }
-    acc = P::compose(m, acc);
+    acc = P::compose(ctx, m, acc);
     if (m2) {
       const Map a0 = shfl_pod(acc, 0);
-      result = P::apply(a0, P::zero_state());
+      result = P::apply(ctx, a0, P::zero_state());
       break;
     }
     base += wsize;
@@ -264,6 +287,14 @@ __device__ __forceinline__ typename P::State lookback(const Workspace& ws, uint3
 //           aggregate(prm, stage, tpos, row, t0, nvalid) -> Map          (phase 1, reads the stage)
 //           finish(prm, State in, stage, tpos, row, t0, nvalid) -> Partial (phase 2, reads and
 //                                                                          overwrites the stage)
+//           Ctx, ctx_stage(stage), ctx_row(prm, row), compose/apply(ctx, ...), thread_state(ctx,
+//           warp prefix, thread prefix, tile-incoming state, lane), warp_scan(ctx, map, lane, level):
+//           PTB_NO_CTX unless the linear
+//           part of the maps lives in a per-row table
+//   optional EXTRA_SMEM > 0: init_extra(extra) (one thread, before the first tile),
+//           prefetch(prm, extra, seq, warp, lane, row, t0, nvalid) (per warp, once per tile, after
+//           the previous tile's phase 2), finish_x(prm, in, stage, extra, seq, warp, lane, row, t0,
+//           nvalid, wait_ns) instead of finish; seq = number of tiles this CTA finished before
 // --------------------------------------------------------------------------------------------------
 template <class P>
 struct EngineSmem {
@@ -287,7 +318,9 @@ struct EngineSmem {
   static constexpr int kHinOff = kTaggOff + D * kMapB;                // State hin[D]
   static constexpr int kPcntOff = kHinOff + D * kStateB;              // u32 partial arrivals[D]
   static constexpr int kPartOff = ((kPcntOff + 4 * D + 15) / 16) * 16;   // Partial[D][NW]
-  static constexpr int kTotal = kPartOff + (int)sizeof(typename P::Partial) * kNW * D + 16;
+  static constexpr int kExtraOff = ((kPartOff + (int)sizeof(typename P::Partial) * kNW * D + 16 + 127) / 128) * 128;
+  static constexpr int kExtra = ExtraSmemOf<P>::value;   // policy-owned area
+  static constexpr int kTotal = kExtraOff + kExtra;
 };
 
 struct TileCoords {
@@ -357,6 +390,7 @@ scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, 
       sm_pcnt[s] = 0;
     }
     for (int i = 0; i < 3; ++i) mbar_init(&sync_bar[i], NT);
+    if constexpr (L::kExtra > 0) P::init_extra(smem + L::kExtraOff);
     *sm_abort = 0;
     fence_mbar_init();
   }
@@ -481,7 +515,7 @@ scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, 
       if (lane == 0) PTB_EV(4, n);
       State hin;
       if (c.chunk == 0) hin = P::row_init(prm, c.row);   // its end state is published in phase 1
-      else hin = lookback<P>(ws, ticket, c.chunk, B, lane, failed, lb_first, kWaitNs);
+      else hin = lookback<P>(P::ctx_row(prm, c.row), ws, ticket, c.chunk, B, lane, failed, lb_first, kWaitNs);
       if (lane == 0) {
         sm_hin[s] = hin;
         mbar_arrive(&lb_done[s]);
@@ -497,7 +531,7 @@ scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, 
       PTB_PROF_END(t_lb_wait_agg, ta0);
       if (lane == 0) {
         if (c.chunk > 0 || nchunks == 1) {
-          const State hend = P::apply(sm_tagg[s], hin);
+          const State hend = P::apply(P::ctx_row(prm, c.row), sm_tagg[s], hin);
           if (c.chunk + 1 < nchunks) slot_store(ws.slots + (size_t)ticket * P::SLOT_WORDS, hend, 2u);
           else P::row_final(prm, c.row, hend);
         }
@@ -550,9 +584,10 @@ scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, 
       }
       cta_sync(0, sync_par0);
     }
+    const typename P::Ctx ctx = P::ctx_stage(stage);
     const Map mine = P::aggregate(prm, stage, tpos, c.row, c.t0, c.nvalid);
     if (tid == 0) PTB_EV(10, p1);
-    const Map inc = warp_scan_inclusive<P>(mine, lane);
+    const Map inc = P::warp_scan(ctx, mine, lane, 0);
     if (tid == 0) PTB_EV(11, p1);
     uint32_t order = 0;
     if (lane == 31) {
@@ -572,7 +607,7 @@ scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, 
       // last warp of the tile: scan the warp totals and publish the tile's record right away
       __threadfence_block();
       const Map w = lane < NW ? wtot[s * NW + lane] : P::identity();
-      const Map winc = warp_scan_inclusive<P>(w, lane);
+      const Map winc = P::warp_scan(ctx, w, lane, 1);
       Map wexc = shfl_up_pod(winc, 1);
       if (lane == 0) wexc = P::identity();
       if (lane < NW) wpre[s * NW + lane] = wexc;
@@ -583,7 +618,7 @@ scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, 
         if (c.chunk > 0) {
           slot_store(slot, winc, 1u);
         } else if (nchunks > 1) {
-          slot_store(slot, P::apply(winc, P::row_init(prm, c.row)), 2u);
+          slot_store(slot, P::apply(ctx, winc, P::row_init(prm, c.row)), 2u);
         }
       }
       __syncwarp();
@@ -600,8 +635,13 @@ scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, 
 #pragma unroll
     for (int i = 1; i < D; ++i)
       if (i == s) e = exc[i];
-    const Map pre = P::compose(wpre[s * NW + warp], e);
-    Partial part = P::finish(prm, P::apply(pre, hin), stage, tpos, c.row, c.t0, c.nvalid);
+    const State mine = P::thread_state(P::ctx_stage(stage), wpre[s * NW + warp], e, hin, lane);
+    if (tid == 0) PTB_EV(12, p2);
+    Partial part;
+    if constexpr (L::kExtra > 0)
+      part = P::finish_x(prm, mine, stage, smem + L::kExtraOff, p2, warp, lane, c.row, c.t0, c.nvalid, kWaitNs);
+    else
+      part = P::finish(prm, mine, stage, tpos, c.row, c.t0, c.nvalid);
 
     if (P::HAS_PARTIAL) {
       // per-tile sum for time-invariant gradients: warp shuffle, then the last warp to arrive adds
@@ -653,6 +693,7 @@ scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, 
   };
 
   bool ended = false;
+  uint32_t pf = 0;           // tiles whose phase-2 operands this warp has requested (policies with a prefetch hook)
   uint32_t idle = 0;
   uint64_t idle_t0 = 0;
   // On the plain-load path both phases contain barriers among the compute threads, so all warps
@@ -660,6 +701,15 @@ scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, 
   const uint32_t ahead = bulk ? (uint32_t)D : 1u;
   while (true) {
     bool progressed = false;
+    if constexpr (L::kExtra > 0) {
+      // operands that phase 2 streams through the policy's own buffers: requested as soon as the
+      // previous tile has left them, long before the tile's incoming state is known
+      if (pf == p2 && p2 < p1) {
+        const TileCoords c = tile_coords<P>(tile_ticket[p2 % D], B, nchunks, T);
+        P::prefetch(prm, smem + L::kExtraOff, p2, warp, lane, c.row, c.t0, c.nvalid);
+        ++pf;
+      }
+    }
     if (p2 < p1) {
       const int s2 = p2 % D;
       // the warp prefixes need every warp's phase 1 (agg_ready), the incoming state the look-back
@@ -700,6 +750,7 @@ scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, 
 #endif
     }
   }
+  if constexpr (L::kExtra > 0) bulk_wait_all();   // bulk copies issued by the policy's hooks
   PTB_PROF_END(t_c_total, tc0);
   if (tid == 0) {
     PTB_PROF_FLUSH(8, t_c_idle); PTB_PROF_FLUSH(10, t_c_total);

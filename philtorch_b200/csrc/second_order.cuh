@@ -47,6 +47,7 @@ struct MatAffine {
     r.v[1] = m.v[2] * s.v[0] + m.v[3] * s.v[1] + m.v[5];
     return r;
   }
+  PTB_NO_CTX
 };
 
 // ---- per-sample shared-memory accessors ---------------------------------------------------------

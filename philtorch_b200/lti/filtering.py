@@ -13,11 +13,12 @@ import torch
 import torch.nn.functional as F
 from torch import Tensor
 
-from ..autograd import BiquadTDF2
+from ..autograd import BiquadTDF2, SOSCascade
+from ..ops import SOS_CASCADE_SIZES
 from ..mat import companion
 from .ssm import state_space
 
-__all__ = ["lfilter", "filtfilt", "lfilter_zi"]
+__all__ = ["lfilter", "filtfilt", "lfilter_zi", "sosfilt"]
 
 
 def _pad_to_order2(b: Tensor, a: Tensor):
@@ -104,6 +105,53 @@ def lfilter(b: Tensor, a: Tensor, x: Tensor, zi: Optional[Tensor] = None, form: 
             y, zf = y.squeeze(0), zf.squeeze(0)
         return y, zf
     return y.squeeze(0) if squeeze_first else y
+
+
+def sosfilt(b: Tensor, a: Tensor, x: Tensor, zi: Optional[Tensor] = None) -> Union[Tensor, tuple[Tensor, Tensor]]:
+    """A cascade of K second-order sections, the result of
+    ``for k in range(K): x = lfilter(b[k], a[k], x, form="tdf2")`` (the way a cascade is run with
+    philtorch/lti/filtering.py:211-333), computed by fused kernels: up to eight sections per pass
+    over the signal, forward and backward.
+
+    Args:
+        b: numerators, (K, 3) or (K, B, 3).
+        a: denominators without a0 = 1, (K, 2) or (K, B, 2).
+        x: input, (B, N), CUDA, float32 or float64.
+        zi: initial states of all sections, (K, B, 2); when given, ``(y, zf)`` is returned.
+    """
+    if x.dim() != 2:
+        raise ValueError("Input signal x must be 2D (batch, time).")
+    if b.dim() not in (2, 3) or a.dim() not in (2, 3) or b.size(0) != a.size(0):
+        raise ValueError("b must be (K,3) or (K,B,3) and a (K,2) or (K,B,2) with the same K.")
+    if b.dim() != a.dim():   # one batched, one shared
+        B = x.size(0)
+        b = b.unsqueeze(1).expand(-1, B, -1) if b.dim() == 2 else b
+        a = a.unsqueeze(1).expand(-1, B, -1) if a.dim() == 2 else a
+    K = b.size(0)
+    kmax = max(SOS_CASCADE_SIZES)
+    y, zfs, k0 = x, [], 0
+    while k0 < K:
+        n = min(kmax, K - k0)
+        bg, ag = b[k0:k0 + n], a[k0:k0 + n]
+        zg = None if zi is None else zi[k0:k0 + n]
+        if n == 1:
+            y, zf = BiquadTDF2.apply(bg[0], ag[0], None if zg is None else zg[0], y)
+            zf = zf.unsqueeze(0)
+        else:
+            m = min(q for q in SOS_CASCADE_SIZES if q >= n)
+            if m > n:   # pad with identity sections: y = x, no state
+                eye_b = torch.zeros_like(bg[:1]).index_fill(-1, torch.zeros(1, dtype=torch.long, device=b.device), 1.0)
+                bg = torch.cat([bg] + [eye_b] * (m - n))
+                ag = torch.cat([ag] + [torch.zeros_like(ag[:1])] * (m - n))
+                if zg is not None:
+                    zg = torch.cat([zg] + [torch.zeros_like(zg[:1])] * (m - n))
+            y, zf = SOSCascade.apply(bg, ag, zg, y)
+            zf = zf[:n]
+        zfs.append(zf)
+        k0 += n
+    if zi is None:
+        return y
+    return y, torch.cat(zfs)
 
 
 def lfilter_zi(a: Tensor, b: Optional[Tensor] = None, transpose: bool = True) -> Tensor:

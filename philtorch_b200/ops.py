@@ -383,6 +383,93 @@ def _(b, a, x, y, gy, gzf, need_coef, need_zi):
             torch.empty_like(x, memory_format=torch.contiguous_format))
 
 
+# =============================================================================== fused SOS cascade
+_LIB.define("sos_cascade(Tensor b, Tensor a, Tensor? zi, Tensor x, bool keep_mid) -> (Tensor, Tensor, Tensor)",
+            tags=_TAGS)
+_LIB.define("sos_cascade_bwd(Tensor b, Tensor a, Tensor x, Tensor mid, Tensor y, Tensor gy, Tensor? gzf, "
+            "bool need_coef, bool need_zi) -> (Tensor, Tensor, Tensor, Tensor)", tags=_TAGS)
+
+SOS_CASCADE_SIZES = (2, 4, 6, 8)   # numbers of sections the fused kernels are built for
+
+
+def _check_sos(b: Tensor, a: Tensor, zi: Optional[Tensor], x: Tensor) -> None:
+    torch._check(x.dim() == 2, lambda: "x must be 2D (batch, time).")
+    torch._check(b.dim() in (2, 3) and b.shape[-1] == 3, lambda: "b must be (K,3) or (K,B,3).")
+    torch._check(a.dim() == b.dim() and a.shape[-1] == 2 and a.shape[0] == b.shape[0],
+                 lambda: "a must be (K,2) or (K,B,2), like b.")
+    torch._check(b.shape[0] in SOS_CASCADE_SIZES, lambda: f"the number of sections must be one of {SOS_CASCADE_SIZES}.")
+    if b.dim() == 3:
+        torch._check(b.shape[1] == x.shape[0] and a.shape[1] == x.shape[0],
+                     lambda: "batched coefficients must match x's batch size.")
+    if zi is not None:
+        torch._check(zi.dim() == 3 and zi.shape[0] == b.shape[0] and zi.shape[1] == x.shape[0] and zi.shape[2] == 2,
+                     lambda: "zi must be (K,B,2).")
+
+
+def _sos_cascade(b, a, zi, x, keep_mid):
+    _check_sos(b, a, zi, x)
+    dev = _lib.require_cuda(b, a, zi, x)
+    if b.dtype != x.dtype or a.dtype != x.dtype or (zi is not None and zi.dtype != x.dtype):
+        raise RuntimeError("b, a and zi must have the same scalar type as input")
+    K = b.shape[0]
+    B, T = x.shape
+    b_c, a_c, zi_c, x_c = b.contiguous(), a.contiguous(), _opt(zi), x.contiguous()
+    y = torch.empty_like(x_c)
+    mid = x.new_empty((K - 1, B, T) if keep_mid else (0,))
+    zf = x.new_empty(K, B, 2)
+    if B and T:
+        code = _lib.dtype_code(x)
+        _lib.call(lib.ptb_sos_cascade_fwd, dev, B, T, code, K, B, T, ptr(b_c), ptr(a_c), int(b.dim() == 3),
+                  ptr(zi_c), ptr(x_c), ptr(y), ptr(mid) if keep_mid else None, ptr(zf),
+                  ws_bytes=lib.ptb_sos_cascade_workspace_bytes(code, K, B, T))
+    elif B:
+        zf.copy_(zi_c) if zi_c is not None else zf.zero_()
+    return y, mid, zf
+
+
+def _sos_cascade_bwd(b, a, x, mid, y, gy, gzf, need_coef, need_zi):
+    dev = _lib.require_cuda(b, a, x, mid, y, gy, gzf)
+    K = b.shape[0]
+    B, T = x.shape
+    b_c, a_c, x_c, mid_c, y_c, gy_c, gzf_c = b.contiguous(), a.contiguous(), x.contiguous(), mid.contiguous(), \
+        y.contiguous(), gy.contiguous(), _opt(gzf)
+    if need_coef and mid.numel() != (K - 1) * B * T:
+        raise RuntimeError("coefficient gradients need the intermediate section outputs (keep_mid=True)")
+    gx = torch.empty_like(x_c)
+    gb = torch.zeros_like(b_c) if need_coef else b.new_empty(0)
+    ga = torch.zeros_like(a_c) if need_coef else a.new_empty(0)
+    gzi = x.new_empty(K, B, 2) if need_zi else x.new_empty(0)
+    if B and T:
+        code = _lib.dtype_code(x)
+        _lib.call(lib.ptb_sos_cascade_bwd, dev, B, T, code, K, B, T, ptr(b_c), ptr(a_c), int(b.dim() == 3),
+                  ptr(x_c), ptr(mid_c) if need_coef else None, ptr(y_c), ptr(gy_c), ptr(gzf_c), ptr(gx),
+                  ptr(gb) if need_coef else None, ptr(ga) if need_coef else None, ptr(gzi) if need_zi else None,
+                  ws_bytes=lib.ptb_sos_cascade_workspace_bytes(code, K, B, T))
+    elif need_zi:
+        gzi.copy_(gzf_c) if gzf_c is not None else gzi.zero_()
+    return gb, ga, gzi, gx
+
+
+_LIB.impl("sos_cascade", _sos_cascade, "CUDA")
+_LIB.impl("sos_cascade_bwd", _sos_cascade_bwd, "CUDA")
+
+
+@torch.library.register_fake("philtorch_b200::sos_cascade")
+def _(b, a, zi, x, keep_mid):
+    _check_sos(b, a, zi, x)
+    K = b.shape[0]
+    return (torch.empty_like(x, memory_format=torch.contiguous_format),
+            x.new_empty((K - 1, x.shape[0], x.shape[1]) if keep_mid else (0,)), x.new_empty(K, x.shape[0], 2))
+
+
+@torch.library.register_fake("philtorch_b200::sos_cascade_bwd")
+def _(b, a, x, mid, y, gy, gzf, need_coef, need_zi):
+    return (torch.empty_like(b) if need_coef else b.new_empty(0),
+            torch.empty_like(a) if need_coef else a.new_empty(0),
+            x.new_empty(b.shape[0], x.shape[0], 2) if need_zi else x.new_empty(0),
+            torch.empty_like(x, memory_format=torch.contiguous_format))
+
+
 # CPU (and any other backend) tensors: fail loudly instead of "no kernel registered" noise.
 def _no_backend(name):
     def fn(*args, **kwargs):
@@ -391,5 +478,6 @@ def _no_backend(name):
 
 
 for _name in ("lti_recur", "lti_recur_bwd", "lpv_recur", "lpv_recur_bwd", "lti_recur2", "lti_recur2_sx", "recur2",
-              "recur2_sx", "lti_recur2_bwd", "recur2_bwd", "biquad_tdf2", "biquad_tdf2_bwd", "lpv_recur_carry", "lpv_recur_zero_carry"):
+              "recur2_sx", "lti_recur2_bwd", "recur2_bwd", "biquad_tdf2", "biquad_tdf2_bwd", "lpv_recur_carry", "lpv_recur_zero_carry",
+              "sos_cascade", "sos_cascade_bwd"):
     _LIB.impl(_name, _no_backend(_name), "CPU")
