@@ -319,6 +319,61 @@ def run_time_sharded(args, rank: int, world: int, local_rank: int):
     dist.destroy_process_group()
 
 
+def run_sos_cascade(args):
+    """Secondary line (not the headline metric): six second-order sections, B = 512, T = 2^18, fp32,
+    forward + backward with gradients for x, b and a, through ``lti.sosfilt`` (fused passes) and,
+    for comparison, through six chained ``lti.lfilter`` calls (how the reference runs a cascade)."""
+    import torch
+
+    import philtorch_b200 as ptb
+    from philtorch_b200 import workloads
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    Bc, Tc, K = args.rows if args.rows != B else 512, 1 << 18, 6
+    w = workloads.sos_cascade(B=Bc, T=Tc, sections=K, device=dev)
+    b, a, x, gy = w["b"].requires_grad_(), w["a"].requires_grad_(), w["x"].requires_grad_(), w["gy"]
+
+    def fused():
+        return torch.autograd.grad(ptb.lti.sosfilt(b, a, x), (b, a, x), gy)
+
+    def chained():
+        u = x
+        for k in range(K):
+            u = ptb.lti.lfilter(b[k], a[k], u)
+        return torch.autograd.grad(u, (b, a, x), gy)
+
+    def timed(fn):
+        for _ in range(max(3, args.warmup)):
+            fn()
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        return e0.elapsed_time(e1) / args.steps
+
+    ms, ms_chain = timed(fused), timed(chained)
+    ptb.check_errors(dev)
+    peak, kind = measured_peak()
+    n = Bc * Tc
+    # bytes per input sample: forward K passes of 8 B (the section outputs are kept), backward one
+    # pass reading gy, x and the K outputs and writing grad_x
+    alg = (8 * K + 4 * (K + 3)) * n
+    print(json.dumps({"metric": METRIC, "value": n / (ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+                      "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+                      "vs_baseline": None, "dtype": "f32", "data": "synthetic (seeded, generated on device)",
+                      "config": {"workload": f"cascade of {K} second-order sections fwd+bwd (x, b, a grads), fp32, "
+                                             f"B={Bc}, T=2^18", "inputs": "larger than L2"},
+                      "chained_single_sections_ms": ms_chain,
+                      "roofline": {"bound": "hbm", "achieved": alg / (ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                                   "peak_source": f"{kind} copy bandwidth", "frac": alg / (ms * 1e-3) / 1e9 / peak,
+                                   "note": f"algorithmic {alg // n} B per input sample (chained sections: {24 * K} B)"}}),
+          flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -331,12 +386,18 @@ def main():
     ap.add_argument("--time-sharded", action="store_true",
                     help="secondary workload: B=8 long rows split along time over the ranks")
     ap.add_argument("--log2-T", type=int, default=28, dest="log2_T", help="total row length of --time-sharded")
+    ap.add_argument("--sos-cascade", action="store_true",
+                    help="secondary workload: six fused second-order sections, B=512, T=2^18 (one GPU)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference_arm(args, rank)
+        return
+    if args.sos_cascade:
+        if rank == 0:
+            run_sos_cascade(args)
         return
     if args.time_sharded:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
