@@ -19,6 +19,15 @@
 
 namespace ptb {
 
+// The loops over a thread's 16-byte units are unrolled PTB_BQ_UNROLL times, not completely: the
+// samples stay in shared memory and the hot code stays small enough for the instruction caches
+// (a kernel unrolled over all its samples waits for instruction fetches instead of data).
+#ifndef PTB_BQ_UNROLL
+#define PTB_BQ_UNROLL 1
+#endif
+#define PTB_PRAGMA_(x) _Pragma(#x)
+#define PTB_UNROLL_(n) PTB_PRAGMA_(unroll n)
+
 // Derived constants of a row's section {b0, b1 - b0 a1, b2 - b0 a2, -a1, -a2}: computed once per tile
 // by the DMA warp (row_constants) and read from the stage by every thread.
 template <class S>
@@ -125,23 +134,29 @@ struct BqFwd : MatAffine<S> {
                                                   int64_t row, int64_t, int nvalid) {
     BqCoef<S> k;
     k.load(stage + ROWC_OFF);
-    S x[SPT];
-    const int nv = load_x(stage, tpos, nvalid, x);
     Map m = Alg::identity();
-    if (nv == SPT) {
+    if (nvalid - tpos * SPT >= SPT) {
       // full thread: offsets by the recurrence, linear part M^SPT by binary powering
+      const unsigned char* px = stage + X_OFF + (size_t)tpos * SPT * sizeof(S);
       S s0 = S(0), s1 = S(0);
+      PTB_UNROLL_(PTB_BQ_UNROLL)
+      for (int c = 0; c < CH; ++c) {
+        S xv[V];
+        VecIO<S, V>::ld(px + 16 * c, xv);
 #pragma unroll
-      for (int j = 0; j < SPT; ++j) {
-        const S t = s1 + k.B0 * x[j];   // off the chain through s0
-        s1 = k.na2 * s0 + k.B1 * x[j];
-        s0 = k.na1 * s0 + t;
+        for (int q = 0; q < V; ++q) {
+          const S t = s1 + k.B0 * xv[q];   // off the chain through s0
+          s1 = k.na2 * s0 + k.B1 * xv[q];
+          s0 = k.na1 * s0 + t;
+        }
       }
       const S M[4] = {k.na1, S(1), k.na2, S(0)};
       mat2_power<S, SPT>(M, m.v);
       m.v[4] = s0; m.v[5] = s1;
       return m;
     }
+    S x[SPT];
+    const int nv = load_x(stage, tpos, nvalid, x);
 #pragma unroll
     for (int j = 0; j < SPT; ++j) {
       if (j < nv) {
@@ -175,13 +190,30 @@ struct BqFwd : MatAffine<S> {
                                                    int tpos, int64_t row, int64_t, int nvalid) {
     BqCoef<S> k;
     k.load(stage + ROWC_OFF);
-    S x[SPT];
-    const int nv = load_x(stage, tpos, nvalid, x);
-    if (nv == SPT) replay<true>(k, in.v[0], in.v[1], nv, x);
-    else replay<false>(k, in.v[0], in.v[1], nv, x);
     unsigned char* px = stage + X_OFF + (size_t)tpos * SPT * sizeof(S);
+    if (nvalid - tpos * SPT >= SPT) {
+      S h0 = in.v[0], h1 = in.v[1];
+      PTB_UNROLL_(PTB_BQ_UNROLL)
+      for (int c = 0; c < CH; ++c) {
+        S xv[V];
+        VecIO<S, V>::ld(px + 16 * c, xv);
 #pragma unroll
-    for (int c = 0; c < CH; ++c) VecIO<S, V>::st(px + 16 * c, &x[c * V]);
+        for (int q = 0; q < V; ++q) {
+          const S xj = xv[q];
+          xv[q] = h0 + k.b0 * xj;
+          const S t = h1 + k.B0 * xj;   // off the chain through h0
+          h1 = k.na2 * h0 + k.B1 * xj;
+          h0 = k.na1 * h0 + t;
+        }
+        VecIO<S, V>::st(px + 16 * c, xv);
+      }
+    } else {
+      S x[SPT];
+      const int nv = load_x(stage, tpos, nvalid, x);
+      replay<false>(k, in.v[0], in.v[1], nv, x);
+#pragma unroll
+      for (int c = 0; c < CH; ++c) VecIO<S, V>::st(px + 16 * c, &x[c * V]);
+    }
     Partial r; r.v[0] = S(0); return r;
   }
 };
@@ -261,22 +293,28 @@ struct BqBwd : MatAffine<S> {
                                                   int64_t row, int64_t, int nvalid) {
     BqCoef<S> k;
     k.load(stage + ROWC_OFF);
-    S g[SPT];
-    const int nv = load_slot(stage, G_OFF, tpos, nvalid, g);
     Map m = Alg::identity();
-    if (nv == SPT) {
+    if (nvalid - tpos * SPT >= SPT) {
+      const unsigned char* pg = stage + G_OFF + (size_t)tpos * SPT * sizeof(S);
       S s0 = S(0), s1 = S(0);
+      PTB_UNROLL_(PTB_BQ_UNROLL)
+      for (int c = CH - 1; c >= 0; --c) {
+        S gv[V];
+        VecIO<S, V>::ld(pg + 16 * c, gv);
 #pragma unroll
-      for (int j = SPT - 1; j >= 0; --j) {
-        const S t = k.na2 * s1 + g[j];   // off the chain through s0
-        s1 = s0;
-        s0 = k.na1 * s0 + t;
+        for (int q = V - 1; q >= 0; --q) {
+          const S t = k.na2 * s1 + gv[q];   // off the chain through s0
+          s1 = s0;
+          s0 = k.na1 * s0 + t;
+        }
       }
       const S Mt[4] = {k.na1, k.na2, S(1), S(0)};
       mat2_power<S, SPT>(Mt, m.v);
       m.v[4] = s0; m.v[5] = s1;
       return m;
     }
+    S g[SPT];
+    const int nv = load_slot(stage, G_OFF, tpos, nvalid, g);
 #pragma unroll
     for (int j = SPT - 1; j >= 0; --j) {
       if (j < nv) {
@@ -321,6 +359,54 @@ struct BqBwd : MatAffine<S> {
                                                    int tpos, int64_t row, int64_t, int nvalid) {
     BqCoef<S> k;
     k.load(stage + ROWC_OFF);
+    unsigned char* pg = stage + G_OFF + (size_t)tpos * SPT * sizeof(S);
+    if (nvalid - tpos * SPT >= SPT) {
+      const unsigned char* pxs = stage + X_OFF + (size_t)tpos * SPT * sizeof(S);
+      const unsigned char* pys = stage + Y_OFF + (size_t)tpos * SPT * sizeof(S);
+      S l0 = in.v[0], l1 = in.v[1];
+      S a0 = S(0), a1 = S(0), a2 = S(0), a3 = S(0), a4 = S(0);
+      if (p.want_coef) {
+        PTB_UNROLL_(PTB_BQ_UNROLL)
+        for (int c = CH - 1; c >= 0; --c) {
+          S gv[V], xv[V], yv[V];
+          VecIO<S, V>::ld(pg + 16 * c, gv);
+          VecIO<S, V>::ld(pxs + 16 * c, xv);
+          VecIO<S, V>::ld(pys + 16 * c, yv);
+#pragma unroll
+          for (int q = V - 1; q >= 0; --q) {
+            const S gj = gv[q];
+            gv[q] = k.b0 * gj + k.B0 * l0 + k.B1 * l1;
+            a0 += gj * xv[q];
+            a1 += xv[q] * l0;
+            a2 += xv[q] * l1;
+            a3 += yv[q] * l0;
+            a4 += yv[q] * l1;
+            const S t = k.na2 * l1 + gj;   // off the chain through l0
+            l1 = l0;
+            l0 = k.na1 * l0 + t;
+          }
+          VecIO<S, V>::st(pg + 16 * c, gv);
+        }
+      } else {
+        PTB_UNROLL_(PTB_BQ_UNROLL)
+        for (int c = CH - 1; c >= 0; --c) {
+          S gv[V];
+          VecIO<S, V>::ld(pg + 16 * c, gv);
+#pragma unroll
+          for (int q = V - 1; q >= 0; --q) {
+            const S gj = gv[q];
+            gv[q] = k.b0 * gj + k.B0 * l0 + k.B1 * l1;
+            const S t = k.na2 * l1 + gj;
+            l1 = l0;
+            l0 = k.na1 * l0 + t;
+          }
+          VecIO<S, V>::st(pg + 16 * c, gv);
+        }
+      }
+      Partial r;
+      r.v[0] = a0; r.v[1] = a1; r.v[2] = a2; r.v[3] = a3; r.v[4] = a4;
+      return r;
+    }
     S g[SPT], x[SPT], y[SPT];
     const int nv = load_slot(stage, G_OFF, tpos, nvalid, g);
     Partial acc;
@@ -333,7 +419,6 @@ struct BqBwd : MatAffine<S> {
       acc = nv == SPT ? replay<true, false>(k, in.v[0], in.v[1], nv, g, x, y)
                       : replay<false, false>(k, in.v[0], in.v[1], nv, g, x, y);
     }
-    unsigned char* pg = stage + G_OFF + (size_t)tpos * SPT * sizeof(S);
 #pragma unroll
     for (int c = 0; c < CH; ++c) VecIO<S, V>::st(pg + 16 * c, &g[c * V]);
     return acc;
