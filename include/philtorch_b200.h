@@ -215,7 +215,12 @@ int ptb_biquad_tdf2_bwd(int dtype, int64_t B, int64_t T, const void* b, const vo
  *                coefficient gradients
  * Backward: gy (B,T), g_zf optional (K,B,2) -> grad_x (B,T), grad_b / grad_a shaped like b / a
  * (optional, both or none; need x, mid, y), grad_zi optional (K,B,2).
- * Workspace: ptb_sos_cascade_workspace_bytes (holds the per-row table of matrix powers too). */
+ * Workspace: ptb_sos_cascade_workspace_bytes (holds the per-row table of matrix powers too).
+ * Two families of kernels serve these entry points: chained ones (a tile takes over the end states
+ * of its predecessor; fastest when there are at least as many rows as SMs) and decoupled ones
+ * (look-back over aggregates; for few long rows).  ptb_sos_cascade_set_mode: 0 picks by batch size
+ * (default), 1 / 2 force the decoupled / chained family (process-wide; meant for tests). */
+int ptb_sos_cascade_set_mode(int mode);
 int64_t ptb_sos_cascade_workspace_bytes(int dtype, int K, int64_t B, int64_t T);
 int ptb_sos_cascade_fwd(int dtype, int K, int64_t B, int64_t T, const void* b, const void* a, int coef_batched,
                         const void* zi, const void* x, void* y, void* mid, void* zf, void* workspace,

@@ -68,6 +68,8 @@ lib.ptb_selftest_wait_expiry_elems.restype = _i64
 lib.ptb_selftest_wait_expiry.argtypes = [_vp, _i64, _vp, _i64, _vp, _vp]
 lib.ptb_selftest_wait_expiry.restype = _i32
 
+lib.ptb_sos_cascade_set_mode.argtypes = [_i32]
+lib.ptb_sos_cascade_set_mode.restype = _i32
 lib.ptb_sos_cascade_workspace_bytes.argtypes = [_i32, _i32, _i64, _i64]
 lib.ptb_sos_cascade_workspace_bytes.restype = _i64
 lib.ptb_sos_cascade_fwd.argtypes = [_i32, _i32, _i64, _i64, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp] + _tail

@@ -2,6 +2,7 @@
 #include "launch.cuh"
 
 #include "sos_cascade.cuh"
+#include "sos_chain.cuh"
 
 namespace ptb {
 
@@ -21,6 +22,94 @@ namespace ptb {
 template <class S, int K> using SosFwdP = SosFwd<S, K, PTB_SOS_FWD_CH, PTB_SOS_FWD_STAGES, PTB_SOS_FWD_NT, PTB_SOS_FWD_CTAS>;
 template <class S, int K> using SosBwdP = SosBwd<S, K, PTB_SOS_BWD_CH, PTB_SOS_BWD_STAGES, PTB_SOS_BWD_NT, PTB_SOS_BWD_CTAS>;
 
+#ifndef PTB_CHAIN_CH
+#define PTB_CHAIN_CH 9
+#define PTB_CHAIN_NT 256
+#endif
+template <class S, int K> using ChainC = ChainCfg<S, K, PTB_CHAIN_CH, PTB_CHAIN_NT>;
+
+// 0: pick by batch size, 1: always the decoupled kernels, 2: always the chained kernels
+static int g_sos_mode = 0;
+
+static int device_sms(int* sms) {
+  static int cached[kMaxDevices] = {};
+  int dev = 0;
+  PTB_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return PTB_ERR_ARG;
+  if (!cached[dev]) PTB_CUDA(cudaDeviceGetAttribute(&cached[dev], cudaDevAttrMultiProcessorCount, dev));
+  *sms = cached[dev];
+  return PTB_OK;
+}
+// the chained kernels never wait when every resident CTA can work on a row of its own
+static bool use_chain(int64_t B, int sms) { return g_sos_mode == 2 || (g_sos_mode == 0 && B >= sms); }
+
+template <class S, int K>
+static int64_t chain_ws_bytes(int64_t B, int64_t T) {
+  using C = ChainC<S, K>;
+  const int64_t ntiles = B * ((T + C::TILE - 1) / C::TILE);
+  return align_up(B * C::ROW * (int64_t)sizeof(S), 256) + ws_layout(ntiles, C::SLOT_WORDS, 5 * K * sizeof(S)).total;
+}
+
+template <class S, int K>
+static int chain_fwd(int64_t B, int64_t T, const void* b, const void* a, int coef_batched, const void* zi,
+                     const void* x, void* y, void* mid, void* zf, void* ws, int64_t wsb, uint32_t* status,
+                     cudaStream_t st) {
+  using C = ChainC<S, K>;
+  using L = ChainFwdSmem<C>;
+  static_assert(L::kTotal <= 227 * 1024, "shared memory of an SM");
+  const int64_t rows = coef_batched ? B : 1;
+  const int64_t tb = align_up(rows * C::ROW * (int64_t)sizeof(S), 256);
+  const int64_t nchunks = (T + C::TILE - 1) / C::TILE;
+  const int64_t ntiles = B * nchunks;
+  if (ntiles >= 0xFFFFFFFEll || B >= 0xFFFFFFFFll) return PTB_ERR_TOO_LARGE;
+  const WsLayout l = ws_layout(ntiles, C::SLOT_WORDS, 0);
+  if (!ws || (reinterpret_cast<uintptr_t>(ws) & 255u) || wsb < tb + l.total) return PTB_ERR_WORKSPACE;
+  chain_setup_kernel<S, C, false><<<(unsigned)((rows * K + 127) / 128), 128, 0, st>>>(
+      static_cast<const S*>(b), rows * 3, coef_batched ? 3 : 0, static_cast<const S*>(a), rows * 2,
+      coef_batched ? 2 : 0, static_cast<S*>(ws), rows);
+  PTB_CUDA(cudaGetLastError());
+  char* w = static_cast<char*>(ws) + tb;
+  PTB_CUDA(cudaMemsetAsync(w, 0, (size_t)l.part_off, st));
+  Workspace wk;
+  wk.ticket = reinterpret_cast<uint32_t*>(w);
+  wk.error = status ? status : reinterpret_cast<uint32_t*>(w + 4);
+  wk.slots = reinterpret_cast<uint64_t*>(w + l.slots_off);
+  wk.partial = nullptr;
+  ChainFwdParams<S> p;
+  p.tab = static_cast<const S*>(ws);
+  p.tab_stride = coef_batched ? C::ROW : 0;
+  p.zi = static_cast<const S*>(zi);
+  p.x = static_cast<const S*>(x);
+  p.y = static_cast<S*>(y);
+  p.mid = static_cast<S*>(mid);
+  p.zf = static_cast<S*>(zf);
+  p.T = T;
+  p.B = B;
+  const bool bulk = aligned16(x) && aligned16(y) && (!mid || aligned16(mid)) && (T * sizeof(S)) % 16 == 0;
+  int sms = 0;
+  int rc = device_sms(&sms);
+  if (rc != PTB_OK) return rc;
+  static bool attr_set[kMaxDevices] = {};
+  int dev = 0;
+  PTB_CUDA(cudaGetDevice(&dev));
+  if (!attr_set[dev]) {
+    PTB_CUDA(cudaFuncSetAttribute(chain_fwd_kernel<S, C>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+    attr_set[dev] = true;
+  }
+  const unsigned grid = (unsigned)std::min<int64_t>(ntiles, sms);
+  chain_fwd_kernel<S, C><<<grid, C::NT, L::kTotal, st>>>(p, wk, (uint32_t)B, (uint32_t)nchunks, (uint32_t)ntiles,
+                                                         bulk ? 1 : 0, g_wait_ns);
+  PTB_CUDA(cudaGetLastError());
+  return PTB_OK;
+}
+
+template <class S, int K> struct SosCoefGrads;
+
+template <class S, int K>
+static int chain_bwd(int64_t B, int64_t T, const void* b, const void* a, int coef_batched, const void* x,
+                     const void* mid, const void* y, const void* gy, const void* g_zf, void* grad_x, void* grad_b,
+                     void* grad_a, void* grad_zi, void* ws, int64_t wsb, uint32_t* status, cudaStream_t st);
+
 template <class S, int K>
 static int64_t table_bytes(int64_t rows) { return align_up(rows * SosDims<K>::ROWTAB * (int64_t)sizeof(S), 256); }
 
@@ -32,8 +121,9 @@ static int64_t scan_ws_bytes(int64_t B, int64_t T) {
 
 template <class S, int K>
 static int64_t sos_ws_bytes(int64_t B, int64_t T) {
-  return std::max(table_bytes<S, K>(B) + std::max(scan_ws_bytes<SosFwdP<S, K>>(B, T), scan_ws_bytes<SosBwdP<S, K>>(B, T)),
-                  ptb_workspace_bytes(B, T));
+  return std::max(std::max(table_bytes<S, K>(B) + std::max(scan_ws_bytes<SosFwdP<S, K>>(B, T), scan_ws_bytes<SosBwdP<S, K>>(B, T)),
+                           ptb_workspace_bytes(B, T)),
+                  chain_ws_bytes<S, K>(B, T));
 }
 
 template <class S, int K, bool ADJ>
@@ -114,6 +204,68 @@ struct SosCoefGrads {
 };
 
 template <class S, int K>
+static int chain_bwd(int64_t B, int64_t T, const void* b, const void* a, int coef_batched, const void* x,
+                     const void* mid, const void* y, const void* gy, const void* g_zf, void* grad_x, void* grad_b,
+                     void* grad_a, void* grad_zi, void* ws, int64_t wsb, uint32_t* status, cudaStream_t st) {
+  using C = ChainC<S, K>;
+  using L = ChainBwdSmem<C>;
+  static_assert(L::kTotal <= 227 * 1024, "shared memory of an SM");
+  const int64_t rows = coef_batched ? B : 1;
+  const int64_t tb = align_up(rows * C::ROW * (int64_t)sizeof(S), 256);
+  const int64_t nchunks = (T + C::TILE - 1) / C::TILE;
+  const int64_t ntiles = B * nchunks;
+  if (ntiles >= 0xFFFFFFFEll || B >= 0xFFFFFFFFll) return PTB_ERR_TOO_LARGE;
+  const WsLayout l = ws_layout(ntiles, C::SLOT_WORDS, 5 * K * sizeof(S));
+  if (!ws || (reinterpret_cast<uintptr_t>(ws) & 255u) || wsb < tb + l.total) return PTB_ERR_WORKSPACE;
+  const bool want_coef = grad_b != nullptr || grad_a != nullptr;
+  if (want_coef && (!x || !mid || !y)) return PTB_ERR_ARG;
+  chain_setup_kernel<S, C, true><<<(unsigned)((rows * K + 127) / 128), 128, 0, st>>>(
+      static_cast<const S*>(b), rows * 3, coef_batched ? 3 : 0, static_cast<const S*>(a), rows * 2,
+      coef_batched ? 2 : 0, static_cast<S*>(ws), rows);
+  PTB_CUDA(cudaGetLastError());
+  char* w = static_cast<char*>(ws) + tb;
+  PTB_CUDA(cudaMemsetAsync(w, 0, (size_t)l.part_off, st));
+  Workspace wk;
+  wk.ticket = reinterpret_cast<uint32_t*>(w);
+  wk.error = status ? status : reinterpret_cast<uint32_t*>(w + 4);
+  wk.slots = reinterpret_cast<uint64_t*>(w + l.slots_off);
+  wk.partial = w + l.part_off;
+  ChainBwdParams<S> p;
+  p.tab = static_cast<const S*>(ws);
+  p.tab_stride = coef_batched ? C::ROW : 0;
+  p.gy = static_cast<const S*>(gy);
+  p.x = static_cast<const S*>(x);
+  p.mid = static_cast<const S*>(mid);
+  p.y = static_cast<const S*>(y);
+  p.g_in = static_cast<const S*>(g_zf);
+  p.grad_x = static_cast<S*>(grad_x);
+  p.grad_zi = static_cast<S*>(grad_zi);
+  p.T = T;
+  p.B = B;
+  p.want_coef = want_coef ? 1 : 0;
+  const bool bulk = aligned16(gy) && aligned16(grad_x) &&
+                    (!want_coef || (aligned16(x) && aligned16(mid) && aligned16(y))) && (T * sizeof(S)) % 16 == 0;
+  int sms = 0;
+  int rc = device_sms(&sms);
+  if (rc != PTB_OK) return rc;
+  static bool attr_set[kMaxDevices] = {};
+  int dev = 0;
+  PTB_CUDA(cudaGetDevice(&dev));
+  if (!attr_set[dev]) {
+    PTB_CUDA(cudaFuncSetAttribute(chain_bwd_kernel<S, C>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+    attr_set[dev] = true;
+  }
+  const unsigned grid = (unsigned)std::min<int64_t>(ntiles, sms);
+  chain_bwd_kernel<S, C><<<grid, C::NT, L::kTotal, st>>>(p, wk, (uint32_t)B, (uint32_t)nchunks, (uint32_t)ntiles,
+                                                         bulk ? 1 : 0, g_wait_ns);
+  PTB_CUDA(cudaGetLastError());
+  if (!want_coef) return PTB_OK;
+  SosCoefGrads<S, K> epi{static_cast<const S*>(a), rows * 2, coef_batched ? 2 : 0, static_cast<S*>(grad_b),
+                         static_cast<S*>(grad_a), rows};
+  return launch_reduce<S, 5 * K>(wk.partial, B, nchunks, coef_batched, epi, st);
+}
+
+template <class S, int K>
 static int sos_bwd(int64_t B, int64_t T, const void* b, const void* a, int coef_batched, const void* x,
                    const void* mid, const void* y, const void* gy, const void* g_zf, void* grad_x, void* grad_b,
                    void* grad_a, void* grad_zi, void* ws, int64_t wsb, uint32_t* status, cudaStream_t st) {
@@ -184,6 +336,12 @@ using namespace ptb;
 
 extern "C" {
 
+int ptb_sos_cascade_set_mode(int mode) {
+  if (mode < 0 || mode > 2) return PTB_ERR_ARG;
+  g_sos_mode = mode;
+  return PTB_OK;
+}
+
 int64_t ptb_sos_cascade_workspace_bytes(int dtype, int K, int64_t B, int64_t T) {
   if (B <= 0 || T <= 0) return 0;
   PTB_SOS_DISPATCH(sos_ws_bytes, B, T);   // includes the bound of the single-section passes
@@ -194,6 +352,14 @@ int ptb_sos_cascade_fwd(int dtype, int K, int64_t B, int64_t T, const void* b, c
                         const void* zi, const void* x, void* y, void* mid, void* zf, void* workspace,
                         int64_t workspace_bytes, uint32_t* status, ptb_stream_t stream) {
   if (B <= 0 || T <= 0 || !b || !a || !x || !y) return PTB_ERR_ARG;
+  int sms = 0;
+  const int rcs = device_sms(&sms);
+  if (rcs != PTB_OK) return rcs;
+  if (use_chain(B, sms)) {
+    PTB_SOS_DISPATCH(chain_fwd, B, T, b, a, coef_batched, zi, x, y, mid, zf, workspace, workspace_bytes, status,
+                     (cudaStream_t)stream);
+    return PTB_ERR_ARG;
+  }
   if (mid != nullptr) {
     if (K < 2 || K > 8) return PTB_ERR_ARG;
     if (dtype == PTB_F32)
@@ -216,6 +382,14 @@ int ptb_sos_cascade_bwd(int dtype, int K, int64_t B, int64_t T, const void* b, c
                         void* grad_x, void* grad_b, void* grad_a, void* grad_zi, void* workspace,
                         int64_t workspace_bytes, uint32_t* status, ptb_stream_t stream) {
   if (B <= 0 || T <= 0 || !b || !a || !gy || !grad_x) return PTB_ERR_ARG;
+  int sms = 0;
+  const int rcs = device_sms(&sms);
+  if (rcs != PTB_OK) return rcs;
+  if (use_chain(B, sms)) {
+    PTB_SOS_DISPATCH(chain_bwd, B, T, b, a, coef_batched, x, mid, y, gy, g_zf, grad_x, grad_b, grad_a, grad_zi,
+                     workspace, workspace_bytes, status, (cudaStream_t)stream);
+    return PTB_ERR_ARG;
+  }
   PTB_SOS_DISPATCH(sos_bwd, B, T, b, a, coef_batched, x, mid, y, gy, g_zf, grad_x, grad_b, grad_a, grad_zi, workspace,
                    workspace_bytes, status, (cudaStream_t)stream);
   return PTB_ERR_ARG;

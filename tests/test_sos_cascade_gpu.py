@@ -13,6 +13,15 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
+@pytest.fixture(autouse=True, params=[1, 2], ids=["decoupled", "chained"])
+def kernel_family(request):
+    """Every case runs on both kernel families (normally picked by the batch size)."""
+    from philtorch_b200 import _lib
+    assert _lib.lib.ptb_sos_cascade_set_mode(request.param) == 0
+    yield request.param
+    assert _lib.lib.ptb_sos_cascade_set_mode(0) == 0
+
+
 def _workload(K, B, T, dtype, shared=False, seed=0):
     w = workloads.sos_cascade(B=B, T=T, sections=K, dtype=dtype)
     g = torch.Generator().manual_seed(seed)
