@@ -22,11 +22,22 @@ namespace ptb {
 template <class S, int K> using SosFwdP = SosFwd<S, K, PTB_SOS_FWD_CH, PTB_SOS_FWD_STAGES, PTB_SOS_FWD_NT, PTB_SOS_FWD_CTAS>;
 template <class S, int K> using SosBwdP = SosBwd<S, K, PTB_SOS_BWD_CH, PTB_SOS_BWD_STAGES, PTB_SOS_BWD_NT, PTB_SOS_BWD_CTAS>;
 
-#ifndef PTB_CHAIN_CH
-#define PTB_CHAIN_CH 9
-#define PTB_CHAIN_NT 256
+// chained kernels: (16-byte units per thread, threads, output buffers, CTAs per SM) per direction.
+// Small CTAs, many per SM: inside a CTA the sections run in lock-step (a barrier per section), the
+// overlap of one tile's scan latency with another tile's arithmetic comes from the other CTAs.
+#ifndef PTB_CHAINF_CH
+#define PTB_CHAINF_CH 9
+#define PTB_CHAINF_NT 64
+#define PTB_CHAINF_NOUT 1
+#define PTB_CHAINF_MINB 8
 #endif
-template <class S, int K> using ChainC = ChainCfg<S, K, PTB_CHAIN_CH, PTB_CHAIN_NT>;
+#ifndef PTB_CHAINB_CH
+#define PTB_CHAINB_CH 9
+#define PTB_CHAINB_NT 64
+#define PTB_CHAINB_MINB 5
+#endif
+template <class S, int K> using ChainF = ChainCfg<S, K, PTB_CHAINF_CH, PTB_CHAINF_NT, PTB_CHAINF_NOUT, PTB_CHAINF_MINB>;
+template <class S, int K> using ChainB = ChainCfg<S, K, PTB_CHAINB_CH, PTB_CHAINB_NT, 1, PTB_CHAINB_MINB>;
 
 // 0: pick by batch size, 1: always the decoupled kernels, 2: always the chained kernels
 static int g_sos_mode = 0;
@@ -40,21 +51,24 @@ static int device_sms(int* sms) {
   *sms = cached[dev];
   return PTB_OK;
 }
-// the chained kernels never wait when every resident CTA can work on a row of its own
-static bool use_chain(int64_t B, int sms) { return g_sos_mode == 2 || (g_sos_mode == 0 && B >= sms); }
+// A row keeps at most K tiles busy in the chained kernels (staggered by one section), so they need
+// enough rows to fill the GPU; measured on B200 (K = 6) they win from about 64 rows on.
+static bool use_chain(int64_t B, int sms) { return g_sos_mode == 2 || (g_sos_mode == 0 && 8 * B >= 3 * (int64_t)sms); }
 
 template <class S, int K>
 static int64_t chain_ws_bytes(int64_t B, int64_t T) {
-  using C = ChainC<S, K>;
-  const int64_t ntiles = B * ((T + C::TILE - 1) / C::TILE);
-  return align_up(B * C::ROW * (int64_t)sizeof(S), 256) + ws_layout(ntiles, C::SLOT_WORDS, 5 * K * sizeof(S)).total;
+  using CF = ChainF<S, K>;
+  using CB = ChainB<S, K>;
+  const int64_t nf = B * ((T + CF::TILE - 1) / CF::TILE), nb = B * ((T + CB::TILE - 1) / CB::TILE);
+  return std::max(align_up(B * CF::ROW * (int64_t)sizeof(S), 256) + ws_layout(nf, CF::SLOT_WORDS, 0).total,
+                  align_up(B * CB::ROW * (int64_t)sizeof(S), 256) + ws_layout(nb, CB::SLOT_WORDS, 5 * K * sizeof(S)).total);
 }
 
 template <class S, int K>
 static int chain_fwd(int64_t B, int64_t T, const void* b, const void* a, int coef_batched, const void* zi,
                      const void* x, void* y, void* mid, void* zf, void* ws, int64_t wsb, uint32_t* status,
                      cudaStream_t st) {
-  using C = ChainC<S, K>;
+  using C = ChainF<S, K>;
   using L = ChainFwdSmem<C>;
   static_assert(L::kTotal <= 227 * 1024, "shared memory of an SM");
   const int64_t rows = coef_batched ? B : 1;
@@ -96,7 +110,9 @@ static int chain_fwd(int64_t B, int64_t T, const void* b, const void* a, int coe
     PTB_CUDA(cudaFuncSetAttribute(chain_fwd_kernel<S, C>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
     attr_set[dev] = true;
   }
-  const unsigned grid = (unsigned)std::min<int64_t>(ntiles, sms);
+  int occ = 1;
+  PTB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, chain_fwd_kernel<S, C>, C::NT, L::kTotal));
+  const unsigned grid = (unsigned)std::min<int64_t>(ntiles, (int64_t)sms * std::max(occ, 1));
   chain_fwd_kernel<S, C><<<grid, C::NT, L::kTotal, st>>>(p, wk, (uint32_t)B, (uint32_t)nchunks, (uint32_t)ntiles,
                                                          bulk ? 1 : 0, g_wait_ns);
   PTB_CUDA(cudaGetLastError());
@@ -207,7 +223,7 @@ template <class S, int K>
 static int chain_bwd(int64_t B, int64_t T, const void* b, const void* a, int coef_batched, const void* x,
                      const void* mid, const void* y, const void* gy, const void* g_zf, void* grad_x, void* grad_b,
                      void* grad_a, void* grad_zi, void* ws, int64_t wsb, uint32_t* status, cudaStream_t st) {
-  using C = ChainC<S, K>;
+  using C = ChainB<S, K>;
   using L = ChainBwdSmem<C>;
   static_assert(L::kTotal <= 227 * 1024, "shared memory of an SM");
   const int64_t rows = coef_batched ? B : 1;
@@ -255,7 +271,9 @@ static int chain_bwd(int64_t B, int64_t T, const void* b, const void* a, int coe
     PTB_CUDA(cudaFuncSetAttribute(chain_bwd_kernel<S, C>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
     attr_set[dev] = true;
   }
-  const unsigned grid = (unsigned)std::min<int64_t>(ntiles, sms);
+  int occ = 1;
+  PTB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, chain_bwd_kernel<S, C>, C::NT, L::kTotal));
+  const unsigned grid = (unsigned)std::min<int64_t>(ntiles, (int64_t)sms * std::max(occ, 1));
   chain_bwd_kernel<S, C><<<grid, C::NT, L::kTotal, st>>>(p, wk, (uint32_t)B, (uint32_t)nchunks, (uint32_t)ntiles,
                                                          bulk ? 1 : 0, g_wait_ns);
   PTB_CUDA(cudaGetLastError());

@@ -28,11 +28,14 @@
 
 namespace ptb {
 
-template <class S, int K_, int CH_, int NT_>
+template <class S, int K_, int CH_, int NT_, int NOUT_ = 1, int MINB_ = 2>
 struct ChainCfg {
   static_assert(K_ % 2 == 0, "output buffers alternate per section across tiles");
+  static_assert(NOUT_ == 1 || NOUT_ == 2, "one or two output buffers");
   using Scalar = S;
   static constexpr int K = K_, CH = CH_, NT = NT_, NW = NT_ / 32;
+  static constexpr int NOUT = NOUT_;   // forward: tile buffers for section outputs on their way out
+  static constexpr int MINB = MINB_;   // CTAs per SM the kernels are built for
   static constexpr int V = Vec16<S>::V;
   static constexpr int SPT = V * CH;
   static constexpr int TILE = NT * SPT;
@@ -171,10 +174,10 @@ struct ChainFwdParams {
 
 template <class C>
 struct ChainFwdSmem {
-  static constexpr int kXin = 0;                                   // [2][TILE]  operands of two tiles
-  static constexpr int kRowc = kXin + 2 * C::TILE_BYTES;           // [2][ROWB]  their table rows
-  static constexpr int kOut = kRowc + 2 * C::ROWB;                 // [2][TILE]  section outputs on their way out
-  static constexpr int kBar = kOut + 2 * C::TILE_BYTES;            // u64 full[2]
+  static constexpr int kXin = 0;                                   // [TILE]     samples of the tile being loaded
+  static constexpr int kRowc = kXin + C::TILE_BYTES;               // [2][ROWB]  table rows of this tile and the next
+  static constexpr int kOut = kRowc + 2 * C::ROWB;                 // [NOUT][TILE] section outputs on their way out
+  static constexpr int kBar = kOut + C::NOUT * C::TILE_BYTES;      // u64 full[2]
   static constexpr int kMisc = kBar + 16;                          // u32 ticket[2], ok
   static constexpr int kHin = kMisc + 16;                          // S hin[2][2]
   static constexpr int kWtot = kHin + 4 * 8;                       // S wtot[2][NW][2]
@@ -182,7 +185,7 @@ struct ChainFwdSmem {
 };
 
 template <class S, class C>
-__global__ void __launch_bounds__(C::NT, 1)
+__global__ void __launch_bounds__(C::NT, C::MINB)
 chain_fwd_kernel(const ChainFwdParams<S> p, const Workspace ws, const uint32_t B, const uint32_t nchunks,
                  const uint32_t ntiles, const int bulk, const uint64_t wait_ns) {
   using L = ChainFwdSmem<C>;
@@ -213,7 +216,7 @@ chain_fwd_kernel(const ChainFwdParams<S> p, const Workspace ws, const uint32_t B
     coords(ticket, chunk, row, t0, nvalid);
     const uint32_t bytes = (uint32_t)nvalid * sizeof(S);
     mbar_arrive_expect_tx(&full[s], bytes + C::ROW_BYTES);
-    bulk_g2s(smem + L::kXin + s * C::TILE_BYTES, p.x + (int64_t)row * p.T + t0, bytes, &full[s]);
+    bulk_g2s(smem + L::kXin, p.x + (int64_t)row * p.T + t0, bytes, &full[s]);
     bulk_g2s(smem + L::kRowc + s * C::ROWB, p.tab + (int64_t)row * p.tab_stride, C::ROW_BYTES, &full[s]);
   };
   if (tid == 0) {
@@ -226,19 +229,11 @@ chain_fwd_kernel(const ChainFwdParams<S> p, const Workspace ws, const uint32_t B
   uint32_t failed = 0;
   for (uint32_t n = 0;; ++n) {
     const int s = n & 1;
-    if (tid == 0) {   // the other stage's tile is finished: fetch the tile after this one into it
-      const uint32_t t = failed ? ntiles : atomicAdd(ws.ticket, 1u);
-      sm_ticket[s ^ 1] = t < ntiles ? t : kNoTile;
-      if (t < ntiles && bulk) {
-        fence_proxy_async_smem();
-        issue(s ^ 1, t);
-      }
-    }
     const uint32_t ticket = sm_ticket[s];
     if (ticket == kNoTile) break;
     uint32_t chunk, row; int64_t t0; int nvalid;
     coords(ticket, chunk, row, t0, nvalid);
-    unsigned char* xin = smem + L::kXin + s * C::TILE_BYTES;
+    unsigned char* xin = smem + L::kXin;
     S* rowc = reinterpret_cast<S*>(smem + L::kRowc + s * C::ROWB);
     if (bulk) {
       if (tid == 0) {
@@ -257,7 +252,8 @@ chain_fwd_kernel(const ChainFwdParams<S> p, const Workspace ws, const uint32_t B
     }
     __syncthreads();
     if (*sm_ok == 0u) failed = 1;
-    if (failed) {   // results are invalid from here on: only drain what is in flight
+    if (failed) {   // results are invalid from here on: stop taking work
+      if (tid == 0) sm_ticket[s ^ 1] = kNoTile;
       __syncthreads();
       continue;
     }
@@ -275,6 +271,15 @@ chain_fwd_kernel(const ChainFwdParams<S> p, const Workspace ws, const uint32_t B
 #pragma unroll
         for (int j = 0; j < SPT; ++j)
           if (j >= nv) x[j] = S(0);
+      }
+    }
+    __syncthreads();   // everyone holds its samples: the tile buffer is free
+    if (tid == 0) {    // fetch the tile after this one
+      const uint32_t t = atomicAdd(ws.ticket, 1u);
+      sm_ticket[s ^ 1] = t < ntiles ? t : kNoTile;
+      if (t < ntiles && bulk) {
+        fence_proxy_async_smem();
+        issue(s ^ 1, t);
       }
     }
     const bool owner = p.zf != nullptr && nv > 0 && (t0 + (int64_t)tid * SPT + nv == p.T);
@@ -312,8 +317,9 @@ chain_fwd_kernel(const ChainFwdParams<S> p, const Workspace ws, const uint32_t B
           atomicOr(ws.error, kErrLookbackTimeout);
         }
         hin[0] = h0; hin[1] = h1;
-        // the bulk store that last read the output buffer of this section's parity has finished
-        asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+        // the bulk store that last read this section's output buffer has finished
+        if (C::NOUT == 2) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+        else asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
       }
       __syncthreads();
       S h0, h1;
@@ -346,7 +352,7 @@ chain_fwd_kernel(const ChainFwdParams<S> p, const Workspace ws, const uint32_t B
         p.zf[((int64_t)k * p.B + row) * 2 + 1] = h1;
       }
       const bool store = (k == K - 1) || (p.mid != nullptr);
-      unsigned char* ob = smem + L::kOut + (k & 1) * C::TILE_BYTES;
+      unsigned char* ob = smem + L::kOut + (C::NOUT == 2 ? (k & 1) : 0) * C::TILE_BYTES;
       if (store) {
         unsigned char* po = ob + (size_t)tid * SPT * sizeof(S);
 #pragma unroll
@@ -395,9 +401,9 @@ struct ChainBwdParams {
 
 template <class C>
 struct ChainBwdSmem {
-  static constexpr int kGin = 0;                                   // [2][TILE]  gy in, grad_x out
-  static constexpr int kRowc = kGin + 2 * C::TILE_BYTES;           // [2][ROWB]
-  static constexpr int kZ = kRowc + 2 * C::ROWB;                   // [3][TILE]  ring of section inputs/outputs
+  static constexpr int kGin = 0;                                   // [TILE]     gy of the tile being loaded
+  static constexpr int kRowc = kGin + C::TILE_BYTES;               // [2][ROWB]
+  static constexpr int kZ = kRowc + 2 * C::ROWB;                   // [3][TILE]  ring of section inputs/outputs; grad_x leaves from [2]
   static constexpr int kBar = kZ + 3 * C::TILE_BYTES;              // u64 full[2], zbar[K+1]
   static constexpr int kMisc = kBar + 8 * (2 + C::K + 1);          // u32 ticket[2], ok
   static constexpr int kHin = kMisc + 16;                          // S hin[2][2]
@@ -407,7 +413,7 @@ struct ChainBwdSmem {
 };
 
 template <class S, class C>
-__global__ void __launch_bounds__(C::NT, 1)
+__global__ void __launch_bounds__(C::NT, C::MINB)
 chain_bwd_kernel(const ChainBwdParams<S> p, const Workspace ws, const uint32_t B, const uint32_t nchunks,
                  const uint32_t ntiles, const int bulk, const uint64_t wait_ns) {
   using L = ChainBwdSmem<C>;
@@ -442,7 +448,7 @@ chain_bwd_kernel(const ChainBwdParams<S> p, const Workspace ws, const uint32_t B
     coords(ticket, chunk, row, t0, nvalid);
     const uint32_t bytes = (uint32_t)nvalid * sizeof(S);
     mbar_arrive_expect_tx(&full[s], bytes + C::ROW_BYTES);
-    bulk_g2s(smem + L::kGin + s * C::TILE_BYTES, p.gy + (int64_t)row * p.T + t0, bytes, &full[s]);
+    bulk_g2s(smem + L::kGin, p.gy + (int64_t)row * p.T + t0, bytes, &full[s]);
     bulk_g2s(smem + L::kRowc + s * C::ROWB, p.tab + (int64_t)row * p.tab_stride, C::ROW_BYTES, &full[s]);
   };
   auto zrow = [&](int m, int64_t row) -> const S* {
@@ -462,20 +468,11 @@ chain_bwd_kernel(const ChainBwdParams<S> p, const Workspace ws, const uint32_t B
   for (uint32_t n = 0;; ++n) {
     const int s = n & 1;
     const uint32_t par = n & 1u;   // every Z barrier completes once per tile
-    if (tid == 0) {
-      const uint32_t t = failed ? ntiles : atomicAdd(ws.ticket, 1u);
-      sm_ticket[s ^ 1] = t < ntiles ? t : kNoTile;
-      if (t < ntiles && bulk) {
-        bulk_wait_read_all();   // grad_x of the tile before last has left that stage
-        fence_proxy_async_smem();
-        issue(s ^ 1, t);
-      }
-    }
     const uint32_t ticket = sm_ticket[s];
     if (ticket == kNoTile) break;
     uint32_t chunk, row; int64_t t0; int nvalid;
     coords(ticket, chunk, row, t0, nvalid);
-    unsigned char* gin = smem + L::kGin + s * C::TILE_BYTES;
+    unsigned char* gin = smem + L::kGin;
     S* rowc = reinterpret_cast<S*>(smem + L::kRowc + s * C::ROWB);
     const uint32_t tile_bytes = (uint32_t)nvalid * sizeof(S);
     auto zrequest = [&](int m) {   // one thread: array Z_m of this tile into its ring buffer
@@ -490,6 +487,7 @@ chain_bwd_kernel(const ChainBwdParams<S> p, const Workspace ws, const uint32_t B
     if (bulk) {
       if (tid == 0) {
         if (p.want_coef && !failed) {
+          bulk_wait_read_all();   // grad_x of the previous tile has left ring buffer 2
           fence_proxy_async_smem();
           zrequest(K);
           zrequest(K - 1);
@@ -511,6 +509,7 @@ chain_bwd_kernel(const ChainBwdParams<S> p, const Workspace ws, const uint32_t B
     __syncthreads();
     if (*sm_ok == 0u) failed = 1;
     if (failed) {
+      if (tid == 0) sm_ticket[s ^ 1] = kNoTile;
       __syncthreads();
       continue;
     }
@@ -527,6 +526,15 @@ chain_bwd_kernel(const ChainBwdParams<S> p, const Workspace ws, const uint32_t B
 #pragma unroll
         for (int j = 0; j < SPT; ++j)
           if (j >= nv) g[j] = S(0);
+      }
+    }
+    __syncthreads();   // everyone holds its samples: the tile buffer is free
+    if (tid == 0) {    // fetch the tile after this one
+      const uint32_t t = atomicAdd(ws.ticket, 1u);
+      sm_ticket[s ^ 1] = t < ntiles ? t : kNoTile;
+      if (t < ntiles && bulk) {
+        fence_proxy_async_smem();
+        issue(s ^ 1, t);
       }
     }
     // the gradient entering through the final states is injected by the thread that owns sample T-1
@@ -679,9 +687,15 @@ chain_bwd_kernel(const ChainBwdParams<S> p, const Workspace ws, const uint32_t B
         }
       }
     }
-    // grad_x back into the stage and out
+    // grad_x out through ring buffer 2 (free since section 1; the tile buffer already holds the next tile)
+    unsigned char* gout = smem + L::kZ + 2 * C::TILE_BYTES;
+    if (!p.want_coef && bulk && tid == 0) bulk_wait_read_all();   // (with the sums: waited for before the ring was refilled)
+    if (!p.want_coef) __syncthreads();
+    {
+      unsigned char* po = gout + (size_t)tpos * SPT * sizeof(S);
 #pragma unroll
-    for (int cc = 0; cc < CH; ++cc) VecIO<S, V>::st(pg + 16 * cc, &g[cc * V]);
+      for (int cc = 0; cc < CH; ++cc) VecIO<S, V>::st(po + 16 * cc, &g[cc * V]);
+    }
     if (bulk) fence_proxy_async_smem();
     __syncthreads();
     if (p.want_coef && tid < 5) {   // the sums of section 0
@@ -693,11 +707,11 @@ chain_bwd_kernel(const ChainBwdParams<S> p, const Workspace ws, const uint32_t B
     S* dst = p.grad_x + (int64_t)row * p.T + t0;
     if (bulk) {
       if (tid == 0) {
-        bulk_s2g(dst, gin, tile_bytes);
+        bulk_s2g(dst, gout, tile_bytes);
         bulk_commit();
       }
     } else {
-      const uint32_t* so = reinterpret_cast<const uint32_t*>(gin);
+      const uint32_t* so = reinterpret_cast<const uint32_t*>(gout);
       uint32_t* go = reinterpret_cast<uint32_t*>(dst);
       for (uint32_t w = tid; w < tile_bytes / 4; w += NT) go[w] = so[w];
     }
