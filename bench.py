@@ -359,9 +359,9 @@ def run_sos_cascade(args):
     ptb.check_errors(dev)
     peak, kind = measured_peak()
     n = Bc * Tc
-    # bytes per input sample: forward K passes of 8 B (the section outputs are kept), backward one
-    # pass reading gy, x and the K outputs and writing grad_x
-    alg = (8 * K + 4 * (K + 3)) * n
+    # bytes per input sample: forward one pass reading x and writing the K section outputs (kept for
+    # the backward), backward one pass reading gy, x and the K outputs and writing grad_x
+    alg = (4 * (K + 1) + 4 * (K + 3)) * n
     print(json.dumps({"metric": METRIC, "value": n / (ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": args.steps,
                       "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
                       "vs_baseline": None, "dtype": "f32", "data": "synthetic (seeded, generated on device)",
