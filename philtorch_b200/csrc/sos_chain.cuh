@@ -140,6 +140,20 @@ __device__ __forceinline__ void chain_publish(uint64_t* slot, S h0, S h1) {
   Pod<S, 2> v; v.v[0] = h0; v.v[1] = h1;
   slot_store(slot, v, 2u);
 }
+// one look without waiting; false when they are not there yet
+template <class S>
+__device__ __forceinline__ bool chain_try_fetch(const uint64_t* slot, S& h0, S& h1) {
+  constexpr int W = Words<Pod<S, 2>>::W;
+  uint64_t raw[W];
+#pragma unroll
+  for (int i = 0; i < W; ++i) raw[i] = ld_relaxed_u64(slot + i);
+  bool ok = true;
+  typename Words<Pod<S, 2>>::U u;
+#pragma unroll
+  for (int i = 0; i < W; ++i) { ok = ok && ((uint32_t)(raw[i] >> 32) == 2u); u.w[i] = (uint32_t)raw[i]; }
+  h0 = u.t.v[0]; h1 = u.t.v[1];
+  return ok;
+}
 // waits (bounded) for them; false when the wait ran out
 template <class S>
 __device__ __forceinline__ bool chain_fetch(const uint64_t* slot, S& h0, S& h1, uint64_t wait_ns) {
@@ -181,7 +195,8 @@ struct ChainFwdSmem {
   static constexpr int kMisc = kBar + 16;                          // u32 ticket[2], ok
   static constexpr int kHin = kMisc + 16;                          // S hin[2][2]
   static constexpr int kWtot = kHin + 4 * 8;                       // S wtot[2][NW][2]
-  static constexpr int kTotal = kWtot + 2 * C::NW * 2 * 8 + 16;
+  static constexpr int kPre = kWtot + 2 * C::NW * 2 * 8;           // S pre[K][2], u32 pre_ok[K]: states found at tile start
+  static constexpr int kTotal = kPre + C::K * (2 * 8 + 4) + 16;
 };
 
 template <class S, class C>
@@ -196,6 +211,8 @@ chain_fwd_kernel(const ChainFwdParams<S> p, const Workspace ws, const uint32_t B
   volatile uint32_t* sm_ok = sm_ticket + 2;
   S* sm_hin = reinterpret_cast<S*>(smem + L::kHin);
   S* sm_wtot = reinterpret_cast<S*>(smem + L::kWtot);
+  S* sm_pre = reinterpret_cast<S*>(smem + L::kPre);
+  volatile uint32_t* sm_pre_ok = reinterpret_cast<volatile uint32_t*>(smem + L::kPre + C::K * 2 * 8);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
   if (tid == 0) {
@@ -273,6 +290,16 @@ chain_fwd_kernel(const ChainFwdParams<S> p, const Workspace ws, const uint32_t B
           if (j >= nv) x[j] = S(0);
       }
     }
+    const uint64_t* pred = ws.slots + ((size_t)ticket - B) * C::SLOT_WORDS;   // read only when chunk > 0
+    // The predecessor has normally finished: one look at all its K records now (K lanes, one round
+    // trip) instead of a round trip per section later; what is missing is waited for section by section.
+    if (tid < K) {
+      S q0 = S(0), q1 = S(0);
+      const bool ok = chunk > 0 && chain_try_fetch<S>(pred + tid * (C::SLOT_WORDS / K), q0, q1);
+      sm_pre[2 * tid] = q0;
+      sm_pre[2 * tid + 1] = q1;
+      sm_pre_ok[tid] = ok ? 1u : 0u;
+    }
     __syncthreads();   // everyone holds its samples: the tile buffer is free
     if (tid == 0) {    // fetch the tile after this one
       const uint32_t t = atomicAdd(ws.ticket, 1u);
@@ -284,7 +311,6 @@ chain_fwd_kernel(const ChainFwdParams<S> p, const Workspace ws, const uint32_t B
     }
     const bool owner = p.zf != nullptr && nv > 0 && (t0 + (int64_t)tid * SPT + nv == p.T);
     const bool full_tile = nvalid == TILE;
-    const uint64_t* pred = ws.slots + ((size_t)ticket - B) * C::SLOT_WORDS;   // read only when chunk > 0
     uint64_t* mine_slot = ws.slots + (size_t)ticket * C::SLOT_WORDS;
 
 #pragma unroll 1
@@ -313,6 +339,9 @@ chain_fwd_kernel(const ChainFwdParams<S> p, const Workspace ws, const uint32_t B
             h0 = __ldg(p.zi + ((int64_t)k * p.B + row) * 2);
             h1 = __ldg(p.zi + ((int64_t)k * p.B + row) * 2 + 1);
           }
+        } else if (sm_pre_ok[k]) {
+          h0 = sm_pre[2 * k];
+          h1 = sm_pre[2 * k + 1];
         } else if (!chain_fetch<S>(pred + k * (C::SLOT_WORDS / K), h0, h1, wait_ns)) {
           atomicOr(ws.error, kErrLookbackTimeout);
         }
@@ -409,7 +438,8 @@ struct ChainBwdSmem {
   static constexpr int kHin = kMisc + 16;                          // S hin[2][2]
   static constexpr int kWtot = kHin + 4 * 8;                       // S wtot[2][NW][2]
   static constexpr int kPsum = kWtot + 2 * C::NW * 2 * 8;          // S psum[2][NW][5]
-  static constexpr int kTotal = kPsum + 2 * C::NW * 5 * 8 + 16;
+  static constexpr int kPre = kPsum + 2 * C::NW * 5 * 8;           // S pre[K][2], u32 pre_ok[K]: states found at tile start
+  static constexpr int kTotal = kPre + C::K * (2 * 8 + 4) + 16;
 };
 
 template <class S, class C>
@@ -426,6 +456,8 @@ chain_bwd_kernel(const ChainBwdParams<S> p, const Workspace ws, const uint32_t B
   S* sm_hin = reinterpret_cast<S*>(smem + L::kHin);
   S* sm_wtot = reinterpret_cast<S*>(smem + L::kWtot);
   S* sm_psum = reinterpret_cast<S*>(smem + L::kPsum);
+  S* sm_pre = reinterpret_cast<S*>(smem + L::kPre);
+  volatile uint32_t* sm_pre_ok = reinterpret_cast<volatile uint32_t*>(smem + L::kPre + C::K * 2 * 8);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int tpos = NT - 1 - tid;   // time runs against the scan order
 
@@ -528,6 +560,14 @@ chain_bwd_kernel(const ChainBwdParams<S> p, const Workspace ws, const uint32_t B
           if (j >= nv) g[j] = S(0);
       }
     }
+    const uint64_t* pred = ws.slots + ((size_t)ticket - B) * C::SLOT_WORDS;
+    if (tid < K) {   // one early look at all K records of the predecessor (see the forward kernel)
+      S q0 = S(0), q1 = S(0);
+      const bool ok = chunk > 0 && chain_try_fetch<S>(pred + tid * (C::SLOT_WORDS / K), q0, q1);
+      sm_pre[2 * tid] = q0;
+      sm_pre[2 * tid + 1] = q1;
+      sm_pre_ok[tid] = ok ? 1u : 0u;
+    }
     __syncthreads();   // everyone holds its samples: the tile buffer is free
     if (tid == 0) {    // fetch the tile after this one
       const uint32_t t = atomicAdd(ws.ticket, 1u);
@@ -540,7 +580,6 @@ chain_bwd_kernel(const ChainBwdParams<S> p, const Workspace ws, const uint32_t B
     // the gradient entering through the final states is injected by the thread that owns sample T-1
     const bool owner = p.g_in != nullptr && nv > 0 && (t0 + (int64_t)tpos * SPT + nv == p.T);
     const bool full_tile = nvalid == TILE;
-    const uint64_t* pred = ws.slots + ((size_t)ticket - B) * C::SLOT_WORDS;
     uint64_t* mine_slot = ws.slots + (size_t)ticket * C::SLOT_WORDS;
     S* part = static_cast<S*>(ws.partial) + ((size_t)row * nchunks + chunk) * (5 * K);
 
@@ -582,8 +621,14 @@ chain_bwd_kernel(const ChainBwdParams<S> p, const Workspace ws, const uint32_t B
       if (lane == 31) { wt[2 * warp] = a0; wt[2 * warp + 1] = a1; }
       if (tid == 0) {
         S h0 = S(0), h1 = S(0);
-        if (chunk > 0 && !chain_fetch<S>(pred + k * (C::SLOT_WORDS / K), h0, h1, wait_ns))
-          atomicOr(ws.error, kErrLookbackTimeout);
+        if (chunk > 0) {
+          if (sm_pre_ok[k]) {
+            h0 = sm_pre[2 * k];
+            h1 = sm_pre[2 * k + 1];
+          } else if (!chain_fetch<S>(pred + k * (C::SLOT_WORDS / K), h0, h1, wait_ns)) {
+            atomicOr(ws.error, kErrLookbackTimeout);
+          }
+        }
         hin[0] = h0; hin[1] = h1;
         if (p.want_coef && bulk) {
           bool ok = true;
