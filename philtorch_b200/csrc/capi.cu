@@ -5,6 +5,13 @@
 #include "biquad.cuh"
 
 namespace ptb {
+// single section through the chained kernels, defined with the cascade (capi_sos.cu); -1: not applicable
+int biquad_chain_bwd(int dtype, int64_t B, int64_t T, const void* b, const void* a, int coef_batched, const void* x,
+                     const void* y, const void* gy, const void* g_zf, void* grad_x, void* grad_b, void* grad_a,
+                     void* grad_zi, void* ws, int64_t wsb, uint32_t* status, cudaStream_t st);
+}  // namespace ptb
+
+namespace ptb {
 
 // ---------------------------------------------------------------------------- first order
 // Tile geometry: an ODD number of 16-byte units per thread and array (bank-conflict-free strided
@@ -517,6 +524,11 @@ int ptb_biquad_tdf2_bwd(int dtype, int64_t B, int64_t T, const void* b, const vo
   if (B < 0 || T < 0) return PTB_ERR_ARG;
   if (B == 0 || T == 0) return PTB_OK;
   if (!b || !a || !gy || !grad_x || ((grad_b || grad_a) && (!x || !y))) return PTB_ERR_ARG;
+  {   // large batches: the chained kernel of capi_sos.cu (measured faster for the backward pass only)
+    const int rc = biquad_chain_bwd(dtype, B, T, b, a, coef_batched, x, y, gy, g_zf, grad_x, grad_b, grad_a, grad_zi,
+                                    workspace, workspace_bytes, status, (cudaStream_t)stream);
+    if (rc >= 0) return rc;
+  }
   PTB_DISPATCH(dtype, (bq_bwd<S>(B, T, b, a, coef_batched, x, y, gy, g_zf, grad_x, grad_b, grad_a, grad_zi,
                                  workspace, workspace_bytes, status, (cudaStream_t)stream)));
 }

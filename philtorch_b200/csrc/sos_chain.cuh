@@ -30,8 +30,7 @@ namespace ptb {
 
 template <class S, int K_, int CH_, int NT_, int NOUT_ = 1, int MINB_ = 2>
 struct ChainCfg {
-  static_assert(K_ % 2 == 0, "output buffers alternate per section across tiles");
-  static_assert(NOUT_ == 1 || NOUT_ == 2, "one or two output buffers");
+  static_assert(NOUT_ == 1 || (NOUT_ == 2 && K_ % 2 == 0), "two output buffers alternate per section across tiles");
   using Scalar = S;
   static constexpr int K = K_, CH = CH_, NT = NT_, NW = NT_ / 32;
   static constexpr int NOUT = NOUT_;   // forward: tile buffers for section outputs on their way out

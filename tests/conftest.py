@@ -28,7 +28,7 @@ def pytest_collection_modifyitems(config, items):
 def load_golden(name):
     """Golden vectors produced by running the reference (tests/golden/make_golden.py)."""
     with np.load(os.path.join(GOLDEN, name + ".npz")) as z:
-        return {k: torch.from_numpy(np.asarray(z[k])) for k in z.files}
+        return {k: torch.from_numpy(np.asarray(z[k])) for k in z.files if np.asarray(z[k]).dtype.kind in "fiub"}
 
 
 def rel_err(out, ref):

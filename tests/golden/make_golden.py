@@ -69,8 +69,49 @@ def grads(out, gy, *inputs):
     return [_np(g) for g in gs]
 
 
+def lpv_lfilter_cases(pt):
+    """Time-varying filters of order 1 and 2 through philtorch.lpv.lfilter (backend 'ssm', the
+    extension route), forms df2 and tdf2, per-row and shared coefficients."""
+    import math
+    g = torch.Generator().manual_seed(20240611)
+    B, N = 3, 300
+    for dt, tag in ((torch.float64, "f64"), (torch.float32, "f32")):
+        for order in (1, 2):
+            for mode in ("batched", "shared"):
+                lead = (B, N) if mode == "batched" else (N,)
+                r = 0.3 + 0.6 * torch.rand(lead, generator=g, dtype=torch.float64)
+                th = math.pi * torch.rand(lead, generator=g, dtype=torch.float64)
+                if order == 2:
+                    a = torch.stack([-2 * r * torch.cos(th), r * r], -1)
+                else:
+                    a = (-r * torch.cos(th)).unsqueeze(-1)
+                b = torch.randn(lead + (order + 1,), generator=g, dtype=torch.float64)
+                x = torch.randn(B, N, generator=g, dtype=torch.float64)
+                zi = torch.randn(B, order, generator=g, dtype=torch.float64)
+                gy = torch.randn(B, N, generator=g, dtype=torch.float64)
+                b, a, x, zi, gy = (t.to(dt) for t in (b, a, x, zi, gy))
+                out = {}
+                # order 2 goes through the reference's compiled extension (unroll_factor=1); order 1
+                # would go to torchlpc there, so it takes the reference's blocked pure-PyTorch scan
+                uf = 1 if order == 2 else 8
+                for form in ("df2", "tdf2"):
+                    bb, aa, xx, zz = (t.clone().requires_grad_() for t in (b, a, x, zi))
+                    y = pt.lpv.lfilter(bb, aa, xx, form=form, unroll_factor=uf)
+                    gb, ga, gx = grads(y, gy, bb, aa, xx)
+                    y_zi, zf = pt.lpv.lfilter(bb, aa, xx, zi=zz, form=form, unroll_factor=uf)
+                    (gzi,) = grads(y_zi, gy, zz)
+                    out.update({f"y_{form}": _np(y), f"grad_b_{form}": gb, f"grad_a_{form}": ga,
+                                f"grad_x_{form}": gx, f"y_zi_{form}": _np(y_zi), f"zf_{form}": _np(zf),
+                                f"grad_zi_{form}": gzi})
+                save(f"lpv_lfilter_order{order}_{mode}_{tag}", b=_np(b), a=_np(a), x=_np(x), zi=_np(zi),
+                     gy=_np(gy), case=np.array(f"philtorch.lpv.lfilter(backend='ssm', unroll_factor={uf})"), **out)
+
+
 def main():
     pt = import_reference()
+    if len(sys.argv) > 1 and sys.argv[1] == "lpv_lfilter":   # only this group (the others are unchanged)
+        lpv_lfilter_cases(pt)
+        return
     from philtorch.lti.recur import LTIRecurrence
     from philtorch.lti.ssm import LTIMatrixRecurrence
     from philtorch.lpv.ssm import MatrixRecurrence
@@ -244,6 +285,8 @@ def main():
     y = MatrixRecurrence.apply(a[..., None, None], zi[:, None], x[..., None])[..., 0]
     ga, gzi, gx = grads(y, w["gy"], a, zi, x)
     save("config5_small", y=_np(y), grad_a=ga, grad_x=gx, B=2, T=16384)
+
+    lpv_lfilter_cases(pt)
 
 
 if __name__ == "__main__":

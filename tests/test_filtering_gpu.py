@@ -10,6 +10,16 @@ from conftest import load_golden, rel_err, tol
 from oracle import cport
 
 pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True, params=[1, 2], ids=["decoupled", "chained"])
+def kernel_family(request):
+    """Second-order sections run on two kernel families, normally picked by the batch size: every
+    case here runs on both."""
+    from philtorch_b200 import _lib
+    assert _lib.lib.ptb_sos_cascade_set_mode(request.param) == 0
+    yield request.param
+    assert _lib.lib.ptb_sos_cascade_set_mode(0) == 0
 DEV = "cuda"
 DT = {"f32": torch.float32, "f64": torch.float64}
 
