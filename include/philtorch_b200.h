@@ -230,6 +230,25 @@ int ptb_sos_cascade_bwd(int dtype, int K, int64_t B, int64_t T, const void* b, c
                         void* grad_x, void* grad_b, void* grad_a, void* grad_zi, void* workspace,
                         int64_t workspace_bytes, uint32_t* status, ptb_stream_t stream);
 
+/* ---- time-varying second-order filter, direct form II, fused -------------------------------------
+ * philtorch.lpv.lfilter(b, a, x, zi, form="df2") for orders <= 2 (philtorch/lpv/filtering.py:288-313,
+ * philtorch/lpv/ssm.py:413-500) in one pass per direction.
+ *   b, a     per-sample coefficients (B,T,3), (B,T,2) when coef_batched, else (T,3), (T,2); a0 = 1
+ *   zi / zf  optional (B,2);  x, y (B,T)
+ *   hp       optional (B,T,2): the state before every sample, which the backward pass needs
+ * Backward: gy (B,T), g_zf optional (B,2) -> grad_x (B,T), grad_b (B,T,3) and grad_a (B,T,2) PER
+ * ROW (a caller with shared coefficients sums them over the rows), grad_zi optional (B,2).
+ * Chained scan (a tile takes over the end state of the row's previous tile): meant for batches of
+ * at least a few dozen rows.  Workspace: ptb_lpv_biquad_workspace_bytes. */
+int64_t ptb_lpv_biquad_workspace_bytes(int dtype, int64_t B, int64_t T);
+int ptb_lpv_biquad_df2_fwd(int dtype, int64_t B, int64_t T, const void* b, const void* a, int coef_batched,
+                           const void* zi, const void* x, void* y, void* hp, void* zf, void* workspace,
+                           int64_t workspace_bytes, uint32_t* status, ptb_stream_t stream);
+int ptb_lpv_biquad_df2_bwd(int dtype, int64_t B, int64_t T, const void* b, const void* a, int coef_batched,
+                           const void* x, const void* hp, const void* gy, const void* g_zf, void* grad_x,
+                           void* grad_b, void* grad_a, void* grad_zi, void* workspace, int64_t workspace_bytes,
+                           uint32_t* status, ptb_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

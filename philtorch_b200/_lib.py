@@ -77,6 +77,13 @@ lib.ptb_sos_cascade_fwd.restype = _i32
 lib.ptb_sos_cascade_bwd.argtypes = [_i32, _i32, _i64, _i64, _vp, _vp, _i32] + [_vp] * 9 + _tail
 lib.ptb_sos_cascade_bwd.restype = _i32
 
+lib.ptb_lpv_biquad_workspace_bytes.argtypes = [_i32, _i64, _i64]
+lib.ptb_lpv_biquad_workspace_bytes.restype = _i64
+lib.ptb_lpv_biquad_df2_fwd.argtypes = [_i32, _i64, _i64, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp] + _tail
+lib.ptb_lpv_biquad_df2_fwd.restype = _i32
+lib.ptb_lpv_biquad_df2_bwd.argtypes = [_i32, _i64, _i64, _vp, _vp, _i32] + [_vp] * 8 + _tail
+lib.ptb_lpv_biquad_df2_bwd.restype = _i32
+
 _status: dict[int, torch.Tensor] = {}
 
 ERROR_BITS = {1: "look-back wait expired", 2: "tile load wait expired", 4: "tile drain wait expired",

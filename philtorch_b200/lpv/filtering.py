@@ -15,7 +15,13 @@ import torch
 import torch.nn.functional as F
 from torch import Tensor
 
+from ..autograd import LPVBiquadDF2
 from .ssm import state_space_recursion
+
+# From this many rows on, form 'df2' runs on the fused chained kernels (one pass per direction, first
+# derivatives only); below it, and for 'tdf2', on the decoupled 2x2 scan kernels with elementwise
+# passes around them (differentiable to any order).  Set to a huge value to switch the fused path off.
+FUSED_MIN_ROWS = 32
 
 __all__ = ["lfilter"]
 
@@ -50,6 +56,9 @@ def _ssm_lfilter(b: Tensor, a: Tensor, x: Tensor, zi: Optional[Tensor], form: st
     b0 = b[..., :1]
     Bv = b[..., 1:] - b0 * a          # (.., N, 2): C of the df2 form, B of the tdf2 form
     D = b[..., 0]
+    if form == "df2" and B >= FUSED_MIN_ROWS:
+        y, zf = LPVBiquadDF2.apply(b, a, zi2 if return_zf else None, x)
+        return (y, zf[:, :order]) if return_zf else y
     if form == "df2":
         # h_t = companion(a_t) h_{t-1} + [x_t, 0];  y_t = C_t . h_{t-1} + D_t x_t
         A = torch.stack([torch.stack([-a1, -a2], -1), torch.stack([one, zero], -1)], -2)

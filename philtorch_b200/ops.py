@@ -470,6 +470,85 @@ def _(b, a, x, mid, y, gy, gzf, need_coef, need_zi):
             torch.empty_like(x, memory_format=torch.contiguous_format))
 
 
+# =============================================================================== fused LPV biquad (df2)
+_LIB.define("lpv_biquad_df2(Tensor b, Tensor a, Tensor? zi, Tensor x, bool keep_states) -> (Tensor, Tensor, Tensor)",
+            tags=_TAGS)
+_LIB.define("lpv_biquad_df2_bwd(Tensor b, Tensor a, Tensor x, Tensor hp, Tensor gy, Tensor? gzf, bool need_zi) "
+            "-> (Tensor, Tensor, Tensor, Tensor)", tags=_TAGS)
+
+
+def _check_lpv_biquad(b: Tensor, a: Tensor, zi: Optional[Tensor], x: Tensor) -> None:
+    torch._check(x.dim() == 2, lambda: "x must be 2D (batch, time).")
+    torch._check(b.dim() in (2, 3) and b.shape[-1] == 3 and b.shape[-2] == x.shape[1],
+                 lambda: "b must be (N,3) or (B,N,3).")
+    torch._check(a.dim() == b.dim() and a.shape[-1] == 2 and a.shape[-2] == x.shape[1],
+                 lambda: "a must be (N,2) or (B,N,2), like b.")
+    if b.dim() == 3:
+        torch._check(b.shape[0] == x.shape[0] and a.shape[0] == x.shape[0],
+                     lambda: "batched coefficients must match x's batch size.")
+    if zi is not None:
+        torch._check(zi.dim() == 2 and zi.shape[0] == x.shape[0] and zi.shape[1] == 2, lambda: "zi must be (B,2).")
+
+
+def _lpv_biquad_df2(b, a, zi, x, keep_states):
+    _check_lpv_biquad(b, a, zi, x)
+    dev = _lib.require_cuda(b, a, zi, x)
+    if b.dtype != x.dtype or a.dtype != x.dtype or (zi is not None and zi.dtype != x.dtype):
+        raise RuntimeError("b, a and zi must have the same scalar type as input")
+    B, T = x.shape
+    b_c, a_c, zi_c, x_c = b.contiguous(), a.contiguous(), _opt(zi), x.contiguous()
+    y = torch.empty_like(x_c)
+    hp = x.new_empty((B, T, 2) if keep_states else (0,))
+    zf = x.new_empty(B, 2)
+    if B and T:
+        code = _lib.dtype_code(x)
+        _lib.call(lib.ptb_lpv_biquad_df2_fwd, dev, B, T, code, B, T, ptr(b_c), ptr(a_c), int(b.dim() == 3), ptr(zi_c),
+                  ptr(x_c), ptr(y), ptr(hp) if keep_states else None, ptr(zf),
+                  ws_bytes=lib.ptb_lpv_biquad_workspace_bytes(code, B, T))
+    elif B:
+        zf.copy_(zi_c) if zi_c is not None else zf.zero_()
+    return y, hp, zf
+
+
+def _lpv_biquad_df2_bwd(b, a, x, hp, gy, gzf, need_zi):
+    dev = _lib.require_cuda(b, a, x, hp, gy, gzf)
+    B, T = x.shape
+    b_c, a_c, x_c, hp_c, gy_c, gzf_c = b.contiguous(), a.contiguous(), x.contiguous(), hp.contiguous(), \
+        gy.contiguous(), _opt(gzf)
+    if hp.numel() != B * T * 2:
+        raise RuntimeError("the backward pass needs the states kept by the forward pass (keep_states=True)")
+    gx = torch.empty_like(x_c)
+    gb = x.new_empty(B, T, 3)
+    ga = x.new_empty(B, T, 2)
+    gzi = x.new_empty(B, 2) if need_zi else x.new_empty(0)
+    if B and T:
+        code = _lib.dtype_code(x)
+        _lib.call(lib.ptb_lpv_biquad_df2_bwd, dev, B, T, code, B, T, ptr(b_c), ptr(a_c), int(b.dim() == 3), ptr(x_c),
+                  ptr(hp_c), ptr(gy_c), ptr(gzf_c), ptr(gx), ptr(gb), ptr(ga), ptr(gzi) if need_zi else None,
+                  ws_bytes=lib.ptb_lpv_biquad_workspace_bytes(code, B, T))
+    elif need_zi:
+        gzi.copy_(gzf_c) if gzf_c is not None else gzi.zero_()
+    return gb, ga, gzi, gx
+
+
+_LIB.impl("lpv_biquad_df2", _lpv_biquad_df2, "CUDA")
+_LIB.impl("lpv_biquad_df2_bwd", _lpv_biquad_df2_bwd, "CUDA")
+
+
+@torch.library.register_fake("philtorch_b200::lpv_biquad_df2")
+def _(b, a, zi, x, keep_states):
+    _check_lpv_biquad(b, a, zi, x)
+    return (torch.empty_like(x, memory_format=torch.contiguous_format),
+            x.new_empty((x.shape[0], x.shape[1], 2) if keep_states else (0,)), x.new_empty(x.shape[0], 2))
+
+
+@torch.library.register_fake("philtorch_b200::lpv_biquad_df2_bwd")
+def _(b, a, x, hp, gy, gzf, need_zi):
+    return (x.new_empty(x.shape[0], x.shape[1], 3), x.new_empty(x.shape[0], x.shape[1], 2),
+            x.new_empty(x.shape[0], 2) if need_zi else x.new_empty(0),
+            torch.empty_like(x, memory_format=torch.contiguous_format))
+
+
 # CPU (and any other backend) tensors: fail loudly instead of "no kernel registered" noise.
 def _no_backend(name):
     def fn(*args, **kwargs):
@@ -479,5 +558,5 @@ def _no_backend(name):
 
 for _name in ("lti_recur", "lti_recur_bwd", "lpv_recur", "lpv_recur_bwd", "lti_recur2", "lti_recur2_sx", "recur2",
               "recur2_sx", "lti_recur2_bwd", "recur2_bwd", "biquad_tdf2", "biquad_tdf2_bwd", "lpv_recur_carry", "lpv_recur_zero_carry",
-              "sos_cascade", "sos_cascade_bwd"):
+              "sos_cascade", "sos_cascade_bwd", "lpv_biquad_df2", "lpv_biquad_df2_bwd"):
     _LIB.impl(_name, _no_backend(_name), "CPU")

@@ -10,6 +10,14 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
+@pytest.fixture(autouse=True, params=[10**9, 1], ids=["scan+glue", "fused"])
+def df2_path(request, monkeypatch):
+    """Form 'df2' has two implementations, normally picked by the batch size: every case runs on both."""
+    from philtorch_b200.lpv import filtering
+    monkeypatch.setattr(filtering, "FUSED_MIN_ROWS", request.param)
+    return request.param
+
+
 @pytest.mark.parametrize("tag", ["f32", "f64"])
 @pytest.mark.parametrize("mode", ["batched", "shared"])
 @pytest.mark.parametrize("order", [1, 2])
@@ -49,3 +57,33 @@ def test_one_dimensional_call_and_errors():
         ptb.lpv.lfilter(b, a, x, form="nope")
     with pytest.raises(RuntimeError):
         ptb.lpv.lfilter(b.cpu(), a.cpu(), x.cpu())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+@pytest.mark.parametrize("B,T,shared", [(40, 5000, False), (33, 961, False), (64, 20003, False), (48, 7000, True),
+                                        (130, 12000, False)])
+def test_fused_df2_matches_scan_path(dtype, B, T, shared, monkeypatch):
+    """The fused kernels against the 2x2 scan kernels plus elementwise maps (pinned above to the
+    reference) on batches, lengths (ragged, unaligned) and coefficient layouts the golden files lack."""
+    from philtorch_b200.lpv import filtering
+    g = torch.Generator().manual_seed(B * 7 + T)
+    lead = (T,) if shared else (B, T)
+    r = 0.3 + 0.65 * torch.rand(lead, generator=g, dtype=torch.float64)
+    th = 3.14159 * torch.rand(lead, generator=g, dtype=torch.float64)
+    a = torch.stack([-2 * r * torch.cos(th), r * r], -1).to(dtype)
+    b = torch.randn(lead + (3,), generator=g, dtype=torch.float64).to(dtype)
+    x = torch.randn(B, T, generator=g, dtype=torch.float64).to(dtype)
+    zi = torch.randn(B, 2, generator=g, dtype=torch.float64).to(dtype)
+    gy = torch.randn(B, T, generator=g, dtype=torch.float64).to(dtype)
+    gzf = torch.randn(B, 2, generator=g, dtype=torch.float64).to(dtype)
+    outs = []
+    for min_rows in (1, 10**9):
+        monkeypatch.setattr(filtering, "FUSED_MIN_ROWS", min_rows)
+        ins = [t.to(DEV).requires_grad_() for t in (b, a, x, zi)]
+        y, zf = ptb.lpv.lfilter(ins[0], ins[1], ins[2], zi=ins[3])
+        outs.append((y, zf) + torch.autograd.grad([y, zf], ins, [gy.to(DEV), gzf.to(DEV)]))
+    t = tol(dtype)
+    for got, ref, name in zip(outs[0], outs[1], ("y", "zf", "grad_b", "grad_a", "grad_x", "grad_zi")):
+        # shared coefficients: the gradient sums over the rows, in another order
+        assert rel_err(got, ref) <= (10 * t if shared and name in ("grad_b", "grad_a") else t), name
+    ptb.check_errors()
