@@ -12,18 +12,26 @@
 //     grad_b0 = gy x - a . grad_C,  grad_b[1:] = grad_C
 // all per sample, so nothing is reduced.
 //
-// Chained scan for large batches, as in sos_chain.cuh: a CTA takes one tile of one row, needs the
-// END STATE of the row's previous tile ({flag, payload} record, bounded wait) and publishes its
-// own; tiles are handed out chunk-major so the predecessor has normally finished long before.
-// Inside a tile: every thread folds its SPT samples into a 2x2 affine map (phase A), the maps are
-// scanned over the lanes and warps, every thread replays its samples from its true state (phase B).
+// Single-pass scan with decoupled look-back in small CTAs: a CTA takes one tile of one row
+// (chunk-major tickets, as in scan_engine.cuh); every thread folds its SPT samples into a 2x2 affine
+// map (phase A), the maps are scanned over the lanes and warps, warp 0 publishes the tile's
+// aggregate and looks back over the row's earlier tiles (scan_engine.cuh's lookback: aggregates
+// until an end state is met, bounded waits), publishes the tile's end state, and every thread
+// replays its samples from its true state (phase B).
 // SPT is odd: per-thread strides of 2 SPT, 3 SPT and SPT words make the 8-byte / 4-byte shared
 // memory accesses conflict-free.  Small CTAs, several per SM, overlap one tile's scan latency with
 // another tile's arithmetic.
 #pragma once
 #include "sos_chain.cuh"
+#include "second_order.cuh"
 
 namespace ptb {
+
+// the look-back's view of the maps: second_order.cuh's 2x2 affine algebra
+template <class S>
+struct LpvLb : MatAffine<S> {
+  static constexpr int SLOT_WORDS = Words<typename MatAffine<S>::Map>::W;
+};
 
 template <class S, int SPT_, int NT_, int MINB_>
 struct LpvBqCfg {
@@ -31,7 +39,7 @@ struct LpvBqCfg {
   static constexpr int SPT = SPT_, NT = NT_, NW = NT_ / 32, MINB = MINB_;
   static constexpr int TILE = NT * SPT;
   static constexpr int XB = TILE * (int)sizeof(S);   // bytes of a tile of a scalar array
-  static constexpr int SLOT_WORDS = 2 * (int)(sizeof(S) / 4);
+  static constexpr int SLOT_WORDS = LpvLb<S>::SLOT_WORDS;
   static_assert(XB % 16 == 0, "bulk copies move multiples of 16 bytes");
 };
 
@@ -57,6 +65,34 @@ __device__ __forceinline__ void affine_warp_scan(S* m, int lane) {
     for (int i = 0; i < 6; ++i) o[i] = __shfl_up_sync(0xffffffffu, m[i], d);
     if (lane >= d) affine_compose<S>(o, m, m);
   }
+}
+
+// Warp 0, after the warps' totals are in shared memory: tile aggregate, look-back, end state.
+// Returns (in every lane) the state entering the tile; zi: the row's initial state (chunk 0).
+template <class S, int NW>
+__device__ __forceinline__ typename LpvLb<S>::State lpv_tile_state(const Workspace& ws, const S* wtot, uint32_t ticket,
+                                                                   uint32_t chunk, uint32_t nchunks, uint32_t B,
+                                                                   int lane, S zi0, S zi1, uint64_t wait_ns) {
+  using P = LpvLb<S>;
+  typename P::Map agg = P::identity();
+#pragma unroll
+  for (int w = 0; w < NW; ++w) {
+    typename P::Map t;
+#pragma unroll
+    for (int i = 0; i < 6; ++i) t.v[i] = wtot[w * 6 + i];
+    agg = P::compose(agg, t);
+  }
+  uint64_t* slot = ws.slots + (size_t)ticket * P::SLOT_WORDS;
+  typename P::State hin;
+  if (chunk == 0) {
+    hin.v[0] = zi0; hin.v[1] = zi1;
+  } else {
+    if (lane == 0 && chunk + 1 < nchunks) slot_store(slot, agg, 1u);
+    uint32_t failed = 0;
+    hin = lookback<P>(0, ws, ticket, chunk, B, lane, failed, 8, wait_ns);
+  }
+  if (lane == 0 && chunk + 1 < nchunks) slot_store(slot, P::apply(agg, hin), 2u);
+  return hin;
 }
 
 // ------------------------------------------------------------------------------------ forward
@@ -211,15 +247,14 @@ lpv_bq_fwd_kernel(const LpvBqFwdParams<S> p, const Workspace ws, const uint32_t 
 #pragma unroll
       for (int i = 0; i < 6; ++i) sm_wtot[warp * 6 + i] = m[i];
     }
-    if (tid == 0) {
-      S h0 = S(0), h1 = S(0);
-      if (chunk == 0) {
-        if (p.zi) { h0 = __ldg(p.zi + (int64_t)row * 2); h1 = __ldg(p.zi + (int64_t)row * 2 + 1); }
-      } else if (!chain_fetch<S>(ws.slots + ((size_t)ticket - B) * C::SLOT_WORDS, h0, h1, wait_ns)) {
-        atomicOr(ws.error, kErrLookbackTimeout);
-      }
-      sm_hin[0] = h0; sm_hin[1] = h1;
-      asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the previous tile's outputs have left
+    if (tid == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the previous tile's outputs have left
+    __syncthreads();
+    if (warp == 0) {
+      S z0 = S(0), z1 = S(0);
+      if (chunk == 0 && p.zi) { z0 = __ldg(p.zi + (int64_t)row * 2); z1 = __ldg(p.zi + (int64_t)row * 2 + 1); }
+      const typename LpvLb<S>::State hin =
+          lpv_tile_state<S, C::NW>(ws, sm_wtot, ticket, chunk, nchunks, B, lane, z0, z1, wait_ns);
+      if (lane == 0) { sm_hin[0] = hin.v[0]; sm_hin[1] = hin.v[1]; }
     }
     __syncthreads();
     // state entering my warp, then my thread
@@ -248,7 +283,6 @@ lpv_bq_fwd_kernel(const LpvBqFwdParams<S> p, const Workspace ws, const uint32_t 
         }
       }
     }
-    if (tid == NT - 1 && chunk + 1 < nchunks) chain_publish<S>(ws.slots + (size_t)ticket * C::SLOT_WORDS, h0, h1);
     if (p.zf != nullptr && nv > 0 && (t0 + (int64_t)tid * SPT + nv == p.T)) {
       p.zf[(int64_t)row * 2] = h0;
       p.zf[(int64_t)row * 2 + 1] = h1;
@@ -416,11 +450,11 @@ lpv_bq_bwd_kernel(const LpvBqBwdParams<S> p, const Workspace ws, const uint32_t 
 #pragma unroll
       for (int i = 0; i < 6; ++i) sm_wtot[warp * 6 + i] = m[i];
     }
-    if (tid == 0) {
-      S h0 = S(0), h1 = S(0);
-      if (chunk > 0 && !chain_fetch<S>(ws.slots + ((size_t)ticket - B) * C::SLOT_WORDS, h0, h1, wait_ns))
-        atomicOr(ws.error, kErrLookbackTimeout);
-      sm_hin[0] = h0; sm_hin[1] = h1;
+    __syncthreads();
+    if (warp == 0) {
+      const typename LpvLb<S>::State hin =
+          lpv_tile_state<S, C::NW>(ws, sm_wtot, ticket, chunk, nchunks, B, lane, S(0), S(0), wait_ns);
+      if (lane == 0) { sm_hin[0] = hin.v[0]; sm_hin[1] = hin.v[1]; }
     }
     __syncthreads();
     S l0 = sm_hin[0], l1 = sm_hin[1];
@@ -454,9 +488,9 @@ lpv_bq_bwd_kernel(const LpvBqBwdParams<S> p, const Workspace ws, const uint32_t 
         l0 = n0; l1 = n1;
       }
     }
-    if (tid == NT - 1) {
-      if (chunk + 1 < nchunks) chain_publish<S>(ws.slots + (size_t)ticket * C::SLOT_WORDS, l0, l1);
-      else if (p.grad_zi) { p.grad_zi[(int64_t)row * 2] = l0; p.grad_zi[(int64_t)row * 2 + 1] = l1; }
+    if (tid == NT - 1 && chunk + 1 == nchunks && p.grad_zi) {
+      p.grad_zi[(int64_t)row * 2] = l0;
+      p.grad_zi[(int64_t)row * 2 + 1] = l1;
     }
     S* ox = p.grad_x + off;
     S* oa = p.grad_a + 2 * off;
