@@ -56,6 +56,9 @@ int ptb_read_status(const uint32_t* status, ptb_stream_t stream, uint32_t* host_
  * is bounded in time; when a bound expires the kernel sets a bit in `status`, finishes its copies
  * and runs to completion, so the context stays usable.  The bound is 2000 ms by default. */
 int ptb_set_wait_limit_ms(int64_t ms);
+/* ptb_lpv_recur2_fwd runs on one of two kernels: small CTAs (several per SM) from this many rows on,
+ * else one large CTA per SM.  Default 48; process-wide; meant for tests and tuning. */
+int ptb_lpv_recur2_set_small_cta_min_rows(int64_t rows);
 /* Self-test of that path without faulting anything: runs the first-order forward kernel on two
  * tiles of which the FIRST IS NEVER PROCESSED, so the second one's look-back waits for a record
  * that nothing writes, gives up after the wait limit and reports kErrLookbackTimeout (bit 0) in

@@ -62,6 +62,8 @@ lib.ptb_lpv_recur_carry.restype = _i32
 lib.ptb_lpv_recur_fwd_carry.argtypes = [_i32, _i64, _i64, _vp, _i32, _vp, _vp, _vp] + _tail
 lib.ptb_lpv_recur_fwd_carry.restype = _i32
 
+lib.ptb_lpv_recur2_set_small_cta_min_rows.argtypes = [_i64]
+lib.ptb_lpv_recur2_set_small_cta_min_rows.restype = _i32
 lib.ptb_set_wait_limit_ms.argtypes = [_i64]
 lib.ptb_set_wait_limit_ms.restype = _i32
 lib.ptb_selftest_wait_expiry_elems.restype = _i64

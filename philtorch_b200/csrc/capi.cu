@@ -3,6 +3,7 @@
 #include "launch.cuh"
 
 #include "biquad.cuh"
+#include "so_small.cuh"
 
 namespace ptb {
 // single section through the chained kernels, defined with the cascade (capi_sos.cu); -1: not applicable
@@ -150,9 +151,74 @@ using SoFwdP = SoFwd<S, SoCfg<S>::FWD_NS, SoCfg<S>::FWD_ST, PTB_SO_CTAS, PTB_SO_
 template <class S, bool LPV, bool XS>
 using SoBwdP = SoBwd<S, SoCfg<S>::BWD_NS, SoCfg<S>::BWD_ST, PTB_SO_CTAS, PTB_SO_NT, LPV, XS>;
 
+// 2x2 LPV forward in small CTAs (so_small.cuh): from this many rows on
+#ifndef PTB_SO_SMALL_MIN_ROWS
+#define PTB_SO_SMALL_MIN_ROWS 48
+#endif
+template <class S> struct SoSmallSel;
+#ifndef PTB_SO_SMALL_NT
+#define PTB_SO_SMALL_NT 128
+#define PTB_SO_SMALL_MINB 4
+#define PTB_SO_SMALL_MINB64 3
+#endif
+template <> struct SoSmallSel<float> { using C = LpvBqCfg<float, 15, PTB_SO_SMALL_NT, PTB_SO_SMALL_MINB>; };
+template <> struct SoSmallSel<double> { using C = LpvBqCfg<double, 9, PTB_SO_SMALL_NT, PTB_SO_SMALL_MINB64>; };
+
+template <class S, bool XS>
+static int so_small_fwd(int64_t B, int64_t T, const void* A, int A_batched, const void* zi, const void* x, void* y,
+                        void* zf, void* ws, int64_t wsb, uint32_t* status, cudaStream_t st) {
+  using C = typename SoSmallSel<S>::C;
+  using L = SoSmallFwdSmem<C, XS>;
+  static_assert(C::TILE >= kMinTile && C::SLOT_WORDS * 8 <= kTileRecordBytes, "generic workspace bound");
+  const int64_t nchunks = (T + C::TILE - 1) / C::TILE;
+  const int64_t ntiles = B * nchunks;
+  if (ntiles >= 0xFFFFFFFEll || B >= 0xFFFFFFFFll) return PTB_ERR_TOO_LARGE;
+  const WsLayout l = ws_layout(ntiles, C::SLOT_WORDS, 0);
+  if (!ws || (reinterpret_cast<uintptr_t>(ws) & 255u) || wsb < l.total) return PTB_ERR_WORKSPACE;
+  char* w = static_cast<char*>(ws);
+  PTB_CUDA(cudaMemsetAsync(w, 0, (size_t)l.part_off, st));
+  Workspace wk;
+  wk.ticket = reinterpret_cast<uint32_t*>(w);
+  wk.error = status ? status : reinterpret_cast<uint32_t*>(w + 4);
+  wk.slots = reinterpret_cast<uint64_t*>(w + l.slots_off);
+  wk.partial = nullptr;
+  SoSmallFwdParams<S> p;
+  p.A = static_cast<const S*>(A);
+  p.a_row = A_batched ? 4 * T : 0;
+  p.zi = static_cast<const S*>(zi);
+  p.x = static_cast<const S*>(x);
+  p.y = static_cast<S*>(y);
+  p.zf = static_cast<S*>(zf);
+  p.T = T;
+  const bool bulk = aligned16(x) && aligned16(y) && aligned16(A) && (T * (XS ? 1 : 2) * sizeof(S)) % 16 == 0;
+  static bool attr_set[kMaxDevices] = {};
+  static int grid_max[kMaxDevices] = {};
+  int dev = 0;
+  PTB_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return PTB_ERR_ARG;
+  if (!attr_set[dev]) {
+    PTB_CUDA(cudaFuncSetAttribute(so_small_fwd_kernel<S, C, XS>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+    int sms = 0, occ = 1;
+    PTB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    PTB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, so_small_fwd_kernel<S, C, XS>, C::NT, L::kTotal));
+    grid_max[dev] = sms * std::max(occ, 1);
+    attr_set[dev] = true;
+  }
+  const unsigned grid = (unsigned)std::min<int64_t>(ntiles, grid_max[dev]);
+  so_small_fwd_kernel<S, C, XS><<<grid, C::NT, L::kTotal, st>>>(p, wk, (uint32_t)B, (uint32_t)nchunks, (uint32_t)ntiles,
+                                                                bulk ? 1 : 0, g_wait_ns);
+  PTB_CUDA(cudaGetLastError());
+  return PTB_OK;
+}
+
+static int g_so_small_min_rows = PTB_SO_SMALL_MIN_ROWS;
+
 template <class S, bool LPV, bool XS>
 static int so_fwd(int64_t B, int64_t T, const void* A, int A_batched, const void* zi, const void* x, void* y,
                   void* zf, void* ws, int64_t wsb, uint32_t* status, cudaStream_t st) {
+  if constexpr (LPV) {
+    if (B >= g_so_small_min_rows) return so_small_fwd<S, XS>(B, T, A, A_batched, zi, x, y, zf, ws, wsb, status, st);
+  }
   using P = SoFwdP<S, LPV, XS>;
   typename P::Params p;
   p.A = static_cast<const S*>(A);
@@ -389,6 +455,12 @@ int ptb_lpv_recur_fwd_carry(int dtype, int64_t B, int64_t T, const void* a, int 
   if (T == 0 || !a || !x || !y || !carry) return PTB_ERR_ARG;
   PTB_DISPATCH(dtype, (fo_carry<S, false, true>(B, T, a, a_batched, x, y, carry, workspace, workspace_bytes,
                                                  status, (cudaStream_t)stream)));
+}
+
+int ptb_lpv_recur2_set_small_cta_min_rows(int64_t rows) {
+  if (rows < 1) return PTB_ERR_ARG;
+  g_so_small_min_rows = rows > 0x7fffffff ? 0x7fffffff : (int)rows;
+  return PTB_OK;
 }
 
 int ptb_set_wait_limit_ms(int64_t ms) {

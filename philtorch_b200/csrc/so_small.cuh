@@ -1,0 +1,220 @@
+// Time-varying 2x2 recurrence  h[t] = A[t] h[t-1] + x[t]  (philtorch::recur2,
+// philtorch/csrc/recur2.cu:69-117) in small CTAs: the single-pass scan with decoupled look-back of
+// lpv_biquad.cuh (64 threads, several CTAs per SM, operands in registers, one tile prefetched)
+// with the plain matrix recurrence as the per-sample step.  Batches of a few dozen rows and more
+// run faster here than on the one-CTA-per-SM engine (the scan and look-back latency of one tile
+// overlaps other tiles' arithmetic); the host picks.
+#pragma once
+#include "lpv_biquad.cuh"
+
+namespace ptb {
+
+template <class S>
+struct SoSmallFwdParams {
+  const S* A; int64_t a_row;   // (B,T,2,2) or (T,2,2): row stride 4T or 0
+  const S* zi;                 // (B,2)
+  const S* x;                  // (B,T) into state 0 (XS) or (B,T,2)
+  S* y;                        // (B,T,2)
+  S* zf;                       // optional (B,2)
+  int64_t T;
+};
+
+template <class C, bool XS>
+struct SoSmallFwdSmem {
+  static constexpr int kA = 0;                               // [TILE][4]
+  static constexpr int kX = kA + 4 * C::XB;                  // [TILE] or [TILE][2]
+  static constexpr int kY = kX + (XS ? 1 : 2) * C::XB;       // [TILE][2] out
+  static constexpr int kBar = kY + 2 * C::XB;                // u64 full[2]
+  static constexpr int kMisc = kBar + 16;                    // u32 ticket[2], ok
+  static constexpr int kHin = kMisc + 16;                    // S hin[2]
+  static constexpr int kWtot = kHin + 16;                    // S wtot[NW][6]
+  static constexpr int kTotal = kWtot + C::NW * 6 * 8 + 16;
+};
+
+template <class S> struct Vec4T;
+template <> struct Vec4T<float> {
+  static __device__ __forceinline__ void ld(const float* p, float* r) {
+    const float4 q = *reinterpret_cast<const float4*>(p);
+    r[0] = q.x; r[1] = q.y; r[2] = q.z; r[3] = q.w;
+  }
+};
+template <> struct Vec4T<double> {
+  static __device__ __forceinline__ void ld(const double* p, double* r) {
+    const double2 q = *reinterpret_cast<const double2*>(p), t = *reinterpret_cast<const double2*>(p + 2);
+    r[0] = q.x; r[1] = q.y; r[2] = t.x; r[3] = t.y;
+  }
+};
+
+template <class S, class C, bool XS>
+__global__ void __launch_bounds__(C::NT, C::MINB)
+so_small_fwd_kernel(const SoSmallFwdParams<S> p, const Workspace ws, const uint32_t B, const uint32_t nchunks,
+                    const uint32_t ntiles, const int bulk, const uint64_t wait_ns) {
+  using L = SoSmallFwdSmem<C, XS>;
+  using V2 = typename Vec2T<S>::type;
+  constexpr int SPT = C::SPT, TILE = C::TILE, NT = C::NT, XW = XS ? 1 : 2;
+  extern __shared__ __align__(128) unsigned char smem[];
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::kBar);
+  volatile uint32_t* sm_ticket = reinterpret_cast<volatile uint32_t*>(smem + L::kMisc);
+  volatile uint32_t* sm_ok = sm_ticket + 2;
+  S* sm_hin = reinterpret_cast<S*>(smem + L::kHin);
+  S* sm_wtot = reinterpret_cast<S*>(smem + L::kWtot);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  if (tid == 0) {
+    mbar_init(&full[0], 1);
+    mbar_init(&full[1], 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+  auto coords = [&](uint32_t ticket, uint32_t& chunk, uint32_t& row, int64_t& t0, int& nvalid) {
+    chunk = ticket / B;
+    row = ticket - chunk * B;
+    t0 = (int64_t)chunk * TILE;
+    const int64_t rem = p.T - t0;
+    nvalid = rem < (int64_t)TILE ? (int)rem : TILE;
+  };
+  auto issue = [&](int s, uint32_t ticket) {
+    uint32_t chunk, row; int64_t t0; int nvalid;
+    coords(ticket, chunk, row, t0, nvalid);
+    const uint32_t bytes = (uint32_t)nvalid * sizeof(S);
+    mbar_arrive_expect_tx(&full[s], (4 + XW) * bytes);
+    bulk_g2s(smem + L::kA, p.A + (int64_t)row * p.a_row + 4 * t0, 4 * bytes, &full[s]);
+    bulk_g2s(smem + L::kX, p.x + ((int64_t)row * p.T + t0) * XW, XW * bytes, &full[s]);
+  };
+  if (tid == 0) {
+    const uint32_t t = atomicAdd(ws.ticket, 1u);
+    sm_ticket[0] = t < ntiles ? t : kNoTile;
+    if (t < ntiles && bulk) issue(0, t);
+  }
+  __syncthreads();
+
+  for (uint32_t n = 0;; ++n) {
+    const int s = n & 1;
+    const uint32_t ticket = sm_ticket[s];
+    if (ticket == kNoTile) break;
+    uint32_t chunk, row; int64_t t0; int nvalid;
+    coords(ticket, chunk, row, t0, nvalid);
+    const uint32_t nbytes = (uint32_t)nvalid * sizeof(S);
+    if (bulk) {
+      if (tid == 0) {
+        const bool ok = mbar_wait_bounded(&full[s], (n >> 1) & 1u, wait_ns);
+        if (!ok) atomicOr(ws.error, kErrLoadTimeout);
+        *sm_ok = ok ? 1u : 0u;
+      }
+    } else {
+      auto copy = [&](int off, const S* g, uint32_t words) {
+        const uint32_t* gg = reinterpret_cast<const uint32_t*>(g);
+        uint32_t* d = reinterpret_cast<uint32_t*>(smem + off);
+        for (uint32_t w = tid; w < words; w += NT) d[w] = __ldg(gg + w);
+      };
+      copy(L::kA, p.A + (int64_t)row * p.a_row + 4 * t0, 4 * nbytes / 4);
+      copy(L::kX, p.x + ((int64_t)row * p.T + t0) * XW, XW * nbytes / 4);
+      if (tid == 0) *sm_ok = 1u;
+    }
+    __syncthreads();
+    if (*sm_ok == 0u) {   // results are invalid from here on: stop taking work
+      if (tid == 0) sm_ticket[s ^ 1] = kNoTile;
+      __syncthreads();
+      continue;
+    }
+    if (bulk) mbar_test_wait(&full[s], (n >> 1) & 1u);   // every thread observes the completed phase itself
+
+    int nv = nvalid - tid * SPT;
+    nv = nv < 0 ? 0 : (nv > SPT ? SPT : nv);
+    S A[SPT][4], x0[SPT], x1[SPT];
+    {
+      const S* pa = reinterpret_cast<const S*>(smem + L::kA) + tid * SPT * 4;
+      const S* px = reinterpret_cast<const S*>(smem + L::kX) + tid * SPT * XW;
+#pragma unroll
+      for (int j = 0; j < SPT; ++j) {
+        Vec4T<S>::ld(pa + 4 * j, A[j]);
+        if (XS) { x0[j] = px[j]; x1[j] = S(0); }
+        else { const V2 v = reinterpret_cast<const V2*>(px)[j]; x0[j] = v.x; x1[j] = v.y; }
+      }
+    }
+    __syncthreads();   // everyone holds its samples: the tile buffers are free
+    if (tid == 0) {    // fetch the tile after this one
+      const uint32_t t = atomicAdd(ws.ticket, 1u);
+      sm_ticket[s ^ 1] = t < ntiles ? t : kNoTile;
+      if (t < ntiles && bulk) {
+        fence_proxy_async_smem();
+        issue(s ^ 1, t);
+      }
+    }
+    // phase A: my samples as one affine map (samples beyond the end of the row are skipped)
+    S m[6] = {S(1), S(0), S(0), S(1), S(0), S(0)};
+#pragma unroll
+    for (int j = 0; j < SPT; ++j) {
+      if (j < nv) {
+        const S n0 = A[j][0] * m[0] + A[j][1] * m[2], n1 = A[j][0] * m[1] + A[j][1] * m[3];
+        const S n2 = A[j][2] * m[0] + A[j][3] * m[2], n3 = A[j][2] * m[1] + A[j][3] * m[3];
+        const S n4 = A[j][0] * m[4] + A[j][1] * m[5] + x0[j], n5 = A[j][2] * m[4] + A[j][3] * m[5] + x1[j];
+        m[0] = n0; m[1] = n1; m[2] = n2; m[3] = n3; m[4] = n4; m[5] = n5;
+      }
+    }
+    affine_warp_scan<S>(m, lane);
+    S e[6];
+#pragma unroll
+    for (int i = 0; i < 6; ++i) e[i] = __shfl_up_sync(0xffffffffu, m[i], 1);
+    if (lane == 0) { e[0] = S(1); e[1] = S(0); e[2] = S(0); e[3] = S(1); e[4] = S(0); e[5] = S(0); }
+    if (lane == 31) {
+#pragma unroll
+      for (int i = 0; i < 6; ++i) sm_wtot[warp * 6 + i] = m[i];
+    }
+    if (tid == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the previous tile's outputs have left
+    __syncthreads();
+    if (warp == 0) {
+      S z0 = S(0), z1 = S(0);
+      if (chunk == 0) { z0 = __ldg(p.zi + (int64_t)row * 2); z1 = __ldg(p.zi + (int64_t)row * 2 + 1); }
+      const typename LpvLb<S>::State hin =
+          lpv_tile_state<S, C::NW>(ws, sm_wtot, ticket, chunk, nchunks, B, lane, z0, z1, wait_ns);
+      if (lane == 0) { sm_hin[0] = hin.v[0]; sm_hin[1] = hin.v[1]; }
+    }
+    __syncthreads();
+    S h0 = sm_hin[0], h1 = sm_hin[1];
+    for (int w = 0; w < warp; ++w) {
+      const S* t = sm_wtot + w * 6;
+      const S g0 = t[0] * h0 + t[1] * h1 + t[4], g1 = t[2] * h0 + t[3] * h1 + t[5];
+      h0 = g0; h1 = g1;
+    }
+    {
+      const S g0 = e[0] * h0 + e[1] * h1 + e[4], g1 = e[2] * h0 + e[3] * h1 + e[5];
+      h0 = g0; h1 = g1;
+    }
+    // phase B: replay; the states after every sample are the output
+    {
+      V2* py = reinterpret_cast<V2*>(smem + L::kY) + tid * SPT;
+#pragma unroll
+      for (int j = 0; j < SPT; ++j) {
+        if (j < nv) {
+          const S n0 = A[j][0] * h0 + A[j][1] * h1 + x0[j], n1 = A[j][2] * h0 + A[j][3] * h1 + x1[j];
+          h0 = n0; h1 = n1;
+          V2 hv; hv.x = h0; hv.y = h1;
+          py[j] = hv;
+        }
+      }
+    }
+    if (p.zf != nullptr && nv > 0 && (t0 + (int64_t)tid * SPT + nv == p.T)) {
+      p.zf[(int64_t)row * 2] = h0;
+      p.zf[(int64_t)row * 2 + 1] = h1;
+    }
+    S* gy = p.y + ((int64_t)row * p.T + t0) * 2;
+    if (bulk) {
+      fence_proxy_async_smem();
+      __syncthreads();
+      if (tid == 0) {
+        bulk_s2g(gy, smem + L::kY, 2 * nbytes);
+        bulk_commit();
+      }
+    } else {
+      __syncthreads();
+      const uint32_t* sy = reinterpret_cast<const uint32_t*>(smem + L::kY);
+      uint32_t* oy = reinterpret_cast<uint32_t*>(gy);
+      for (uint32_t w = tid; w < 2 * nbytes / 4; w += NT) oy[w] = sy[w];
+      __syncthreads();
+    }
+  }
+  if (tid == 0) bulk_wait_all();
+}
+
+}  // namespace ptb

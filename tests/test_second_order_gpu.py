@@ -13,6 +13,16 @@ from conftest import load_golden, rel_err, tol
 from oracle import cport
 
 pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True, params=[10**9, 1], ids=["large-cta", "small-cta"])
+def lpv_forward_kernel(request):
+    """The time-varying 2x2 forward runs on one of two kernels, normally picked by the batch size:
+    every case here runs on both."""
+    from philtorch_b200 import _lib
+    assert _lib.lib.ptb_lpv_recur2_set_small_cta_min_rows(request.param) == 0
+    yield request.param
+    assert _lib.lib.ptb_lpv_recur2_set_small_cta_min_rows(48) == 0
 DEV = "cuda"
 DT = {"f32": torch.float32, "f64": torch.float64}
 # tiles are a few thousand samples (e.g. 3840 forward / 2816 backward in fp32, 1792 / 1280 in fp64)
