@@ -213,6 +213,70 @@ static int so_small_fwd(int64_t B, int64_t T, const void* A, int A_batched, cons
 
 static int g_so_small_min_rows = PTB_SO_SMALL_MIN_ROWS;
 
+#ifndef PTB_SO_SMALL_BWD_MINB
+#define PTB_SO_SMALL_BWD_NT 128
+#define PTB_SO_SMALL_BWD_SPT 11
+#define PTB_SO_SMALL_BWD_MINB 4
+#define PTB_SO_SMALL_BWD_SPT64 5
+#define PTB_SO_SMALL_BWD_MINB64 4
+#endif
+template <class S> struct SoSmallBwdSel;
+template <> struct SoSmallBwdSel<float> { using C = LpvBqCfg<float, PTB_SO_SMALL_BWD_SPT, PTB_SO_SMALL_BWD_NT, PTB_SO_SMALL_BWD_MINB>; };
+template <> struct SoSmallBwdSel<double> { using C = LpvBqCfg<double, PTB_SO_SMALL_BWD_SPT64, PTB_SO_SMALL_BWD_NT, PTB_SO_SMALL_BWD_MINB64>; };
+
+template <class S, bool XS>
+static int so_small_bwd(int64_t B, int64_t T, const void* A, int A_batched, const void* zi, const void* y,
+                        const void* gy, const void* g_in, void* grad_x, void* grad_A, void* grad_zi, void* ws,
+                        int64_t wsb, uint32_t* status, cudaStream_t st) {
+  using C = typename SoSmallBwdSel<S>::C;
+  using L = SoSmallBwdSmem<C, XS>;
+  static_assert(C::TILE >= kMinTile && C::SLOT_WORDS * 8 <= kTileRecordBytes, "generic workspace bound");
+  static_assert(L::kTotal * C::MINB <= 227 * 1024, "shared memory of an SM");
+  const int64_t nchunks = (T + C::TILE - 1) / C::TILE;
+  const int64_t ntiles = B * nchunks;
+  if (ntiles >= 0xFFFFFFFEll || B >= 0xFFFFFFFFll) return PTB_ERR_TOO_LARGE;
+  const WsLayout l = ws_layout(ntiles, C::SLOT_WORDS, 0);
+  if (!ws || (reinterpret_cast<uintptr_t>(ws) & 255u) || wsb < l.total) return PTB_ERR_WORKSPACE;
+  char* w = static_cast<char*>(ws);
+  PTB_CUDA(cudaMemsetAsync(w, 0, (size_t)l.part_off, st));
+  Workspace wk;
+  wk.ticket = reinterpret_cast<uint32_t*>(w);
+  wk.error = status ? status : reinterpret_cast<uint32_t*>(w + 4);
+  wk.slots = reinterpret_cast<uint64_t*>(w + l.slots_off);
+  wk.partial = nullptr;
+  SoSmallBwdParams<S> p;
+  p.A = static_cast<const S*>(A);
+  p.a_row = A_batched ? 4 * T : 0;
+  p.zi = static_cast<const S*>(zi);
+  p.y = static_cast<const S*>(y);
+  p.gy = static_cast<const S*>(gy);
+  p.g_in = static_cast<const S*>(g_in);
+  p.grad_x = static_cast<S*>(grad_x);
+  p.grad_A = static_cast<S*>(grad_A);
+  p.grad_zi = static_cast<S*>(grad_zi);
+  p.T = T;
+  const bool bulk = aligned16(gy) && aligned16(grad_x) && aligned16(A) &&
+                    (!grad_A || (aligned16(y) && aligned16(grad_A))) && (T * (XS ? 1 : 2) * sizeof(S)) % 16 == 0;
+  static bool attr_set[kMaxDevices] = {};
+  static int grid_max[kMaxDevices] = {};
+  int dev = 0;
+  PTB_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return PTB_ERR_ARG;
+  if (!attr_set[dev]) {
+    PTB_CUDA(cudaFuncSetAttribute(so_small_bwd_kernel<S, C, XS>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+    int sms = 0, occ = 1;
+    PTB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    PTB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, so_small_bwd_kernel<S, C, XS>, C::NT, L::kTotal));
+    grid_max[dev] = sms * std::max(occ, 1);
+    attr_set[dev] = true;
+  }
+  const unsigned grid = (unsigned)std::min<int64_t>(ntiles, grid_max[dev]);
+  so_small_bwd_kernel<S, C, XS><<<grid, C::NT, L::kTotal, st>>>(p, wk, (uint32_t)B, (uint32_t)nchunks, (uint32_t)ntiles,
+                                                                bulk ? 1 : 0, g_wait_ns);
+  PTB_CUDA(cudaGetLastError());
+  return PTB_OK;
+}
+
 template <class S, bool LPV, bool XS>
 static int so_fwd(int64_t B, int64_t T, const void* A, int A_batched, const void* zi, const void* x, void* y,
                   void* zf, void* ws, int64_t wsb, uint32_t* status, cudaStream_t st) {
@@ -238,6 +302,10 @@ template <class S, bool LPV, bool XS>
 static int so_bwd(int64_t B, int64_t T, const void* A, int A_batched, const void* zi, const void* y,
                   const void* gy, const void* g_in, void* grad_x, void* grad_A, void* grad_zi, void* ws,
                   int64_t wsb, uint32_t* status, cudaStream_t st) {
+  if constexpr (LPV) {
+    if (B >= g_so_small_min_rows && (grad_A == nullptr || A_batched))
+      return so_small_bwd<S, XS>(B, T, A, A_batched, zi, y, gy, g_in, grad_x, grad_A, grad_zi, ws, wsb, status, st);
+  }
   using P = SoBwdP<S, LPV, XS>;
   typename P::Params p;
   p.A = static_cast<const S*>(A);
