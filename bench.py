@@ -374,6 +374,92 @@ def run_sos_cascade(args):
           flush=True)
 
 
+def _secondary_line(args, workload: str, n: int, ms: float, alg_bytes_per_sample: int, extra: dict):
+    peak, kind = measured_peak()
+    alg = alg_bytes_per_sample * n
+    line = {"metric": METRIC, "value": n / (ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": extra.pop("dtype", "f32"), "data": "synthetic (seeded, generated on device)",
+            "config": {"workload": workload, "inputs": "larger than L2"},
+            "roofline": {"bound": "hbm", "achieved": alg / (ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                         "peak_source": f"{kind} copy bandwidth", "frac": alg / (ms * 1e-3) / 1e9 / peak,
+                         "note": f"algorithmic {alg_bytes_per_sample} B per sample"}}
+    line.update(extra)
+    print(json.dumps(line), flush=True)
+
+
+def _timed(fn, args, dev):
+    import torch
+    for _ in range(max(3, args.warmup)):
+        fn()
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize(dev)
+    return e0.elapsed_time(e1) / args.steps
+
+
+def run_state_space(args):
+    """Secondary line: time-varying 2x2 state-space recursion (scalar input into state 0), B = 128,
+    T = 2^20, forward + backward with gradients for x and A, fp32 or fp64 (--f64)."""
+    import torch
+
+    import philtorch_b200 as ptb
+    from philtorch_b200 import workloads
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    dt = torch.float64 if args.f64 else torch.float32
+    Bc, Tc = (args.rows if args.rows != B else 128), 1 << 20
+    w = workloads.lpv_second_order(B=Bc, T=Tc, dtype=dt, device=dev)
+    A, x, zi, gy = w["A"].requires_grad_(), w["x"].requires_grad_(), w["zi"], w["gy"]
+
+    def step():
+        return torch.autograd.grad(ptb.lpv.state_space_recursion(A, zi, x), (A, x), gy)
+
+    ms = _timed(step, args, dev)
+    ptb.check_errors(dev)
+    s = 8 if args.f64 else 4
+    _secondary_line(args, f"LPV 2x2 state_space_recursion fwd+bwd (grads x, A), {'fp64' if args.f64 else 'fp32'}, "
+                          f"B={Bc}, T=2^20", Bc * Tc, ms, 20 * s, {"dtype": "f64" if args.f64 else "f32"})
+
+
+def run_lpv_lfilter(args):
+    """Secondary line: time-varying second-order filter ``lpv.lfilter(form='df2')``, B = 128, T = 2^20,
+    fp32, forward + backward with gradients for b, a and x."""
+    import math
+
+    import torch
+
+    import philtorch_b200 as ptb
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    Bc, Tc = (args.rows if args.rows != B else 128), 1 << 20
+    g = torch.Generator(device=dev).manual_seed(SEED_LPV)
+    r = 0.3 + 0.65 * torch.rand(Bc, Tc, device=dev, generator=g)
+    th = math.pi * torch.rand(Bc, Tc, device=dev, generator=g)
+    a = torch.stack([-2 * r * torch.cos(th), r * r], -1).requires_grad_()
+    b = torch.randn(Bc, Tc, 3, device=dev, generator=g).requires_grad_()
+    x = torch.randn(Bc, Tc, device=dev, generator=g).requires_grad_()
+    gy = torch.randn(Bc, Tc, device=dev, generator=g)
+    del r, th
+
+    def step():
+        return torch.autograd.grad(ptb.lpv.lfilter(b, a, x), (b, a, x), gy)
+
+    ms = _timed(step, args, dev)
+    ptb.check_errors(dev)
+    _secondary_line(args, f"LPV lfilter df2 (order 2) fwd+bwd (grads b, a, x), fp32, B={Bc}, T=2^20", Bc * Tc, ms,
+                    36 + 60, {})
+
+
+SEED_LPV = 1240
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -386,6 +472,11 @@ def main():
     ap.add_argument("--time-sharded", action="store_true",
                     help="secondary workload: B=8 long rows split along time over the ranks")
     ap.add_argument("--log2-T", type=int, default=28, dest="log2_T", help="total row length of --time-sharded")
+    ap.add_argument("--state-space", action="store_true",
+                    help="secondary workload: LPV 2x2 state-space recursion, B=128, T=2^20 (one GPU)")
+    ap.add_argument("--lpv-lfilter", action="store_true",
+                    help="secondary workload: time-varying second-order lfilter, B=128, T=2^20 (one GPU)")
+    ap.add_argument("--f64", action="store_true", help="float64 for --state-space")
     ap.add_argument("--sos-cascade", action="store_true",
                     help="secondary workload: six fused second-order sections, B=512, T=2^18 (one GPU)")
     args = ap.parse_args()
@@ -395,9 +486,9 @@ def main():
     if args.impl == "reference":
         run_reference_arm(args, rank)
         return
-    if args.sos_cascade:
+    if args.sos_cascade or args.state_space or args.lpv_lfilter:
         if rank == 0:
-            run_sos_cascade(args)
+            (run_sos_cascade if args.sos_cascade else run_state_space if args.state_space else run_lpv_lfilter)(args)
         return
     if args.time_sharded:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")

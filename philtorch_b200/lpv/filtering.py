@@ -51,14 +51,14 @@ def _ssm_lfilter(b: Tensor, a: Tensor, x: Tensor, zi: Optional[Tensor], form: st
         if zi.dim() == 1:
             zi = zi.unsqueeze(0).expand(B, -1)
         zi2 = F.pad(zi, (0, 2 - zi.size(-1))) if zi.size(-1) < 2 else zi
+    if form == "df2" and B >= FUSED_MIN_ROWS:   # one fused kernel per direction
+        y, zf = LPVBiquadDF2.apply(b, a, zi2 if return_zf else None, x)
+        return (y, zf[:, :order]) if return_zf else y
     a1, a2 = a[..., 0], a[..., 1]
     zero, one = torch.zeros_like(a1), torch.ones_like(a1)
     b0 = b[..., :1]
     Bv = b[..., 1:] - b0 * a          # (.., N, 2): C of the df2 form, B of the tdf2 form
     D = b[..., 0]
-    if form == "df2" and B >= FUSED_MIN_ROWS:
-        y, zf = LPVBiquadDF2.apply(b, a, zi2 if return_zf else None, x)
-        return (y, zf[:, :order]) if return_zf else y
     if form == "df2":
         # h_t = companion(a_t) h_{t-1} + [x_t, 0];  y_t = C_t . h_{t-1} + D_t x_t
         A = torch.stack([torch.stack([-a1, -a2], -1), torch.stack([one, zero], -1)], -2)
