@@ -241,13 +241,21 @@ int ptb_sos_cascade_bwd(int dtype, int K, int64_t B, int64_t T, const void* b, c
  *   hp       optional (B,T,2): the state before every sample, which the backward pass needs
  * Backward: gy (B,T), g_zf optional (B,2) -> grad_x (B,T), grad_b (B,T,3) and grad_a (B,T,2) PER
  * ROW (a caller with shared coefficients sums them over the rows), grad_zi optional (B,2).
- * Chained scan (a tile takes over the end state of the row's previous tile): meant for batches of
- * at least a few dozen rows.  Workspace: ptb_lpv_biquad_workspace_bytes. */
+ * Small CTAs with decoupled look-back: meant for batches of at least a few dozen rows.
+ * Workspace: ptb_lpv_biquad_workspace_bytes. */
 int64_t ptb_lpv_biquad_workspace_bytes(int dtype, int64_t B, int64_t T);
 int ptb_lpv_biquad_df2_fwd(int dtype, int64_t B, int64_t T, const void* b, const void* a, int coef_batched,
                            const void* zi, const void* x, void* y, void* hp, void* zf, void* workspace,
                            int64_t workspace_bytes, uint32_t* status, ptb_stream_t stream);
 int ptb_lpv_biquad_df2_bwd(int dtype, int64_t B, int64_t T, const void* b, const void* a, int coef_batched,
+                           const void* x, const void* hp, const void* gy, const void* g_zf, void* grad_x,
+                           void* grad_b, void* grad_a, void* grad_zi, void* workspace, int64_t workspace_bytes,
+                           uint32_t* status, ptb_stream_t stream);
+/* the same for form="tdf2" (philtorch/lpv/filtering.py:314-326): identical arguments */
+int ptb_lpv_biquad_tdf2_fwd(int dtype, int64_t B, int64_t T, const void* b, const void* a, int coef_batched,
+                           const void* zi, const void* x, void* y, void* hp, void* zf, void* workspace,
+                           int64_t workspace_bytes, uint32_t* status, ptb_stream_t stream);
+int ptb_lpv_biquad_tdf2_bwd(int dtype, int64_t B, int64_t T, const void* b, const void* a, int coef_batched,
                            const void* x, const void* hp, const void* gy, const void* g_zf, void* grad_x,
                            void* grad_b, void* grad_a, void* grad_zi, void* workspace, int64_t workspace_bytes,
                            uint32_t* status, ptb_stream_t stream);

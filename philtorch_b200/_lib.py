@@ -85,6 +85,10 @@ lib.ptb_lpv_biquad_df2_fwd.argtypes = [_i32, _i64, _i64, _vp, _vp, _i32, _vp, _v
 lib.ptb_lpv_biquad_df2_fwd.restype = _i32
 lib.ptb_lpv_biquad_df2_bwd.argtypes = [_i32, _i64, _i64, _vp, _vp, _i32] + [_vp] * 8 + _tail
 lib.ptb_lpv_biquad_df2_bwd.restype = _i32
+lib.ptb_lpv_biquad_tdf2_fwd.argtypes = lib.ptb_lpv_biquad_df2_fwd.argtypes
+lib.ptb_lpv_biquad_tdf2_fwd.restype = _i32
+lib.ptb_lpv_biquad_tdf2_bwd.argtypes = lib.ptb_lpv_biquad_df2_bwd.argtypes
+lib.ptb_lpv_biquad_tdf2_bwd.restype = _i32
 
 _status: dict[int, torch.Tensor] = {}
 

@@ -333,16 +333,18 @@ class SOSCascade(Function):
                 _none_if_empty(gx, need_x))
 
 
-class LPVBiquadDF2(Function):
-    """Time-varying second-order filter in direct form II, fused: (b, a, zi, x) -> (y, zf) with
-    per-sample b (N,3) | (B,N,3) and a (N,2) | (B,N,2); philtorch.lpv.lfilter(form="df2") for
-    orders <= 2 (philtorch/lpv/filtering.py:288-313).  First derivatives only."""
+class LPVBiquad(Function):
+    """Time-varying second-order filter, fused: (b, a, zi, x, form) -> (y, zf) with per-sample
+    b (N,3) | (B,N,3) and a (N,2) | (B,N,2), form 'df2' or 'tdf2'; philtorch.lpv.lfilter for orders
+    <= 2 (philtorch/lpv/filtering.py:288-326).  First derivatives only."""
 
     @staticmethod
-    def forward(ctx: Any, b: Tensor, a: Tensor, zi: Optional[Tensor], x: Tensor):
+    def forward(ctx: Any, b: Tensor, a: Tensor, zi: Optional[Tensor], x: Tensor, form: str):
         need = any(ctx.needs_input_grad)
-        y, hp, zf = _ops.lpv_biquad_df2(b, a, zi, x, need)
+        fwd = _ops.lpv_biquad_df2 if form == "df2" else _ops.lpv_biquad_tdf2
+        y, hp, zf = fwd(b, a, zi, x, need)
         ctx.has_zi = zi is not None
+        ctx.form = form
         ctx.save_for_backward(b, a, x, hp)
         return y, zf
 
@@ -350,15 +352,16 @@ class LPVBiquadDF2(Function):
     @torch.autograd.function.once_differentiable
     def backward(ctx: Any, grad_y: Tensor, grad_zf: Tensor):
         b, a, x, hp = ctx.saved_tensors
-        need_b, need_a, need_zi, need_x = ctx.needs_input_grad
+        need_b, need_a, need_zi, need_x = ctx.needs_input_grad[:4]
         need_zi = need_zi and ctx.has_zi
         if grad_y is None:
             grad_y = torch.zeros_like(x)
-        gb, ga, gzi, gx = _ops.lpv_biquad_df2_bwd(b, a, x, hp, grad_y, grad_zf, need_zi)
+        bwd = _ops.lpv_biquad_df2_bwd if ctx.form == "df2" else _ops.lpv_biquad_tdf2_bwd
+        gb, ga, gzi, gx = bwd(b, a, x, hp, grad_y, grad_zf, need_zi)
         if b.dim() == 2:   # coefficients shared by the rows
             gb, ga = gb.sum(0), ga.sum(0)
         return (gb if need_b else None, ga if need_a else None, _none_if_empty(gzi, need_zi),
-                gx if need_x else None)
+                gx if need_x else None, None)
 
 
 def _biquad_reference_form(b: Tensor, a: Tensor, zi: Optional[Tensor], x: Tensor):

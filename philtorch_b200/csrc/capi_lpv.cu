@@ -47,7 +47,7 @@ static int launch_chained(K kernel, int smem, const P& p, int64_t B, int64_t T, 
   return PTB_OK;
 }
 
-template <class S>
+template <class S, bool TDF2>
 static int lpv_fwd(int64_t B, int64_t T, const void* b, const void* a, int coef_batched, const void* zi, const void* x,
                    void* y, void* hp, void* zf, void* ws, int64_t wsb, uint32_t* status, cudaStream_t st) {
   using C = typename LpvSel<S>::F;
@@ -64,10 +64,10 @@ static int lpv_fwd(int64_t B, int64_t T, const void* b, const void* a, int coef_
   const bool bulk = aligned16(a) && aligned16(b) && aligned16(x) && aligned16(y) && (!hp || aligned16(hp)) &&
                     (T * sizeof(S)) % 16 == 0;
   static bool attr_set[kMaxDevices] = {};
-  return launch_chained<C>(lpv_bq_fwd_kernel<S, C>, L::kTotal, p, B, T, ws, wsb, status, bulk, st, attr_set);
+  return launch_chained<C>(lpv_bq_fwd_kernel<S, C, TDF2>, L::kTotal, p, B, T, ws, wsb, status, bulk, st, attr_set);
 }
 
-template <class S>
+template <class S, bool TDF2>
 static int lpv_bwd(int64_t B, int64_t T, const void* b, const void* a, int coef_batched, const void* x, const void* hp,
                    const void* gy, const void* g_zf, void* grad_x, void* grad_b, void* grad_a, void* grad_zi, void* ws,
                    int64_t wsb, uint32_t* status, cudaStream_t st) {
@@ -88,7 +88,7 @@ static int lpv_bwd(int64_t B, int64_t T, const void* b, const void* a, int coef_
   const bool bulk = aligned16(a) && aligned16(b) && aligned16(x) && aligned16(hp) && aligned16(gy) &&
                     aligned16(grad_x) && aligned16(grad_a) && aligned16(grad_b) && (T * sizeof(S)) % 16 == 0;
   static bool attr_set[kMaxDevices] = {};
-  return launch_chained<C>(lpv_bq_bwd_kernel<S, C>, L::kTotal, p, B, T, ws, wsb, status, bulk, st, attr_set);
+  return launch_chained<C>(lpv_bq_bwd_kernel<S, C, TDF2>, L::kTotal, p, B, T, ws, wsb, status, bulk, st, attr_set);
 }
 
 }  // namespace ptb
@@ -109,10 +109,10 @@ int ptb_lpv_biquad_df2_fwd(int dtype, int64_t B, int64_t T, const void* b, const
                            int64_t workspace_bytes, uint32_t* status, ptb_stream_t stream) {
   if (B <= 0 || T <= 0 || !b || !a || !x || !y) return PTB_ERR_ARG;
   if (dtype == PTB_F32)
-    return lpv_fwd<float>(B, T, b, a, coef_batched, zi, x, y, hp, zf, workspace, workspace_bytes, status,
+    return lpv_fwd<float, false>(B, T, b, a, coef_batched, zi, x, y, hp, zf, workspace, workspace_bytes, status,
                           (cudaStream_t)stream);
   if (dtype == PTB_F64)
-    return lpv_fwd<double>(B, T, b, a, coef_batched, zi, x, y, hp, zf, workspace, workspace_bytes, status,
+    return lpv_fwd<double, false>(B, T, b, a, coef_batched, zi, x, y, hp, zf, workspace, workspace_bytes, status,
                            (cudaStream_t)stream);
   return PTB_ERR_ARG;
 }
@@ -123,10 +123,37 @@ int ptb_lpv_biquad_df2_bwd(int dtype, int64_t B, int64_t T, const void* b, const
                            uint32_t* status, ptb_stream_t stream) {
   if (B <= 0 || T <= 0 || !b || !a || !x || !hp || !gy || !grad_x || !grad_b || !grad_a) return PTB_ERR_ARG;
   if (dtype == PTB_F32)
-    return lpv_bwd<float>(B, T, b, a, coef_batched, x, hp, gy, g_zf, grad_x, grad_b, grad_a, grad_zi, workspace,
+    return lpv_bwd<float, false>(B, T, b, a, coef_batched, x, hp, gy, g_zf, grad_x, grad_b, grad_a, grad_zi, workspace,
                           workspace_bytes, status, (cudaStream_t)stream);
   if (dtype == PTB_F64)
-    return lpv_bwd<double>(B, T, b, a, coef_batched, x, hp, gy, g_zf, grad_x, grad_b, grad_a, grad_zi, workspace,
+    return lpv_bwd<double, false>(B, T, b, a, coef_batched, x, hp, gy, g_zf, grad_x, grad_b, grad_a, grad_zi, workspace,
+                           workspace_bytes, status, (cudaStream_t)stream);
+  return PTB_ERR_ARG;
+}
+
+int ptb_lpv_biquad_tdf2_fwd(int dtype, int64_t B, int64_t T, const void* b, const void* a, int coef_batched,
+                           const void* zi, const void* x, void* y, void* hp, void* zf, void* workspace,
+                           int64_t workspace_bytes, uint32_t* status, ptb_stream_t stream) {
+  if (B <= 0 || T <= 0 || !b || !a || !x || !y) return PTB_ERR_ARG;
+  if (dtype == PTB_F32)
+    return lpv_fwd<float, true>(B, T, b, a, coef_batched, zi, x, y, hp, zf, workspace, workspace_bytes, status,
+                          (cudaStream_t)stream);
+  if (dtype == PTB_F64)
+    return lpv_fwd<double, true>(B, T, b, a, coef_batched, zi, x, y, hp, zf, workspace, workspace_bytes, status,
+                           (cudaStream_t)stream);
+  return PTB_ERR_ARG;
+}
+
+int ptb_lpv_biquad_tdf2_bwd(int dtype, int64_t B, int64_t T, const void* b, const void* a, int coef_batched,
+                           const void* x, const void* hp, const void* gy, const void* g_zf, void* grad_x,
+                           void* grad_b, void* grad_a, void* grad_zi, void* workspace, int64_t workspace_bytes,
+                           uint32_t* status, ptb_stream_t stream) {
+  if (B <= 0 || T <= 0 || !b || !a || !x || !hp || !gy || !grad_x || !grad_b || !grad_a) return PTB_ERR_ARG;
+  if (dtype == PTB_F32)
+    return lpv_bwd<float, true>(B, T, b, a, coef_batched, x, hp, gy, g_zf, grad_x, grad_b, grad_a, grad_zi, workspace,
+                          workspace_bytes, status, (cudaStream_t)stream);
+  if (dtype == PTB_F64)
+    return lpv_bwd<double, true>(B, T, b, a, coef_batched, x, hp, gy, g_zf, grad_x, grad_b, grad_a, grad_zi, workspace,
                            workspace_bytes, status, (cudaStream_t)stream);
   return PTB_ERR_ARG;
 }

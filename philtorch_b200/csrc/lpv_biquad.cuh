@@ -1,5 +1,7 @@
-// Time-varying (parameter-varying) second-order filter, direct form II, scalar in and scalar out,
-// with per-sample coefficients: the whole of philtorch.lpv.lfilter(form="df2") for orders <= 2
+// Time-varying (parameter-varying) second-order filter, direct form II (and transposed direct form
+// II, TDF2 = true: h' = A_t^T h + (b_t[1:] - b0_t a_t) x_t, y_t = h0 + b0_t x_t, adjoint likewise),
+// scalar in and scalar out, with per-sample coefficients: the whole of
+// philtorch.lpv.lfilter(form="df2" | "tdf2") for orders <= 2
 // (philtorch/lpv/filtering.py:288-313 builds companion(a_t), C_t = b_t[1:] - b0_t a_t, D_t = b0_t;
 // philtorch/lpv/ssm.py:413-500 runs  h_t = A_t h_{t-1} + e0 x_t,  y_t = C_t . h_{t-1} + D_t x_t
 // as a dozen full passes over (B,T,2,2) / (B,T,2) tensors) in ONE pass per direction:
@@ -122,7 +124,7 @@ struct LpvBqFwdSmem {
   static constexpr int kTotal = kWtot + C::NW * 6 * 8 + 16;
 };
 
-template <class S, class C>
+template <class S, class C, bool TDF2>
 __global__ void __launch_bounds__(C::NT, C::MINB)
 lpv_bq_fwd_kernel(const LpvBqFwdParams<S> p, const Workspace ws, const uint32_t B, const uint32_t nchunks,
                   const uint32_t ntiles, const int bulk, const uint64_t wait_ns) {
@@ -233,10 +235,16 @@ lpv_bq_fwd_kernel(const LpvBqFwdParams<S> p, const Workspace ws, const uint32_t 
     S m[6] = {S(1), S(0), S(0), S(1), S(0), S(0)};
 #pragma unroll
     for (int j = 0; j < SPT; ++j) {
-      const S n0 = -a1[j] * m[0] - a2[j] * m[2], n1 = -a1[j] * m[1] - a2[j] * m[3];
-      const S n4 = -a1[j] * m[4] - a2[j] * m[5] + x[j];
-      m[2] = m[0]; m[3] = m[1]; m[5] = m[4];
-      m[0] = n0; m[1] = n1; m[4] = n4;
+      if (!TDF2) {   // h' = [[-a1,-a2],[1,0]] h + [x, 0]
+        const S n0 = -a1[j] * m[0] - a2[j] * m[2], n1 = -a1[j] * m[1] - a2[j] * m[3];
+        const S n4 = -a1[j] * m[4] - a2[j] * m[5] + x[j];
+        m[2] = m[0]; m[3] = m[1]; m[5] = m[4];
+        m[0] = n0; m[1] = n1; m[4] = n4;
+      } else {       // h' = [[-a1,1],[-a2,0]] h + [c0, c1] x
+        const S n0 = -a1[j] * m[0] + m[2], n1 = -a1[j] * m[1] + m[3], n4 = -a1[j] * m[4] + m[5] + c0[j] * x[j];
+        const S n2 = -a2[j] * m[0], n3 = -a2[j] * m[1], n5 = -a2[j] * m[4] + c1[j] * x[j];
+        m[0] = n0; m[1] = n1; m[2] = n2; m[3] = n3; m[4] = n4; m[5] = n5;
+      }
     }
     affine_warp_scan<S>(m, lane);
     S e[6];
@@ -275,11 +283,18 @@ lpv_bq_fwd_kernel(const LpvBqFwdParams<S> p, const Workspace ws, const uint32_t 
 #pragma unroll
       for (int j = 0; j < SPT; ++j) {
         if (j < nv) {
-          py[j] = c0[j] * h0 + c1[j] * h1 + d0[j] * x[j];
           if (p.hp) { V2 hv; hv.x = h0; hv.y = h1; ph[j] = hv; }
-          const S n0 = -a1[j] * h0 - a2[j] * h1 + x[j];
-          h1 = h0;
-          h0 = n0;
+          if (!TDF2) {
+            py[j] = c0[j] * h0 + c1[j] * h1 + d0[j] * x[j];
+            const S n0 = -a1[j] * h0 - a2[j] * h1 + x[j];
+            h1 = h0;
+            h0 = n0;
+          } else {
+            py[j] = h0 + d0[j] * x[j];
+            const S n0 = -a1[j] * h0 + h1 + c0[j] * x[j];
+            h1 = -a2[j] * h0 + c1[j] * x[j];
+            h0 = n0;
+          }
         }
       }
     }
@@ -343,7 +358,7 @@ struct LpvBqBwdSmem {
   static constexpr int kTotal = kWtot + C::NW * 6 * 8 + 16;
 };
 
-template <class S, class C>
+template <class S, class C, bool TDF2>
 __global__ void __launch_bounds__(C::NT, C::MINB)
 lpv_bq_bwd_kernel(const LpvBqBwdParams<S> p, const Workspace ws, const uint32_t B, const uint32_t nchunks,
                   const uint32_t ntiles, const int bulk, const uint64_t wait_ns) {
@@ -431,10 +446,17 @@ lpv_bq_bwd_kernel(const LpvBqBwdParams<S> p, const Workspace ws, const uint32_t 
       if (j < nv) {
         const V2 av = pa[j];
         const S b0 = pb[3 * j], b1 = pb[3 * j + 1], b2 = pb[3 * j + 2], g = pg[j];
-        const S c0 = b1 - b0 * av.x, c1 = b2 - b0 * av.y;
-        const S n0 = -av.x * m[0] + m[2], n1 = -av.x * m[1] + m[3], n4 = -av.x * m[4] + m[5] + c0 * g;
-        const S n2 = -av.y * m[0], n3 = -av.y * m[1], n5 = -av.y * m[4] + c1 * g;
-        m[0] = n0; m[1] = n1; m[2] = n2; m[3] = n3; m[4] = n4; m[5] = n5;
+        if (!TDF2) {   // lam' = [[-a1,1],[-a2,0]] lam + C gy
+          const S c0 = b1 - b0 * av.x, c1 = b2 - b0 * av.y;
+          const S n0 = -av.x * m[0] + m[2], n1 = -av.x * m[1] + m[3], n4 = -av.x * m[4] + m[5] + c0 * g;
+          const S n2 = -av.y * m[0], n3 = -av.y * m[1], n5 = -av.y * m[4] + c1 * g;
+          m[0] = n0; m[1] = n1; m[2] = n2; m[3] = n3; m[4] = n4; m[5] = n5;
+        } else {       // lam' = [[-a1,-a2],[1,0]] lam + [gy, 0]
+          const S n0 = -av.x * m[0] - av.y * m[2], n1 = -av.x * m[1] - av.y * m[3];
+          const S n4 = -av.x * m[4] - av.y * m[5] + g;
+          m[2] = m[0]; m[3] = m[1]; m[5] = m[4];
+          m[0] = n0; m[1] = n1; m[4] = n4;
+        }
       }
     }
     if (owner) {   // its incoming state is g_in, not zero: as seen by the threads after it
@@ -475,17 +497,32 @@ lpv_bq_bwd_kernel(const LpvBqBwdParams<S> p, const Workspace ws, const uint32_t 
         const S b0 = pb[3 * j], b1 = pb[3 * j + 1], b2 = pb[3 * j + 2], g = pg[j], xj = px[j];
         const V2 hv = ph[j];
         const S c0 = b1 - b0 * av.x, c1 = b2 - b0 * av.y;
-        const S gc0 = g * hv.x, gc1 = g * hv.y;
-        pg[j] = l0 + b0 * g;
-        V2 gav;
-        gav.x = -l0 * hv.x - b0 * gc0;
-        gav.y = -l0 * hv.y - b0 * gc1;
-        pa[j] = gav;
-        pb[3 * j] = g * xj - av.x * gc0 - av.y * gc1;
-        pb[3 * j + 1] = gc0;
-        pb[3 * j + 2] = gc1;
-        const S n0 = -av.x * l0 + l1 + c0 * g, n1 = -av.y * l0 + c1 * g;
-        l0 = n0; l1 = n1;
+        if (!TDF2) {
+          const S gc0 = g * hv.x, gc1 = g * hv.y;   // gradient w.r.t. C_t
+          pg[j] = l0 + b0 * g;
+          V2 gav;
+          gav.x = -l0 * hv.x - b0 * gc0;
+          gav.y = -l0 * hv.y - b0 * gc1;
+          pa[j] = gav;
+          pb[3 * j] = g * xj - av.x * gc0 - av.y * gc1;
+          pb[3 * j + 1] = gc0;
+          pb[3 * j + 2] = gc1;
+          const S n0 = -av.x * l0 + l1 + c0 * g, n1 = -av.y * l0 + c1 * g;
+          l0 = n0; l1 = n1;
+        } else {
+          const S gb0 = xj * l0, gb1 = xj * l1;     // gradient w.r.t. B_t
+          pg[j] = c0 * l0 + c1 * l1 + b0 * g;
+          V2 gav;
+          gav.x = -l0 * hv.x - b0 * gb0;
+          gav.y = -l1 * hv.x - b0 * gb1;
+          pa[j] = gav;
+          pb[3 * j] = g * xj - av.x * gb0 - av.y * gb1;
+          pb[3 * j + 1] = gb0;
+          pb[3 * j + 2] = gb1;
+          const S n0 = -av.x * l0 - av.y * l1 + g;
+          l1 = l0;
+          l0 = n0;
+        }
       }
     }
     if (tid == NT - 1 && chunk + 1 == nchunks && p.grad_zi) {

@@ -1,10 +1,11 @@
 """Parameter-varying IIR filtering (orders 1 and 2) on the GPU kernels.
 
 ``lfilter`` keeps the signature of philtorch/lpv/filtering.py:138-194 for the state-space backend
-and the forms 'df2' and 'tdf2': the per-sample companion matrices drive the fused 2x2 scan kernels
-(``state_space_recursion``); the input and output maps around them (B_t x_t, the one-sample delay,
-C_t h_{t-1} + D_t x_t; philtorch/lpv/filtering.py:288-325, philtorch/lpv/ssm.py:413-500) are a
-few elementwise passes.  The FIR-based forms 'df1' / 'tdf1', orders above two and the 'torchlpc'
+and the forms 'df2' and 'tdf2'.  Batches of a few dozen rows and more run on one fused kernel per
+direction (csrc/lpv_biquad.cuh); smaller ones on the 2x2 scan kernels (``state_space_recursion``)
+driven by the per-sample companion matrices, with the input and output maps around them (B_t x_t,
+the one-sample delay, C_t h_{t-1} + D_t x_t; philtorch/lpv/filtering.py:288-325,
+philtorch/lpv/ssm.py:413-500) as a few elementwise passes.  The FIR-based forms 'df1' / 'tdf1', orders above two and the 'torchlpc'
 backend are outside this package.
 """
 from __future__ import annotations
@@ -15,12 +16,12 @@ import torch
 import torch.nn.functional as F
 from torch import Tensor
 
-from ..autograd import LPVBiquadDF2
+from ..autograd import LPVBiquad
 from .ssm import state_space_recursion
 
-# From this many rows on, form 'df2' runs on the fused chained kernels (one pass per direction, first
-# derivatives only); below it, and for 'tdf2', on the decoupled 2x2 scan kernels with elementwise
-# passes around them (differentiable to any order).  Set to a huge value to switch the fused path off.
+# From this many rows on, the filter runs on the fused kernels (one pass per direction, first
+# derivatives only); below it on the 2x2 scan kernels with elementwise passes around them
+# (differentiable to any order).  Set to a huge value to switch the fused path off.
 FUSED_MIN_ROWS = 32
 
 __all__ = ["lfilter"]
@@ -51,8 +52,8 @@ def _ssm_lfilter(b: Tensor, a: Tensor, x: Tensor, zi: Optional[Tensor], form: st
         if zi.dim() == 1:
             zi = zi.unsqueeze(0).expand(B, -1)
         zi2 = F.pad(zi, (0, 2 - zi.size(-1))) if zi.size(-1) < 2 else zi
-    if form == "df2" and B >= FUSED_MIN_ROWS:   # one fused kernel per direction
-        y, zf = LPVBiquadDF2.apply(b, a, zi2 if return_zf else None, x)
+    if form in ("df2", "tdf2") and B >= FUSED_MIN_ROWS:   # one fused kernel per direction
+        y, zf = LPVBiquad.apply(b, a, zi2 if return_zf else None, x, form)
         return (y, zf[:, :order]) if return_zf else y
     a1, a2 = a[..., 0], a[..., 1]
     zero, one = torch.zeros_like(a1), torch.ones_like(a1)

@@ -471,10 +471,11 @@ def _(b, a, x, mid, y, gy, gzf, need_coef, need_zi):
 
 
 # =============================================================================== fused LPV biquad (df2)
-_LIB.define("lpv_biquad_df2(Tensor b, Tensor a, Tensor? zi, Tensor x, bool keep_states) -> (Tensor, Tensor, Tensor)",
-            tags=_TAGS)
-_LIB.define("lpv_biquad_df2_bwd(Tensor b, Tensor a, Tensor x, Tensor hp, Tensor gy, Tensor? gzf, bool need_zi) "
-            "-> (Tensor, Tensor, Tensor, Tensor)", tags=_TAGS)
+for _form in ("df2", "tdf2"):
+    _LIB.define(f"lpv_biquad_{_form}(Tensor b, Tensor a, Tensor? zi, Tensor x, bool keep_states) "
+                "-> (Tensor, Tensor, Tensor)", tags=_TAGS)
+    _LIB.define(f"lpv_biquad_{_form}_bwd(Tensor b, Tensor a, Tensor x, Tensor hp, Tensor gy, Tensor? gzf, "
+                "bool need_zi) -> (Tensor, Tensor, Tensor, Tensor)", tags=_TAGS)
 
 
 def _check_lpv_biquad(b: Tensor, a: Tensor, zi: Optional[Tensor], x: Tensor) -> None:
@@ -490,7 +491,7 @@ def _check_lpv_biquad(b: Tensor, a: Tensor, zi: Optional[Tensor], x: Tensor) -> 
         torch._check(zi.dim() == 2 and zi.shape[0] == x.shape[0] and zi.shape[1] == 2, lambda: "zi must be (B,2).")
 
 
-def _lpv_biquad_df2(b, a, zi, x, keep_states):
+def _lpv_biquad_fwd(fn, b, a, zi, x, keep_states):
     _check_lpv_biquad(b, a, zi, x)
     dev = _lib.require_cuda(b, a, zi, x)
     if b.dtype != x.dtype or a.dtype != x.dtype or (zi is not None and zi.dtype != x.dtype):
@@ -502,7 +503,7 @@ def _lpv_biquad_df2(b, a, zi, x, keep_states):
     zf = x.new_empty(B, 2)
     if B and T:
         code = _lib.dtype_code(x)
-        _lib.call(lib.ptb_lpv_biquad_df2_fwd, dev, B, T, code, B, T, ptr(b_c), ptr(a_c), int(b.dim() == 3), ptr(zi_c),
+        _lib.call(fn, dev, B, T, code, B, T, ptr(b_c), ptr(a_c), int(b.dim() == 3), ptr(zi_c),
                   ptr(x_c), ptr(y), ptr(hp) if keep_states else None, ptr(zf),
                   ws_bytes=lib.ptb_lpv_biquad_workspace_bytes(code, B, T))
     elif B:
@@ -510,7 +511,7 @@ def _lpv_biquad_df2(b, a, zi, x, keep_states):
     return y, hp, zf
 
 
-def _lpv_biquad_df2_bwd(b, a, x, hp, gy, gzf, need_zi):
+def _lpv_biquad_bwd(fn, b, a, x, hp, gy, gzf, need_zi):
     dev = _lib.require_cuda(b, a, x, hp, gy, gzf)
     B, T = x.shape
     b_c, a_c, x_c, hp_c, gy_c, gzf_c = b.contiguous(), a.contiguous(), x.contiguous(), hp.contiguous(), \
@@ -523,7 +524,7 @@ def _lpv_biquad_df2_bwd(b, a, x, hp, gy, gzf, need_zi):
     gzi = x.new_empty(B, 2) if need_zi else x.new_empty(0)
     if B and T:
         code = _lib.dtype_code(x)
-        _lib.call(lib.ptb_lpv_biquad_df2_bwd, dev, B, T, code, B, T, ptr(b_c), ptr(a_c), int(b.dim() == 3), ptr(x_c),
+        _lib.call(fn, dev, B, T, code, B, T, ptr(b_c), ptr(a_c), int(b.dim() == 3), ptr(x_c),
                   ptr(hp_c), ptr(gy_c), ptr(gzf_c), ptr(gx), ptr(gb), ptr(ga), ptr(gzi) if need_zi else None,
                   ws_bytes=lib.ptb_lpv_biquad_workspace_bytes(code, B, T))
     elif need_zi:
@@ -531,22 +532,26 @@ def _lpv_biquad_df2_bwd(b, a, x, hp, gy, gzf, need_zi):
     return gb, ga, gzi, gx
 
 
-_LIB.impl("lpv_biquad_df2", _lpv_biquad_df2, "CUDA")
-_LIB.impl("lpv_biquad_df2_bwd", _lpv_biquad_df2_bwd, "CUDA")
-
-
-@torch.library.register_fake("philtorch_b200::lpv_biquad_df2")
-def _(b, a, zi, x, keep_states):
+def _lpv_fake_fwd(b, a, zi, x, keep_states):
     _check_lpv_biquad(b, a, zi, x)
     return (torch.empty_like(x, memory_format=torch.contiguous_format),
             x.new_empty((x.shape[0], x.shape[1], 2) if keep_states else (0,)), x.new_empty(x.shape[0], 2))
 
 
-@torch.library.register_fake("philtorch_b200::lpv_biquad_df2_bwd")
-def _(b, a, x, hp, gy, gzf, need_zi):
+def _lpv_fake_bwd(b, a, x, hp, gy, gzf, need_zi):
     return (x.new_empty(x.shape[0], x.shape[1], 3), x.new_empty(x.shape[0], x.shape[1], 2),
             x.new_empty(x.shape[0], 2) if need_zi else x.new_empty(0),
             torch.empty_like(x, memory_format=torch.contiguous_format))
+
+
+for _form, _ffn, _bfn in (("df2", lib.ptb_lpv_biquad_df2_fwd, lib.ptb_lpv_biquad_df2_bwd),
+                          ("tdf2", lib.ptb_lpv_biquad_tdf2_fwd, lib.ptb_lpv_biquad_tdf2_bwd)):
+    _LIB.impl(f"lpv_biquad_{_form}",
+              (lambda fn: lambda b, a, zi, x, keep: _lpv_biquad_fwd(fn, b, a, zi, x, keep))(_ffn), "CUDA")
+    _LIB.impl(f"lpv_biquad_{_form}_bwd",
+              (lambda fn: lambda b, a, x, hp, gy, gzf, nz: _lpv_biquad_bwd(fn, b, a, x, hp, gy, gzf, nz))(_bfn), "CUDA")
+    torch.library.register_fake(f"philtorch_b200::lpv_biquad_{_form}")(_lpv_fake_fwd)
+    torch.library.register_fake(f"philtorch_b200::lpv_biquad_{_form}_bwd")(_lpv_fake_bwd)
 
 
 # CPU (and any other backend) tensors: fail loudly instead of "no kernel registered" noise.
@@ -558,5 +563,6 @@ def _no_backend(name):
 
 for _name in ("lti_recur", "lti_recur_bwd", "lpv_recur", "lpv_recur_bwd", "lti_recur2", "lti_recur2_sx", "recur2",
               "recur2_sx", "lti_recur2_bwd", "recur2_bwd", "biquad_tdf2", "biquad_tdf2_bwd", "lpv_recur_carry", "lpv_recur_zero_carry",
-              "sos_cascade", "sos_cascade_bwd", "lpv_biquad_df2", "lpv_biquad_df2_bwd"):
+              "sos_cascade", "sos_cascade_bwd", "lpv_biquad_df2", "lpv_biquad_df2_bwd",
+              "lpv_biquad_tdf2", "lpv_biquad_tdf2_bwd"):
     _LIB.impl(_name, _no_backend(_name), "CPU")

@@ -12,7 +12,7 @@ DEV = "cuda"
 
 @pytest.fixture(autouse=True, params=[10**9, 1], ids=["scan+glue", "fused"])
 def df2_path(request, monkeypatch):
-    """Form 'df2' has two implementations, normally picked by the batch size: every case runs on both."""
+    """The filter has two implementations, normally picked by the batch size: every case runs on both."""
     from philtorch_b200.lpv import filtering
     monkeypatch.setattr(filtering, "FUSED_MIN_ROWS", request.param)
     return request.param
@@ -59,10 +59,11 @@ def test_one_dimensional_call_and_errors():
         ptb.lpv.lfilter(b.cpu(), a.cpu(), x.cpu())
 
 
+@pytest.mark.parametrize("form", ["df2", "tdf2"])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
 @pytest.mark.parametrize("B,T,shared", [(40, 5000, False), (33, 961, False), (64, 20003, False), (48, 7000, True),
                                         (130, 12000, False)])
-def test_fused_df2_matches_scan_path(dtype, B, T, shared, monkeypatch):
+def test_fused_matches_scan_path(form, dtype, B, T, shared, monkeypatch):
     """The fused kernels against the 2x2 scan kernels plus elementwise maps (pinned above to the
     reference) on batches, lengths (ragged, unaligned) and coefficient layouts the golden files lack."""
     from philtorch_b200.lpv import filtering
@@ -80,7 +81,7 @@ def test_fused_df2_matches_scan_path(dtype, B, T, shared, monkeypatch):
     for min_rows in (1, 10**9):
         monkeypatch.setattr(filtering, "FUSED_MIN_ROWS", min_rows)
         ins = [t.to(DEV).requires_grad_() for t in (b, a, x, zi)]
-        y, zf = ptb.lpv.lfilter(ins[0], ins[1], ins[2], zi=ins[3])
+        y, zf = ptb.lpv.lfilter(ins[0], ins[1], ins[2], zi=ins[3], form=form)
         outs.append((y, zf) + torch.autograd.grad([y, zf], ins, [gy.to(DEV), gzf.to(DEV)]))
     t = tol(dtype)
     for got, ref, name in zip(outs[0], outs[1], ("y", "zf", "grad_b", "grad_a", "grad_x", "grad_zi")):
