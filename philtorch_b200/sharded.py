@@ -18,6 +18,16 @@ all-gather of (P_r, adjoint end state), and a fix-up of grad_x / grad_a over a s
 
 The collectives are tiny (W x B x 2 scalars) and latency-bound; everything else is local, so a
 rank moves the same 12 + 20 bytes per sample as an unsharded run.
+
+Segments.  A handful of long rows is the kernels' worst case: tiles of one row depend on one
+another, so with B = 8 the single-pass scan runs at ~0.7 of the memory bandwidth.  The same
+algebra fixes that inside a rank: the local shard is cut into S segments per row, which the
+kernels see as B*S independent rows (a reshape, no copy); the segments' maps are folded exactly
+like the ranks' maps, and the fix-up runs over all segments at once.  S is chosen so that
+B*S >= 128 rows (``segments=None``) or given; S = 1 is the plain algorithm.  Without an
+initialised process group the function runs as a single rank, so it also serves one GPU.
+The folds over the segments stay on the device: they are queued behind the scan and cost nothing,
+whereas folding on the host would stall the stream twice per direction (measured slower).
 """
 from __future__ import annotations
 
@@ -109,54 +119,106 @@ def fixup_backward(k, a: Tensor, s_in: Tensor, y: Tensor, c: Tensor, gx: Tensor,
         hi, blk = lo, blk * 2
 
 
+SEGMENT_MIN_ROWS = 128        # segments are added until the kernels see at least this many rows ...
+SEGMENT_MIN_LENGTH = 1 << 18  # ... of at least this many samples
+
+
+def auto_segments(B: int, T: int, batched: bool) -> int:
+    if not batched:
+        return 1   # coefficients shared by the rows cannot be reshaped into more rows
+    S = 1
+    while B * S < SEGMENT_MIN_ROWS and T % (2 * S) == 0 and T // (2 * S) >= SEGMENT_MIN_LENGTH:
+        S *= 2
+    return S
+
+
+def _rank_world(group):
+    if group is None and not dist.is_initialized():
+        return 0, 1
+    return dist.get_rank(group), dist.get_world_size(group)
+
+
 class TimeShardedLPVRecurrence(Function):
     @staticmethod
-    def forward(ctx: Any, a: Tensor, zi: Tensor, x: Tensor, group, kernels) -> Tensor:
+    def forward(ctx: Any, a: Tensor, zi: Tensor, x: Tensor, group, kernels, segments) -> Tensor:
         k = kernels or _GpuKernels
-        rank, world = dist.get_rank(group), dist.get_world_size(group)
-        if world > 1:
-            y, carry = k.scan_zero(a, x)
-            carries = _all_gather(carry, group)
-            s = fold_carries_forward(carries, zi, rank).contiguous()
-            fixup_forward(k, a, y, s)
+        rank, world = _rank_world(group)
+        B, T = x.shape
+        S = segments if segments is not None else auto_segments(B, T, a.dim() == 2)
+        if S > 1 and (a.dim() != 2 or T % S != 0):
+            raise ValueError("segments need per-row coefficients (B, T) and a row length divisible by them")
+        L = T // S
+        av = a.contiguous().view(B * S, L) if S > 1 else a.contiguous()
+        xv = x.contiguous().view(B * S, L)
+        if world * S > 1:
+            y, carry = k.scan_zero(av, xv)                       # (B*S, L), (B*S, 2) = {prod a, y[:, -1]}
+            c = carry.view(B, S, 2)
+            P_tot, e_tot = torch.ones_like(c[:, 0, 0]), torch.zeros_like(c[:, 0, 0])
+            for j in range(S):                                    # this rank's total map
+                e_tot = c[:, j, 0] * e_tot + c[:, j, 1]
+                P_tot = c[:, j, 0] * P_tot
+            mine = torch.stack([P_tot, e_tot], dim=1)
+            carries = _all_gather(mine, group) if world > 1 else mine.unsqueeze(0)
+            s = fold_carries_forward(carries, zi, rank)
+            states = [s]                                          # states entering the segments
+            for j in range(S - 1):
+                states.append(c[:, j, 0] * states[-1] + c[:, j, 1])
+            s_v = torch.stack(states, dim=1).reshape(B * S).contiguous()
+            fixup_forward(k, av, y, s_v)
             ctx.P = carry[:, 0].contiguous()
         else:
-            s = zi.contiguous()
-            y = k.forward(a, s, x)
+            s_v = zi.contiguous()
+            y = k.forward(av, s_v, xv)
             ctx.P = None
-        ctx.group, ctx.kernels, ctx.rank, ctx.world = group, k, rank, world
-        ctx.save_for_backward(a, s, y)
-        return y
+        ctx.group, ctx.kernels, ctx.rank, ctx.world, ctx.S, ctx.shape = group, k, rank, world, S, (B, T)
+        ctx.a_shape = a.shape
+        ctx.save_for_backward(av, s_v, y)
+        return y.view(B, T)
 
     @staticmethod
     def backward(ctx: Any, gy: Tensor):
-        a, s, y = ctx.saved_tensors
-        k = ctx.kernels
+        av, s_v, y = ctx.saved_tensors
+        k, S, (B, T) = ctx.kernels, ctx.S, ctx.shape
         need_a, need_zi, need_x = ctx.needs_input_grad[:3]
-        gy = gy.contiguous()
-        ga, gs, gx = k.backward(a, s, y, gy, None, need_a)   # adjoint with nothing entering from the right
-        if ctx.world > 1:
-            carries = _all_gather(torch.stack([ctx.P, gs], dim=1), ctx.group)
-            c = fold_carries_backward(carries, ctx.rank)
-            if ctx.rank < ctx.world - 1:
-                fixup_backward(k, a, s, y, c, gx, ga if need_a else None)
-            gs = ctx.P * c + gs   # adjoint state leaving this shard on the left
+        gyv = gy.contiguous().view(B * S, T // S)
+        ga, gs, gx = k.backward(av, s_v, y, gyv, None, need_a)   # adjoint with nothing entering from the right
+        if ctx.world * S > 1:
+            P, g = ctx.P.view(B, S), gs.view(B, S)
+            P_tot, e_tot = torch.ones_like(P[:, 0]), torch.zeros_like(P[:, 0])
+            for j in range(S - 1, -1, -1):                        # this rank's total adjoint map, from the right
+                e_tot = P[:, j] * e_tot + g[:, j]
+                P_tot = P[:, j] * P_tot
+            mine = torch.stack([P_tot, e_tot], dim=1)
+            carries = _all_gather(mine, ctx.group) if ctx.world > 1 else mine.unsqueeze(0)
+            c = fold_carries_backward(carries, ctx.rank)          # adjoint entering this rank from the right
+            cs = [None] * S                                       # ... and each of its segments
+            cs[S - 1] = c
+            for j in range(S - 1, 0, -1):
+                cs[j - 1] = P[:, j] * cs[j] + g[:, j]
+            c_v = torch.stack(cs, dim=1).reshape(B * S).contiguous()
+            fixup_backward(k, av, s_v, y, c_v, gx, ga if need_a else None)
+            gs = P[:, 0] * cs[0] + g[:, 0]                        # adjoint state leaving this rank on the left
         # only rank 0's is the gradient of zi (sum over ranks = the gradient)
         gzi = gs if ctx.rank == 0 else torch.zeros_like(gs)
-        return (ga if need_a else None, gzi if need_zi else None, gx if need_x else None, None, None)
+        return (ga.view(ctx.a_shape) if need_a else None, gzi if need_zi else None,
+                gx.view(B, T) if need_x else None, None, None, None)
 
 
-def time_sharded_linear_recurrence(a: Tensor, zi: Tensor, x: Tensor, group=None, *, _kernels=None) -> Tensor:
+def time_sharded_linear_recurrence(a: Tensor, zi: Tensor, x: Tensor, group=None, *, segments=None,
+                                   _kernels=None) -> Tensor:
     """``lpv.linear_recurrence`` on a sequence whose time axis is sharded over ``group``.
 
     Args:
         a: this rank's coefficients, (B, T_local) (or (T_local,) shared by the batch).
         zi: initial state of the WHOLE sequence, (B,), identical on every rank.
         x: this rank's samples, (B, T_local).
-        group: process group (default: the world).  Ranks own consecutive time ranges in rank order.
+        group: process group (default: the world; without an initialised process group: one rank).
+            Ranks own consecutive time ranges in rank order.
+        segments: segments per row inside a rank (a power of two dividing T_local); default: as many
+            as give the kernels 128 rows, 1 for batches that are large enough.
 
     Returns:
         this rank's outputs, (B, T_local).  The gradient w.r.t. ``zi`` is returned on rank 0 and is
         zero elsewhere (sum over ranks = the gradient).
     """
-    return TimeShardedLPVRecurrence.apply(a, zi, x, group, _kernels)
+    return TimeShardedLPVRecurrence.apply(a, zi, x, group, _kernels, segments)

@@ -124,3 +124,32 @@ def test_real_ranks_nccl(tmp_path):
                          env=env, capture_output=True, text=True, timeout=300)
     assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
     assert "ERRS" in out.stdout
+
+
+@pytest.mark.parametrize("segments", [1, 4, 16])
+def test_single_gpu_segments(segments):
+    """One rank, its rows cut into segments that the kernels see as more rows: same results as the
+    plain kernels, for coefficients near one (the fix-up runs over several blocks) too."""
+    import philtorch_b200 as ptb
+    from philtorch_b200 import sharded
+
+    B, T = 4, 1 << 16
+    g = torch.Generator().manual_seed(5)
+    a = (0.9 + 0.0999 * torch.rand(B, T, generator=g)).cuda()
+    x = torch.randn(B, T, generator=g).cuda()
+    zi = torch.randn(B, generator=g).cuda()
+    gy = torch.randn(B, T, generator=g).cuda()
+    old = sharded.FIXUP_BLOCK
+    sharded.FIXUP_BLOCK = 1 << 10
+    try:
+        ins = [t.clone().requires_grad_() for t in (a, zi, x)]
+        y = sharded.time_sharded_linear_recurrence(ins[0], ins[1], ins[2], segments=segments)
+        ga, gzi, gx = torch.autograd.grad(y, ins, gy)
+    finally:
+        sharded.FIXUP_BLOCK = old
+    ref = [t.clone().requires_grad_() for t in (a, zi, x)]
+    y_r = ptb.lpv.linear_recurrence(ref[0], ref[1], ref[2])
+    ga_r, gzi_r, gx_r = torch.autograd.grad(y_r, ref, gy)
+    assert rel_err(y, y_r) <= 1e-4 and rel_err(gx, gx_r) <= 1e-4
+    assert rel_err(ga, ga_r) <= 1e-4 and rel_err(gzi, gzi_r) <= 1e-4
+    ptb.check_errors()
