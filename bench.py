@@ -268,8 +268,9 @@ def run_ours(args, rank: int, world: int, local_rank: int):
 
 def run_time_sharded(args, rank: int, world: int, local_rank: int):
     """Secondary line (not the headline metric): the long-sequence configuration, B = 8 rows of
-    T = 2^28 samples split along TIME over the ranks (strong scaling): per rank a carry pass, one
-    all-gather of (B,2) carries per direction, the seeded scan and the adjoint with its incoming state."""
+    T = 2^28 samples split along TIME over the ranks (strong scaling): per rank and direction one pass
+    over the shard (cut into segments the kernels see as rows), one all-gather of (B,2) maps when
+    there is more than one rank, and a fix-up over the few thousand samples the incoming state reaches."""
     import torch
     import torch.distributed as dist
 
@@ -314,7 +315,7 @@ def run_time_sharded(args, rank: int, world: int, local_rank: int):
                           "roofline": {"bound": "hbm", "achieved": 32 * Bl * Ttot / world / (ms * 1e-3) / 1e9,
                                        "peak": peak, "unit": "GB/s", "peak_source": f"{kind} copy bandwidth",
                                        "frac": 32 * Bl * Ttot / world / (ms * 1e-3) / 1e9 / peak,
-                                       "note": "algorithmic 32 B/sample per GPU; the carry passes are overhead"}}),
+                                       "note": "algorithmic 32 B/sample per GPU; folds and fix-ups are overhead"}}),
               flush=True)
     dist.destroy_process_group()
 

@@ -24,10 +24,11 @@ another, so with B = 8 the single-pass scan runs at ~0.7 of the memory bandwidth
 algebra fixes that inside a rank: the local shard is cut into S segments per row, which the
 kernels see as B*S independent rows (a reshape, no copy); the segments' maps are folded exactly
 like the ranks' maps, and the fix-up runs over all segments at once.  S is chosen so that
-B*S >= 128 rows (``segments=None``) or given; S = 1 is the plain algorithm.  Without an
+B*S >= 256 rows of at least 2^20 samples (``segments=None``) or given; S = 1 is the plain algorithm.  Without an
 initialised process group the function runs as a single rank, so it also serves one GPU.
-The folds over the segments stay on the device: they are queued behind the scan and cost nothing,
-whereas folding on the host would stall the stream twice per direction (measured slower).
+The fold over the segments is the same recurrence over the (B, S) maps and runs as one more
+launch of the kernel, queued behind the scan (folding on the host would stall the stream twice
+per direction, and a Python loop over the segments is launch-bound for S >= 32).
 """
 from __future__ import annotations
 
@@ -38,7 +39,12 @@ import torch.distributed as dist
 from torch import Tensor
 from torch.autograd import Function
 
-FIXUP_BLOCK = 1 << 16   # first fix-up block (samples); later blocks double
+FIXUP_BLOCK = 1 << 16     # first fix-up block (samples per row) at most; later blocks double
+FIXUP_SAMPLES = 1 << 20   # ... and about this many samples over all rows (more rows: shorter first block)
+
+
+def _first_block(rows: int) -> int:
+    return max(min(FIXUP_BLOCK, 1024), min(FIXUP_BLOCK, FIXUP_SAMPLES // max(rows, 1)))
 
 
 class _GpuKernels:
@@ -90,7 +96,7 @@ def _rows(a: Tensor, lo: int, hi: int) -> Tensor:
 def fixup_forward(k, a: Tensor, y: Tensor, s: Tensor) -> None:
     """In place: y[t] += (prod_{u<=t} a[u]) s, block by block until the correction has died out."""
     T = y.shape[1]
-    lo, blk = 0, FIXUP_BLOCK
+    lo, blk = 0, _first_block(y.shape[0])
     while lo < T:
         hi = min(T, lo + blk)
         z = k.forward(_rows(a, lo, hi), s.contiguous(), torch.zeros_like(y[:, lo:hi]))
@@ -105,7 +111,7 @@ def fixup_backward(k, a: Tensor, s_in: Tensor, y: Tensor, c: Tensor, gx: Tensor,
     """In place: adds to grad_x (and grad_a) the adjoint driven by the state ``c`` entering the shard
     from the right, suffix block by suffix block until it has died out."""
     T = y.shape[1]
-    hi, blk = T, FIXUP_BLOCK
+    hi, blk = T, _first_block(y.shape[0])
     while hi > 0:
         lo = max(0, hi - blk)
         y_prev = s_in if lo == 0 else y[:, lo - 1]
@@ -119,8 +125,8 @@ def fixup_backward(k, a: Tensor, s_in: Tensor, y: Tensor, c: Tensor, gx: Tensor,
         hi, blk = lo, blk * 2
 
 
-SEGMENT_MIN_ROWS = 128        # segments are added until the kernels see at least this many rows ...
-SEGMENT_MIN_LENGTH = 1 << 18  # ... of at least this many samples
+SEGMENT_MIN_ROWS = 256        # segments are added until the kernels see at least this many rows ...
+SEGMENT_MIN_LENGTH = 1 << 20  # ... of at least this many samples
 
 
 def auto_segments(B: int, T: int, batched: bool) -> int:
@@ -153,17 +159,18 @@ class TimeShardedLPVRecurrence(Function):
         if world * S > 1:
             y, carry = k.scan_zero(av, xv)                       # (B*S, L), (B*S, 2) = {prod a, y[:, -1]}
             c = carry.view(B, S, 2)
-            P_tot, e_tot = torch.ones_like(c[:, 0, 0]), torch.zeros_like(c[:, 0, 0])
-            for j in range(S):                                    # this rank's total map
-                e_tot = c[:, j, 0] * e_tot + c[:, j, 1]
-                P_tot = c[:, j, 0] * P_tot
-            mine = torch.stack([P_tot, e_tot], dim=1)
-            carries = _all_gather(mine, group) if world > 1 else mine.unsqueeze(0)
-            s = fold_carries_forward(carries, zi, rank)
-            states = [s]                                          # states entering the segments
-            for j in range(S - 1):
-                states.append(c[:, j, 0] * states[-1] + c[:, j, 1])
-            s_v = torch.stack(states, dim=1).reshape(B * S).contiguous()
+            P_seg, e_seg = c[:, :, 0].contiguous(), c[:, :, 1].contiguous()
+            if world > 1:                                         # this rank's total map, then the fold over ranks
+                e_tot = k.forward(P_seg, torch.zeros_like(zi), e_seg)[:, -1] if S > 1 else e_seg[:, 0]
+                mine = torch.stack([P_seg.prod(dim=1), e_tot], dim=1)
+                s = fold_carries_forward(_all_gather(mine, group), zi, rank)
+            else:
+                s = zi
+            states = s.reshape(B, 1)                              # states entering the segments: the same
+            if S > 1:                                             # recurrence over the segments' maps, one launch
+                after = k.forward(P_seg, s.contiguous(), e_seg)
+                states = torch.cat([states, after[:, :-1]], dim=1)
+            s_v = states.reshape(B * S).contiguous()
             fixup_forward(k, av, y, s_v)
             ctx.P = carry[:, 0].contiguous()
         else:
@@ -183,21 +190,20 @@ class TimeShardedLPVRecurrence(Function):
         gyv = gy.contiguous().view(B * S, T // S)
         ga, gs, gx = k.backward(av, s_v, y, gyv, None, need_a)   # adjoint with nothing entering from the right
         if ctx.world * S > 1:
-            P, g = ctx.P.view(B, S), gs.view(B, S)
-            P_tot, e_tot = torch.ones_like(P[:, 0]), torch.zeros_like(P[:, 0])
-            for j in range(S - 1, -1, -1):                        # this rank's total adjoint map, from the right
-                e_tot = P[:, j] * e_tot + g[:, j]
-                P_tot = P[:, j] * P_tot
-            mine = torch.stack([P_tot, e_tot], dim=1)
-            carries = _all_gather(mine, ctx.group) if ctx.world > 1 else mine.unsqueeze(0)
-            c = fold_carries_backward(carries, ctx.rank)          # adjoint entering this rank from the right
-            cs = [None] * S                                       # ... and each of its segments
-            cs[S - 1] = c
-            for j in range(S - 1, 0, -1):
-                cs[j - 1] = P[:, j] * cs[j] + g[:, j]
-            c_v = torch.stack(cs, dim=1).reshape(B * S).contiguous()
+            Pr = ctx.P.view(B, S).flip(1).contiguous()            # segments from the right
+            gr = gs.view(B, S).flip(1).contiguous()
+            zero = torch.zeros_like(gr[:, 0])
+            if ctx.world > 1:                                     # this rank's total adjoint map, then the fold
+                e_tot = k.forward(Pr, zero, gr)[:, -1] if S > 1 else gr[:, 0]
+                mine = torch.stack([Pr.prod(dim=1), e_tot], dim=1)
+                c = fold_carries_backward(_all_gather(mine, ctx.group), ctx.rank)
+            else:
+                c = zero
+            after = k.forward(Pr, c.contiguous(), gr)             # adjoint leaving each segment on its left
+            cs = torch.cat([c.reshape(B, 1), after[:, :-1]], dim=1).flip(1)   # ... = entering the one before it
+            c_v = cs.reshape(B * S).contiguous()
             fixup_backward(k, av, s_v, y, c_v, gx, ga if need_a else None)
-            gs = P[:, 0] * cs[0] + g[:, 0]                        # adjoint state leaving this rank on the left
+            gs = after[:, -1]                                     # adjoint state leaving this rank on the left
         # only rank 0's is the gradient of zi (sum over ranks = the gradient)
         gzi = gs if ctx.rank == 0 else torch.zeros_like(gs)
         return (ga.view(ctx.a_shape) if need_a else None, gzi if need_zi else None,
@@ -215,7 +221,7 @@ def time_sharded_linear_recurrence(a: Tensor, zi: Tensor, x: Tensor, group=None,
         group: process group (default: the world; without an initialised process group: one rank).
             Ranks own consecutive time ranges in rank order.
         segments: segments per row inside a rank (a power of two dividing T_local); default: as many
-            as give the kernels 128 rows, 1 for batches that are large enough.
+            as give the kernels 256 rows, 1 for batches that are large enough.
 
     Returns:
         this rank's outputs, (B, T_local).  The gradient w.r.t. ``zi`` is returned on rank 0 and is

@@ -39,7 +39,8 @@ def _worker(rank, world, port, B, T, q, slow_decay, segments=1):
         zi_l = zi.clone().requires_grad_()
         y = time_sharded_linear_recurrence(a_l, zi_l, x_l, segments=segments, _kernels=OracleKernels)
         ga, gzi, gx = torch.autograd.grad(y, (a_l, zi_l, x_l), gy[:, sl].contiguous())
-        q.put((rank, y.detach(), ga, gzi, gx))
+        # numpy arrays are pickled by value; a tensor travels as a file descriptor its sender must outlive
+        q.put((rank,) + tuple(t.detach().numpy() for t in (y, ga, gzi, gx)))
     finally:
         dist.destroy_process_group()
 
@@ -57,6 +58,7 @@ def test_two_rank_gloo(world, slow_decay, segments):
     for p in procs:
         p.start()
     res = sorted([q.get(timeout=60) for _ in range(world)], key=lambda t: t[0])
+    res = [(r[0],) + tuple(torch.from_numpy(v) for v in r[1:]) for r in res]
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
@@ -118,7 +120,8 @@ def test_single_process_segments(segments, slow_decay):
 def test_auto_segments():
     from philtorch_b200.sharded import auto_segments
 
-    assert auto_segments(8, 1 << 26, True) == 16
+    assert auto_segments(8, 1 << 26, True) == 32
     assert auto_segments(256, 1 << 20, True) == 1
     assert auto_segments(8, 1 << 26, False) == 1
-    assert auto_segments(8, 1 << 19, True) == 2      # segments stay at least 2^18 samples long
+    assert auto_segments(8, 1 << 22, True) == 4      # segments stay at least 2^20 samples long
+    assert auto_segments(8, 1 << 20, True) == 1
