@@ -8,7 +8,11 @@
  * synchronises nothing.
  *
  * Common conventions
- *   dtype        PTB_F32 or PTB_F64; all arrays of a call share it.
+ *   dtype        PTB_F32 or PTB_F64; all arrays of a call share it.  The first-order recurrences
+ *                (ptb_lti_recur_*, ptb_lpv_recur_fwd / _bwd) also take PTB_C64 / PTB_C128: arrays of
+ *                interleaved {re, im} pairs, element counts unchanged; their adjoint uses conj(a) and
+ *                grad_a = sum g[t] conj(y[t-1]) as the reference's autograd Function does
+ *                (philtorch/lti/recur.py:31-57).
  *   recurrence   y[-1] := zi, y[t] = A[t] * y[t-1] + x[t], t = 0..T-1: the coefficient with time
  *                index t multiplies the PREVIOUS state (philtorch/csrc/host_recurN.cpp:254-255).
  *   *_batched    1: the array has a leading batch axis of length B; 0: one copy shared by all rows.
@@ -30,7 +34,8 @@ extern "C" {
 
 typedef void* ptb_stream_t; /* a cudaStream_t */
 
-enum { PTB_F32 = 0, PTB_F64 = 1 };
+enum { PTB_F32 = 0, PTB_F64 = 1,
+       PTB_C64 = 2, PTB_C128 = 3 /* interleaved {re, im}; first-order recurrences only */ };
 enum {
   PTB_OK = 0,
   PTB_ERR_ARG = 1,       /* null pointer, negative size, unknown dtype */

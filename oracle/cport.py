@@ -1,7 +1,7 @@
 """ctypes front-end of ``recur_oracle.c``.  TEST INFRASTRUCTURE ONLY.
 
-All functions take and return CPU ``torch`` tensors (fp32 or fp64, made contiguous
-here) with the shapes of the reference ops:
+All functions take and return CPU ``torch`` tensors (fp32 or fp64; the first-order
+routines also complex64 / complex128; made contiguous here) with the shapes of the reference ops:
 
 * ``lti_recur(a, zi, x)``     a: () | (1,) | (B,), zi: (B,), x: (B,T)
   -- philtorch/csrc/host_lti_recur.cpp:42-80
@@ -38,7 +38,11 @@ def _suf(t: torch.Tensor) -> str:
         return "f32"
     if t.dtype == torch.float64:
         return "f64"
-    raise TypeError(f"oracle handles fp32/fp64 only, got {t.dtype}")
+    if t.dtype == torch.complex64:
+        return "c64"
+    if t.dtype == torch.complex128:
+        return "c128"
+    raise TypeError(f"oracle handles fp32/fp64 (first order: also complex64/128), got {t.dtype}")
 
 
 def _p(t):
@@ -47,7 +51,7 @@ def _p(t):
 
 def _c(t: torch.Tensor) -> torch.Tensor:
     assert t.device.type == "cpu"
-    return t.detach().contiguous()
+    return t.detach().resolve_conj().contiguous()
 
 
 def _i64(v):

@@ -175,3 +175,76 @@
 
 DEFINE_ALL(float, f32)
 DEFINE_ALL(double, f64)
+
+/*
+ * Complex first-order recurrences (complex64 / complex128, C99 _Complex = interleaved {re, im}).
+ * The reference dispatches its first-order ops over complex types as well
+ * (philtorch/csrc/host_lti_recur.cpp:61-78, philtorch/csrc/host_recurN.cpp:259-281) and its
+ * autograd rule conjugates the coefficient and the saved states
+ * (philtorch/lti/recur.py:31-57: recursion on a.conj_physical(), grad_init = g[0]*conj(a),
+ * grad_a = vecdot(y_prev, g) = sum conj(y[t-1])*g[t]).
+ */
+#include <complex.h>
+
+#define DEFINE_CX(S, SUF, CONJ)                                                                  \
+  void CAT(oracle_lti_recur_, SUF)(int64_t B, int64_t T, const S *a, int a_batched,              \
+                                   const S *zi, const S *x, S *y) {                              \
+    _Pragma("omp parallel for") for (int64_t b = 0; b < B; ++b) {                                \
+      const S ab = a_batched ? a[b] : a[0];                                                      \
+      S h = zi[b];                                                                               \
+      for (int64_t t = 0; t < T; ++t) {                                                          \
+        h = x[b * T + t] + ab * h;                                                               \
+        y[b * T + t] = h;                                                                        \
+      }                                                                                          \
+    }                                                                                            \
+  }                                                                                              \
+  void CAT(oracle_lti_recur_bwd_, SUF)(int64_t B, int64_t T, const S *a, int a_batched,          \
+                                       const S *zi, const S *y, const S *gy, const S *g_in,      \
+                                       S *grad_x, S *grad_a, S *grad_zi) {                       \
+    if (!a_batched) grad_a[0] = 0;                                                               \
+    for (int64_t b = 0; b < B; ++b) {                                                            \
+      const S ab = CONJ(a_batched ? a[b] : a[0]);                                                \
+      S c = g_in ? g_in[b] : (S)0;                                                               \
+      S acc = 0;                                                                                 \
+      for (int64_t t = T - 1; t >= 0; --t) {                                                     \
+        const S g = gy[b * T + t] + c;                                                           \
+        grad_x[b * T + t] = g;                                                                   \
+        const S yp = (t == 0) ? zi[b] : y[b * T + t - 1];                                        \
+        acc += CONJ(yp) * g;                                                                     \
+        c = ab * g;                                                                              \
+      }                                                                                          \
+      grad_zi[b] = c;                                                                            \
+      if (a_batched) grad_a[b] = acc; else grad_a[0] += acc;                                     \
+    }                                                                                            \
+  }                                                                                              \
+  void CAT(oracle_recur1_, SUF)(int64_t B, int64_t T, const S *a, int a_batched, const S *zi,    \
+                                const S *x, S *y) {                                              \
+    _Pragma("omp parallel for") for (int64_t b = 0; b < B; ++b) {                                \
+      const S *ab = a_batched ? a + b * T : a;                                                   \
+      S h = zi[b];                                                                               \
+      for (int64_t t = 0; t < T; ++t) {                                                          \
+        h = x[b * T + t] + ab[t] * h;                                                            \
+        y[b * T + t] = h;                                                                        \
+      }                                                                                          \
+    }                                                                                            \
+  }                                                                                              \
+  void CAT(oracle_recur1_bwd_, SUF)(int64_t B, int64_t T, const S *a, int a_batched,             \
+                                    const S *zi, const S *y, const S *gy, const S *g_in,         \
+                                    S *grad_x, S *grad_a, S *grad_zi) {                          \
+    if (!a_batched) for (int64_t t = 0; t < T; ++t) grad_a[t] = 0;                               \
+    for (int64_t b = 0; b < B; ++b) {                                                            \
+      const S *ab = a_batched ? a + b * T : a;                                                   \
+      S c = g_in ? g_in[b] : (S)0;                                                               \
+      for (int64_t t = T - 1; t >= 0; --t) {                                                     \
+        const S g = gy[b * T + t] + c;                                                           \
+        grad_x[b * T + t] = g;                                                                   \
+        const S yp = (t == 0) ? zi[b] : y[b * T + t - 1];                                        \
+        if (a_batched) grad_a[b * T + t] = g * CONJ(yp); else grad_a[t] += g * CONJ(yp);         \
+        c = CONJ(ab[t]) * g;                                                                     \
+      }                                                                                          \
+      grad_zi[b] = c;                                                                            \
+    }                                                                                            \
+  }
+
+DEFINE_CX(float _Complex, c64, conjf)
+DEFINE_CX(double _Complex, c128, conj)

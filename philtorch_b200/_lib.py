@@ -15,7 +15,9 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("PHILTORCH_B200_LIB") or os.path.join(_HERE, "libphiltorch_b200.so")
 
 PTB_F32, PTB_F64 = 0, 1
+PTB_C64, PTB_C128 = 2, 3
 _DTYPES = {torch.float32: PTB_F32, torch.float64: PTB_F64}
+_COMPLEX_DTYPES = {torch.complex64: PTB_C64, torch.complex128: PTB_C128}
 
 if not os.path.exists(LIB_PATH):
     raise ImportError(
@@ -96,11 +98,15 @@ ERROR_BITS = {1: "look-back wait expired", 2: "tile load wait expired", 4: "tile
               8: "pipeline wait expired"}
 
 
-def dtype_code(t: torch.Tensor) -> int:
+def dtype_code(t: torch.Tensor, complex_ok: bool = False) -> int:
+    """dtype code of the C ABI; complex64/complex128 only where the kernels have them (first order)."""
+    if complex_ok and t.dtype in _COMPLEX_DTYPES:
+        return _COMPLEX_DTYPES[t.dtype]
     try:
         return _DTYPES[t.dtype]
     except KeyError:
-        raise RuntimeError(f"philtorch_b200 kernels support float32 and float64, got {t.dtype}") from None
+        kinds = "float32, float64, complex64 and complex128" if complex_ok else "float32 and float64"
+        raise RuntimeError(f"these philtorch_b200 kernels support {kinds}, got {t.dtype}") from None
 
 
 def require_cuda(*tensors: torch.Tensor) -> torch.device:

@@ -54,14 +54,16 @@ class LTIRecurrence(Function):
             ga, gi, gx = _ops.lti_recur_bwd(a, init, out, grad_out, None, need_a, need_init)
             return _none_if_empty(ga, need_a), _none_if_empty(gi, need_init), _none_if_empty(gx, need_x)
         # differentiable form: the adjoint is the same recurrence on the reversed sequence
-        g = LTIRecurrence.apply(a, torch.zeros_like(init), grad_out.flip(1)).flip(1)
+        # (complex data: on conj(a), with conj(y[t-1]) in the coefficient gradient; .conj() of a real
+        # tensor is the tensor itself)
+        g = LTIRecurrence.apply(a.conj(), torch.zeros_like(init), grad_out.flip(1)).flip(1)
         grad_a = grad_init = grad_x = None
         if need_init:
-            grad_init = g[:, 0] * a
+            grad_init = g[:, 0] * a.conj()
         if need_x:
             grad_x = g
         if need_a:
-            prod = _prev_states(init, out) * g
+            prod = _prev_states(init, out).conj() * g
             grad_a = prod.sum(1) if (a.dim() == 1 and a.shape[0] == out.shape[0] and a.shape[0] > 1) \
                 else prod.sum().reshape(a.shape)
         return grad_a, grad_init, grad_x
@@ -97,15 +99,15 @@ class LPVRecurrence(Function):
             ga, gi, gx = _ops.lpv_recur_bwd(a, init, out, grad_out, None, need_a, need_init)
             return _none_if_empty(ga, need_a), _none_if_empty(gi, need_init), _none_if_empty(gx, need_x)
         # g[t] = a[t+1] g[t+1] + gy[t]: coefficients shifted by one sample, then reversed
-        a_rev = torch.roll(a, shifts=-1, dims=-1).flip(-1)
+        a_rev = torch.roll(a.conj(), shifts=-1, dims=-1).flip(-1)
         g = LPVRecurrence.apply(a_rev, torch.zeros_like(init), grad_out.flip(1)).flip(1)
         grad_a = grad_init = grad_x = None
         if need_init:
-            grad_init = g[:, 0] * a[..., 0]
+            grad_init = g[:, 0] * a[..., 0].conj()
         if need_x:
             grad_x = g
         if need_a:
-            grad_a = _prev_states(init, out) * g
+            grad_a = _prev_states(init, out).conj() * g
             if a.dim() == 1:
                 grad_a = grad_a.sum(0)
         return grad_a, grad_init, grad_x

@@ -3,6 +3,7 @@
 #include "launch.cuh"
 
 #include "biquad.cuh"
+#include "first_order_host.cuh"
 #include "so_small.cuh"
 
 namespace ptb {
@@ -10,92 +11,15 @@ namespace ptb {
 int biquad_chain_bwd(int dtype, int64_t B, int64_t T, const void* b, const void* a, int coef_batched, const void* x,
                      const void* y, const void* gy, const void* g_zf, void* grad_x, void* grad_b, void* grad_a,
                      void* grad_zi, void* ws, int64_t wsb, uint32_t* status, cudaStream_t st);
+// complex first-order recurrences (capi_cx.cu)
+int cx_fo_fwd(int dtype, int lpv, int64_t B, int64_t T, const void* a, int a_batched, const void* zi, int zi_batched,
+              const void* x, void* y, void* zf, void* ws, int64_t wsb, uint32_t* status, cudaStream_t st);
+int cx_fo_bwd(int dtype, int lpv, int64_t B, int64_t T, const void* a, int a_batched, const void* zi, int zi_batched,
+              const void* y, const void* gy, const void* g_in, void* grad_x, void* grad_a, void* grad_zi, void* ws,
+              int64_t wsb, uint32_t* status, cudaStream_t st);
 }  // namespace ptb
 
 namespace ptb {
-
-// ---------------------------------------------------------------------------- first order
-// Tile geometry: an ODD number of 16-byte units per thread and array (bank-conflict-free strided
-// access), large tiles (tens of KB per bulk copy are the most DRAM-efficient), one CTA per SM with
-// 2-4 stages filling its shared memory.
-// (16-byte units per thread and array, stages, CTAs per SM); overridable for tuning experiments
-#ifndef PTB_FO_FWD_CH
-#define PTB_FO_FWD_CH 9
-#define PTB_FO_FWD_STAGES 3
-#define PTB_FO_FWD_CTAS 1
-#endif
-#ifndef PTB_FO_LBW
-#define PTB_FO_LBW 1   // look-back warps per CTA: 1, or one per stage
-#endif
-#ifndef PTB_FO_BWD_CH
-#define PTB_FO_BWD_CH 5
-#define PTB_FO_BWD_STAGES 3
-#define PTB_FO_BWD_CTAS 1
-#endif
-// time-invariant variants stage fewer arrays per tile: larger tiles / more stages fill shared memory
-#ifndef PTB_FOLTI_FWD_CH
-#define PTB_FOLTI_FWD_CH 13
-#define PTB_FOLTI_FWD_STAGES 4
-#define PTB_FOLTI_FWD_CTAS 1
-#endif
-#ifndef PTB_FOLTI_BWD_CH
-#define PTB_FOLTI_BWD_CH 9
-#define PTB_FOLTI_BWD_STAGES 3
-#define PTB_FOLTI_BWD_CTAS 1
-#endif
-template <class S, bool LPV> struct FoFwdSel { using type = FoFwd<S, PTB_FO_FWD_CH, PTB_FO_FWD_STAGES, PTB_FO_FWD_CTAS, 1, true>; };
-template <class S> struct FoFwdSel<S, false> { using type = FoFwd<S, PTB_FOLTI_FWD_CH, PTB_FOLTI_FWD_STAGES, PTB_FOLTI_FWD_CTAS, 1, false>; };
-template <class S, bool LPV> struct FoBwdSel { using type = FoBwd<S, PTB_FO_BWD_CH, PTB_FO_BWD_STAGES, PTB_FO_BWD_CTAS, 1, true>; };
-template <class S> struct FoBwdSel<S, false> { using type = FoBwd<S, PTB_FOLTI_BWD_CH, PTB_FOLTI_BWD_STAGES, PTB_FOLTI_BWD_CTAS, 1, false>; };
-template <class S, bool LPV> using FoFwdP = typename FoFwdSel<S, LPV>::type;
-template <class S, bool LPV> using FoBwdP = typename FoBwdSel<S, LPV>::type;
-
-template <class S, bool LPV>
-static int fo_fwd(int64_t B, int64_t T, const void* a, int a_batched, const void* zi, int zi_batched,
-                  const void* x, void* y, void* zf, void* ws, int64_t wsb, uint32_t* status, cudaStream_t st) {
-  using P = FoFwdP<S, LPV>;
-  typename P::Params p;
-  p.a = static_cast<const S*>(a);
-  p.a_row_stride = a_batched ? (LPV ? T : 1) : 0;
-  p.zi = static_cast<const S*>(zi);
-  p.zi_stride = zi_batched ? 1 : 0;
-  p.x = static_cast<const S*>(x);
-  p.y = static_cast<S*>(y);
-  p.zf = static_cast<S*>(zf);
-  p.T = T;
-  const bool bulk = aligned16(x) && aligned16(y) && (!LPV || aligned16(a)) && (T * sizeof(S)) % 16 == 0;
-  return launch_scan<P>(p, B, T, bulk, ws, wsb, status, st, nullptr, nullptr);
-}
-
-template <class S, bool LPV>
-static int fo_bwd(int64_t B, int64_t T, const void* a, int a_batched, const void* zi, int zi_batched,
-                  const void* y, const void* gy, const void* g_in, void* grad_x, void* grad_a, void* grad_zi,
-                  void* ws, int64_t wsb, uint32_t* status, cudaStream_t st) {
-  using P = FoBwdP<S, LPV>;
-  typename P::Params p;
-  p.a = static_cast<const S*>(a);
-  p.a_row_stride = a_batched ? (LPV ? T : 1) : 0;
-  p.zi = static_cast<const S*>(zi);
-  p.zi_stride = zi_batched ? 1 : 0;
-  p.y = static_cast<const S*>(y);
-  p.gy = static_cast<const S*>(gy);
-  p.g_in = static_cast<const S*>(g_in);
-  p.grad_x = static_cast<S*>(grad_x);
-  p.grad_a = LPV ? static_cast<S*>(grad_a) : nullptr;
-  p.grad_zi = static_cast<S*>(grad_zi);
-  p.T = T;
-  p.want_ga = grad_a != nullptr;
-  const bool bulk = aligned16(gy) && aligned16(grad_x) && (!LPV || aligned16(a)) &&
-                    (!p.want_ga || (aligned16(y) && (!LPV || aligned16(grad_a)))) &&
-                    (T * sizeof(S)) % 16 == 0;
-  void* partial = nullptr;
-  int64_t nchunks = 0;
-  int rc = launch_scan<P>(p, B, T, bulk, ws, wsb, status, st, &partial, &nchunks);
-  if (rc != PTB_OK) return rc;
-  if (!LPV && grad_a)
-    rc = launch_reduce<S, 1>(partial, B, nchunks, a_batched, StoreSums<S, 1>{static_cast<S*>(grad_a)}, st);
-  return rc;
-}
 
 template <class S, bool REV, bool WRITE = false>
 static int fo_carry(int64_t B, int64_t T, const void* a, int a_batched, const void* x, void* y, void* carry,
@@ -480,6 +404,9 @@ int ptb_lti_recur_fwd(int dtype, int64_t B, int64_t T, const void* a, int a_batc
   if (B < 0 || T < 0) return PTB_ERR_ARG;
   if (B == 0 || T == 0) return PTB_OK;
   if (!a || !zi || !x || !y) return PTB_ERR_ARG;
+  if (dtype == PTB_C64 || dtype == PTB_C128)
+    return cx_fo_fwd(dtype, 0, B, T, a, a_batched, zi, zi_batched, x, y, zf, workspace, workspace_bytes, status,
+                     (cudaStream_t)stream);
   PTB_DISPATCH(dtype, (fo_fwd<S, false>(B, T, a, a_batched, zi, zi_batched, x, y, zf, workspace,
                                         workspace_bytes, status, (cudaStream_t)stream)));
 }
@@ -490,6 +417,9 @@ int ptb_lpv_recur_fwd(int dtype, int64_t B, int64_t T, const void* a, int a_batc
   if (B < 0 || T < 0) return PTB_ERR_ARG;
   if (B == 0 || T == 0) return PTB_OK;
   if (!a || !zi || !x || !y) return PTB_ERR_ARG;
+  if (dtype == PTB_C64 || dtype == PTB_C128)
+    return cx_fo_fwd(dtype, 1, B, T, a, a_batched, zi, zi_batched, x, y, zf, workspace, workspace_bytes, status,
+                     (cudaStream_t)stream);
   PTB_DISPATCH(dtype, (fo_fwd<S, true>(B, T, a, a_batched, zi, zi_batched, x, y, zf, workspace,
                                        workspace_bytes, status, (cudaStream_t)stream)));
 }
@@ -579,6 +509,9 @@ int ptb_lti_recur_bwd(int dtype, int64_t B, int64_t T, const void* a, int a_batc
   if (B < 0 || T < 0) return PTB_ERR_ARG;
   if (B == 0 || T == 0) return PTB_OK;
   if (!a || !gy || !grad_x || (grad_a && (!y || !zi))) return PTB_ERR_ARG;
+  if (dtype == PTB_C64 || dtype == PTB_C128)
+    return cx_fo_bwd(dtype, 0, B, T, a, a_batched, zi, zi_batched, y, gy, g_in, grad_x, grad_a, grad_zi, workspace,
+                     workspace_bytes, status, (cudaStream_t)stream);
   PTB_DISPATCH(dtype, (fo_bwd<S, false>(B, T, a, a_batched, zi, zi_batched, y, gy, g_in, grad_x, grad_a,
                                         grad_zi, workspace, workspace_bytes, status, (cudaStream_t)stream)));
 }
@@ -590,6 +523,9 @@ int ptb_lpv_recur_bwd(int dtype, int64_t B, int64_t T, const void* a, int a_batc
   if (B < 0 || T < 0) return PTB_ERR_ARG;
   if (B == 0 || T == 0) return PTB_OK;
   if (!a || !gy || !grad_x || (grad_a && (!y || !zi))) return PTB_ERR_ARG;
+  if (dtype == PTB_C64 || dtype == PTB_C128)
+    return cx_fo_bwd(dtype, 1, B, T, a, a_batched, zi, zi_batched, y, gy, g_in, grad_x, grad_a, grad_zi, workspace,
+                     workspace_bytes, status, (cudaStream_t)stream);
   PTB_DISPATCH(dtype, (fo_bwd<S, true>(B, T, a, a_batched, zi, zi_batched, y, gy, g_in, grad_x, grad_a,
                                        grad_zi, workspace, workspace_bytes, status, (cudaStream_t)stream)));
 }

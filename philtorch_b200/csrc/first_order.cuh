@@ -3,6 +3,7 @@
 // and its adjoint
 //     g[t] = gy[t] + c[t+1],  c[t] = a[t] * g[t],  c[T] = g_in (0 unless the row continues to the right)
 //     grad_x = g,  grad_a[t] = g[t] * y[t-1],  grad_zi = c[0].
+// For complex scalars (Cx<float>, Cx<double>) the adjoint uses conj(a) and conj(y[t-1]).
 // LPV = true : a is per sample, (B,T) or (T,) (row stride 0)
 // LPV = false: a is per row, (B,) or a single value (row stride 0); grad_a is a sum over time,
 //              emitted as one partial per tile and reduced by reduce_partials_kernel.
@@ -21,7 +22,28 @@ template <class S> struct Vec16;
 template <> struct Vec16<float> { using type = float4; static constexpr int V = 4; };
 template <> struct Vec16<double> { using type = double2; static constexpr int V = 2; };
 
+template <> struct Vec16<Cx<float>> { using type = float4; static constexpr int V = 2; };
+template <> struct Vec16<Cx<double>> { using type = double2; static constexpr int V = 1; };
+
 template <class S, int V> struct VecIO;
+template <> struct VecIO<Cx<float>, 2> {
+  static __device__ __forceinline__ void ld(const unsigned char* p, Cx<float>* r) {
+    const float4 q = *reinterpret_cast<const float4*>(p);
+    r[0] = Cx<float>(q.x, q.y); r[1] = Cx<float>(q.z, q.w);
+  }
+  static __device__ __forceinline__ void st(unsigned char* p, const Cx<float>* r) {
+    *reinterpret_cast<float4*>(p) = make_float4(r[0].re, r[0].im, r[1].re, r[1].im);
+  }
+};
+template <> struct VecIO<Cx<double>, 1> {
+  static __device__ __forceinline__ void ld(const unsigned char* p, Cx<double>* r) {
+    const double2 q = *reinterpret_cast<const double2*>(p);
+    r[0] = Cx<double>(q.x, q.y);
+  }
+  static __device__ __forceinline__ void st(unsigned char* p, const Cx<double>* r) {
+    *reinterpret_cast<double2*>(p) = make_double2(r[0].re, r[0].im);
+  }
+};
 template <> struct VecIO<float, 4> {
   static __device__ __forceinline__ void ld(const unsigned char* p, float* r) {
     const float4 q = *reinterpret_cast<const float4*>(p);
@@ -98,7 +120,7 @@ struct FoFwd : ScalarAffine<S> {
   static constexpr int ROWC_OFF = LPV ? 2 * SLOT : SLOT;
   static constexpr int STAGE_BYTES = ROWC_OFF + (LPV ? 0 : 128);
   static __device__ __forceinline__ void row_constants(const Params& p, int64_t row, S* out) {
-    out[0] = __ldg(p.a + row * p.a_row_stride);
+    out[0] = ld_ro(p.a + row * p.a_row_stride);
   }
 
   static __device__ __forceinline__ void plan(const Params& p, bool, int64_t row, int64_t t0, int nvalid,
@@ -109,7 +131,7 @@ struct FoFwd : ScalarAffine<S> {
     io.store(X_OFF, p.y + row * p.T + t0, bytes);
   }
   static __device__ __forceinline__ State row_init(const Params& p, int64_t row) {
-    State s; s.v[0] = __ldg(p.zi + row * p.zi_stride); return s;
+    State s; s.v[0] = ld_ro(p.zi + row * p.zi_stride); return s;
   }
   static __device__ __forceinline__ void row_final(const Params& p, int64_t row, const State& s) {
     if (p.zf) p.zf[row] = s.v[0];
@@ -209,7 +231,7 @@ struct FoBwd : ScalarAffine<S> {
   static constexpr int ROWC_OFF = HALO_OFF + 64;         // second half of the halo line
   static constexpr int STAGE_BYTES = (LPV ? 3 * SLOT : 2 * SLOT) + 128;
   static __device__ __forceinline__ void row_constants(const Params& p, int64_t row, S* out) {
-    out[0] = __ldg(p.a + row * p.a_row_stride);
+    out[0] = ld_ro(p.a + row * p.a_row_stride);
   }
 
   static __device__ __forceinline__ void plan(const Params& p, bool bulk, int64_t row, int64_t t0, int nvalid,
@@ -228,7 +250,7 @@ struct FoBwd : ScalarAffine<S> {
     if (LPV && p.want_ga) io.store(A_OFF, p.grad_a + row * p.T + t0, bytes);
   }
   static __device__ __forceinline__ State row_init(const Params& p, int64_t row) {
-    State s; s.v[0] = p.g_in ? __ldg(p.g_in + row) : S(0); return s;
+    State s; s.v[0] = p.g_in ? ld_ro(p.g_in + row) : S(0); return s;
   }
   static __device__ __forceinline__ void row_final(const Params& p, int64_t row, const State& s) {
     if (p.grad_zi) p.grad_zi[row] = s.v[0];
@@ -252,8 +274,10 @@ struct FoBwd : ScalarAffine<S> {
         const unsigned char* pa = stage + A_OFF + (size_t)p0 * sizeof(S);
 #pragma unroll
         for (int c = 0; c < CH; ++c) VecIO<S, V>::ld(pa + 16 * c, &a[c * V]);
+#pragma unroll
+        for (int j = 0; j < SPT; ++j) a[j] = cj(a[j]);   // the adjoint runs on conj(a) (no-op for reals)
       } else {
-        a[0] = *reinterpret_cast<const S*>(stage + ROWC_OFF);
+        a[0] = cj(*reinterpret_cast<const S*>(stage + ROWC_OFF));
       }
       if (nv < SPT) {
 #pragma unroll
@@ -286,7 +310,7 @@ struct FoBwd : ScalarAffine<S> {
       for (int c = 0; c < CH; ++c) VecIO<S, V>::ld(py + 16 * c, &y[c * V]);
       if (tpos > 0) yprev = *reinterpret_cast<const S*>(py - sizeof(S));
       else if (t0 > 0) yprev = *reinterpret_cast<const S*>(stage + HALO_OFF + 16 - sizeof(S));
-      else yprev = __ldg(p.zi + row * p.zi_stride);
+      else yprev = ld_ro(p.zi + row * p.zi_stride);
     }
     S c = in.v[0];
     S acc = S(0);
@@ -296,7 +320,7 @@ struct FoBwd : ScalarAffine<S> {
       r.g[j] = gj;
       c = r.coef(j) * gj;
       if (p.want_ga) {
-        const S yp = j > 0 ? y[j - 1] : yprev;
+        const S yp = cj(j > 0 ? y[j - 1] : yprev);
         if (LPV) y[j] = gj * yp;
         else if (j < r.nv) acc += gj * yp;
       }

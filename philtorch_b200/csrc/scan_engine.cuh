@@ -44,6 +44,7 @@
 // any decoupled look-back scan.
 #pragma once
 #include "ptx.cuh"
+#include "complex.cuh"
 
 #include <type_traits>
 
@@ -148,21 +149,21 @@ template <class T>
 __device__ __forceinline__ T shfl_up_pod(const T& x, int d) {
   T r;
 #pragma unroll
-  for (int i = 0; i < T::N; ++i) r.v[i] = __shfl_up_sync(0xffffffffu, x.v[i], d);
+  for (int i = 0; i < T::N; ++i) r.v[i] = shfl_up_s(x.v[i], d);
   return r;
 }
 template <class T>
 __device__ __forceinline__ T shfl_down_pod(const T& x, int d) {
   T r;
 #pragma unroll
-  for (int i = 0; i < T::N; ++i) r.v[i] = __shfl_down_sync(0xffffffffu, x.v[i], d);
+  for (int i = 0; i < T::N; ++i) r.v[i] = shfl_down_s(x.v[i], d);
   return r;
 }
 template <class T>
 __device__ __forceinline__ T shfl_pod(const T& x, int src) {
   T r;
 #pragma unroll
-  for (int i = 0; i < T::N; ++i) r.v[i] = __shfl_sync(0xffffffffu, x.v[i], src);
+  for (int i = 0; i < T::N; ++i) r.v[i] = shfl_s(x.v[i], src);
   return r;
 }
 

@@ -7,7 +7,7 @@ per-sample-coefficient op and fused adjoint ops, so a backward pass is one kerne
 flip/roll/cat copies around a second forward call.
 
 Every op runs the hand-written sm_100a kernels through the C ABI (``_lib``); CPU tensors and
-dtypes other than float32/float64 raise.
+dtypes other than float32/float64 (and, for the first-order recurrences, complex64/complex128) raise.
 """
 from __future__ import annotations
 
@@ -30,8 +30,13 @@ def _same_dtype(a: Tensor, zi: Tensor, x: Tensor) -> None:
         raise RuntimeError("A must have the same scalar type as input")
 
 
+def _dense(t: Tensor) -> Tensor:
+    """Dense memory holding the tensor's VALUES (a lazily conjugated complex view is materialised)."""
+    return t.resolve_conj().contiguous()
+
+
 def _opt(t: Optional[Tensor]) -> Optional[Tensor]:
-    return None if t is None else t.contiguous()
+    return None if t is None else _dense(t)
 
 
 # =============================================================================== first order, LTI
@@ -54,10 +59,10 @@ def _lti_recur(a: Tensor, zi: Tensor, x: Tensor) -> Tensor:
     dev = _lib.require_cuda(a, zi, x)
     _same_dtype(a, zi, x)
     B, T = x.shape
-    a_c, zi_c, x_c = a.contiguous(), zi.contiguous(), x.contiguous()
+    a_c, zi_c, x_c = _dense(a), _dense(zi), _dense(x)
     y = torch.empty_like(x_c)
     if B and T:
-        _lib.call(lib.ptb_lti_recur_fwd, dev, B, T, _lib.dtype_code(x), B, T, ptr(a_c),
+        _lib.call(lib.ptb_lti_recur_fwd, dev, B, T, _lib.dtype_code(x, True), B, T, ptr(a_c),
                   int(a.dim() == 1 and a.shape[0] == B), ptr(zi_c), 1, ptr(x_c), ptr(y), None)
     return y
 
@@ -65,12 +70,12 @@ def _lti_recur(a: Tensor, zi: Tensor, x: Tensor) -> Tensor:
 def _lti_recur_bwd(a, zi, y, gy, g_in, need_a, need_zi):
     dev = _lib.require_cuda(a, zi, y, gy, g_in)
     B, T = y.shape
-    a_c, zi_c, y_c, gy_c, gin_c = a.contiguous(), zi.contiguous(), y.contiguous(), gy.contiguous(), _opt(g_in)
+    a_c, zi_c, y_c, gy_c, gin_c = _dense(a), _dense(zi), _dense(y), _dense(gy), _opt(g_in)
     gx = torch.empty_like(y_c)
     ga = torch.zeros_like(a_c) if need_a else a.new_empty(0)
     gzi = torch.empty_like(zi_c) if need_zi else zi.new_empty(0)
     if B and T:
-        _lib.call(lib.ptb_lti_recur_bwd, dev, B, T, _lib.dtype_code(y), B, T, ptr(a_c),
+        _lib.call(lib.ptb_lti_recur_bwd, dev, B, T, _lib.dtype_code(y, True), B, T, ptr(a_c),
                   int(a.dim() == 1 and a.shape[0] == B), ptr(zi_c), 1, ptr(y_c), ptr(gy_c), ptr(gin_c),
                   ptr(gx), ptr(ga) if need_a else None, ptr(gzi) if need_zi else None)
     elif need_zi:
@@ -116,10 +121,10 @@ def _lpv_recur(a: Tensor, zi: Tensor, x: Tensor) -> Tensor:
     dev = _lib.require_cuda(a, zi, x)
     _same_dtype(a, zi, x)
     B, T = x.shape
-    a_c, zi_c, x_c = a.contiguous(), zi.contiguous(), x.contiguous()
+    a_c, zi_c, x_c = _dense(a), _dense(zi), _dense(x)
     y = torch.empty_like(x_c)
     if B and T:
-        _lib.call(lib.ptb_lpv_recur_fwd, dev, B, T, _lib.dtype_code(x), B, T, ptr(a_c), int(a.dim() == 2),
+        _lib.call(lib.ptb_lpv_recur_fwd, dev, B, T, _lib.dtype_code(x, True), B, T, ptr(a_c), int(a.dim() == 2),
                   ptr(zi_c), 1, ptr(x_c), ptr(y), None)
     return y
 
@@ -127,12 +132,12 @@ def _lpv_recur(a: Tensor, zi: Tensor, x: Tensor) -> Tensor:
 def _lpv_recur_bwd(a, zi, y, gy, g_in, need_a, need_zi):
     dev = _lib.require_cuda(a, zi, y, gy, g_in)
     B, T = y.shape
-    a_c, zi_c, y_c, gy_c, gin_c = a.contiguous(), zi.contiguous(), y.contiguous(), gy.contiguous(), _opt(g_in)
+    a_c, zi_c, y_c, gy_c, gin_c = _dense(a), _dense(zi), _dense(y), _dense(gy), _opt(g_in)
     gx = torch.empty_like(y_c)
     ga_rows = torch.empty_like(y_c) if need_a else a.new_empty(0)   # per-row, (B,T)
     gzi = torch.empty_like(zi_c) if need_zi else zi.new_empty(0)
     if B and T:
-        _lib.call(lib.ptb_lpv_recur_bwd, dev, B, T, _lib.dtype_code(y), B, T, ptr(a_c), int(a.dim() == 2),
+        _lib.call(lib.ptb_lpv_recur_bwd, dev, B, T, _lib.dtype_code(y, True), B, T, ptr(a_c), int(a.dim() == 2),
                   ptr(zi_c), 1, ptr(y_c), ptr(gy_c), ptr(gin_c), ptr(gx),
                   ptr(ga_rows) if need_a else None, ptr(gzi) if need_zi else None)
     elif need_zi:

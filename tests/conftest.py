@@ -28,13 +28,14 @@ def pytest_collection_modifyitems(config, items):
 def load_golden(name):
     """Golden vectors produced by running the reference (tests/golden/make_golden.py)."""
     with np.load(os.path.join(GOLDEN, name + ".npz")) as z:
-        return {k: torch.from_numpy(np.asarray(z[k])) for k in z.files if np.asarray(z[k]).dtype.kind in "fiub"}
+        return {k: torch.from_numpy(np.asarray(z[k])) for k in z.files if np.asarray(z[k]).dtype.kind in "fiubc"}
 
 
 def rel_err(out, ref):
     """max|out - ref| / max|ref|: the parity metric of the path (<=1e-4 fp32, <=1e-10 fp64)."""
-    out = out.detach().double().cpu()
-    ref = ref.detach().double().cpu()
+    wide = torch.complex128 if (out.is_complex() or ref.is_complex()) else torch.float64
+    out = out.detach().resolve_conj().to(wide).cpu()
+    ref = ref.detach().resolve_conj().to(wide).cpu()
     assert out.shape == ref.shape, (out.shape, ref.shape)
     if ref.numel() == 0:
         return 0.0
@@ -43,4 +44,4 @@ def rel_err(out, ref):
 
 
 def tol(dtype):
-    return 1e-4 if dtype == torch.float32 else 1e-10
+    return 1e-4 if dtype in (torch.float32, torch.complex64) else 1e-10

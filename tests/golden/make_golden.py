@@ -107,8 +107,51 @@ def lpv_lfilter_cases(pt):
                      gy=_np(gy), case=np.array(f"philtorch.lpv.lfilter(backend='ssm', unroll_factor={uf})"), **out)
 
 
+def complex_first_order_cases(pt):
+    """Complex first-order recurrences: the reference's ``LTIRecurrence`` (op ``lti_recur``, which
+    ``diag_state_space`` runs on complex poles) with its conjugating backward, and the per-sample
+    form through ``MatrixRecurrence`` with 1x1 matrices."""
+    from philtorch.lti.recur import LTIRecurrence
+    from philtorch.lpv.ssm import MatrixRecurrence
+
+    torch.manual_seed(20240611)
+
+    def poles(shape, rdt):
+        r = 0.2 + 0.79 * torch.rand(*shape, dtype=rdt)
+        return torch.polar(r, 2 * np.pi * torch.rand(*shape, dtype=rdt))
+
+    for dt, rdt, tag in ((torch.complex128, torch.float64, "c128"), (torch.complex64, torch.float32, "c64")):
+        for mode in ("batched", "shared1", "scalar"):
+            B, T = 3, 101
+            a = poles((B if mode == "batched" else 1,), rdt)
+            if mode == "scalar":
+                a = a[0]
+            a = a.clone().requires_grad_()
+            zi = torch.randn(B, dtype=dt, requires_grad=True)
+            x = torch.randn(B, T, dtype=dt, requires_grad=True)
+            gy = torch.randn(B, T, dtype=dt)
+            y = LTIRecurrence.apply(a, zi, x)
+            ga, gzi, gx = grads(y, gy, a, zi, x)
+            save(f"lti_recur_{mode}_{tag}", a=_np(a), zi=_np(zi), x=_np(x), gy=_np(gy), y=_np(y),
+                 grad_a=ga, grad_zi=gzi, grad_x=gx)
+        for mode in ("batched", "shared"):
+            B, T = 3, 257
+            a = poles((B, T) if mode == "batched" else (T,), rdt).requires_grad_()
+            zi = torch.randn(B, dtype=dt, requires_grad=True)
+            x = torch.randn(B, T, dtype=dt, requires_grad=True)
+            gy = torch.randn(B, T, dtype=dt)
+            y = MatrixRecurrence.apply(a[..., None, None], zi[:, None], x[..., None])[..., 0]
+            ga, gzi, gx = grads(y, gy, a, zi, x)
+            y_loop = pt.lpv.linear_recurrence(a.detach(), zi.detach(), x.detach())
+            save(f"lpv_recur1_{mode}_{tag}", a=_np(a), zi=_np(zi), x=_np(x), gy=_np(gy), y=_np(y),
+                 y_python_loop=_np(y_loop), grad_a=ga, grad_zi=gzi, grad_x=gx)
+
+
 def main():
     pt = import_reference()
+    if len(sys.argv) > 1 and sys.argv[1] == "complex":       # only this group
+        complex_first_order_cases(pt)
+        return
     if len(sys.argv) > 1 and sys.argv[1] == "lpv_lfilter":   # only this group (the others are unchanged)
         lpv_lfilter_cases(pt)
         return

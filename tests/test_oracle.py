@@ -38,6 +38,25 @@ def test_recur1_golden(tag, mode):
     assert rel_err(gx, g["grad_x"]) <= t
 
 
+@pytest.mark.parametrize("tag,dtype", [("c64", torch.complex64), ("c128", torch.complex128)])
+def test_complex_first_order_golden(tag, dtype):
+    """The complex restatement (conjugating adjoint) against vectors made by the reference's
+    ``LTIRecurrence`` / 1x1 ``MatrixRecurrence`` on complex data."""
+    t = tol(dtype)
+    for mode in ("batched", "shared1", "scalar"):
+        g = load_golden(f"lti_recur_{mode}_{tag}")
+        assert g["y"].dtype == dtype
+        assert rel_err(cport.lti_recur(g["a"], g["zi"], g["x"]), g["y"]) <= t
+        ga, gzi, gx = cport.lti_recur_bwd(g["a"], g["zi"], g["y"], g["gy"])
+        assert rel_err(ga, g["grad_a"]) <= t and rel_err(gzi, g["grad_zi"]) <= t and rel_err(gx, g["grad_x"]) <= t
+    for mode in ("batched", "shared"):
+        g = load_golden(f"lpv_recur1_{mode}_{tag}")
+        y = cport.recur1(g["a"], g["zi"], g["x"])
+        assert rel_err(y, g["y"]) <= t and rel_err(y, g["y_python_loop"]) <= t
+        ga, gzi, gx = cport.recur1_bwd(g["a"], g["zi"], g["y"], g["gy"])
+        assert rel_err(ga, g["grad_a"]) <= t and rel_err(gzi, g["grad_zi"]) <= t and rel_err(gx, g["grad_x"]) <= t
+
+
 @pytest.mark.parametrize("tag", ["f32", "f64"])
 @pytest.mark.parametrize("mode", ["batched", "shared"])
 @pytest.mark.parametrize("kind", ["lti", "lpv"])
