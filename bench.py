@@ -458,6 +458,43 @@ def run_lpv_lfilter(args):
                     36 + 60, {})
 
 
+def run_complex_poles(args):
+    """Secondary line: complex first-order recurrence, the inner call of ``diag_state_space`` on
+    complex poles: 256 rows (e.g. 64 signals x 4 poles) of 2^19 complex samples, forward + backward
+    with gradients for the poles and x; complex64, or complex128 with --f64.  With --per-sample the
+    poles vary per sample (the per-sample-coefficient kernels)."""
+    import math
+
+    import torch
+
+    import philtorch_b200 as ptb
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    rdt = torch.float64 if args.f64 else torch.float32
+    Bc, Tc = (args.rows if args.rows != B else 256), 1 << 19
+    g = torch.Generator(device=dev).manual_seed(SEED_LPV + 1)
+    shape = (Bc, Tc) if args.per_sample else (Bc,)
+    a = torch.polar(0.9 + 0.099 * torch.rand(*shape, device=dev, generator=g, dtype=rdt),
+                    2 * math.pi * torch.rand(*shape, device=dev, generator=g, dtype=rdt)).requires_grad_()
+    x = torch.view_as_complex(torch.randn(Bc, Tc, 2, device=dev, generator=g, dtype=rdt)).requires_grad_()
+    gy = torch.view_as_complex(torch.randn(Bc, Tc, 2, device=dev, generator=g, dtype=rdt))
+    zi = torch.zeros(Bc, device=dev, dtype=x.dtype)
+    fn = ptb.lpv.linear_recurrence if args.per_sample else ptb.lti.linear_recurrence
+
+    def step():
+        return torch.autograd.grad(fn(a, zi, x), (a, x), gy)
+
+    ms = _timed(step, args, dev)
+    ptb.check_errors(dev)
+    s = 16 if args.f64 else 8
+    units = (3 + 5) if args.per_sample else (2 + 3)   # arrays read or written, forward + backward
+    name = "complex128" if args.f64 else "complex64"
+    _secondary_line(args, f"complex first-order {'per-sample' if args.per_sample else 'time-invariant'} recurrence "
+                          f"fwd+bwd (grads a, x), {name}, B={Bc}, T=2^19", Bc * Tc, ms, units * s,
+                    {"dtype": "c128" if args.f64 else "c64"})
+
+
 SEED_LPV = 1240
 
 
@@ -477,7 +514,10 @@ def main():
                     help="secondary workload: LPV 2x2 state-space recursion, B=128, T=2^20 (one GPU)")
     ap.add_argument("--lpv-lfilter", action="store_true",
                     help="secondary workload: time-varying second-order lfilter, B=128, T=2^20 (one GPU)")
-    ap.add_argument("--f64", action="store_true", help="float64 for --state-space")
+    ap.add_argument("--f64", action="store_true", help="float64 for --state-space, complex128 for --complex-poles")
+    ap.add_argument("--complex-poles", action="store_true",
+                    help="secondary workload: complex first-order recurrence, B=256, T=2^19 (one GPU)")
+    ap.add_argument("--per-sample", action="store_true", help="--complex-poles with per-sample coefficients")
     ap.add_argument("--sos-cascade", action="store_true",
                     help="secondary workload: six fused second-order sections, B=512, T=2^18 (one GPU)")
     args = ap.parse_args()
@@ -487,9 +527,12 @@ def main():
     if args.impl == "reference":
         run_reference_arm(args, rank)
         return
-    if args.sos_cascade or args.state_space or args.lpv_lfilter:
+    secondary = [fn for flag, fn in ((args.sos_cascade, run_sos_cascade), (args.state_space, run_state_space),
+                                     (args.lpv_lfilter, run_lpv_lfilter), (args.complex_poles, run_complex_poles))
+                 if flag]
+    if secondary:
         if rank == 0:
-            (run_sos_cascade if args.sos_cascade else run_state_space if args.state_space else run_lpv_lfilter)(args)
+            secondary[0](args)
         return
     if args.time_sharded:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")

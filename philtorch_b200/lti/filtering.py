@@ -16,9 +16,60 @@ from torch import Tensor
 from ..autograd import BiquadTDF2, SOSCascade
 from ..ops import SOS_CASCADE_SIZES
 from ..mat import companion
+from .recur import linear_recurrence
 from .ssm import state_space
 
-__all__ = ["lfilter", "filtfilt", "lfilter_zi", "sosfilt"]
+__all__ = ["lfilter", "filtfilt", "lfilter_zi", "sosfilt", "comb_filter"]
+
+
+def comb_filter(a: Tensor, delay: int, x: Tensor, zi: Optional[Tensor] = None, **kwargs):
+    """Feedback comb filter ``y[t] = x[t] - a * y[t - delay]`` (philtorch/lti/filtering.py:15-71).
+
+    The ``delay`` interleaved phases of a row are independent first-order recurrences with the
+    coefficient ``-a``: the signal is folded to ``B * delay`` rows of ``ceil(N / delay)`` samples
+    and runs through the first-order time-invariant kernel (forward and adjoint).
+
+    Args:
+        a: feedback coefficient, shape () (shared) or (B,).
+        delay: the delay in samples, >= 1.
+        x: input, shape (B, N).
+        zi: the last ``delay`` outputs before the signal, oldest last, shape (delay,) or (B, delay).
+        **kwargs: accepted for compatibility (``unroll_factor``).
+
+    Returns:
+        y of shape (B, N); for ``delay > 1`` and a given ``zi`` the pair ``(y, zf)`` with
+        ``zf = y[:, -delay:]`` reversed, as the reference does (with ``delay == 1`` it returns y
+        alone, also with a ``zi``).
+    """
+    assert a.dim() <= 1, "Denominator coefficients a must be at most 1D."
+    assert x.dim() == 2, "Input signal x must be 2D."
+    assert delay >= 0, "Delay must be non-negative."
+    if a.dim() == 1:
+        assert a.size(0) == x.size(0), "The first dimension of a must match the batch size of x."
+    if delay == 1:
+        return linear_recurrence(-a, torch.zeros_like(a) if zi is None else zi.squeeze(-1), x, **kwargs)
+
+    batch, n = x.shape
+    tail = (-n) % delay
+    if tail:
+        x = F.pad(x, (0, tail))
+    phases = x.view(batch, -1, delay).transpose(1, 2).reshape(batch * delay, -1)   # row b*delay + d: phase d of row b
+    if a.dim() == 1:
+        a = a.repeat_interleave(delay)
+    return_zf = zi is not None
+    if zi is None:
+        zi = torch.zeros_like(a)
+    elif zi.dim() == 1:
+        zi = zi.flip(0).repeat(batch)
+    else:
+        zi = zi.flip(1).flatten()
+    y = linear_recurrence(-a, zi, phases, **kwargs)
+    y = y.view(batch, delay, -1).transpose(1, 2).reshape(batch, -1)
+    if tail:
+        y = y[:, :-tail]
+    if return_zf:
+        return y, y[:, -delay:].flip(1)
+    return y
 
 
 def _pad_to_order2(b: Tensor, a: Tensor):

@@ -147,8 +147,55 @@ def complex_first_order_cases(pt):
                  y_python_loop=_np(y_loop), grad_a=ga, grad_zi=gzi, grad_x=gx)
 
 
+def first_order_caller_cases(pt):
+    """Callers that are pure first-order passes: ``cspline`` / ``cubic_spline``
+    (philtorch/lti/interp.py) and ``comb_filter`` (philtorch/lti/filtering.py)."""
+    from philtorch.lti.interp import cspline, cubic_spline
+    from philtorch.lti import comb_filter
+
+    torch.manual_seed(20240612)
+    for dt, tag in ((torch.float64, "f64"), (torch.float32, "f32")):
+        out = {}
+        x = torch.randn(3, 61, dtype=dt, requires_grad=True)
+        gy = torch.randn(3, 61, dtype=dt)
+        out["x"], out["gy"] = _np(x), _np(gy)
+        for pfe in (True, False):
+            for sp in (True, False):
+                c = cspline(x, parallel_form=pfe, scipy_padding=sp)
+                key = f"{'parallel' if pfe else 'cascade'}_{'scipy' if sp else 'reflect'}"
+                out["c_" + key] = _np(c)
+                out["grad_x_" + key] = grads(c, gy, x)[0]
+        for m in (2, 3, 7):
+            for sp in (True, False):
+                y = cubic_spline(x, m, scipy_padding=sp)
+                gu = torch.linspace(-1, 1, y.shape[1], dtype=dt).expand_as(y)
+                key = f"m{m}_{'scipy' if sp else 'reflect'}"
+                out["up_" + key] = _np(y)
+                out["up_grad_x_" + key] = grads(y, gu, x)[0]
+        save(f"cspline_{tag}", **out)
+
+    B, T = 5, 97
+    for dt, tag in ((torch.float64, "f64"), (torch.float32, "f32")):
+        for delay, zi_shape in ((1, None), (5, None), (13, (13,)), (5, (5, 5)), (32, None)):
+            for batched in (True, False):
+                a = (torch.rand(B, dtype=dt) * 1.8 - 0.9) if batched else (torch.rand((), dtype=dt) * 1.8 - 0.9)
+                a = a.clone().requires_grad_()
+                x = torch.randn(B, T, dtype=dt, requires_grad=True)
+                gy = torch.randn(B, T, dtype=dt)
+                zi = torch.randn(*zi_shape, dtype=dt) if zi_shape else None
+                res = comb_filter(a, delay, x, zi=zi)
+                y, zf = res if isinstance(res, tuple) else (res, None)
+                ga, gx = grads(y, gy, a, x)
+                zs = "none" if zi is None else ("shared" if zi.dim() == 1 else "batched")
+                save(f"comb_d{delay}_zi{zs}_{'batched' if batched else 'scalar'}_{tag}", a=_np(a), x=_np(x), gy=_np(gy),
+                     zi=_np(zi), y=_np(y), zf=_np(zf), grad_a=ga, grad_x=gx)
+
+
 def main():
     pt = import_reference()
+    if len(sys.argv) > 1 and sys.argv[1] == "callers":       # only this group
+        first_order_caller_cases(pt)
+        return
     if len(sys.argv) > 1 and sys.argv[1] == "complex":       # only this group
         complex_first_order_cases(pt)
         return

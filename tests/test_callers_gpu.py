@@ -1,0 +1,115 @@
+"""GPU parity of the callers that are pure first-order passes: ``lti.comb_filter`` and
+``lti.interp.cspline`` / ``cubic_spline``, against the golden vectors made by running the reference
+(outputs and gradients), the numpy restatements in oracle/callers.py at larger sizes, and scipy
+(the reference's own check, tests/test_interp.py).  Tolerance: max|out-ref|/max|ref| <= 1e-4 (fp32),
+<= 1e-10 (fp64)."""
+import numpy as np
+import pytest
+import torch
+
+import philtorch_b200 as ptb
+from philtorch_b200.lti import comb_filter
+from philtorch_b200.lti.interp import cspline, cubic_spline
+from conftest import load_golden, rel_err, tol
+from oracle import callers
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+DT = {"f32": torch.float32, "f64": torch.float64}
+COMB_CASES = [(1, "none"), (5, "none"), (13, "shared"), (5, "batched"), (32, "none")]
+
+
+@pytest.mark.parametrize("tag", ["f32", "f64"])
+@pytest.mark.parametrize("delay,zs", COMB_CASES)
+@pytest.mark.parametrize("mode", ["batched", "scalar"])
+def test_comb_golden(tag, delay, zs, mode):
+    g = load_golden(f"comb_d{delay}_zi{zs}_{mode}_{tag}")
+    t = tol(DT[tag])
+    a = g["a"].to(DEV).requires_grad_()
+    x = g["x"].to(DEV).requires_grad_()
+    zi = g["zi"].to(DEV) if "zi" in g else None
+    res = comb_filter(a, delay, x, zi=zi)
+    if zi is not None and delay > 1:
+        y, zf = res
+        assert rel_err(zf, g["zf"]) <= t
+    else:
+        y = res
+    ga, gx = torch.autograd.grad(y, (a, x), g["gy"].to(DEV))
+    ptb.check_errors()
+    assert rel_err(y, g["y"]) <= t
+    assert rel_err(ga, g["grad_a"]) <= t
+    assert rel_err(gx, g["grad_x"]) <= t
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+@pytest.mark.parametrize("delay,n", [(2, 50001), (7, 30000), (100, 100000), (1000, 65536), (4096, 10000)])
+def test_comb_sizes(dtype, delay, n):
+    g = torch.Generator().manual_seed(delay)
+    rows = 6
+    a = (torch.rand(rows, generator=g, dtype=torch.float64) * 1.9 - 0.95).to(dtype)
+    x = torch.randn(rows, n, generator=g, dtype=torch.float64).to(dtype)
+    zi = torch.randn(rows, delay, generator=g, dtype=torch.float64).to(dtype)
+    y, zf = comb_filter(a.to(DEV), delay, x.to(DEV), zi=zi.to(DEV))
+    ptb.check_errors()
+    ref = torch.from_numpy(callers.comb_filter(a.numpy(), delay, x.numpy(), zi.numpy()))
+    assert rel_err(y, ref) <= tol(dtype)
+    assert rel_err(zf, ref[:, -delay:].flip(1)) <= tol(dtype)
+
+
+def test_comb_argument_checks():
+    x = torch.zeros(4, 100, device=DEV)
+    with pytest.raises(AssertionError, match="at most 1D"):
+        comb_filter(torch.zeros(4, 1, device=DEV), 3, x)
+    with pytest.raises(AssertionError, match="must be 2D"):
+        comb_filter(torch.zeros(4, device=DEV), 3, x[0])
+    with pytest.raises(AssertionError, match="batch size"):
+        comb_filter(torch.zeros(3, device=DEV), 3, x)
+
+
+@pytest.mark.parametrize("tag", ["f32", "f64"])
+def test_cspline_golden(tag):
+    g = load_golden(f"cspline_{tag}")
+    t = tol(DT[tag])
+    x = g["x"].to(DEV).requires_grad_()
+    gy = g["gy"].to(DEV)
+    for form, pfe in (("parallel", True), ("cascade", False)):
+        for pad, sp in (("scipy", True), ("reflect", False)):
+            c = cspline(x, parallel_form=pfe, scipy_padding=sp)
+            (gx,) = torch.autograd.grad(c, x, gy)
+            assert rel_err(c, g[f"c_{form}_{pad}"]) <= t
+            assert rel_err(gx, g[f"grad_x_{form}_{pad}"]) <= t
+    for m in (2, 3, 7):
+        for pad, sp in (("scipy", True), ("reflect", False)):
+            y = cubic_spline(x, m, scipy_padding=sp)
+            gu = torch.linspace(-1, 1, y.shape[1], dtype=y.dtype, device=DEV).expand_as(y)
+            (gx,) = torch.autograd.grad(y, x, gu)
+            assert rel_err(y, g[f"up_m{m}_{pad}"]) <= t
+            assert rel_err(gx, g[f"up_grad_x_m{m}_{pad}"]) <= t
+    ptb.check_errors()
+    assert cubic_spline(x, 1) is x
+    with pytest.raises(NotImplementedError):
+        cspline(x, lamb=0.1)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+@pytest.mark.parametrize("n", [20, 100, 20000])
+@pytest.mark.parametrize("pfe", [True, False])
+def test_cspline_scipy(dtype, n, pfe):
+    """As tests/test_interp.py:60-70 of the reference: the coefficients of scipy.signal.cspline1d."""
+    from scipy.signal import cspline1d
+    x = torch.randn(3, n, dtype=torch.float64, generator=torch.Generator().manual_seed(n))
+    c = cspline(x.to(dtype).to(DEV), parallel_form=pfe, scipy_padding=True)
+    ref = torch.from_numpy(np.stack([cspline1d(row) for row in x.to(dtype).double().numpy()]))
+    assert rel_err(c, ref) <= tol(dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+@pytest.mark.parametrize("m", [2, 5])
+@pytest.mark.parametrize("scipy_padding", [True, False])
+def test_cubic_spline_sizes(dtype, m, scipy_padding):
+    x = torch.randn(5, 30000, dtype=torch.float64, generator=torch.Generator().manual_seed(m)).to(dtype)
+    y = cubic_spline(x.to(DEV), m, scipy_padding=scipy_padding)
+    ptb.check_errors()
+    ref = torch.from_numpy(callers.cubic_spline(x.double().numpy(), m, scipy_padding))
+    assert rel_err(y, ref) <= tol(dtype)
+    assert rel_err(y[:, ::m], x) <= tol(dtype)        # the spline interpolates the samples

@@ -141,3 +141,40 @@ def test_against_reference_extension(dtype):
         assert rel_err(y, refext.recur2(A, zi2, x2)) <= t
         for o, r in zip(cport.recur2_bwd(A, zi2, y, gy2), refext.recur2_bwd(A, zi2, y, gy2)):
             assert rel_err(o, r) <= t
+
+
+# ---- callers that are pure first-order passes (numpy restatements in oracle/callers.py) ----------
+COMB_CASES = [(1, "none"), (5, "none"), (13, "shared"), (5, "batched"), (32, "none")]
+
+
+@pytest.mark.parametrize("delay,zs", COMB_CASES)
+@pytest.mark.parametrize("mode", ["batched", "scalar"])
+def test_comb_oracle_golden(delay, zs, mode):
+    from oracle import callers
+    g = load_golden(f"comb_d{delay}_zi{zs}_{mode}_f64")
+    zi = g.get("zi")
+    y = callers.comb_filter(g["a"].numpy(), delay, g["x"].numpy(), None if zi is None else zi.numpy())
+    assert rel_err(torch.from_numpy(y), g["y"]) <= 1e-12
+
+
+@pytest.mark.parametrize("scipy_padding", [True, False])
+def test_cspline_oracle_golden(scipy_padding):
+    from oracle import callers
+    g = load_golden("cspline_f64")
+    pad = "scipy" if scipy_padding else "reflect"
+    c = torch.from_numpy(callers.cspline(g["x"].numpy(), scipy_padding))
+    assert rel_err(c, g[f"c_parallel_{pad}"]) <= 1e-12
+    assert rel_err(c, g[f"c_cascade_{pad}"]) <= 1e-12     # the reference's two evaluations agree
+    for m in (2, 3, 7):
+        y = torch.from_numpy(callers.cubic_spline(g["x"].numpy(), m, scipy_padding))
+        assert rel_err(y, g[f"up_m{m}_{pad}"]) <= 1e-12
+
+
+def test_cspline_oracle_scipy():
+    """The check the reference's own test makes (tests/test_interp.py:60-70)."""
+    from scipy.signal import cspline1d
+    from oracle import callers
+    x = torch.randn(4, 200, dtype=torch.float64, generator=torch.Generator().manual_seed(1)).numpy()
+    c = callers.cspline(x, True)
+    for row in range(4):
+        assert abs(c[row] - cspline1d(x[row])).max() <= 1e-10
