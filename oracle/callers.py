@@ -70,3 +70,22 @@ def cubic_spline(x, m: int, scipy_padding: bool):
         idx = base + k
         y += ext[:, idx + 1] * _beta3(t - idx)
     return y
+
+
+def state_space(A, x, B, C, D=None, zi=None):
+    """Sequential h[t+1] = A h[t] + B x[t], y[t] = C h[t] + D x[t] for x (rows, N), B (M,), C (M,),
+    A (M, M) or (rows, M, M): what philtorch/lti/ssm.py:590-850 (``diag_state_space``) evaluates in
+    the eigenbasis, restated in the original basis.  Returns (y, final state)."""
+    A = np.asarray(A, dtype=np.float64)
+    x = np.asarray(x, dtype=np.float64)
+    B, C = np.asarray(B, dtype=np.float64), np.asarray(C, dtype=np.float64)
+    rows, n = x.shape
+    M = A.shape[-1]
+    h = np.zeros((rows, M)) if zi is None else np.broadcast_to(np.asarray(zi, dtype=np.float64), (rows, M)).copy()
+    y = np.empty((rows, n))
+    for t in range(n):
+        y[:, t] = h @ C
+        h = (np.einsum("rij,rj->ri", A, h) if A.ndim == 3 else h @ A.T) + x[:, t:t + 1] * B
+    if D is not None:
+        y = y + np.asarray(D, dtype=np.float64) * x
+    return y, h

@@ -14,7 +14,8 @@ from torch import Tensor
 
 from ..autograd import LTIMatrixRecurrence, LTIRecurrence, matrix_recurrence_scalar_input
 
-__all__ = ["LTIMatrixRecurrence", "state_space_recursion", "state_space", "extension_backend_indicator"]
+__all__ = ["LTIMatrixRecurrence", "state_space_recursion", "state_space", "diag_state_space",
+           "extension_backend_indicator"]
 
 
 def extension_backend_indicator(x: Tensor, M: int) -> bool:
@@ -161,5 +162,118 @@ def state_space(A: Tensor, x: Tensor, B: Optional[Tensor] = None, C: Optional[Te
         zf = None
         h = _ext_ss_recur(A, zi, Bx, out_idx=out_idx)
         h = torch.cat([zi[:, None, out_idx], h[:, :-1]], dim=1)
+    y = _output_map(h, x, C, D, batch_size, M)
+    return (y, zf) if return_zf else y
+
+
+def _eigen_basis(L: Optional[Tensor], V: Optional[Tensor], Vinv: Optional[Tensor], A: Optional[Tensor],
+                 x: Tensor, batch_size: int):
+    """Eigenvalues (M,) | (batch, M), eigenvectors and their inverse, M -- with the argument
+    contract of philtorch/lti/ssm.py:640-721."""
+    if L is None:
+        assert A is not None, "Either L or A must be provided"
+        assert A.dim() in (2, 3), f"State matrix A must be 2D or 3D, got {A.shape}"
+        assert A.size(-2) == A.size(-1), f"State matrix A must be square, got {A.shape}"
+        if A.dim() == 3:
+            assert x.size(0) == A.size(0), \
+                f"Batch size of A must match batch size of x, got A: {A.size(0)}, x: {x.size(0)}"
+        L, V = torch.linalg.eig(A)
+        return L, V, torch.linalg.inv(V), A.size(-1)
+    if L.dim() == 1:
+        M, nd, lead = L.size(0), 2, ()
+    elif L.dim() == 2 and L.size(0) == batch_size:
+        M, nd, lead = L.size(1), 3, (batch_size,)
+        assert not (V is None and Vinv is None), "P and Vinv cannot both be None when L is a batch of vectors"
+    else:
+        raise ValueError(f"L must be a vector or a batch of vectors, got {L.shape}")
+    for name, mat in (("P", V), ("Vinv", Vinv), ("A", A)):
+        if mat is not None:
+            assert mat.dim() == nd, f"{name} must be {nd}D, got {mat.shape}"
+            assert tuple(mat.shape) == lead + (M, M), f"{name} must be square with size {M}, got {mat.shape}"
+    if V is None and Vinv is None:
+        if A is None:      # scalar modes: the states are the modes themselves
+            V = Vinv = torch.eye(M, device=x.device, dtype=x.dtype)
+        elif M == 1:
+            V = Vinv = torch.ones(lead + (1, 1), device=x.device, dtype=L.dtype)
+        else:              # eigenvectors of A for the given eigenvalues: null vectors of A - l I
+            # (columns scaled to a unit first entry; V V^-1 cancels any scaling)
+            eye = torch.eye(M, device=A.device, dtype=L.dtype)
+            shifted = A.to(L.dtype).unsqueeze(-3) - L[..., None, None] * eye          # (..., M, M, M)
+            rest = torch.linalg.lstsq(shifted[..., 1:], -shifted[..., :1]).solution    # (..., M, M-1, 1)
+            V = torch.cat([torch.ones_like(rest[..., :1, 0]), rest[..., 0]], dim=-1).mT
+            Vinv = torch.linalg.inv(V)
+    elif V is None:
+        V = torch.linalg.inv(Vinv)
+    elif Vinv is None:
+        Vinv = torch.linalg.inv(V)
+    return L, V, Vinv, M
+
+
+def diag_state_space(x: Tensor, L: Optional[Tensor] = None, V: Optional[Tensor] = None,
+                     Vinv: Optional[Tensor] = None, A: Optional[Tensor] = None, B: Optional[Tensor] = None,
+                     C: Optional[Tensor] = None, D: Optional[Tensor] = None, zi: Optional[Tensor] = None,
+                     out_idx: Optional[int] = None, unroll_factor: Optional[int] = None):
+    """State-space model evaluated in the eigenbasis ``A = V diag(L) V^-1`` (signature and argument
+    contract of philtorch/lti/ssm.py:590-850).
+
+    In that basis the M states are independent first-order recurrences with the (in general
+    complex) poles ``L``: ``batch * M`` rows of the first-order time-invariant kernel, complex64 /
+    complex128 when the poles are.  Input and output maps are folded into the basis first
+    (``V^-1 B`` before, ``C V`` after the recurrence), so nothing of size (batch, N, M) is formed
+    unless the states themselves are the result.  Returns ``y``, or ``(y, zf)`` when ``zi`` is given.
+    ``unroll_factor`` is accepted for compatibility and ignored.
+    """
+    assert x.dim() in (2, 3), f"Input signal must be 2D or 3D (batch, time, [features]), got {x.shape}"
+    if not (C is None or out_idx is None):
+        raise ValueError("C and out_idx cannot be used together. Use either C or out_idx.")
+    batch_size, N = x.size(0), x.size(1)
+    L, V, Vinv, M = _eigen_basis(L, V, Vinv, A, x, batch_size)
+    return_zf = zi is not None
+    if zi is None:
+        zi = x.new_zeros(batch_size, M)
+    elif zi.dim() == 1:
+        zi = zi.unsqueeze(0).expand(batch_size, -1)
+    cdt = torch.promote_types(torch.promote_types(L.dtype, Vinv.dtype), x.dtype)   # complex as soon as the basis is
+    Lc, Vc, Vic, xc, zc = L.to(cdt), V.to(cdt), Vinv.to(cdt), x.to(cdt), zi.to(cdt)
+
+    # ---- into the eigenbasis: w0 = V^-1 zi, u[b, m, t] = (V^-1 B x[b, t])[m]
+    w0 = (Vic @ zc.unsqueeze(-1)).squeeze(-1)                                   # (batch, M)
+    if B is None:
+        G = Vic[..., 0] if x.dim() == 2 else Vic        # the input enters state 0 / x carries M features
+    else:
+        Bc = B.to(cdt)
+        shp = tuple(B.shape)
+        if shp == (M,):
+            G = Vic @ Bc                                 # (M,) | (batch, M)
+        elif shp == (batch_size, M):
+            assert x.dim() == 2, f"Input signal x must be 2D when B is of shape {(batch_size, M)}, got {x.shape}"
+            G = (Vic @ Bc.unsqueeze(-1)).squeeze(-1)     # (batch, M)
+        elif B.dim() in (2, 3) and shp[-2] == M:
+            G = Vic @ Bc                                 # (M, features) | (batch, M, features)
+        else:
+            features = -1 if x.dim() == 2 else x.size(-1)
+            raise ValueError(f"Input matrix B must be of shape ({M},), ({batch_size}, {M}), ({M}, {features}) or "
+                             f"({batch_size}, {M}, {features}), got {shp}")
+    if x.dim() == 2 and tuple(G.shape) in ((M,), (batch_size, M)):
+        u = G.unsqueeze(-1) * xc.unsqueeze(1)            # (batch, M, N) without a transpose
+    else:
+        u = _input_map(xc, G, batch_size, M).mT
+    u = u.expand(batch_size, M, N).reshape(batch_size * M, N)
+    poles = Lc.expand(batch_size, M).reshape(-1)
+    w = LTIRecurrence.apply(poles, w0.reshape(-1).contiguous(), u).view(batch_size, M, N)
+
+    # ---- back: the state BEFORE sample t is h[t] = V [w0, w[0], ..., w[N-2]][t]
+    real_out = C is not None and not C.is_complex()
+    zf = None
+    if return_zf:
+        zf = (Vc @ w[:, :, -1:]).squeeze(-1)
+        zf = zf.real if real_out else zf
+    w_prev = torch.cat([w0.unsqueeze(-1), w[:, :, :-1]], dim=2)                 # (batch, M, N)
+    if out_idx is not None:
+        h = (Vc[..., out_idx, None, :] @ w_prev).squeeze(-2)                    # (batch, N)
+    else:
+        h = (Vc @ w_prev).mT                                                    # (batch, N, M)
+    if real_out:
+        h = h.real
     y = _output_map(h, x, C, D, batch_size, M)
     return (y, zf) if return_zf else y

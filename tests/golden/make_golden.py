@@ -191,8 +191,62 @@ def first_order_caller_cases(pt):
                      zi=_np(zi), y=_np(y), zf=_np(zf), grad_a=ga, grad_x=gx)
 
 
+def diag_state_space_cases(pt):
+    """``philtorch.lti.diag_state_space`` (philtorch/lti/ssm.py:590-850): real matrices with complex
+    eigenvalues, given eigen-decompositions, vector inputs, a selected state."""
+    from philtorch.lti import diag_state_space
+
+    torch.manual_seed(20240613)
+    Bn, N, M = 5, 97, 3
+
+    def stable(*lead):
+        A = torch.randn(*lead, M, M, dtype=torch.float64)
+        return A / (1.1 * torch.linalg.eigvals(A).abs().amax(-1)[..., None, None])
+
+    for dt, tag in ((torch.float64, "f64"), (torch.float32, "f32")):
+        cdt = torch.complex128 if dt == torch.float64 else torch.complex64
+        # (1) real system from its matrix: B (M,), C (M,), scalar D, zi per row
+        A = stable().to(dt).requires_grad_()
+        x = torch.randn(Bn, N, dtype=dt, requires_grad=True)
+        Bm = torch.randn(M, dtype=dt, requires_grad=True)
+        Cm = torch.randn(M, dtype=dt, requires_grad=True)
+        Dm = torch.randn(1, dtype=dt)
+        zi = torch.randn(Bn, M, dtype=dt)
+        gy = torch.randn(Bn, N, dtype=dt)
+        y, zf = diag_state_space(x, A=A, B=Bm, C=Cm, D=Dm, zi=zi, unroll_factor=1)   # 1: its compiled op
+        gA, gx, gB, gC = grads(y, gy, A, x, Bm, Cm)
+        save(f"diag_ssm_matrix_{tag}", A=_np(A), x=_np(x), B=_np(Bm), C=_np(Cm), D=_np(Dm), zi=_np(zi), gy=_np(gy),
+             y=_np(y), zf=_np(zf), grad_A=gA, grad_x=gx, grad_B=gB, grad_C=gC)
+        # (2) batched eigen-decomposition given: complex L (batch, M), V (batch, M, M); vector input and output
+        Ab = stable(Bn)
+        Lb, Vb = torch.linalg.eig(Ab)
+        Lb, Vb = Lb.to(cdt).requires_grad_(), Vb.to(cdt)
+        x3 = torch.randn(Bn, N, 2, dtype=dt, requires_grad=True)
+        B3 = torch.randn(M, 2, dtype=dt)
+        C3 = torch.randn(2, M, dtype=dt)
+        gy3 = torch.randn(Bn, N, 2, dtype=dt)
+        y3 = diag_state_space(x3, L=Lb, V=Vb, B=B3, C=C3, unroll_factor=1)
+        gL, gx3 = grads(y3, gy3, Lb, x3)
+        save(f"diag_ssm_eig_batched_{tag}", L=_np(Lb), V=_np(Vb), x=_np(x3), B=_np(B3), C=_np(C3), gy=_np(gy3),
+             y=_np(y3), grad_L=gL, grad_x=gx3)
+        # (3) independent modes (L only), complex states returned; and one selected state of a matrix system
+        Ls = torch.polar(0.5 + 0.45 * torch.rand(M, dtype=dt), 3.0 * torch.rand(M, dtype=dt)).requires_grad_()
+        xs = torch.randn(Bn, N, M, dtype=cdt)
+        ys = diag_state_space(xs, L=Ls, unroll_factor=1)
+        gys = torch.randn(Bn, N, M, dtype=cdt)
+        (gLs,) = grads(ys, gys, Ls)
+        A2 = stable().to(dt)
+        x2 = torch.randn(Bn, N, dtype=dt)
+        y_idx = diag_state_space(x2, A=A2, out_idx=1)   # default unroll factor: its pure-PyTorch scan
+        save(f"diag_ssm_modes_{tag}", L=_np(Ls), x=_np(xs), gy=_np(gys), y=_np(ys), grad_L=gLs,
+             A2=_np(A2), x2=_np(x2), y_idx=_np(y_idx))
+
+
 def main():
     pt = import_reference()
+    if len(sys.argv) > 1 and sys.argv[1] == "diag_ssm":      # only this group
+        diag_state_space_cases(pt)
+        return
     if len(sys.argv) > 1 and sys.argv[1] == "callers":       # only this group
         first_order_caller_cases(pt)
         return

@@ -1,0 +1,106 @@
+"""GPU parity of ``lti.diag_state_space`` (state-space model in its eigenbasis: batch * M complex
+first-order recurrences) against the golden vectors made by running the reference's
+``philtorch.lti.diag_state_space`` (outputs, final states, gradients) and, at larger sizes, the
+sequential state-space restatement in oracle/callers.py.
+Tolerance: max|out-ref|/max|ref| <= 1e-4 (fp32), <= 1e-10 (fp64); gradients that pass through the
+eigen-decomposition of a matrix are compared at 1e-3 / 1e-8 (two different, equally valid
+eigenvector normalisations are differentiated)."""
+import pytest
+import torch
+
+import philtorch_b200 as ptb
+from philtorch_b200.lti import diag_state_space
+from conftest import load_golden, rel_err, tol
+from oracle import callers
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+DT = {"f32": torch.float32, "f64": torch.float64}
+
+
+def _dev(g, *names):
+    return [g[n].to(DEV) for n in names]
+
+
+@pytest.mark.parametrize("tag", ["f32", "f64"])
+def test_matrix_system_golden(tag):
+    g = load_golden(f"diag_ssm_matrix_{tag}")
+    t = tol(DT[tag])
+    A, x, Bm, Cm = (v.requires_grad_() for v in _dev(g, "A", "x", "B", "C"))
+    D, zi, gy = _dev(g, "D", "zi", "gy")
+    y, zf = diag_state_space(x, A=A, B=Bm, C=Cm, D=D, zi=zi)
+    gA, gx, gB, gC = torch.autograd.grad(y, (A, x, Bm, Cm), gy)
+    ptb.check_errors()
+    assert y.dtype == DT[tag] and zf.dtype == DT[tag]
+    assert rel_err(y, g["y"]) <= t and rel_err(zf, g["zf"]) <= t
+    assert rel_err(gx, g["grad_x"]) <= t and rel_err(gB, g["grad_B"]) <= t and rel_err(gC, g["grad_C"]) <= t
+    assert rel_err(gA, g["grad_A"]) <= (1e-3 if tag == "f32" else 1e-8)
+
+
+@pytest.mark.parametrize("tag", ["f32", "f64"])
+def test_given_eigenbasis_golden(tag):
+    g = load_golden(f"diag_ssm_eig_batched_{tag}")
+    t = tol(DT[tag])
+    L, x = (v.requires_grad_() for v in _dev(g, "L", "x"))
+    V, Bm, Cm, gy = _dev(g, "V", "B", "C", "gy")
+    y = diag_state_space(x, L=L, V=V, B=Bm, C=Cm)
+    gL, gx = torch.autograd.grad(y, (L, x), gy)
+    ptb.check_errors()
+    assert rel_err(y, g["y"]) <= t
+    assert rel_err(gL, g["grad_L"]) <= t and rel_err(gx, g["grad_x"]) <= t
+    # the inverse given instead of the eigenvectors
+    y2 = diag_state_space(x, L=L, Vinv=torch.linalg.inv(V), B=Bm, C=Cm)
+    assert rel_err(y2, g["y"]) <= 10 * t
+
+
+@pytest.mark.parametrize("tag", ["f32", "f64"])
+def test_modes_and_selected_state_golden(tag):
+    g = load_golden(f"diag_ssm_modes_{tag}")
+    t = tol(DT[tag])
+    L = g["L"].to(DEV).requires_grad_()
+    y = diag_state_space(g["x"].to(DEV), L=L)
+    (gL,) = torch.autograd.grad(y, L, g["gy"].to(DEV))
+    assert y.is_complex()
+    assert rel_err(y, g["y"]) <= t and rel_err(gL, g["grad_L"]) <= t
+    A2, x2 = _dev(g, "A2", "x2")
+    y_idx = diag_state_space(x2, A=A2, out_idx=1)
+    assert rel_err(y_idx, g["y_idx"]) <= t
+    # eigenvalues AND the matrix given: eigenvectors are solved for
+    y_la = diag_state_space(x2, L=torch.linalg.eigvals(A2), A=A2, out_idx=1)
+    assert rel_err(y_la, g["y_idx"]) <= 10 * t
+    ptb.check_errors()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+@pytest.mark.parametrize("M,batched", [(2, False), (4, True), (6, False)])
+def test_against_sequential_state_space(dtype, M, batched):
+    """Orders above two run as M first-order modes; compared with the time loop in the original basis."""
+    gen = torch.Generator().manual_seed(M)
+    rows, n = 7, 20000
+    A = torch.randn(*((rows,) if batched else ()), M, M, generator=gen, dtype=torch.float64)
+    A = A / (1.05 * torch.linalg.eigvals(A).abs().amax(-1)[..., None, None])
+    x = torch.randn(rows, n, generator=gen, dtype=torch.float64)
+    Bm, Cm = torch.randn(M, generator=gen, dtype=torch.float64), torch.randn(M, generator=gen, dtype=torch.float64)
+    zi = torch.randn(rows, M, generator=gen, dtype=torch.float64)
+    D = torch.tensor([0.3], dtype=torch.float64)
+    y, zf = diag_state_space(x.to(dtype).to(DEV), A=A.to(dtype).to(DEV), B=Bm.to(dtype).to(DEV),
+                             C=Cm.to(dtype).to(DEV), D=D.to(dtype).to(DEV), zi=zi.to(dtype).to(DEV))
+    ptb.check_errors()
+    y_ref, zf_ref = callers.state_space(A.to(dtype).double().numpy(), x.to(dtype).double().numpy(),
+                                        Bm.to(dtype).double().numpy(), Cm.to(dtype).double().numpy(), D.numpy(),
+                                        zi.to(dtype).double().numpy())
+    t = 2e-3 if dtype == torch.float32 else 1e-9      # the eigenbasis change costs a few digits (cond(V))
+    assert rel_err(y, torch.from_numpy(y_ref)) <= t
+    assert rel_err(zf, torch.from_numpy(zf_ref)) <= t
+
+
+def test_argument_checks():
+    x = torch.zeros(4, 50, device=DEV)
+    with pytest.raises(ValueError, match="C and out_idx"):
+        diag_state_space(x, A=torch.eye(2, device=DEV), C=torch.ones(2, device=DEV), out_idx=0)
+    with pytest.raises(AssertionError, match="Either L or A"):
+        diag_state_space(x)
+    with pytest.raises(AssertionError, match="cannot both be None"):
+        diag_state_space(x, L=torch.zeros(4, 2, device=DEV))
+    with pytest.raises(ValueError, match="Input matrix B"):
+        diag_state_space(x, A=torch.eye(2, device=DEV), B=torch.ones(5, device=DEV))

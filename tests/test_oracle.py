@@ -178,3 +178,13 @@ def test_cspline_oracle_scipy():
     c = callers.cspline(x, True)
     for row in range(4):
         assert abs(c[row] - cspline1d(x[row])).max() <= 1e-10
+
+
+def test_state_space_oracle_golden():
+    """The sequential state-space restatement against ``diag_state_space`` run by the reference."""
+    from oracle import callers
+    g = load_golden("diag_ssm_matrix_f64")
+    y, zf = callers.state_space(g["A"].numpy(), g["x"].numpy(), g["B"].numpy(), g["C"].numpy(), g["D"].numpy(),
+                                g["zi"].numpy())
+    assert rel_err(torch.from_numpy(y), g["y"]) <= 1e-10
+    assert rel_err(torch.from_numpy(zf), g["zf"]) <= 1e-10
