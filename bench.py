@@ -495,6 +495,55 @@ def run_complex_poles(args):
                     {"dtype": "c128" if args.f64 else "c64"})
 
 
+def run_callers(args):
+    """Secondary lines for the callers that are pure first-order passes (one per invocation):
+    --comb-filter   y[t] = x[t] - a y[t-1000], B = 64, T = 2^22, fp32, fwd+bwd (grads a, x);
+    --cubic-spline  cspline coefficients (parallel form), B = 64, T = 2^22, fp32, fwd+bwd (grad x);
+    --diag-ssm      4th-order real system with complex poles through diag_state_space (B (M,), C (M,)),
+                    B = 64, T = 2^20, fp32, fwd+bwd (grads x, L)."""
+    import math
+
+    import torch
+
+    import philtorch_b200 as ptb
+    from philtorch_b200.lti.interp import cspline
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    g = torch.Generator(device=dev).manual_seed(SEED_LPV + 2)
+    Bc = args.rows if args.rows != B else 64
+    if args.comb_filter:
+        Tc, delay = 1 << 22, 1000
+        a = (torch.rand(Bc, device=dev, generator=g) * 1.8 - 0.9).requires_grad_()
+        x = torch.randn(Bc, Tc, device=dev, generator=g).requires_grad_()
+        gy = torch.randn(Bc, Tc, device=dev, generator=g)
+        step = lambda: torch.autograd.grad(ptb.lti.comb_filter(a, delay, x), (a, x), gy)   # noqa: E731
+        name, alg = f"comb_filter delay={delay} fwd+bwd (grads a, x), fp32, B={Bc}, T=2^22", 8 + 12
+    elif args.cubic_spline:
+        Tc = 1 << 22
+        x = torch.randn(Bc, Tc, device=dev, generator=g).requires_grad_()
+        gy = torch.randn(Bc, Tc, device=dev, generator=g)
+        step = lambda: torch.autograd.grad(cspline(x), (x,), gy)   # noqa: E731
+        name, alg = f"cspline (parallel form) fwd+bwd (grad x), fp32, B={Bc}, T=2^22", 8 + 8
+    else:
+        Tc, M = 1 << 20, 4
+        r = 0.9 + 0.09 * torch.rand(M // 2, device=dev, generator=g)
+        th = math.pi * torch.rand(M // 2, device=dev, generator=g)
+        half = torch.polar(r, th)
+        L = torch.cat([half, half.conj()]).requires_grad_()                     # conjugate pole pairs
+        V = torch.view_as_complex(torch.randn(M // 2, M, 2, device=dev, generator=g))
+        V = torch.cat([V, V.conj()]).T.contiguous()                              # conjugate eigenvector pairs
+        x = torch.randn(Bc, Tc, device=dev, generator=g).requires_grad_()
+        gy = torch.randn(Bc, Tc, device=dev, generator=g)
+        Bm, Cm = torch.randn(M, device=dev, generator=g), torch.randn(M, device=dev, generator=g)
+        step = lambda: torch.autograd.grad(ptb.lti.diag_state_space(x, L=L, V=V, B=Bm, C=Cm), (x, L), gy)   # noqa: E731
+        name, alg = f"diag_state_space M={M} (complex pole pairs, B (M,), C (M,)) fwd+bwd (grads x, L), fp32, " \
+                    f"B={Bc}, T=2^20", 8 + 8
+    ms = _timed(step, args, dev)
+    ptb.check_errors(dev)
+    _secondary_line(args, name, Bc * Tc, ms, alg, {})
+
+
 SEED_LPV = 1240
 
 
@@ -518,6 +567,9 @@ def main():
     ap.add_argument("--complex-poles", action="store_true",
                     help="secondary workload: complex first-order recurrence, B=256, T=2^19 (one GPU)")
     ap.add_argument("--per-sample", action="store_true", help="--complex-poles with per-sample coefficients")
+    ap.add_argument("--comb-filter", action="store_true", help="secondary workload: comb filter (one GPU)")
+    ap.add_argument("--cubic-spline", action="store_true", help="secondary workload: cubic spline coefficients (one GPU)")
+    ap.add_argument("--diag-ssm", action="store_true", help="secondary workload: diag_state_space, 4 complex modes (one GPU)")
     ap.add_argument("--sos-cascade", action="store_true",
                     help="secondary workload: six fused second-order sections, B=512, T=2^18 (one GPU)")
     args = ap.parse_args()
@@ -528,7 +580,8 @@ def main():
         run_reference_arm(args, rank)
         return
     secondary = [fn for flag, fn in ((args.sos_cascade, run_sos_cascade), (args.state_space, run_state_space),
-                                     (args.lpv_lfilter, run_lpv_lfilter), (args.complex_poles, run_complex_poles))
+                                     (args.lpv_lfilter, run_lpv_lfilter), (args.complex_poles, run_complex_poles),
+                                     (args.comb_filter or args.cubic_spline or args.diag_ssm, run_callers))
                  if flag]
     if secondary:
         if rank == 0:

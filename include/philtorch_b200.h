@@ -265,6 +265,25 @@ int ptb_lpv_biquad_tdf2_bwd(int dtype, int64_t B, int64_t T, const void* b, cons
                            void* grad_b, void* grad_a, void* grad_zi, void* workspace, int64_t workspace_bytes,
                            uint32_t* status, ptb_stream_t stream);
 
+/* ---- feedback comb filter (replaces the fold / transpose route of philtorch/lti/filtering.py:15-71,
+ *      comb_filter) -------------------------------------------------------------------------------
+ * y[t] = x[t] - a * y[t - delay] on the signal's own (B, N) layout: one thread per (row, phase).
+ *   a         (B,) when a_batched, else one value
+ *   zi_mode   0: zero initial state; 1: zi is (delay,) shared by the rows; 2: zi is (B, delay).
+ *             zi[..., k] is the output k + 1 samples before the start (the reference's order).
+ * Adjoint: grad_x (B, N); `partial` (may be NULL) receives B * ptb_comb_partial_blocks(delay)
+ * partial sums of grad_a, row-major (row, block): grad_a[row] is the sum over its blocks, a shared
+ * coefficient sums all of them; `grad_state` (may be NULL) receives the (B, delay) gradient of the
+ * initial state in zi's order.  workspace and status are unused (no device-side waits) and may be NULL.
+ * float32 / float64. */
+int64_t ptb_comb_partial_blocks(int64_t delay);
+int ptb_comb_fwd(int dtype, int64_t B, int64_t N, int64_t delay, const void* a, int a_batched, const void* zi,
+                 int zi_mode, const void* x, void* y, void* workspace, int64_t workspace_bytes, uint32_t* status,
+                 ptb_stream_t stream);
+int ptb_comb_bwd(int dtype, int64_t B, int64_t N, int64_t delay, const void* a, int a_batched, const void* zi,
+                 int zi_mode, const void* y, const void* gy, void* grad_x, void* partial, void* grad_state,
+                 void* workspace, int64_t workspace_bytes, uint32_t* status, ptb_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

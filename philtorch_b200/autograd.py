@@ -295,6 +295,28 @@ class BiquadTDF2(Function):
                 _none_if_empty(gx, need_x))
 
 
+class CombFilter(Function):
+    """y[t] = x[t] - a*y[t-delay] on the signal's own layout, (a, zi, x, delay) -> y; zi: None, (delay,)
+    or (B, delay) in the reference's order (zi[..., k] = the output k+1 samples before the start)."""
+
+    @staticmethod
+    def forward(ctx: Any, a: Tensor, zi: Optional[Tensor], x: Tensor, delay: int) -> Tensor:
+        y = _ops.comb(a, zi, x, delay)
+        ctx.delay, ctx.has_zi = delay, zi is not None
+        ctx.save_for_backward(a, y, *([zi] if zi is not None else []))
+        return y
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx: Any, grad_y: Tensor):
+        a, y, *rest = ctx.saved_tensors
+        zi = rest[0] if rest else None
+        need_a, need_zi, need_x = ctx.needs_input_grad[:3]
+        need_zi = need_zi and ctx.has_zi
+        ga, gzi, gx = _ops.comb_bwd(a, zi, y, grad_y, ctx.delay, need_a, need_zi)
+        return _none_if_empty(ga, need_a), _none_if_empty(gzi, need_zi), _none_if_empty(gx, need_x), None
+
+
 class SOSCascade(Function):
     """K second-order sections (TDF-II) in one fused pass, (b, a, zi, x) -> (y, zf) with b (K,3) or
     (K,B,3), a (K,2) or (K,B,2), zi/zf (K,B,2).  Same results as K chained ``BiquadTDF2`` calls

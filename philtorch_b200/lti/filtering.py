@@ -13,7 +13,7 @@ import torch
 import torch.nn.functional as F
 from torch import Tensor
 
-from ..autograd import BiquadTDF2, SOSCascade
+from ..autograd import BiquadTDF2, CombFilter, SOSCascade
 from ..ops import SOS_CASCADE_SIZES
 from ..mat import companion
 from .recur import linear_recurrence
@@ -22,12 +22,17 @@ from .ssm import state_space
 __all__ = ["lfilter", "filtfilt", "lfilter_zi", "sosfilt", "comb_filter"]
 
 
+COMB_KERNEL_MIN_LANES = 8192   # (row, phase) pairs from which the comb kernels replace the folded scan
+
+
 def comb_filter(a: Tensor, delay: int, x: Tensor, zi: Optional[Tensor] = None, **kwargs):
     """Feedback comb filter ``y[t] = x[t] - a * y[t - delay]`` (philtorch/lti/filtering.py:15-71).
 
     The ``delay`` interleaved phases of a row are independent first-order recurrences with the
-    coefficient ``-a``: the signal is folded to ``B * delay`` rows of ``ceil(N / delay)`` samples
-    and runs through the first-order time-invariant kernel (forward and adjoint).
+    coefficient ``-a``.  With at least ``COMB_KERNEL_MIN_LANES`` (row, phase) pairs the comb kernels
+    run on the signal as it lies in memory, one thread per pair (no fold, no transposes; once
+    differentiable).  Smaller problems are folded to ``B * delay`` rows of ``ceil(N / delay)``
+    samples and run through the first-order time-invariant scan, as the reference does.
 
     Args:
         a: feedback coefficient, shape () (shared) or (B,).
@@ -50,6 +55,9 @@ def comb_filter(a: Tensor, delay: int, x: Tensor, zi: Optional[Tensor] = None, *
         return linear_recurrence(-a, torch.zeros_like(a) if zi is None else zi.squeeze(-1), x, **kwargs)
 
     batch, n = x.shape
+    if batch * delay >= COMB_KERNEL_MIN_LANES and not (a.dim() == 1 and a.size(0) == 1 and batch > 1):
+        y = CombFilter.apply(a, zi, x, delay)
+        return (y, y[:, -delay:].flip(1)) if zi is not None else y
     tail = (-n) % delay
     if tail:
         x = F.pad(x, (0, tail))

@@ -388,6 +388,83 @@ def _(b, a, x, y, gy, gzf, need_coef, need_zi):
             torch.empty_like(x, memory_format=torch.contiguous_format))
 
 
+# =============================================================================== comb filter
+_LIB.define("comb(Tensor a, Tensor? zi, Tensor x, int delay) -> Tensor", tags=_TAGS)
+_LIB.define("comb_bwd(Tensor a, Tensor? zi, Tensor y, Tensor gy, int delay, bool need_a, bool need_zi)"
+            " -> (Tensor, Tensor, Tensor)", tags=_TAGS)
+
+
+def _check_comb(a: Tensor, zi: Optional[Tensor], x: Tensor, delay: int) -> None:
+    torch._check(x.dim() == 2, lambda: "x must be 2D (batch, time).")
+    torch._check(delay >= 1, lambda: "delay must be at least 1.")
+    torch._check(a.dim() == 0 or (a.dim() == 1 and a.shape[0] in (1, x.shape[0])),
+                 lambda: "a must be a scalar or (B,).")
+    if zi is not None:
+        torch._check(tuple(zi.shape) in ((delay,), (x.shape[0], delay)), lambda: "zi must be (delay,) or (B, delay).")
+
+
+def _comb_args(a, zi, x):
+    B = x.shape[0]
+    a_batched = int(a.dim() == 1 and a.shape[0] == B and B > 1)
+    zi_mode = 0 if zi is None else (1 if zi.dim() == 1 else 2)
+    return a_batched, zi_mode
+
+
+def _comb(a, zi, x, delay):
+    _check_comb(a, zi, x, delay)
+    dev = _lib.require_cuda(a, zi, x)
+    if a.dtype != x.dtype or (zi is not None and zi.dtype != x.dtype):
+        raise RuntimeError("a and zi must have the same scalar type as input")
+    B, N = x.shape
+    a_c, zi_c, x_c = a.contiguous(), _opt(zi), x.contiguous()
+    a_batched, zi_mode = _comb_args(a, zi, x)
+    y = torch.empty_like(x_c)
+    if B and N:
+        _lib.call(lib.ptb_comb_fwd, dev, B, N, _lib.dtype_code(x), B, N, delay, ptr(a_c), a_batched, ptr(zi_c),
+                  zi_mode, ptr(x_c), ptr(y), ws_bytes=0)
+    return y
+
+
+def _comb_bwd(a, zi, y, gy, delay, need_a, need_zi):
+    dev = _lib.require_cuda(a, zi, y, gy)
+    B, N = y.shape
+    a_c, zi_c, y_c, gy_c = a.contiguous(), _opt(zi), y.contiguous(), gy.contiguous()
+    a_batched, zi_mode = _comb_args(a, zi, y)
+    gx = torch.empty_like(y_c)
+    nblk = lib.ptb_comb_partial_blocks(delay)
+    part = y.new_zeros(B, nblk) if need_a else None
+    gst = y.new_zeros(B, delay) if need_zi else None
+    if B and N:
+        _lib.call(lib.ptb_comb_bwd, dev, B, N, _lib.dtype_code(y), B, N, delay, ptr(a_c), a_batched, ptr(zi_c),
+                  zi_mode, ptr(y_c), ptr(gy_c), ptr(gx), ptr(part), ptr(gst), ws_bytes=0)
+    if need_a:
+        ga = part.sum(1) if a_batched else part.sum().reshape(a.shape)
+    else:
+        ga = a.new_empty(0)
+    if need_zi:
+        gzi = gst if zi.dim() == 2 else gst.sum(0)
+    else:
+        gzi = y.new_empty(0)
+    return ga, gzi, gx
+
+
+_LIB.impl("comb", _comb, "CUDA")
+_LIB.impl("comb_bwd", _comb_bwd, "CUDA")
+
+
+@torch.library.register_fake("philtorch_b200::comb")
+def _(a, zi, x, delay):
+    _check_comb(a, zi, x, delay)
+    return torch.empty_like(x, memory_format=torch.contiguous_format)
+
+
+@torch.library.register_fake("philtorch_b200::comb_bwd")
+def _(a, zi, y, gy, delay, need_a, need_zi):
+    return (torch.empty_like(a) if need_a else a.new_empty(0),
+            torch.empty_like(zi) if need_zi else y.new_empty(0),
+            torch.empty_like(y, memory_format=torch.contiguous_format))
+
+
 # =============================================================================== fused SOS cascade
 _LIB.define("sos_cascade(Tensor b, Tensor a, Tensor? zi, Tensor x, bool keep_mid) -> (Tensor, Tensor, Tensor)",
             tags=_TAGS)
@@ -569,5 +646,5 @@ def _no_backend(name):
 for _name in ("lti_recur", "lti_recur_bwd", "lpv_recur", "lpv_recur_bwd", "lti_recur2", "lti_recur2_sx", "recur2",
               "recur2_sx", "lti_recur2_bwd", "recur2_bwd", "biquad_tdf2", "biquad_tdf2_bwd", "lpv_recur_carry", "lpv_recur_zero_carry",
               "sos_cascade", "sos_cascade_bwd", "lpv_biquad_df2", "lpv_biquad_df2_bwd",
-              "lpv_biquad_tdf2", "lpv_biquad_tdf2_bwd"):
+              "lpv_biquad_tdf2", "lpv_biquad_tdf2_bwd", "comb", "comb_bwd"):
     _LIB.impl(_name, _no_backend(_name), "CPU")

@@ -19,6 +19,14 @@ DT = {"f32": torch.float32, "f64": torch.float64}
 COMB_CASES = [(1, "none"), (5, "none"), (13, "shared"), (5, "batched"), (32, "none")]
 
 
+@pytest.fixture(params=["folded_scan", "comb_kernels"], autouse=True)
+def comb_route(request, monkeypatch):
+    """Every test runs on both routes of comb_filter: the folded first-order scan and the comb kernels."""
+    from philtorch_b200.lti import filtering
+    monkeypatch.setattr(filtering, "COMB_KERNEL_MIN_LANES", 10 ** 12 if request.param == "folded_scan" else 1)
+    return request.param
+
+
 @pytest.mark.parametrize("tag", ["f32", "f64"])
 @pytest.mark.parametrize("delay,zs", COMB_CASES)
 @pytest.mark.parametrize("mode", ["batched", "scalar"])
@@ -54,6 +62,37 @@ def test_comb_sizes(dtype, delay, n):
     ref = torch.from_numpy(callers.comb_filter(a.numpy(), delay, x.numpy(), zi.numpy()))
     assert rel_err(y, ref) <= tol(dtype)
     assert rel_err(zf, ref[:, -delay:].flip(1)) <= tol(dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+@pytest.mark.parametrize("delay,n,zi_kind", [(3, 1000, "batched"), (129, 5000, "shared"), (1000, 30011, "batched"),
+                                              (500, 300, "batched"), (64, 64 * 40, None)])
+@pytest.mark.parametrize("a_batched", [True, False])
+def test_comb_routes_agree(dtype, delay, n, zi_kind, a_batched, comb_route, monkeypatch):
+    """Outputs and all gradients (a, zi, x) of the comb kernels against the folded scan."""
+    if comb_route == "folded_scan":
+        pytest.skip("compares the two routes once")
+    from philtorch_b200.lti import filtering
+    gen = torch.Generator().manual_seed(delay + n)
+    rows = 5
+    a0 = (torch.rand(rows if a_batched else (), generator=gen, dtype=torch.float64) * 1.9 - 0.95).to(dtype).to(DEV)
+    x0 = torch.randn(rows, n, generator=gen, dtype=torch.float64).to(dtype).to(DEV)
+    gy = torch.randn(rows, n, generator=gen, dtype=torch.float64).to(dtype).to(DEV)
+    zi0 = None if zi_kind is None else torch.randn(*((rows, delay) if zi_kind == "batched" else (delay,)),
+                                                   generator=gen, dtype=torch.float64).to(dtype).to(DEV)
+    out = {}
+    for route, lanes in (("kernels", 1), ("fold", 10 ** 12)):
+        monkeypatch.setattr(filtering, "COMB_KERNEL_MIN_LANES", lanes)
+        a, x = a0.clone().requires_grad_(), x0.clone().requires_grad_()
+        zi = None if zi0 is None else zi0.clone().requires_grad_()
+        res = comb_filter(a, delay, x, zi=zi)
+        y = res[0] if isinstance(res, tuple) else res
+        ins = [a, x] + ([zi] if zi is not None else [])
+        out[route] = [y] + list(torch.autograd.grad(y, ins, gy))
+    ptb.check_errors()
+    t = tol(dtype)
+    for got, ref in zip(out["kernels"], out["fold"]):
+        assert rel_err(got, ref) <= (10 * t if got.dim() < 2 else t)
 
 
 def test_comb_argument_checks():
