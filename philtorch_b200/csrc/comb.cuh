@@ -19,7 +19,8 @@
 namespace ptb {
 
 constexpr int kCombThreads = 128;
-constexpr int kCombAhead = 8;
+constexpr int kCombAhead = 32;      // forward: loads in flight per thread
+constexpr int kCombAheadBwd = 16;   // adjoint: per array (gy and y)
 
 // zi_mode: 0 none, 1 (D,) shared by the rows, 2 (B, D).  zi[..., k] is the output k + 1 samples
 // before the start, so phase d starts from zi[..., D - 1 - d].
@@ -68,12 +69,12 @@ comb_bwd_kernel(const S* __restrict__ gy, const S* __restrict__ y, const S* __re
     const int64_t steps = (N - d + D - 1) / D;
     S c = S(0);                        // coef * g[t + D]
     int64_t k = steps - 1;
-    for (; k - kCombAhead >= 0; k -= kCombAhead) {      // steps k .. k - kCombAhead + 1, all with k - u >= 1
-      S v[kCombAhead], p[kCombAhead];
+    for (; k - kCombAheadBwd >= 0; k -= kCombAheadBwd) {      // steps k .. k - kCombAheadBwd + 1, all with k - u >= 1
+      S v[kCombAheadBwd], p[kCombAheadBwd];
 #pragma unroll
-      for (int u = 0; u < kCombAhead; ++u) { v[u] = gr[(k - u) * D]; p[u] = partial ? yr[(k - u - 1) * D] : S(0); }
+      for (int u = 0; u < kCombAheadBwd; ++u) { v[u] = gr[(k - u) * D]; p[u] = partial ? yr[(k - u - 1) * D] : S(0); }
 #pragma unroll
-      for (int u = 0; u < kCombAhead; ++u) {
+      for (int u = 0; u < kCombAheadBwd; ++u) {
         const S g = v[u] + c;
         xr[(k - u) * D] = g;
         acc += g * p[u];
