@@ -78,6 +78,42 @@ class LTIRecurrence(Function):
         return LTIRecurrence.apply(a, fwd_init, fwd_x)
 
 
+class ReverseLTIRecurrence(Function):
+    """g[t] = a*g[t+1] + x[t] with g[T] = end: the first-order recurrence running from the last
+    sample to the first, (a, end, x) -> g, without reversing anything in memory: the forward pass
+    is the adjoint kernel of ``LTIRecurrence`` and the backward pass its forward kernel.  The
+    reference reaches the same result with flip -> recurrence -> flip
+    (philtorch/lti/interp.py:41-56, philtorch/lti/filtering.py:413-484)."""
+
+    @staticmethod
+    def forward(a: Tensor, end: Tensor, x: Tensor) -> Tensor:
+        # the adjoint kernel conjugates its coefficient and takes a*g[T] as the state entering from the right
+        _, _, g = _ops.lti_recur_bwd(a.conj(), end, x, x, a * end, False, False)
+        return g
+
+    @staticmethod
+    def setup_context(ctx: Any, inputs, output) -> None:
+        a, end, _ = inputs
+        ctx.save_for_backward(a, end, output)
+
+    @staticmethod
+    def backward(ctx: Any, grad_out: Tensor):
+        a, end, out = ctx.saved_tensors
+        need_a, need_end, need_x = ctx.needs_input_grad
+        if torch.is_grad_enabled():   # higher-order graph: the same function through LTIRecurrence
+            q = LTIRecurrence.apply(a.conj(), torch.zeros_like(end), grad_out)
+        else:
+            q = _ops.lti_recur(a.conj(), torch.zeros_like(end), grad_out)
+        grad_a = grad_end = None
+        if need_end:
+            grad_end = q[:, -1] * a.conj()
+        if need_a:
+            prod = torch.cat([out[:, 1:], end.unsqueeze(1)], dim=1).conj() * q
+            grad_a = prod.sum(1) if (a.dim() == 1 and a.shape[0] == out.shape[0] and a.shape[0] > 1) \
+                else prod.sum().reshape(a.shape)
+        return grad_a, grad_end, (q if need_x else None)
+
+
 class LPVRecurrence(Function):
     """y[t] = a[t]*y[t-1] + x[t] with a of shape (T,) or (B,T)."""
 

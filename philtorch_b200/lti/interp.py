@@ -2,7 +2,10 @@
 
 The spline coefficients are the input filtered by the symmetric all-pole filter with the pole
 ``r = sqrt(3) - 2`` (Unser, "B-Spline Signal Processing: Part II"): a causal and an anticausal
-first-order time-invariant recurrence, both of which run on the first-order kernel.
+first-order time-invariant recurrence.  The causal pass is the forward kernel of the first-order
+recurrence and the anticausal pass its adjoint kernel, which runs from the last sample to the
+first: the signal is never mirrored, concatenated or reversed in memory (the reference filters
+the mirrored signal and flips the halves back).
 """
 from __future__ import annotations
 
@@ -12,46 +15,52 @@ import torch
 import torch.nn.functional as F
 from torch import Tensor
 
-from ..autograd import LTIRecurrence
+from ..autograd import LTIRecurrence, ReverseLTIRecurrence
 
 __all__ = ["cspline", "cubic_spline"]
 
 POLE = math.sqrt(3.0) - 2.0
+MIRROR_TERMS = 1024   # POLE**k is exactly zero (also as a denormal float64) long before k = 1024
 
 
-def _recur(x: Tensor, pole: Tensor, init: Tensor, gain=None) -> Tensor:
-    """h[t] = pole * h[t-1] + gain * x[t] per row, h[-1] = init (philtorch/lti/interp.py:10-20)."""
+def _causal(x: Tensor, pole: Tensor, init: Tensor) -> Tensor:
+    """h[t] = pole * h[t-1] + x[t] per row, h[-1] = init (philtorch/lti/interp.py:10-20)."""
     rows = x.shape[0]
-    return LTIRecurrence.apply(pole.expand(rows), init.expand(rows).contiguous(), x if gain is None else x * gain)
+    return LTIRecurrence.apply(pole.expand(rows), init.expand(rows).contiguous(), x)
+
+
+def _anticausal(x: Tensor, pole: Tensor, end: Tensor) -> Tensor:
+    """g[t] = pole * g[t+1] + x[t] per row, g[L] = end."""
+    rows = x.shape[0]
+    return ReverseLTIRecurrence.apply(pole.expand(rows), end.expand(rows).contiguous(), x)
 
 
 def _coefficients(x: Tensor, parallel_form: bool, scipy_padding: bool) -> Tensor:
     """philtorch/lti/interp.py:23-57.  The signal is continued by mirroring: with the sample at the
     border repeated (scipy's cspline1d) or not (torch's 'reflect' padding)."""
-    length = x.shape[-1]
     r = torch.tensor(POLE, device=x.device, dtype=x.dtype)
-    # state of the causal recurrence at t = -1: the geometric sum over the mirrored past
-    if scipy_padding:
-        start = x @ r.pow(torch.arange(length, device=x.device, dtype=x.dtype))
-    else:
-        start = x[..., 1:] @ r.pow(torch.arange(length - 1, device=x.device, dtype=x.dtype))
+    # state of the causal recurrence at t = -1: the geometric sum over the mirrored past, of which
+    # only the first terms are non-zero in floating point
+    past = x if scipy_padding else x[..., 1:]
+    terms = min(past.shape[-1], MIRROR_TERMS)
+    start = past[..., :terms] @ r.pow(torch.arange(terms, device=x.device, dtype=x.dtype))
+    h = _causal(x, r, start)
 
     if parallel_form:
-        # partial fractions: causal + anticausal part, the second being the same recurrence continued
-        # over the mirrored signal
-        back = x.flip(-1) if scipy_padding else x[..., :-1].flip(-1)
-        h = _recur(torch.cat([x, back], dim=-1), r, start)
-        causal, anticausal = h[..., :length], h[..., -length:].flip(-1)
-        return (causal + anticausal - x) * (-6.0 * POLE / (1.0 - POLE * POLE))
+        # partial fractions: causal + anticausal part.  The anticausal part continues the causal
+        # recurrence over the mirrored signal, i.e. it runs backwards over x from the causal end state
+        end = h[..., -1] if scipy_padding else (h[..., -1] - x[..., -1]) / POLE
+        g = _anticausal(x, r, end)
+        return (h + g).sub_(x).mul_(-6.0 * POLE / (1.0 - POLE * POLE))
 
-    # cascade: causal pass, then the anticausal pass over its output
-    h = _recur(x, r, start)
+    # cascade: the anticausal pass runs over the output of the causal one, from its own last value
     if scipy_padding:
         last = h[..., -1] * (POLE / (POLE - 1.0))
     else:
         last = (2.0 * h[..., -1] - x[..., -1]) * (-POLE / (1.0 - POLE * POLE))
-    rest = _recur(h[..., :-1].flip(-1), r, last, gain=-r).flip(-1)
-    return torch.cat([rest, last.unsqueeze(-1)], dim=-1) * 6.0
+    drive = h * (-POLE)
+    drive[..., -1] = last                  # so that c[L-1] = last with a zero state beyond the end
+    return _anticausal(drive, r, torch.zeros_like(last)) * 6.0
 
 
 def cspline(x: Tensor, parallel_form: bool = True, scipy_padding: bool = False, lamb: float = 0.0,

@@ -262,18 +262,41 @@ def diag_state_space(x: Tensor, L: Optional[Tensor] = None, V: Optional[Tensor] 
     poles = Lc.expand(batch_size, M).reshape(-1)
     w = LTIRecurrence.apply(poles, w0.reshape(-1).contiguous(), u).view(batch_size, M, N)
 
-    # ---- back: the state BEFORE sample t is h[t] = V [w0, w[0], ..., w[N-2]][t]
+    # ---- back: the state BEFORE sample t is h[t] = V [w0, w[0], ..., w[N-2]][t].  An output map is
+    # folded into the basis (C V) and applied to the modes directly; the one-sample shift then
+    # happens on the (smaller) output instead of on the (batch, M, N) modes.
     real_out = C is not None and not C.is_complex()
     zf = None
     if return_zf:
         zf = (Vc @ w[:, :, -1:]).squeeze(-1)
         zf = zf.real if real_out else zf
-    w_prev = torch.cat([w0.unsqueeze(-1), w[:, :, :-1]], dim=2)                 # (batch, M, N)
+    if C is None and out_idx is None:
+        w_prev = torch.cat([w0.unsqueeze(-1), w[:, :, :-1]], dim=2)             # (batch, M, N)
+        return_y = _output_map((Vc @ w_prev).mT, x, None, D, batch_size, M)     # all states, (batch, N, M)
+        return (return_y, zf) if return_zf else return_y
     if out_idx is not None:
-        h = (Vc[..., out_idx, None, :] @ w_prev).squeeze(-2)                    # (batch, N)
+        CV = Vc[..., out_idx, :]                                                # (M,) | (batch, M)
     else:
-        h = (Vc @ w_prev).mT                                                    # (batch, N, M)
+        shp = tuple(C.shape)
+        Cc = C.to(cdt)
+        if shp == (M,):
+            CV = Cc @ Vc
+        elif shp == (batch_size, M):
+            CV = (Cc.unsqueeze(1) @ Vc).squeeze(1)
+        elif (len(shp) == 2 and shp[1] == M) or (len(shp) == 3 and shp[0] == batch_size and shp[2] == M):
+            CV = Cc @ Vc                                                        # (K, M) | (batch, K, M)
+        else:
+            raise ValueError(f"Output matrix C must be of shape ({M},), ({batch_size}, {M}), (_, {M}) or "
+                             f"({batch_size}, _, {M}), got {shp}")
+    vector_out = out_idx is None and C.dim() >= 2 and tuple(C.shape) != (batch_size, M)
+    if vector_out:
+        after = (CV @ w).mT                                                     # (batch, N, K)
+        first = (CV @ w0.unsqueeze(-1)).squeeze(-1).expand(batch_size, -1)      # (batch, K)
+    else:
+        after = (CV.unsqueeze(-2) @ w).squeeze(-2)                              # (batch, N)
+        first = (CV * w0).sum(-1)                                               # (batch,)
+    h = torch.cat([first.unsqueeze(1), after[:, :-1]], dim=1)
     if real_out:
         h = h.real
-    y = _output_map(h, x, C, D, batch_size, M)
+    y = _output_map(h, x, None, D, batch_size, M)
     return (y, zf) if return_zf else y
