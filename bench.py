@@ -524,7 +524,9 @@ def run_callers(args):
         x = torch.randn(Bc, Tc, device=dev, generator=g).requires_grad_()
         gy = torch.randn(Bc, Tc, device=dev, generator=g)
         step = lambda: torch.autograd.grad(cspline(x), (x,), gy)   # noqa: E731
-        name, alg = f"cspline (parallel form) fwd+bwd (grad x), fp32, B={Bc}, T=2^22", 8 + 8
+        # two kernel passes per direction: causal (read x, write h) and reverse-time with the fused
+        # combination (read x and h, write c); a single pass (16 B in total) cannot form a two-sided filter
+        name, alg = f"cspline (parallel form) fwd+bwd (grad x), fp32, B={Bc}, T=2^22", 2 * (8 + 12)
     else:
         Tc, M = 1 << 20, 4
         r = 0.9 + 0.09 * torch.rand(M // 2, device=dev, generator=g)

@@ -96,6 +96,17 @@ int ptb_lti_recur_bwd(int dtype, int64_t B, int64_t T, const void* a, int a_batc
                       void* grad_a, void* grad_zi, void* workspace, int64_t workspace_bytes,
                       uint32_t* status, ptb_stream_t stream);
 
+/* Reverse-time first-order time-invariant recurrence fused with a three-term combination: the
+ * second pass of the symmetric (causal + anticausal) filters, e.g. the cubic-spline prefilter of
+ * philtorch/lti/interp.py:23-57, which the reference evaluates on a mirrored copy of the signal.
+ *   g[t]   = x[t] + a * g[t+1],  g[T-1] = x[T-1] + g_in[row]   (g_in may be NULL: 0)
+ *   out[t] = scale * (g[t] + second[t] - x[t])
+ *   first_state (may be NULL) receives a * g[0] per row.
+ * a: (B,) when a_batched, else one value; x, second, out: (B,T).  float32 / float64. */
+int ptb_lti_recur_reverse_fused(int dtype, int64_t B, int64_t T, const void* a, int a_batched, const void* x,
+                                const void* second, const void* g_in, double scale, void* out, void* first_state,
+                                void* workspace, int64_t workspace_bytes, uint32_t* status, ptb_stream_t stream);
+
 /* ---- first-order, per-sample coefficients ---------------------------------------------------
  * Replaces philtorch.lpv.linear_recurrence (philtorch/lpv/recur.py:20-101, pure PyTorch in the
  * reference) and the N = 1 case of op philtorch::recurN (philtorch/csrc/host_recurN.cpp:236-281).

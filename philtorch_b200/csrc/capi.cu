@@ -516,6 +516,16 @@ int ptb_lti_recur_bwd(int dtype, int64_t B, int64_t T, const void* a, int a_batc
                                         grad_zi, workspace, workspace_bytes, status, (cudaStream_t)stream)));
 }
 
+int ptb_lti_recur_reverse_fused(int dtype, int64_t B, int64_t T, const void* a, int a_batched, const void* x,
+                                const void* second, const void* g_in, double scale, void* out, void* first_state,
+                                void* workspace, int64_t workspace_bytes, uint32_t* status, ptb_stream_t stream) {
+  if (B < 0 || T < 0) return PTB_ERR_ARG;
+  if (B == 0 || T == 0) return PTB_OK;
+  if (!a || !x || !second || !out) return PTB_ERR_ARG;
+  PTB_DISPATCH(dtype, (fo_reverse_fused<S>(B, T, a, a_batched, x, second, g_in, scale, out, first_state, workspace,
+                                           workspace_bytes, status, (cudaStream_t)stream)));
+}
+
 int ptb_lpv_recur_bwd(int dtype, int64_t B, int64_t T, const void* a, int a_batched, const void* zi,
                       int zi_batched, const void* y, const void* gy, const void* g_in, void* grad_x,
                       void* grad_a, void* grad_zi, void* workspace, int64_t workspace_bytes,

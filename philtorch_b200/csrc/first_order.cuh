@@ -202,9 +202,13 @@ struct FoBwdParams {
   S* grad_zi;        // optional (B,)
   int64_t T;
   int want_ga;
+  S fuse_scale;      // FUSE: the kernel writes fuse_scale * (g + y - gy) instead of g (y = any second signal)
 };
 
-template <class S, int CH, int STAGES_, int MIN_CTAS_, int LBW_, bool LPV>
+// FUSE (time-invariant use): the result of the reverse-time recurrence is combined with its own
+// input and one more signal on the way out, out[t] = fuse_scale * (g[t] + y[t] - gy[t]): the
+// symmetric two-pass filters (causal pass y, then this pass) need no separate combining pass.
+template <class S, int CH, int STAGES_, int MIN_CTAS_, int LBW_, bool LPV, bool FUSE = false>
 struct FoBwd : ScalarAffine<S> {
   using Alg = ScalarAffine<S>;
   using typename Alg::Map;
@@ -239,6 +243,7 @@ struct FoBwd : ScalarAffine<S> {
     const uint32_t bytes = (uint32_t)nvalid * sizeof(S);
     io.load(G_OFF, p.gy + row * p.T + t0, bytes);
     if (LPV) io.load(A_OFF, p.a + row * p.a_row_stride + t0, bytes);
+    if (FUSE && !p.want_ga) io.load(Y_OFF, p.y + row * p.T + t0, bytes);
     if (p.want_ga) {
       io.load(Y_OFF, p.y + row * p.T + t0, bytes);
       if (t0 > 0) {
@@ -305,6 +310,10 @@ struct FoBwd : ScalarAffine<S> {
     S yprev = S(0);
     const int p0 = tpos * SPT;
     unsigned char* py = stage + Y_OFF + (size_t)p0 * sizeof(S);
+    if (FUSE && !p.want_ga) {
+#pragma unroll
+      for (int c = 0; c < CH; ++c) VecIO<S, V>::ld(py + 16 * c, &y[c * V]);
+    }
     if (p.want_ga) {
 #pragma unroll
       for (int c = 0; c < CH; ++c) VecIO<S, V>::ld(py + 16 * c, &y[c * V]);
@@ -316,8 +325,9 @@ struct FoBwd : ScalarAffine<S> {
     S acc = S(0);
 #pragma unroll
     for (int j = SPT - 1; j >= 0; --j) {
-      const S gj = r.g[j] + c;
-      r.g[j] = gj;
+      const S gyj = r.g[j];
+      const S gj = gyj + c;
+      r.g[j] = FUSE ? p.fuse_scale * (gj + y[j] - gyj) : gj;
       c = r.coef(j) * gj;
       if (p.want_ga) {
         const S yp = cj(j > 0 ? y[j - 1] : yprev);

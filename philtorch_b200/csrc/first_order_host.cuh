@@ -96,4 +96,29 @@ static int fo_bwd(int64_t B, int64_t T, const void* a, int a_batched, const void
   return rc;
 }
 
+// Reverse-time time-invariant recurrence fused with the combination out = scale * (g + second - x),
+// g[t] = x[t] + a g[t+1]  (g beyond the end: g_in / a, i.e. g[T-1] = x[T-1] + g_in).
+template <class S>
+static int fo_reverse_fused(int64_t B, int64_t T, const void* a, int a_batched, const void* x, const void* second,
+                            const void* g_in, double scale, void* out, void* first_state, void* ws, int64_t wsb,
+                            uint32_t* status, cudaStream_t st) {
+  using P = FoBwd<S, PTB_FOLTI_BWD_CH, PTB_FOLTI_BWD_STAGES, PTB_FOLTI_BWD_CTAS, 1, false, true>;
+  typename P::Params p;
+  p.a = static_cast<const S*>(a);
+  p.a_row_stride = a_batched ? 1 : 0;
+  p.zi = nullptr;
+  p.zi_stride = 0;
+  p.y = static_cast<const S*>(second);
+  p.gy = static_cast<const S*>(x);
+  p.g_in = static_cast<const S*>(g_in);
+  p.grad_x = static_cast<S*>(out);
+  p.grad_a = nullptr;
+  p.grad_zi = static_cast<S*>(first_state);
+  p.T = T;
+  p.want_ga = 0;
+  p.fuse_scale = (S)scale;
+  const bool bulk = aligned16(x) && aligned16(out) && aligned16(second) && (T * sizeof(S)) % 16 == 0;
+  return launch_scan<P>(p, B, T, bulk, ws, wsb, status, st, nullptr, nullptr);
+}
+
 }  // namespace ptb

@@ -20,6 +20,7 @@ from ..autograd import LTIRecurrence, ReverseLTIRecurrence
 __all__ = ["cspline", "cubic_spline"]
 
 POLE = math.sqrt(3.0) - 2.0
+GAIN = -6.0 * POLE / (1.0 - POLE * POLE)   # of the partial-fraction form
 MIRROR_TERMS = 1024   # POLE**k is exactly zero (also as a denormal float64) long before k = 1024
 
 
@@ -35,12 +36,61 @@ def _anticausal(x: Tensor, pole: Tensor, end: Tensor) -> Tensor:
     return ReverseLTIRecurrence.apply(pole.expand(rows), end.expand(rows).contiguous(), x)
 
 
-def _coefficients(x: Tensor, parallel_form: bool, scipy_padding: bool) -> Tensor:
+class _ParallelFormCoefficients(torch.autograd.Function):
+    """The partial-fraction evaluation as two kernel passes per direction: the causal recurrence,
+    then the reverse-time recurrence that also forms ``k (h + g - x)`` on its way out (20 B per
+    sample in fp32).  The operator is linear in x, so the backward pass is the transposed pair of
+    passes and needs nothing saved; boundary terms (mirror sum, end state) are rank-one corrections."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, scipy_padding: bool) -> Tensor:
+        ops = torch.ops.philtorch_b200
+        r = torch.full((1,), POLE, device=x.device, dtype=x.dtype)
+        off = 0 if scipy_padding else 1
+        terms = min(x.shape[-1] - off, MIRROR_TERMS)
+        pw = r.pow(torch.arange(terms, device=x.device, dtype=x.dtype))
+        start = x[:, off:off + terms] @ pw
+        h = ops.lti_recur(r, start, x)
+        end = h[:, -1] if scipy_padding else (h[:, -1] - x[:, -1]) / POLE
+        out, _ = ops.lti_recur_reverse_fused(r, x, h, end * POLE, GAIN, False)
+        ctx.scipy_padding = scipy_padding
+        ctx.save_for_backward(x)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out: Tensor):
+        (x,) = ctx.saved_tensors
+        sp = ctx.scipy_padding
+        if torch.is_grad_enabled():       # higher-order graph: differentiate the composite evaluation
+            with torch.enable_grad():
+                xr = x.detach().requires_grad_()
+                (gx,) = torch.autograd.grad(_coefficients(xr, True, sp, fused=False), xr, grad_out,
+                                            create_graph=True)
+            return gx, None
+        ops = torch.ops.philtorch_b200
+        G = grad_out.contiguous()
+        r = torch.full((1,), POLE, device=G.device, dtype=G.dtype)
+        off = 0 if sp else 1
+        terms = min(G.shape[-1] - off, MIRROR_TERMS)
+        pw = r.pow(torch.arange(terms, device=G.device, dtype=G.dtype))
+        q = ops.lti_recur(r, torch.zeros_like(G[:, 0]), G)          # transpose of the reverse-time pass
+        e_bar = q[:, -1] * POLE                                      # gradient of its end state
+        g_in = e_bar if sp else e_bar / POLE                         # ... which enters the causal pass at its last sample
+        gx, s_bar = ops.lti_recur_reverse_fused(r, G, q, g_in, GAIN, True)   # transpose of the causal pass + combine
+        gx[:, off:off + terms] += (GAIN * s_bar).unsqueeze(1) * pw   # the mirror sum that starts the causal pass
+        if not sp:
+            gx[:, -1] -= GAIN * e_bar / POLE
+        return gx, None
+
+
+def _coefficients(x: Tensor, parallel_form: bool, scipy_padding: bool, fused: bool = True) -> Tensor:
     """philtorch/lti/interp.py:23-57.  The signal is continued by mirroring: with the sample at the
     border repeated (scipy's cspline1d) or not (torch's 'reflect' padding)."""
     r = torch.tensor(POLE, device=x.device, dtype=x.dtype)
     # state of the causal recurrence at t = -1: the geometric sum over the mirrored past, of which
     # only the first terms are non-zero in floating point
+    if parallel_form and fused and x.dim() == 2 and x.shape[-1] >= 2:
+        return _ParallelFormCoefficients.apply(x, scipy_padding)
     past = x if scipy_padding else x[..., 1:]
     terms = min(past.shape[-1], MIRROR_TERMS)
     start = past[..., :terms] @ r.pow(torch.arange(terms, device=x.device, dtype=x.dtype))
@@ -51,7 +101,7 @@ def _coefficients(x: Tensor, parallel_form: bool, scipy_padding: bool) -> Tensor
         # recurrence over the mirrored signal, i.e. it runs backwards over x from the causal end state
         end = h[..., -1] if scipy_padding else (h[..., -1] - x[..., -1]) / POLE
         g = _anticausal(x, r, end)
-        return (h + g).sub_(x).mul_(-6.0 * POLE / (1.0 - POLE * POLE))
+        return (h + g).sub_(x).mul_(GAIN)
 
     # cascade: the anticausal pass runs over the output of the causal one, from its own last value
     if scipy_padding:

@@ -388,6 +388,38 @@ def _(b, a, x, y, gy, gzf, need_coef, need_zi):
             torch.empty_like(x, memory_format=torch.contiguous_format))
 
 
+# =============================================================================== reverse-time pass, fused combine
+_LIB.define("lti_recur_reverse_fused(Tensor a, Tensor x, Tensor second, Tensor? g_in, float scale, bool need_first)"
+            " -> (Tensor, Tensor)", tags=_TAGS)
+
+
+def _lti_recur_reverse_fused(a, x, second, g_in, scale, need_first):
+    """out = scale * (g + second - x), g[t] = x[t] + a g[t+1], g[T-1] = x[T-1] + g_in; (out, a g[0])."""
+    torch._check(x.dim() == 2 and second.shape == x.shape, lambda: "x and second must be (B, T) alike.")
+    torch._check(a.dim() <= 1 and a.numel() in (1, x.shape[0]), lambda: "a must hold one value or one per row.")
+    dev = _lib.require_cuda(a, x, second, g_in)
+    if a.dtype != x.dtype or second.dtype != x.dtype or (g_in is not None and g_in.dtype != x.dtype):
+        raise RuntimeError("a, second and g_in must have the same scalar type as input")
+    B, T = x.shape
+    a_c, x_c, s_c, gin_c = a.contiguous(), x.contiguous(), second.contiguous(), _opt(g_in)
+    out = torch.empty_like(x_c)
+    first = x.new_zeros(B) if need_first else x.new_empty(0)
+    if B and T:
+        _lib.call(lib.ptb_lti_recur_reverse_fused, dev, B, T, _lib.dtype_code(x), B, T, ptr(a_c),
+                  int(a.dim() == 1 and a.shape[0] == B and B > 1), ptr(x_c), ptr(s_c), ptr(gin_c), float(scale),
+                  ptr(out), ptr(first) if need_first else None)
+    return out, first
+
+
+_LIB.impl("lti_recur_reverse_fused", _lti_recur_reverse_fused, "CUDA")
+
+
+@torch.library.register_fake("philtorch_b200::lti_recur_reverse_fused")
+def _(a, x, second, g_in, scale, need_first):
+    return (torch.empty_like(x, memory_format=torch.contiguous_format),
+            x.new_empty(x.shape[0]) if need_first else x.new_empty(0))
+
+
 # =============================================================================== comb filter
 _LIB.define("comb(Tensor a, Tensor? zi, Tensor x, int delay) -> Tensor", tags=_TAGS)
 _LIB.define("comb_bwd(Tensor a, Tensor? zi, Tensor y, Tensor gy, int delay, bool need_a, bool need_zi)"
@@ -646,5 +678,5 @@ def _no_backend(name):
 for _name in ("lti_recur", "lti_recur_bwd", "lpv_recur", "lpv_recur_bwd", "lti_recur2", "lti_recur2_sx", "recur2",
               "recur2_sx", "lti_recur2_bwd", "recur2_bwd", "biquad_tdf2", "biquad_tdf2_bwd", "lpv_recur_carry", "lpv_recur_zero_carry",
               "sos_cascade", "sos_cascade_bwd", "lpv_biquad_df2", "lpv_biquad_df2_bwd",
-              "lpv_biquad_tdf2", "lpv_biquad_tdf2_bwd", "comb", "comb_bwd"):
+              "lpv_biquad_tdf2", "lpv_biquad_tdf2_bwd", "comb", "comb_bwd", "lti_recur_reverse_fused"):
     _LIB.impl(_name, _no_backend(_name), "CPU")

@@ -152,3 +152,35 @@ def test_cubic_spline_sizes(dtype, m, scipy_padding):
     ref = torch.from_numpy(callers.cubic_spline(x.double().numpy(), m, scipy_padding))
     assert rel_err(y, ref) <= tol(dtype)
     assert rel_err(y[:, ::m], x) <= tol(dtype)        # the spline interpolates the samples
+
+
+@pytest.mark.parametrize("scipy_padding", [True, False])
+@pytest.mark.parametrize("pfe", [True, False])
+def test_cspline_gradcheck(scipy_padding, pfe, comb_route):
+    if comb_route == "comb_kernels":
+        pytest.skip("independent of the comb route")
+    x = torch.randn(2, 40, dtype=torch.float64, device=DEV, generator=torch.Generator(DEV).manual_seed(3))
+    x.requires_grad_()
+    fn = lambda v: cspline(v, parallel_form=pfe, scipy_padding=scipy_padding)   # noqa: E731
+    assert torch.autograd.gradcheck(fn, (x,), eps=1e-6, atol=1e-7)
+    assert torch.autograd.gradgradcheck(fn, (x,), eps=1e-6, atol=1e-6)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+@pytest.mark.parametrize("n", [2, 3, 7, 1500, 40000])
+@pytest.mark.parametrize("scipy_padding", [True, False])
+def test_cspline_forms_agree(dtype, n, scipy_padding, comb_route):
+    """The fused two-pass evaluation against the cascaded one (different kernels), values and gradients."""
+    if comb_route == "comb_kernels":
+        pytest.skip("independent of the comb route")
+    gen = torch.Generator().manual_seed(n)
+    x0 = torch.randn(4, n, generator=gen, dtype=torch.float64).to(dtype).to(DEV)
+    gy = torch.randn(4, n, generator=gen, dtype=torch.float64).to(dtype).to(DEV)
+    res = []
+    for pfe in (True, False):
+        x = x0.clone().requires_grad_()
+        c = cspline(x, parallel_form=pfe, scipy_padding=scipy_padding)
+        res.append((c, torch.autograd.grad(c, x, gy)[0]))
+    ptb.check_errors()
+    assert rel_err(res[0][0], res[1][0]) <= 10 * tol(dtype)
+    assert rel_err(res[0][1], res[1][1]) <= 10 * tol(dtype)
