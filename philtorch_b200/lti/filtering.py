@@ -3,7 +3,8 @@
 ``lfilter`` / ``filtfilt`` / ``lfilter_zi`` keep the signatures of philtorch/lti/filtering.py.
 The default transposed-direct-form-II path runs ONE fused kernel per direction for a section
 (scalar in, scalar out); ``form="df2"`` goes through the 2x2 state-space kernels.  The FIR-based
-forms (``df1`` / ``tdf1``), orders above two and the ``diag_ssm`` backend are outside this package.
+forms (``df1`` / ``tdf1``) are outside this package; orders above two run through
+``backend="diag_ssm"`` (complex first-order modes) or, factored into sections, through ``sosfilt``.
 """
 from __future__ import annotations
 
@@ -17,7 +18,7 @@ from ..autograd import BiquadTDF2, CombFilter, SOSCascade
 from ..ops import SOS_CASCADE_SIZES
 from ..mat import companion
 from .recur import linear_recurrence
-from .ssm import state_space
+from .ssm import diag_state_space, state_space
 
 __all__ = ["lfilter", "filtfilt", "lfilter_zi", "sosfilt", "comb_filter"]
 
@@ -133,6 +134,27 @@ def _ssm_lfilter(b: Tensor, a: Tensor, x: Tensor, zi: Optional[Tensor] = None, f
     raise ValueError(f"Unknown filter form: {form}")
 
 
+def _diag_ssm_lfilter(b: Tensor, a: Tensor, x: Tensor, zi: Optional[Tensor] = None, form: str = "df2",
+                      delayed_form: bool = False, **kwargs):
+    """The filter as a state-space model evaluated in its eigenbasis (philtorch/lti/filtering.py:336-410)
+    for numerators no longer than the denominator (longer ones need the FIR quotient of a
+    polynomial division, which is outside this package)."""
+    if b.size(-1) > a.size(-1) + 1:
+        raise NotImplementedError("backend='diag_ssm' with more numerator than denominator coefficients needs an FIR "
+                                  "stage, which is outside this package")
+    if b.size(-1) < a.size(-1) + 1:
+        b = F.pad(b, (0, a.size(-1) + 1 - b.size(-1)))
+    A = companion(a)
+    b0 = b[..., :1]
+    mix = b[..., 1:] - b0 * a
+    if form == "df2":
+        return diag_state_space(x, A=A, B=None, C=mix, D=b[..., 0], zi=zi, **kwargs)
+    if form == "tdf2":
+        return diag_state_space(x, A=A.mT.conj(), B=mix.conj(), C=None, D=b[..., 0].conj(), zi=zi, out_idx=0,
+                                **kwargs)
+    raise ValueError(f"Unknown filter form: {form}")
+
+
 def lfilter(b: Tensor, a: Tensor, x: Tensor, zi: Optional[Tensor] = None, form: str = "tdf2",
             backend: str = "ssm", **kwargs) -> Union[Tensor, tuple[Tensor, Tensor]]:
     """Apply a batch of time-invariant IIR filters (``a0 = 1`` implicit, ``a`` excludes it).
@@ -143,7 +165,11 @@ def lfilter(b: Tensor, a: Tensor, x: Tensor, zi: Optional[Tensor] = None, form: 
         x: input, (B, N) or (N,), CUDA, float32 or float64.
         zi: initial state, (B, max(Mb, Ma)) or (max(Mb, Ma),); when given, ``(y, zf)`` is returned.
         form: 'tdf2' (default, fused kernel) or 'df2'.
-        backend: only 'ssm'.
+        backend: 'ssm' (orders 1-2, real kernels) or 'diag_ssm': the filter's companion system in its
+            eigenbasis, ANY order, as Ma complex first-order recurrences (``diag_state_space``); it
+            takes ``L`` / ``V`` / ``Vinv`` (poles and eigenvectors, when known) through ``**kwargs``
+            and returns a complex tensor with a vanishing imaginary part for form 'tdf2', as the
+            reference does.
         **kwargs: ``unroll_factor`` is accepted for compatibility and ignored.
     """
     squeeze_first = (x.dim() == 1) & (b.dim() == 1) & (a.dim() == 1) & ((zi is None) or (zi.dim() == 1))
@@ -153,11 +179,12 @@ def lfilter(b: Tensor, a: Tensor, x: Tensor, zi: Optional[Tensor] = None, form: 
         raise ValueError("Input signal x must be 1D or 2D.")
     assert b.dim() in (1, 2), "Numerator coefficients b must be 1D or 2D."
     assert a.dim() in (1, 2), "Denominator coefficients a must be 1D or 2D."
-    if backend != "ssm":
-        if backend == "diag_ssm":
-            raise NotImplementedError("backend='diag_ssm' (complex eigen-domain filtering) is outside this package")
+    if backend == "diag_ssm":
+        y = _diag_ssm_lfilter(b, a, x, zi, form=form, **kwargs)
+    elif backend == "ssm":
+        y = _ssm_lfilter(b, a, x, zi, form=form, **kwargs)
+    else:
         raise ValueError(f"Unknown backend: {backend}")
-    y = _ssm_lfilter(b, a, x, zi, form=form, **kwargs)
     if isinstance(y, tuple):
         y, zf = y
         if squeeze_first:

@@ -104,3 +104,56 @@ def test_argument_checks():
         diag_state_space(x, L=torch.zeros(4, 2, device=DEV))
     with pytest.raises(ValueError, match="Input matrix B"):
         diag_state_space(x, A=torch.eye(2, device=DEV), B=torch.ones(5, device=DEV))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+@pytest.mark.parametrize("num_order,den_order", [(1, 1), (2, 2), (3, 3), (4, 5), (4, 6), (0, 8)])
+@pytest.mark.parametrize("form", ["df2", "tdf2"])
+@pytest.mark.parametrize("batched", [True, False])
+def test_lfilter_diag_backend_scipy(dtype, num_order, den_order, form, batched):
+    """``lfilter(..., backend='diag_ssm')`` of any order against scipy.signal.lfilter, the check of the
+    reference's tests/test_lti_lfilter.py:355-422."""
+    import numpy as np
+    from scipy import signal
+    from philtorch_b200.lti import lfilter
+    rng = np.random.default_rng(num_order * 10 + den_order)
+    rows, n = 6, 4000
+    nb = rows if batched else 1
+    # stable denominators from random poles inside the unit circle (conjugate pairs + real poles)
+    a_rows = []
+    for _ in range(nb):
+        pairs = den_order // 2
+        p = 0.3 + 0.65 * rng.random(pairs)
+        ph = np.pi * rng.random(pairs)
+        roots = np.concatenate([p * np.exp(1j * ph), p * np.exp(-1j * ph), rng.uniform(-0.9, 0.9, den_order % 2)])
+        a_rows.append(np.real(np.poly(roots))[1:])
+    a = np.stack(a_rows)
+    b = rng.standard_normal((nb, num_order + 1))
+    x = rng.standard_normal((rows, n))
+    to = lambda v: torch.from_numpy(v if batched else v[0]).to(dtype).to(DEV)   # noqa: E731
+    y = lfilter(to(b), to(a), torch.from_numpy(x).to(dtype).to(DEV), form=form, backend="diag_ssm")
+    ptb.check_errors()
+    bq, aq = to(b).double().cpu().numpy().reshape(nb, -1), to(a).double().cpu().numpy().reshape(nb, -1)
+    xq = torch.from_numpy(x).to(dtype).double().numpy()
+    ref = np.stack([signal.lfilter(bq[i % nb], np.concatenate([[1.0], aq[i % nb]]), xq[i]) for i in range(rows)])
+    if y.is_complex():
+        assert y.imag.abs().max().item() <= (1e-3 if dtype == torch.float32 else 1e-9) * max(1.0, np.abs(ref).max())
+        y = y.real
+    assert rel_err(y, torch.from_numpy(ref)) <= (2e-3 if dtype == torch.float32 else 1e-9)
+
+
+@pytest.mark.parametrize("form", ["df2", "tdf2"])
+def test_lfilter_diag_backend_matches_ssm_backend(form):
+    """Second order with an initial state: both backends return the same (y, zf)."""
+    from philtorch_b200.lti import lfilter
+    gen = torch.Generator().manual_seed(2)
+    rows, n = 5, 3000
+    r, th = 0.5 + 0.4 * torch.rand(rows, generator=gen, dtype=torch.float64), 3.0 * torch.rand(rows, generator=gen, dtype=torch.float64)
+    a = torch.stack([-2 * r * torch.cos(th), r * r], -1).to(DEV)
+    b = torch.randn(rows, 3, generator=gen, dtype=torch.float64).to(DEV)
+    x = torch.randn(rows, n, generator=gen, dtype=torch.float64).to(DEV)
+    zi = torch.randn(rows, 2, generator=gen, dtype=torch.float64).to(DEV)
+    y1, zf1 = lfilter(b, a, x, zi=zi, form=form, backend="ssm")
+    y2, zf2 = lfilter(b, a, x, zi=zi, form=form, backend="diag_ssm")
+    assert rel_err(y2.real if y2.is_complex() else y2, y1) <= 1e-9
+    assert rel_err(zf2.real if zf2.is_complex() else zf2, zf1) <= 1e-9
