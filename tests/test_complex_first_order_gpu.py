@@ -133,3 +133,59 @@ def test_real_only_ops_reject_complex():
     with pytest.raises(RuntimeError, match="float32 and float64"):
         torch.ops.philtorch_b200.lti_recur2(A, torch.zeros(2, 2, dtype=torch.complex64, device=DEV),
                                             torch.zeros(2, 8, 2, dtype=torch.complex64, device=DEV))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64, torch.complex64, torch.complex128])
+@pytest.mark.parametrize("T", [1, 2, 37, 2561, 9300])
+@pytest.mark.parametrize("mode", ["batched", "scalar"])
+def test_reverse_time_recurrence(dtype, T, mode):
+    """``ReverseLTIRecurrence`` (the adjoint kernel as a forward operator) against the oracle run on
+    the reversed signal, values and all gradients."""
+    from philtorch_b200.autograd import ReverseLTIRecurrence
+    B = 3
+    g = torch.Generator().manual_seed(T + len(mode))
+    cplx = dtype.is_complex
+    a = _poles((B,), g) if cplx else torch.rand(B, generator=g, dtype=torch.float64) * 1.9 - 0.95
+    a = (a if mode == "batched" else a[0]).to(dtype)
+    mk = (lambda s: _randc(s, g)) if cplx else (lambda s: torch.randn(*s, generator=g, dtype=torch.float64))
+    end, x, gy = mk((B,)).to(dtype), mk((B, T)).to(dtype), mk((B, T)).to(dtype)
+    a_, end_, x_ = (t.to(DEV).requires_grad_() for t in (a, end, x))
+    out = ReverseLTIRecurrence.apply(a_, end_, x_)
+    ga, gend, gx = torch.autograd.grad(out, (a_, end_, x_), gy.to(DEV))
+    ptb.check_errors()
+    ref = cport.lti_recur(a, end, x.flip(1)).flip(1)
+    ga_ref, gend_ref, gx_ref = cport.lti_recur_bwd(a, end, ref.flip(1).contiguous(), gy.flip(1).contiguous())
+    t = tol(dtype)
+    assert rel_err(out, ref) <= t
+    assert rel_err(gx, gx_ref.flip(1)) <= t
+    assert rel_err(gend, gend_ref) <= t
+    assert rel_err(ga, ga_ref.reshape(ga.shape)) <= 10 * t
+
+
+def test_reverse_time_gradcheck():
+    from philtorch_b200.autograd import ReverseLTIRecurrence
+    g = torch.Generator().manual_seed(4)
+    a = _poles((2,), g).to(DEV).requires_grad_()
+    end = _randc((2,), g).to(DEV).requires_grad_()
+    x = _randc((2, 19), g).to(DEV).requires_grad_()
+    assert torch.autograd.gradcheck(ReverseLTIRecurrence.apply, (a, end, x), eps=1e-6, atol=1e-6)
+    assert torch.autograd.gradgradcheck(ReverseLTIRecurrence.apply, (a, end, x), eps=1e-6, atol=1e-5)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+@pytest.mark.parametrize("T", [1, 5, 2560, 2561, 30000])
+def test_reverse_fused_op(dtype, T):
+    """out = scale * (g + second - x) with g the reverse-time recurrence of x; first state a * g[0]."""
+    B = 4
+    g = torch.Generator().manual_seed(T)
+    a = (torch.rand(B, generator=g, dtype=torch.float64) * 1.9 - 0.95).to(dtype)
+    x, second = (torch.randn(B, T, generator=g, dtype=torch.float64).to(dtype) for _ in range(2))
+    g_in = torch.randn(B, generator=g, dtype=torch.float64).to(dtype)
+    out, first = torch.ops.philtorch_b200.lti_recur_reverse_fused(a.to(DEV), x.to(DEV), second.to(DEV),
+                                                                  g_in.to(DEV), 0.75, True)
+    ptb.check_errors()
+    xr = x.flip(1).contiguous()
+    xr[:, 0] += g_in                       # the state entering from the right adds to the last sample
+    rev = cport.lti_recur(a, torch.zeros(B, dtype=dtype), xr).flip(1)
+    assert rel_err(out, 0.75 * (rev + second - x)) <= tol(dtype)
+    assert rel_err(first, a * rev[:, 0]) <= tol(dtype)
