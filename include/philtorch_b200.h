@@ -295,6 +295,22 @@ int ptb_comb_bwd(int dtype, int64_t B, int64_t N, int64_t delay, const void* a, 
                  int zi_mode, const void* y, const void* gy, void* grad_x, void* partial, void* grad_state,
                  void* workspace, int64_t workspace_bytes, uint32_t* status, ptb_stream_t stream);
 
+/* ---- output map of a state-space model in its eigenbasis (replaces V w, the shifting
+ *      concatenation and the complex product with C of philtorch/lti/ssm.py:805-830) ---------------
+ * y[r, t] = sum_m coef[r, m] * w[r, m, t-1], with w[r, m, -1] = w0[r, m]; the real part only when
+ * real_out.  dtype PTB_C64 / PTB_C128: w (rows, M, N), w0 (rows, M), coef (M,) or (rows, M) when
+ * coef_batched are complex; y and gy are (rows, N), real of the matching precision when real_out,
+ * else complex.  Adjoint: grad_w (rows, M, N), grad_w0 (rows, M); `partial` (may be NULL) receives
+ * rows * ptb_modal_mix_partial_blocks(N) * M complex partial sums of grad_coef, (row, block, m).
+ * workspace and status are unused and may be NULL. */
+int64_t ptb_modal_mix_partial_blocks(int64_t N);
+int ptb_modal_mix_fwd(int dtype, int64_t rows, int64_t M, int64_t N, const void* w, const void* w0, const void* coef,
+                      int coef_batched, int real_out, void* y, void* workspace, int64_t workspace_bytes,
+                      uint32_t* status, ptb_stream_t stream);
+int ptb_modal_mix_bwd(int dtype, int64_t rows, int64_t M, int64_t N, const void* w, const void* w0, const void* coef,
+                      int coef_batched, int real_out, const void* gy, void* grad_w, void* grad_w0, void* partial,
+                      void* workspace, int64_t workspace_bytes, uint32_t* status, ptb_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -331,6 +331,36 @@ class BiquadTDF2(Function):
                 _none_if_empty(gx, need_x))
 
 
+def modal_mix_reference(w: Tensor, w0: Tensor, coef: Tensor, real_out: bool) -> Tensor:
+    """``ModalMix`` in plain torch operations (the differentiable form behind higher-order graphs)."""
+    prev = torch.cat([w0.unsqueeze(-1), w[:, :, :-1]], dim=2)
+    y = (coef.unsqueeze(-1) * prev).sum(1)
+    return y.real if real_out else y
+
+
+class ModalMix(Function):
+    """y[r,t] = sum_m coef[(r,)m] * w[r,m,t-1] with w[r,m,-1] = w0[r,m], optionally its real part:
+    the output map of ``diag_state_space`` (mode sum, one-sample shift, real part) in one pass."""
+
+    @staticmethod
+    def forward(ctx: Any, w: Tensor, w0: Tensor, coef: Tensor, real_out: bool) -> Tensor:
+        ctx.real_out = real_out
+        ctx.save_for_backward(w, w0, coef)
+        return _ops.modal_mix(w, w0, coef, real_out)
+
+    @staticmethod
+    def backward(ctx: Any, grad_y: Tensor):
+        w, w0, coef = ctx.saved_tensors
+        need_w, need_w0, need_coef = ctx.needs_input_grad[:3]
+        if torch.is_grad_enabled():
+            with torch.enable_grad():
+                ins = [t.detach().requires_grad_() for t in (w, w0, coef)]
+                gs = torch.autograd.grad(modal_mix_reference(*ins, ctx.real_out), ins, grad_y, create_graph=True)
+            return gs[0] if need_w else None, gs[1] if need_w0 else None, gs[2] if need_coef else None, None
+        gw, gw0, gc = _ops.modal_mix_bwd(w, w0, coef, grad_y, ctx.real_out, need_coef)
+        return gw if need_w else None, gw0 if need_w0 else None, _none_if_empty(gc, need_coef), None
+
+
 class CombFilter(Function):
     """y[t] = x[t] - a*y[t-delay] on the signal's own layout, (a, zi, x, delay) -> y; zi: None, (delay,)
     or (B, delay) in the reference's order (zi[..., k] = the output k+1 samples before the start)."""

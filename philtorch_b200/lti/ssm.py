@@ -12,7 +12,7 @@ from typing import Optional
 import torch
 from torch import Tensor
 
-from ..autograd import LTIMatrixRecurrence, LTIRecurrence, matrix_recurrence_scalar_input
+from ..autograd import LTIMatrixRecurrence, LTIRecurrence, ModalMix, matrix_recurrence_scalar_input
 
 __all__ = ["LTIMatrixRecurrence", "state_space_recursion", "state_space", "diag_state_space",
            "extension_backend_indicator"]
@@ -292,11 +292,10 @@ def diag_state_space(x: Tensor, L: Optional[Tensor] = None, V: Optional[Tensor] 
     if vector_out:
         after = (CV @ w).mT                                                     # (batch, N, K)
         first = (CV @ w0.unsqueeze(-1)).squeeze(-1).expand(batch_size, -1)      # (batch, K)
-    else:
-        after = (CV.unsqueeze(-2) @ w).squeeze(-2)                              # (batch, N)
-        first = (CV * w0).sum(-1)                                               # (batch,)
-    h = torch.cat([first.unsqueeze(1), after[:, :-1]], dim=1)
-    if real_out:
-        h = h.real
+        h = torch.cat([first.unsqueeze(1), after[:, :-1]], dim=1)
+        if real_out:
+            h = h.real
+    else:                                                                       # one pass: mode sum, shift, real part
+        h = ModalMix.apply(w, w0, CV.contiguous(), real_out)
     y = _output_map(h, x, None, D, batch_size, M)
     return (y, zf) if return_zf else y

@@ -420,6 +420,70 @@ def _(a, x, second, g_in, scale, need_first):
             x.new_empty(x.shape[0]) if need_first else x.new_empty(0))
 
 
+# =============================================================================== eigenbasis output map
+_LIB.define("modal_mix(Tensor w, Tensor w0, Tensor coef, bool real_out) -> Tensor", tags=_TAGS)
+_LIB.define("modal_mix_bwd(Tensor w, Tensor w0, Tensor coef, Tensor gy, bool real_out, bool need_coef)"
+            " -> (Tensor, Tensor, Tensor)", tags=_TAGS)
+
+
+def _check_modal(w: Tensor, w0: Tensor, coef: Tensor) -> None:
+    torch._check(w.dim() == 3 and w.is_complex(), lambda: "w must be complex (rows, M, N).")
+    torch._check(tuple(w0.shape) == tuple(w.shape[:2]), lambda: "w0 must be (rows, M).")
+    torch._check(tuple(coef.shape) in ((w.shape[1],), tuple(w.shape[:2])), lambda: "coef must be (M,) or (rows, M).")
+    torch._check(w0.dtype == w.dtype and coef.dtype == w.dtype, lambda: "w, w0 and coef must share a complex dtype.")
+
+
+def _real_of(dtype):
+    return torch.float32 if dtype == torch.complex64 else torch.float64
+
+
+def _modal_mix(w, w0, coef, real_out):
+    """y[r,t] = sum_m coef[r,m] w[r,m,t-1] (w[r,m,-1] = w0[r,m]); the real part when real_out."""
+    _check_modal(w, w0, coef)
+    dev = _lib.require_cuda(w, w0, coef)
+    R, M, N = w.shape
+    w_c, w0_c, c_c = _dense(w), _dense(w0), _dense(coef)
+    y = torch.empty(R, N, dtype=_real_of(w.dtype) if real_out else w.dtype, device=w.device)
+    if R and N:
+        _lib.call(lib.ptb_modal_mix_fwd, dev, R, N, _lib.dtype_code(w, True), R, M, N, ptr(w_c), ptr(w0_c), ptr(c_c),
+                  int(coef.dim() == 2), int(real_out), ptr(y), ws_bytes=0)
+    return y
+
+
+def _modal_mix_bwd(w, w0, coef, gy, real_out, need_coef):
+    dev = _lib.require_cuda(w, w0, coef, gy)
+    R, M, N = w.shape
+    w_c, w0_c, c_c, gy_c = _dense(w), _dense(w0), _dense(coef), _dense(gy)
+    gw = torch.empty_like(w_c)
+    gw0 = torch.zeros_like(w0_c)
+    nblk = lib.ptb_modal_mix_partial_blocks(N)
+    part = torch.zeros(R, nblk, M, dtype=w.dtype, device=w.device) if need_coef else None
+    if R and N:
+        _lib.call(lib.ptb_modal_mix_bwd, dev, R, N, _lib.dtype_code(w, True), R, M, N, ptr(w_c), ptr(w0_c), ptr(c_c),
+                  int(coef.dim() == 2), int(real_out), ptr(gy_c), ptr(gw), ptr(gw0), ptr(part), ws_bytes=0)
+    if need_coef:
+        gc = part.sum(1) if coef.dim() == 2 else part.sum((0, 1))
+    else:
+        gc = coef.new_empty(0)
+    return gw, gw0, gc
+
+
+_LIB.impl("modal_mix", _modal_mix, "CUDA")
+_LIB.impl("modal_mix_bwd", _modal_mix_bwd, "CUDA")
+
+
+@torch.library.register_fake("philtorch_b200::modal_mix")
+def _(w, w0, coef, real_out):
+    _check_modal(w, w0, coef)
+    return torch.empty(w.shape[0], w.shape[2], dtype=_real_of(w.dtype) if real_out else w.dtype, device=w.device)
+
+
+@torch.library.register_fake("philtorch_b200::modal_mix_bwd")
+def _(w, w0, coef, gy, real_out, need_coef):
+    return (torch.empty_like(w, memory_format=torch.contiguous_format), torch.empty_like(w0),
+            torch.empty_like(coef) if need_coef else coef.new_empty(0))
+
+
 # =============================================================================== comb filter
 _LIB.define("comb(Tensor a, Tensor? zi, Tensor x, int delay) -> Tensor", tags=_TAGS)
 _LIB.define("comb_bwd(Tensor a, Tensor? zi, Tensor y, Tensor gy, int delay, bool need_a, bool need_zi)"
@@ -678,5 +742,6 @@ def _no_backend(name):
 for _name in ("lti_recur", "lti_recur_bwd", "lpv_recur", "lpv_recur_bwd", "lti_recur2", "lti_recur2_sx", "recur2",
               "recur2_sx", "lti_recur2_bwd", "recur2_bwd", "biquad_tdf2", "biquad_tdf2_bwd", "lpv_recur_carry", "lpv_recur_zero_carry",
               "sos_cascade", "sos_cascade_bwd", "lpv_biquad_df2", "lpv_biquad_df2_bwd",
-              "lpv_biquad_tdf2", "lpv_biquad_tdf2_bwd", "comb", "comb_bwd", "lti_recur_reverse_fused"):
+              "lpv_biquad_tdf2", "lpv_biquad_tdf2_bwd", "comb", "comb_bwd", "lti_recur_reverse_fused",
+              "modal_mix", "modal_mix_bwd"):
     _LIB.impl(_name, _no_backend(_name), "CPU")

@@ -25,6 +25,15 @@ class _Reverse:
         return cport.lti_recur(a, end.contiguous(), x.flip(1)).flip(1)
 
 
+class _Mix:
+    """Stand-in for ``ModalMix``: its plain-torch form."""
+
+    @staticmethod
+    def apply(w, w0, coef, real_out):
+        from philtorch_b200.autograd import modal_mix_reference
+        return modal_mix_reference(w, w0, coef, real_out)
+
+
 @pytest.fixture
 def cpu_kernels(monkeypatch):
     import philtorch_b200.lti.filtering as filtering
@@ -34,6 +43,7 @@ def cpu_kernels(monkeypatch):
     for mod in (recur, interp, ssm):
         monkeypatch.setattr(mod, "LTIRecurrence", _Forward)
     monkeypatch.setattr(interp, "ReverseLTIRecurrence", _Reverse)
+    monkeypatch.setattr(ssm, "ModalMix", _Mix)
     monkeypatch.setattr(filtering, "COMB_KERNEL_MIN_LANES", 10 ** 12)   # the folded route is the host logic
 
 

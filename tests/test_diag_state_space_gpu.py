@@ -157,3 +157,27 @@ def test_lfilter_diag_backend_matches_ssm_backend(form):
     y2, zf2 = lfilter(b, a, x, zi=zi, form=form, backend="diag_ssm")
     assert rel_err(y2.real if y2.is_complex() else y2, y1) <= 1e-9
     assert rel_err(zf2.real if zf2.is_complex() else zf2, zf1) <= 1e-9
+
+
+@pytest.mark.parametrize("dtype", [torch.complex64, torch.complex128])
+@pytest.mark.parametrize("real_out", [True, False])
+@pytest.mark.parametrize("coef_batched", [True, False])
+@pytest.mark.parametrize("rows,M,N", [(1, 1, 1), (3, 4, 2), (5, 3, 255), (2, 6, 256), (4, 2, 257), (3, 5, 5000)])
+def test_modal_mix_kernels(dtype, real_out, coef_batched, rows, M, N):
+    """The fused output map (mode sum, one-sample shift, real part) and its adjoint against plain torch."""
+    from philtorch_b200.autograd import ModalMix, modal_mix_reference
+    gen = torch.Generator().manual_seed(rows * 100 + M * 10 + N)
+    mk = lambda *s: torch.complex(torch.randn(*s, generator=gen, dtype=torch.float64),   # noqa: E731
+                                  torch.randn(*s, generator=gen, dtype=torch.float64)).to(dtype).to(DEV)
+    w, w0, coef = mk(rows, M, N), mk(rows, M), mk(*((rows, M) if coef_batched else (M,)))
+    gy = mk(rows, N)
+    gy = gy.real.contiguous() if real_out else gy
+    outs = []
+    for fn in (lambda *a: ModalMix.apply(*a), modal_mix_reference):
+        ins = [t.clone().requires_grad_() for t in (w, w0, coef)]
+        y = fn(*ins, real_out)
+        outs.append([y] + list(torch.autograd.grad(y, ins, gy)))
+    ptb.check_errors()
+    t = 1e-5 if dtype == torch.complex64 else 1e-12
+    for got, ref in zip(outs[0], outs[1]):
+        assert got.dtype == ref.dtype and rel_err(got, ref) <= t
