@@ -298,7 +298,9 @@ int ptb_comb_bwd(int dtype, int64_t B, int64_t N, int64_t delay, const void* a, 
 /* ---- output map of a state-space model in its eigenbasis (replaces V w, the shifting
  *      concatenation and the complex product with C of philtorch/lti/ssm.py:805-830) ---------------
  * y[r, t] = sum_m coef[r, m] * w[r, m, t-1], with w[r, m, -1] = w0[r, m]; the real part only when
- * real_out.  dtype PTB_C64 / PTB_C128: w (rows, M, N), w0 (rows, M), coef (M,) or (rows, M) when
+ * real_out.  ptb_modal_mix_fwd with w0 == NULL applies no delay: y[r, t] = sum_m coef[r, m] * w[r, m, t]
+ * (the transposed input map, i.e. the gradient of a real input broadcast into the modes).
+ * dtype PTB_C64 / PTB_C128: w (rows, M, N), w0 (rows, M), coef (M,) or (rows, M) when
  * coef_batched are complex; y and gy are (rows, N), real of the matching precision when real_out,
  * else complex.  Adjoint: grad_w (rows, M, N), grad_w0 (rows, M); `partial` (may be NULL) receives
  * rows * ptb_modal_mix_partial_blocks(N) * M complex partial sums of grad_coef, (row, block, m).
@@ -307,6 +309,13 @@ int64_t ptb_modal_mix_partial_blocks(int64_t N);
 int ptb_modal_mix_fwd(int dtype, int64_t rows, int64_t M, int64_t N, const void* w, const void* w0, const void* coef,
                       int coef_batched, int real_out, void* y, void* workspace, int64_t workspace_bytes,
                       uint32_t* status, ptb_stream_t stream);
+/* Input map for a real scalar input: u[r, m, t] = gain[r, m] * x[r, t]; x real (rows, N) of the
+ * precision matching dtype (PTB_C64: float, PTB_C128: double), gain (M,) or (rows, M) complex,
+ * u (rows, M, N) complex (philtorch/lti/ssm.py:783-788).  Its adjoint w.r.t. x is
+ * ptb_modal_mix_fwd with w0 == NULL, coef = conj(gain) and real_out = 1. */
+int ptb_modal_drive_fwd(int dtype, int64_t rows, int64_t M, int64_t N, const void* x, const void* gain,
+                        int gain_batched, void* u, void* workspace, int64_t workspace_bytes, uint32_t* status,
+                        ptb_stream_t stream);
 int ptb_modal_mix_bwd(int dtype, int64_t rows, int64_t M, int64_t N, const void* w, const void* w0, const void* coef,
                       int coef_batched, int real_out, const void* gy, void* grad_w, void* grad_w0, void* partial,
                       void* workspace, int64_t workspace_bytes, uint32_t* status, ptb_stream_t stream);

@@ -87,6 +87,8 @@ lib.ptb_modal_mix_partial_blocks.argtypes = [_i64]
 lib.ptb_modal_mix_partial_blocks.restype = _i64
 lib.ptb_modal_mix_fwd.argtypes = [_i32, _i64, _i64, _i64, _vp, _vp, _vp, _i32, _i32, _vp] + _tail
 lib.ptb_modal_mix_fwd.restype = _i32
+lib.ptb_modal_drive_fwd.argtypes = [_i32, _i64, _i64, _i64, _vp, _vp, _i32, _vp] + _tail
+lib.ptb_modal_drive_fwd.restype = _i32
 lib.ptb_modal_mix_bwd.argtypes = [_i32, _i64, _i64, _i64, _vp, _vp, _vp, _i32, _i32, _vp, _vp, _vp, _vp] + _tail
 lib.ptb_modal_mix_bwd.restype = _i32
 lib.ptb_comb_partial_blocks.argtypes = [_i64]

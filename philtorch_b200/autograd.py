@@ -361,6 +361,36 @@ class ModalMix(Function):
         return gw if need_w else None, gw0 if need_w0 else None, _none_if_empty(gc, need_coef), None
 
 
+class ModalDrive(Function):
+    """u[r,m,t] = gain[(r,)m] * x[r,t]: a real signal broadcast into M complex modes (the input map
+    of ``diag_state_space`` for a scalar input).  The backward pass is one ``modal_mix`` launch
+    (the mode sum with conj(gain), no delay) instead of a complex product and a strided reduction."""
+
+    @staticmethod
+    def forward(ctx: Any, x: Tensor, gain: Tensor) -> Tensor:
+        ctx.save_for_backward(x, gain)
+        if x.is_cuda and not x.is_complex() and gain.is_complex() and gain.real.dtype == x.dtype:
+            return _ops.modal_drive(x, gain)
+        return gain.unsqueeze(-1) * x.unsqueeze(1)
+
+    @staticmethod
+    def backward(ctx: Any, grad_u: Tensor):
+        x, gain = ctx.saved_tensors
+        need_x, need_gain = ctx.needs_input_grad
+        if torch.is_grad_enabled():
+            with torch.enable_grad():
+                ins = [x.detach().requires_grad_(), gain.detach().requires_grad_()]
+                gs = torch.autograd.grad(ins[1].unsqueeze(-1) * ins[0].unsqueeze(1), ins, grad_u, create_graph=True)
+            return gs[0] if need_x else None, gs[1] if need_gain else None
+        gx = _ops.modal_mix(grad_u, None, gain.conj(), not x.is_complex()).to(x.dtype) if need_x else None
+        ggain = None
+        if need_gain:
+            ggain = (grad_u * x.conj().unsqueeze(1)).sum(-1)
+            if gain.dim() == 1:
+                ggain = ggain.sum(0)
+        return gx, ggain
+
+
 class CombFilter(Function):
     """y[t] = x[t] - a*y[t-delay] on the signal's own layout, (a, zi, x, delay) -> y; zi: None, (delay,)
     or (B, delay) in the reference's order (zi[..., k] = the output k+1 samples before the start)."""

@@ -12,7 +12,7 @@ from typing import Optional
 import torch
 from torch import Tensor
 
-from ..autograd import LTIMatrixRecurrence, LTIRecurrence, ModalMix, matrix_recurrence_scalar_input
+from ..autograd import LTIMatrixRecurrence, LTIRecurrence, ModalDrive, ModalMix, matrix_recurrence_scalar_input
 
 __all__ = ["LTIMatrixRecurrence", "state_space_recursion", "state_space", "diag_state_space",
            "extension_backend_indicator"]
@@ -254,8 +254,10 @@ def diag_state_space(x: Tensor, L: Optional[Tensor] = None, V: Optional[Tensor] 
             features = -1 if x.dim() == 2 else x.size(-1)
             raise ValueError(f"Input matrix B must be of shape ({M},), ({batch_size}, {M}), ({M}, {features}) or "
                              f"({batch_size}, {M}, {features}), got {shp}")
-    if x.dim() == 2 and tuple(G.shape) in ((M,), (batch_size, M)):
-        u = G.unsqueeze(-1) * xc.unsqueeze(1)            # (batch, M, N) without a transpose
+    if x.dim() == 2 and tuple(G.shape) in ((M,), (batch_size, M)) and G.is_complex():
+        u = ModalDrive.apply(x, G)                       # (batch, M, N) without a transpose
+    elif x.dim() == 2 and tuple(G.shape) in ((M,), (batch_size, M)):
+        u = G.unsqueeze(-1) * xc.unsqueeze(1)
     else:
         u = _input_map(xc, G, batch_size, M).mT
     u = u.expand(batch_size, M, N).reshape(batch_size * M, N)

@@ -421,16 +421,17 @@ def _(a, x, second, g_in, scale, need_first):
 
 
 # =============================================================================== eigenbasis output map
-_LIB.define("modal_mix(Tensor w, Tensor w0, Tensor coef, bool real_out) -> Tensor", tags=_TAGS)
+_LIB.define("modal_mix(Tensor w, Tensor? w0, Tensor coef, bool real_out) -> Tensor", tags=_TAGS)
 _LIB.define("modal_mix_bwd(Tensor w, Tensor w0, Tensor coef, Tensor gy, bool real_out, bool need_coef)"
             " -> (Tensor, Tensor, Tensor)", tags=_TAGS)
 
 
 def _check_modal(w: Tensor, w0: Tensor, coef: Tensor) -> None:
     torch._check(w.dim() == 3 and w.is_complex(), lambda: "w must be complex (rows, M, N).")
-    torch._check(tuple(w0.shape) == tuple(w.shape[:2]), lambda: "w0 must be (rows, M).")
+    torch._check(w0 is None or tuple(w0.shape) == tuple(w.shape[:2]), lambda: "w0 must be (rows, M).")
     torch._check(tuple(coef.shape) in ((w.shape[1],), tuple(w.shape[:2])), lambda: "coef must be (M,) or (rows, M).")
-    torch._check(w0.dtype == w.dtype and coef.dtype == w.dtype, lambda: "w, w0 and coef must share a complex dtype.")
+    torch._check((w0 is None or w0.dtype == w.dtype) and coef.dtype == w.dtype,
+                 lambda: "w, w0 and coef must share a complex dtype.")
 
 
 def _real_of(dtype):
@@ -438,11 +439,12 @@ def _real_of(dtype):
 
 
 def _modal_mix(w, w0, coef, real_out):
-    """y[r,t] = sum_m coef[r,m] w[r,m,t-1] (w[r,m,-1] = w0[r,m]); the real part when real_out."""
+    """y[r,t] = sum_m coef[r,m] w[r,m,t-1] (w[r,m,-1] = w0[r,m]); the real part when real_out.
+    Without w0 there is no delay: y[r,t] = sum_m coef[r,m] w[r,m,t]."""
     _check_modal(w, w0, coef)
     dev = _lib.require_cuda(w, w0, coef)
     R, M, N = w.shape
-    w_c, w0_c, c_c = _dense(w), _dense(w0), _dense(coef)
+    w_c, w0_c, c_c = _dense(w), _opt(w0), _dense(coef)
     y = torch.empty(R, N, dtype=_real_of(w.dtype) if real_out else w.dtype, device=w.device)
     if R and N:
         _lib.call(lib.ptb_modal_mix_fwd, dev, R, N, _lib.dtype_code(w, True), R, M, N, ptr(w_c), ptr(w0_c), ptr(c_c),
@@ -466,6 +468,39 @@ def _modal_mix_bwd(w, w0, coef, gy, real_out, need_coef):
     else:
         gc = coef.new_empty(0)
     return gw, gw0, gc
+
+
+_LIB.define("modal_drive(Tensor x, Tensor gain) -> Tensor", tags=_TAGS)
+
+
+def _check_modal_drive(x: Tensor, gain: Tensor) -> None:
+    torch._check(x.dim() == 2 and not x.is_complex(), lambda: "x must be real (rows, N).")
+    torch._check(gain.is_complex() and (gain.dim() == 1 or (gain.dim() == 2 and gain.shape[0] == x.shape[0])),
+                 lambda: "gain must be complex (M,) or (rows, M).")
+    torch._check(_real_of(gain.dtype) == x.dtype, lambda: "x must have the precision of gain.")
+
+
+def _modal_drive(x, gain):
+    """u[r,m,t] = gain[(r,)m] * x[r,t]."""
+    _check_modal_drive(x, gain)
+    dev = _lib.require_cuda(x, gain)
+    R, N = x.shape
+    M = gain.shape[-1]
+    x_c, g_c = x.contiguous(), _dense(gain)
+    u = torch.empty(R, M, N, dtype=gain.dtype, device=x.device)
+    if R and N:
+        _lib.call(lib.ptb_modal_drive_fwd, dev, R, N, _lib.dtype_code(gain, True), R, M, N, ptr(x_c), ptr(g_c),
+                  int(gain.dim() == 2), ptr(u), ws_bytes=0)
+    return u
+
+
+_LIB.impl("modal_drive", _modal_drive, "CUDA")
+
+
+@torch.library.register_fake("philtorch_b200::modal_drive")
+def _(x, gain):
+    _check_modal_drive(x, gain)
+    return torch.empty(x.shape[0], gain.shape[-1], x.shape[1], dtype=gain.dtype, device=x.device)
 
 
 _LIB.impl("modal_mix", _modal_mix, "CUDA")
@@ -743,5 +778,5 @@ for _name in ("lti_recur", "lti_recur_bwd", "lpv_recur", "lpv_recur_bwd", "lti_r
               "recur2_sx", "lti_recur2_bwd", "recur2_bwd", "biquad_tdf2", "biquad_tdf2_bwd", "lpv_recur_carry", "lpv_recur_zero_carry",
               "sos_cascade", "sos_cascade_bwd", "lpv_biquad_df2", "lpv_biquad_df2_bwd",
               "lpv_biquad_tdf2", "lpv_biquad_tdf2_bwd", "comb", "comb_bwd", "lti_recur_reverse_fused",
-              "modal_mix", "modal_mix_bwd"):
+              "modal_mix", "modal_mix_bwd", "modal_drive"):
     _LIB.impl(_name, _no_backend(_name), "CPU")

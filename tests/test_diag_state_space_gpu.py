@@ -181,3 +181,27 @@ def test_modal_mix_kernels(dtype, real_out, coef_batched, rows, M, N):
     t = 1e-5 if dtype == torch.complex64 else 1e-12
     for got, ref in zip(outs[0], outs[1]):
         assert got.dtype == ref.dtype and rel_err(got, ref) <= t
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+@pytest.mark.parametrize("gain_batched", [True, False])
+def test_modal_drive(dtype, gain_batched):
+    """Real input broadcast into complex modes: values and both gradients against plain torch."""
+    from philtorch_b200.autograd import ModalDrive
+    gen = torch.Generator().manual_seed(8)
+    rows, M, N = 4, 3, 3000
+    cdt = torch.complex64 if dtype == torch.float32 else torch.complex128
+    x = torch.randn(rows, N, generator=gen, dtype=torch.float64).to(dtype).to(DEV)
+    gain = torch.complex(torch.randn(*((rows, M) if gain_batched else (M,)), generator=gen, dtype=torch.float64),
+                         torch.randn(*((rows, M) if gain_batched else (M,)), generator=gen, dtype=torch.float64))
+    gain = gain.to(cdt).to(DEV)
+    gu = torch.complex(torch.randn(rows, M, N, generator=gen, dtype=torch.float64),
+                       torch.randn(rows, M, N, generator=gen, dtype=torch.float64)).to(cdt).to(DEV)
+    outs = []
+    for fn in (ModalDrive.apply, lambda a, b: b.unsqueeze(-1) * a.unsqueeze(1)):
+        a, b = x.clone().requires_grad_(), gain.clone().requires_grad_()
+        u = fn(a, b)
+        outs.append([u] + list(torch.autograd.grad(u, (a, b), gu)))
+    ptb.check_errors()
+    for got, ref in zip(outs[0], outs[1]):
+        assert got.dtype == ref.dtype and rel_err(got, ref) <= (1e-5 if dtype == torch.float32 else 1e-12)
