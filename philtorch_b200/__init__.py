@@ -8,9 +8,9 @@ and every op raises for CPU tensors.
 """
 from . import _lib  # noqa: F401  raises ImportError if libphiltorch_b200.so is not built
 from . import ops  # noqa: F401
-from . import lti, lpv  # noqa: F401
+from . import lti, lpv, prototype  # noqa: F401
 from ._lib import check_errors
 
 EXTENSION_LOADED = True
 __version__ = "0.1"
-__all__ = ["lti", "lpv", "ops", "check_errors", "EXTENSION_LOADED"]
+__all__ = ["lti", "lpv", "prototype", "ops", "check_errors", "EXTENSION_LOADED"]

@@ -242,8 +242,58 @@ def diag_state_space_cases(pt):
              A2=_np(A2), x2=_np(x2), y_idx=_np(y_idx))
 
 
+def newton_cases(pt):
+    """``philtorch.prototype.nl.newton_solve`` on the feed-forward compressor smoother of the
+    reference's tests/test_nl.py (first order) and on a two-state nonlinear recurrence."""
+    from philtorch.prototype.nl import newton_solve
+
+    torch.manual_seed(20240614)
+    Bn, N = 3, 100
+    g = torch.rand(Bn, N, 1, dtype=torch.float64)
+    at, rt = torch.rand(Bn, 1, 1, dtype=torch.float64), torch.rand(Bn, 1, 1, dtype=torch.float64)
+    init = torch.ones(Bn, 1, dtype=torch.float64)
+
+    def smoother(prev, x):
+        coeff = torch.where(x < prev, at, rt)
+        return coeff * x + (1 - coeff) * prev
+
+    def smoother_jac(prev, x):
+        return (1 - torch.where(x < prev, at, rt)).unsqueeze(-2)
+
+    y, iters = newton_solve(smoother, g, torch.ones(Bn, N, 1, dtype=torch.float64), init=init, max_iter=10,
+                            atol=1e-8, rtol=1e-6, fprime=smoother_jac,
+                            unroll_factor=4)   # its pure-PyTorch scan: order 1 with factor 1 needs torchlpc
+    seq, h = [], init
+    for t in range(N):
+        h = smoother(h.unsqueeze(1), g[:, t:t + 1]).squeeze(1)
+        seq.append(h)
+    W = 0.4 * torch.randn(2, 2, dtype=torch.float64)
+    x2 = torch.randn(Bn, N, 2, dtype=torch.float64)
+    init2 = torch.zeros(Bn, 2, dtype=torch.float64)
+
+    def cell(prev, x):
+        return torch.tanh(prev @ W.T + x)
+
+    def cell_jac(prev, x):
+        return (1 - torch.tanh(prev @ W.T + x) ** 2).unsqueeze(-1) * W
+
+    y2, iters2 = newton_solve(cell, x2, torch.zeros(Bn, N, 2, dtype=torch.float64), init=init2, max_iter=12,
+                              atol=1e-10, rtol=1e-8, fprime=cell_jac)
+    seq2, h = [], init2
+    for t in range(N):
+        h = cell(h.unsqueeze(1), x2[:, t:t + 1]).squeeze(1)
+        seq2.append(h)
+    save("newton_solve_f64", g=_np(g), at=_np(at), rt=_np(rt), init=_np(init), y=_np(y),
+         iters=np.array(iters), y_sequential=_np(torch.stack(seq, 1)),
+         W=_np(W), x2=_np(x2), init2=_np(init2), y2=_np(y2), iters2=np.array(iters2),
+         y2_sequential=_np(torch.stack(seq2, 1)))
+
+
 def main():
     pt = import_reference()
+    if len(sys.argv) > 1 and sys.argv[1] == "newton":        # only this group
+        newton_cases(pt)
+        return
     if len(sys.argv) > 1 and sys.argv[1] == "diag_ssm":      # only this group
         diag_state_space_cases(pt)
         return
