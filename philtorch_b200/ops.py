@@ -7,7 +7,8 @@ per-sample-coefficient op and fused adjoint ops, so a backward pass is one kerne
 flip/roll/cat copies around a second forward call.
 
 Every op runs the hand-written sm_100a kernels through the C ABI (``_lib``); CPU tensors and
-dtypes other than float32/float64 (and, for the first-order recurrences, complex64/complex128) raise.
+dtypes other than float32/float64 (and, for the first-order recurrences, complex64/complex128 and
+float16/bfloat16 with float32 arithmetic) raise.
 """
 from __future__ import annotations
 
@@ -35,6 +36,29 @@ def _dense(t: Tensor) -> Tensor:
     return t.resolve_conj().contiguous()
 
 
+_LOW_PRECISION = (torch.float16, torch.bfloat16)
+
+
+def _fp32_arithmetic(fn):
+    """float16 / bfloat16 tensors (which the reference's first-order ops also dispatch,
+    philtorch/csrc/lti_recur.cu:135-156): the recurrence is evaluated in float32 and every result is
+    rounded once to the storage type, instead of rounding after every step as a 16-bit scan does.
+    The conversion passes are separate kernels here (a 2-byte storage variant of the tiles would
+    move 4 instead of ~20 bytes per sample)."""
+    def wrapped(*args):
+        low = next((a.dtype for a in args if isinstance(a, Tensor) and a.dtype in _LOW_PRECISION), None)
+        if low is None:
+            return fn(*args)
+        up = [a.float() if isinstance(a, Tensor) and a.dtype in _LOW_PRECISION else a for a in args]
+        out = fn(*up)
+        if isinstance(out, tuple):
+            return tuple(o.to(low) for o in out)
+        return out.to(low)
+    wrapped.__name__ = fn.__name__
+    wrapped.__doc__ = fn.__doc__
+    return wrapped
+
+
 def _opt(t: Optional[Tensor]) -> Optional[Tensor]:
     return None if t is None else _dense(t)
 
@@ -54,6 +78,7 @@ def _check_lti_recur(a: Tensor, zi: Tensor, x: Tensor) -> None:
         torch._check(a.shape[0] == x.shape[0], lambda: "If A is 1D, its length must match x's batch size.")
 
 
+@_fp32_arithmetic
 def _lti_recur(a: Tensor, zi: Tensor, x: Tensor) -> Tensor:
     _check_lti_recur(a, zi, x)
     dev = _lib.require_cuda(a, zi, x)
@@ -67,6 +92,7 @@ def _lti_recur(a: Tensor, zi: Tensor, x: Tensor) -> Tensor:
     return y
 
 
+@_fp32_arithmetic
 def _lti_recur_bwd(a, zi, y, gy, g_in, need_a, need_zi):
     dev = _lib.require_cuda(a, zi, y, gy, g_in)
     B, T = y.shape
@@ -116,6 +142,7 @@ def _check_lpv_recur(a: Tensor, zi: Tensor, x: Tensor) -> None:
         torch._check(a.shape[0] == x.shape[0], lambda: "If a is 2D, its first dimension must match x's batch size.")
 
 
+@_fp32_arithmetic
 def _lpv_recur(a: Tensor, zi: Tensor, x: Tensor) -> Tensor:
     _check_lpv_recur(a, zi, x)
     dev = _lib.require_cuda(a, zi, x)
@@ -129,6 +156,7 @@ def _lpv_recur(a: Tensor, zi: Tensor, x: Tensor) -> Tensor:
     return y
 
 
+@_fp32_arithmetic
 def _lpv_recur_bwd(a, zi, y, gy, g_in, need_a, need_zi):
     dev = _lib.require_cuda(a, zi, y, gy, g_in)
     B, T = y.shape

@@ -289,8 +289,30 @@ def newton_cases(pt):
          y2_sequential=_np(torch.stack(seq2, 1)))
 
 
+def low_precision_cases(pt):
+    """float16 / bfloat16 through the reference's ``LTIRecurrence`` (its ops dispatch both,
+    philtorch/csrc/host_lti_recur.cpp:61-78); the reference rounds after every step."""
+    from philtorch.lti.recur import LTIRecurrence
+
+    torch.manual_seed(20240615)
+    for dt, tag in ((torch.float16, "f16"), (torch.bfloat16, "bf16")):
+        B, T = 3, 101
+        a = (torch.rand(B) * 1.8 - 0.9).to(dt).requires_grad_()
+        zi = torch.randn(B).to(dt).requires_grad_()
+        x = torch.randn(B, T).to(dt).requires_grad_()
+        gy = torch.randn(B, T).to(dt)
+        y = LTIRecurrence.apply(a, zi, x)
+        ga, gzi, gx = torch.autograd.grad(y, (a, zi, x), gy)
+        f = lambda t: t.detach().float().numpy()   # noqa: E731  (npz has no 16-bit float types for bf16)
+        save(f"lti_recur_batched_{tag}", a=f(a), zi=f(zi), x=f(x), gy=f(gy), y=f(y), grad_a=f(ga), grad_zi=f(gzi),
+             grad_x=f(gx))
+
+
 def main():
     pt = import_reference()
+    if len(sys.argv) > 1 and sys.argv[1] == "low_precision":   # only this group
+        low_precision_cases(pt)
+        return
     if len(sys.argv) > 1 and sys.argv[1] == "newton":        # only this group
         newton_cases(pt)
         return

@@ -183,3 +183,24 @@ def test_repeatable():
     y2 = ptb.lpv.linear_recurrence(a, zi, x)
     assert rel_err(y1, y2) <= 1e-6   # look-back association may differ in the last bits only
     ptb.check_errors()
+
+
+@pytest.mark.parametrize("tag,dtype,eps", [("f16", torch.float16, 2.0 ** -11), ("bf16", torch.bfloat16, 2.0 ** -8)])
+def test_low_precision_storage(tag, dtype, eps):
+    """float16 / bfloat16 inputs: float32 arithmetic, one rounding per result.  Against the float64
+    oracle on the same 16-bit inputs the error is one rounding; the reference, which rounds after
+    every step, is matched within a few of its own roundings (vectors made by running it)."""
+    g = load_golden(f"lti_recur_batched_{tag}")
+    a, zi, x, gy = (g[k].to(dtype) for k in ("a", "zi", "x", "gy"))     # exactly representable: stored from 16-bit values
+    y, ga, gzi, gx = _run_fo("lti", a, zi, x, gy)
+    assert y.dtype == dtype and ga.dtype == dtype and gx.dtype == dtype
+    y64 = cport.lti_recur(a.double(), zi.double(), x.double())
+    ga64, gzi64, gx64 = cport.lti_recur_bwd(a.double(), zi.double(), y64, gy.double())
+    assert rel_err(y, y64) <= 1.01 * eps and rel_err(gx, gx64) <= 1.01 * eps
+    assert rel_err(ga, ga64) <= 4 * eps and rel_err(gzi, gzi64) <= 1.01 * eps
+    assert rel_err(y, g["y"]) <= 16 * eps and rel_err(gx, g["grad_x"]) <= 16 * eps
+    assert rel_err(ga, g["grad_a"]) <= 64 * eps and rel_err(gzi, g["grad_zi"]) <= 16 * eps
+    # per-sample coefficients take the same route
+    al = a.unsqueeze(1).expand(-1, x.shape[1]).contiguous()
+    yl, _, _, _ = _run_fo("lpv", al, zi, x, gy)
+    assert yl.dtype == dtype and rel_err(yl, y64) <= 1.01 * eps
