@@ -5,7 +5,7 @@
 
 namespace ptb {
 
-static int comb_blocks_per_row(int64_t D) { return (int)((D + kCombThreads - 1) / kCombThreads); }
+static int comb_blocks_per_row(int64_t D) { return (int)((D + 31) / 32); }   // a block: 32 phases
 
 template <class S>
 static int comb_fwd(int64_t B, int64_t N, int64_t D, const void* a, int a_batched, const void* zi, int zi_mode,
