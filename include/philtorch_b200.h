@@ -143,6 +143,42 @@ int ptb_lpv_recur_fwd_carry(int dtype, int64_t B, int64_t T, const void* a, int 
                             void* carry, void* workspace, int64_t workspace_bytes, uint32_t* status,
                             ptb_stream_t stream);
 
+/* ---- fix-up of a first-order scan cut into pieces along time --------------------------------------
+ * New with the time-sharded mode (the reference has no multi-device code; its scalar recurrence is
+ * philtorch/lpv/recur.py:20-101).  A row is cut into `world` time shards (one per device, in rank
+ * order) and every shard into `nseg` segments of L samples, which the scan kernels treat as
+ * B * nseg independent rows (kernel row r = b * nseg + j) started from a ZERO state.  These three
+ * entry points turn such zero-start results into the results of the uncut recurrence without any
+ * host round trip.  They need no workspace and are asynchronous on `stream`.
+ *
+ * ptb_lpv_recur_fold_maps: total map of every row's nseg pieces, out (B,2) = fold of maps (B,nseg,2)
+ *   = {P_k, e_k}: s -> P_k s + e_k taken over k = 0..nseg-1 (reverse = 0) or nseg-1..0 (reverse = 1,
+ *   the adjoint maps).  This is what a rank contributes to the all-gather over the shards.
+ *
+ * ptb_lpv_recur_fixup_fwd: for every kernel row, the state s entering it is folded from zi (B,), the
+ *   shards' maps rank_maps (world,B,2) of ranks < rank (NULL when world == 1) and the maps
+ *   seg_maps (B*nseg,2) of the segments before it; s is written to states (B*nseg,) and
+ *   y[t] += (prod_{u<=t} a[u]) s is applied in place, block by block, until the running correction
+ *   is exactly zero (it stays zero from there on, so stopping is exact).
+ *   a: (B*nseg, L) if a_batched, else (L,) shared by the rows (then nseg must be 1).
+ *
+ * ptb_lpv_recur_fixup_bwd: the mirror image for the adjoint.  seg_maps (B*nseg,2) = {P_k, adjoint
+ *   state leaving segment k on its left when nothing enters on its right}, rank_maps those of the
+ *   shards; the adjoint state c entering a segment from its right is folded from the pieces to its
+ *   right and  grad_x[t] += d[t],  grad_a[t] += d[t] y[t-1]  (y[-1] = states[r]),
+ *   d[t] = c prod_{t<u<L} a[u], walking from the segment's end until d is exactly zero.
+ *   grad_a: optional; (B*nseg, L), or (L,) with shared coefficients (atomic adds).
+ *   grad_zi: optional (B,), receives the adjoint state leaving the shard on its left (the gradient
+ *   of zi on rank 0). */
+int ptb_lpv_recur_fold_maps(int dtype, int64_t B, int64_t nseg, const void* maps, int reverse, void* out,
+                            ptb_stream_t stream);
+int ptb_lpv_recur_fixup_fwd(int dtype, int64_t B, int64_t nseg, int64_t L, const void* a, int a_batched, void* y,
+                            const void* seg_maps, const void* zi, const void* rank_maps, int rank, int world,
+                            void* states, ptb_stream_t stream);
+int ptb_lpv_recur_fixup_bwd(int dtype, int64_t B, int64_t nseg, int64_t L, const void* a, int a_batched,
+                            const void* y, const void* states, const void* seg_maps, const void* rank_maps, int rank,
+                            int world, void* grad_x, void* grad_a, void* grad_zi, ptb_stream_t stream);
+
 /* ---- first-order forward without any caller-side or library-side allocation -----------------
  * No counterpart in the reference.  Same computation and arguments as ptb_lpv_recur_fwd, minus the
  * workspace: the look-back scratch is a fixed 2 MiB array inside the library image (every GPU
@@ -211,6 +247,11 @@ int ptb_lpv_recur2_bwd(int dtype, int64_t B, int64_t T, const void* A, int A_bat
 int ptb_biquad_tdf2_fwd(int dtype, int64_t B, int64_t T, const void* b, const void* a, int coef_batched,
                         const void* zi, const void* x, void* y, void* zf, void* workspace,
                         int64_t workspace_bytes, uint32_t* status, ptb_stream_t stream);
+/* The single-section entry points run on kernels that take the powers of the section's 2x2 matrix
+ * from a per-row table built in double precision (policy 0, default); policy 1 forces the generic
+ * 2x2 scan, which multiplies matrices in the data's precision and loses accuracy in float32 for
+ * nearly double poles close to the unit circle.  Process-wide; meant for tests. */
+int ptb_biquad_set_policy(int policy);
 
 /* Adjoint of the section above (what autograd derives in the reference through the state-space
  * glue).  Reads gy, x and the forward OUTPUT y only; no state sequence is stored.

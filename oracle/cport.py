@@ -152,3 +152,38 @@ def biquad_tdf2(b, a, zi, x):
     getattr(lib(), "oracle_biquad_tdf2_" + _suf(x))(
         _i64(B), _i64(T), _p(b), _p(a), batched, _p(zi), _p(x), _p(y), _p(zf))
     return y, zf
+
+
+def biquad_tdf2_bwd(b, a, zi, x, gy, gzf=None):
+    """Adjoint of ``biquad_tdf2``: (grad_b, grad_a, grad_zi, grad_x)."""
+    b, a, x, gy = _c(b), _c(a), _c(x), _c(gy)
+    zi = _c(zi) if zi is not None else None
+    gzf = _c(gzf) if gzf is not None else None
+    B, T = x.shape
+    gx = torch.empty_like(x)
+    gb, ga = torch.empty_like(b), torch.empty_like(a)
+    gzi = x.new_empty(B, 2)
+    getattr(lib(), "oracle_biquad_tdf2_bwd_" + _suf(x))(
+        _i64(B), _i64(T), _p(b), _p(a), int(b.dim() == 2), _p(zi), _p(x), _p(gy), _p(gzf),
+        _p(gx), _p(gb), _p(ga), _p(gzi))
+    return gb, ga, gzi, gx
+
+
+def sos_chain(b, a, x):
+    """K chained TDF-II sections (b (K,3)|(K,B,3), a (K,2)|(K,B,2)), the way the reference runs a
+    cascade (K ``lfilter`` calls, philtorch/lti/filtering.py:304-317): returns the inputs of every
+    section and the final output."""
+    u, ins = x, []
+    for k in range(b.shape[0]):
+        ins.append(u)
+        u, _ = biquad_tdf2(b[k], a[k], None, u)
+    return ins, u
+
+
+def sos_chain_bwd(b, a, ins, gy):
+    """Adjoint of ``sos_chain``: (grad_b, grad_a, grad_x), sections taken in reverse order."""
+    gb, ga = torch.empty_like(b), torch.empty_like(a)
+    g = gy
+    for k in range(b.shape[0] - 1, -1, -1):
+        gb[k], ga[k], _, g = biquad_tdf2_bwd(b[k], a[k], None, ins[k], g)
+    return gb, ga, g

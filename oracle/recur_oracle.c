@@ -20,6 +20,7 @@
  */
 #include <stddef.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define CAT_(a, b) a##b
 #define CAT(a, b) CAT_(a, b)
@@ -84,7 +85,8 @@
                                     const S *zi, const S *y, const S *gy, const S *g_in,         \
                                     S *grad_x, S *grad_a, S *grad_zi) {                          \
     if (!a_batched) for (int64_t t = 0; t < T; ++t) grad_a[t] = 0;                               \
-    for (int64_t b = 0; b < B; ++b) {                                                            \
+    /* rows are independent unless they share (and sum into) one coefficient gradient */         \
+    _Pragma("omp parallel for if (a_batched)") for (int64_t b = 0; b < B; ++b) {                 \
       const S *ab = a_batched ? a + b * T : a;                                                   \
       S c = g_in ? g_in[b] : (S)0;                                                               \
       for (int64_t t = T - 1; t >= 0; --t) {                                                     \
@@ -171,6 +173,65 @@
       }                                                                                          \
       if (zf) { zf[b * 2] = h0; zf[b * 2 + 1] = h1; }                                            \
     }                                                                                            \
+  }                                                                                              \
+  /* Adjoint of that section: what autograd derives in the reference through the glue of         \
+     philtorch/lti/filtering.py:304-317 and philtorch/lti/ssm.py:466-504 and the rule of         \
+     LTIMatrixRecurrence (philtorch/lti/ssm.py:67-96), written out sequentially.  With           \
+     M = [[-a1,1],[-a2,0]], Bv = [b1-b0*a1, b2-b0*a2] and l[t] the adjoint of the state h[t]:    \
+       l[T-1] = gzf,  l[t] = M^T l[t+1] + [gy[t+1], 0];   grad_x[t] = b0*gy[t] + Bv.l[t];        \
+       grad_b1 = sum l0[t]*x[t], grad_b2 = sum l1[t]*x[t],                                       \
+       grad_b0 = sum gy[t]*x[t] - a1*grad_b1 - a2*grad_b2;                                       \
+       grad_a1 = -sum l0[t]*(h0[t-1] + b0*x[t]), grad_a2 = -sum l1[t]*(h0[t-1] + b0*x[t])        \
+       (through M: -l0[t]*h0[t-1], through Bv: -b0*l0[t]*x[t]);  grad_zi = M^T l[0] + [gy[0],0]. \
+     h0[t-1] is recomputed by running the section forward first.  Sums are accumulated in        \
+     double; shared coefficients: summed over the rows as well.  gzf, grad_zi may be NULL. */    \
+  void CAT(oracle_biquad_tdf2_bwd_, SUF)(int64_t B, int64_t T, const S *bc, const S *ac,         \
+                                         int batched, const S *zi, const S *x, const S *gy,      \
+                                         const S *gzf, S *grad_x, S *grad_b, S *grad_a,          \
+                                         S *grad_zi) {                                           \
+    double *acc = (double *)calloc((size_t)B * 5, sizeof(double));                               \
+    _Pragma("omp parallel for") for (int64_t b = 0; b < B; ++b) {                                \
+      const S *bb = batched ? bc + b * 3 : bc;                                                   \
+      const S *aa = batched ? ac + b * 2 : ac;                                                   \
+      const S B0 = bb[1] - bb[0] * aa[0], B1 = bb[2] - bb[0] * aa[1];                            \
+      S *h0prev = (S *)malloc((size_t)T * sizeof(S)); /* h0[t-1] for every t */                  \
+      S h0 = zi ? zi[b * 2] : (S)0, h1 = zi ? zi[b * 2 + 1] : (S)0;                              \
+      for (int64_t t = 0; t < T; ++t) {                                                          \
+        const S xt = x[b * T + t];                                                               \
+        h0prev[t] = h0;                                                                          \
+        const S n0 = xt * B0 + ((-aa[0]) * h0 + h1);                                             \
+        const S n1 = xt * B1 + (-aa[1]) * h0;                                                    \
+        h0 = n0; h1 = n1;                                                                        \
+      }                                                                                          \
+      S l0 = gzf ? gzf[b * 2] : (S)0, l1 = gzf ? gzf[b * 2 + 1] : (S)0;                          \
+      double sgx = 0, s0x = 0, s1x = 0, s0y = 0, s1y = 0;                                        \
+      for (int64_t t = T - 1; t >= 0; --t) {                                                     \
+        const S xt = x[b * T + t], gt = gy[b * T + t];                                           \
+        grad_x[b * T + t] = bb[0] * gt + (B0 * l0 + B1 * l1);                                    \
+        const S yt = h0prev[t] + bb[0] * xt;                                                     \
+        sgx += (double)gt * xt; s0x += (double)l0 * xt; s1x += (double)l1 * xt;                  \
+        s0y += (double)l0 * yt; s1y += (double)l1 * yt;                                          \
+        const S m0 = (-aa[0]) * l0 + (-aa[1]) * l1 + gt; /* M^T l + [gy[t], 0] */                \
+        const S m1 = l0;                                                                         \
+        l0 = m0; l1 = m1;                                                                        \
+      }                                                                                          \
+      if (grad_zi) { grad_zi[b * 2] = l0; grad_zi[b * 2 + 1] = l1; }                             \
+      acc[b * 5] = sgx - (double)aa[0] * s0x - (double)aa[1] * s1x;                              \
+      acc[b * 5 + 1] = s0x; acc[b * 5 + 2] = s1x; acc[b * 5 + 3] = -s0y; acc[b * 5 + 4] = -s1y;  \
+      free(h0prev);                                                                              \
+    }                                                                                            \
+    if (batched) {                                                                               \
+      for (int64_t b = 0; b < B; ++b) {                                                          \
+        for (int i = 0; i < 3; ++i) grad_b[b * 3 + i] = (S)acc[b * 5 + i];                       \
+        for (int i = 0; i < 2; ++i) grad_a[b * 2 + i] = (S)acc[b * 5 + 3 + i];                   \
+      }                                                                                          \
+    } else {                                                                                     \
+      double tot[5] = {0, 0, 0, 0, 0};                                                           \
+      for (int64_t b = 0; b < B; ++b) for (int i = 0; i < 5; ++i) tot[i] += acc[b * 5 + i];      \
+      for (int i = 0; i < 3; ++i) grad_b[i] = (S)tot[i];                                         \
+      for (int i = 0; i < 2; ++i) grad_a[i] = (S)tot[3 + i];                                     \
+    }                                                                                            \
+    free(acc);                                                                                   \
   }
 
 DEFINE_ALL(float, f32)
@@ -232,7 +293,8 @@ DEFINE_ALL(double, f64)
                                     const S *zi, const S *y, const S *gy, const S *g_in,         \
                                     S *grad_x, S *grad_a, S *grad_zi) {                          \
     if (!a_batched) for (int64_t t = 0; t < T; ++t) grad_a[t] = 0;                               \
-    for (int64_t b = 0; b < B; ++b) {                                                            \
+    /* rows are independent unless they share (and sum into) one coefficient gradient */         \
+    _Pragma("omp parallel for if (a_batched)") for (int64_t b = 0; b < B; ++b) {                 \
       const S *ab = a_batched ? a + b * T : a;                                                   \
       S c = g_in ? g_in[b] : (S)0;                                                               \
       for (int64_t t = T - 1; t >= 0; --t) {                                                     \

@@ -64,8 +64,18 @@ lib.ptb_lpv_recur_carry.restype = _i32
 lib.ptb_lpv_recur_fwd_carry.argtypes = [_i32, _i64, _i64, _vp, _i32, _vp, _vp, _vp] + _tail
 lib.ptb_lpv_recur_fwd_carry.restype = _i32
 
+lib.ptb_lpv_recur_fold_maps.argtypes = [_i32, _i64, _i64, _vp, _i32, _vp, _vp]
+lib.ptb_lpv_recur_fold_maps.restype = _i32
+lib.ptb_lpv_recur_fixup_fwd.argtypes = [_i32, _i64, _i64, _i64, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _vp, _vp]
+lib.ptb_lpv_recur_fixup_fwd.restype = _i32
+lib.ptb_lpv_recur_fixup_bwd.argtypes = [_i32, _i64, _i64, _i64, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _vp, _vp,
+                                        _vp, _vp]
+lib.ptb_lpv_recur_fixup_bwd.restype = _i32
+
 lib.ptb_lpv_recur2_set_small_cta_min_rows.argtypes = [_i64]
 lib.ptb_lpv_recur2_set_small_cta_min_rows.restype = _i32
+lib.ptb_biquad_set_policy.argtypes = [_i32]
+lib.ptb_biquad_set_policy.restype = _i32
 lib.ptb_set_wait_limit_ms.argtypes = [_i64]
 lib.ptb_set_wait_limit_ms.restype = _i32
 lib.ptb_selftest_wait_expiry_elems.restype = _i64

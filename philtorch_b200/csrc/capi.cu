@@ -11,6 +11,12 @@ namespace ptb {
 int biquad_chain_bwd(int dtype, int64_t B, int64_t T, const void* b, const void* a, int coef_batched, const void* x,
                      const void* y, const void* gy, const void* g_zf, void* grad_x, void* grad_b, void* grad_a,
                      void* grad_zi, void* ws, int64_t wsb, uint32_t* status, cudaStream_t st);
+// single section on the decoupled kernels with a per-row table of matrix powers (capi_sos.cu); -1: not applicable
+int biquad_table_fwd(int dtype, int64_t B, int64_t T, const void* b, const void* a, int coef_batched, const void* zi,
+                     const void* x, void* y, void* zf, void* ws, int64_t wsb, uint32_t* status, cudaStream_t st);
+int biquad_table_bwd(int dtype, int64_t B, int64_t T, const void* b, const void* a, int coef_batched, const void* x,
+                     const void* y, const void* gy, const void* g_zf, void* grad_x, void* grad_b, void* grad_a,
+                     void* grad_zi, void* ws, int64_t wsb, uint32_t* status, cudaStream_t st);
 // complex first-order recurrences (capi_cx.cu)
 int cx_fo_fwd(int dtype, int lpv, int64_t B, int64_t T, const void* a, int a_batched, const void* zi, int zi_batched,
               const void* x, void* y, void* zf, void* ws, int64_t wsb, uint32_t* status, cudaStream_t st);
@@ -136,6 +142,7 @@ static int so_small_fwd(int64_t B, int64_t T, const void* A, int A_batched, cons
 }
 
 static int g_so_small_min_rows = PTB_SO_SMALL_MIN_ROWS;
+static int g_bq_policy = 0;   // ptb_biquad_set_policy: 0 table-of-powers kernels, 1 generic 2x2 policy (tests)
 
 #ifndef PTB_SO_SMALL_BWD_MINB
 #define PTB_SO_SMALL_BWD_NT 128
@@ -461,6 +468,12 @@ int ptb_lpv_recur2_set_small_cta_min_rows(int64_t rows) {
   return PTB_OK;
 }
 
+int ptb_biquad_set_policy(int policy) {
+  if (policy < 0 || policy > 1) return PTB_ERR_ARG;
+  g_bq_policy = policy;
+  return PTB_OK;
+}
+
 int ptb_set_wait_limit_ms(int64_t ms) {
   if (ms < 1 || ms > 600000) return PTB_ERR_ARG;
   g_wait_ns = (uint64_t)ms * 1000000ull;
@@ -599,6 +612,11 @@ int ptb_biquad_tdf2_fwd(int dtype, int64_t B, int64_t T, const void* b, const vo
   if (B < 0 || T < 0) return PTB_ERR_ARG;
   if (B == 0 || T == 0) return PTB_OK;
   if (!b || !a || !x || !y) return PTB_ERR_ARG;
+  if (g_bq_policy != 1) {   // the kernels whose matrix powers come from a table built in double
+    const int rc = biquad_table_fwd(dtype, B, T, b, a, coef_batched, zi, x, y, zf, workspace, workspace_bytes, status,
+                                    (cudaStream_t)stream);
+    if (rc >= 0) return rc;
+  }
   PTB_DISPATCH(dtype, (bq_fwd<S>(B, T, b, a, coef_batched, zi, x, y, zf, workspace, workspace_bytes, status,
                                  (cudaStream_t)stream)));
 }
@@ -612,6 +630,11 @@ int ptb_biquad_tdf2_bwd(int dtype, int64_t B, int64_t T, const void* b, const vo
   if (!b || !a || !gy || !grad_x || ((grad_b || grad_a) && (!x || !y))) return PTB_ERR_ARG;
   {   // large batches: the chained kernel of capi_sos.cu (measured faster for the backward pass only)
     const int rc = biquad_chain_bwd(dtype, B, T, b, a, coef_batched, x, y, gy, g_zf, grad_x, grad_b, grad_a, grad_zi,
+                                    workspace, workspace_bytes, status, (cudaStream_t)stream);
+    if (rc >= 0) return rc;
+  }
+  if (g_bq_policy != 1) {
+    const int rc = biquad_table_bwd(dtype, B, T, b, a, coef_batched, x, y, gy, g_zf, grad_x, grad_b, grad_a, grad_zi,
                                     workspace, workspace_bytes, status, (cudaStream_t)stream);
     if (rc >= 0) return rc;
   }

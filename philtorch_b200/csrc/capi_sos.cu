@@ -19,7 +19,15 @@ namespace ptb {
 #define PTB_SOS_BWD_NT 256
 #define PTB_SOS_BWD_CTAS 1
 #endif
-template <class S, int K> using SosFwdP = SosFwd<S, K, PTB_SOS_FWD_CH, PTB_SOS_FWD_STAGES, PTB_SOS_FWD_NT, PTB_SOS_FWD_CTAS>;
+// a single section moves a third of the cascade's bytes per sample: larger tiles, two CTAs per SM
+#ifndef PTB_SOS1_FWD_CH
+#define PTB_SOS1_FWD_CH 13
+#define PTB_SOS1_FWD_STAGES 2
+#define PTB_SOS1_FWD_CTAS 2
+#endif
+template <class S, int K> struct SosFwdSel { using type = SosFwd<S, K, PTB_SOS_FWD_CH, PTB_SOS_FWD_STAGES, PTB_SOS_FWD_NT, PTB_SOS_FWD_CTAS>; };
+template <class S> struct SosFwdSel<S, 1> { using type = SosFwd<S, 1, PTB_SOS1_FWD_CH, PTB_SOS1_FWD_STAGES, 256, PTB_SOS1_FWD_CTAS>; };
+template <class S, int K> using SosFwdP = typename SosFwdSel<S, K>::type;
 template <class S, int K> using SosBwdP = SosBwd<S, K, PTB_SOS_BWD_CH, PTB_SOS_BWD_STAGES, PTB_SOS_BWD_NT, PTB_SOS_BWD_CTAS>;
 
 // chained kernels: (16-byte units per thread, threads, output buffers, CTAs per SM) per direction.
@@ -372,6 +380,45 @@ int biquad_chain_bwd(int dtype, int64_t B, int64_t T, const void* b, const void*
     if (wsb < chain_ws_bytes<double, 1>(B, T)) return -1;
     return chain_bwd<double, 1>(B, T, b, a, coef_batched, x, mid, y, gy, g_zf, grad_x, grad_b, grad_a, grad_zi, ws,
                                 wsb, status, st);
+  }
+  return -1;
+}
+
+// Single section through the decoupled kernels with K = 1: the linear parts of all maps come from
+// the row's table of powers M^(SPT 2^i), built in double, so no matrices are multiplied in the
+// section's own precision.  (Squaring a rounded power doubles its relative error; after the ~14
+// doublings of a thread / warp / tile hierarchy a float32 section with a nearly double pole close to
+// the unit circle -- pole angle near 0 or pi, radius ~0.99 -- misses the sequential result by
+// ~3e-4 of max|y| when the powers are formed in float32.)  Returns -1 when the caller's workspace
+// cannot hold the table (very short rows): the caller then takes the generic 2x2 policy.
+int biquad_table_fwd(int dtype, int64_t B, int64_t T, const void* b, const void* a, int coef_batched, const void* zi,
+                     const void* x, void* y, void* zf, void* ws, int64_t wsb, uint32_t* status, cudaStream_t st) {
+  const int64_t rows = coef_batched ? B : 1;
+  if (dtype == PTB_F32) {
+    if (wsb < table_bytes<float, 1>(rows) + scan_ws_bytes<SosFwdP<float, 1>>(B, T)) return -1;
+    return sos_fwd<float, 1>(B, T, b, a, coef_batched, zi, x, y, zf, ws, wsb, status, st);
+  }
+  if (dtype == PTB_F64) {
+    if (wsb < table_bytes<double, 1>(rows) + scan_ws_bytes<SosFwdP<double, 1>>(B, T)) return -1;
+    return sos_fwd<double, 1>(B, T, b, a, coef_batched, zi, x, y, zf, ws, wsb, status, st);
+  }
+  return -1;
+}
+
+int biquad_table_bwd(int dtype, int64_t B, int64_t T, const void* b, const void* a, int coef_batched, const void* x,
+                     const void* y, const void* gy, const void* g_zf, void* grad_x, void* grad_b, void* grad_a,
+                     void* grad_zi, void* ws, int64_t wsb, uint32_t* status, cudaStream_t st) {
+  const int64_t rows = coef_batched ? B : 1;
+  const void* mid = x;   // K = 1: no intermediate outputs (never read)
+  if (dtype == PTB_F32) {
+    if (wsb < table_bytes<float, 1>(rows) + scan_ws_bytes<SosBwdP<float, 1>>(B, T)) return -1;
+    return sos_bwd<float, 1>(B, T, b, a, coef_batched, x, mid, y, gy, g_zf, grad_x, grad_b, grad_a, grad_zi, ws, wsb,
+                             status, st);
+  }
+  if (dtype == PTB_F64) {
+    if (wsb < table_bytes<double, 1>(rows) + scan_ws_bytes<SosBwdP<double, 1>>(B, T)) return -1;
+    return sos_bwd<double, 1>(B, T, b, a, coef_batched, x, mid, y, gy, g_zf, grad_x, grad_b, grad_a, grad_zi, ws, wsb,
+                              status, st);
   }
   return -1;
 }

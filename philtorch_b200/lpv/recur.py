@@ -1,6 +1,8 @@
 """First-order recurrence with per-sample coefficients: public API of philtorch/lpv/recur.py."""
 from __future__ import annotations
 
+import torch
+import torch.autograd.forward_ad as fwAD
 from torch import Tensor
 
 from ..autograd import LPVRecurrence
@@ -37,4 +39,17 @@ def linear_recurrence(a: Tensor, init: Tensor, x: Tensor, *, unroll_factor: int 
         raise ValueError("Unroll factor must be >= 1")
     if init.dim() == 0 or init.size(0) != batch_size:
         init = init.expand(batch_size)
+    if x.is_cuda and a.dim() == 2 and not x.is_complex():
+        # a handful of long rows: cut into segments the kernels see as independent rows (the tiles of
+        # one row wait on one another, so few rows leave most of the memory bandwidth unused)
+        from .. import sharded
+
+        S = sharded.auto_segments(batch_size, x.size(1), True)
+        if S > 1 and x.dtype in (torch.float32, torch.float64) and not _has_tangent(a, init, x):
+            return sharded.TimeShardedLPVRecurrence.apply(a, init, x, sharded.LOCAL, None, S)
     return LPVRecurrence.apply(a, init, x)
+
+
+def _has_tangent(*tensors: Tensor) -> bool:
+    """True inside forward-mode AD (the segmented path has no jvp rule; LPVRecurrence has)."""
+    return any(fwAD.unpack_dual(t).tangent is not None for t in tensors)

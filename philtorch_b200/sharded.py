@@ -8,11 +8,12 @@ Forward, per rank
       total affine map (P_r, e_r) = (product of a, y0's last sample);
   (2) ONE all-gather of the (B, 2) maps; every rank folds the maps of the ranks before it into its
       true incoming state  s_r = P_{r-1} s_{r-1} + e_{r-1}  (s_0 = zi);
-  (3) fix-up  y[t] = y0[t] + (prod_{u<=t} a[u]) s_r.  The running product normally underflows to
-      exactly zero after a few thousand samples (|a| < 1), from where the correction is exactly
-      zero: it is applied block by block from the shard's start and stops at the first block that
-      ends with an all-zero correction (one tiny device->host read per block).  If the products
-      never vanish the blocks double until the whole shard has been corrected: still exact.
+  (3) fix-up  y[t] = y0[t] + (prod_{u<=t} a[u]) s_r, ONE kernel launch (``ptb_lpv_recur_fixup_fwd``)
+      that also does the fold of step (2) on the device.  The running correction normally
+      underflows to exactly zero after a few thousand samples (|a| < 1) and stays zero from there
+      on, so every row is corrected block by block from its start and the walk stops, per row, at
+      the first block that the correction enters as exactly 0.0.  If the products never vanish the
+      walk covers the whole shard: still exact.  No device->host read anywhere on the path.
 Backward mirrors it from the right: the local adjoint scan with a zero incoming state, one
 all-gather of (P_r, adjoint end state), and a fix-up of grad_x / grad_a over a suffix.
 
@@ -26,9 +27,9 @@ kernels see as B*S independent rows (a reshape, no copy); the segments' maps are
 like the ranks' maps, and the fix-up runs over all segments at once.  S is chosen so that
 B*S >= 256 rows of at least 2^20 samples (``segments=None``) or given; S = 1 is the plain algorithm.  Without an
 initialised process group the function runs as a single rank, so it also serves one GPU.
-The fold over the segments is the same recurrence over the (B, S) maps and runs as one more
-launch of the kernel, queued behind the scan (folding on the host would stall the stream twice
-per direction, and a Python loop over the segments is launch-bound for S >= 32).
+The fold over the segments happens inside the fix-up kernel (each (row, segment) CTA folds the at
+most W-1 + S-1 maps before it from shared memory), so a direction is: scan, [fold_maps +
+all-gather when W > 1], fix-up.
 """
 from __future__ import annotations
 
@@ -39,13 +40,8 @@ import torch.distributed as dist
 from torch import Tensor
 from torch.autograd import Function
 
-FIXUP_BLOCK = 1 << 16     # first fix-up block (samples per row) at most; later blocks double
-FIXUP_SAMPLES = 1 << 20   # ... and about this many samples over all rows (more rows: shorter first block)
-
-
-def _first_block(rows: int) -> int:
-    return max(min(FIXUP_BLOCK, 1024), min(FIXUP_BLOCK, FIXUP_SAMPLES // max(rows, 1)))
-
+from . import _lib
+from ._lib import lib, ptr
 
 class _GpuKernels:
     """The compiled kernels (default).  Tests substitute a CPU stand-in with the same methods to
@@ -53,7 +49,7 @@ class _GpuKernels:
 
     @staticmethod
     def scan_zero(a: Tensor, x: Tensor):
-        """(y from a zero state, carry (B,2) = {prod a, y[:, -1]})"""
+        """(y from a zero state, maps (R,2) = {prod a, y[:, -1]})"""
         return torch.ops.philtorch_b200.lpv_recur_zero_carry(a, x)
 
     @staticmethod
@@ -64,6 +60,36 @@ class _GpuKernels:
     def backward(a, zi, y, gy, g_in, need_a: bool):
         return torch.ops.philtorch_b200.lpv_recur_bwd(a, zi, y, gy, g_in, need_a, True)
 
+    @staticmethod
+    def fold_maps(maps: Tensor, B: int, S: int, reverse: bool) -> Tensor:
+        """(B*S,2) piece maps -> (B,2) total map of every row (one tiny launch)."""
+        out = maps.new_empty(B, 2)
+        _stream_call(lib.ptb_lpv_recur_fold_maps, maps.device, _lib.dtype_code(maps), B, S, ptr(maps), int(reverse),
+                     ptr(out))
+        return out
+
+    @staticmethod
+    def fixup_forward(a, y, maps, zi, rank_maps, rank: int, world: int, B: int, S: int) -> Tensor:
+        """Corrects y (B*S, L) in place; returns the states (B*S,) entering the pieces."""
+        states = y.new_empty(B * S)
+        _stream_call(lib.ptb_lpv_recur_fixup_fwd, y.device, _lib.dtype_code(y), B, S, y.shape[1], ptr(a),
+                     int(a.dim() == 2), ptr(y), ptr(maps), ptr(zi), ptr(rank_maps), rank, world, ptr(states))
+        return states
+
+    @staticmethod
+    def fixup_backward(a, y, states, maps, rank_maps, rank: int, world: int, gx, ga, B: int, S: int) -> Tensor:
+        """Corrects gx (and ga) in place; returns the adjoint state (B,) leaving the shard on its left."""
+        gzi = y.new_empty(B)
+        _stream_call(lib.ptb_lpv_recur_fixup_bwd, y.device, _lib.dtype_code(y), B, S, y.shape[1], ptr(a),
+                     int(a.dim() == 2), ptr(y), ptr(states), ptr(maps), ptr(rank_maps), rank, world, ptr(gx), ptr(ga),
+                     ptr(gzi))
+        return gzi
+
+
+def _stream_call(fn, device, *args) -> None:
+    with torch.cuda.device(device):
+        _lib.check(fn(*args, torch.cuda.current_stream(device).cuda_stream), fn.__name__)
+
 
 def _all_gather(t: Tensor, group) -> Tensor:
     world = dist.get_world_size(group)
@@ -73,7 +99,8 @@ def _all_gather(t: Tensor, group) -> Tensor:
 
 
 def fold_carries_forward(carries: Tensor, zi: Tensor, rank: int) -> Tensor:
-    """State entering shard ``rank``: s_0 = zi, s_{q+1} = P_q s_q + e_q.  carries: (W, B, 2)."""
+    """State entering shard ``rank``: s_0 = zi, s_{q+1} = P_q s_q + e_q.  carries: (W, B, 2).
+    (What the fix-up kernel computes on the device; kept as the readable statement of the rule.)"""
     s = zi
     for q in range(rank):
         s = carries[q, :, 0] * s + carries[q, :, 1]
@@ -87,42 +114,6 @@ def fold_carries_backward(carries: Tensor, rank: int) -> Tensor:
     for q in range(world - 1, rank, -1):
         c = carries[q, :, 0] * c + carries[q, :, 1]
     return c
-
-
-def _rows(a: Tensor, lo: int, hi: int) -> Tensor:
-    return a[..., lo:hi].contiguous()
-
-
-def fixup_forward(k, a: Tensor, y: Tensor, s: Tensor) -> None:
-    """In place: y[t] += (prod_{u<=t} a[u]) s, block by block until the correction has died out."""
-    T = y.shape[1]
-    lo, blk = 0, _first_block(y.shape[0])
-    while lo < T:
-        hi = min(T, lo + blk)
-        z = k.forward(_rows(a, lo, hi), s.contiguous(), torch.zeros_like(y[:, lo:hi]))
-        y[:, lo:hi] += z
-        s = z[:, -1]
-        if not bool((s != 0).any()):
-            break
-        lo, blk = hi, blk * 2
-
-
-def fixup_backward(k, a: Tensor, s_in: Tensor, y: Tensor, c: Tensor, gx: Tensor, ga: Optional[Tensor]) -> None:
-    """In place: adds to grad_x (and grad_a) the adjoint driven by the state ``c`` entering the shard
-    from the right, suffix block by suffix block until it has died out."""
-    T = y.shape[1]
-    hi, blk = T, _first_block(y.shape[0])
-    while hi > 0:
-        lo = max(0, hi - blk)
-        y_prev = s_in if lo == 0 else y[:, lo - 1]
-        ga_b, c, gx_b = k.backward(_rows(a, lo, hi), y_prev.contiguous(), y[:, lo:hi].contiguous(),
-                                   torch.zeros_like(y[:, lo:hi]), c.contiguous(), ga is not None)
-        gx[:, lo:hi] += gx_b
-        if ga is not None:
-            ga[..., lo:hi] += ga_b   # (B,T) per row, or (T,) when the coefficients are shared
-        if not bool((c != 0).any()):
-            break
-        hi, blk = lo, blk * 2
 
 
 SEGMENT_MIN_ROWS = 256        # segments are added until the kernels see at least this many rows ...
@@ -139,9 +130,12 @@ def auto_segments(B: int, T: int, batched: bool) -> int:
 
 
 def _rank_world(group):
-    if group is None and not dist.is_initialized():
+    if group is LOCAL or (group is None and not dist.is_initialized()):
         return 0, 1
     return dist.get_rank(group), dist.get_world_size(group)
+
+
+LOCAL = object()   # `group` value: this device alone, whatever process groups exist
 
 
 class TimeShardedLPVRecurrence(Function):
@@ -156,57 +150,53 @@ class TimeShardedLPVRecurrence(Function):
         L = T // S
         av = a.contiguous().view(B * S, L) if S > 1 else a.contiguous()
         xv = x.contiguous().view(B * S, L)
+        zi_c = zi.contiguous()
         if world * S > 1:
-            y, carry = k.scan_zero(av, xv)                       # (B*S, L), (B*S, 2) = {prod a, y[:, -1]}
-            c = carry.view(B, S, 2)
-            P_seg, e_seg = c[:, :, 0].contiguous(), c[:, :, 1].contiguous()
-            if world > 1:                                         # this rank's total map, then the fold over ranks
-                e_tot = k.forward(P_seg, torch.zeros_like(zi), e_seg)[:, -1] if S > 1 else e_seg[:, 0]
-                mine = torch.stack([P_seg.prod(dim=1), e_tot], dim=1)
-                s = fold_carries_forward(_all_gather(mine, group), zi, rank)
-            else:
-                s = zi
-            states = s.reshape(B, 1)                              # states entering the segments: the same
-            if S > 1:                                             # recurrence over the segments' maps, one launch
-                after = k.forward(P_seg, s.contiguous(), e_seg)
-                states = torch.cat([states, after[:, :-1]], dim=1)
-            s_v = states.reshape(B * S).contiguous()
-            fixup_forward(k, av, y, s_v)
-            ctx.P = carry[:, 0].contiguous()
+            y, maps = k.scan_zero(av, xv)                         # (B*S, L), (B*S, 2) = {prod a, y[:, -1]}
+            rank_maps = None
+            if world > 1:                                         # this rank's total map; ONE all-gather
+                rank_maps = _all_gather(k.fold_maps(maps, B, S, False), group)
+            s_v = k.fixup_forward(av, y, maps, zi_c, rank_maps, rank, world, B, S)
+            ctx.P = maps[:, 0]
         else:
-            s_v = zi.contiguous()
+            s_v = zi_c
             y = k.forward(av, s_v, xv)
             ctx.P = None
         ctx.group, ctx.kernels, ctx.rank, ctx.world, ctx.S, ctx.shape = group, k, rank, world, S, (B, T)
-        ctx.a_shape = a.shape
-        ctx.save_for_backward(av, s_v, y)
-        return y.view(B, T)
+        out = y.view(B, T)
+        ctx.save_for_backward(a, zi, out, s_v)
+        return out
 
     @staticmethod
     def backward(ctx: Any, gy: Tensor):
-        av, s_v, y = ctx.saved_tensors
+        a, zi, out, s_v = ctx.saved_tensors
         k, S, (B, T) = ctx.kernels, ctx.S, ctx.shape
         need_a, need_zi, need_x = ctx.needs_input_grad[:3]
+        if torch.is_grad_enabled():
+            # a higher-order graph is being recorded: the adjoint written with differentiable pieces
+            # (philtorch/lpv/ssm.py:64-99 with M = 1), on one device only
+            if ctx.world > 1:
+                raise RuntimeError("double backward through the time-sharded recurrence is not supported")
+            from .autograd import LPVRecurrence
+            a_rev = torch.roll(a, shifts=-1, dims=-1).flip(-1)
+            g = LPVRecurrence.apply(a_rev, torch.zeros_like(zi), gy.flip(1)).flip(1)
+            prev = torch.cat([zi.unsqueeze(1), out[:, :-1]], dim=1)
+            ga = prev * g
+            return ((ga if a.dim() == 2 else ga.sum(0)) if need_a else None, g[:, 0] * a[..., 0] if need_zi else None,
+                    g if need_x else None, None, None, None)
+        av = a.contiguous().view(B * S, T // S) if S > 1 else a.contiguous()
+        y = out.view(B * S, T // S)
         gyv = gy.contiguous().view(B * S, T // S)
         ga, gs, gx = k.backward(av, s_v, y, gyv, None, need_a)   # adjoint with nothing entering from the right
         if ctx.world * S > 1:
-            Pr = ctx.P.view(B, S).flip(1).contiguous()            # segments from the right
-            gr = gs.view(B, S).flip(1).contiguous()
-            zero = torch.zeros_like(gr[:, 0])
-            if ctx.world > 1:                                     # this rank's total adjoint map, then the fold
-                e_tot = k.forward(Pr, zero, gr)[:, -1] if S > 1 else gr[:, 0]
-                mine = torch.stack([Pr.prod(dim=1), e_tot], dim=1)
-                c = fold_carries_backward(_all_gather(mine, ctx.group), ctx.rank)
-            else:
-                c = zero
-            after = k.forward(Pr, c.contiguous(), gr)             # adjoint leaving each segment on its left
-            cs = torch.cat([c.reshape(B, 1), after[:, :-1]], dim=1).flip(1)   # ... = entering the one before it
-            c_v = cs.reshape(B * S).contiguous()
-            fixup_backward(k, av, s_v, y, c_v, gx, ga if need_a else None)
-            gs = after[:, -1]                                     # adjoint state leaving this rank on the left
+            maps = torch.stack([ctx.P, gs], dim=1)                # (B*S, 2) adjoint maps of the pieces
+            rank_maps = None
+            if ctx.world > 1:
+                rank_maps = _all_gather(k.fold_maps(maps, B, S, True), ctx.group)
+            gs = k.fixup_backward(av, y, s_v, maps, rank_maps, ctx.rank, ctx.world, gx, ga if need_a else None, B, S)
         # only rank 0's is the gradient of zi (sum over ranks = the gradient)
         gzi = gs if ctx.rank == 0 else torch.zeros_like(gs)
-        return (ga.view(ctx.a_shape) if need_a else None, gzi if need_zi else None,
+        return (ga.view(a.shape) if need_a else None, gzi if need_zi else None,
                 gx.view(B, T) if need_x else None, None, None, None)
 
 

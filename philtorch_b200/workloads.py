@@ -19,9 +19,11 @@ import torch
 SEED_BASE = 1234
 
 
-def _gen(device, idx):
+def _gen(device, idx, shard=0):
+    """Generator of configuration ``idx``; ``shard`` > 0 gives an independent stream for another
+    shard (rows or time range) of the same configuration."""
     g = torch.Generator(device=device)
-    g.manual_seed(SEED_BASE + idx)
+    g.manual_seed(SEED_BASE + idx + 1000 * shard)
     return g
 
 
@@ -33,30 +35,30 @@ def _randn(shape, g, device):
     return torch.randn(shape, generator=g, device=device, dtype=torch.float64)
 
 
-def lti_first_order(B=64, T=65536, dtype=torch.float32, device="cpu"):
+def lti_first_order(B=64, T=65536, dtype=torch.float32, device="cpu", shard=0):
     """Config 1: y[n] = a*y[n-1] + x[n]; a per channel ~U(0.5,0.99) with random sign,
     x ~ N(0,1), zero initial state."""
-    g = _gen(device, 1)
+    g = _gen(device, 1, shard)
     mag = 0.5 + 0.49 * _rand((B,), g, device)
     sgn = torch.where(_rand((B,), g, device) < 0.5, -1.0, 1.0)
     return dict(a=(mag * sgn).to(dtype), zi=torch.zeros(B, dtype=dtype, device=device),
                 x=_randn((B, T), g, device).to(dtype), gy=_randn((B, T), g, device).to(dtype))
 
 
-def lpv_first_order(B=256, T=1 << 20, dtype=torch.float32, device="cpu"):
+def lpv_first_order(B=256, T=1 << 20, dtype=torch.float32, device="cpu", shard=0):
     """Config 2: per-sample coefficients a[b,n] ~ U(-0.99,0.99) i.i.d., x ~ N(0,1),
     initial state ~ N(0,1) per channel."""
-    g = _gen(device, 2)
+    g = _gen(device, 2, shard)
     return dict(a=(-0.99 + 1.98 * _rand((B, T), g, device)).to(dtype),
                 zi=_randn((B,), g, device).to(dtype),
                 x=_randn((B, T), g, device).to(dtype), gy=_randn((B, T), g, device).to(dtype))
 
 
-def sos_cascade(B=512, T=1 << 18, sections=6, dtype=torch.float32, device="cpu"):
+def sos_cascade(B=512, T=1 << 18, sections=6, dtype=torch.float32, device="cpu", shard=0):
     """Config 3: cascade of second-order sections; poles at radius ~U(0.5,0.99), angle
     ~U(0,pi); zeros at radius ~U(0,1.2), angle ~U(0,pi); gain 1, a0 = 1.
     b: (sections, B, 3), a: (sections, B, 2)."""
-    g = _gen(device, 3)
+    g = _gen(device, 3, shard)
     r = 0.5 + 0.49 * _rand((sections, B), g, device)
     th = math.pi * _rand((sections, B), g, device)
     rho = 1.2 * _rand((sections, B), g, device)
@@ -67,11 +69,11 @@ def sos_cascade(B=512, T=1 << 18, sections=6, dtype=torch.float32, device="cpu")
                 gy=_randn((B, T), g, device).to(dtype))
 
 
-def lpv_second_order(B=128, T=1 << 20, dtype=torch.float32, device="cpu"):
+def lpv_second_order(B=128, T=1 << 20, dtype=torch.float32, device="cpu", shard=0):
     """Config 4: time-varying 2x2 companion matrix; per-sample pole radius ~U(0.6,0.98),
     pole angle a random walk (step ~N(0,0.01)) reflected into (0,pi); x ~ N(0,1) into
     state 0; zero initial state.  A[b,n] = [[2 r cos(th), -r^2], [1, 0]]."""
-    g = _gen(device, 4)
+    g = _gen(device, 4, shard)
     r = 0.6 + 0.38 * _rand((B, T), g, device)
     th0 = math.pi * _rand((B, 1), g, device)
     walk = th0 + torch.cumsum(0.01 * _randn((B, T), g, device), dim=1)
@@ -87,10 +89,10 @@ def lpv_second_order(B=128, T=1 << 20, dtype=torch.float32, device="cpu"):
                 gy=_randn((B, T, 2), g, device).to(dtype))
 
 
-def long_first_order(B=8, T=1 << 28, dtype=torch.float32, device="cpu"):
+def long_first_order(B=8, T=1 << 28, dtype=torch.float32, device="cpu", shard=0):
     """Config 5: long-sequence first-order LPV; a[b,n] ~ U(0.9,0.999), x ~ N(0,1),
     zero initial state."""
-    g = _gen(device, 5)
+    g = _gen(device, 5, shard)
     return dict(a=(0.9 + 0.099 * _rand((B, T), g, device)).to(dtype),
                 zi=torch.zeros(B, dtype=dtype, device=device),
                 x=_randn((B, T), g, device).to(dtype), gy=_randn((B, T), g, device).to(dtype))

@@ -87,6 +87,32 @@ def test_biquad_golden(tag, mode):
     assert rel_err(zf, g["tdf2_zf"]) <= t
 
 
+@pytest.mark.parametrize("tag", ["f32", "f64"])
+@pytest.mark.parametrize("mode", ["batched", "shared"])
+def test_biquad_adjoint_golden(tag, mode):
+    """The section's adjoint against gradients the reference's autograd produced."""
+    g = load_golden(f"lfilter_order2_{mode}_{tag}")
+    t = tol(DT[tag])
+    gb, ga, _, gx = cport.biquad_tdf2_bwd(g["b"], g["a"], None, g["x"], g["gy"])
+    assert rel_err(gb, g["tdf2_grad_b"]) <= t and rel_err(ga, g["tdf2_grad_a"]) <= t
+    assert rel_err(gx, g["tdf2_grad_x"]) <= t
+    gb, ga, gzi, gx = cport.biquad_tdf2_bwd(g["b"], g["a"], g["zi"], g["x"], g["gy"], g["gzf"])
+    assert rel_err(gb, g["tdf2_zi_grad_b"]) <= t and rel_err(ga, g["tdf2_zi_grad_a"]) <= t
+    assert rel_err(gx, g["tdf2_zi_grad_x"]) <= t and rel_err(gzi, g["tdf2_zi_grad_zi"]) <= t
+
+
+def test_sos_chain_golden():
+    """Six chained sections (the reduced third benchmark configuration) against the reference's run."""
+    from philtorch_b200.workloads import sos_cascade
+
+    g = load_golden("config3_small")
+    w = sos_cascade(B=4, T=4096, sections=6)
+    ins, y = cport.sos_chain(w["b"], w["a"], w["x"])
+    gb, ga, gx = cport.sos_chain_bwd(w["b"], w["a"], ins, w["gy"])
+    assert rel_err(y, g["y"]) <= 1e-4 and rel_err(gx, g["grad_x"]) <= 1e-4
+    assert rel_err(gb, g["grad_b"]) <= 1e-4 and rel_err(ga, g["grad_a"]) <= 1e-4
+
+
 def test_g_in_chains_adjoint():
     """An adjoint state entering from the right equals running the adjoint on the
     concatenated sequence (used when a long sequence is split along time)."""

@@ -24,7 +24,6 @@ def _worker(rank, world, port, B, T, q, slow_decay, segments=1):
         from philtorch_b200.sharded import time_sharded_linear_recurrence
         from sharded_common import OracleKernels
 
-        sharded.FIXUP_BLOCK = 16   # several (doubling) fix-up blocks inside a 96-sample shard
         g = torch.Generator().manual_seed(7)
         a = torch.rand(B, T, generator=g, dtype=torch.float64) * 1.9 - 0.95
         if slow_decay:
@@ -96,9 +95,7 @@ def test_single_process_segments(segments, slow_decay):
     from philtorch_b200 import sharded
     from sharded_common import OracleKernels, full_reference
 
-    old = sharded.FIXUP_BLOCK
-    sharded.FIXUP_BLOCK = 16
-    try:
+    if True:
         g = torch.Generator().manual_seed(11)
         B, T = 3, 256
         a = torch.rand(B, T, generator=g, dtype=torch.float64) * 1.9 - 0.95
@@ -113,8 +110,6 @@ def test_single_process_segments(segments, slow_decay):
         y_ref, ga_ref, gzi_ref, gx_ref = full_reference(a, zi, x, gy)
         assert rel_err(y, y_ref) <= 1e-12 and rel_err(ga, ga_ref) <= 1e-12
         assert rel_err(gx, gx_ref) <= 1e-12 and rel_err(gzi, gzi_ref) <= 1e-12
-    finally:
-        sharded.FIXUP_BLOCK = old
 
 
 def test_auto_segments():

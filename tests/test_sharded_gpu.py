@@ -127,29 +127,102 @@ def test_real_ranks_nccl(tmp_path):
 
 
 @pytest.mark.parametrize("segments", [1, 4, 16])
-def test_single_gpu_segments(segments):
+@pytest.mark.parametrize("slow_decay", [False, True])
+def test_single_gpu_segments(segments, slow_decay):
     """One rank, its rows cut into segments that the kernels see as more rows: same results as the
-    plain kernels, for coefficients near one (the fix-up runs over several blocks) too."""
-    import philtorch_b200 as ptb
+    plain kernels; with coefficients so close to one that the correction never dies out the fix-up
+    walks whole segments."""
     from philtorch_b200 import sharded
 
     B, T = 4, 1 << 16
     g = torch.Generator().manual_seed(5)
-    a = (0.9 + 0.0999 * torch.rand(B, T, generator=g)).cuda()
-    x = torch.randn(B, T, generator=g).cuda()
-    zi = torch.randn(B, generator=g).cuda()
-    gy = torch.randn(B, T, generator=g).cuda()
-    old = sharded.FIXUP_BLOCK
-    sharded.FIXUP_BLOCK = 1 << 10
-    try:
-        ins = [t.clone().requires_grad_() for t in (a, zi, x)]
-        y = sharded.time_sharded_linear_recurrence(ins[0], ins[1], ins[2], segments=segments)
-        ga, gzi, gx = torch.autograd.grad(y, ins, gy)
-    finally:
-        sharded.FIXUP_BLOCK = old
-    ref = [t.clone().requires_grad_() for t in (a, zi, x)]
-    y_r = ptb.lpv.linear_recurrence(ref[0], ref[1], ref[2])
-    ga_r, gzi_r, gx_r = torch.autograd.grad(y_r, ref, gy)
+    # the never-decaying case is ill-conditioned in float32 (a random walk of 65536 steps): float64 there
+    dt = torch.float64 if slow_decay else torch.float32
+    a = ((0.99995 + 0.0001 * torch.rand(B, T, generator=g, dtype=dt)) if slow_decay
+         else (0.9 + 0.0999 * torch.rand(B, T, generator=g))).cuda()
+    x = torch.randn(B, T, generator=g, dtype=dt).cuda()
+    zi = torch.randn(B, generator=g, dtype=dt).cuda()
+    gy = torch.randn(B, T, generator=g, dtype=dt).cuda()
+    ins = [t.clone().requires_grad_() for t in (a, zi, x)]
+    y = sharded.time_sharded_linear_recurrence(ins[0], ins[1], ins[2], sharded.LOCAL, segments=segments)
+    ga, gzi, gx = torch.autograd.grad(y, ins, gy)
+    y_r, ga_r, gzi_r, gx_r = full_reference(a.cpu(), zi.cpu(), x.cpu(), gy.cpu())
+    t = 1e-9 if slow_decay else 1e-4
+    assert rel_err(y, y_r) <= t and rel_err(gx, gx_r) <= t
+    assert rel_err(ga, ga_r) <= t and rel_err(gzi, gzi_r) <= t
+    ptb.check_errors()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+@pytest.mark.parametrize("world,S,L,shared,slow_decay", [
+    (2, 1, 5000, False, False), (3, 4, 3001, False, False), (2, 8, 1024, False, True), (4, 2, 2500, False, True),
+    (2, 1, 4099, True, False), (3, 1, 2048, True, True), (8, 32, 1500, False, False)])
+def test_fixup_kernels_emulated_ranks(dtype, world, S, L, shared, slow_decay):
+    """The device-side fold + fix-up with several time shards emulated on one GPU: every shard runs
+    the calls a rank makes (zero-start scan, fold of its segment maps, fix-up with the gathered
+    shard maps; then the same from the right for the adjoint), the stacked maps standing in for the
+    all-gather.  Lengths that are not multiples of the fix-up block or of 16 bytes included."""
+    from philtorch_b200.sharded import _GpuKernels as K
+
+    B = 3
+    T = world * S * L
+    g = torch.Generator().manual_seed(world * 100 + S)
+    lo, width = (0.999, 0.001) if slow_decay else (0.6, 0.39)   # slow: the correction outlives every piece
+    a = (lo + width * torch.rand((T,) if shared else (B, T), generator=g, dtype=torch.float64)).to(dtype)
+    x = torch.randn(B, T, generator=g, dtype=torch.float64).to(dtype)
+    zi = torch.randn(B, generator=g, dtype=torch.float64).to(dtype)
+    gy = torch.randn(B, T, generator=g, dtype=torch.float64).to(dtype)
+    Tl = T // world
+    a_s = [a[..., r * Tl:(r + 1) * Tl].contiguous().to(DEV) for r in range(world)]
+    av = [t if shared else t.view(B * S, L) for t in a_s]
+    xv = [x[:, r * Tl:(r + 1) * Tl].contiguous().to(DEV).view(B * S, L) for r in range(world)]
+    gv = [gy[:, r * Tl:(r + 1) * Tl].contiguous().to(DEV).view(B * S, L) for r in range(world)]
+    zi_d = zi.to(DEV)
+    ys, maps = zip(*[K.scan_zero(av[r], xv[r]) for r in range(world)])
+    rank_maps = torch.stack([K.fold_maps(maps[r], B, S, False) for r in range(world)])
+    states = [K.fixup_forward(av[r], ys[r], maps[r], zi_d, rank_maps, r, world, B, S) for r in range(world)]
+    outs = [K.backward(av[r], states[r], ys[r], gv[r], None, True) for r in range(world)]
+    bmaps = [torch.stack([maps[r][:, 0], outs[r][1]], dim=1) for r in range(world)]
+    brank = torch.stack([K.fold_maps(bmaps[r], B, S, True) for r in range(world)])
+    gz = [K.fixup_backward(av[r], ys[r], states[r], bmaps[r], brank, r, world, outs[r][2], outs[r][0], B, S)
+          for r in range(world)]
+    ptb.check_errors()
+    y_ref, ga_ref, gzi_ref, gx_ref = full_reference(a, zi, x, gy)
+    t = tol(dtype) * (10 if slow_decay else 1)
+    assert rel_err(torch.cat([v.view(B, Tl) for v in ys], 1), y_ref) <= t
+    assert rel_err(torch.cat([o[2].view(B, Tl) for o in outs], 1), gx_ref) <= t
+    ga = torch.cat([o[0].view(-1, Tl) if not shared else o[0].view(1, Tl) for o in outs], 1)
+    assert rel_err(ga.view(ga_ref.shape), ga_ref) <= t
+    assert rel_err(gz[0], gzi_ref) <= t
+
+
+def test_few_long_rows_take_the_segmented_path():
+    """lpv.linear_recurrence cuts a handful of long rows into segments by itself (same values and
+    gradients as the oracle; double backward still works through the differentiable form)."""
+    B, T = 2, 1 << 22
+    w = workloads.long_first_order(B=B, T=T)
+    a, x, gy = w["a"], w["x"], w["gy"]
+    zi = torch.randn(B, generator=torch.Generator().manual_seed(3))
+    from philtorch_b200.sharded import auto_segments
+    assert auto_segments(B, T, True) == 4
+    ins = [t.to(DEV).requires_grad_() for t in (a, zi, x)]
+    y = ptb.lpv.linear_recurrence(*ins)
+    assert type(y.grad_fn).__name__.startswith("TimeShardedLPVRecurrence")
+    ga, gzi, gx = torch.autograd.grad(y, ins, gy.to(DEV))
+    y_r, ga_r, gzi_r, gx_r = full_reference(a, zi, x, gy)
     assert rel_err(y, y_r) <= 1e-4 and rel_err(gx, gx_r) <= 1e-4
     assert rel_err(ga, ga_r) <= 1e-4 and rel_err(gzi, gzi_r) <= 1e-4
     ptb.check_errors()
+
+
+def test_segmented_path_double_backward():
+    from philtorch_b200 import sharded
+
+    g = torch.Generator().manual_seed(9)
+    B, T = 2, 64
+    a = (torch.rand(B, T, generator=g, dtype=torch.float64) * 1.6 - 0.8).to(DEV).requires_grad_()
+    zi = torch.randn(B, generator=g, dtype=torch.float64).to(DEV).requires_grad_()
+    x = torch.randn(B, T, generator=g, dtype=torch.float64).to(DEV).requires_grad_()
+    fn = lambda a_, zi_, x_: sharded.time_sharded_linear_recurrence(a_, zi_, x_, sharded.LOCAL, segments=4)  # noqa: E731
+    assert torch.autograd.gradcheck(fn, (a, zi, x))
+    assert torch.autograd.gradgradcheck(fn, (a, zi, x))
