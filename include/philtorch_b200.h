@@ -180,8 +180,9 @@ int ptb_lpv_recur_fixup_bwd(int dtype, int64_t B, int64_t nseg, int64_t L, const
                             int world, void* grad_x, void* grad_a, void* grad_zi, ptb_stream_t stream);
 
 /* ---- first-order forward without any caller-side or library-side allocation -----------------
- * No counterpart in the reference.  Same computation and arguments as ptb_lpv_recur_fwd, minus the
- * workspace: the look-back scratch is a fixed 2 MiB array inside the library image (every GPU
+ * No counterpart in the reference.  Same computation and arguments as ptb_lpv_recur_fwd for
+ * PTB_F32 and PTB_F64 (the complex codes return PTB_ERR_ARG here, and
+ * ptb_lpv_recur_fwd_static_max_tiles returns 0 for them), minus the workspace: the look-back scratch is a fixed 2 MiB array inside the library image (every GPU
  * that loads the library holds it until the process exits).  It is for callers whose processing
  * call is not allowed to allocate device memory -- a real-time audio or DSP callback, where
  * cudaMalloc may stall the whole device for an unbounded time, or a host application that has
@@ -236,6 +237,29 @@ int ptb_lpv_recur2_bwd(int dtype, int64_t B, int64_t T, const void* A, int A_bat
                        const void* y, const void* gy, const void* g_in, int x_scalar, void* grad_x,
                        void* grad_A, void* grad_zi, void* workspace, int64_t workspace_bytes,
                        uint32_t* status, ptb_stream_t stream);
+
+/* ---- dense N x N recurrences, 2 < N <= 8 ---------------------------------------------------------
+ * Replace ops philtorch::recurN / philtorch::lti_recurN for state dimensions above two
+ * (philtorch/csrc/host_recur2.cpp:165,168; CPU kernels philtorch/csrc/host_recurN.cpp:81-140,236-281 and
+ * philtorch/csrc/host_lti_recurN.cpp:63-108; the reference has no GPU kernel for them).
+ *   h[t] = A[t] h[t-1] + x[t],  h[-1] = zi.
+ * A: row-major (N,N) matrices; A_timevar = 1: one per sample, (B,T,N,N) if A_batched else (T,N,N);
+ * A_timevar = 0: constant along time, (B,N,N) if A_batched else (N,N).  zi (B,N); x, y (B,T,N);
+ * zf optional (B,N).  N = 1 and 2 are accepted too (the dedicated kernels are faster).
+ * Workspace: ptb_recur_n_workspace_bytes (the look-back records hold N x N maps).
+ *
+ * ptb_recur_n_adj is the scan inside the adjoint rules MatrixRecurrence.backward
+ * (philtorch/lpv/ssm.py:64-99) and LTIMatrixRecurrence.backward (philtorch/lti/ssm.py:67-96):
+ *   g[t] = gy[t] + c[t+1],  c[t] = A[t]^T g[t],  c[T] = g_in (optional (B,N), zero if NULL);
+ * g (B,T,N) is grad_x, c0 (optional (B,N)) is grad_zi.  grad_A = g[t] (x) h[t-1] (summed over t for a
+ * time-invariant A) is left to the caller: per row it is an (N x T)(T x N) matrix product. */
+int64_t ptb_recur_n_workspace_bytes(int dtype, int N, int64_t B, int64_t T);
+int ptb_recur_n_fwd(int dtype, int N, int64_t B, int64_t T, const void* A, int A_batched, int A_timevar,
+                    const void* zi, const void* x, void* y, void* zf, void* workspace, int64_t workspace_bytes,
+                    uint32_t* status, ptb_stream_t stream);
+int ptb_recur_n_adj(int dtype, int N, int64_t B, int64_t T, const void* A, int A_batched, int A_timevar,
+                    const void* gy, const void* g_in, void* g, void* c0, void* workspace, int64_t workspace_bytes,
+                    uint32_t* status, ptb_stream_t stream);
 
 /* ---- one second-order section, transposed direct form II, scalar in / scalar out --------------
  * Replaces the whole lfilter(b, a, x, zi, form="tdf2") call stack for order <= 2

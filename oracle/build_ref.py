@@ -23,7 +23,8 @@ import sysconfig
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 REF_SRC_ENV = "PHILTORCH_REFERENCE_DIR"
-DEFAULT_REF = "/root/reference"
+# default location of the reference checkout: a directory named "reference" beside this repository
+DEFAULT_REF = os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 ORACLE_SO = os.path.join(HERE, "_build", "librecur_oracle.so")
 REF_SO = os.path.join(HERE, "_ref", "philtorch_ref_C.so")
 

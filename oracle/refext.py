@@ -23,12 +23,17 @@ _loaded = False
 
 
 def available() -> bool:
-    return os.path.exists(build_ref.REF_SO)
+    return os.path.exists(build_ref.REF_SO) or hasattr(torch.ops.philtorch, "lti_recur")
 
 
 def load() -> None:
     global _loaded
     if _loaded:
+        return
+    if hasattr(torch.ops.philtorch, "lti_recur"):
+        # the ops are defined already (an installed copy of the reference package was imported and
+        # brought its own build of the same extension): defining the library twice would fail
+        _loaded = True
         return
     if not available():
         raise RuntimeError("reference CPU extension not built: run oracle/build_ref.py "

@@ -64,6 +64,12 @@ lib.ptb_lpv_recur_carry.restype = _i32
 lib.ptb_lpv_recur_fwd_carry.argtypes = [_i32, _i64, _i64, _vp, _i32, _vp, _vp, _vp] + _tail
 lib.ptb_lpv_recur_fwd_carry.restype = _i32
 
+lib.ptb_recur_n_workspace_bytes.argtypes = [_i32, _i32, _i64, _i64]
+lib.ptb_recur_n_workspace_bytes.restype = _i64
+lib.ptb_recur_n_fwd.argtypes = [_i32, _i32, _i64, _i64, _vp, _i32, _i32, _vp, _vp, _vp, _vp] + _tail
+lib.ptb_recur_n_fwd.restype = _i32
+lib.ptb_recur_n_adj.argtypes = [_i32, _i32, _i64, _i64, _vp, _i32, _i32, _vp, _vp, _vp, _vp] + _tail
+lib.ptb_recur_n_adj.restype = _i32
 lib.ptb_lpv_recur_fold_maps.argtypes = [_i32, _i64, _i64, _vp, _i32, _vp, _vp]
 lib.ptb_lpv_recur_fold_maps.restype = _i32
 lib.ptb_lpv_recur_fixup_fwd.argtypes = [_i32, _i64, _i64, _i64, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _vp, _vp]
@@ -188,6 +194,15 @@ def call(fn, device: torch.device, B: int, T: int, *args, ws_bytes: int = -1) ->
         rc = fn(*args, ws.data_ptr(), ws.numel(), st.data_ptr(),
                 torch.cuda.current_stream(device).cuda_stream)
     check(rc, fn.__name__)
+    if CHECK_EVERY_CALL:
+        check_errors(device)
+
+
+# PHILTORCH_B200_CHECK=1: every call synchronises and raises at once if a device-side wait expired
+# (a debugging aid: it serialises host and device).  Without it a kernel that gave up on a wait only
+# sets a bit in the device's status word, and the results of that launch flow on until
+# ``check_errors()`` is called.
+CHECK_EVERY_CALL = os.environ.get("PHILTORCH_B200_CHECK", "0") not in ("", "0")
 
 
 def check_errors(device=None) -> None:

@@ -172,9 +172,14 @@ class LTIMatrixRecurrence(Function):
 
     @staticmethod
     def forward(A: Tensor, zi: Tensor, x: Tensor) -> Tensor:
-        if x.size(-1) != 2:
-            raise NotImplementedError("philtorch_b200 implements state dimensions 1 and 2 only")
-        return _ops.lti_recur2(A, zi, x)
+        n = x.size(-1)
+        if n == 2:
+            return _ops.lti_recur2(A, zi, x)
+        if n == 1:
+            return _ops.lti_recur(A.reshape(A.shape[:-2]), zi[:, 0], x[..., 0]).unsqueeze(-1)
+        if n > ops.MAX_STATE_DIM:
+            raise NotImplementedError(f"state dimension {n}: the kernels cover 1..{ops.MAX_STATE_DIM}")
+        return _ops.lti_recur_n(A, zi, x)
 
     @staticmethod
     def setup_context(ctx: Any, inputs, output) -> None:
@@ -186,9 +191,17 @@ class LTIMatrixRecurrence(Function):
     def backward(ctx: Any, grad_y: Tensor):
         A, zi, y = ctx.saved_tensors
         need_A, need_zi, need_x = ctx.needs_input_grad
-        if not torch.is_grad_enabled():
+        if not torch.is_grad_enabled() and y.size(-1) == 2:
             gA, gzi, gx = _ops.lti_recur2_bwd(A, zi, y, grad_y, None, False, need_A, need_zi)
             return _none_if_empty(gA, need_A), _none_if_empty(gzi, need_zi), _none_if_empty(gx, need_x)
+        if not torch.is_grad_enabled() and y.size(-1) > 2:
+            # one reversed scan on the kernels; grad_A is an (n x T)(T x n) product per row
+            g, c0 = _ops.recur_n_adj(A, grad_y, None, False)
+            gA = None
+            if need_A:
+                prev = _prev_states2(zi, y)
+                gA = g.flatten(0, 1).T @ prev.flatten(0, 1) if A.dim() == 2 else g.mT @ prev
+            return gA, (c0 if need_zi else None), (g if need_x else None)
         AmT = A.mT
         g = LTIMatrixRecurrence.apply(AmT, torch.zeros_like(zi), grad_y.flip(1)).flip(1)
         grad_A = grad_zi = grad_x = None
@@ -218,9 +231,14 @@ class MatrixRecurrence(Function):
 
     @staticmethod
     def forward(A: Tensor, zi: Tensor, x: Tensor) -> Tensor:
-        if x.size(-1) != 2:
-            raise NotImplementedError("philtorch_b200 implements state dimensions 1 and 2 only")
-        return _ops.recur2(A, zi, x)
+        n = x.size(-1)
+        if n == 2:
+            return _ops.recur2(A, zi, x)
+        if n == 1:
+            return _ops.lpv_recur(A[..., 0, 0], zi[:, 0], x[..., 0]).unsqueeze(-1)
+        if n > ops.MAX_STATE_DIM:
+            raise NotImplementedError(f"state dimension {n}: the kernels cover 1..{ops.MAX_STATE_DIM}")
+        return _ops.recur_n(A, zi, x)
 
     @staticmethod
     def setup_context(ctx: Any, inputs, output) -> None:
@@ -232,9 +250,17 @@ class MatrixRecurrence(Function):
     def backward(ctx: Any, grad_y: Tensor):
         A, zi, y = ctx.saved_tensors
         need_A, need_zi, need_x = ctx.needs_input_grad
-        if not torch.is_grad_enabled():
+        if not torch.is_grad_enabled() and y.size(-1) == 2:
             gA, gzi, gx = _ops.recur2_bwd(A, zi, y, grad_y, None, False, need_A, need_zi)
             return _none_if_empty(gA, need_A), _none_if_empty(gzi, need_zi), _none_if_empty(gx, need_x)
+        if not torch.is_grad_enabled() and y.size(-1) > 2:
+            g, c0 = _ops.recur_n_adj(A, grad_y, None, True)
+            gA = None
+            if need_A:
+                gA = g.unsqueeze(-1) * _prev_states2(zi, y).unsqueeze(-2)
+                if A.dim() == 3:
+                    gA = gA.sum(0)
+            return gA, (c0 if need_zi else None), (g if need_x else None)
         AmT = A.mT
         A_rev = torch.roll(AmT, shifts=-1, dims=-3).flip(-3)
         g = MatrixRecurrence.apply(A_rev, torch.zeros_like(zi), grad_y.flip(1)).flip(1)

@@ -126,13 +126,16 @@ static int so_small_fwd(int64_t B, int64_t T, const void* A, int A_batched, cons
   int dev = 0;
   PTB_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= kMaxDevices) return PTB_ERR_ARG;
-  if (!attr_set[dev]) {
-    PTB_CUDA(cudaFuncSetAttribute(so_small_fwd_kernel<S, C, XS>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
-    int sms = 0, occ = 1;
-    PTB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    PTB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, so_small_fwd_kernel<S, C, XS>, C::NT, L::kTotal));
-    grid_max[dev] = sms * std::max(occ, 1);
-    attr_set[dev] = true;
+  {   // first use on this device: one thread fills the cache, the others wait
+    std::lock_guard<std::mutex> init_lock(init_mutex());
+    if (!attr_set[dev]) {
+      PTB_CUDA(cudaFuncSetAttribute(so_small_fwd_kernel<S, C, XS>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+      int sms = 0, occ = 1;
+      PTB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+      PTB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, so_small_fwd_kernel<S, C, XS>, C::NT, L::kTotal));
+      grid_max[dev] = sms * std::max(occ, 1);
+      attr_set[dev] = true;
+    }
   }
   const unsigned grid = (unsigned)std::min<int64_t>(ntiles, grid_max[dev]);
   so_small_fwd_kernel<S, C, XS><<<grid, C::NT, L::kTotal, st>>>(p, wk, (uint32_t)B, (uint32_t)nchunks, (uint32_t)ntiles,
@@ -193,13 +196,16 @@ static int so_small_bwd(int64_t B, int64_t T, const void* A, int A_batched, cons
   int dev = 0;
   PTB_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= kMaxDevices) return PTB_ERR_ARG;
-  if (!attr_set[dev]) {
-    PTB_CUDA(cudaFuncSetAttribute(so_small_bwd_kernel<S, C, XS>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
-    int sms = 0, occ = 1;
-    PTB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    PTB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, so_small_bwd_kernel<S, C, XS>, C::NT, L::kTotal));
-    grid_max[dev] = sms * std::max(occ, 1);
-    attr_set[dev] = true;
+  {   // first use on this device: one thread fills the cache, the others wait
+    std::lock_guard<std::mutex> init_lock(init_mutex());
+    if (!attr_set[dev]) {
+      PTB_CUDA(cudaFuncSetAttribute(so_small_bwd_kernel<S, C, XS>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+      int sms = 0, occ = 1;
+      PTB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+      PTB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, so_small_bwd_kernel<S, C, XS>, C::NT, L::kTotal));
+      grid_max[dev] = sms * std::max(occ, 1);
+      attr_set[dev] = true;
+    }
   }
   const unsigned grid = (unsigned)std::min<int64_t>(ntiles, grid_max[dev]);
   so_small_bwd_kernel<S, C, XS><<<grid, C::NT, L::kTotal, st>>>(p, wk, (uint32_t)B, (uint32_t)nchunks, (uint32_t)ntiles,
@@ -338,10 +344,13 @@ static int static_scratch(void** out) {
   int dev = 0;
   PTB_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= kMaxDevices) return PTB_ERR_ARG;
-  if (!g_static_scratch_addr[dev]) {
-    void* p = nullptr;
-    PTB_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));   // device `dev` is current
-    g_static_scratch_addr[dev] = p;
+  {   // first use on this device: one thread fills the cache, the others wait
+    std::lock_guard<std::mutex> init_lock(init_mutex());
+    if (!g_static_scratch_addr[dev]) {
+      void* p = nullptr;
+      PTB_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));   // device `dev` is current
+      g_static_scratch_addr[dev] = p;
+    }
   }
   *out = g_static_scratch_addr[dev];
   return PTB_OK;
@@ -500,6 +509,7 @@ int ptb_selftest_wait_expiry(void* workspace, int64_t workspace_bytes, void* buf
 }
 
 int64_t ptb_lpv_recur_fwd_static_max_tiles(int dtype) {
+  if (dtype != PTB_F32 && dtype != PTB_F64) return 0;   // the entry point dispatches real types only
   // header + one look-back record and one (unused) partial slot per tile
   const int64_t per_tile = dtype == PTB_F64 ? (4 * 8 + 8) : (2 * 8 + 4);
   return (kStaticScratchBytes - kHeaderBytes - 2 * 256) / per_tile;

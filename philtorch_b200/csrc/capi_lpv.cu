@@ -35,9 +35,12 @@ static int launch_chained(K kernel, int smem, const P& p, int64_t B, int64_t T, 
   int dev = 0, sms = 0, occ = 1;
   PTB_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= kMaxDevices) return PTB_ERR_ARG;
-  if (!attr_set[dev]) {
-    PTB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    attr_set[dev] = true;
+  {   // first use on this device: one thread fills the cache, the others wait
+    std::lock_guard<std::mutex> init_lock(init_mutex());
+    if (!attr_set[dev]) {
+      PTB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      attr_set[dev] = true;
+    }
   }
   PTB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   PTB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, C::NT, smem));

@@ -1,0 +1,97 @@
+// C ABI of the dense N x N recurrences, 2 < N <= 8 (see include/philtorch_b200.h).
+#include "launch.cuh"
+
+#include "mat_n.cuh"
+
+namespace ptb {
+
+// (threads, samples per thread, stages) per padded size and precision: the stage holds
+// TILE * (NMAX + NMAX^2) scalars
+template <class S, int NMAX> struct MatNGeom;
+template <> struct MatNGeom<float, 4> { static constexpr int NT = 256, SPT = 2, ST = 3; };
+template <> struct MatNGeom<double, 4> { static constexpr int NT = 256, SPT = 1, ST = 3; };
+template <> struct MatNGeom<float, 8> { static constexpr int NT = 128, SPT = 1, ST = 3; };
+template <> struct MatNGeom<double, 8> { static constexpr int NT = 128, SPT = 1, ST = 2; };
+template <class S, int NMAX, bool REV>
+using MatNP = MatN<S, NMAX, MatNGeom<S, NMAX>::NT, MatNGeom<S, NMAX>::SPT, MatNGeom<S, NMAX>::ST, REV>;
+
+template <class P>
+static int64_t matn_ws(int64_t B, int64_t T) {
+  const int64_t ntiles = B * ((T + P::TILE - 1) / P::TILE);
+  return ws_layout(ntiles, P::SLOT_WORDS, sizeof(typename P::Partial)).total;
+}
+
+template <class S, int NMAX, bool REV>
+static int matn_run(int N, int64_t B, int64_t T, const void* A, int A_batched, int A_timevar, const void* zi,
+                    const void* x, void* y, void* zf, void* ws, int64_t wsb, uint32_t* status, cudaStream_t st) {
+  using P = MatNP<S, NMAX, REV>;
+  typename P::Params p;
+  p.A = static_cast<const S*>(A);
+  p.a_t_stride = A_timevar ? (int64_t)N * N : 0;
+  p.a_row_stride = A_batched ? (A_timevar ? T * N * N : (int64_t)N * N) : 0;
+  p.zi = static_cast<const S*>(zi);
+  p.x = static_cast<const S*>(x);
+  p.y = static_cast<S*>(y);
+  p.zf = static_cast<S*>(zf);
+  p.T = T;
+  p.N = N;
+  const bool bulk = aligned16(x) && aligned16(y) && (!A_timevar || aligned16(A)) && (T * N * sizeof(S)) % 16 == 0 &&
+                    ((int64_t)P::TILE * N * sizeof(S)) % 16 == 0;
+  return launch_scan<P, false>(p, B, T, bulk, ws, wsb, status, st, nullptr, nullptr);
+}
+
+template <class S, bool REV>
+static int matn_dispatch(int N, int64_t B, int64_t T, const void* A, int A_batched, int A_timevar, const void* zi,
+                         const void* x, void* y, void* zf, void* ws, int64_t wsb, uint32_t* status, cudaStream_t st) {
+  if (N <= 4) return matn_run<S, 4, REV>(N, B, T, A, A_batched, A_timevar, zi, x, y, zf, ws, wsb, status, st);
+  return matn_run<S, 8, REV>(N, B, T, A, A_batched, A_timevar, zi, x, y, zf, ws, wsb, status, st);
+}
+
+}  // namespace ptb
+
+using namespace ptb;
+
+extern "C" {
+
+int64_t ptb_recur_n_workspace_bytes(int dtype, int N, int64_t B, int64_t T) {
+  if (B <= 0 || T <= 0 || N < 1 || N > 8) return 0;
+  if (dtype == PTB_F32)
+    return N <= 4 ? std::max(matn_ws<MatNP<float, 4, false>>(B, T), matn_ws<MatNP<float, 4, true>>(B, T))
+                  : std::max(matn_ws<MatNP<float, 8, false>>(B, T), matn_ws<MatNP<float, 8, true>>(B, T));
+  if (dtype == PTB_F64)
+    return N <= 4 ? std::max(matn_ws<MatNP<double, 4, false>>(B, T), matn_ws<MatNP<double, 4, true>>(B, T))
+                  : std::max(matn_ws<MatNP<double, 8, false>>(B, T), matn_ws<MatNP<double, 8, true>>(B, T));
+  return 0;
+}
+
+int ptb_recur_n_fwd(int dtype, int N, int64_t B, int64_t T, const void* A, int A_batched, int A_timevar,
+                    const void* zi, const void* x, void* y, void* zf, void* workspace, int64_t workspace_bytes,
+                    uint32_t* status, ptb_stream_t stream) {
+  if (B < 0 || T < 0 || N < 1 || N > 8) return PTB_ERR_ARG;
+  if (B == 0 || T == 0) return PTB_OK;
+  if (!A || !zi || !x || !y) return PTB_ERR_ARG;
+  if (dtype == PTB_F32)
+    return matn_dispatch<float, false>(N, B, T, A, A_batched, A_timevar, zi, x, y, zf, workspace, workspace_bytes,
+                                       status, (cudaStream_t)stream);
+  if (dtype == PTB_F64)
+    return matn_dispatch<double, false>(N, B, T, A, A_batched, A_timevar, zi, x, y, zf, workspace, workspace_bytes,
+                                        status, (cudaStream_t)stream);
+  return PTB_ERR_ARG;
+}
+
+int ptb_recur_n_adj(int dtype, int N, int64_t B, int64_t T, const void* A, int A_batched, int A_timevar,
+                    const void* gy, const void* g_in, void* g, void* c0, void* workspace, int64_t workspace_bytes,
+                    uint32_t* status, ptb_stream_t stream) {
+  if (B < 0 || T < 0 || N < 1 || N > 8) return PTB_ERR_ARG;
+  if (B == 0 || T == 0) return PTB_OK;
+  if (!A || !gy || !g) return PTB_ERR_ARG;
+  if (dtype == PTB_F32)
+    return matn_dispatch<float, true>(N, B, T, A, A_batched, A_timevar, g_in, gy, g, c0, workspace, workspace_bytes,
+                                      status, (cudaStream_t)stream);
+  if (dtype == PTB_F64)
+    return matn_dispatch<double, true>(N, B, T, A, A_batched, A_timevar, g_in, gy, g, c0, workspace, workspace_bytes,
+                                       status, (cudaStream_t)stream);
+  return PTB_ERR_ARG;
+}
+
+}  // extern "C"

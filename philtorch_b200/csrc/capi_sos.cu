@@ -55,6 +55,7 @@ static int device_sms(int* sms) {
   int dev = 0;
   PTB_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= kMaxDevices) return PTB_ERR_ARG;
+  std::lock_guard<std::mutex> init_lock(init_mutex());
   if (!cached[dev]) PTB_CUDA(cudaDeviceGetAttribute(&cached[dev], cudaDevAttrMultiProcessorCount, dev));
   *sms = cached[dev];
   return PTB_OK;
@@ -114,9 +115,12 @@ static int chain_fwd(int64_t B, int64_t T, const void* b, const void* a, int coe
   static bool attr_set[kMaxDevices] = {};
   int dev = 0;
   PTB_CUDA(cudaGetDevice(&dev));
-  if (!attr_set[dev]) {
-    PTB_CUDA(cudaFuncSetAttribute(chain_fwd_kernel<S, C>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
-    attr_set[dev] = true;
+  {   // first use on this device: one thread fills the cache, the others wait
+    std::lock_guard<std::mutex> init_lock(init_mutex());
+    if (!attr_set[dev]) {
+      PTB_CUDA(cudaFuncSetAttribute(chain_fwd_kernel<S, C>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+      attr_set[dev] = true;
+    }
   }
   int occ = 1;
   PTB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, chain_fwd_kernel<S, C>, C::NT, L::kTotal));
@@ -275,9 +279,12 @@ static int chain_bwd(int64_t B, int64_t T, const void* b, const void* a, int coe
   static bool attr_set[kMaxDevices] = {};
   int dev = 0;
   PTB_CUDA(cudaGetDevice(&dev));
-  if (!attr_set[dev]) {
-    PTB_CUDA(cudaFuncSetAttribute(chain_bwd_kernel<S, C>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
-    attr_set[dev] = true;
+  {   // first use on this device: one thread fills the cache, the others wait
+    std::lock_guard<std::mutex> init_lock(init_mutex());
+    if (!attr_set[dev]) {
+      PTB_CUDA(cudaFuncSetAttribute(chain_bwd_kernel<S, C>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+      attr_set[dev] = true;
+    }
   }
   int occ = 1;
   PTB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, chain_bwd_kernel<S, C>, C::NT, L::kTotal));

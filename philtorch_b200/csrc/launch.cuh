@@ -7,6 +7,7 @@
 #include "scan_engine.cuh"
 
 #include <algorithm>
+#include <mutex>
 
 namespace ptb {
 
@@ -16,6 +17,11 @@ constexpr int kHeaderBytes = 256;
 constexpr int kMaxDevices = 64;
 
 inline thread_local int g_last_cuda_error = 0;
+// guards the lazily filled per-device launch caches (occupancy, function attributes, symbol addresses)
+inline std::mutex& init_mutex() {
+  static std::mutex m;
+  return m;
+}
 inline uint64_t g_wait_ns = kDefaultWaitNs;   // bound of every device-side wait (ptb_set_wait_limit_ms)
 
 #define PTB_CUDA(expr)                                   \
@@ -82,15 +88,18 @@ static int launch_scan(const typename P::Params& prm, int64_t B, int64_t T, bool
   PTB_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= kMaxDevices) return PTB_ERR_ARG;
   constexpr int smem = EngineSmem<P>::kTotal;
-  if (!cache.ready[dev]) {
-    PTB_CUDA(cudaFuncSetAttribute(scan_kernel<P>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    int occ = 0;
-    PTB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, scan_kernel<P>, P::NT + 32 * (P::LBW + 1), smem));
-    int sms = 0;
-    PTB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    cache.ctas_per_sm[dev] = std::max(occ, 1);
-    cache.sms[dev] = sms;
-    cache.ready[dev] = true;
+  {   // first use on this device: one thread fills the cache, the others wait
+    std::lock_guard<std::mutex> init_lock(init_mutex());
+    if (!cache.ready[dev]) {
+      PTB_CUDA(cudaFuncSetAttribute(scan_kernel<P>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      int occ = 0;
+      PTB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, scan_kernel<P>, P::NT + 32 * (P::LBW + 1), smem));
+      int sms = 0;
+      PTB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+      cache.ctas_per_sm[dev] = std::max(occ, 1);
+      cache.sms[dev] = sms;
+      cache.ready[dev] = true;
+    }
   }
   const int64_t resident = (int64_t)cache.sms[dev] * cache.ctas_per_sm[dev];
   const unsigned grid = (unsigned)std::min<int64_t>(ntiles, resident);

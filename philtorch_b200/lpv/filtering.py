@@ -53,6 +53,14 @@ def _ssm_lfilter(b: Tensor, a: Tensor, x: Tensor, zi: Optional[Tensor], form: st
             zi = zi.unsqueeze(0).expand(B, -1)
         zi2 = F.pad(zi, (0, 2 - zi.size(-1))) if zi.size(-1) < 2 else zi
     if form in ("df2", "tdf2") and B >= FUSED_MIN_ROWS:   # one fused kernel per direction
+        if b.dim() != a.dim():
+            # one tensor shared by the rows, the other per row (the reference broadcasts them,
+            # philtorch/lpv/filtering.py:297-320): give the shared one a batch axis; autograd's expand
+            # rule then sums its gradient over the rows
+            if b.dim() == 2:
+                b = b.unsqueeze(0).expand(B, -1, -1)
+            else:
+                a = a.unsqueeze(0).expand(B, -1, -1)
         y, zf = LPVBiquad.apply(b, a, zi2 if return_zf else None, x, form)
         return (y, zf[:, :order]) if return_zf else y
     a1, a2 = a[..., 0], a[..., 1]

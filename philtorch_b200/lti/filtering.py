@@ -20,6 +20,8 @@ from ..mat import companion
 from .recur import linear_recurrence
 from .ssm import diag_state_space, state_space
 
+MAX_ORDER = 8   # largest state dimension of the dense recurrence kernels
+
 __all__ = ["lfilter", "filtfilt", "lfilter_zi", "sosfilt", "comb_filter"]
 
 
@@ -117,17 +119,24 @@ def _ssm_lfilter(b: Tensor, a: Tensor, x: Tensor, zi: Optional[Tensor] = None, f
     kwargs.pop("unroll_factor", None)   # block size of the reference's Python scan; meaningless here
     if kwargs:
         raise TypeError(f"unexpected keyword arguments: {sorted(kwargs)}")
-    if form == "tdf2":
-        return _tdf2_section(b, a, x, zi)
-    if form == "df2":
+    order = max(b.size(-1) - 1, a.size(-1))
+    if form == "tdf2" and order <= 2:
+        return _tdf2_section(b, a, x, zi)     # the fused section kernel
+    if form in ("tdf2", "df2"):
+        # the filter's companion system on the recurrence kernels (orders up to 8 on the dense N x N
+        # kernels), with the input / output maps of philtorch/lti/filtering.py:288-313
+        if order > MAX_ORDER:
+            raise NotImplementedError(f"filter order {order}: the 'ssm' backend covers orders up to {MAX_ORDER}; "
+                                      "cascade second-order sections (sosfilt) or use backend='diag_ssm'")
         if b.size(-1) < a.size(-1) + 1:
             b = F.pad(b, (0, a.size(-1) + 1 - b.size(-1)))
         elif b.size(-1) > a.size(-1) + 1:
             a = F.pad(a, (0, b.size(-1) - a.size(-1) - 1))
-        if a.size(-1) > 2:
-            raise NotImplementedError("philtorch_b200 implements first- and second-order sections only")
         b0 = b[..., :1]
-        return state_space(companion(a), x, B=None, C=b[..., 1:] - b0 * a, D=b[..., 0], zi=zi, out_idx=None)
+        mix = b[..., 1:] - b0 * a
+        if form == "df2":
+            return state_space(companion(a), x, B=None, C=mix, D=b[..., 0], zi=zi, out_idx=None)
+        return state_space(companion(a).mT, x, B=mix, C=None, D=b[..., 0], zi=zi, out_idx=0)
     if form in ("df1", "tdf1"):
         raise NotImplementedError(f"form={form!r} is built on an FIR convolution, which is outside this package; "
                                   "use 'tdf2' or 'df2'")

@@ -1,4 +1,4 @@
-"""Time-invariant state-space front-end on the GPU kernels (orders 1 and 2).
+"""Time-invariant state-space front-end on the GPU kernels (state dimensions 1 to 8).
 
 Public names and argument conventions follow philtorch/lti/ssm.py of the reference:
 ``state_space_recursion`` (:198-383 there, pure PyTorch) and ``state_space`` (:386-510).  Every
@@ -19,8 +19,8 @@ __all__ = ["LTIMatrixRecurrence", "state_space_recursion", "state_space", "diag_
 
 
 def extension_backend_indicator(x: Tensor, M: int) -> bool:
-    """True when the compiled kernels handle this input (CUDA, fp32/fp64, state dimension <= 2)."""
-    return x.is_cuda and M in (1, 2) and x.dtype in (torch.float32, torch.float64)
+    """True when the compiled kernels handle this input (CUDA, fp32/fp64, state dimension <= 8)."""
+    return x.is_cuda and 1 <= M <= 8 and x.dtype in (torch.float32, torch.float64)
 
 
 def _ext_ss_recur(A: Tensor, zi: Tensor, x: Tensor, *, out_idx: Optional[int] = None, **_) -> Tensor:
@@ -35,7 +35,9 @@ def _ext_ss_recur(A: Tensor, zi: Tensor, x: Tensor, *, out_idx: Optional[int] = 
         else:
             y = LTIMatrixRecurrence.apply(A, zi, x)
     else:
-        raise NotImplementedError(f"state dimension {M}: philtorch_b200 implements orders 1 and 2 only")
+        if x.dim() == 2:   # the sequence feeds state 0 (zero-padded, as the reference does before its op)
+            x = torch.cat([x.unsqueeze(-1), x.new_zeros(x.shape + (M - 1,))], dim=-1)
+        y = LTIMatrixRecurrence.apply(A, zi, x)   # dense N x N kernels, M <= 8
     if out_idx is not None and y.dim() == 3:
         y = y[:, :, out_idx]
     return y

@@ -345,6 +345,84 @@ for _n, _lpv in (("lti_recur2_bwd", False), ("recur2_bwd", True)):
     torch.library.register_fake(f"philtorch_b200::{_n}")(_fake)
 
 
+# =============================================================================== N x N, 2 < N <= 8
+# Dense state matrices above 2x2: the reference's recurN / lti_recurN ops (CPU only there,
+# philtorch/csrc/host_recurN.cpp:236-281, philtorch/csrc/host_lti_recurN.cpp:63-108).
+MAX_STATE_DIM = 8
+_LIB.define("recur_n(Tensor A, Tensor zi, Tensor x) -> Tensor", tags=_TAGS)
+_LIB.define("lti_recur_n(Tensor A, Tensor zi, Tensor x) -> Tensor", tags=_TAGS)
+_LIB.define("recur_n_adj(Tensor A, Tensor gy, Tensor? g_in, bool timevar) -> (Tensor, Tensor)", tags=_TAGS)
+
+
+def _check_recur_n(A: Tensor, zi: Optional[Tensor], x: Tensor, lpv: bool) -> None:
+    torch._check(x.dim() == 3, lambda: "x must be 3D (batch, time, state).")
+    n = x.shape[2]
+    torch._check(A.dim() >= 2 and A.shape[-1] == n and A.shape[-2] == n, lambda: "A must be square.")
+    torch._check(1 <= n <= MAX_STATE_DIM, lambda: f"state dimension {n}: the kernels cover 1..{MAX_STATE_DIM}.")
+    if lpv:
+        torch._check(A.dim() in (3, 4), lambda: "A must be 3D or 4D.")
+        torch._check(x.shape[1] == A.shape[-3], lambda: "x's second dimension must match A's last-3 dimension.")
+    else:
+        torch._check(A.dim() in (2, 3), lambda: "A must be 2D or 3D.")
+    if zi is not None:
+        torch._check(zi.dim() == 2 and zi.shape[1] == n, lambda: "zi must have the state dimension of x.")
+        torch._check(x.shape[0] == zi.shape[0], lambda: "x and zi must have the same batch size.")
+    if A.dim() == (4 if lpv else 3):
+        torch._check(A.shape[0] == x.shape[0], lambda: "A's first dimension must match x's batch size.")
+
+
+def _make_recur_n(lpv: bool):
+    def impl(A: Tensor, zi: Tensor, x: Tensor) -> Tensor:
+        _check_recur_n(A, zi, x, lpv)
+        dev = _lib.require_cuda(A, zi, x)
+        _same_dtype(A, zi, x)
+        B, T, n = x.shape
+        A_c, zi_c, x_c = A.contiguous(), zi.contiguous(), x.contiguous()
+        y = torch.empty_like(x_c)
+        if B and T:
+            code = _lib.dtype_code(x)
+            _lib.call(lib.ptb_recur_n_fwd, dev, B, T, code, n, B, T, ptr(A_c), int(A.dim() == (4 if lpv else 3)),
+                      int(lpv), ptr(zi_c), ptr(x_c), ptr(y), None,
+                      ws_bytes=lib.ptb_recur_n_workspace_bytes(code, n, B, T))
+        return y
+
+    def fake(A, zi, x):
+        _check_recur_n(A, zi, x, lpv)
+        return torch.empty_like(x, memory_format=torch.contiguous_format)
+
+    return impl, fake
+
+
+def _recur_n_adj(A: Tensor, gy: Tensor, g_in: Optional[Tensor], timevar: bool):
+    """g[t] = gy[t] + c[t+1], c[t] = A[t]^T g[t], c[T] = g_in: returns (g, c[0])."""
+    _check_recur_n(A, g_in, gy, timevar)
+    dev = _lib.require_cuda(A, gy, g_in)
+    if A.dtype != gy.dtype or (g_in is not None and g_in.dtype != gy.dtype):
+        raise RuntimeError("A and g_in must have the same scalar type as gy")
+    B, T, n = gy.shape
+    A_c, gy_c, gin_c = A.contiguous(), gy.contiguous(), _opt(g_in)
+    g = torch.empty_like(gy_c)
+    c0 = gy.new_zeros(B, n) if g_in is None else gin_c.clone()
+    if B and T:
+        code = _lib.dtype_code(gy)
+        _lib.call(lib.ptb_recur_n_adj, dev, B, T, code, n, B, T, ptr(A_c), int(A.dim() == (4 if timevar else 3)),
+                  int(timevar), ptr(gy_c), ptr(gin_c), ptr(g), ptr(c0),
+                  ws_bytes=lib.ptb_recur_n_workspace_bytes(code, n, B, T))
+    return g, c0
+
+
+for _n, _lpv in (("recur_n", True), ("lti_recur_n", False)):
+    _impl, _fake = _make_recur_n(_lpv)
+    _LIB.impl(_n, _impl, "CUDA")
+    torch.library.register_fake(f"philtorch_b200::{_n}")(_fake)
+_LIB.impl("recur_n_adj", _recur_n_adj, "CUDA")
+
+
+@torch.library.register_fake("philtorch_b200::recur_n_adj")
+def _(A, gy, g_in, timevar):
+    return torch.empty_like(gy, memory_format=torch.contiguous_format), gy.new_empty(gy.shape[0], gy.shape[2])
+
+
 # =============================================================================== TDF-II section
 _LIB.define("biquad_tdf2(Tensor b, Tensor a, Tensor? zi, Tensor x) -> (Tensor, Tensor)", tags=_TAGS)
 _LIB.define("biquad_tdf2_bwd(Tensor b, Tensor a, Tensor x, Tensor y, Tensor gy, Tensor? gzf, bool need_coef, "
@@ -806,5 +884,5 @@ for _name in ("lti_recur", "lti_recur_bwd", "lpv_recur", "lpv_recur_bwd", "lti_r
               "recur2_sx", "lti_recur2_bwd", "recur2_bwd", "biquad_tdf2", "biquad_tdf2_bwd", "lpv_recur_carry", "lpv_recur_zero_carry",
               "sos_cascade", "sos_cascade_bwd", "lpv_biquad_df2", "lpv_biquad_df2_bwd",
               "lpv_biquad_tdf2", "lpv_biquad_tdf2_bwd", "comb", "comb_bwd", "lti_recur_reverse_fused",
-              "modal_mix", "modal_mix_bwd", "modal_drive"):
+              "modal_mix", "modal_mix_bwd", "modal_drive", "recur_n", "lti_recur_n", "recur_n_adj"):
     _LIB.impl(_name, _no_backend(_name), "CPU")

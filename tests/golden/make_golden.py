@@ -61,7 +61,10 @@ def _np(t):
 def save(name, **arrays):
     arrays = {k: v for k, v in arrays.items() if v is not None}
     np.savez_compressed(os.path.join(HERE, name + ".npz"), **arrays)
-    print(name, {k: getattr(v, "shape", None) for k, v in arrays.items()})
+    if len(arrays) > 40:
+        print(name, f"{len(arrays)} arrays")
+    else:
+        print(name, {k: getattr(v, "shape", None) for k, v in arrays.items()})
 
 
 def grads(out, gy, *inputs):
@@ -308,8 +311,123 @@ def low_precision_cases(pt):
              grad_x=f(gx))
 
 
+def state_space_cases(pt):
+    """philtorch.lpv.state_space with every accepted shape of B, C and D (extension route,
+    unroll_factor=1), state dimensions 2 and 3, scalar and feature inputs; all tensors of one case go
+    into one file, keyed "<case>/<name>"."""
+    g = torch.Generator().manual_seed(777)
+    batch, N, F, P = 3, 12, 2, 4
+    dt = torch.float64
+
+    def rnd(*shape):
+        return torch.randn(tuple(shape), generator=g, dtype=dt)
+
+    store = {}
+    names = []
+    for M in (2, 3):
+        B2 = [None, (M,), (N, M), (batch, M), (batch, N, M)]                     # x (batch, N)
+        B3 = [(M, F), (N, M, F), (batch, M, F), (batch, N, M, F)]                # x (batch, N, F)
+        C_scalar = [(M,), (N, M), (batch, M), (batch, N, M)]                      # y (batch, N)
+        C_vector = [(P, M), (N, P, M), (batch, P, M), (batch, N, P, M)]           # y (batch, N, P)
+        D2_scalar = [None, (), (N,), (batch,), (batch, N)]
+        D3_scalar = [None, (F,), (N, F), (batch, F), (batch, N, F)]
+        D2_vector = [None, (P,), (N, P), (batch, P), (batch, N, P)]
+        D3_vector = [None, (P, F), (N, P, F), (batch, P, F), (batch, N, P, F)]
+        cases = []
+
+        def cycle(kind, Bs, Cs, Ds):   # every shape of every list at least once, consistent output ranks
+            for i in range(max(len(Bs), len(Cs), len(Ds))):
+                cases.append((kind, Bs[i % len(Bs)], Cs[i % len(Cs)], Ds[i % len(Ds)]))
+
+        cycle("2d", B2, C_scalar, D2_scalar)
+        cycle("2d", B2, C_vector, D2_vector)
+        cycle("3d", B3, C_scalar, D3_scalar)
+        cycle("3d", B3, C_vector, D3_vector)
+        cases.append(("2d", (M,), None, None))          # all states out
+        cases.append(("2d-outidx", (M,), None, ()))
+        for ci, (kind, bs, cs, ds) in enumerate(cases):
+            for A_batched in (True, False):
+                r = 0.5 * torch.rand((batch, N, M, M) if A_batched else (N, M, M), generator=g, dtype=dt) / M
+                A = (r - r.mean()).requires_grad_()
+                x = (rnd(batch, N) if kind.startswith("2d") else rnd(batch, N, F)).requires_grad_()
+                Bm = None if bs is None else rnd(*bs).requires_grad_()
+                Cm = None if cs is None else rnd(*cs).requires_grad_()
+                Dm = None if ds is None else rnd(*ds).requires_grad_()
+                zi = rnd(batch, M).requires_grad_()
+                out_idx = 1 if kind == "2d-outidx" else None
+                y, zf = pt.lpv.state_space(A, x, B=Bm, C=Cm, D=Dm, zi=zi, unroll_factor=1, out_idx=out_idx)
+                y2 = pt.lpv.state_space(A, x, B=Bm, C=Cm, D=Dm, unroll_factor=1, out_idx=out_idx)
+                gy, gzf = rnd(*y.shape), rnd(*zf.shape)
+                ins = [t for t in (A, x, Bm, Cm, Dm, zi) if t is not None]
+                gs = torch.autograd.grad([y, zf], ins, [gy, gzf], allow_unused=True)
+                key = f"M{M}_{ci}_{'Ab' if A_batched else 'As'}"
+                names.append(key)
+                store[f"{key}/out_idx"] = np.array(-1 if out_idx is None else out_idx)
+                for nm, t in (("A", A), ("x", x), ("B", Bm), ("C", Cm), ("D", Dm), ("zi", zi), ("gy", gy), ("gzf", gzf),
+                              ("y", y), ("zf", zf), ("y_nozi", y2)):
+                    if t is not None:
+                        store[f"{key}/{nm}"] = _np(t)
+                for t, gt in zip(ins, gs):
+                    nm = next(n for n, u in (("A", A), ("x", x), ("B", Bm), ("C", Cm), ("D", Dm), ("zi", zi)) if u is t)
+                    if gt is not None:
+                        store[f"{key}/grad_{nm}"] = _np(gt)
+    store["cases"] = np.array(names)
+    save("lpv_state_space_f64", **store)
+
+
+def dense_recurrence_cases(pt):
+    """State dimensions above two through the reference's recurN / lti_recurN ops and its autograd
+    Functions (CPU extension): N = 3, 4, 5, 8, per-row and shared matrices, float64 and float32;
+    and time-invariant filters of order 3 and 5 through lti.lfilter(unroll_factor=1)."""
+    from philtorch.lti.ssm import LTIMatrixRecurrence
+    from philtorch.lpv.ssm import MatrixRecurrence
+    g = torch.Generator().manual_seed(4242)
+    Bn, T = 2, 150
+    for dt, tag in ((torch.float64, "f64"), (torch.float32, "f32")):
+        store = {}
+        for n in (3, 5, 8):
+            for lpv in (True, False):
+                for batched in (True, False):
+                    lead = ((Bn,) if batched else ()) + ((T,) if lpv else ())
+                    A = (torch.randn(lead + (n, n), generator=g, dtype=torch.float64) * (0.55 / n ** 0.5)).to(dt)
+                    zi = torch.randn(Bn, n, generator=g, dtype=torch.float64).to(dt)
+                    x = torch.randn(Bn, T, n, generator=g, dtype=torch.float64).to(dt)
+                    gy = torch.randn(Bn, T, n, generator=g, dtype=torch.float64).to(dt)
+                    Ar, zr, xr = (t.clone().requires_grad_() for t in (A, zi, x))
+                    y = (MatrixRecurrence if lpv else LTIMatrixRecurrence).apply(Ar, zr, xr)
+                    gA, gzi, gx = grads(y, gy, Ar, zr, xr)
+                    key = f"n{n}_{'lpv' if lpv else 'lti'}_{'batched' if batched else 'shared'}"
+                    for nm, t in (("A", _np(A)), ("zi", _np(zi)), ("x", _np(x)), ("gy", _np(gy)), ("y", _np(y)),
+                                  ("grad_A", gA), ("grad_zi", gzi), ("grad_x", gx)):
+                        store[f"{key}/{nm}"] = t
+        for order in (3, 5):
+            rad = 0.4 + 0.5 * torch.rand(Bn, order, generator=g, dtype=torch.float64)
+            poles = torch.polar(rad, 3.0 * torch.rand(Bn, order, generator=g, dtype=torch.float64))
+            a = torch.stack([torch.from_numpy(np.poly(np.concatenate([p.numpy()[: order // 2], p.numpy()[: order // 2].conj(),
+                                                                      p.numpy()[order - 1:].real])).real[1:])
+                             for p in poles]).to(dt)
+            b = torch.randn(Bn, order + 1, generator=g, dtype=torch.float64).to(dt)
+            x = torch.randn(Bn, T, generator=g, dtype=torch.float64).to(dt)
+            gy = torch.randn(Bn, T, generator=g, dtype=torch.float64).to(dt)
+            for form in ("tdf2", "df2"):
+                br, ar, xr = (t.clone().requires_grad_() for t in (b, a, x))
+                y = pt.lti.lfilter(br, ar, xr, form=form, unroll_factor=1)
+                gb, ga, gx = grads(y, gy, br, ar, xr)
+                key = f"lfilter{order}_{form}"
+                for nm, t in (("b", _np(b)), ("a", _np(a)), ("x", _np(x)), ("gy", _np(gy)), ("y", _np(y)),
+                              ("grad_b", gb), ("grad_a", ga), ("grad_x", gx)):
+                    store[f"{key}/{nm}"] = t
+        save(f"dense_recurrence_{tag}", **store)
+
+
 def main():
     pt = import_reference()
+    if len(sys.argv) > 1 and sys.argv[1] == "state_space":     # only this group
+        state_space_cases(import_reference())
+        return
+    if len(sys.argv) > 1 and sys.argv[1] == "dense":           # only this group
+        dense_recurrence_cases(import_reference())
+        return
     if len(sys.argv) > 1 and sys.argv[1] == "low_precision":   # only this group
         low_precision_cases(pt)
         return

@@ -88,3 +88,35 @@ def test_fused_matches_scan_path(form, dtype, B, T, shared, monkeypatch):
         # shared coefficients: the gradient sums over the rows, in another order
         assert rel_err(got, ref) <= (10 * t if shared and name in ("grad_b", "grad_a") else t), name
     ptb.check_errors()
+
+
+@pytest.mark.parametrize("form", ["df2", "tdf2"])
+@pytest.mark.parametrize("order", [1, 2])
+@pytest.mark.parametrize("shared", ["b", "a"])
+def test_one_coefficient_shared_one_per_row(form, order, shared, df2_path):
+    """b shared by the rows and a per row (or the reverse), as the reference's broadcasting allows:
+    the same values and gradient shapes on the fused kernels (32 rows) as on the scan route."""
+    from philtorch_b200.lpv import filtering
+
+    B, N = 32, 700
+    g = torch.Generator().manual_seed(order * 10 + (shared == "a"))
+    bs = (N, order + 1) if shared == "b" else (B, N, order + 1)
+    as_ = (N, order) if shared == "a" else (B, N, order)
+    b = torch.randn(bs, generator=g, dtype=torch.float64).to(DEV).requires_grad_()
+    a = (0.4 * (torch.rand(as_, generator=g, dtype=torch.float64) - 0.5)).to(DEV).requires_grad_()
+    x = torch.randn(B, N, generator=g, dtype=torch.float64).to(DEV).requires_grad_()
+    gy = torch.randn(B, N, generator=g, dtype=torch.float64).to(DEV)
+    y = ptb.lpv.lfilter(b, a, x, form=form)
+    grads = torch.autograd.grad(y, (b, a, x), gy)
+    assert grads[0].shape == b.shape and grads[1].shape == a.shape
+    old = filtering.FUSED_MIN_ROWS
+    filtering.FUSED_MIN_ROWS = 10**9 if df2_path == 1 else 1      # the other implementation
+    try:
+        y2 = ptb.lpv.lfilter(b, a, x, form=form)
+        grads2 = torch.autograd.grad(y2, (b, a, x), gy)
+    finally:
+        filtering.FUSED_MIN_ROWS = old
+    assert rel_err(y, y2) <= 1e-10
+    for g1, g2 in zip(grads, grads2):
+        assert rel_err(g1, g2) <= 1e-9
+    ptb.check_errors()

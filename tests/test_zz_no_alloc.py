@@ -75,3 +75,36 @@ def test_static_scratch_limit_is_refused():
                                       None, None, torch.cuda.current_stream().cuda_stream)
     assert rc == 5
     assert b"scratch" in lib.ptb_error_string(rc)
+
+
+def test_static_shared_coefficients_without_status_word():
+    """Coefficients shared by the rows (a_batched = 0) and no status word (NULL): same results as the
+    entry point with a workspace."""
+    lib = _bind()
+    stream = torch.cuda.current_stream().cuda_stream
+    B, T = 5, 30001
+    a, zi, x = _inputs(B, T, 9, torch.float32)
+    a = a[0].contiguous()
+    y_static, y_ws = torch.empty_like(x), torch.empty_like(x)
+    rc = lib.ptb_lpv_recur_fwd_static(0, B, T, a.data_ptr(), 0, zi.data_ptr(), 1, x.data_ptr(), y_static.data_ptr(),
+                                      None, None, stream)
+    assert rc == 0, lib.ptb_error_string(rc)
+    nbytes = lib.ptb_workspace_bytes(B, T)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    rc = lib.ptb_lpv_recur_fwd(0, B, T, a.data_ptr(), 0, zi.data_ptr(), 1, x.data_ptr(), y_ws.data_ptr(), None,
+                               ws.data_ptr(), nbytes, None, stream)
+    assert rc == 0, lib.ptb_error_string(rc)
+    torch.cuda.synchronize()
+    assert (y_static - y_ws).abs().max().item() / y_ws.abs().max().item() <= 1e-4
+
+
+def test_static_entry_point_is_real_only():
+    """Complex dtype codes are not dispatched here: the size query answers 0 and the call is refused."""
+    lib = _bind()
+    for code in (2, 3, 7):
+        assert lib.ptb_lpv_recur_fwd_static_max_tiles(code) == 0
+    a, zi, x = _inputs(2, 64, 1, torch.float32)
+    y = torch.empty_like(x)
+    rc = lib.ptb_lpv_recur_fwd_static(2, 2, 32, a.data_ptr(), 1, zi.data_ptr(), 1, x.data_ptr(), y.data_ptr(), None,
+                                      None, torch.cuda.current_stream().cuda_stream)
+    assert rc == 1
