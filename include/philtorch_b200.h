@@ -13,6 +13,11 @@
  *                interleaved {re, im} pairs, element counts unchanged; their adjoint uses conj(a) and
  *                grad_a = sum g[t] conj(y[t-1]) as the reference's autograd Function does
  *                (philtorch/lti/recur.py:31-57).
+ *                They also take PTB_F16 / PTB_BF16 (the reference dispatches both,
+ *                philtorch/csrc/lti_recur.cu:135-136, philtorch/csrc/host_recurN.cpp:259-260): every
+ *                array of the call holds 2-byte floats, the recurrence runs in float32 registers and
+ *                each result is rounded once.  These need rows that qualify for bulk copies (all
+ *                base pointers 16-byte aligned, T a multiple of 8), else PTB_ERR_ARG.
  *   recurrence   y[-1] := zi, y[t] = A[t] * y[t-1] + x[t], t = 0..T-1: the coefficient with time
  *                index t multiplies the PREVIOUS state (philtorch/csrc/host_recurN.cpp:254-255).
  *   *_batched    1: the array has a leading batch axis of length B; 0: one copy shared by all rows.
@@ -35,7 +40,8 @@ extern "C" {
 typedef void* ptb_stream_t; /* a cudaStream_t */
 
 enum { PTB_F32 = 0, PTB_F64 = 1,
-       PTB_C64 = 2, PTB_C128 = 3 /* interleaved {re, im}; first-order recurrences only */ };
+       PTB_C64 = 2, PTB_C128 = 3, /* interleaved {re, im}; first-order recurrences only */
+       PTB_F16 = 4, PTB_BF16 = 5  /* 2-byte arrays, float32 arithmetic; first-order recurrences only */ };
 enum {
   PTB_OK = 0,
   PTB_ERR_ARG = 1,       /* null pointer, negative size, unknown dtype */

@@ -17,7 +17,9 @@ LIB_PATH = os.environ.get("PHILTORCH_B200_LIB") or os.path.join(_HERE, "libphilt
 PTB_F32, PTB_F64 = 0, 1
 PTB_C64, PTB_C128 = 2, 3
 _DTYPES = {torch.float32: PTB_F32, torch.float64: PTB_F64}
-_COMPLEX_DTYPES = {torch.complex64: PTB_C64, torch.complex128: PTB_C128}
+PTB_F16, PTB_BF16 = 4, 5
+_COMPLEX_DTYPES = {torch.complex64: PTB_C64, torch.complex128: PTB_C128,
+                   torch.float16: PTB_F16, torch.bfloat16: PTB_BF16}   # first-order kernels only
 
 if not os.path.exists(LIB_PATH):
     raise ImportError(
@@ -132,7 +134,8 @@ ERROR_BITS = {1: "look-back wait expired", 2: "tile load wait expired", 4: "tile
 
 
 def dtype_code(t: torch.Tensor, complex_ok: bool = False) -> int:
-    """dtype code of the C ABI; complex64/complex128 only where the kernels have them (first order)."""
+    """dtype code of the C ABI; complex64/complex128 and the 2-byte floats only where the kernels
+    have them (first order)."""
     if complex_ok and t.dtype in _COMPLEX_DTYPES:
         return _COMPLEX_DTYPES[t.dtype]
     try:

@@ -423,6 +423,12 @@ int ptb_lti_recur_fwd(int dtype, int64_t B, int64_t T, const void* a, int a_batc
   if (dtype == PTB_C64 || dtype == PTB_C128)
     return cx_fo_fwd(dtype, 0, B, T, a, a_batched, zi, zi_batched, x, y, zf, workspace, workspace_bytes, status,
                      (cudaStream_t)stream);
+  if (dtype == PTB_F16)
+    return fo_fwd<float, false, __half>(B, T, a, a_batched, zi, zi_batched, x, y, zf, workspace, workspace_bytes, status,
+                                       (cudaStream_t)stream);
+  if (dtype == PTB_BF16)
+    return fo_fwd<float, false, __nv_bfloat16>(B, T, a, a_batched, zi, zi_batched, x, y, zf, workspace, workspace_bytes,
+                                              status, (cudaStream_t)stream);
   PTB_DISPATCH(dtype, (fo_fwd<S, false>(B, T, a, a_batched, zi, zi_batched, x, y, zf, workspace,
                                         workspace_bytes, status, (cudaStream_t)stream)));
 }
@@ -436,6 +442,12 @@ int ptb_lpv_recur_fwd(int dtype, int64_t B, int64_t T, const void* a, int a_batc
   if (dtype == PTB_C64 || dtype == PTB_C128)
     return cx_fo_fwd(dtype, 1, B, T, a, a_batched, zi, zi_batched, x, y, zf, workspace, workspace_bytes, status,
                      (cudaStream_t)stream);
+  if (dtype == PTB_F16)
+    return fo_fwd<float, true, __half>(B, T, a, a_batched, zi, zi_batched, x, y, zf, workspace, workspace_bytes, status,
+                                       (cudaStream_t)stream);
+  if (dtype == PTB_BF16)
+    return fo_fwd<float, true, __nv_bfloat16>(B, T, a, a_batched, zi, zi_batched, x, y, zf, workspace, workspace_bytes,
+                                              status, (cudaStream_t)stream);
   PTB_DISPATCH(dtype, (fo_fwd<S, true>(B, T, a, a_batched, zi, zi_batched, x, y, zf, workspace,
                                        workspace_bytes, status, (cudaStream_t)stream)));
 }
@@ -535,6 +547,12 @@ int ptb_lti_recur_bwd(int dtype, int64_t B, int64_t T, const void* a, int a_batc
   if (dtype == PTB_C64 || dtype == PTB_C128)
     return cx_fo_bwd(dtype, 0, B, T, a, a_batched, zi, zi_batched, y, gy, g_in, grad_x, grad_a, grad_zi, workspace,
                      workspace_bytes, status, (cudaStream_t)stream);
+  if (dtype == PTB_F16)
+    return fo_bwd<float, false, __half>(B, T, a, a_batched, zi, zi_batched, y, gy, g_in, grad_x, grad_a, grad_zi, workspace,
+                                       workspace_bytes, status, (cudaStream_t)stream);
+  if (dtype == PTB_BF16)
+    return fo_bwd<float, false, __nv_bfloat16>(B, T, a, a_batched, zi, zi_batched, y, gy, g_in, grad_x, grad_a, grad_zi,
+                                              workspace, workspace_bytes, status, (cudaStream_t)stream);
   PTB_DISPATCH(dtype, (fo_bwd<S, false>(B, T, a, a_batched, zi, zi_batched, y, gy, g_in, grad_x, grad_a,
                                         grad_zi, workspace, workspace_bytes, status, (cudaStream_t)stream)));
 }
@@ -559,6 +577,12 @@ int ptb_lpv_recur_bwd(int dtype, int64_t B, int64_t T, const void* a, int a_batc
   if (dtype == PTB_C64 || dtype == PTB_C128)
     return cx_fo_bwd(dtype, 1, B, T, a, a_batched, zi, zi_batched, y, gy, g_in, grad_x, grad_a, grad_zi, workspace,
                      workspace_bytes, status, (cudaStream_t)stream);
+  if (dtype == PTB_F16)
+    return fo_bwd<float, true, __half>(B, T, a, a_batched, zi, zi_batched, y, gy, g_in, grad_x, grad_a, grad_zi, workspace,
+                                       workspace_bytes, status, (cudaStream_t)stream);
+  if (dtype == PTB_BF16)
+    return fo_bwd<float, true, __nv_bfloat16>(B, T, a, a_batched, zi, zi_batched, y, gy, g_in, grad_x, grad_a, grad_zi,
+                                              workspace, workspace_bytes, status, (cudaStream_t)stream);
   PTB_DISPATCH(dtype, (fo_bwd<S, true>(B, T, a, a_batched, zi, zi_batched, y, gy, g_in, grad_x, grad_a,
                                        grad_zi, workspace, workspace_bytes, status, (cudaStream_t)stream)));
 }

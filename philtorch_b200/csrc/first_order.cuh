@@ -10,6 +10,9 @@
 #pragma once
 #include "scan_engine.cuh"
 
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
 namespace ptb {
 
 template <class S, int N_>
@@ -25,7 +28,57 @@ template <> struct Vec16<double> { using type = double2; static constexpr int V 
 template <> struct Vec16<Cx<float>> { using type = float4; static constexpr int V = 2; };
 template <> struct Vec16<Cx<double>> { using type = double2; static constexpr int V = 1; };
 
+// ---- storage types narrower than the arithmetic type -------------------------------------------
+// float16 / bfloat16 tensors are staged and stored as they are (2 bytes per sample in HBM and in
+// shared memory) while the recurrence runs in float32 registers: one rounding per result instead of
+// one per step, and 2 instead of 4 bytes per sample of traffic.
+template <> struct Vec16<__half> { using type = uint4; static constexpr int V = 8; };
+template <> struct Vec16<__nv_bfloat16> { using type = uint4; static constexpr int V = 8; };
+
+template <class S, class G> struct Cvt {
+  static __device__ __forceinline__ S in(const G& v) { return v; }
+  static __device__ __forceinline__ G out(const S& v) { return v; }
+};
+template <> struct Cvt<float, __half> {
+  static __device__ __forceinline__ float in(const __half& v) { return __half2float(v); }
+  static __device__ __forceinline__ __half out(const float& v) { return __float2half_rn(v); }
+};
+template <> struct Cvt<float, __nv_bfloat16> {
+  static __device__ __forceinline__ float in(const __nv_bfloat16& v) { return __bfloat162float(v); }
+  static __device__ __forceinline__ __nv_bfloat16 out(const float& v) { return __float2bfloat16_rn(v); }
+};
+
 template <class S, int V> struct VecIO;
+template <> struct VecIO<__half, 8> {
+  static __device__ __forceinline__ void ld(const unsigned char* p, float* r) {
+    const uint4 q = *reinterpret_cast<const uint4*>(p);
+    const __half2* h = reinterpret_cast<const __half2*>(&q);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 f = __half22float2(h[i]); r[2 * i] = f.x; r[2 * i + 1] = f.y; }
+  }
+  static __device__ __forceinline__ void st(unsigned char* p, const float* r) {
+    uint4 q;
+    __half2* h = reinterpret_cast<__half2*>(&q);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(r[2 * i], r[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = q;
+  }
+};
+template <> struct VecIO<__nv_bfloat16, 8> {
+  static __device__ __forceinline__ void ld(const unsigned char* p, float* r) {
+    const uint4 q = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); r[2 * i] = f.x; r[2 * i + 1] = f.y; }
+  }
+  static __device__ __forceinline__ void st(unsigned char* p, const float* r) {
+    uint4 q;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&q);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(r[2 * i], r[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = q;
+  }
+};
 template <> struct VecIO<Cx<float>, 2> {
   static __device__ __forceinline__ void ld(const unsigned char* p, Cx<float>* r) {
     const float4 q = *reinterpret_cast<const float4*>(p);
@@ -85,25 +138,27 @@ struct ScalarAffine {
 };
 
 // ------------------------------------------------------------------------------------ forward
-template <class S>
+// S: arithmetic type; G: type of the arrays in memory (S itself, or a 2-byte float with S = float)
+template <class G>
 struct FoFwdParams {
-  const S* a; int64_t a_row_stride;   // LPV: T or 0; LTI: 1 or 0
-  const S* zi; int64_t zi_stride;     // 1, or 0 when one value is shared by all rows
-  const S* x;
-  S* y;
-  S* zf;                              // optional (B,) final state
+  const G* a; int64_t a_row_stride;   // LPV: T or 0; LTI: 1 or 0
+  const G* zi; int64_t zi_stride;     // 1, or 0 when one value is shared by all rows
+  const G* x;
+  G* y;
+  G* zf;                              // optional (B,) final state
   int64_t T;
 };
 
-template <class S, int CH, int STAGES_, int MIN_CTAS_, int LBW_, bool LPV>
+template <class S, int CH, int STAGES_, int MIN_CTAS_, int LBW_, bool LPV, class G = S>
 struct FoFwd : ScalarAffine<S> {
   using Alg = ScalarAffine<S>;
   using typename Alg::Map;
   using typename Alg::State;
   using Partial = Pod<S, 1>;
-  using Params = FoFwdParams<S>;
+  using Params = FoFwdParams<G>;
   using Scalar = S;
-  static constexpr int V = Vec16<S>::V;
+  using C = Cvt<S, G>;
+  static constexpr int V = Vec16<G>::V;
   static constexpr int NT = 256;
   static constexpr int SPT = V * CH;
   static constexpr int TILE = NT * SPT;
@@ -113,28 +168,28 @@ struct FoFwd : ScalarAffine<S> {
   static constexpr bool REVERSE = false;
   static constexpr bool HAS_PARTIAL = false;
   static constexpr int SLOT_WORDS = Words<Map>::W;
-  static constexpr int SLOT = TILE * (int)sizeof(S);
+  static constexpr int SLOT = TILE * (int)sizeof(G);
   static constexpr int X_OFF = 0;
   static constexpr int A_OFF = SLOT;
   static constexpr int NROWC = LPV ? 0 : 1;                 // time-invariant: the row's coefficient
   static constexpr int ROWC_OFF = LPV ? 2 * SLOT : SLOT;
   static constexpr int STAGE_BYTES = ROWC_OFF + (LPV ? 0 : 128);
   static __device__ __forceinline__ void row_constants(const Params& p, int64_t row, S* out) {
-    out[0] = ld_ro(p.a + row * p.a_row_stride);
+    out[0] = C::in(ld_ro(p.a + row * p.a_row_stride));
   }
 
   static __device__ __forceinline__ void plan(const Params& p, bool, int64_t row, int64_t t0, int nvalid,
                                               IoPlan& io) {
-    const uint32_t bytes = (uint32_t)nvalid * sizeof(S);
+    const uint32_t bytes = (uint32_t)nvalid * sizeof(G);
     io.load(X_OFF, p.x + row * p.T + t0, bytes);
     if (LPV) io.load(A_OFF, p.a + row * p.a_row_stride + t0, bytes);
     io.store(X_OFF, p.y + row * p.T + t0, bytes);
   }
   static __device__ __forceinline__ State row_init(const Params& p, int64_t row) {
-    State s; s.v[0] = ld_ro(p.zi + row * p.zi_stride); return s;
+    State s; s.v[0] = C::in(ld_ro(p.zi + row * p.zi_stride)); return s;
   }
   static __device__ __forceinline__ void row_final(const Params& p, int64_t row, const State& s) {
-    if (p.zf) p.zf[row] = s.v[0];
+    if (p.zf) p.zf[row] = C::out(s.v[0]);
   }
 
   struct Regs {
@@ -148,13 +203,13 @@ struct FoFwd : ScalarAffine<S> {
       const int p0 = tpos * SPT;
       nv = nvalid - p0;
       nv = nv < 0 ? 0 : (nv > SPT ? SPT : nv);
-      const unsigned char* px = stage + X_OFF + (size_t)p0 * sizeof(S);
+      const unsigned char* px = stage + X_OFF + (size_t)p0 * sizeof(G);
 #pragma unroll
-      for (int c = 0; c < CH; ++c) VecIO<S, V>::ld(px + 16 * c, &x[c * V]);
+      for (int c = 0; c < CH; ++c) VecIO<G, V>::ld(px + 16 * c, &x[c * V]);
       if (LPV) {
-        const unsigned char* pa = stage + A_OFF + (size_t)p0 * sizeof(S);
+        const unsigned char* pa = stage + A_OFF + (size_t)p0 * sizeof(G);
 #pragma unroll
-        for (int c = 0; c < CH; ++c) VecIO<S, V>::ld(pa + 16 * c, &a[c * V]);
+        for (int c = 0; c < CH; ++c) VecIO<G, V>::ld(pa + 16 * c, &a[c * V]);
       } else {
         a[0] = *reinterpret_cast<const S*>(stage + ROWC_OFF);
       }
@@ -182,24 +237,24 @@ struct FoFwd : ScalarAffine<S> {
     S h = in.v[0];
 #pragma unroll
     for (int j = 0; j < SPT; ++j) { h = r.coef(j) * h + r.x[j]; r.x[j] = h; }
-    unsigned char* px = stage + X_OFF + (size_t)tpos * SPT * sizeof(S);
+    unsigned char* px = stage + X_OFF + (size_t)tpos * SPT * sizeof(G);
 #pragma unroll
-    for (int c = 0; c < CH; ++c) VecIO<S, V>::st(px + 16 * c, &r.x[c * V]);
+    for (int c = 0; c < CH; ++c) VecIO<G, V>::st(px + 16 * c, &r.x[c * V]);
     Partial out; out.v[0] = S(0); return out;
   }
 };
 
 // ------------------------------------------------------------------------------------ adjoint
-template <class S>
+template <class G, class S = G>
 struct FoBwdParams {
-  const S* a; int64_t a_row_stride;
-  const S* zi; int64_t zi_stride;
-  const S* y;        // forward output, needed only when grad_a is wanted
-  const S* gy;       // upstream gradient
-  const S* g_in;     // optional (B,): adjoint state entering from the right of the last sample
-  S* grad_x;
-  S* grad_a;         // LPV: (B,T) per-sample; LTI: unused here (partials go to the workspace)
-  S* grad_zi;        // optional (B,)
+  const G* a; int64_t a_row_stride;
+  const G* zi; int64_t zi_stride;
+  const G* y;        // forward output, needed only when grad_a is wanted
+  const G* gy;       // upstream gradient
+  const G* g_in;     // optional (B,): adjoint state entering from the right of the last sample
+  G* grad_x;
+  G* grad_a;         // LPV: (B,T) per-sample; LTI: unused here (partials go to the workspace)
+  G* grad_zi;        // optional (B,)
   int64_t T;
   int want_ga;
   S fuse_scale;      // FUSE: the kernel writes fuse_scale * (g + y - gy) instead of g (y = any second signal)
@@ -208,15 +263,16 @@ struct FoBwdParams {
 // FUSE (time-invariant use): the result of the reverse-time recurrence is combined with its own
 // input and one more signal on the way out, out[t] = fuse_scale * (g[t] + y[t] - gy[t]): the
 // symmetric two-pass filters (causal pass y, then this pass) need no separate combining pass.
-template <class S, int CH, int STAGES_, int MIN_CTAS_, int LBW_, bool LPV, bool FUSE = false>
+template <class S, int CH, int STAGES_, int MIN_CTAS_, int LBW_, bool LPV, bool FUSE = false, class G = S>
 struct FoBwd : ScalarAffine<S> {
   using Alg = ScalarAffine<S>;
   using typename Alg::Map;
   using typename Alg::State;
   using Partial = Pod<S, 1>;
-  using Params = FoBwdParams<S>;
+  using Params = FoBwdParams<G, S>;
   using Scalar = S;
-  static constexpr int V = Vec16<S>::V;
+  using C = Cvt<S, G>;
+  static constexpr int V = Vec16<G>::V;
   static constexpr int NT = 256;
   static constexpr int SPT = V * CH;
   static constexpr int TILE = NT * SPT;
@@ -226,7 +282,7 @@ struct FoBwd : ScalarAffine<S> {
   static constexpr bool REVERSE = true;
   static constexpr bool HAS_PARTIAL = !LPV;
   static constexpr int SLOT_WORDS = Words<Map>::W;
-  static constexpr int SLOT = TILE * (int)sizeof(S);
+  static constexpr int SLOT = TILE * (int)sizeof(G);
   static constexpr int G_OFF = 0;                       // gy in, grad_x out
   static constexpr int Y_OFF = SLOT;                    // y in (read-only)
   static constexpr int HALO_OFF = 2 * SLOT;             // 16 bytes ending with y[t0-1]
@@ -235,12 +291,12 @@ struct FoBwd : ScalarAffine<S> {
   static constexpr int ROWC_OFF = HALO_OFF + 64;         // second half of the halo line
   static constexpr int STAGE_BYTES = (LPV ? 3 * SLOT : 2 * SLOT) + 128;
   static __device__ __forceinline__ void row_constants(const Params& p, int64_t row, S* out) {
-    out[0] = ld_ro(p.a + row * p.a_row_stride);
+    out[0] = C::in(ld_ro(p.a + row * p.a_row_stride));
   }
 
   static __device__ __forceinline__ void plan(const Params& p, bool bulk, int64_t row, int64_t t0, int nvalid,
                                               IoPlan& io) {
-    const uint32_t bytes = (uint32_t)nvalid * sizeof(S);
+    const uint32_t bytes = (uint32_t)nvalid * sizeof(G);
     io.load(G_OFF, p.gy + row * p.T + t0, bytes);
     if (LPV) io.load(A_OFF, p.a + row * p.a_row_stride + t0, bytes);
     if (FUSE && !p.want_ga) io.load(Y_OFF, p.y + row * p.T + t0, bytes);
@@ -248,17 +304,17 @@ struct FoBwd : ScalarAffine<S> {
       io.load(Y_OFF, p.y + row * p.T + t0, bytes);
       if (t0 > 0) {
         if (bulk) io.load(HALO_OFF, p.y + row * p.T + t0 - V, 16);
-        else io.load(HALO_OFF + 16 - (int)sizeof(S), p.y + row * p.T + t0 - 1, sizeof(S));
+        else io.load(HALO_OFF + 16 - (int)sizeof(G), p.y + row * p.T + t0 - 1, sizeof(G));
       }
     }
     io.store(G_OFF, p.grad_x + row * p.T + t0, bytes);
     if (LPV && p.want_ga) io.store(A_OFF, p.grad_a + row * p.T + t0, bytes);
   }
   static __device__ __forceinline__ State row_init(const Params& p, int64_t row) {
-    State s; s.v[0] = p.g_in ? ld_ro(p.g_in + row) : S(0); return s;
+    State s; s.v[0] = p.g_in ? C::in(ld_ro(p.g_in + row)) : S(0); return s;
   }
   static __device__ __forceinline__ void row_final(const Params& p, int64_t row, const State& s) {
-    if (p.grad_zi) p.grad_zi[row] = s.v[0];
+    if (p.grad_zi) p.grad_zi[row] = C::out(s.v[0]);
   }
 
   struct Regs {
@@ -272,17 +328,17 @@ struct FoBwd : ScalarAffine<S> {
       const int p0 = tpos * SPT;
       nv = nvalid - p0;
       nv = nv < 0 ? 0 : (nv > SPT ? SPT : nv);
-      const unsigned char* pg = stage + G_OFF + (size_t)p0 * sizeof(S);
+      const unsigned char* pg = stage + G_OFF + (size_t)p0 * sizeof(G);
 #pragma unroll
-      for (int c = 0; c < CH; ++c) VecIO<S, V>::ld(pg + 16 * c, &g[c * V]);
+      for (int c = 0; c < CH; ++c) VecIO<G, V>::ld(pg + 16 * c, &g[c * V]);
       if (LPV) {
-        const unsigned char* pa = stage + A_OFF + (size_t)p0 * sizeof(S);
+        const unsigned char* pa = stage + A_OFF + (size_t)p0 * sizeof(G);
 #pragma unroll
-        for (int c = 0; c < CH; ++c) VecIO<S, V>::ld(pa + 16 * c, &a[c * V]);
+        for (int c = 0; c < CH; ++c) VecIO<G, V>::ld(pa + 16 * c, &a[c * V]);
 #pragma unroll
         for (int j = 0; j < SPT; ++j) a[j] = cj(a[j]);   // the adjoint runs on conj(a) (no-op for reals)
       } else {
-        a[0] = cj(*reinterpret_cast<const S*>(stage + ROWC_OFF));
+        a[0] = cj(*reinterpret_cast<const S*>(stage + ROWC_OFF));   // row constants are staged in S
       }
       if (nv < SPT) {
 #pragma unroll
@@ -309,17 +365,17 @@ struct FoBwd : ScalarAffine<S> {
     S y[SPT];
     S yprev = S(0);
     const int p0 = tpos * SPT;
-    unsigned char* py = stage + Y_OFF + (size_t)p0 * sizeof(S);
+    unsigned char* py = stage + Y_OFF + (size_t)p0 * sizeof(G);
     if (FUSE && !p.want_ga) {
 #pragma unroll
-      for (int c = 0; c < CH; ++c) VecIO<S, V>::ld(py + 16 * c, &y[c * V]);
+      for (int c = 0; c < CH; ++c) VecIO<G, V>::ld(py + 16 * c, &y[c * V]);
     }
     if (p.want_ga) {
 #pragma unroll
-      for (int c = 0; c < CH; ++c) VecIO<S, V>::ld(py + 16 * c, &y[c * V]);
-      if (tpos > 0) yprev = *reinterpret_cast<const S*>(py - sizeof(S));
-      else if (t0 > 0) yprev = *reinterpret_cast<const S*>(stage + HALO_OFF + 16 - sizeof(S));
-      else yprev = ld_ro(p.zi + row * p.zi_stride);
+      for (int c = 0; c < CH; ++c) VecIO<G, V>::ld(py + 16 * c, &y[c * V]);
+      if (tpos > 0) yprev = C::in(*reinterpret_cast<const G*>(py - sizeof(G)));
+      else if (t0 > 0) yprev = C::in(*reinterpret_cast<const G*>(stage + HALO_OFF + 16 - sizeof(G)));
+      else yprev = C::in(ld_ro(p.zi + row * p.zi_stride));
     }
     S c = in.v[0];
     S acc = S(0);
@@ -335,15 +391,15 @@ struct FoBwd : ScalarAffine<S> {
         else if (j < r.nv) acc += gj * yp;
       }
     }
-    unsigned char* pg = stage + G_OFF + (size_t)p0 * sizeof(S);
+    unsigned char* pg = stage + G_OFF + (size_t)p0 * sizeof(G);
 #pragma unroll
-    for (int c2 = 0; c2 < CH; ++c2) VecIO<S, V>::st(pg + 16 * c2, &r.g[c2 * V]);
+    for (int c2 = 0; c2 < CH; ++c2) VecIO<G, V>::st(pg + 16 * c2, &r.g[c2 * V]);
     if (LPV && p.want_ga) {
       // grad_a goes over this thread's own coefficients: the y slot stays read-only, because the
       // neighbouring thread reads its previous sample from it at an unsynchronised time
-      unsigned char* pa = stage + A_OFF + (size_t)p0 * sizeof(S);
+      unsigned char* pa = stage + A_OFF + (size_t)p0 * sizeof(G);
 #pragma unroll
-      for (int c2 = 0; c2 < CH; ++c2) VecIO<S, V>::st(pa + 16 * c2, &y[c2 * V]);
+      for (int c2 = 0; c2 < CH; ++c2) VecIO<G, V>::st(pa + 16 * c2, &y[c2 * V]);
     }
     Partial out; out.v[0] = acc; return out;
   }

@@ -40,59 +40,82 @@ template <class R_> struct RealOf<Cx<R_>> { using R = R_; static constexpr int N
 #define PTB_FOLTI_BWD_STAGES 3
 #define PTB_FOLTI_BWD_CTAS 1
 #endif
-template <class S, bool LPV> struct FoFwdSel { using type = FoFwd<S, PTB_FO_FWD_CH, PTB_FO_FWD_STAGES, PTB_FO_FWD_CTAS, 1, true>; };
-template <class S> struct FoFwdSel<S, false> { using type = FoFwd<S, PTB_FOLTI_FWD_CH, PTB_FOLTI_FWD_STAGES, PTB_FOLTI_FWD_CTAS, 1, false>; };
-template <class S, bool LPV> struct FoBwdSel { using type = FoBwd<S, PTB_FO_BWD_CH, PTB_FO_BWD_STAGES, PTB_FO_BWD_CTAS, 1, true>; };
-template <class S> struct FoBwdSel<S, false> { using type = FoBwd<S, PTB_FOLTI_BWD_CH, PTB_FOLTI_BWD_STAGES, PTB_FOLTI_BWD_CTAS, 1, false>; };
-template <class S, bool LPV> using FoFwdP = typename FoFwdSel<S, LPV>::type;
-template <class S, bool LPV> using FoBwdP = typename FoBwdSel<S, LPV>::type;
+template <class S, bool LPV, class G = S> struct FoFwdSel { using type = FoFwd<S, PTB_FO_FWD_CH, PTB_FO_FWD_STAGES, PTB_FO_FWD_CTAS, 1, true>; };
+template <class S> struct FoFwdSel<S, false, S> { using type = FoFwd<S, PTB_FOLTI_FWD_CH, PTB_FOLTI_FWD_STAGES, PTB_FOLTI_FWD_CTAS, 1, false>; };
+template <class S, bool LPV, class G = S> struct FoBwdSel { using type = FoBwd<S, PTB_FO_BWD_CH, PTB_FO_BWD_STAGES, PTB_FO_BWD_CTAS, 1, true>; };
+template <class S> struct FoBwdSel<S, false, S> { using type = FoBwd<S, PTB_FOLTI_BWD_CH, PTB_FOLTI_BWD_STAGES, PTB_FOLTI_BWD_CTAS, 1, false>; };
+// 2-byte storage (float16 / bfloat16 arrays, float32 arithmetic): a 16-byte unit holds 8 samples, so
+// fewer units per thread keep the register count of the fp32 kernels
+template <bool LPV> struct FoFwdSel<float, LPV, __half> { using type = FoFwd<float, LPV ? 5 : 7, 4, 1, 1, LPV, __half>; };
+template <bool LPV> struct FoFwdSel<float, LPV, __nv_bfloat16> { using type = FoFwd<float, LPV ? 5 : 7, 4, 1, 1, LPV, __nv_bfloat16>; };
+template <bool LPV> struct FoBwdSel<float, LPV, __half> { using type = FoBwd<float, LPV ? 3 : 5, 4, 1, 1, LPV, false, __half>; };
+template <bool LPV> struct FoBwdSel<float, LPV, __nv_bfloat16> { using type = FoBwd<float, LPV ? 3 : 5, 4, 1, 1, LPV, false, __nv_bfloat16>; };
+template <class S, bool LPV, class G = S> using FoFwdP = typename FoFwdSel<S, LPV, G>::type;
+template <class S, bool LPV, class G = S> using FoBwdP = typename FoBwdSel<S, LPV, G>::type;
 
-template <class S, bool LPV>
+// write-out of the per-row sums of a time-invariant gradient in the storage type
+template <class S, int N, class G>
+struct StoreSumsAs {
+  G* out;
+  __device__ void operator()(int64_t row, const double* acc) const {
+    for (int i = 0; i < N; ++i) out[row * N + i] = Cvt<S, G>::out((S)acc[i]);
+  }
+};
+
+template <class S, bool LPV, class G = S>
 static int fo_fwd(int64_t B, int64_t T, const void* a, int a_batched, const void* zi, int zi_batched,
                   const void* x, void* y, void* zf, void* ws, int64_t wsb, uint32_t* status, cudaStream_t st) {
-  using P = FoFwdP<S, LPV>;
+  using P = FoFwdP<S, LPV, G>;
   typename P::Params p;
-  p.a = static_cast<const S*>(a);
+  p.a = static_cast<const G*>(a);
   p.a_row_stride = a_batched ? (LPV ? T : 1) : 0;
-  p.zi = static_cast<const S*>(zi);
+  p.zi = static_cast<const G*>(zi);
   p.zi_stride = zi_batched ? 1 : 0;
-  p.x = static_cast<const S*>(x);
-  p.y = static_cast<S*>(y);
-  p.zf = static_cast<S*>(zf);
+  p.x = static_cast<const G*>(x);
+  p.y = static_cast<G*>(y);
+  p.zf = static_cast<G*>(zf);
   p.T = T;
-  const bool bulk = aligned16(x) && aligned16(y) && (!LPV || aligned16(a)) && (T * sizeof(S)) % 16 == 0;
+  const bool bulk = aligned16(x) && aligned16(y) && (!LPV || aligned16(a)) && (T * sizeof(G)) % 16 == 0;
+  // the plain-load path copies 32-bit words: arrays of 2-byte samples must qualify for bulk copies
+  if (!bulk && sizeof(G) < 4) return PTB_ERR_ARG;
   return launch_scan<P>(p, B, T, bulk, ws, wsb, status, st, nullptr, nullptr);
 }
 
-template <class S, bool LPV>
+template <class S, bool LPV, class G = S>
 static int fo_bwd(int64_t B, int64_t T, const void* a, int a_batched, const void* zi, int zi_batched,
                   const void* y, const void* gy, const void* g_in, void* grad_x, void* grad_a, void* grad_zi,
                   void* ws, int64_t wsb, uint32_t* status, cudaStream_t st) {
-  using P = FoBwdP<S, LPV>;
+  using P = FoBwdP<S, LPV, G>;
   typename P::Params p;
-  p.a = static_cast<const S*>(a);
+  p.a = static_cast<const G*>(a);
   p.a_row_stride = a_batched ? (LPV ? T : 1) : 0;
-  p.zi = static_cast<const S*>(zi);
+  p.zi = static_cast<const G*>(zi);
   p.zi_stride = zi_batched ? 1 : 0;
-  p.y = static_cast<const S*>(y);
-  p.gy = static_cast<const S*>(gy);
-  p.g_in = static_cast<const S*>(g_in);
-  p.grad_x = static_cast<S*>(grad_x);
-  p.grad_a = LPV ? static_cast<S*>(grad_a) : nullptr;
-  p.grad_zi = static_cast<S*>(grad_zi);
+  p.y = static_cast<const G*>(y);
+  p.gy = static_cast<const G*>(gy);
+  p.g_in = static_cast<const G*>(g_in);
+  p.grad_x = static_cast<G*>(grad_x);
+  p.grad_a = LPV ? static_cast<G*>(grad_a) : nullptr;
+  p.grad_zi = static_cast<G*>(grad_zi);
   p.T = T;
   p.want_ga = grad_a != nullptr;
   const bool bulk = aligned16(gy) && aligned16(grad_x) && (!LPV || aligned16(a)) &&
                     (!p.want_ga || (aligned16(y) && (!LPV || aligned16(grad_a)))) &&
-                    (T * sizeof(S)) % 16 == 0;
+                    (T * sizeof(G)) % 16 == 0;
+  if (!bulk && sizeof(G) < 4) return PTB_ERR_ARG;
   void* partial = nullptr;
   int64_t nchunks = 0;
   int rc = launch_scan<P>(p, B, T, bulk, ws, wsb, status, st, &partial, &nchunks);
   if (rc != PTB_OK) return rc;
-  if (!LPV && grad_a)
-    rc = launch_reduce<typename RealOf<S>::R, RealOf<S>::N>(
-        partial, B, nchunks, a_batched,
-        StoreSums<typename RealOf<S>::R, RealOf<S>::N>{static_cast<typename RealOf<S>::R*>(grad_a)}, st);
+  if (!LPV && grad_a) {
+    if constexpr (std::is_same<S, G>::value) {
+      rc = launch_reduce<typename RealOf<S>::R, RealOf<S>::N>(
+          partial, B, nchunks, a_batched,
+          StoreSums<typename RealOf<S>::R, RealOf<S>::N>{static_cast<typename RealOf<S>::R*>(grad_a)}, st);
+    } else {
+      rc = launch_reduce<S, 1>(partial, B, nchunks, a_batched, StoreSumsAs<S, 1, G>{static_cast<G*>(grad_a)}, st);
+    }
+  }
   return rc;
 }
 

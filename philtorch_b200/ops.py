@@ -39,15 +39,32 @@ def _dense(t: Tensor) -> Tensor:
 _LOW_PRECISION = (torch.float16, torch.bfloat16)
 
 
+def _two_byte_kernels_apply(args) -> bool:
+    """The first-order kernels read and write float16 / bfloat16 arrays directly (float32 arithmetic in
+    registers, 2 bytes per sample of traffic) when every array qualifies for bulk copies: one common
+    2-byte dtype, rows of a multiple of 8 samples, 16-byte aligned data."""
+    tensors = [a for a in args if isinstance(a, Tensor)]
+    if len({t.dtype for t in tensors}) != 1:
+        return False
+    for t in tensors:
+        if t.dim() >= 1 and t.shape[-1] % 8 != 0 and t.dim() == 2:
+            return False
+        if t.is_contiguous() and t.data_ptr() % 16 != 0:
+            return False
+    return True
+
+
 def _fp32_arithmetic(fn):
     """float16 / bfloat16 tensors (which the reference's first-order ops also dispatch,
     philtorch/csrc/lti_recur.cu:135-156): the recurrence is evaluated in float32 and every result is
     rounded once to the storage type, instead of rounding after every step as a 16-bit scan does.
-    The conversion passes are separate kernels here (a 2-byte storage variant of the tiles would
-    move 4 instead of ~20 bytes per sample)."""
+    Arrays that qualify (see ``_two_byte_kernels_apply``) go to the kernels as they are; others are
+    converted to float32 and back around the float32 kernels."""
     def wrapped(*args):
         low = next((a.dtype for a in args if isinstance(a, Tensor) and a.dtype in _LOW_PRECISION), None)
         if low is None:
+            return fn(*args)
+        if _two_byte_kernels_apply(args):
             return fn(*args)
         up = [a.float() if isinstance(a, Tensor) and a.dtype in _LOW_PRECISION else a for a in args]
         out = fn(*up)

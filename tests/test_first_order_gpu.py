@@ -204,3 +204,36 @@ def test_low_precision_storage(tag, dtype, eps):
     al = a.unsqueeze(1).expand(-1, x.shape[1]).contiguous()
     yl, _, _, _ = _run_fo("lpv", al, zi, x, gy)
     assert yl.dtype == dtype and rel_err(yl, y64) <= 1.01 * eps
+
+
+@pytest.mark.parametrize("dtype,eps", [(torch.float16, 2.0 ** -11), (torch.bfloat16, 2.0 ** -8)])
+@pytest.mark.parametrize("kind", ["lti", "lpv"])
+@pytest.mark.parametrize("T", [8, 20000, 65536])
+def test_two_byte_tile_storage(dtype, eps, kind, T):
+    """Rows of a multiple of 8 samples go through the kernels that stage and store 2-byte samples
+    (the others through a float32 copy): both routes agree with the float64 oracle on the same
+    16-bit inputs to one rounding, several tiles per row included."""
+    from philtorch_b200 import ops as ops_mod
+
+    B = 6
+    g = torch.Generator().manual_seed(T)
+    a = ((torch.rand(B, T, generator=g) * 1.6 - 0.8) if kind == "lpv" else (torch.rand(B, generator=g) * 1.6 - 0.8)).to(dtype)
+    zi = torch.randn(B, generator=g).to(dtype)
+    x, gy = torch.randn(B, T, generator=g).to(dtype), torch.randn(B, T, generator=g).to(dtype)
+    assert ops_mod._two_byte_kernels_apply((a.cuda(), zi.cuda(), x.cuda()))
+    y, ga, gzi, gx = _run_fo(kind, a, zi, x, gy)
+    assert y.dtype == dtype and ga.dtype == dtype and gzi.dtype == dtype and gx.dtype == dtype
+    fwd = cport.lti_recur if kind == "lti" else cport.recur1
+    bwd = cport.lti_recur_bwd if kind == "lti" else cport.recur1_bwd
+    y64 = fwd(a.double(), zi.double(), x.double())
+    # the adjoint reads the ROUNDED outputs, as any caller that keeps y in 16 bits does
+    ga64, gzi64, gx64 = bwd(a.double(), zi.double(), y.double().cpu(), gy.double())
+    assert rel_err(y, y64) <= 1.01 * eps and rel_err(gx, gx64) <= 1.01 * eps
+    assert rel_err(gzi, gzi64) <= 1.01 * eps
+    assert rel_err(ga, ga64) <= (1.01 * eps if kind == "lpv" else 4 * eps)
+    # the same call with a row length that is not a multiple of 8 takes the float32-copy route
+    if T > 8:
+        y2, *_ = _run_fo(kind, a[..., :T - 3].contiguous() if kind == "lpv" else a, zi, x[:, :T - 3].contiguous(),
+                         gy[:, :T - 3].contiguous())
+        assert rel_err(y2, y64[:, :T - 3]) <= 1.01 * eps
+    ptb.check_errors()
