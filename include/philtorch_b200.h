@@ -391,6 +391,28 @@ int ptb_modal_mix_bwd(int dtype, int64_t rows, int64_t M, int64_t N, const void*
                       int coef_batched, int real_out, const void* gy, void* grad_w, void* grad_w0, void* partial,
                       void* workspace, int64_t workspace_bytes, uint32_t* status, ptb_stream_t stream);
 
+/* ---- a state-space model with a scalar input and a real scalar output in its eigenbasis, fused ------
+ * The whole of philtorch/lti/ssm.py:590-850 (diag_state_space) for that case in one read of x and one
+ * write of y; the (rows, M, N) complex mode signals are never formed:
+ *   w_m[t] = lam_m w_m[t-1] + gain_m x[t],  w_m[-1] = w0_m;   y[t] = Re(sum_m coef_m w_m[t-1]) + d x[t].
+ * dtype PTB_F32 / PTB_F64 = the precision R of the real arrays x, y, d (rows,) (d may be NULL);
+ * lam, gain, coef, w0, wf are (rows, M) complex of that precision, 1 <= M <= 8.
+ * chk: (rows, ptb_modal_bank_tiles(M, N), M) complex; on return it holds the modes entering every
+ * tile, which the adjoint needs (keep it until then).  wf (may be NULL): the modes after the last
+ * sample.  Adjoint (gy real (rows, N); g_wf optional gradient of wf): grad_x (rows, N), grad_w0
+ * (rows, M); `partial` receives (rows, tiles, 6 M + 1) reals per tile: {grad_gain, grad_lam, grad_coef}
+ * as interleaved complex (M each) followed by grad_d -- the caller sums them over the tiles; `need`
+ * selects the parameter sums that are computed (bit 0 grad_gain, bit 1 grad_lam, bit 2 grad_coef); chk for
+ * the adjoint is a second scratch array of the same size as the forward one (fwd_chk). */
+int64_t ptb_modal_bank_tiles(int64_t M, int64_t N);
+int ptb_modal_bank_fwd(int dtype, int64_t rows, int64_t M, int64_t N, const void* x, const void* lam,
+                       const void* gain, const void* coef, const void* d, const void* w0, void* y, void* wf,
+                       void* chk, ptb_stream_t stream);
+int ptb_modal_bank_bwd(int dtype, int64_t rows, int64_t M, int64_t N, const void* x, const void* lam,
+                       const void* gain, const void* coef, const void* d, const void* fwd_chk, const void* gy,
+                       const void* g_wf, int need, void* grad_x, void* grad_w0, void* partial, void* chk,
+                       ptb_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -417,6 +417,34 @@ class ModalDrive(Function):
         return gx, ggain
 
 
+class ModalBank(Function):
+    """A real signal through M complex first-order modes and back into one real output, fused:
+    ``(x, lam, gain, coef, d, w0) -> (y, wf)`` with x (rows, N) real, lam / gain / coef / w0 (rows, M)
+    complex, d (rows,) real or None;  w_m[t] = lam_m w_m[t-1] + gain_m x[t],
+    y[t] = Re(sum_m coef_m w_m[t-1]) + d x[t], wf = w[:, :, N-1].  The scalar-in / real-scalar-out case
+    of ``diag_state_space`` without ever forming the (rows, M, N) mode signals.  First derivatives."""
+
+    @staticmethod
+    def forward(ctx: Any, x: Tensor, lam: Tensor, gain: Tensor, coef: Tensor, d: Optional[Tensor], w0: Tensor):
+        y, wf, chk = _ops.modal_bank(x, lam, gain, coef, d, w0)
+        ctx.has_d = d is not None
+        ctx.save_for_backward(x, lam, gain, coef, chk, *([d] if d is not None else []))
+        return y, wf
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx: Any, grad_y: Tensor, grad_wf: Tensor):
+        x, lam, gain, coef, chk, *rest = ctx.saved_tensors
+        d = rest[0] if rest else None
+        if grad_y is None:
+            grad_y = torch.zeros_like(x)
+        need = ctx.needs_input_grad
+        mask = (1 if need[2] else 0) | (2 if need[1] else 0) | (4 if need[3] else 0)
+        gx, glam, ggain, gcoef, gd, gw0 = _ops.modal_bank_bwd(x, lam, gain, coef, d, chk, grad_y, grad_wf, mask)
+        return (gx if need[0] else None, glam if need[1] else None, ggain if need[2] else None,
+                gcoef if need[3] else None, gd if (ctx.has_d and need[4]) else None, gw0 if need[5] else None)
+
+
 class CombFilter(Function):
     """y[t] = x[t] - a*y[t-delay] on the signal's own layout, (a, zi, x, delay) -> y; zi: None, (delay,)
     or (B, delay) in the reference's order (zi[..., k] = the output k+1 samples before the start)."""

@@ -12,7 +12,13 @@ from typing import Optional
 import torch
 from torch import Tensor
 
-from ..autograd import LTIMatrixRecurrence, LTIRecurrence, ModalDrive, ModalMix, matrix_recurrence_scalar_input
+from ..autograd import (LTIMatrixRecurrence, LTIRecurrence, ModalBank, ModalDrive, ModalMix,
+                        matrix_recurrence_scalar_input)
+from ..ops import MODAL_BANK_MAX_MODES
+
+# scalar-input / real-scalar-output models of up to eight modes take the fused kernels (first
+# derivatives only); False: always the composite route (mode signals in memory, any order of derivative)
+FUSED_MODAL_BANK = True
 
 __all__ = ["LTIMatrixRecurrence", "state_space_recursion", "state_space", "diag_state_space",
            "extension_backend_indicator"]
@@ -236,7 +242,7 @@ def diag_state_space(x: Tensor, L: Optional[Tensor] = None, V: Optional[Tensor] 
     elif zi.dim() == 1:
         zi = zi.unsqueeze(0).expand(batch_size, -1)
     cdt = torch.promote_types(torch.promote_types(L.dtype, Vinv.dtype), x.dtype)   # complex as soon as the basis is
-    Lc, Vc, Vic, xc, zc = L.to(cdt), V.to(cdt), Vinv.to(cdt), x.to(cdt), zi.to(cdt)
+    Lc, Vc, Vic, zc = L.to(cdt), V.to(cdt), Vinv.to(cdt), zi.to(cdt)
 
     # ---- into the eigenbasis: w0 = V^-1 zi, u[b, m, t] = (V^-1 B x[b, t])[m]
     w0 = (Vic @ zc.unsqueeze(-1)).squeeze(-1)                                   # (batch, M)
@@ -256,12 +262,27 @@ def diag_state_space(x: Tensor, L: Optional[Tensor] = None, V: Optional[Tensor] 
             features = -1 if x.dim() == 2 else x.size(-1)
             raise ValueError(f"Input matrix B must be of shape ({M},), ({batch_size}, {M}), ({M}, {features}) or "
                              f"({batch_size}, {M}, {features}), got {shp}")
+    if (FUSED_MODAL_BANK and x.dim() == 2 and x.is_cuda and x.dtype in (torch.float32, torch.float64)
+            and M <= MODAL_BANK_MAX_MODES and cdt == (torch.complex64 if x.dtype == torch.float32 else torch.complex128)
+            and tuple(G.shape) in ((M,), (batch_size, M)) and out_idx is None
+            and C is not None and not C.is_complex() and tuple(C.shape) in ((M,), (batch_size, M))
+            and (D is None or (not D.is_complex() and tuple(D.shape) in ((), (1,), (batch_size,))))):
+        # scalar in, real scalar out: ONE fused pass per direction over x / y; the (batch, M, N) modes
+        # are never formed (csrc/modal_bank.cuh)
+        Cc = C.to(cdt)
+        CV = Cc @ Vc if C.dim() == 1 else (Cc.unsqueeze(1) @ Vc).squeeze(1)
+        d = None if D is None else D.to(x.dtype).reshape(-1).expand(batch_size)
+        y, wf = ModalBank.apply(x, Lc.expand(batch_size, M), G.to(cdt).expand(batch_size, M),
+                                CV.expand(batch_size, M), d, w0)
+        if return_zf:
+            return y, (Vc @ wf.unsqueeze(-1)).squeeze(-1).real
+        return y
     if x.dim() == 2 and tuple(G.shape) in ((M,), (batch_size, M)) and G.is_complex():
         u = ModalDrive.apply(x, G)                       # (batch, M, N) without a transpose
     elif x.dim() == 2 and tuple(G.shape) in ((M,), (batch_size, M)):
-        u = G.unsqueeze(-1) * xc.unsqueeze(1)
+        u = G.unsqueeze(-1) * x.to(cdt).unsqueeze(1)
     else:
-        u = _input_map(xc, G, batch_size, M).mT
+        u = _input_map(x.to(cdt), G, batch_size, M).mT
     u = u.expand(batch_size, M, N).reshape(batch_size * M, N)
     poles = Lc.expand(batch_size, M).reshape(-1)
     w = LTIRecurrence.apply(poles, w0.reshape(-1).contiguous(), u).view(batch_size, M, N)

@@ -642,6 +642,87 @@ def _(w, w0, coef, gy, real_out, need_coef):
             torch.empty_like(coef) if need_coef else coef.new_empty(0))
 
 
+# =============================================================================== fused bank of modes
+_LIB.define("modal_bank(Tensor x, Tensor lam, Tensor gain, Tensor coef, Tensor? d, Tensor w0)"
+            " -> (Tensor, Tensor, Tensor)", tags=_TAGS)
+_LIB.define("modal_bank_bwd(Tensor x, Tensor lam, Tensor gain, Tensor coef, Tensor? d, Tensor chk, Tensor gy, "
+            "Tensor? g_wf, int need) -> (Tensor, Tensor, Tensor, Tensor, Tensor, Tensor)", tags=_TAGS)
+MODAL_BANK_MAX_MODES = 8
+
+
+def _cplx_of(dtype):
+    return torch.complex64 if dtype == torch.float32 else torch.complex128
+
+
+def _check_modal_bank(x, lam, gain, coef, d, w0) -> None:
+    torch._check(x.dim() == 2 and x.dtype in (torch.float32, torch.float64), lambda: "x must be real (rows, N).")
+    R, M = x.shape[0], lam.shape[-1]
+    torch._check(1 <= M <= MODAL_BANK_MAX_MODES, lambda: f"1..{MODAL_BANK_MAX_MODES} modes, got {M}.")
+    for name, t in (("lam", lam), ("gain", gain), ("coef", coef), ("w0", w0)):
+        torch._check(tuple(t.shape) == (R, M) and t.dtype == _cplx_of(x.dtype),
+                     lambda: f"{name} must be complex (rows, M) of x's precision.")
+    torch._check(d is None or (tuple(d.shape) == (R,) and d.dtype == x.dtype), lambda: "d must be real (rows,).")
+
+
+def _modal_bank(x, lam, gain, coef, d, w0):
+    """y[r,t] = Re(sum_m coef w_m[t-1]) + d x[t], w_m[t] = lam w_m[t-1] + gain x[t]; returns
+    (y, final modes, the modes entering every tile -- needed by the backward op)."""
+    _check_modal_bank(x, lam, gain, coef, d, w0)
+    dev = _lib.require_cuda(x, lam, gain, coef, d, w0)
+    R, N = x.shape
+    M = lam.shape[1]
+    x_c, lam_c, gain_c, coef_c, d_c, w0_c = x.contiguous(), _dense(lam), _dense(gain), _dense(coef), _opt(d), _dense(w0)
+    y = torch.empty_like(x_c)
+    wf = w0_c.clone()
+    chk = w0.new_empty(R, lib.ptb_modal_bank_tiles(M, max(N, 1)), M)
+    if R and N:
+        with torch.cuda.device(dev):
+            _lib.check(lib.ptb_modal_bank_fwd(_lib.dtype_code(x), R, M, N, ptr(x_c), ptr(lam_c), ptr(gain_c),
+                                              ptr(coef_c), ptr(d_c), ptr(w0_c), ptr(y), ptr(wf), ptr(chk),
+                                              torch.cuda.current_stream(dev).cuda_stream), "ptb_modal_bank_fwd")
+    return y, wf, chk
+
+
+def _modal_bank_bwd(x, lam, gain, coef, d, chk, gy, g_wf, need):
+    dev = _lib.require_cuda(x, lam, gain, coef, d, chk, gy, g_wf)
+    R, N = x.shape
+    M = lam.shape[1]
+    x_c, lam_c, gain_c, coef_c, d_c = x.contiguous(), _dense(lam), _dense(gain), _dense(coef), _opt(d)
+    gy_c, gwf_c, chk_c = gy.contiguous(), _opt(g_wf), chk.contiguous()
+    gx = torch.empty_like(x_c)
+    gw0 = torch.zeros_like(lam_c) if g_wf is None else gwf_c.clone()
+    nt = chk.shape[1]
+    part = x.new_zeros(R, nt, 6 * M + 1)
+    if R and N:
+        scratch = torch.empty_like(chk_c)
+        with torch.cuda.device(dev):
+            _lib.check(lib.ptb_modal_bank_bwd(_lib.dtype_code(x), R, M, N, ptr(x_c), ptr(lam_c), ptr(gain_c),
+                                              ptr(coef_c), ptr(d_c), ptr(chk_c), ptr(gy_c), ptr(gwf_c), int(need), ptr(gx),
+                                              ptr(gw0), ptr(part), ptr(scratch),
+                                              torch.cuda.current_stream(dev).cuda_stream), "ptb_modal_bank_bwd")
+    sums = part.sum(1)                                                    # (R, 6M + 1)
+    cz = torch.view_as_complex(sums[:, :6 * M].reshape(R, 3, M, 2).contiguous())
+    return gx, cz[:, 1].contiguous(), cz[:, 0].contiguous(), cz[:, 2].contiguous(), sums[:, 6 * M].contiguous(), gw0
+
+
+_LIB.impl("modal_bank", _modal_bank, "CUDA")
+_LIB.impl("modal_bank_bwd", _modal_bank_bwd, "CUDA")
+
+
+@torch.library.register_fake("philtorch_b200::modal_bank")
+def _(x, lam, gain, coef, d, w0):
+    _check_modal_bank(x, lam, gain, coef, d, w0)
+    nt = (x.shape[1] + (2048 if lam.shape[1] <= 4 else 1024) - 1) // (2048 if lam.shape[1] <= 4 else 1024)
+    return (torch.empty_like(x, memory_format=torch.contiguous_format), torch.empty_like(w0),
+            w0.new_empty(x.shape[0], max(nt, 1), lam.shape[1]))
+
+
+@torch.library.register_fake("philtorch_b200::modal_bank_bwd")
+def _(x, lam, gain, coef, d, chk, gy, g_wf, need):
+    return (torch.empty_like(x, memory_format=torch.contiguous_format), torch.empty_like(lam), torch.empty_like(lam),
+            torch.empty_like(lam), x.new_empty(x.shape[0]), torch.empty_like(lam))
+
+
 # =============================================================================== comb filter
 _LIB.define("comb(Tensor a, Tensor? zi, Tensor x, int delay) -> Tensor", tags=_TAGS)
 _LIB.define("comb_bwd(Tensor a, Tensor? zi, Tensor y, Tensor gy, int delay, bool need_a, bool need_zi)"
@@ -901,5 +982,6 @@ for _name in ("lti_recur", "lti_recur_bwd", "lpv_recur", "lpv_recur_bwd", "lti_r
               "recur2_sx", "lti_recur2_bwd", "recur2_bwd", "biquad_tdf2", "biquad_tdf2_bwd", "lpv_recur_carry", "lpv_recur_zero_carry",
               "sos_cascade", "sos_cascade_bwd", "lpv_biquad_df2", "lpv_biquad_df2_bwd",
               "lpv_biquad_tdf2", "lpv_biquad_tdf2_bwd", "comb", "comb_bwd", "lti_recur_reverse_fused",
-              "modal_mix", "modal_mix_bwd", "modal_drive", "recur_n", "lti_recur_n", "recur_n_adj"):
+              "modal_mix", "modal_mix_bwd", "modal_drive", "recur_n", "lti_recur_n", "recur_n_adj", "modal_bank",
+              "modal_bank_bwd"):
     _LIB.impl(_name, _no_backend(_name), "CPU")

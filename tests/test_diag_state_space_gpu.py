@@ -18,6 +18,16 @@ DEV = "cuda"
 DT = {"f32": torch.float32, "f64": torch.float64}
 
 
+@pytest.fixture(autouse=True, params=[True, False], ids=["fused-bank", "mode-signals"])
+def modal_route(request, monkeypatch):
+    """Scalar-in / real-scalar-out models run on the fused bank-of-modes kernels, everything else
+    (and every higher-order derivative) on the route that keeps the mode signals in memory: every
+    case here runs with the fused kernels enabled and disabled."""
+    from philtorch_b200.lti import ssm
+    monkeypatch.setattr(ssm, "FUSED_MODAL_BANK", request.param)
+    return request.param
+
+
 def _dev(g, *names):
     return [g[n].to(DEV) for n in names]
 
@@ -205,3 +215,41 @@ def test_modal_drive(dtype, gain_batched):
     ptb.check_errors()
     for got, ref in zip(outs[0], outs[1]):
         assert got.dtype == ref.dtype and rel_err(got, ref) <= (1e-5 if dtype == torch.float32 else 1e-12)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+@pytest.mark.parametrize("M,N,batch", [(1, 300, 3), (2, 2048, 2), (4, 5000, 5), (5, 1023, 3), (8, 4097, 2), (4, 70001, 4)])
+def test_fused_bank_matches_mode_signal_route(dtype, M, N, batch, modal_route):
+    """The fused kernels against the route that materialises the modes (itself pinned to the
+    reference's golden vectors above): outputs, final states and every gradient, with initial
+    states, a feed-through term and row lengths that end inside a tile and inside a thread."""
+    from philtorch_b200.lti import ssm
+    if not modal_route:
+        pytest.skip("compares the two routes itself")
+    import math
+    g = torch.Generator().manual_seed(M * 100 + N)
+    cdt = torch.complex64 if dtype == torch.float32 else torch.complex128
+    r = 0.6 + 0.39 * torch.rand(batch, M, generator=g, dtype=torch.float64)
+    th = 2 * math.pi * torch.rand(batch, M, generator=g, dtype=torch.float64)
+    L = torch.polar(r, th).to(cdt).to(DEV)
+    V = torch.view_as_complex(torch.randn(batch, M, M, 2, generator=g, dtype=torch.float64)).to(cdt).to(DEV)
+    V = V + 2 * torch.eye(M, device=DEV, dtype=cdt)
+    Bm = torch.randn(batch, M, generator=g, dtype=torch.float64).to(dtype).to(DEV)
+    Cm = torch.randn(batch, M, generator=g, dtype=torch.float64).to(dtype).to(DEV)
+    D = torch.randn(batch, generator=g, dtype=torch.float64).to(dtype).to(DEV)
+    zi = torch.randn(batch, M, generator=g, dtype=torch.float64).to(dtype).to(DEV)
+    x = torch.randn(batch, N, generator=g, dtype=torch.float64).to(dtype).to(DEV)
+    gy = torch.randn(batch, N, generator=g, dtype=torch.float64).to(dtype).to(DEV)
+    gzf = torch.randn(batch, M, generator=g, dtype=torch.float64).to(dtype).to(DEV)
+    res = []
+    for fused in (True, False):
+        ssm.FUSED_MODAL_BANK = fused
+        ins = [t.clone().requires_grad_() for t in (x, L, Bm, Cm, D, zi)]
+        y, zf = diag_state_space(ins[0], L=ins[1], V=V, B=ins[2], C=ins[3], D=ins[4], zi=ins[5])
+        res.append((y, zf) + torch.autograd.grad([y, zf], ins, [gy, gzf]))
+        if fused:
+            assert type(y.grad_fn).__name__ != "AddBackward0"    # the feed-through term is inside the kernel
+    t = tol(dtype) * 10
+    for name, a, b in zip(("y", "zf", "gx", "gL", "gB", "gC", "gD", "gzi"), *res):
+        assert a.shape == b.shape and rel_err(a, b) <= t, name
+    ptb.check_errors()
