@@ -138,8 +138,9 @@ def test_unsupported():
     b = torch.ones(4, device=DEV)
     a = torch.zeros(3, device=DEV)
     x = torch.randn(2, 50, device=DEV)
+    assert ptb.lti.lfilter(b, a, x).shape == x.shape   # order 3: the dense N x N kernels
     with pytest.raises(NotImplementedError):
-        ptb.lti.lfilter(b, a, x)                        # order 3
+        ptb.lti.lfilter(torch.ones(10, device=DEV), torch.zeros(9, device=DEV), x)   # order 9: beyond them
     with pytest.raises(NotImplementedError):
         ptb.lti.lfilter(b[:3], a[:2], x, form="df1")    # FIR-based form
     with pytest.raises(ValueError):

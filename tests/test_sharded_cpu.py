@@ -118,5 +118,7 @@ def test_auto_segments():
     assert auto_segments(8, 1 << 26, True) == 32
     assert auto_segments(256, 1 << 20, True) == 1
     assert auto_segments(8, 1 << 26, False) == 1
-    assert auto_segments(8, 1 << 22, True) == 4      # segments stay at least 2^20 samples long
-    assert auto_segments(8, 1 << 20, True) == 1
+    assert auto_segments(32, 1 << 20, True) == 8     # 256 kernel rows of 2^17 samples
+    assert auto_segments(64, 1 << 20, True) == 4
+    assert auto_segments(8, 1 << 22, True) == 32     # segments stay at least 2^17 samples long
+    assert auto_segments(8, 1 << 20, True) == 1      # small problems are launch-bound: no extra launches

@@ -199,12 +199,12 @@ def test_fixup_kernels_emulated_ranks(dtype, world, S, L, shared, slow_decay):
 def test_few_long_rows_take_the_segmented_path():
     """lpv.linear_recurrence cuts a handful of long rows into segments by itself (same values and
     gradients as the oracle; double backward still works through the differentiable form)."""
-    B, T = 2, 1 << 22
+    B, T = 4, 1 << 22
     w = workloads.long_first_order(B=B, T=T)
     a, x, gy = w["a"], w["x"], w["gy"]
     zi = torch.randn(B, generator=torch.Generator().manual_seed(3))
     from philtorch_b200.sharded import auto_segments
-    assert auto_segments(B, T, True) == 4
+    assert auto_segments(B, T, True) == 32
     ins = [t.to(DEV).requires_grad_() for t in (a, zi, x)]
     y = ptb.lpv.linear_recurrence(*ins)
     assert type(y.grad_fn).__name__.startswith("TimeShardedLPVRecurrence")
