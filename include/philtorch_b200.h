@@ -130,6 +130,17 @@ int ptb_lpv_recur_bwd(int dtype, int64_t B, int64_t T, const void* a, int a_batc
                       void* grad_a, void* grad_zi, void* workspace, int64_t workspace_bytes,
                       uint32_t* status, ptb_stream_t stream);
 
+/* The same adjoint for coefficients SHARED by the rows (a: (T,)), with the sum over the rows that the
+ * reference's rule takes afterwards (philtorch/__init__.py:62-65) done on the way out: every row's
+ * tiles of g[t]*y[t-1] are ADDED into the one grad_a (T,) by bulk reduce copies, so no (B,T) array of
+ * per-row gradients is written and read again.  grad_a must be zero on entry (it is accumulated
+ * into; the order of the additions is not fixed).  Needs rows that qualify for bulk copies (16-byte
+ * aligned arrays, T*sizeof a multiple of 16), else PTB_ERR_ARG: use ptb_lpv_recur_bwd and sum. */
+int ptb_lpv_recur_bwd_shared(int dtype, int64_t B, int64_t T, const void* a, const void* zi, int zi_batched,
+                             const void* y, const void* gy, const void* g_in, void* grad_x, void* grad_a,
+                             void* grad_zi, void* workspace, int64_t workspace_bytes, uint32_t* status,
+                             ptb_stream_t stream);
+
 /* ---- carry pass of a first-order scan whose time axis is split across devices --------------------
  * New with the time-sharded mode (the reference has no multi-device code).  Reads a shard's
  * coefficients and inputs once and returns, per row, the shard's total affine map

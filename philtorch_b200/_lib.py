@@ -48,6 +48,9 @@ for _n in ("ptb_lti_recur_bwd", "ptb_lpv_recur_bwd"):
     getattr(lib, _n).argtypes = _fo_bwd
     getattr(lib, _n).restype = _i32
 
+lib.ptb_lpv_recur_bwd_shared.argtypes = [_i32, _i64, _i64, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp] + _tail
+lib.ptb_lpv_recur_bwd_shared.restype = _i32
+
 _so_fwd = [_i32, _i64, _i64, _vp, _i32, _vp, _vp, _i32, _vp, _vp] + _tail
 _so_bwd = [_i32, _i64, _i64, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp] + _tail
 for _n in ("ptb_lti_recur2_fwd", "ptb_lpv_recur2_fwd"):

@@ -22,7 +22,7 @@ int cx_fo_fwd(int dtype, int lpv, int64_t B, int64_t T, const void* a, int a_bat
               const void* x, void* y, void* zf, void* ws, int64_t wsb, uint32_t* status, cudaStream_t st);
 int cx_fo_bwd(int dtype, int lpv, int64_t B, int64_t T, const void* a, int a_batched, const void* zi, int zi_batched,
               const void* y, const void* gy, const void* g_in, void* grad_x, void* grad_a, void* grad_zi, void* ws,
-              int64_t wsb, uint32_t* status, cudaStream_t st);
+              int64_t wsb, uint32_t* status, cudaStream_t st, int ga_shared = 0);
 }  // namespace ptb
 
 namespace ptb {
@@ -585,6 +585,20 @@ int ptb_lpv_recur_bwd(int dtype, int64_t B, int64_t T, const void* a, int a_batc
                                               workspace, workspace_bytes, status, (cudaStream_t)stream);
   PTB_DISPATCH(dtype, (fo_bwd<S, true>(B, T, a, a_batched, zi, zi_batched, y, gy, g_in, grad_x, grad_a,
                                        grad_zi, workspace, workspace_bytes, status, (cudaStream_t)stream)));
+}
+
+int ptb_lpv_recur_bwd_shared(int dtype, int64_t B, int64_t T, const void* a, const void* zi, int zi_batched,
+                             const void* y, const void* gy, const void* g_in, void* grad_x, void* grad_a,
+                             void* grad_zi, void* workspace, int64_t workspace_bytes, uint32_t* status,
+                             ptb_stream_t stream) {
+  if (B < 0 || T < 0) return PTB_ERR_ARG;
+  if (B == 0 || T == 0) return PTB_OK;
+  if (!a || !gy || !grad_x || !grad_a || !y || !zi) return PTB_ERR_ARG;
+  if (dtype == PTB_C64 || dtype == PTB_C128)
+    return cx_fo_bwd(dtype, 1, B, T, a, 0, zi, zi_batched, y, gy, g_in, grad_x, grad_a, grad_zi, workspace,
+                     workspace_bytes, status, (cudaStream_t)stream, 1);
+  PTB_DISPATCH(dtype, (fo_bwd<S, true>(B, T, a, 0, zi, zi_batched, y, gy, g_in, grad_x, grad_a, grad_zi, workspace,
+                                       workspace_bytes, status, (cudaStream_t)stream, true)));
 }
 
 #define PTB_SO_DISPATCH(dtype, FN, ...)                                                      \

@@ -21,10 +21,10 @@ int cx_fo_fwd(int dtype, int lpv, int64_t B, int64_t T, const void* a, int a_bat
 
 int cx_fo_bwd(int dtype, int lpv, int64_t B, int64_t T, const void* a, int a_batched, const void* zi, int zi_batched,
               const void* y, const void* gy, const void* g_in, void* grad_x, void* grad_a, void* grad_zi, void* ws,
-              int64_t wsb, uint32_t* status, cudaStream_t st) {
+              int64_t wsb, uint32_t* status, cudaStream_t st, int ga_shared) {
   if (lpv) {
     PTB_CX_DISPATCH(dtype, (fo_bwd<S, true>(B, T, a, a_batched, zi, zi_batched, y, gy, g_in, grad_x, grad_a, grad_zi,
-                                            ws, wsb, status, st)));
+                                            ws, wsb, status, st, ga_shared != 0)));
   }
   PTB_CX_DISPATCH(dtype, (fo_bwd<S, false>(B, T, a, a_batched, zi, zi_batched, y, gy, g_in, grad_x, grad_a, grad_zi,
                                            ws, wsb, status, st)));

@@ -15,6 +15,10 @@
 
 namespace ptb {
 
+// the real type a scalar is made of (complex sums add component-wise)
+template <class S> struct RealOfScalar { using type = S; };
+template <class R> struct RealOfScalar<Cx<R>> { using type = R; };
+
 template <class S, int N_>
 struct Pod {
   static constexpr int N = N_;
@@ -254,6 +258,8 @@ struct FoBwdParams {
   const G* g_in;     // optional (B,): adjoint state entering from the right of the last sample
   G* grad_x;
   G* grad_a;         // LPV: (B,T) per-sample; LTI: unused here (partials go to the workspace)
+  int64_t ga_row_stride;   // LPV: T, or 0 when the rows share one (T,) gradient array: tiles are then ADDED into it
+                           // by bulk reduce copies (bulk path only; the array must start at zero)
   G* grad_zi;        // optional (B,)
   int64_t T;
   int want_ga;
@@ -308,7 +314,9 @@ struct FoBwd : ScalarAffine<S> {
       }
     }
     io.store(G_OFF, p.grad_x + row * p.T + t0, bytes);
-    if (LPV && p.want_ga) io.store(A_OFF, p.grad_a + row * p.T + t0, bytes);
+    if (LPV && p.want_ga)
+      io.store(A_OFF, p.grad_a + row * p.ga_row_stride + t0, bytes,
+               p.ga_row_stride == 0 ? (int)sizeof(typename RealOfScalar<S>::type) : 0);
   }
   static __device__ __forceinline__ State row_init(const Params& p, int64_t row) {
     State s; s.v[0] = p.g_in ? C::in(ld_ro(p.g_in + row)) : S(0); return s;

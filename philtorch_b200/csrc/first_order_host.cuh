@@ -81,10 +81,12 @@ static int fo_fwd(int64_t B, int64_t T, const void* a, int a_batched, const void
   return launch_scan<P>(p, B, T, bulk, ws, wsb, status, st, nullptr, nullptr);
 }
 
+// ga_shared (per-sample coefficients only): grad_a is ONE (T,) array that every row adds its tile
+// into (TMA reduce copies); needs the bulk path and 4- or 8-byte scalars, else PTB_ERR_ARG.
 template <class S, bool LPV, class G = S>
 static int fo_bwd(int64_t B, int64_t T, const void* a, int a_batched, const void* zi, int zi_batched,
                   const void* y, const void* gy, const void* g_in, void* grad_x, void* grad_a, void* grad_zi,
-                  void* ws, int64_t wsb, uint32_t* status, cudaStream_t st) {
+                  void* ws, int64_t wsb, uint32_t* status, cudaStream_t st, bool ga_shared = false) {
   using P = FoBwdP<S, LPV, G>;
   typename P::Params p;
   p.a = static_cast<const G*>(a);
@@ -99,10 +101,12 @@ static int fo_bwd(int64_t B, int64_t T, const void* a, int a_batched, const void
   p.grad_zi = static_cast<G*>(grad_zi);
   p.T = T;
   p.want_ga = grad_a != nullptr;
+  p.ga_row_stride = ga_shared ? 0 : T;
   const bool bulk = aligned16(gy) && aligned16(grad_x) && (!LPV || aligned16(a)) &&
                     (!p.want_ga || (aligned16(y) && (!LPV || aligned16(grad_a)))) &&
                     (T * sizeof(G)) % 16 == 0;
   if (!bulk && sizeof(G) < 4) return PTB_ERR_ARG;
+  if (ga_shared && (!LPV || !bulk || sizeof(G) < 4)) return PTB_ERR_ARG;
   void* partial = nullptr;
   int64_t nchunks = 0;
   int rc = launch_scan<P>(p, B, T, bulk, ws, wsb, status, st, &partial, &nchunks);

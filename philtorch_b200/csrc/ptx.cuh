@@ -87,6 +87,18 @@ __device__ __forceinline__ void bulk_s2g(void* gdst, const void* smem_src, uint3
                "r"(smem_u32(smem_src)), "r"(bytes)
                : "memory");
 }
+// shared -> global with an element-wise ADD into the destination (the TMA unit performs the
+// read-modify-write): rows that share one gradient array accumulate into it without a second pass.
+__device__ __forceinline__ void bulk_s2g_add_f32(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(gdst),
+               "r"(smem_u32(smem_src)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_s2g_add_f64(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f64 [%0], [%1], %2;" ::"l"(gdst),
+               "r"(smem_u32(smem_src)), "r"(bytes)
+               : "memory");
+}
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // all prior groups of this thread have finished READING shared memory
 __device__ __forceinline__ void bulk_wait_read_all() {

@@ -135,12 +135,13 @@ struct IoPlan {
   uint32_t st_soff[kMaxIo];
   uint32_t st_bytes[kMaxIo];
   char* st_g[kMaxIo];
+  int st_add[kMaxIo];   // 0: plain store; 4 / 8: add into the destination as 4- / 8-byte floats (bulk path only)
   int nst;
   __device__ __forceinline__ void load(uint32_t soff, const void* g, uint32_t bytes) {
     ld_soff[nld] = soff; ld_g[nld] = static_cast<const char*>(g); ld_bytes[nld] = bytes; ++nld;
   }
-  __device__ __forceinline__ void store(uint32_t soff, void* g, uint32_t bytes) {
-    st_soff[nst] = soff; st_g[nst] = static_cast<char*>(g); st_bytes[nst] = bytes; ++nst;
+  __device__ __forceinline__ void store(uint32_t soff, void* g, uint32_t bytes, int add = 0) {
+    st_soff[nst] = soff; st_g[nst] = static_cast<char*>(g); st_bytes[nst] = bytes; st_add[nst] = add; ++nst;
   }
 };
 
@@ -430,7 +431,11 @@ scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, 
         unsigned char* stage = smem + s * P::STAGE_BYTES;
 #pragma unroll
         for (int i = 0; i < kMaxIo; ++i)
-          if (i < io.nst && io.st_bytes[i]) bulk_s2g(io.st_g[i], stage + io.st_soff[i], io.st_bytes[i]);
+          if (i < io.nst && io.st_bytes[i]) {
+            if (io.st_add[i] == 4) bulk_s2g_add_f32(io.st_g[i], stage + io.st_soff[i], io.st_bytes[i]);
+            else if (io.st_add[i] == 8) bulk_s2g_add_f64(io.st_g[i], stage + io.st_soff[i], io.st_bytes[i]);
+            else bulk_s2g(io.st_g[i], stage + io.st_soff[i], io.st_bytes[i]);
+          }
         bulk_commit();
         PTB_PROF_BEGIN(tr0);
         bulk_wait_read_all();   // the stage may be overwritten from here on

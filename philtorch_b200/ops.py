@@ -179,8 +179,15 @@ def _lpv_recur_bwd(a, zi, y, gy, g_in, need_a, need_zi):
     B, T = y.shape
     a_c, zi_c, y_c, gy_c, gin_c = _dense(a), _dense(zi), _dense(y), _dense(gy), _opt(g_in)
     gx = torch.empty_like(y_c)
-    ga_rows = torch.empty_like(y_c) if need_a else a.new_empty(0)   # per-row, (B,T)
     gzi = torch.empty_like(zi_c) if need_zi else zi.new_empty(0)
+    if (need_a and a.dim() == 1 and B and T and y.dtype not in _LOW_PRECISION
+            and (T * y.element_size()) % 16 == 0 and all(t.data_ptr() % 16 == 0 for t in (a_c, y_c, gy_c))):
+        # coefficients shared by the rows: the kernel adds every row's tile into the one (T,) gradient
+        ga = torch.zeros_like(a_c)
+        _lib.call(lib.ptb_lpv_recur_bwd_shared, dev, B, T, _lib.dtype_code(y, True), B, T, ptr(a_c), ptr(zi_c), 1,
+                  ptr(y_c), ptr(gy_c), ptr(gin_c), ptr(gx), ptr(ga), ptr(gzi) if need_zi else None)
+        return ga, gzi, gx
+    ga_rows = torch.empty_like(y_c) if need_a else a.new_empty(0)   # per-row, (B,T)
     if B and T:
         _lib.call(lib.ptb_lpv_recur_bwd, dev, B, T, _lib.dtype_code(y, True), B, T, ptr(a_c), int(a.dim() == 2),
                   ptr(zi_c), 1, ptr(y_c), ptr(gy_c), ptr(gin_c), ptr(gx),

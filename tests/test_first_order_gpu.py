@@ -237,3 +237,32 @@ def test_two_byte_tile_storage(dtype, eps, kind, T):
                          gy[:, :T - 3].contiguous())
         assert rel_err(y2, y64[:, :T - 3]) <= 1.01 * eps
     ptb.check_errors()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64, torch.complex64])
+@pytest.mark.parametrize("T", [20000, 20001, 64])
+def test_shared_coefficients_gradient_sum(dtype, T):
+    """Per-sample coefficients shared by the rows, a (T,): grad_a is the sum over the rows
+    (philtorch/__init__.py:62-65 of the reference).  Rows that qualify for bulk copies accumulate
+    into the one (T,) array inside the kernel (TMA reduce copies), others sum per-row gradients
+    afterwards: both against the oracle."""
+    B = 7
+    g = torch.Generator().manual_seed(T)
+    real = torch.float64 if dtype == torch.float64 else torch.float32
+
+    def rnd(*s):
+        v = torch.randn(*s, generator=g, dtype=torch.float64)
+        if dtype.is_complex:
+            v = torch.complex(v, torch.randn(*s, generator=g, dtype=torch.float64))
+        return v.to(dtype)
+
+    a = (rnd(T) * 0.4).contiguous()
+    zi, x, gy = rnd(B), rnd(B, T), rnd(B, T)
+    y, ga, gzi, gx = _run_fo("lpv", a, zi, x, gy)
+    y_ref = cport.recur1(a, zi, x)
+    ga_ref, gzi_ref, gx_ref = cport.recur1_bwd(a, zi, y_ref, gy)
+    t = tol(real)
+    assert ga.shape == (T,)
+    assert rel_err(y, y_ref) <= t and rel_err(gx, gx_ref) <= t and rel_err(gzi, gzi_ref) <= t
+    assert rel_err(ga, ga_ref) <= t * (10 if real == torch.float64 else 1)
+    ptb.check_errors()
