@@ -1061,6 +1061,73 @@ def run_callers(args):
 SEED_LPV = 1240
 
 
+def run_profile_case(args):
+    """Reduced cases for profiler captures (never a bench value): a few launches of one kernel family
+    on inputs larger than L2 but of a few hundred MB, so that a multi-pass capture ends in a minute.
+      biquad   one TDF-II section forward + backward, fp32, B=128, T=2^19
+      half     first-order per-sample recurrence on float16 arrays, forward + backward, B=64, T=2^20
+      modal    fused bank of 4 complex modes, forward + backward, B=32, T=2^20
+      dense    4x4 per-sample recurrence forward + adjoint scan, fp32, B=16, T=2^18
+      fixup    8 rows of 2^24 samples cut into 32 segments: zero-start scans, fold, fix-up, fp32"""
+    import math
+
+    import torch
+
+    import philtorch_b200 as ptb
+    from philtorch_b200 import workloads
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    ops = torch.ops.philtorch_b200
+    g = torch.Generator(device=dev).manual_seed(SEED_LPV + 9)
+    case = args.profile_case
+    if case == "biquad":
+        w = workloads.sos_cascade(B=128, T=1 << 19, sections=1, device=dev)
+        b, a, x, gy = w["b"][0], w["a"][0], w["x"], w["gy"]
+
+        def step():
+            y, _ = ops.biquad_tdf2(b, a, None, x)
+            return ops.biquad_tdf2_bwd(b, a, x, y, gy, None, True, False)
+    elif case == "half":
+        w = workloads.lpv_first_order(B=64, T=1 << 20, device=dev)
+        a, zi, x, gy = (w[k].half() for k in ("a", "zi", "x", "gy"))
+
+        def step():
+            y = ops.lpv_recur(a, zi, x)
+            return ops.lpv_recur_bwd(a, zi, y, gy, None, True, True)
+    elif case == "modal":
+        R, N, M = 32, 1 << 20, 4
+        lam = torch.polar(0.9 + 0.09 * torch.rand(R, M, device=dev, generator=g),
+                          2 * math.pi * torch.rand(R, M, device=dev, generator=g))
+        gain, coef, w0 = (torch.view_as_complex(torch.randn(R, M, 2, device=dev, generator=g)) for _ in range(3))
+        x, gy = torch.randn(R, N, device=dev, generator=g), torch.randn(R, N, device=dev, generator=g)
+
+        def step():
+            y, wf, chk = ops.modal_bank(x, lam, gain, coef, None, w0)
+            return ops.modal_bank_bwd(x, lam, gain, coef, None, chk, gy, None, 7)
+    elif case == "dense":
+        Bn, Tn, n = 16, 1 << 18, 4
+        A = torch.randn(Bn, Tn, n, n, device=dev, generator=g) * 0.25
+        zi = torch.randn(Bn, n, device=dev, generator=g)
+        x, gy = torch.randn(Bn, Tn, n, device=dev, generator=g), torch.randn(Bn, Tn, n, device=dev, generator=g)
+
+        def step():
+            y = ops.recur_n(A, zi, x)
+            return ops.recur_n_adj(A, gy, None, True)
+    elif case == "fixup":
+        w = workloads.long_first_order(B=8, T=1 << 24, device=dev)
+        a, x, gy = w["a"].requires_grad_(), w["x"].requires_grad_(), w["gy"]
+        zi = torch.zeros(8, device=dev, requires_grad=True)
+
+        def step():
+            return torch.autograd.grad(ptb.lpv.linear_recurrence(a, zi, x), (a, zi, x), gy)
+    else:
+        raise SystemExit(f"unknown profile case {case!r}")
+    ms = _time_steps(step, max(1, args.steps), args.warmup, dev)
+    ptb.check_errors(dev)
+    print(json.dumps({"profile_case": case, "ms_per_step": ms}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -1072,6 +1139,8 @@ def main():
     ap.add_argument("--kernels-only", action="store_true", help="skip the host-buffer and CPU legs")
     ap.add_argument("--no-configs", action="store_true", dest="no_configs",
                     help="headline workload only (skip the five-configuration / strong-scaling entries)")
+    ap.add_argument("--profile-case", default=None, dest="profile_case",
+                    help="reduced case for a profiler capture: biquad | half | modal | dense | fixup (one GPU)")
     ap.add_argument("--time-sharded", action="store_true",
                     help="secondary workload: B=8 long rows split along time over the ranks")
     ap.add_argument("--log2-T", type=int, default=28, dest="log2_T", help="total row length of --time-sharded")
@@ -1094,6 +1163,10 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference_arm(args, rank)
+        return
+    if args.profile_case:
+        if rank == 0:
+            run_profile_case(args)
         return
     secondary = [fn for flag, fn in ((args.sos_cascade, run_sos_cascade), (args.state_space, run_state_space),
                                      (args.lpv_lfilter, run_lpv_lfilter), (args.complex_poles, run_complex_poles),
