@@ -58,7 +58,7 @@ static int bank_fwd(BankParams<R> p, cudaStream_t st) {
   const unsigned grid = (unsigned)(p.rows * ((p.ntiles + p.run - 1) / p.run));
   bank_aggregate_kernel<R, MMAX, false><<<grid, kBankNT, 0, st>>>(p);
   PTB_CUDA(cudaGetLastError());
-  bank_fold_kernel<R, false><<<(unsigned)((p.rows * p.M + 127) / 128), 128, 0, st>>>(p, C::TILE);
+  bank_fold_kernel<R, false><<<(unsigned)((p.rows * p.M * 32 + 127) / 128), 128, 0, st>>>(p, C::TILE);
   PTB_CUDA(cudaGetLastError());
   bank_forward_kernel<R, MMAX><<<grid, kBankNT, 0, st>>>(p);
   PTB_CUDA(cudaGetLastError());
@@ -71,7 +71,7 @@ static int bank_bwd(BankParams<R> p, cudaStream_t st) {
   const unsigned grid = (unsigned)(p.rows * ((p.ntiles + p.run - 1) / p.run));
   bank_aggregate_kernel<R, MMAX, true><<<grid, kBankNT, 0, st>>>(p);
   PTB_CUDA(cudaGetLastError());
-  bank_fold_kernel<R, true><<<(unsigned)((p.rows * p.M + 127) / 128), 128, 0, st>>>(p, C::TILE);
+  bank_fold_kernel<R, true><<<(unsigned)((p.rows * p.M * 32 + 127) / 128), 128, 0, st>>>(p, C::TILE);
   PTB_CUDA(cudaGetLastError());
   constexpr int smem = MMAX * C::SPT * kBankNT * (int)sizeof(Cx<R>);   // the tile's forward states
   static bool attr_set[kMaxDevices] = {};

@@ -46,10 +46,16 @@ template <class S, bool LPV, class G = S> struct FoBwdSel { using type = FoBwd<S
 template <class S> struct FoBwdSel<S, false, S> { using type = FoBwd<S, PTB_FOLTI_BWD_CH, PTB_FOLTI_BWD_STAGES, PTB_FOLTI_BWD_CTAS, 1, false>; };
 // 2-byte storage (float16 / bfloat16 arrays, float32 arithmetic): a 16-byte unit holds 8 samples, so
 // fewer units per thread keep the register count of the fp32 kernels
-template <bool LPV> struct FoFwdSel<float, LPV, __half> { using type = FoFwd<float, LPV ? 5 : 7, 4, 1, 1, LPV, __half>; };
-template <bool LPV> struct FoFwdSel<float, LPV, __nv_bfloat16> { using type = FoFwd<float, LPV ? 5 : 7, 4, 1, 1, LPV, __nv_bfloat16>; };
-template <bool LPV> struct FoBwdSel<float, LPV, __half> { using type = FoBwd<float, LPV ? 3 : 5, 4, 1, 1, LPV, false, __half>; };
-template <bool LPV> struct FoBwdSel<float, LPV, __nv_bfloat16> { using type = FoBwd<float, LPV ? 3 : 5, 4, 1, 1, LPV, false, __nv_bfloat16>; };
+#ifndef PTB_FOH_FWD_CH
+#define PTB_FOH_FWD_CH 7       // 14336-sample tiles, 28 KB per array (5 units: 0.307 ms, 7 units: 0.267 ms at B=256, T=2^20)
+#define PTB_FOH_FWD_STAGES 3
+#define PTB_FOH_BWD_CH 5       // 10240-sample tiles, 20 KB per array (3 units: 0.481 ms, 5 units: 0.404 ms)
+#define PTB_FOH_BWD_STAGES 3
+#endif
+template <bool LPV> struct FoFwdSel<float, LPV, __half> { using type = FoFwd<float, LPV ? PTB_FOH_FWD_CH : PTB_FOH_FWD_CH + 2, PTB_FOH_FWD_STAGES, 1, 1, LPV, __half>; };
+template <bool LPV> struct FoFwdSel<float, LPV, __nv_bfloat16> { using type = FoFwd<float, LPV ? PTB_FOH_FWD_CH : PTB_FOH_FWD_CH + 2, PTB_FOH_FWD_STAGES, 1, 1, LPV, __nv_bfloat16>; };
+template <bool LPV> struct FoBwdSel<float, LPV, __half> { using type = FoBwd<float, LPV ? PTB_FOH_BWD_CH : PTB_FOH_BWD_CH + 2, PTB_FOH_BWD_STAGES, 1, 1, LPV, false, __half>; };
+template <bool LPV> struct FoBwdSel<float, LPV, __nv_bfloat16> { using type = FoBwd<float, LPV ? PTB_FOH_BWD_CH : PTB_FOH_BWD_CH + 2, PTB_FOH_BWD_STAGES, 1, 1, LPV, false, __nv_bfloat16>; };
 template <class S, bool LPV, class G = S> using FoFwdP = typename FoFwdSel<S, LPV, G>::type;
 template <class S, bool LPV, class G = S> using FoBwdP = typename FoBwdSel<S, LPV, G>::type;
 

@@ -240,38 +240,49 @@ __global__ void __launch_bounds__(kBankNT) bank_aggregate_kernel(const BankParam
 }
 
 // ---- step B: aggregates -> states entering every tile, in place (double arithmetic) ----------------
+// One warp per (row, mode): 32 consecutive tiles per step, scanned with the powers b^(2^d) of
+// b = lam^TILE; the carry moves on by b^32.
 template <class R, bool ADJ>
 __global__ void bank_fold_kernel(const BankParams<R> p, int tile_len) {
-  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t idx = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
   if (idx >= p.rows * p.M) return;
   const int64_t row = idx / p.M, m = idx % p.M;
   const Cx<R> l = p.lam[idx];
   Cx<double> b((double)l.re, ADJ ? -(double)l.im : (double)l.im);
   for (int s = 1; s < tile_len; s <<= 1) b = b * b;   // lam^TILE
+  Cx<double> pd[5];
+  Cx<double> blane(1.0, 0.0);                          // b^lane
+#pragma unroll
+  for (int d = 0; d < 5; ++d) {
+    pd[d] = b;
+    if (lane & (1 << d)) blane = blane * b;
+    b = b * b;
+  }
+  const Cx<double> b32 = b;
   Cx<double> st(0.0, 0.0);
   if (!ADJ && p.w0) { const Cx<R> z = p.w0[idx]; st = Cx<double>((double)z.re, (double)z.im); }
   Cx<R>* c = p.chk + row * p.ntiles * p.M + m;
-  constexpr int U = 8;   // aggregates fetched together: their latency would otherwise serialise the walk
-  for (int64_t k0 = 0; k0 < p.ntiles; k0 += U) {
-    Cx<R> agg[U];
+  for (int64_t k0 = 0; k0 < p.ntiles; k0 += 32) {
+    const int64_t k = k0 + lane;
+    const int64_t tile = ADJ ? p.ntiles - 1 - k : k;       // the adjoint walks the tiles from the last one
+    Cx<double> a(0.0, 0.0);
+    if (k < p.ntiles) { const Cx<R> g = c[tile * p.M]; a = Cx<double>((double)g.re, (double)g.im); }
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int64_t k = k0 + u;
-      const int64_t tile = ADJ ? p.ntiles - 1 - k : k;     // the adjoint walks the tiles from the last one
-      agg[u] = k < p.ntiles ? c[tile * p.M] : Cx<R>(R(0));
+    for (int d = 0; d < 5; ++d) {
+      const Cx<double> o = shfl_up_s(a, 1 << d);
+      if (lane >= (1 << d)) a = a + pd[d] * o;
     }
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int64_t k = k0 + u;
-      if (k < p.ntiles) {
-        const int64_t tile = ADJ ? p.ntiles - 1 - k : k;
-        c[tile * p.M] = Cx<R>((R)st.re, (R)st.im);
-        st = b * st + Cx<double>((double)agg[u].re, (double)agg[u].im);
-      }
-    }
+    Cx<double> e = shfl_up_s(a, 1);
+    if (lane == 0) e = Cx<double>(0.0, 0.0);
+    const Cx<double> sin = blane * st + e;                 // the state entering tile k
+    if (k < p.ntiles) c[tile * p.M] = Cx<R>((R)sin.re, (R)sin.im);
+    const int64_t rem = p.ntiles - k0;
+    const Cx<double> full = b32 * st + shfl_s(a, 31);      // after 32 tiles
+    st = rem < 32 ? shfl_s(sin, (int)rem) : full;          // after the row's last tile when the step is ragged
   }
   // the state after the whole (zero-padded) row; only the adjoint uses it: r[0] = grad_w0
-  if (ADJ && p.wf) p.wf[idx] = Cx<R>((R)st.re, (R)st.im);
+  if (ADJ && p.wf && lane == 0) p.wf[idx] = Cx<R>((R)st.re, (R)st.im);
 }
 
 // State entering this thread, given the state entering the tile (z_tile), the scan's exclusive
