@@ -301,6 +301,19 @@ def config1(dev, steps, warmup, rows=64, shard=0, parity=True):
 
     ms_raw = _time_steps(raw, steps, warmup, dev)
     ms_graph = _graph_ms(raw, dev)
+
+    class Floor(torch.autograd.Function):   # the same call pattern with no kernel behind it
+        @staticmethod
+        def forward(ctx, a_, zi_, x_):
+            ctx.save_for_backward(a_, zi_, x_)
+            return torch.empty_like(x_)
+
+        @staticmethod
+        def backward(ctx, g):
+            a_, _, _ = ctx.saved_tensors
+            return torch.empty_like(a_), None, torch.empty_like(g)
+
+    ms_floor = _time_steps(lambda: torch.autograd.grad(Floor.apply(a, zi, x), (a, x), gy), steps, warmup, dev)
     par = None
     if parity:
         from oracle import cport, refext
@@ -315,8 +328,10 @@ def config1(dev, steps, warmup, rows=64, shard=0, parity=True):
         par = P.result()
     return _entry(f"LTI first-order linear_recurrence fwd+bwd (grads x, a), fp32, B={rows}, T=65536",
                   "lti.linear_recurrence + autograd.grad (eager)", rows * Tc, ms, 20, par,
-                  eager_ops_ms=ms_raw, cuda_graph_ms=ms_graph,
-                  note="84 MB in total: launch- and latency-bound; cuda_graph_ms = the two ops replayed from a CUDA graph",
+                  eager_ops_ms=ms_raw, cuda_graph_ms=ms_graph, torch_autograd_floor_ms=ms_floor,
+                  note="84 MB in total: launch- and latency-bound; cuda_graph_ms = the two ops replayed from a CUDA "
+                       "graph; torch_autograd_floor_ms = an autograd.Function that only allocates its outputs, "
+                       "called and differentiated the same way (host time of torch itself)",
                   **({"parity_against": _oracle_kind() + " at full size"} if parity else {}))
 
 

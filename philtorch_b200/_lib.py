@@ -178,8 +178,14 @@ def status_word(device: torch.device) -> torch.Tensor:
     return s
 
 
+_ws_bytes: dict = {}
+
+
 def workspace(B: int, T: int, device: torch.device) -> torch.Tensor:
-    return torch.empty(lib.ptb_workspace_bytes(B, T), dtype=torch.uint8, device=device)
+    n = _ws_bytes.get((B, T))
+    if n is None:
+        n = _ws_bytes[(B, T)] = lib.ptb_workspace_bytes(B, T)
+    return torch.empty(n, dtype=torch.uint8, device=device)
 
 
 def ptr(t):
@@ -194,18 +200,26 @@ def check(rc: int, what: str) -> None:
         raise RuntimeError(f"{what}: {msg}")
 
 
+_current_device = torch._C._cuda_getDevice                # both skip the Python layers of torch.cuda.*:
+_current_raw_stream = torch._C._cuda_getCurrentRawStream  # this function runs once per kernel launch
+
+
 def call(fn, device: torch.device, B: int, T: int, *args, ws_bytes: int = -1) -> None:
     """Runs ``fn(*args, workspace, bytes, status, stream)`` on ``device``'s current stream."""
     ws = workspace(B, T, device) if ws_bytes < 0 else torch.empty(ws_bytes, dtype=torch.uint8, device=device)
-    st = status_word(device)
-    if device.index is not None and device.index != torch.cuda.current_device():
-        with torch.cuda.device(device):
-            rc = fn(*args, ws.data_ptr(), ws.numel(), st.data_ptr(),
-                    torch.cuda.current_stream(device).cuda_stream)
+    idx = device.index
+    if idx is None:
+        idx = _current_device()
+    st = _status.get(idx)
+    if st is None:
+        st = status_word(device)
+    if idx != _current_device():
+        with torch.cuda.device(idx):
+            rc = fn(*args, ws.data_ptr(), ws.numel(), st.data_ptr(), _current_raw_stream(idx))
     else:
-        rc = fn(*args, ws.data_ptr(), ws.numel(), st.data_ptr(),
-                torch.cuda.current_stream(device).cuda_stream)
-    check(rc, fn.__name__)
+        rc = fn(*args, ws.data_ptr(), ws.numel(), st.data_ptr(), _current_raw_stream(idx))
+    if rc != 0:
+        check(rc, fn.__name__)
     if CHECK_EVERY_CALL:
         check_errors(device)
 

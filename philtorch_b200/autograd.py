@@ -36,15 +36,14 @@ def _none_if_empty(t: Tensor, needed: bool) -> Optional[Tensor]:
 class LTIRecurrence(Function):
     """y[t] = a*y[t-1] + x[t] with a of shape (), (1,) or (B,)."""
 
+    # forward takes the context itself (no separate setup_context): Function.apply then skips binding
+    # the arguments to forward's signature on every call, ~10 us of host time per application
     @staticmethod
-    def forward(a: Tensor, init: Tensor, x: Tensor) -> Tensor:
-        return _ops.lti_recur(a, init, x)
-
-    @staticmethod
-    def setup_context(ctx: Any, inputs, output) -> None:
-        a, init, _ = inputs
+    def forward(ctx: Any, a: Tensor, init: Tensor, x: Tensor) -> Tensor:
+        output = _ops.lti_recur(a, init, x)
         ctx.save_for_backward(a, init, output)
         ctx.save_for_forward(a, init, output)
+        return output
 
     @staticmethod
     def backward(ctx: Any, grad_out: Tensor):
@@ -118,14 +117,11 @@ class LPVRecurrence(Function):
     """y[t] = a[t]*y[t-1] + x[t] with a of shape (T,) or (B,T)."""
 
     @staticmethod
-    def forward(a: Tensor, init: Tensor, x: Tensor) -> Tensor:
-        return _ops.lpv_recur(a, init, x)
-
-    @staticmethod
-    def setup_context(ctx: Any, inputs, output) -> None:
-        a, init, _ = inputs
+    def forward(ctx: Any, a: Tensor, init: Tensor, x: Tensor) -> Tensor:   # context in forward: see LTIRecurrence
+        output = _ops.lpv_recur(a, init, x)
         ctx.save_for_backward(a, init, output)
         ctx.save_for_forward(a, init, output)
+        return output
 
     @staticmethod
     def backward(ctx: Any, grad_out: Tensor):

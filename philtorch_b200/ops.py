@@ -33,6 +33,8 @@ def _same_dtype(a: Tensor, zi: Tensor, x: Tensor) -> None:
 
 def _dense(t: Tensor) -> Tensor:
     """Dense memory holding the tensor's VALUES (a lazily conjugated complex view is materialised)."""
+    if t.is_contiguous() and not t.is_conj():
+        return t
     return t.resolve_conj().contiguous()
 
 
