@@ -698,9 +698,13 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     t_end.record()
     barrier()
     ms_total = t_start.elapsed_time(t_end)
-    for _ in range(40):   # keep the device under the same load a little longer: more clock samples
-        step()
-    torch.cuda.synchronize(dev)
+    # keep the device under the same load for about a second more: tens of clock samples instead
+    # of the two or three that fit into the timed region itself
+    t_load = time.perf_counter()
+    while time.perf_counter() - t_load < 1.0:
+        for _ in range(20):
+            step()
+        torch.cuda.synchronize(dev)
     clocks = sampler.stop() if sampler else None
     ptb.check_errors(dev)
     fwd_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in evs)

@@ -255,6 +255,17 @@ int ptb_lpv_recur2_bwd(int dtype, int64_t B, int64_t T, const void* A, int A_bat
                        void* grad_A, void* grad_zi, void* workspace, int64_t workspace_bytes,
                        uint32_t* status, ptb_stream_t stream);
 
+/* The same adjoint for matrices SHARED by the rows (A: (T,2,2)), with the sum over the rows that the
+ * reference's rule takes afterwards (philtorch/__init__.py:62-65) done on the way out: every row ADDS
+ * its tiles of g[t] (x) y[t-1] into the one grad_A (T,2,2) by bulk reduce copies.  grad_A must be zero
+ * on entry (the order of the additions is not fixed).  Needs arrays that qualify for bulk copies
+ * (16-byte aligned, row length in bytes a multiple of 16), else PTB_ERR_ARG: use ptb_lpv_recur2_bwd
+ * and sum. */
+int ptb_lpv_recur2_bwd_shared(int dtype, int64_t B, int64_t T, const void* A, const void* zi, const void* y,
+                              const void* gy, const void* g_in, int x_scalar, void* grad_x, void* grad_A,
+                              void* grad_zi, void* workspace, int64_t workspace_bytes, uint32_t* status,
+                              ptb_stream_t stream);
+
 /* ---- dense N x N recurrences, 2 < N <= 8 ---------------------------------------------------------
  * Replace ops philtorch::recurN / philtorch::lti_recurN for state dimensions above two
  * (philtorch/csrc/host_recur2.cpp:165,168; CPU kernels philtorch/csrc/host_recurN.cpp:81-140,236-281 and

@@ -59,6 +59,8 @@ for _n in ("ptb_lti_recur2_fwd", "ptb_lpv_recur2_fwd"):
 for _n in ("ptb_lti_recur2_bwd", "ptb_lpv_recur2_bwd"):
     getattr(lib, _n).argtypes = _so_bwd
     getattr(lib, _n).restype = _i32
+lib.ptb_lpv_recur2_bwd_shared.argtypes = [_i32, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp] + _tail
+lib.ptb_lpv_recur2_bwd_shared.restype = _i32
 lib.ptb_biquad_tdf2_fwd.argtypes = [_i32, _i64, _i64, _vp, _vp, _i32, _vp, _vp, _vp, _vp] + _tail
 lib.ptb_biquad_tdf2_fwd.restype = _i32
 lib.ptb_biquad_tdf2_bwd.argtypes = [_i32, _i64, _i64, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp] + _tail

@@ -161,7 +161,7 @@ template <> struct SoSmallBwdSel<double> { using C = LpvBqCfg<double, PTB_SO_SMA
 template <class S, bool XS>
 static int so_small_bwd(int64_t B, int64_t T, const void* A, int A_batched, const void* zi, const void* y,
                         const void* gy, const void* g_in, void* grad_x, void* grad_A, void* grad_zi, void* ws,
-                        int64_t wsb, uint32_t* status, cudaStream_t st) {
+                        int64_t wsb, uint32_t* status, cudaStream_t st, bool gA_shared = false) {
   using C = typename SoSmallBwdSel<S>::C;
   using L = SoSmallBwdSmem<C, XS>;
   static_assert(C::TILE >= kMinTile && C::SLOT_WORDS * 8 <= kTileRecordBytes, "generic workspace bound");
@@ -189,8 +189,10 @@ static int so_small_bwd(int64_t B, int64_t T, const void* A, int A_batched, cons
   p.grad_A = static_cast<S*>(grad_A);
   p.grad_zi = static_cast<S*>(grad_zi);
   p.T = T;
+  p.gA_shared = gA_shared ? 1 : 0;
   const bool bulk = aligned16(gy) && aligned16(grad_x) && aligned16(A) &&
                     (!grad_A || (aligned16(y) && aligned16(grad_A))) && (T * (XS ? 1 : 2) * sizeof(S)) % 16 == 0;
+  if (gA_shared && !bulk) return PTB_ERR_ARG;
   static bool attr_set[kMaxDevices] = {};
   static int grid_max[kMaxDevices] = {};
   int dev = 0;
@@ -238,10 +240,12 @@ static int so_fwd(int64_t B, int64_t T, const void* A, int A_batched, const void
 template <class S, bool LPV, bool XS>
 static int so_bwd(int64_t B, int64_t T, const void* A, int A_batched, const void* zi, const void* y,
                   const void* gy, const void* g_in, void* grad_x, void* grad_A, void* grad_zi, void* ws,
-                  int64_t wsb, uint32_t* status, cudaStream_t st) {
+                  int64_t wsb, uint32_t* status, cudaStream_t st, bool gA_shared = false) {
+  if (gA_shared && (!LPV || A_batched || !grad_A)) return PTB_ERR_ARG;
   if constexpr (LPV) {
-    if (B >= g_so_small_min_rows && (grad_A == nullptr || A_batched))
-      return so_small_bwd<S, XS>(B, T, A, A_batched, zi, y, gy, g_in, grad_x, grad_A, grad_zi, ws, wsb, status, st);
+    if (B >= g_so_small_min_rows && (grad_A == nullptr || A_batched || gA_shared))
+      return so_small_bwd<S, XS>(B, T, A, A_batched, zi, y, gy, g_in, grad_x, grad_A, grad_zi, ws, wsb, status, st,
+                                 gA_shared);
   }
   using P = SoBwdP<S, LPV, XS>;
   typename P::Params p;
@@ -257,9 +261,11 @@ static int so_bwd(int64_t B, int64_t T, const void* A, int A_batched, const void
   p.grad_zi = static_cast<S*>(grad_zi);
   p.T = T;
   p.want_gA = grad_A != nullptr;
+  p.gA_shared = gA_shared ? 1 : 0;
   const bool bulk = aligned16(gy) && aligned16(grad_x) && (!LPV || aligned16(A)) &&
                     (!p.want_gA || (aligned16(y) && (!LPV || aligned16(grad_A)))) &&
                     (T * (XS ? 1 : 2) * sizeof(S)) % 16 == 0;
+  if (gA_shared && !bulk) return PTB_ERR_ARG;
   void* partial = nullptr;
   int64_t nchunks = 0;
   int rc = launch_scan<P>(p, B, T, bulk, ws, wsb, status, st, &partial, &nchunks);
@@ -652,6 +658,18 @@ int ptb_lpv_recur2_bwd(int dtype, int64_t B, int64_t T, const void* A, int A_bat
   constexpr bool kLpv = true;
   PTB_SO_DISPATCH(dtype, so_bwd, B, T, A, A_batched, zi, y, gy, g_in, grad_x, grad_A, grad_zi, workspace,
                   workspace_bytes, status, (cudaStream_t)stream);
+}
+
+int ptb_lpv_recur2_bwd_shared(int dtype, int64_t B, int64_t T, const void* A, const void* zi, const void* y,
+                              const void* gy, const void* g_in, int x_scalar, void* grad_x, void* grad_A,
+                              void* grad_zi, void* workspace, int64_t workspace_bytes, uint32_t* status,
+                              ptb_stream_t stream) {
+  if (B < 0 || T < 0) return PTB_ERR_ARG;
+  if (B == 0 || T == 0) return PTB_OK;
+  if (!A || !gy || !grad_x || !grad_A || !y || !zi) return PTB_ERR_ARG;
+  constexpr bool kLpv = true;
+  PTB_SO_DISPATCH(dtype, so_bwd, B, T, A, 0, zi, y, gy, g_in, grad_x, grad_A, grad_zi, workspace, workspace_bytes,
+                  status, (cudaStream_t)stream, true);
 }
 
 int ptb_biquad_tdf2_fwd(int dtype, int64_t B, int64_t T, const void* b, const void* a, int coef_batched,

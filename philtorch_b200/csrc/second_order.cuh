@@ -236,6 +236,7 @@ struct SoBwdParams {
   S* grad_zi;        // optional (B,2)
   int64_t T;
   int want_gA;
+  int gA_shared;     // LPV: grad_A is ONE (T,2,2) array that every row ADDS its tiles into (bulk path only)
 };
 
 template <class S, int NS, int STAGES_, int MIN_CTAS_, int NT_, bool LPV, bool XS>
@@ -282,7 +283,9 @@ struct SoBwd : MatAffine<S> {
     }
     if (XS) io.store(GX_OFF, p.grad_x + row * p.T + t0, (uint32_t)nvalid * SZ);
     else io.store(G_OFF, p.grad_x + (row * p.T + t0) * 2, (uint32_t)nvalid * 2 * SZ);
-    if (LPV && p.want_gA) io.store(A_OFF, p.grad_A + (row * p.T + t0) * 4, (uint32_t)nvalid * 4 * SZ);
+    if (LPV && p.want_gA)
+      io.store(A_OFF, p.grad_A + ((p.gA_shared ? 0 : row * p.T) + t0) * 4, (uint32_t)nvalid * 4 * SZ,
+               p.gA_shared ? SZ : 0);
   }
   static __device__ __forceinline__ State row_init(const Params& p, int64_t row) {
     State s = Alg::zero_state();

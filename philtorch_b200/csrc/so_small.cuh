@@ -230,9 +230,10 @@ struct SoSmallBwdParams {
   const S* gy;       // (B,T,2)
   const S* g_in;     // optional (B,2): c entering from the right end
   S* grad_x;         // (B,T,2), or (B,T) when XS
-  S* grad_A;         // optional (B,T,2,2)
+  S* grad_A;         // optional (B,T,2,2); (T,2,2) when gA_shared
   S* grad_zi;        // optional (B,2)
   int64_t T;
+  int gA_shared;     // the rows ADD their tiles of grad_A into one (T,2,2) array (bulk path only)
 };
 
 template <class C, bool XS>
@@ -398,14 +399,18 @@ so_small_bwd_kernel(const SoSmallBwdParams<S> p, const Workspace ws, const uint3
       p.grad_zi[(int64_t)row * 2 + 1] = c1;
     }
     S* ox = XS ? p.grad_x + off : p.grad_x + 2 * off;
-    S* oa = want_gA ? p.grad_A + 4 * off : nullptr;
+    S* oa = want_gA ? p.grad_A + 4 * (p.gA_shared ? t0 : off) : nullptr;
     if (bulk) {
       fence_proxy_async_smem();
       __syncthreads();
       if (tid == 0) {
         if (XS) bulk_s2g(ox, smem + L::kGX, nbytes);
         else bulk_s2g(ox, smem + L::kG, 2 * nbytes);
-        if (want_gA) bulk_s2g(oa, smem + L::kA, 4 * nbytes);
+        if (want_gA) {
+          if (!p.gA_shared) bulk_s2g(oa, smem + L::kA, 4 * nbytes);
+          else if (sizeof(S) == 4) bulk_s2g_add_f32(oa, smem + L::kA, 4 * nbytes);
+          else bulk_s2g_add_f64(oa, smem + L::kA, 4 * nbytes);
+        }
         bulk_commit();
       }
     } else {

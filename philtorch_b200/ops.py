@@ -39,6 +39,11 @@ def _dense(t: Tensor) -> Tensor:
 
 
 _LOW_PRECISION = (torch.float16, torch.bfloat16)
+# Coefficients shared by the rows: from this many samples on, the adjoint kernels add every row's
+# tile of the coefficient gradient into the one shared array while they write it out (the order of
+# the additions, and so the last bits of the sums, varies from run to run); smaller problems write
+# per-row gradients and sum them afterwards, which is bit-reproducible (what gradcheck expects)
+SHARED_ACCUMULATE_MIN_SAMPLES = 1 << 16
 
 
 def _two_byte_kernels_apply(args) -> bool:
@@ -182,7 +187,7 @@ def _lpv_recur_bwd(a, zi, y, gy, g_in, need_a, need_zi):
     a_c, zi_c, y_c, gy_c, gin_c = _dense(a), _dense(zi), _dense(y), _dense(gy), _opt(g_in)
     gx = torch.empty_like(y_c)
     gzi = torch.empty_like(zi_c) if need_zi else zi.new_empty(0)
-    if (need_a and a.dim() == 1 and B and T and y.dtype not in _LOW_PRECISION
+    if (need_a and a.dim() == 1 and B * T >= SHARED_ACCUMULATE_MIN_SAMPLES and y.dtype not in _LOW_PRECISION
             and (T * y.element_size()) % 16 == 0 and all(t.data_ptr() % 16 == 0 for t in (a_c, y_c, gy_c))):
         # coefficients shared by the rows: the kernel adds every row's tile into the one (T,) gradient
         ga = torch.zeros_like(a_c)
@@ -334,13 +339,21 @@ def _make_recur2_bwd(lpv: bool):
         A_c, zi_c, y_c, gy_c, gin_c = A.contiguous(), zi.contiguous(), y.contiguous(), gy.contiguous(), _opt(g_in)
         gx = y.new_empty((B, T) if x_scalar else (B, T, 2))
         batched = A.dim() == (4 if lpv else 3)
+        gzi = torch.empty_like(zi_c) if need_zi else zi.new_empty(0)
+        if (lpv and need_A and not batched and B * T >= SHARED_ACCUMULATE_MIN_SAMPLES
+                and (T * (1 if x_scalar else 2) * y.element_size()) % 16 == 0
+                and all(t.data_ptr() % 16 == 0 for t in (A_c, y_c, gy_c, gx))):
+            # matrices shared by the rows: the kernel adds every row's tile into the one (T,2,2) gradient
+            gA = torch.zeros_like(A_c)
+            _lib.call(lib.ptb_lpv_recur2_bwd_shared, dev, B, T, _lib.dtype_code(y), B, T, ptr(A_c), ptr(zi_c), ptr(y_c),
+                      ptr(gy_c), ptr(gin_c), int(x_scalar), ptr(gx), ptr(gA), ptr(gzi) if need_zi else None)
+            return gA, gzi, gx
         if not need_A:
             gA = A.new_empty(0)
         elif lpv:
             gA = y.new_empty(B, T, 2, 2)            # per row
         else:
             gA = torch.zeros_like(A_c)
-        gzi = torch.empty_like(zi_c) if need_zi else zi.new_empty(0)
         if B and T:
             _lib.call(fn, dev, B, T, _lib.dtype_code(y), B, T, ptr(A_c), int(batched), ptr(zi_c), ptr(y_c),
                       ptr(gy_c), ptr(gin_c), int(x_scalar), ptr(gx), ptr(gA) if need_A else None,

@@ -159,3 +159,32 @@ def test_many_tiles(dtype):
     xp = torch.stack([w["x"], torch.zeros_like(w["x"])], -1)
     _check("lpv", w["A"], torch.randn(B, 2, dtype=dtype), xp, w["gy"], dtype)
     _check("lti", w["A"][:, 0].contiguous(), torch.randn(B, 2, dtype=dtype), xp, w["gy"], dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+@pytest.mark.parametrize("scalar_x", [False, True])
+def test_shared_matrix_gradient_sum(dtype, scalar_x):
+    """Matrices shared by the rows, (T,2,2): the kernels add every row's outer products into the one
+    gradient array; compared with the per-row gradients of the same matrices expanded over the rows,
+    summed afterwards, and with the oracle."""
+    B, T = 40, 6000
+    g = torch.Generator().manual_seed(23)
+    A = _stable_A((T,), g, dtype)
+    zi = torch.randn(B, 2, generator=g, dtype=torch.float64).to(dtype)
+    x = torch.randn((B, T) if scalar_x else (B, T, 2), generator=g, dtype=torch.float64).to(dtype)
+    gy = torch.randn(B, T, 2, generator=g, dtype=torch.float64).to(dtype)
+    A_, zi_, x_ = (t.to(DEV).requires_grad_() for t in (A, zi, x))
+    y = ptb.lpv.state_space_recursion(A_, zi_, x_)
+    gA, gzi, gx = torch.autograd.grad(y, (A_, zi_, x_), gy.to(DEV))
+    assert gA.shape == A.shape
+    Ab = A.to(DEV).expand(B, T, 2, 2).contiguous().requires_grad_()
+    yb = ptb.lpv.state_space_recursion(Ab, zi_, x_)
+    gAb, gzib, gxb = torch.autograd.grad(yb, (Ab, zi_, x_), gy.to(DEV))
+    t = tol(dtype)
+    assert rel_err(y, yb.cpu()) == 0
+    assert rel_err(gx, gxb.cpu()) == 0 and rel_err(gzi, gzib.cpu()) == 0
+    assert rel_err(gA, gAb.sum(0).cpu()) <= t
+    xp = torch.stack([x, torch.zeros_like(x)], -1) if scalar_x else x
+    y_ref = cport.recur2(A, zi, xp)
+    gA_ref, _, _ = cport.recur2_bwd(A, zi, y_ref, gy)
+    assert rel_err(gA, gA_ref) <= t
