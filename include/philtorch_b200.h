@@ -266,6 +266,41 @@ int ptb_lpv_recur2_bwd_shared(int dtype, int64_t B, int64_t T, const void* A, co
                               void* grad_zi, void* workspace, int64_t workspace_bytes, uint32_t* status,
                               ptb_stream_t stream);
 
+/* ---- 2x2, per-sample coefficients: rows cut into segments along time ------------------------------
+ * No counterpart in the reference (its recurrence is philtorch/csrc/recur2.cu:69-117).  A handful of
+ * long rows is cut into nseg segments of L samples each, which the scan kernel treats as B * nseg
+ * independent rows (kernel row r = b * nseg + j) started from a ZERO state; the fix-up turns the
+ * zero-start results into those of the uncut recurrence on the device.
+ *
+ * ptb_lpv_recur2_zero_carry: the forward scan of R kernel rows of T samples from a zero state
+ *   (A (R,T,2,2), x (R,T,2) or (R,T) if x_scalar) -> y (R,T,2), end_state (R,2) = y[:, T-1], and
+ *   tile_prod (R, ptb_lpv_recur2_carry_chunks(dtype, T), 4): the ordered product of the matrices
+ *   of every tile of every row.  Workspace as for ptb_lpv_recur2_fwd.
+ * ptb_lpv_recur2_fold_products: P (R,4) = the ordered product of a row's tile products
+ *   = A[T-1] ... A[0].
+ * ptb_lpv_recur2_fixup_fwd: the state s entering kernel row (b, j) is folded from zi (B,2) and the
+ *   maps s -> P_i s + e_i of the segments before it; s goes to states (B*nseg,2) and
+ *   y[t] += k[t], k[t] = A[t] k[t-1], k[-1] = s, is applied in place block by block until k is
+ *   exactly zero (it stays zero from there on, so stopping is exact).
+ * ptb_lpv_recur2_fixup_bwd: the mirror image for the adjoint.  e (B*nseg,2) = the adjoint state
+ *   leaving every segment on its left when nothing enters on its right (grad_zi of
+ *   ptb_lpv_recur2_bwd run on the kernel rows with zi = states); the state c entering a segment
+ *   from its right is folded with P^T from the segments to its right, and
+ *   grad_x[t] += d[t], grad_A[t] += d[t] (x) y[t-1] (y[-1] = states[r]), d[L-1] = c,
+ *   d[t-1] = A[t]^T d[t], from the segment's end until d is exactly zero.  grad_x: (B*nseg,L,2), or
+ *   (B*nseg,L) if x_scalar (component 0 only); grad_A optional; grad_zi (B,2) optional. */
+int64_t ptb_lpv_recur2_carry_chunks(int dtype, int64_t T);
+int ptb_lpv_recur2_zero_carry(int dtype, int64_t B, int64_t T, const void* A, const void* x, int x_scalar, void* y,
+                              void* tile_prod, void* end_state, void* workspace, int64_t workspace_bytes,
+                              uint32_t* status, ptb_stream_t stream);
+int ptb_lpv_recur2_fold_products(int dtype, int64_t R, int64_t nchunks, const void* tile_prod, void* P,
+                                 ptb_stream_t stream);
+int ptb_lpv_recur2_fixup_fwd(int dtype, int64_t B, int64_t nseg, int64_t L, const void* A, void* y, const void* P,
+                             const void* e, const void* zi, void* states, ptb_stream_t stream);
+int ptb_lpv_recur2_fixup_bwd(int dtype, int64_t B, int64_t nseg, int64_t L, const void* A, const void* y,
+                             const void* states, const void* P, const void* e, int x_scalar, void* grad_x,
+                             void* grad_A, void* grad_zi, ptb_stream_t stream);
+
 /* ---- dense N x N recurrences, 2 < N <= 8 ---------------------------------------------------------
  * Replace ops philtorch::recurN / philtorch::lti_recurN for state dimensions above two
  * (philtorch/csrc/host_recur2.cpp:165,168; CPU kernels philtorch/csrc/host_recurN.cpp:81-140,236-281 and

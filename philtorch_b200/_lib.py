@@ -61,6 +61,16 @@ for _n in ("ptb_lti_recur2_bwd", "ptb_lpv_recur2_bwd"):
     getattr(lib, _n).restype = _i32
 lib.ptb_lpv_recur2_bwd_shared.argtypes = [_i32, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp] + _tail
 lib.ptb_lpv_recur2_bwd_shared.restype = _i32
+lib.ptb_lpv_recur2_carry_chunks.argtypes = [_i32, _i64]
+lib.ptb_lpv_recur2_carry_chunks.restype = _i64
+lib.ptb_lpv_recur2_zero_carry.argtypes = [_i32, _i64, _i64, _vp, _vp, _i32, _vp, _vp, _vp] + _tail
+lib.ptb_lpv_recur2_zero_carry.restype = _i32
+lib.ptb_lpv_recur2_fold_products.argtypes = [_i32, _i64, _i64, _vp, _vp, _vp]
+lib.ptb_lpv_recur2_fold_products.restype = _i32
+lib.ptb_lpv_recur2_fixup_fwd.argtypes = [_i32, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp]
+lib.ptb_lpv_recur2_fixup_fwd.restype = _i32
+lib.ptb_lpv_recur2_fixup_bwd.argtypes = [_i32, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp]
+lib.ptb_lpv_recur2_fixup_bwd.restype = _i32
 lib.ptb_biquad_tdf2_fwd.argtypes = [_i32, _i64, _i64, _vp, _vp, _i32, _vp, _vp, _vp, _vp] + _tail
 lib.ptb_biquad_tdf2_fwd.restype = _i32
 lib.ptb_biquad_tdf2_bwd.argtypes = [_i32, _i64, _i64, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp] + _tail

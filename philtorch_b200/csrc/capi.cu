@@ -96,7 +96,7 @@ template <> struct SoSmallSel<double> { using C = LpvBqCfg<double, 9, PTB_SO_SMA
 
 template <class S, bool XS>
 static int so_small_fwd(int64_t B, int64_t T, const void* A, int A_batched, const void* zi, const void* x, void* y,
-                        void* zf, void* ws, int64_t wsb, uint32_t* status, cudaStream_t st) {
+                        void* zf, void* ws, int64_t wsb, uint32_t* status, cudaStream_t st, void* tile_prod = nullptr) {
   using C = typename SoSmallSel<S>::C;
   using L = SoSmallFwdSmem<C, XS>;
   static_assert(C::TILE >= kMinTile && C::SLOT_WORDS * 8 <= kTileRecordBytes, "generic workspace bound");
@@ -120,6 +120,7 @@ static int so_small_fwd(int64_t B, int64_t T, const void* A, int A_batched, cons
   p.y = static_cast<S*>(y);
   p.zf = static_cast<S*>(zf);
   p.T = T;
+  p.tile_prod = static_cast<S*>(tile_prod);
   const bool bulk = aligned16(x) && aligned16(y) && aligned16(A) && (T * (XS ? 1 : 2) * sizeof(S)) % 16 == 0;
   static bool attr_set[kMaxDevices] = {};
   static int grid_max[kMaxDevices] = {};
@@ -658,6 +659,37 @@ int ptb_lpv_recur2_bwd(int dtype, int64_t B, int64_t T, const void* A, int A_bat
   constexpr bool kLpv = true;
   PTB_SO_DISPATCH(dtype, so_bwd, B, T, A, A_batched, zi, y, gy, g_in, grad_x, grad_A, grad_zi, workspace,
                   workspace_bytes, status, (cudaStream_t)stream);
+}
+
+int64_t ptb_lpv_recur2_carry_chunks(int dtype, int64_t T) {
+  if (T < 0) return -1;
+  switch (dtype) {
+    case PTB_F32: return (T + SoSmallSel<float>::C::TILE - 1) / SoSmallSel<float>::C::TILE;
+    case PTB_F64: return (T + SoSmallSel<double>::C::TILE - 1) / SoSmallSel<double>::C::TILE;
+    default: return -1;
+  }
+}
+
+int ptb_lpv_recur2_zero_carry(int dtype, int64_t B, int64_t T, const void* A, const void* x, int x_scalar, void* y,
+                              void* tile_prod, void* end_state, void* workspace, int64_t workspace_bytes,
+                              uint32_t* status, ptb_stream_t stream) {
+  if (B < 0 || T < 0) return PTB_ERR_ARG;
+  if (B == 0 || T == 0) return PTB_OK;
+  if (!A || !x || !y || !tile_prod || !end_state) return PTB_ERR_ARG;
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (dtype) {
+    case PTB_F32:
+      return x_scalar ? so_small_fwd<float, true>(B, T, A, 1, nullptr, x, y, end_state, workspace, workspace_bytes,
+                                                  status, st, tile_prod)
+                      : so_small_fwd<float, false>(B, T, A, 1, nullptr, x, y, end_state, workspace, workspace_bytes,
+                                                   status, st, tile_prod);
+    case PTB_F64:
+      return x_scalar ? so_small_fwd<double, true>(B, T, A, 1, nullptr, x, y, end_state, workspace, workspace_bytes,
+                                                   status, st, tile_prod)
+                      : so_small_fwd<double, false>(B, T, A, 1, nullptr, x, y, end_state, workspace, workspace_bytes,
+                                                    status, st, tile_prod);
+    default: return PTB_ERR_ARG;
+  }
 }
 
 int ptb_lpv_recur2_bwd_shared(int dtype, int64_t B, int64_t T, const void* A, const void* zi, const void* y,

@@ -17,6 +17,7 @@ struct SoSmallFwdParams {
   S* y;                        // (B,T,2)
   S* zf;                       // optional (B,2)
   int64_t T;
+  S* tile_prod;                // optional (B, nchunks, 4): the ordered product of every tile's matrices
 };
 
 template <class C, bool XS>
@@ -163,9 +164,20 @@ so_small_fwd_kernel(const SoSmallFwdParams<S> p, const Workspace ws, const uint3
     }
     if (tid == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the previous tile's outputs have left
     __syncthreads();
+    if (p.tile_prod != nullptr && tid == NT - 1) {   // rows cut into segments: the fix-up needs the segment's matrix
+      S q0 = S(1), q1 = S(0), q2 = S(0), q3 = S(1);
+      for (int w = 0; w < C::NW; ++w) {
+        const S* t = sm_wtot + w * 6;
+        const S n0 = t[0] * q0 + t[1] * q2, n1 = t[0] * q1 + t[1] * q3;
+        const S n2 = t[2] * q0 + t[3] * q2, n3 = t[2] * q1 + t[3] * q3;
+        q0 = n0; q1 = n1; q2 = n2; q3 = n3;
+      }
+      S* o = p.tile_prod + ((int64_t)row * nchunks + chunk) * 4;
+      o[0] = q0; o[1] = q1; o[2] = q2; o[3] = q3;
+    }
     if (warp == 0) {
       S z0 = S(0), z1 = S(0);
-      if (chunk == 0) { z0 = __ldg(p.zi + (int64_t)row * 2); z1 = __ldg(p.zi + (int64_t)row * 2 + 1); }
+      if (chunk == 0 && p.zi != nullptr) { z0 = __ldg(p.zi + (int64_t)row * 2); z1 = __ldg(p.zi + (int64_t)row * 2 + 1); }
       const typename LpvLb<S>::State hin =
           lpv_tile_state<S, C::NW>(ws, sm_wtot, ticket, chunk, nchunks, B, lane, z0, z1, wait_ns);
       if (lane == 0) { sm_hin[0] = hin.v[0]; sm_hin[1] = hin.v[1]; }

@@ -12,7 +12,9 @@ from typing import Optional
 import torch
 from torch import Tensor
 
+from .. import sharded
 from ..autograd import LPVRecurrence, MatrixRecurrence, matrix_recurrence_scalar_input
+from .recur import _has_tangent
 
 __all__ = ["MatrixRecurrence", "state_space_recursion", "state_space", "extension_backend_indicator"]
 
@@ -29,7 +31,14 @@ def _ext_ss_recur(A: Tensor, zi: Tensor, x: Tensor, *, out_idx: Optional[int] = 
         xs = x if x.dim() == 2 else x.squeeze(-1)
         y = LPVRecurrence.apply(A[..., 0, 0], zi.squeeze(-1), xs).unsqueeze(-1)
     elif M == 2:
-        if x.dim() == 2:
+        S = 1
+        if A.dim() == 4 and x.is_cuda and x.dtype in (torch.float32, torch.float64):
+            # a handful of long rows: cut into segments the kernels see as independent rows (the tiles of
+            # one row wait on one another, so few rows leave most of the memory bandwidth unused)
+            S = sharded.auto_segments2(x.size(0), x.size(1))
+        if S > 1 and not _has_tangent(A, zi, x):
+            y = sharded.SegmentedMatrixRecurrence.apply(A, zi, x, S)
+        elif x.dim() == 2:
             y = matrix_recurrence_scalar_input(A, zi, x, True)
         else:
             y = MatrixRecurrence.apply(A, zi, x)

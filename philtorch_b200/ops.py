@@ -122,13 +122,14 @@ def _lti_recur_bwd(a, zi, y, gy, g_in, need_a, need_zi):
     B, T = y.shape
     a_c, zi_c, y_c, gy_c, gin_c = _dense(a), _dense(zi), _dense(y), _dense(gy), _opt(g_in)
     gx = torch.empty_like(y_c)
-    ga = torch.zeros_like(a_c) if need_a else a.new_empty(0)
+    ga = torch.empty_like(a_c) if need_a else a.new_empty(0)   # every entry is written by the reduction
     gzi = torch.empty_like(zi_c) if need_zi else zi.new_empty(0)
     if B and T:
         _lib.call(lib.ptb_lti_recur_bwd, dev, B, T, _lib.dtype_code(y, True), B, T, ptr(a_c),
                   int(a.dim() == 1 and a.shape[0] == B), ptr(zi_c), 1, ptr(y_c), ptr(gy_c), ptr(gin_c),
                   ptr(gx), ptr(ga) if need_a else None, ptr(gzi) if need_zi else None)
-    elif need_zi:
+    else:
+        ga.zero_()
         gzi.zero_()
     return ga, gzi, gx
 

@@ -121,15 +121,32 @@ SEGMENT_MIN_LENGTH = 1 << 17   # ... of at least this many samples (a dozen tile
 SEGMENT_MIN_SAMPLES = 1 << 24  # smaller problems are launch-bound: the extra fix-up launches cost more than they save
 
 
-def auto_segments(B: int, T: int, batched: bool) -> int:
+def auto_segments(B: int, T: int, batched: bool, min_length: int = SEGMENT_MIN_LENGTH,
+                  min_samples: int = SEGMENT_MIN_SAMPLES, min_rows: int = SEGMENT_MIN_ROWS) -> int:
     """Segments per row for B rows of T samples (measured on B200, fwd+bwd replayed from a CUDA graph:
     32 rows x 2^20: 0.219 ms plain, 0.184 ms with 8 segments; 64 rows: 0.386 -> 0.342 ms with 4)."""
-    if not batched or B * T < SEGMENT_MIN_SAMPLES:
+    if not batched or B * T < min_samples:
         return 1   # coefficients shared by the rows cannot be reshaped into more rows
     S = 1
-    while B * S < SEGMENT_MIN_ROWS and T % (2 * S) == 0 and T // (2 * S) >= SEGMENT_MIN_LENGTH:
+    while B * S < min_rows and T % (2 * S) == 0 and T // (2 * S) >= min_length:
         S *= 2
     return S
+
+
+# 2x2 matrices: tiles are a few thousand samples and a sample moves 80 bytes, so shorter segments and
+# smaller problems already pay
+SEGMENT2_MAX_BATCH = 96        # 128 rows already run at 0.96 of the copy bandwidth: segments gain nothing there
+SEGMENT2_MIN_LENGTH = 1 << 16
+SEGMENT2_MIN_SAMPLES = 1 << 23
+
+
+def auto_segments2(B: int, T: int) -> int:
+    """Segments per row for the time-varying 2x2 recurrence with per-row matrices (measured on B200,
+    T = 2^20, fp32, eager fwd+bwd: 16 rows 0.403 ms plain, 0.313 ms with 8 segments; 32 rows
+    0.659 -> 0.519 ms with 8; 64 rows 1.107 -> 0.942 ms with 4; 128 rows 1.778 ms either way)."""
+    if B >= SEGMENT2_MAX_BATCH:
+        return 1
+    return auto_segments(B, T, True, SEGMENT2_MIN_LENGTH, SEGMENT2_MIN_SAMPLES)
 
 
 def _rank_world(group):
@@ -221,3 +238,65 @@ def time_sharded_linear_recurrence(a: Tensor, zi: Tensor, x: Tensor, group=None,
         zero elsewhere (sum over ranks = the gradient).
     """
     return TimeShardedLPVRecurrence.apply(a, zi, x, group, _kernels, segments)
+
+
+class SegmentedMatrixRecurrence(Function):
+    """h[t] = A[t] h[t-1] + x[t] with 2x2 matrices per row and sample, every row cut into S segments
+    that the kernels see as B*S independent rows (one device; A (B,T,2,2), zi (B,2), x (B,T,2) or
+    (B,T) feeding state 0).  Forward: the zero-start scan of all segments (which also yields every
+    segment's matrix product), then ONE fix-up launch that folds the states entering the segments
+    and corrects y in place until the correction is exactly zero.  Backward: the adjoint kernel on
+    the segments with nothing entering from the right, then the mirrored fix-up of grad_x / grad_A.
+    Same values as ``MatrixRecurrence`` (philtorch/lpv/ssm.py:34-115 of the reference) up to rounding."""
+
+    @staticmethod
+    def forward(ctx: Any, A: Tensor, zi: Tensor, x: Tensor, S: int) -> Tensor:
+        B, T = x.shape[0], x.shape[1]
+        xs = x.dim() == 2
+        if A.dim() != 4 or T % S != 0:
+            raise ValueError("segments need per-row matrices (B, T, 2, 2) and a row length divisible by them")
+        dev = _lib.require_cuda(A, zi, x)
+        L, R = T // S, B * S
+        code = _lib.dtype_code(x)
+        Av, xv, zi_c = A.contiguous().view(R, L, 2, 2), x.contiguous().view((R, L) if xs else (R, L, 2)), zi.contiguous()
+        y = x.new_empty(R, L, 2)
+        nch = lib.ptb_lpv_recur2_carry_chunks(code, L)
+        tile_prod, e = x.new_empty(R, nch, 4), x.new_empty(R, 2)
+        _lib.call(lib.ptb_lpv_recur2_zero_carry, dev, R, L, code, R, L, ptr(Av), ptr(xv), int(xs), ptr(y),
+                  ptr(tile_prod), ptr(e))
+        P, states = x.new_empty(R, 4), x.new_empty(R, 2)
+        _stream_call(lib.ptb_lpv_recur2_fold_products, dev, code, R, nch, ptr(tile_prod), ptr(P))
+        _stream_call(lib.ptb_lpv_recur2_fixup_fwd, dev, code, B, S, L, ptr(Av), ptr(y), ptr(P), ptr(e), ptr(zi_c),
+                     ptr(states))
+        out = y.view(B, T, 2)
+        ctx.S, ctx.xs = S, xs
+        ctx.save_for_backward(A, zi, out, states, P)
+        return out
+
+    @staticmethod
+    def backward(ctx: Any, gy: Tensor):
+        A, zi, out, states, P = ctx.saved_tensors
+        S, xs = ctx.S, ctx.xs
+        need_A, need_zi, need_x = ctx.needs_input_grad[:3]
+        B, T = out.shape[0], out.shape[1]
+        if torch.is_grad_enabled():
+            # a higher-order graph is being recorded: the adjoint written with differentiable pieces
+            # (philtorch/lpv/ssm.py:64-99)
+            from .autograd import MatrixRecurrence
+            AmT = A.mT
+            A_rev = torch.roll(AmT, shifts=-1, dims=-3).flip(-3)
+            g = MatrixRecurrence.apply(A_rev, torch.zeros_like(zi), gy.flip(1)).flip(1)
+            prev = torch.cat([zi.unsqueeze(1), out[:, :-1]], dim=1)
+            return (g.unsqueeze(-1) * prev.unsqueeze(-2) if need_A else None,
+                    (AmT[:, 0] @ g[:, 0, :, None]).squeeze(-1) if need_zi else None,
+                    (g[..., 0] if xs else g) if need_x else None, None)
+        dev = out.device
+        L, R = T // S, B * S
+        code = _lib.dtype_code(out)
+        Av, yv, gyv = A.contiguous().view(R, L, 2, 2), out.view(R, L, 2), gy.contiguous().view(R, L, 2)
+        gA, e_adj, gx = torch.ops.philtorch_b200.recur2_bwd(Av, states, yv, gyv, None, xs, need_A, True)
+        gzi = out.new_empty(B, 2)
+        _stream_call(lib.ptb_lpv_recur2_fixup_bwd, dev, code, B, S, L, ptr(Av), ptr(yv), ptr(states), ptr(P),
+                     ptr(e_adj), int(xs), ptr(gx), ptr(gA) if need_A else None, ptr(gzi))
+        return (gA.view(A.shape) if need_A else None, gzi if need_zi else None,
+                gx.view((B, T) if xs else (B, T, 2)) if need_x else None, None)
