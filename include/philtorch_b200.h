@@ -416,6 +416,13 @@ int ptb_lpv_biquad_tdf2_bwd(int dtype, int64_t B, int64_t T, const void* b, cons
  * initial state in zi's order.  workspace and status are unused (no device-side waits) and may be NULL.
  * float32 / float64. */
 int64_t ptb_comb_partial_blocks(int64_t delay);
+/* Kernel family (process-wide; for tests and tuning), low byte of `policy`: 0 = slab kernels
+ * (csrc/comb_slab.cuh: bands of neighbouring phases staged by tiled TMA copies) when delay and N are
+ * multiples of 16 bytes of samples, the arrays are 16-byte aligned and the signal has at least 64 steps
+ * of at least 64 phases, else one lane per phase (csrc/comb.cuh); 1 = lane per phase only; 2 / 3 / 4 =
+ * slab kernels with bands of 256 / 128 / 64 phases wherever the layout allows.  Bits 8 and up: deepest
+ * shared-memory ring of the slab kernels, 3..16 (0: the default, 4). */
+int ptb_comb_set_policy(int policy);
 int ptb_comb_fwd(int dtype, int64_t B, int64_t N, int64_t delay, const void* a, int a_batched, const void* zi,
                  int zi_mode, const void* x, void* y, void* workspace, int64_t workspace_bytes, uint32_t* status,
                  ptb_stream_t stream);

@@ -130,6 +130,8 @@ lib.ptb_modal_bank_fwd.argtypes = [_i32, _i64, _i64, _i64] + [_vp] * 10
 lib.ptb_modal_bank_fwd.restype = _i32
 lib.ptb_modal_bank_bwd.argtypes = [_i32, _i64, _i64, _i64] + [_vp] * 8 + [_i32] + [_vp] * 5
 lib.ptb_modal_bank_bwd.restype = _i32
+lib.ptb_comb_set_policy.argtypes = [_i32]
+lib.ptb_comb_set_policy.restype = _i32
 lib.ptb_comb_partial_blocks.argtypes = [_i64]
 lib.ptb_comb_partial_blocks.restype = _i64
 lib.ptb_comb_fwd.argtypes = [_i32, _i64, _i64, _i64, _vp, _i32, _vp, _i32, _vp, _vp] + _tail

@@ -91,8 +91,11 @@ template <class S> struct SoSmallSel;
 #define PTB_SO_SMALL_MINB 4
 #define PTB_SO_SMALL_MINB64 3
 #endif
+#ifndef PTB_SO_SMALL_SPT64
+#define PTB_SO_SMALL_SPT64 9
+#endif
 template <> struct SoSmallSel<float> { using C = LpvBqCfg<float, 15, PTB_SO_SMALL_NT, PTB_SO_SMALL_MINB>; };
-template <> struct SoSmallSel<double> { using C = LpvBqCfg<double, 9, PTB_SO_SMALL_NT, PTB_SO_SMALL_MINB64>; };
+template <> struct SoSmallSel<double> { using C = LpvBqCfg<double, PTB_SO_SMALL_SPT64, PTB_SO_SMALL_NT, PTB_SO_SMALL_MINB64>; };
 
 template <class S, bool XS>
 static int so_small_fwd(int64_t B, int64_t T, const void* A, int A_batched, const void* zi, const void* x, void* y,

@@ -19,12 +19,18 @@ DT = {"f32": torch.float32, "f64": torch.float64}
 COMB_CASES = [(1, "none"), (5, "none"), (13, "shared"), (5, "batched"), (32, "none")]
 
 
-@pytest.fixture(params=["folded_scan", "comb_kernels"], autouse=True)
+@pytest.fixture(params=["folded_scan", "comb_kernels", "comb_slabs_256", "comb_slabs_128", "comb_slabs_64"], autouse=True)
 def comb_route(request, monkeypatch):
-    """Every test runs on both routes of comb_filter: the folded first-order scan and the comb kernels."""
+    """Every test runs on every route of comb_filter: the folded first-order scan, the lane-per-phase
+    comb kernels, and the slab kernels with bands of 256, 128 and 64 phases (which hand layouts they
+    cannot take -- delay or length not a multiple of 16 bytes -- to the lane-per-phase kernels)."""
+    from philtorch_b200 import _lib
     from philtorch_b200.lti import filtering
     monkeypatch.setattr(filtering, "COMB_KERNEL_MIN_LANES", 10 ** 12 if request.param == "folded_scan" else 1)
-    return request.param
+    policy = {"folded_scan": 0, "comb_kernels": 1, "comb_slabs_256": 2, "comb_slabs_128": 3, "comb_slabs_64": 4}[request.param]
+    assert _lib.lib.ptb_comb_set_policy(policy) == 0
+    yield request.param
+    assert _lib.lib.ptb_comb_set_policy(0) == 0
 
 
 @pytest.mark.parametrize("tag", ["f32", "f64"])
@@ -66,7 +72,9 @@ def test_comb_sizes(dtype, delay, n):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
 @pytest.mark.parametrize("delay,n,zi_kind", [(3, 1000, "batched"), (129, 5000, "shared"), (1000, 30011, "batched"),
-                                              (500, 300, "batched"), (64, 64 * 40, None)])
+                                              (500, 300, "batched"), (64, 64 * 40, None), (1000, 68000, "batched"),
+                                              (300, 300 * 131 + 152, "shared"), (260, 260 * 16, "batched"),
+                                              (4, 4096, None)])
 @pytest.mark.parametrize("a_batched", [True, False])
 def test_comb_routes_agree(dtype, delay, n, zi_kind, a_batched, comb_route, monkeypatch):
     """Outputs and all gradients (a, zi, x) of the comb kernels against the folded scan."""
@@ -157,7 +165,7 @@ def test_cubic_spline_sizes(dtype, m, scipy_padding):
 @pytest.mark.parametrize("scipy_padding", [True, False])
 @pytest.mark.parametrize("pfe", [True, False])
 def test_cspline_gradcheck(scipy_padding, pfe, comb_route):
-    if comb_route == "comb_kernels":
+    if comb_route != "folded_scan":
         pytest.skip("independent of the comb route")
     x = torch.randn(2, 40, dtype=torch.float64, device=DEV, generator=torch.Generator(DEV).manual_seed(3))
     x.requires_grad_()
@@ -171,7 +179,7 @@ def test_cspline_gradcheck(scipy_padding, pfe, comb_route):
 @pytest.mark.parametrize("scipy_padding", [True, False])
 def test_cspline_forms_agree(dtype, n, scipy_padding, comb_route):
     """The fused two-pass evaluation against the cascaded one (different kernels), values and gradients."""
-    if comb_route == "comb_kernels":
+    if comb_route != "folded_scan":
         pytest.skip("independent of the comb route")
     gen = torch.Generator().manual_seed(n)
     x0 = torch.randn(4, n, generator=gen, dtype=torch.float64).to(dtype).to(DEV)
