@@ -70,6 +70,8 @@ static bool comb_tensor_map(CUtensorMap* map, const void* base, int64_t B, int64
   return r == CUDA_SUCCESS;
 }
 
+constexpr int kCombNoTensorMap = -1;   // the tensor maps could not be encoded: the caller uses the other kernels
+
 struct CombPlan {
   int width = 0, stages = 0;
   int64_t ctas = 0;
@@ -131,12 +133,12 @@ struct CombSlabLaunch {
           !comb_tensor_map<S>(&m1, p.yfwd ? static_cast<const void*>(p.yfwd) : static_cast<const void*>(p.gy), B, p.N,
                               p.D, K, W, C::KS) ||
           !comb_tensor_map<S>(&m2, p.grad_x, B, p.N, p.D, K, W, C::KS))
-        return PTB_ERR_ARG;
+        return kCombNoTensorMap;
       comb_slab_bwd_kernel<S, C><<<grid, W, smem, st>>>(m0, m1, m2, p);
     } else {
       if (!comb_tensor_map<S>(&m0, p.x, B, p.N, p.D, K, W, C::KS) ||
           !comb_tensor_map<S>(&m1, p.y, B, p.N, p.D, K, W, C::KS))
-        return PTB_ERR_ARG;
+        return kCombNoTensorMap;
       comb_slab_fwd_kernel<S, C><<<grid, W, smem, st>>>(m0, m1, p);
     }
     PTB_CUDA(cudaGetLastError());
@@ -184,7 +186,8 @@ static int comb_fwd(int64_t B, int64_t N, int64_t D, const void* a, int a_batche
     p.zi = static_cast<const S*>(zi); p.zi_mode = zi_mode;
     p.N = N; p.D = D; p.status = status; p.wait_ns = g_wait_ns;
     p.x = static_cast<const S*>(x); p.y = static_cast<S*>(y);
-    return comb_slab_run<S, false>(pl, p, B, st);
+    const int rc = comb_slab_run<S, false>(pl, p, B, st);
+    if (rc != kCombNoTensorMap) return rc;
   }
   const int bpr = comb_blocks_per_row(D);
   comb_fwd_kernel<S><<<(unsigned)(B * bpr), kCombThreads, 0, st>>>(
@@ -208,7 +211,8 @@ static int comb_bwd(int64_t B, int64_t N, int64_t D, const void* a, int a_batche
     p.gy = static_cast<const S*>(gy); p.yfwd = static_cast<const S*>(y); p.grad_x = static_cast<S*>(grad_x);
     p.partial = static_cast<S*>(partial); p.partial_stride = comb_blocks_per_row(D);
     p.grad_state = static_cast<S*>(grad_state);
-    return comb_slab_run<S, true>(pl, p, B, st);
+    const int rc = comb_slab_run<S, true>(pl, p, B, st);
+    if (rc != kCombNoTensorMap) return rc;
   }
   const int bpr = comb_blocks_per_row(D);
   comb_bwd_kernel<S><<<(unsigned)(B * bpr), kCombThreads, 0, st>>>(
