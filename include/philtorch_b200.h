@@ -315,8 +315,14 @@ int ptb_lpv_recur2_fixup_bwd(int dtype, int64_t B, int64_t nseg, int64_t L, cons
  * (philtorch/lpv/ssm.py:64-99) and LTIMatrixRecurrence.backward (philtorch/lti/ssm.py:67-96):
  *   g[t] = gy[t] + c[t+1],  c[t] = A[t]^T g[t],  c[T] = g_in (optional (B,N), zero if NULL);
  * g (B,T,N) is grad_x, c0 (optional (B,N)) is grad_zi.  grad_A = g[t] (x) h[t-1] (summed over t for a
- * time-invariant A) is left to the caller: per row it is an (N x T)(T x N) matrix product. */
+ * time-invariant A) is left to the caller: per row it is an (N x T)(T x N) matrix product.
+ *
+ * Constant matrices (A_timevar = 0) run on a policy whose maps carry only the N-vector offset and
+ * their length; the linear part A^n comes from a per-row table of powers built in double at the
+ * start of the call (csrc/mat_n_lti.cuh): N^2 work per sample instead of N^3.
+ * ptb_recur_n_set_policy(1) sends them to the general kernels instead (process-wide; tests). */
 int64_t ptb_recur_n_workspace_bytes(int dtype, int N, int64_t B, int64_t T);
+int ptb_recur_n_set_policy(int policy);
 int ptb_recur_n_fwd(int dtype, int N, int64_t B, int64_t T, const void* A, int A_batched, int A_timevar,
                     const void* zi, const void* x, void* y, void* zf, void* workspace, int64_t workspace_bytes,
                     uint32_t* status, ptb_stream_t stream);

@@ -2,6 +2,7 @@
 #include "launch.cuh"
 
 #include "mat_n.cuh"
+#include "mat_n_lti.cuh"
 
 namespace ptb {
 
@@ -14,6 +15,8 @@ template <> struct MatNGeom<float, 8> { static constexpr int NT = 128, SPT = 1, 
 template <> struct MatNGeom<double, 8> { static constexpr int NT = 128, SPT = 1, ST = 2; };
 template <class S, int NMAX, bool REV>
 using MatNP = MatN<S, NMAX, MatNGeom<S, NMAX>::NT, MatNGeom<S, NMAX>::SPT, MatNGeom<S, NMAX>::ST, REV>;
+
+static int g_matn_lti_tables = 1;   // constant matrices: 1 = table-of-powers policy, 0 = the general policy (tests)
 
 template <class P>
 static int64_t matn_ws(int64_t B, int64_t T) {
@@ -40,11 +43,70 @@ static int matn_run(int N, int64_t B, int64_t T, const void* A, int A_batched, i
   return launch_scan<P, false>(p, B, T, bulk, ws, wsb, status, st, nullptr, nullptr);
 }
 
+// constant matrices: table-of-powers policy (mat_n_lti.cuh).  (threads, samples per thread, stages)
+template <class S, int NMAX> struct MatNLtiGeom;
+#ifndef PTB_MATN_LTI_SPT4
+#define PTB_MATN_LTI_SPT4 7
+#define PTB_MATN_LTI_SPT8 9
+#endif
+template <> struct MatNLtiGeom<float, 4> { static constexpr int NT = 256, SPT = PTB_MATN_LTI_SPT4, ST = 3; };
+template <> struct MatNLtiGeom<double, 4> { static constexpr int NT = 256, SPT = 3, ST = 3; };
+template <> struct MatNLtiGeom<float, 8> { static constexpr int NT = 256, SPT = PTB_MATN_LTI_SPT8, ST = 3; };
+template <> struct MatNLtiGeom<double, 8> { static constexpr int NT = 256, SPT = 3, ST = 3; };
+template <class S, int NMAX, bool REV>
+using MatNLtiP = MatNLti<S, NMAX, MatNLtiGeom<S, NMAX>::NT, MatNLtiGeom<S, NMAX>::SPT, MatNLtiGeom<S, NMAX>::ST, REV>;
+
+template <class S, int NMAX>
+static int64_t matn_lti_table_bytes(int64_t B) {
+  return align_up(B * MatNLtiDims<NMAX>::ROWTAB * (int64_t)sizeof(S), 256);
+}
+
+template <class S, int NMAX, bool REV>
+static int matn_lti_run(int N, int64_t B, int64_t T, const void* A, int A_batched, const void* zi, const void* x,
+                        void* y, void* zf, void* ws, int64_t wsb, uint32_t* status, cudaStream_t st) {
+  using P = MatNLtiP<S, NMAX, REV>;
+  using D = MatNLtiDims<NMAX>;
+  if ((T + P::SPT - 1) / P::SPT >= (1ll << D::NPOW)) return PTB_ERR_TOO_LARGE;
+  const int64_t rows = A_batched ? B : 1;
+  const int64_t scan_ws = align_up(matn_ws<P>(B, T), 256);
+  if (!ws || (reinterpret_cast<uintptr_t>(ws) & 255u) || wsb < scan_ws + matn_lti_table_bytes<S, NMAX>(rows))
+    return PTB_ERR_WORKSPACE;
+  S* tab = reinterpret_cast<S*>(static_cast<char*>(ws) + scan_ws);
+  matn_lti_setup_kernel<S, NMAX, REV><<<(unsigned)rows, D::NN, 0, st>>>(static_cast<const S*>(A), A_batched ? (int64_t)N * N : 0,
+                                                                      N, tab, P::SPT);
+  PTB_CUDA(cudaGetLastError());
+  typename P::Params p;
+  p.tab = tab;
+  p.tab_stride = A_batched ? D::ROWTAB : 0;
+  p.zi = static_cast<const S*>(zi);
+  p.x = static_cast<const S*>(x);
+  p.y = static_cast<S*>(y);
+  p.zf = static_cast<S*>(zf);
+  p.T = T;
+  p.N = N;
+  const bool bulk = aligned16(x) && aligned16(y) && (T * N * sizeof(S)) % 16 == 0 &&
+                    ((int64_t)P::TILE * N * sizeof(S)) % 16 == 0;
+  return launch_scan<P, false>(p, B, T, bulk, ws, scan_ws, status, st, nullptr, nullptr);
+}
+
 template <class S, bool REV>
 static int matn_dispatch(int N, int64_t B, int64_t T, const void* A, int A_batched, int A_timevar, const void* zi,
                          const void* x, void* y, void* zf, void* ws, int64_t wsb, uint32_t* status, cudaStream_t st) {
+  if (!A_timevar && g_matn_lti_tables) {
+    const int rc = N <= 4 ? matn_lti_run<S, 4, REV>(N, B, T, A, A_batched, zi, x, y, zf, ws, wsb, status, st)
+                          : matn_lti_run<S, 8, REV>(N, B, T, A, A_batched, zi, x, y, zf, ws, wsb, status, st);
+    if (rc != PTB_ERR_TOO_LARGE) return rc;   // rows beyond 2^24 thread units: the general policy
+  }
   if (N <= 4) return matn_run<S, 4, REV>(N, B, T, A, A_batched, A_timevar, zi, x, y, zf, ws, wsb, status, st);
   return matn_run<S, 8, REV>(N, B, T, A, A_batched, A_timevar, zi, x, y, zf, ws, wsb, status, st);
+}
+
+template <class S, int NMAX>
+static int64_t matn_ws_all(int64_t B, int64_t T) {
+  const int64_t general = std::max(matn_ws<MatNP<S, NMAX, false>>(B, T), matn_ws<MatNP<S, NMAX, true>>(B, T));
+  const int64_t lti = align_up(std::max(matn_ws<MatNLtiP<S, NMAX, false>>(B, T), matn_ws<MatNLtiP<S, NMAX, true>>(B, T)), 256) +
+                      matn_lti_table_bytes<S, NMAX>(B);
+  return std::max(general, lti);
 }
 
 }  // namespace ptb
@@ -55,13 +117,15 @@ extern "C" {
 
 int64_t ptb_recur_n_workspace_bytes(int dtype, int N, int64_t B, int64_t T) {
   if (B <= 0 || T <= 0 || N < 1 || N > 8) return 0;
-  if (dtype == PTB_F32)
-    return N <= 4 ? std::max(matn_ws<MatNP<float, 4, false>>(B, T), matn_ws<MatNP<float, 4, true>>(B, T))
-                  : std::max(matn_ws<MatNP<float, 8, false>>(B, T), matn_ws<MatNP<float, 8, true>>(B, T));
-  if (dtype == PTB_F64)
-    return N <= 4 ? std::max(matn_ws<MatNP<double, 4, false>>(B, T), matn_ws<MatNP<double, 4, true>>(B, T))
-                  : std::max(matn_ws<MatNP<double, 8, false>>(B, T), matn_ws<MatNP<double, 8, true>>(B, T));
+  if (dtype == PTB_F32) return N <= 4 ? matn_ws_all<float, 4>(B, T) : matn_ws_all<float, 8>(B, T);
+  if (dtype == PTB_F64) return N <= 4 ? matn_ws_all<double, 4>(B, T) : matn_ws_all<double, 8>(B, T);
   return 0;
+}
+
+int ptb_recur_n_set_policy(int policy) {
+  if (policy < 0 || policy > 1) return PTB_ERR_ARG;
+  g_matn_lti_tables = policy == 0 ? 1 : 0;
+  return PTB_OK;
 }
 
 int ptb_recur_n_fwd(int dtype, int N, int64_t B, int64_t T, const void* A, int A_batched, int A_timevar,

@@ -25,6 +25,16 @@ def _load(tag):
     return cases
 
 
+@pytest.fixture(autouse=True, params=[0, 1], ids=["power-tables", "general"])
+def constant_matrix_policy(request):
+    """Constant matrices run on one of two kernel families (a table of matrix powers per row, or the
+    general per-sample kernels): every case here runs on both."""
+    from philtorch_b200 import _lib
+    assert _lib.lib.ptb_recur_n_set_policy(request.param) == 0
+    yield request.param
+    assert _lib.lib.ptb_recur_n_set_policy(0) == 0
+
+
 G = {"f32": _load("f32"), "f64": _load("f64")}
 REC = sorted(k for k in G["f64"] if k.startswith("n"))
 FIL = sorted(k for k in G["f64"] if k.startswith("lfilter"))
@@ -67,7 +77,7 @@ def _loop(A, zi, x, lpv):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
-@pytest.mark.parametrize("n,T", [(3, 1537), (4, 4096), (5, 1000), (7, 517), (8, 2050)])
+@pytest.mark.parametrize("n,T", [(3, 1537), (4, 4096), (5, 1000), (7, 517), (8, 2050), (4, 20011), (8, 9001), (6, 1)])
 @pytest.mark.parametrize("lpv", [True, False])
 def test_many_tiles_against_loop(dtype, n, T, lpv):
     """Rows of several tiles, lengths that are not multiples of the tile or of 16 bytes: forward and
