@@ -323,6 +323,13 @@ int ptb_lpv_recur2_fixup_bwd(int dtype, int64_t B, int64_t nseg, int64_t L, cons
  * ptb_recur_n_set_policy(1) sends them to the general kernels instead (process-wide; tests). */
 int64_t ptb_recur_n_workspace_bytes(int dtype, int N, int64_t B, int64_t T);
 int ptb_recur_n_set_policy(int policy);
+/* grad_A of a constant matrix (LTIMatrixRecurrence.backward, philtorch/lti/ssm.py:84-92):
+ *   partial[b][c] = sum over the samples t of time chunk c of  g[b,t] (x) h[b,t-1],   h[b,-1] = zi[b];
+ * partial is (B, ptb_outer_prev_sum_chunks(B, T), N, N) and the caller adds the chunks of a row (and the
+ * rows, when the matrix is shared).  Reads g and h (B,T,N) once; no workspace. */
+int64_t ptb_outer_prev_sum_chunks(int64_t B, int64_t T);
+int ptb_outer_prev_sum(int dtype, int N, int64_t B, int64_t T, const void* g, const void* h, const void* zi,
+                       void* partial, ptb_stream_t stream);
 int ptb_recur_n_fwd(int dtype, int N, int64_t B, int64_t T, const void* A, int A_batched, int A_timevar,
                     const void* zi, const void* x, void* y, void* zf, void* workspace, int64_t workspace_bytes,
                     uint32_t* status, ptb_stream_t stream);

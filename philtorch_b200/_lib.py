@@ -83,6 +83,10 @@ lib.ptb_lpv_recur_fwd_carry.restype = _i32
 
 lib.ptb_recur_n_workspace_bytes.argtypes = [_i32, _i32, _i64, _i64]
 lib.ptb_recur_n_workspace_bytes.restype = _i64
+lib.ptb_outer_prev_sum_chunks.argtypes = [_i64, _i64]
+lib.ptb_outer_prev_sum_chunks.restype = _i64
+lib.ptb_outer_prev_sum.argtypes = [_i32, _i32, _i64, _i64, _vp, _vp, _vp, _vp, _vp]
+lib.ptb_outer_prev_sum.restype = _i32
 lib.ptb_recur_n_set_policy.argtypes = [_i32]
 lib.ptb_recur_n_set_policy.restype = _i32
 lib.ptb_recur_n_fwd.argtypes = [_i32, _i32, _i64, _i64, _vp, _i32, _i32, _vp, _vp, _vp, _vp] + _tail

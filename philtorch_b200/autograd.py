@@ -194,9 +194,10 @@ class LTIMatrixRecurrence(Function):
             # one reversed scan on the kernels; grad_A is an (n x T)(T x n) product per row
             g, c0 = _ops.recur_n_adj(A, grad_y, None, False)
             gA = None
-            if need_A:
-                prev = _prev_states2(zi, y)
-                gA = g.flatten(0, 1).T @ prev.flatten(0, 1) if A.dim() == 2 else g.mT @ prev
+            if need_A:   # sum_t g[t] (x) h[t-1], read once on the way (no shifted copy, no skinny GEMM)
+                gA = _ops.outer_prev_sum(g, y, zi)
+                if A.dim() == 2:
+                    gA = gA.sum(0)
             return gA, (c0 if need_zi else None), (g if need_x else None)
         AmT = A.mT
         g = LTIMatrixRecurrence.apply(AmT, torch.zeros_like(zi), grad_y.flip(1)).flip(1)

@@ -122,6 +122,37 @@ int64_t ptb_recur_n_workspace_bytes(int dtype, int N, int64_t B, int64_t T) {
   return 0;
 }
 
+int64_t ptb_outer_prev_sum_chunks(int64_t B, int64_t T) {
+  if (B <= 0 || T <= 0) return 0;
+  // enough blocks to fill the device, chunks of at least 4096 samples
+  const int64_t want = (8 * 148 + B - 1) / B;
+  const int64_t most = (T + 4095) / 4096;
+  return std::max<int64_t>(1, std::min(want, most));
+}
+
+int ptb_outer_prev_sum(int dtype, int N, int64_t B, int64_t T, const void* g, const void* h, const void* zi,
+                       void* partial, ptb_stream_t stream) {
+  if (B < 0 || T < 0 || N < 1 || N > 8) return PTB_ERR_ARG;
+  if (B == 0 || T == 0) return PTB_OK;
+  if (!g || !h || !zi || !partial) return PTB_ERR_ARG;
+  const int64_t chunks = ptb_outer_prev_sum_chunks(B, T);
+  const int64_t chunk_len = (T + chunks - 1) / chunks;
+  if (B * chunks >= 0x7FFFFFFFll) return PTB_ERR_TOO_LARGE;
+  const unsigned grid = (unsigned)(B * chunks);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == PTB_F32) {
+    if (N <= 4) outer_prev_sum_kernel<float, 4><<<grid, kOuterNT, 0, st>>>((const float*)g, (const float*)h, (const float*)zi, (float*)partial, N, T, (int)chunks, chunk_len);
+    else outer_prev_sum_kernel<float, 8><<<grid, kOuterNT, 0, st>>>((const float*)g, (const float*)h, (const float*)zi, (float*)partial, N, T, (int)chunks, chunk_len);
+  } else if (dtype == PTB_F64) {
+    if (N <= 4) outer_prev_sum_kernel<double, 4><<<grid, kOuterNT, 0, st>>>((const double*)g, (const double*)h, (const double*)zi, (double*)partial, N, T, (int)chunks, chunk_len);
+    else outer_prev_sum_kernel<double, 8><<<grid, kOuterNT, 0, st>>>((const double*)g, (const double*)h, (const double*)zi, (double*)partial, N, T, (int)chunks, chunk_len);
+  } else {
+    return PTB_ERR_ARG;
+  }
+  PTB_CUDA(cudaGetLastError());
+  return PTB_OK;
+}
+
 int ptb_recur_n_set_policy(int policy) {
   if (policy < 0 || policy > 1) return PTB_ERR_ARG;
   g_matn_lti_tables = policy == 0 ? 1 : 0;

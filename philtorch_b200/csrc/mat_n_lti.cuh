@@ -341,4 +341,69 @@ struct MatNLti : MatNLtiAlg<S, NMAX> {
   }
 };
 
+// ---- gradient of a constant matrix: grad_A[r] = sum_t g[r,t] (x) h[r,t-1], h[r,-1] = zi[r] --------------
+// (philtorch/lti/ssm.py:67-96 forms it as a matrix product of the time-reversed scan's output with the
+// shifted states.)  One block per (row, time chunk): every thread accumulates the NMAX x NMAX outer
+// products of its samples in registers, the block adds them up (warp shuffles, then shared memory, in
+// a fixed order) and writes one partial matrix; the caller sums the partials of a row.  Reads g and h
+// once, no shifted copy of h.
+constexpr int kOuterNT = 256;
+
+template <class S, int NMAX>
+__global__ void __launch_bounds__(kOuterNT)
+outer_prev_sum_kernel(const S* __restrict__ g, const S* __restrict__ h, const S* __restrict__ zi, S* __restrict__ partial,
+                      int N, int64_t T, int chunks, int64_t chunk_len) {
+  constexpr int NN = NMAX * NMAX;
+  constexpr int VW = Vec16<S>::V;
+  __shared__ S red[kOuterNT / 32][NN];
+  const int64_t row = blockIdx.x / chunks;
+  const int chunk = (int)(blockIdx.x % chunks);
+  const int64_t c0 = (int64_t)chunk * chunk_len, c1 = (c0 + chunk_len < T) ? c0 + chunk_len : T;
+  const S* gr = g + row * T * N;
+  const S* hr = h + row * T * N;
+  S acc[NN];
+#pragma unroll
+  for (int i = 0; i < NN; ++i) acc[i] = S(0);
+  const bool vec = N == NMAX && ((reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(h)) & 15u) == 0;
+  for (int64_t t = c0 + threadIdx.x; t < c1; t += kOuterNT) {
+    S gv[NMAX], hv[NMAX];
+    if (vec) {
+#pragma unroll
+      for (int i = 0; i < NMAX; i += VW) {
+        VecIO<S, VW>::ld(reinterpret_cast<const unsigned char*>(gr + t * NMAX + i), gv + i);
+        if (t > 0) VecIO<S, VW>::ld(reinterpret_cast<const unsigned char*>(hr + (t - 1) * NMAX + i), hv + i);
+      }
+      if (t == 0) {
+#pragma unroll
+        for (int i = 0; i < NMAX; ++i) hv[i] = zi[row * N + i];
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < NMAX; ++i) {
+        gv[i] = i < N ? gr[t * N + i] : S(0);
+        hv[i] = i < N ? (t > 0 ? hr[(t - 1) * N + i] : zi[row * N + i]) : S(0);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < NMAX; ++i)
+#pragma unroll
+      for (int j = 0; j < NMAX; ++j) acc[i * NMAX + j] += gv[i] * hv[j];
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int i = 0; i < NN; ++i) {
+    S a = acc[i];
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) a += __shfl_down_sync(0xffffffffu, a, d);
+    if (lane == 0) red[warp][i] = a;
+  }
+  __syncthreads();
+  if (threadIdx.x < NN) {
+    S a = S(0);
+    for (int w = 0; w < kOuterNT / 32; ++w) a += red[w][threadIdx.x];
+    const int i = threadIdx.x / NMAX, j = threadIdx.x % NMAX;
+    if (i < N && j < N) partial[((row * chunks + chunk) * N + i) * N + j] = a;
+  }
+}
+
 }  // namespace ptb

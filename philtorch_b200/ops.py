@@ -463,6 +463,37 @@ def _(A, gy, g_in, timevar):
     return torch.empty_like(gy, memory_format=torch.contiguous_format), gy.new_empty(gy.shape[0], gy.shape[2])
 
 
+_LIB.define("outer_prev_sum(Tensor g, Tensor h, Tensor zi) -> Tensor", tags=_TAGS)
+
+
+def _outer_prev_sum(g: Tensor, h: Tensor, zi: Tensor) -> Tensor:
+    """(B,n,n): sum over t of g[b,t] (x) h[b,t-1] with h[b,-1] = zi[b] (grad_A of a constant matrix)."""
+    dev = _lib.require_cuda(g, h, zi)
+    torch._check(g.dim() == 3 and h.shape == g.shape and zi.shape == (g.shape[0], g.shape[2]),
+                 lambda: "g, h must be (B,T,n) and zi (B,n).")
+    torch._check(1 <= g.shape[2] <= MAX_STATE_DIM, lambda: f"state dimension above {MAX_STATE_DIM}")
+    if h.dtype != g.dtype or zi.dtype != g.dtype:
+        raise RuntimeError("g, h and zi must have the same scalar type")
+    B, T, n = g.shape
+    if not (B and T):
+        return g.new_zeros(B, n, n)
+    g_c, h_c, zi_c = g.contiguous(), h.contiguous(), zi.contiguous()
+    chunks = lib.ptb_outer_prev_sum_chunks(B, T)
+    part = g.new_empty(B, chunks, n, n)
+    with torch.cuda.device(dev):
+        _lib.check(lib.ptb_outer_prev_sum(_lib.dtype_code(g), n, B, T, ptr(g_c), ptr(h_c), ptr(zi_c), ptr(part),
+                                          torch.cuda.current_stream(dev).cuda_stream), "ptb_outer_prev_sum")
+    return part.sum(1)
+
+
+_LIB.impl("outer_prev_sum", _outer_prev_sum, "CUDA")
+
+
+@torch.library.register_fake("philtorch_b200::outer_prev_sum")
+def _(g, h, zi):
+    return g.new_empty(g.shape[0], g.shape[2], g.shape[2])
+
+
 # =============================================================================== TDF-II section
 _LIB.define("biquad_tdf2(Tensor b, Tensor a, Tensor? zi, Tensor x) -> (Tensor, Tensor)", tags=_TAGS)
 _LIB.define("biquad_tdf2_bwd(Tensor b, Tensor a, Tensor x, Tensor y, Tensor gy, Tensor? gzf, bool need_coef, "
@@ -1006,5 +1037,5 @@ for _name in ("lti_recur", "lti_recur_bwd", "lpv_recur", "lpv_recur_bwd", "lti_r
               "sos_cascade", "sos_cascade_bwd", "lpv_biquad_df2", "lpv_biquad_df2_bwd",
               "lpv_biquad_tdf2", "lpv_biquad_tdf2_bwd", "comb", "comb_bwd", "lti_recur_reverse_fused",
               "modal_mix", "modal_mix_bwd", "modal_drive", "recur_n", "lti_recur_n", "recur_n_adj", "modal_bank",
-              "modal_bank_bwd"):
+              "modal_bank_bwd", "outer_prev_sum"):
     _LIB.impl(_name, _no_backend(_name), "CPU")
