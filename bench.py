@@ -1087,6 +1087,8 @@ def run_profile_case(args):
       half     first-order per-sample recurrence on float16 arrays, forward + backward, B=64, T=2^20
       modal    fused bank of 4 complex modes, forward + backward, B=32, T=2^20
       dense    4x4 per-sample recurrence forward + adjoint scan, fp32, B=16, T=2^18
+      dense-lti  8x8 constant-matrix recurrence forward + adjoint scan + grad_A sums, fp32, B=64, T=2^17
+      segments2  2x2 per-sample recurrence cut into segments, fwd+bwd, fp32, B=16, T=2^20
       fixup    8 rows of 2^24 samples cut into 32 segments: zero-start scans, fold, fix-up, fp32"""
     import math
 
@@ -1133,6 +1135,22 @@ def run_profile_case(args):
         def step():
             y = ops.recur_n(A, zi, x)
             return ops.recur_n_adj(A, gy, None, True)
+    elif case == "dense-lti":
+        Bn, Tn, n = 64, 1 << 17, 8
+        A = torch.randn(Bn, n, n, device=dev, generator=g) * (0.5 / n ** 0.5)
+        zi = torch.randn(Bn, n, device=dev, generator=g)
+        x, gy = torch.randn(Bn, Tn, n, device=dev, generator=g), torch.randn(Bn, Tn, n, device=dev, generator=g)
+
+        def step():
+            y = ops.lti_recur_n(A, zi, x)
+            g_, _ = ops.recur_n_adj(A, gy, None, False)
+            return ops.outer_prev_sum(g_, y, zi)
+    elif case == "segments2":
+        w = workloads.lpv_second_order(B=16, T=1 << 20, device=dev)
+        A2, x2, zi2, gy2 = w["A"].requires_grad_(), w["x"].requires_grad_(), w["zi"], w["gy"]
+
+        def step():
+            return torch.autograd.grad(ptb.lpv.state_space_recursion(A2, zi2, x2), (A2, x2), gy2)
     elif case == "fixup":
         w = workloads.long_first_order(B=8, T=1 << 24, device=dev)
         a, x, gy = w["a"].requires_grad_(), w["x"].requires_grad_(), w["gy"]
@@ -1159,7 +1177,7 @@ def main():
     ap.add_argument("--no-configs", action="store_true", dest="no_configs",
                     help="headline workload only (skip the five-configuration / strong-scaling entries)")
     ap.add_argument("--profile-case", default=None, dest="profile_case",
-                    help="reduced case for a profiler capture: biquad | half | modal | dense | fixup (one GPU)")
+                    help="reduced case for a profiler capture: biquad | half | modal | dense | dense-lti | segments2 | fixup (one GPU)")
     ap.add_argument("--time-sharded", action="store_true",
                     help="secondary workload: B=8 long rows split along time over the ranks")
     ap.add_argument("--log2-T", type=int, default=28, dest="log2_T", help="total row length of --time-sharded")

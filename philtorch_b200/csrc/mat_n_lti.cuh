@@ -365,8 +365,12 @@ outer_prev_sum_kernel(const S* __restrict__ g, const S* __restrict__ h, const S*
 #pragma unroll
   for (int i = 0; i < NN; ++i) acc[i] = S(0);
   const bool vec = N == NMAX && ((reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(h)) & 15u) == 0;
-  for (int64_t t = c0 + threadIdx.x; t < c1; t += kOuterNT) {
-    S gv[NMAX], hv[NMAX];
+  auto fetch = [&](int64_t t, S* gv, S* hv) {
+    if (t >= c1) {   // beyond the chunk: contributes nothing
+#pragma unroll
+      for (int i = 0; i < NMAX; ++i) { gv[i] = S(0); hv[i] = S(0); }
+      return;
+    }
     if (vec) {
 #pragma unroll
       for (int i = 0; i < NMAX; i += VW) {
@@ -384,10 +388,16 @@ outer_prev_sum_kernel(const S* __restrict__ g, const S* __restrict__ h, const S*
         hv[i] = i < N ? (t > 0 ? hr[(t - 1) * N + i] : zi[row * N + i]) : S(0);
       }
     }
+  };
+  // two samples per trip: their loads are in flight together
+  for (int64_t t = c0 + threadIdx.x; t < c1; t += 2 * kOuterNT) {
+    S g0[NMAX], h0[NMAX], g1[NMAX], h1[NMAX];
+    fetch(t, g0, h0);
+    fetch(t + kOuterNT, g1, h1);
 #pragma unroll
     for (int i = 0; i < NMAX; ++i)
 #pragma unroll
-      for (int j = 0; j < NMAX; ++j) acc[i * NMAX + j] += gv[i] * hv[j];
+      for (int j = 0; j < NMAX; ++j) acc[i * NMAX + j] += g0[i] * h0[j] + g1[i] * h1[j];
   }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
