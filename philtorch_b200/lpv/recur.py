@@ -39,9 +39,10 @@ def linear_recurrence(a: Tensor, init: Tensor, x: Tensor, *, unroll_factor: int 
         raise ValueError("Unroll factor must be >= 1")
     if init.dim() == 0 or init.size(0) != batch_size:
         init = init.expand(batch_size)
-    if x.is_cuda and a.dim() == 2 and not x.is_complex():
+    if x.is_cuda and a.dim() == 2 and not x.is_complex() and not torch.compiler.is_compiling():
         # a handful of long rows: cut into segments the kernels see as independent rows (the tiles of
-        # one row wait on one another, so few rows leave most of the memory bandwidth unused)
+        # one row wait on one another, so few rows leave most of the memory bandwidth unused); the
+        # segmented Function drives the library directly, so a traced graph keeps the plain op
         from .. import sharded
 
         S = sharded.auto_segments(batch_size, x.size(1), True)

@@ -32,7 +32,8 @@ def _ext_ss_recur(A: Tensor, zi: Tensor, x: Tensor, *, out_idx: Optional[int] = 
         y = LPVRecurrence.apply(A[..., 0, 0], zi.squeeze(-1), xs).unsqueeze(-1)
     elif M == 2:
         S = 1
-        if A.dim() == 4 and x.is_cuda and x.dtype in (torch.float32, torch.float64):
+        if (A.dim() == 4 and x.is_cuda and x.dtype in (torch.float32, torch.float64)
+                and not torch.compiler.is_compiling()):   # the segmented Function drives the library directly
             # a handful of long rows: cut into segments the kernels see as independent rows (the tiles of
             # one row wait on one another, so few rows leave most of the memory bandwidth unused)
             S = sharded.auto_segments2(x.size(0), x.size(1))
