@@ -68,19 +68,38 @@ struct MatNLtiAlg {
     m.v[NMAX] = LenCodec<S>::enc(0);
     return m;
   }
-  // o = M v for the dense row-major matrix at table offset `off` (scalars, relative to the powers)
+  // o = M v for the matrix at table offset `off` (scalars, relative to the powers).  Table matrices are
+  // stored with their rows interleaved in pairs, element (r, q) at ((r / 2) * NMAX + q) * 2 + r % 2, so
+  // one 16-byte load yields {M[2p][q], M[2p+1][q], M[2p][q+1], M[2p+1][q+1]}: in float32 the two rows of
+  // a pair advance together with packed multiply-adds (fma.rn.f32x2: half the arithmetic instructions).
   static __device__ __forceinline__ void matvec(Ctx c, int off, const S* v, S* o) {
 #pragma unroll
-    for (int r = 0; r < NMAX; ++r) {
-      S acc = S(0);
+    for (int p = 0; p < NMAX / 2; ++p) {
+      if constexpr (std::is_same<S, float>::value) {
+        float2 acc = make_float2(0.f, 0.f);
 #pragma unroll
-      for (int q = 0; q < NMAX; q += 4) {
-        S m[4];
-        if (c.shared) Ld4<S, true>::ld(c.p + off + r * NMAX + q, m);
-        else Ld4<S, false>::ld(c.p + off + r * NMAX + q, m);
-        acc += m[0] * v[q] + m[1] * v[q + 1] + m[2] * v[q + 2] + m[3] * v[q + 3];
+        for (int q = 0; q < NMAX; q += 2) {
+          float m[4];
+          if (c.shared) Ld4<float, true>::ld(c.p + off + (p * NMAX + q) * 2, m);
+          else Ld4<float, false>::ld(c.p + off + (p * NMAX + q) * 2, m);
+          acc = __ffma2_rn(make_float2(m[0], m[1]), make_float2(v[q], v[q]), acc);
+          acc = __ffma2_rn(make_float2(m[2], m[3]), make_float2(v[q + 1], v[q + 1]), acc);
+        }
+        o[2 * p] = acc.x;
+        o[2 * p + 1] = acc.y;
+      } else {
+        S a0 = S(0), a1 = S(0);
+#pragma unroll
+        for (int q = 0; q < NMAX; q += 2) {
+          S m[4];
+          if (c.shared) Ld4<S, true>::ld(c.p + off + (p * NMAX + q) * 2, m);
+          else Ld4<S, false>::ld(c.p + off + (p * NMAX + q) * 2, m);
+          a0 += m[0] * v[q] + m[2] * v[q + 1];
+          a1 += m[1] * v[q] + m[3] * v[q + 1];
+        }
+        o[2 * p] = a0;
+        o[2 * p + 1] = a1;
       }
-      o[r] = acc;
     }
   }
   // v <- A^(n SPT) v
@@ -145,9 +164,10 @@ __global__ void matn_lti_setup_kernel(const S* __restrict__ A, int64_t a_row_str
   const int r = tid / NMAX, c = tid % NMAX;
   const S* a = A + (int64_t)blockIdx.x * a_row_stride;
   S* out = tab + (int64_t)blockIdx.x * D::ROWTAB;
+  const int at = ((r >> 1) * NMAX + c) * 2 + (r & 1);   // rows interleaved in pairs, see MatNLtiAlg::matvec
   S val = S(0);
   if (r < N && c < N) val = REV ? a[c * N + r] : a[r * N + c];
-  out[tid] = val;
+  out[at] = val;
   A0[r][c] = (double)val;
   U[r][c] = (double)val;
   __syncthreads();
@@ -160,7 +180,7 @@ __global__ void matn_lti_setup_kernel(const S* __restrict__ A, int64_t a_row_str
     __syncthreads();
   }
   for (int i = 0; i < D::NPOW; ++i) {
-    out[NN + (size_t)i * NN + tid] = (S)U[r][c];
+    out[NN + (size_t)i * NN + at] = (S)U[r][c];
     double acc = 0.0;
     for (int q = 0; q < NMAX; ++q) acc += U[r][q] * U[q][c];
     V[r][c] = acc;
