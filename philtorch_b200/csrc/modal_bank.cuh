@@ -136,6 +136,12 @@ __device__ __forceinline__ bool bank_vec_ok(const void* a, const void* b, const 
 // real x complex products written out (a complex product with a zero imaginary part costs twice as much)
 template <class R>
 __device__ __forceinline__ void cfma_r(Cx<R>& acc, const Cx<R>& a, R x) { acc.re += a.re * x; acc.im += a.im * x; }
+// float32: both components in one packed multiply-add (fma.rn.f32x2; same rounding as two scalar ones)
+__device__ __forceinline__ void cfma_r(Cx<float>& acc, const Cx<float>& a, float x) {
+  const float2 r = __ffma2_rn(make_float2(a.re, a.im), make_float2(x, x), make_float2(acc.re, acc.im));
+  acc.re = r.x;
+  acc.im = r.y;
+}
 
 // Per-CTA tables for a thread's SPT samples (l = lam forward, conj(lam) adjoint; g = gain forward,
 // conj(coef) adjoint):  lp[m][k] = l^k, k = 0..SPT;  wt[m][j] = weight of local sample j in the
@@ -499,12 +505,19 @@ __global__ void __launch_bounds__(kBankNT, sizeof(R) == 4 ? 3 : 1) bank_backward
 #pragma unroll
   for (int j = SPT - 1; j >= 0; --j) {
     R acc = dd * gv[j];
+    Cx<R> acc2(R(0), R(0));   // sum over the modes of (g.re r.re, g.im r.im): its two halves add up to Re(conj(gain) r[t+1])
 #pragma unroll
     for (int m = 0; m < MMAX; ++m) {
       if (tb + j == p.N - 1) rin[m] = rin[m] + sm_c[5 * MMAX + m];
       const Cx<R> r1 = rin[m];                                // r[t+1]
       const Cx<R> g = sm_c[MMAX + m];
-      acc += g.re * r1.re + g.im * r1.im;                     // Re(conj(gain) r[t+1])
+      if constexpr (std::is_same<R, float>::value) {
+        const float2 t = __ffma2_rn(make_float2(g.re, g.im), make_float2(r1.re, r1.im), make_float2(acc2.re, acc2.im));
+        acc2.re = t.x;
+        acc2.im = t.y;
+      } else {
+        acc += g.re * r1.re + g.im * r1.im;                   // Re(conj(gain) r[t+1])
+      }
       const Cx<R> wc = cj(wprev[(m * SPT + j) * kBankNT + threadIdx.x]);
       if (p.need & 1) cfma_r(g_gain[m], r1, xv[j]);
       if (p.need & 2) g_lam[m] += r1 * wc;
@@ -513,7 +526,7 @@ __global__ void __launch_bounds__(kBankNT, sizeof(R) == 4 ? 3 : 1) bank_backward
       cfma_r(rin[m], cj(sm_c[2 * MMAX + m]), gv[j]);
     }
     g_d += gv[j] * xv[j];
-    gxv[j] = acc;
+    gxv[j] = acc + (acc2.re + acc2.im);
   }
   bank_store<R, SPT>(p.y + row * p.N, p.N, tb, vec, gxv);
 

@@ -668,6 +668,8 @@ chain_bwd_kernel(const ChainBwdParams<S> p, const Workspace ws, const uint32_t B
         if (p.want_coef) {
           const unsigned char* xs = zbuf(k) + (size_t)tpos * SPT * sizeof(S);
           const unsigned char* ys = zbuf(k + 1) + (size_t)tpos * SPT * sizeof(S);
+          // float32: (s1, s2) and (s3, s4) as packed pairs, two sums per fma.rn.f32x2 (1.074 -> 1.055 ms at K = 6)
+          float2 sx = make_float2(0.f, 0.f), sy = make_float2(0.f, 0.f);
 #pragma unroll
           for (int cc = CH - 1; cc >= 0; --cc) {
             S xv[V], yv[V];
@@ -680,16 +682,23 @@ chain_bwd_kernel(const ChainBwdParams<S> p, const Workspace ws, const uint32_t B
                 const S gj = g[j];
                 g[j] = c.b0 * gj + c.B0 * l0 + c.B1 * l1;
                 s0 += gj * xv[q];
-                s1 += xv[q] * l0;
-                s2 += xv[q] * l1;
-                s3 += yv[q] * l0;
-                s4 += yv[q] * l1;
+                if constexpr (std::is_same<S, float>::value) {
+                  const float2 l = make_float2(l0, l1);
+                  sx = __ffma2_rn(make_float2(xv[q], xv[q]), l, sx);
+                  sy = __ffma2_rn(make_float2(yv[q], yv[q]), l, sy);
+                } else {
+                  s1 += xv[q] * l0;
+                  s2 += xv[q] * l1;
+                  s3 += yv[q] * l0;
+                  s4 += yv[q] * l1;
+                }
                 const S t = c.na2 * l1 + gj;
                 l1 = l0;
                 l0 = c.na1 * l0 + t;
               }
             }
           }
+          if constexpr (std::is_same<S, float>::value) { s1 += sx.x; s2 += sx.y; s3 += sy.x; s4 += sy.y; }
         } else {
 #pragma unroll
           for (int j = SPT - 1; j >= 0; --j) {
