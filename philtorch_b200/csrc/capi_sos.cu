@@ -46,6 +46,11 @@ template <class S, int K> using SosBwdP = SosBwd<S, K, PTB_SOS_BWD_CH, PTB_SOS_B
 #endif
 template <class S, int K> using ChainF = ChainCfg<S, K, PTB_CHAINF_CH, PTB_CHAINF_NT, PTB_CHAINF_NOUT, PTB_CHAINF_MINB>;
 template <class S, int K> using ChainB = ChainCfg<S, K, PTB_CHAINB_CH, PTB_CHAINB_NT, 1, PTB_CHAINB_MINB>;
+// Few rows: a row keeps at most K + 1 tiles busy, so the CTAs that do run should be larger (measured,
+// K = 6, T = 2^18, fwd+bwd: 64 rows 0.504 -> 0.436 ms, 32 rows 0.431 -> 0.354 ms, 128 rows 0.644 -> 0.624 ms)
+template <class S, int K> using ChainFFew = ChainCfg<S, K, 9, 128, 1, 4>;
+template <class S, int K> using ChainBFew = ChainCfg<S, K, 9, 128, 1, 3>;
+static bool chain_few_rows(int64_t B, int sms) { return 10 * B < 11 * (int64_t)sms; }
 
 // 0: pick by batch size, 1: always the decoupled kernels, 2: always the chained kernels
 static int g_sos_mode = 0;
@@ -60,24 +65,27 @@ static int device_sms(int* sms) {
   *sms = cached[dev];
   return PTB_OK;
 }
-// A row keeps at most K tiles busy in the chained kernels (staggered by one section), so they need
-// enough rows to fill the GPU; measured on B200 (K = 6) they win from about 64 rows on.
-static bool use_chain(int64_t B, int sms) { return g_sos_mode == 2 || (g_sos_mode == 0 && 8 * B >= 3 * (int64_t)sms); }
+// A row keeps at most K + 1 tiles busy in the chained kernels (staggered by one section), so they need
+// enough rows to fill the GPU; measured on B200 (K = 6, with the few-row geometry) they win from about
+// 32 rows on (32 rows x 2^18: 0.354 ms against 0.449 ms decoupled; 16 rows x 2^20: 0.834 against 0.668 ms).
+static bool use_chain(int64_t B, int sms) { return g_sos_mode == 2 || (g_sos_mode == 0 && 6 * B >= (int64_t)sms); }
 
-template <class S, int K>
-static int64_t chain_ws_bytes(int64_t B, int64_t T) {
-  using CF = ChainF<S, K>;
-  using CB = ChainB<S, K>;
+template <class S, int K, class CF, class CB>
+static int64_t chain_ws_bytes_of(int64_t B, int64_t T) {
   const int64_t nf = B * ((T + CF::TILE - 1) / CF::TILE), nb = B * ((T + CB::TILE - 1) / CB::TILE);
   return std::max(align_up(B * CF::ROW * (int64_t)sizeof(S), 256) + ws_layout(nf, CF::SLOT_WORDS, 0).total,
                   align_up(B * CB::ROW * (int64_t)sizeof(S), 256) + ws_layout(nb, CB::SLOT_WORDS, 5 * K * sizeof(S)).total);
 }
-
 template <class S, int K>
-static int chain_fwd(int64_t B, int64_t T, const void* b, const void* a, int coef_batched, const void* zi,
-                     const void* x, void* y, void* mid, void* zf, void* ws, int64_t wsb, uint32_t* status,
-                     cudaStream_t st) {
-  using C = ChainF<S, K>;
+static int64_t chain_ws_bytes(int64_t B, int64_t T) {
+  return std::max(chain_ws_bytes_of<S, K, ChainF<S, K>, ChainB<S, K>>(B, T),
+                  chain_ws_bytes_of<S, K, ChainFFew<S, K>, ChainBFew<S, K>>(B, T));
+}
+
+template <class S, int K, class C>
+static int chain_fwd_cfg(int64_t B, int64_t T, const void* b, const void* a, int coef_batched, const void* zi,
+                         const void* x, void* y, void* mid, void* zf, void* ws, int64_t wsb, uint32_t* status,
+                         cudaStream_t st) {
   using L = ChainFwdSmem<C>;
   static_assert(L::kTotal <= 227 * 1024, "shared memory of an SM");
   const int64_t rows = coef_batched ? B : 1;
@@ -129,6 +137,18 @@ static int chain_fwd(int64_t B, int64_t T, const void* b, const void* a, int coe
                                                          bulk ? 1 : 0, g_wait_ns);
   PTB_CUDA(cudaGetLastError());
   return PTB_OK;
+}
+
+template <class S, int K>
+static int chain_fwd(int64_t B, int64_t T, const void* b, const void* a, int coef_batched, const void* zi,
+                     const void* x, void* y, void* mid, void* zf, void* ws, int64_t wsb, uint32_t* status,
+                     cudaStream_t st) {
+  int sms = 0;
+  const int rc = device_sms(&sms);
+  if (rc != PTB_OK) return rc;
+  if (chain_few_rows(B, sms))
+    return chain_fwd_cfg<S, K, ChainFFew<S, K>>(B, T, b, a, coef_batched, zi, x, y, mid, zf, ws, wsb, status, st);
+  return chain_fwd_cfg<S, K, ChainF<S, K>>(B, T, b, a, coef_batched, zi, x, y, mid, zf, ws, wsb, status, st);
 }
 
 template <class S, int K> struct SosCoefGrads;
@@ -231,11 +251,10 @@ struct SosCoefGrads {
   }
 };
 
-template <class S, int K>
-static int chain_bwd(int64_t B, int64_t T, const void* b, const void* a, int coef_batched, const void* x,
-                     const void* mid, const void* y, const void* gy, const void* g_zf, void* grad_x, void* grad_b,
-                     void* grad_a, void* grad_zi, void* ws, int64_t wsb, uint32_t* status, cudaStream_t st) {
-  using C = ChainB<S, K>;
+template <class S, int K, class C>
+static int chain_bwd_cfg(int64_t B, int64_t T, const void* b, const void* a, int coef_batched, const void* x,
+                         const void* mid, const void* y, const void* gy, const void* g_zf, void* grad_x, void* grad_b,
+                         void* grad_a, void* grad_zi, void* ws, int64_t wsb, uint32_t* status, cudaStream_t st) {
   using L = ChainBwdSmem<C>;
   static_assert(L::kTotal <= 227 * 1024, "shared memory of an SM");
   const int64_t rows = coef_batched ? B : 1;
@@ -296,6 +315,20 @@ static int chain_bwd(int64_t B, int64_t T, const void* b, const void* a, int coe
   SosCoefGrads<S, K> epi{static_cast<const S*>(a), rows * 2, coef_batched ? 2 : 0, static_cast<S*>(grad_b),
                          static_cast<S*>(grad_a), rows};
   return launch_reduce<S, 5 * K>(wk.partial, B, nchunks, coef_batched, epi, st);
+}
+
+template <class S, int K>
+static int chain_bwd(int64_t B, int64_t T, const void* b, const void* a, int coef_batched, const void* x,
+                     const void* mid, const void* y, const void* gy, const void* g_zf, void* grad_x, void* grad_b,
+                     void* grad_a, void* grad_zi, void* ws, int64_t wsb, uint32_t* status, cudaStream_t st) {
+  int sms = 0;
+  const int rc = device_sms(&sms);
+  if (rc != PTB_OK) return rc;
+  if (chain_few_rows(B, sms))
+    return chain_bwd_cfg<S, K, ChainBFew<S, K>>(B, T, b, a, coef_batched, x, mid, y, gy, g_zf, grad_x, grad_b, grad_a,
+                                                grad_zi, ws, wsb, status, st);
+  return chain_bwd_cfg<S, K, ChainB<S, K>>(B, T, b, a, coef_batched, x, mid, y, gy, g_zf, grad_x, grad_b, grad_a,
+                                           grad_zi, ws, wsb, status, st);
 }
 
 template <class S, int K>
