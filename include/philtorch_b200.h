@@ -95,7 +95,8 @@ int ptb_lti_recur_fwd(int dtype, int64_t B, int64_t T, const void* a, int a_batc
  *   g[t] = a*g[t+1] + gy[t];  grad_x = g;  grad_zi = a*g[0];
  *   grad_a = sum_t y[t-1]*g[t] per row, summed over rows as well when !a_batched.
  * y: forward output (B,T); gy: (B,T); g_in: optional (B,), an adjoint state a*g[T] entering from the
- * right (rows that continue on another device); grad_x: (B,T); grad_a: optional, (B,) or (1,);
+ * right (rows that continue on another device); grad_x: (B,T), optional (NULL: not written, 4 bytes
+ * per sample less traffic when only coefficient gradients are wanted); grad_a: optional, (B,) or (1,);
  * grad_zi: optional (B,). */
 int ptb_lti_recur_bwd(int dtype, int64_t B, int64_t T, const void* a, int a_batched, const void* zi,
                       int zi_batched, const void* y, const void* gy, const void* g_in, void* grad_x,
@@ -124,7 +125,8 @@ int ptb_lpv_recur_fwd(int dtype, int64_t B, int64_t T, const void* a, int a_batc
 /* Fused adjoint; replaces MatrixRecurrence.backward with M = 1 (philtorch/lpv/ssm.py:64-99),
  * which materialises transposed, rolled and flipped copies of the coefficients.
  *   g[t] = a[t+1]*g[t+1] + gy[t];  grad_x = g;  grad_a[b,t] = g[t]*y[t-1];  grad_zi = a[0]*g[0].
- * grad_a: optional, always (B,T) (per row; a caller with shared coefficients sums over rows). */
+ * grad_a: optional, always (B,T) (per row; a caller with shared coefficients sums over rows);
+ * grad_x: optional (NULL: not written). */
 int ptb_lpv_recur_bwd(int dtype, int64_t B, int64_t T, const void* a, int a_batched, const void* zi,
                       int zi_batched, const void* y, const void* gy, const void* g_in, void* grad_x,
                       void* grad_a, void* grad_zi, void* workspace, int64_t workspace_bytes,

@@ -50,7 +50,7 @@ class LTIRecurrence(Function):
         a, init, out = ctx.saved_tensors
         need_a, need_init, need_x = ctx.needs_input_grad
         if not torch.is_grad_enabled():
-            ga, gi, gx = _ops.lti_recur_bwd(a, init, out, grad_out, None, need_a, need_init)
+            ga, gi, gx = _ops.lti_recur_bwd(a, init, out, grad_out, None, need_a, need_init, need_x)
             return _none_if_empty(ga, need_a), _none_if_empty(gi, need_init), _none_if_empty(gx, need_x)
         # differentiable form: the adjoint is the same recurrence on the reversed sequence
         # (complex data: on conj(a), with conj(y[t-1]) in the coefficient gradient; .conj() of a real
@@ -128,7 +128,7 @@ class LPVRecurrence(Function):
         a, init, out = ctx.saved_tensors
         need_a, need_init, need_x = ctx.needs_input_grad
         if not torch.is_grad_enabled():
-            ga, gi, gx = _ops.lpv_recur_bwd(a, init, out, grad_out, None, need_a, need_init)
+            ga, gi, gx = _ops.lpv_recur_bwd(a, init, out, grad_out, None, need_a, need_init, need_x)
             return _none_if_empty(ga, need_a), _none_if_empty(gi, need_init), _none_if_empty(gx, need_x)
         # g[t] = a[t+1] g[t+1] + gy[t]: coefficients shifted by one sample, then reversed
         a_rev = torch.roll(a.conj(), shifts=-1, dims=-1).flip(-1)

@@ -553,7 +553,7 @@ int ptb_lti_recur_bwd(int dtype, int64_t B, int64_t T, const void* a, int a_batc
                       uint32_t* status, ptb_stream_t stream) {
   if (B < 0 || T < 0) return PTB_ERR_ARG;
   if (B == 0 || T == 0) return PTB_OK;
-  if (!a || !gy || !grad_x || (grad_a && (!y || !zi))) return PTB_ERR_ARG;
+  if (!a || !gy || (grad_a && (!y || !zi))) return PTB_ERR_ARG;   // grad_x may be NULL (not wanted)
   if (dtype == PTB_C64 || dtype == PTB_C128)
     return cx_fo_bwd(dtype, 0, B, T, a, a_batched, zi, zi_batched, y, gy, g_in, grad_x, grad_a, grad_zi, workspace,
                      workspace_bytes, status, (cudaStream_t)stream);
@@ -583,7 +583,7 @@ int ptb_lpv_recur_bwd(int dtype, int64_t B, int64_t T, const void* a, int a_batc
                       uint32_t* status, ptb_stream_t stream) {
   if (B < 0 || T < 0) return PTB_ERR_ARG;
   if (B == 0 || T == 0) return PTB_OK;
-  if (!a || !gy || !grad_x || (grad_a && (!y || !zi))) return PTB_ERR_ARG;
+  if (!a || !gy || (grad_a && (!y || !zi))) return PTB_ERR_ARG;   // grad_x may be NULL (not wanted)
   if (dtype == PTB_C64 || dtype == PTB_C128)
     return cx_fo_bwd(dtype, 1, B, T, a, a_batched, zi, zi_batched, y, gy, g_in, grad_x, grad_a, grad_zi, workspace,
                      workspace_bytes, status, (cudaStream_t)stream);
@@ -603,7 +603,7 @@ int ptb_lpv_recur_bwd_shared(int dtype, int64_t B, int64_t T, const void* a, con
                              ptb_stream_t stream) {
   if (B < 0 || T < 0) return PTB_ERR_ARG;
   if (B == 0 || T == 0) return PTB_OK;
-  if (!a || !gy || !grad_x || !grad_a || !y || !zi) return PTB_ERR_ARG;
+  if (!a || !gy || !grad_a || !y || !zi) return PTB_ERR_ARG;   // grad_x may be NULL (not wanted)
   if (dtype == PTB_C64 || dtype == PTB_C128)
     return cx_fo_bwd(dtype, 1, B, T, a, 0, zi, zi_batched, y, gy, g_in, grad_x, grad_a, grad_zi, workspace,
                      workspace_bytes, status, (cudaStream_t)stream, 1);

@@ -313,7 +313,7 @@ struct FoBwd : ScalarAffine<S> {
         else io.load(HALO_OFF + 16 - (int)sizeof(G), p.y + row * p.T + t0 - 1, sizeof(G));
       }
     }
-    io.store(G_OFF, p.grad_x + row * p.T + t0, bytes);
+    if (p.grad_x) io.store(G_OFF, p.grad_x + row * p.T + t0, bytes);   // optional: coefficient gradients only
     if (LPV && p.want_ga)
       io.store(A_OFF, p.grad_a + row * p.ga_row_stride + t0, bytes,
                p.ga_row_stride == 0 ? (int)sizeof(typename RealOfScalar<S>::type) : 0);

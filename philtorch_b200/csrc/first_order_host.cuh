@@ -108,7 +108,7 @@ static int fo_bwd(int64_t B, int64_t T, const void* a, int a_batched, const void
   p.T = T;
   p.want_ga = grad_a != nullptr;
   p.ga_row_stride = ga_shared ? 0 : T;
-  const bool bulk = aligned16(gy) && aligned16(grad_x) && (!LPV || aligned16(a)) &&
+  const bool bulk = aligned16(gy) && (!grad_x || aligned16(grad_x)) && (!LPV || aligned16(a)) &&
                     (!p.want_ga || (aligned16(y) && (!LPV || aligned16(grad_a)))) &&
                     (T * sizeof(G)) % 16 == 0;
   if (!bulk && sizeof(G) < 4) return PTB_ERR_ARG;

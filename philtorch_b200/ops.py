@@ -89,8 +89,8 @@ def _opt(t: Optional[Tensor]) -> Optional[Tensor]:
 
 # =============================================================================== first order, LTI
 _LIB.define("lti_recur(Tensor a, Tensor zi, Tensor x) -> Tensor", tags=_TAGS)
-_LIB.define("lti_recur_bwd(Tensor a, Tensor zi, Tensor y, Tensor gy, Tensor? g_in, bool need_a, bool need_zi)"
-            " -> (Tensor, Tensor, Tensor)", tags=_TAGS)
+_LIB.define("lti_recur_bwd(Tensor a, Tensor zi, Tensor y, Tensor gy, Tensor? g_in, bool need_a, bool need_zi, "
+            "bool need_x=True) -> (Tensor, Tensor, Tensor)", tags=_TAGS)
 
 
 def _check_lti_recur(a: Tensor, zi: Tensor, x: Tensor) -> None:
@@ -117,17 +117,17 @@ def _lti_recur(a: Tensor, zi: Tensor, x: Tensor) -> Tensor:
 
 
 @_fp32_arithmetic
-def _lti_recur_bwd(a, zi, y, gy, g_in, need_a, need_zi):
+def _lti_recur_bwd(a, zi, y, gy, g_in, need_a, need_zi, need_x=True):
     dev = _lib.require_cuda(a, zi, y, gy, g_in)
     B, T = y.shape
     a_c, zi_c, y_c, gy_c, gin_c = _dense(a), _dense(zi), _dense(y), _dense(gy), _opt(g_in)
-    gx = torch.empty_like(y_c)
+    gx = torch.empty_like(y_c) if need_x else y.new_empty(0)   # not wanted: the kernel skips the store
     ga = torch.empty_like(a_c) if need_a else a.new_empty(0)   # every entry is written by the reduction
     gzi = torch.empty_like(zi_c) if need_zi else zi.new_empty(0)
     if B and T:
         _lib.call(lib.ptb_lti_recur_bwd, dev, B, T, _lib.dtype_code(y, True), B, T, ptr(a_c),
                   int(a.dim() == 1 and a.shape[0] == B), ptr(zi_c), 1, ptr(y_c), ptr(gy_c), ptr(gin_c),
-                  ptr(gx), ptr(ga) if need_a else None, ptr(gzi) if need_zi else None)
+                  ptr(gx) if need_x else None, ptr(ga) if need_a else None, ptr(gzi) if need_zi else None)
     else:
         ga.zero_()
         gzi.zero_()
@@ -145,16 +145,16 @@ def _(a, zi, x):
 
 
 @torch.library.register_fake("philtorch_b200::lti_recur_bwd")
-def _(a, zi, y, gy, g_in, need_a, need_zi):
+def _(a, zi, y, gy, g_in, need_a, need_zi, need_x=True):
     return (torch.empty_like(a) if need_a else a.new_empty(0),
             torch.empty_like(zi) if need_zi else zi.new_empty(0),
-            torch.empty_like(y, memory_format=torch.contiguous_format))
+            torch.empty_like(y, memory_format=torch.contiguous_format) if need_x else y.new_empty(0))
 
 
 # =============================================================================== first order, LPV
 _LIB.define("lpv_recur(Tensor a, Tensor zi, Tensor x) -> Tensor", tags=_TAGS)
-_LIB.define("lpv_recur_bwd(Tensor a, Tensor zi, Tensor y, Tensor gy, Tensor? g_in, bool need_a, bool need_zi)"
-            " -> (Tensor, Tensor, Tensor)", tags=_TAGS)
+_LIB.define("lpv_recur_bwd(Tensor a, Tensor zi, Tensor y, Tensor gy, Tensor? g_in, bool need_a, bool need_zi, "
+            "bool need_x=True) -> (Tensor, Tensor, Tensor)", tags=_TAGS)
 
 
 def _check_lpv_recur(a: Tensor, zi: Tensor, x: Tensor) -> None:
@@ -182,23 +182,23 @@ def _lpv_recur(a: Tensor, zi: Tensor, x: Tensor) -> Tensor:
 
 
 @_fp32_arithmetic
-def _lpv_recur_bwd(a, zi, y, gy, g_in, need_a, need_zi):
+def _lpv_recur_bwd(a, zi, y, gy, g_in, need_a, need_zi, need_x=True):
     dev = _lib.require_cuda(a, zi, y, gy, g_in)
     B, T = y.shape
     a_c, zi_c, y_c, gy_c, gin_c = _dense(a), _dense(zi), _dense(y), _dense(gy), _opt(g_in)
-    gx = torch.empty_like(y_c)
+    gx = torch.empty_like(y_c) if need_x else y.new_empty(0)   # not wanted: the kernel skips the store
     gzi = torch.empty_like(zi_c) if need_zi else zi.new_empty(0)
     if (need_a and a.dim() == 1 and B * T >= SHARED_ACCUMULATE_MIN_SAMPLES and y.dtype not in _LOW_PRECISION
             and (T * y.element_size()) % 16 == 0 and all(t.data_ptr() % 16 == 0 for t in (a_c, y_c, gy_c))):
         # coefficients shared by the rows: the kernel adds every row's tile into the one (T,) gradient
         ga = torch.zeros_like(a_c)
         _lib.call(lib.ptb_lpv_recur_bwd_shared, dev, B, T, _lib.dtype_code(y, True), B, T, ptr(a_c), ptr(zi_c), 1,
-                  ptr(y_c), ptr(gy_c), ptr(gin_c), ptr(gx), ptr(ga), ptr(gzi) if need_zi else None)
+                  ptr(y_c), ptr(gy_c), ptr(gin_c), ptr(gx) if need_x else None, ptr(ga), ptr(gzi) if need_zi else None)
         return ga, gzi, gx
     ga_rows = torch.empty_like(y_c) if need_a else a.new_empty(0)   # per-row, (B,T)
     if B and T:
         _lib.call(lib.ptb_lpv_recur_bwd, dev, B, T, _lib.dtype_code(y, True), B, T, ptr(a_c), int(a.dim() == 2),
-                  ptr(zi_c), 1, ptr(y_c), ptr(gy_c), ptr(gin_c), ptr(gx),
+                  ptr(zi_c), 1, ptr(y_c), ptr(gy_c), ptr(gin_c), ptr(gx) if need_x else None,
                   ptr(ga_rows) if need_a else None, ptr(gzi) if need_zi else None)
     elif need_zi:
         gzi.zero_()
@@ -218,10 +218,10 @@ def _(a, zi, x):
 
 
 @torch.library.register_fake("philtorch_b200::lpv_recur_bwd")
-def _(a, zi, y, gy, g_in, need_a, need_zi):
+def _(a, zi, y, gy, g_in, need_a, need_zi, need_x=True):
     return (torch.empty_like(a) if need_a else a.new_empty(0),
             torch.empty_like(zi) if need_zi else zi.new_empty(0),
-            torch.empty_like(y, memory_format=torch.contiguous_format))
+            torch.empty_like(y, memory_format=torch.contiguous_format) if need_x else y.new_empty(0))
 
 
 # carry pass of a time-sharded first-order scan: (product of a, end state from zero) per row

@@ -266,3 +266,39 @@ def test_shared_coefficients_gradient_sum(dtype, T):
     assert rel_err(y, y_ref) <= t and rel_err(gx, gx_ref) <= t and rel_err(gzi, gzi_ref) <= t
     assert rel_err(ga, ga_ref) <= t * (10 if real == torch.float64 else 1)
     ptb.check_errors()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64, torch.complex64])
+@pytest.mark.parametrize("kind,a_shape", [("lti", "batched"), ("lti", "scalar"), ("lpv", "batched"), ("lpv", "shared")])
+def test_coefficient_gradients_without_grad_x(dtype, kind, a_shape):
+    """Only the coefficients (and the initial state) require gradients: the adjoint kernels are told
+    not to write grad_x at all; grad_a and grad_zi against the oracle."""
+    B, T = 5, 20000
+    g = torch.Generator().manual_seed(31)
+    real = torch.float64 if dtype == torch.float64 else torch.float32
+
+    def rnd(*s):
+        v = torch.randn(*s, generator=g, dtype=torch.float64)
+        if dtype.is_complex:
+            v = torch.complex(v, torch.randn(*s, generator=g, dtype=torch.float64))
+        return v.to(dtype)
+
+    if kind == "lti":
+        a = (rnd(B) if a_shape == "batched" else rnd(1)[0]) * 0.4
+    else:
+        a = (rnd(B, T) if a_shape == "batched" else rnd(T)) * 0.4
+    zi, x, gy = rnd(B), rnd(B, T), rnd(B, T)
+    a_, zi_ = a.to(DEV).requires_grad_(), zi.to(DEV).requires_grad_()
+    fn = ptb.lti.linear_recurrence if kind == "lti" else ptb.lpv.linear_recurrence
+    y = fn(a_, zi_, x.to(DEV))
+    ga, gzi = torch.autograd.grad(y, (a_, zi_), gy.to(DEV))
+    if kind == "lti":
+        y_r = cport.lti_recur(a, zi, x)
+        ga_r, gzi_r, _ = cport.lti_recur_bwd(a, zi, y_r, gy)
+    else:
+        y_r = cport.recur1(a, zi, x)
+        ga_r, gzi_r, _ = cport.recur1_bwd(a, zi, y_r, gy)
+    t = tol(real)
+    assert rel_err(y, y_r) <= t
+    assert rel_err(ga, ga_r.reshape(ga.shape)) <= t * 10 and rel_err(gzi, gzi_r) <= t
+    ptb.check_errors()
