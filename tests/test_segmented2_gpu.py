@@ -103,3 +103,19 @@ def test_segmented_double_backward():
     fn = lambda A_, z_, x_: sharded.SegmentedMatrixRecurrence.apply(A_, z_, x_, S)   # noqa: E731
     assert torch.autograd.gradcheck(fn, (A, zi, x))
     assert torch.autograd.gradgradcheck(fn, (A, zi, x))
+
+
+@pytest.mark.parametrize("which", ["x", "A", "zi"])
+def test_segments_partial_gradients(which):
+    """Only one of the inputs requires a gradient: against the unsegmented kernels."""
+    from philtorch_b200.autograd import MatrixRecurrence
+    B, T, S = 3, 8192, 4
+    A, zi, x, gy = _case(B, T, "contracting", False, torch.float32, seed=9)
+    ins = {"A": A.to(DEV), "zi": zi.to(DEV), "x": x.to(DEV)}
+    ins[which] = ins[which].requires_grad_()
+    y = sharded.SegmentedMatrixRecurrence.apply(ins["A"], ins["zi"], ins["x"], S)
+    g, = torch.autograd.grad(y, (ins[which],), gy.to(DEV))
+    y1 = MatrixRecurrence.apply(ins["A"], ins["zi"], ins["x"])
+    g1, = torch.autograd.grad(y1, (ins[which],), gy.to(DEV))
+    assert rel_err(y, y1.cpu()) <= 1e-5 and rel_err(g, g1.cpu()) <= 1e-5
+    ptb.check_errors()
