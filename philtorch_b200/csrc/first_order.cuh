@@ -264,6 +264,10 @@ struct FoBwdParams {
   int64_t T;
   int want_ga;
   S fuse_scale;      // FUSE: the kernel writes fuse_scale * (g + y - gy) instead of g (y = any second signal)
+  // time-invariant, small launches: the grid's last warp adds the per-tile sums up itself (no second launch)
+  G* ga_out = nullptr;     // (B,) if ga_batched else (1,)
+  int ga_batched = 0;
+  int fuse_reduce = 0;
 };
 
 // FUSE (time-invariant use): the result of the reverse-time recurrence is combined with its own
@@ -287,6 +291,29 @@ struct FoBwd : ScalarAffine<S> {
   static constexpr int LBW = LBW_;
   static constexpr bool REVERSE = true;
   static constexpr bool HAS_PARTIAL = !LPV;
+  static constexpr bool FINAL_REDUCE = !LPV && std::is_arithmetic<S>::value;   // real scalars only
+  static __device__ __forceinline__ bool wants_final_reduce(const Params& p) { return p.fuse_reduce != 0; }
+  // One warp: grad_a = sum over the tiles of a row (rows too when the coefficient is shared) of the
+  // per-tile sums, in double, every lane in a fixed order.  partial: [B][nchunks] scalars.
+  static __device__ void final_reduce(const Params& p, const void* partial, uint32_t B, uint32_t nchunks, int lane) {
+    if constexpr (FINAL_REDUCE) {
+      const volatile S* part = static_cast<const volatile S*>(partial);
+      if (p.ga_batched) {
+        for (uint32_t row = lane; row < B; row += 32) {
+          double acc = 0.0;
+          for (uint32_t c = 0; c < nchunks; ++c) acc += (double)part[(size_t)row * nchunks + c];
+          p.ga_out[row] = C::out((S)acc);
+        }
+      } else {
+        double acc = 0.0;
+        const size_t total = (size_t)B * nchunks;
+        for (size_t i = lane; i < total; i += 32) acc += (double)part[i];
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, d);
+        if (lane == 0) p.ga_out[0] = C::out((S)acc);
+      }
+    }
+  }
   static constexpr int SLOT_WORDS = Words<Map>::W;
   static constexpr int SLOT = TILE * (int)sizeof(G);
   static constexpr int G_OFF = 0;                       // gy in, grad_x out

@@ -59,6 +59,8 @@ template <bool LPV> struct FoBwdSel<float, LPV, __nv_bfloat16> { using type = Fo
 template <class S, bool LPV, class G = S> using FoFwdP = typename FoFwdSel<S, LPV, G>::type;
 template <class S, bool LPV, class G = S> using FoBwdP = typename FoBwdSel<S, LPV, G>::type;
 
+constexpr int64_t kFusedReduceMaxTiles = 2048;   // beyond this one warp would take longer than a second launch
+
 // write-out of the per-row sums of a time-invariant gradient in the storage type
 template <class S, int N, class G>
 struct StoreSumsAs {
@@ -113,11 +115,21 @@ static int fo_bwd(int64_t B, int64_t T, const void* a, int a_batched, const void
                     (T * sizeof(G)) % 16 == 0;
   if (!bulk && sizeof(G) < 4) return PTB_ERR_ARG;
   if (ga_shared && (!LPV || !bulk || sizeof(G) < 4)) return PTB_ERR_ARG;
+  // small launches: the kernel's last warp reduces the per-tile sums of grad_a itself
+  bool fused = false;
+  if constexpr (!LPV && std::is_arithmetic<S>::value) {
+    if (grad_a && B * ((T + P::TILE - 1) / P::TILE) <= kFusedReduceMaxTiles) {
+      p.ga_out = static_cast<G*>(grad_a);
+      p.ga_batched = a_batched ? 1 : 0;
+      p.fuse_reduce = 1;
+      fused = true;
+    }
+  }
   void* partial = nullptr;
   int64_t nchunks = 0;
   int rc = launch_scan<P>(p, B, T, bulk, ws, wsb, status, st, &partial, &nchunks);
   if (rc != PTB_OK) return rc;
-  if (!LPV && grad_a) {
+  if (!LPV && grad_a && !fused) {
     if constexpr (std::is_same<S, G>::value) {
       rc = launch_reduce<typename RealOf<S>::R, RealOf<S>::N>(
           partial, B, nchunks, a_batched,

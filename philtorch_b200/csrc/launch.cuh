@@ -80,6 +80,7 @@ static int launch_scan(const typename P::Params& prm, int64_t B, int64_t T, bool
   ws.error = status ? status : reinterpret_cast<uint32_t*>(w + 4);
   ws.slots = reinterpret_cast<uint64_t*>(w + l.slots_off);
   ws.partial = w + l.part_off;
+  ws.done = reinterpret_cast<uint32_t*>(w + 8);
   if (partial_out) *partial_out = ws.partial;
   if (nchunks_out) *nchunks_out = nchunks;
 

@@ -74,6 +74,14 @@ namespace ptb {
     return m;                                                                                            \
   }
 
+// Optional policy member FINAL_REDUCE = true with wants_final_reduce(prm) and
+// final_reduce(prm, partial, B, nchunks, lane): the last compute warp of the whole grid to finish adds
+// up the per-tile partial sums (one warp, fixed order) instead of a second launch.
+template <class P, class = void>
+struct FinalReduceOf { static constexpr bool value = false; };
+template <class P>
+struct FinalReduceOf<P, std::void_t<decltype(P::FINAL_REDUCE)>> { static constexpr bool value = P::FINAL_REDUCE; };
+
 // Optional policy members: EXTRA_SMEM bytes of policy-owned shared memory behind the engine's
 // (with init_extra / prefetch / finish_x hooks, see scan_kernel).
 template <class P, class = void>
@@ -124,6 +132,7 @@ struct Workspace {
   uint32_t* error;    // [1]   sticky error bits
   uint64_t* slots;    // [ntiles][P::SLOT_WORDS] zeroed before launch: {flag:32 | payload word:32}
   void* partial;      // [ntiles] P::Partial (policy specific)
+  uint32_t* done = nullptr;   // [1] zeroed before launch: compute warps that have finished (policies with a final reduction)
 };
 
 constexpr int kMaxIo = 4;
@@ -757,6 +766,19 @@ scan_kernel(const typename P::Params prm, const Workspace ws, const uint32_t B, 
     }
   }
   if constexpr (L::kExtra > 0) bulk_wait_all();   // bulk copies issued by the policy's hooks
+  if constexpr (FinalReduceOf<P>::value) {
+    if (P::wants_final_reduce(prm)) {
+      // every warp's partial sums precede its own count; the warp that completes the count sees them all
+      __threadfence();
+      uint32_t cnt = 0;
+      if (lane == 0) cnt = atomicAdd(ws.done, 1u);
+      cnt = __shfl_sync(0xffffffffu, cnt, 0);
+      if (cnt == gridDim.x * (uint32_t)NW - 1u) {
+        __threadfence();
+        P::final_reduce(prm, ws.partial, B, nchunks, lane);
+      }
+    }
+  }
   PTB_PROF_END(t_c_total, tc0);
   if (tid == 0) {
     PTB_PROF_FLUSH(8, t_c_idle); PTB_PROF_FLUSH(10, t_c_total);
