@@ -340,7 +340,10 @@ struct FoBwd : ScalarAffine<S> {
         else io.load(HALO_OFF + 16 - (int)sizeof(G), p.y + row * p.T + t0 - 1, sizeof(G));
       }
     }
-    if (p.grad_x) io.store(G_OFF, p.grad_x + row * p.T + t0, bytes);   // optional: coefficient gradients only
+    // grad_x is optional (coefficient gradients only): a store of zero bytes is skipped by the engine.  The
+    // slot itself stays unconditional: a plan whose number of stores depends on run-time data keeps the
+    // compiler from holding it in registers (measured: +2 % on the adjoint kernel).
+    io.store(G_OFF, p.grad_x + row * p.T + t0, p.grad_x ? bytes : 0u);
     if (LPV && p.want_ga)
       io.store(A_OFF, p.grad_a + row * p.ga_row_stride + t0, bytes,
                p.ga_row_stride == 0 ? (int)sizeof(typename RealOfScalar<S>::type) : 0);
