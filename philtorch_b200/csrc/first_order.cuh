@@ -330,22 +330,21 @@ struct FoBwd : ScalarAffine<S> {
   static __device__ __forceinline__ void plan(const Params& p, bool bulk, int64_t row, int64_t t0, int nvalid,
                                               IoPlan& io) {
     const uint32_t bytes = (uint32_t)nvalid * sizeof(G);
+    // every slot is planned unconditionally, with zero bytes when it is not wanted (the engine skips
+    // those): the number of copies then does not depend on run-time data and the plan stays in registers
     io.load(G_OFF, p.gy + row * p.T + t0, bytes);
     if (LPV) io.load(A_OFF, p.a + row * p.a_row_stride + t0, bytes);
-    if (FUSE && !p.want_ga) io.load(Y_OFF, p.y + row * p.T + t0, bytes);
-    if (p.want_ga) {
-      io.load(Y_OFF, p.y + row * p.T + t0, bytes);
-      if (t0 > 0) {
-        if (bulk) io.load(HALO_OFF, p.y + row * p.T + t0 - V, 16);
-        else io.load(HALO_OFF + 16 - (int)sizeof(G), p.y + row * p.T + t0 - 1, sizeof(G));
-      }
-    }
+    const bool want_y = FUSE || p.want_ga;
+    io.load(Y_OFF, p.y + row * p.T + t0, want_y ? bytes : 0u);
+    const bool halo = p.want_ga && t0 > 0;
+    if (bulk) io.load(HALO_OFF, p.y + row * p.T + t0 - V, halo ? 16u : 0u);
+    else io.load(HALO_OFF + 16 - (int)sizeof(G), p.y + row * p.T + t0 - 1, halo ? (uint32_t)sizeof(G) : 0u);
     // grad_x is optional (coefficient gradients only): a store of zero bytes is skipped by the engine.  The
     // slot itself stays unconditional: a plan whose number of stores depends on run-time data keeps the
     // compiler from holding it in registers (measured: +2 % on the adjoint kernel).
     io.store(G_OFF, p.grad_x + row * p.T + t0, p.grad_x ? bytes : 0u);
-    if (LPV && p.want_ga)
-      io.store(A_OFF, p.grad_a + row * p.ga_row_stride + t0, bytes,
+    if (LPV)
+      io.store(A_OFF, p.grad_a + row * p.ga_row_stride + t0, p.want_ga ? bytes : 0u,
                p.ga_row_stride == 0 ? (int)sizeof(typename RealOfScalar<S>::type) : 0);
   }
   static __device__ __forceinline__ State row_init(const Params& p, int64_t row) {
