@@ -192,3 +192,27 @@ def test_cspline_forms_agree(dtype, n, scipy_padding, comb_route):
     ptb.check_errors()
     assert rel_err(res[0][0], res[1][0]) <= 10 * tol(dtype)
     assert rel_err(res[0][1], res[1][1]) <= 10 * tol(dtype)
+
+
+def test_comb_large_signal_routes_agree(comb_route, monkeypatch):
+    """A signal of benchmark proportions (16 rows x 2^20 samples, delay 1000: 1048 steps of 1000
+    phases, a ragged tail of 576 samples): the default kernel choice against the folded scan, outputs
+    and all gradients."""
+    if comb_route != "folded_scan":
+        pytest.skip("compares the default choice with the folded scan once")
+    from philtorch_b200.lti import filtering
+    rows, n, delay = 16, 1 << 20, 1000
+    gen = torch.Generator(device=DEV).manual_seed(3)
+    a0 = torch.rand(rows, device=DEV, generator=gen) * 1.8 - 0.9
+    x0 = torch.randn(rows, n, device=DEV, generator=gen)
+    zi0 = torch.randn(rows, delay, device=DEV, generator=gen)
+    gy = torch.randn(rows, n, device=DEV, generator=gen)
+    out = {}
+    for route, lanes in (("kernels", 1), ("fold", 10 ** 12)):
+        monkeypatch.setattr(filtering, "COMB_KERNEL_MIN_LANES", lanes)
+        a, x, zi = a0.clone().requires_grad_(), x0.clone().requires_grad_(), zi0.clone().requires_grad_()
+        y, zf = comb_filter(a, delay, x, zi=zi)
+        out[route] = [y, zf] + list(torch.autograd.grad(y, (a, x, zi), gy))
+    ptb.check_errors()
+    for got, ref in zip(out["kernels"], out["fold"]):
+        assert rel_err(got, ref.cpu()) <= (1e-3 if got.dim() < 2 else 1e-4)
