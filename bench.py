@@ -20,6 +20,8 @@ state) over one batch of seeded synthetic input.  One JSON line is printed by ra
                    the measured copy bandwidth and of the nominal 8 TB/s, and ``parity`` =
                    max|out - ref| / max|ref| of the output and of every gradient against the CPU
                    oracle at full size.
+* ``callers``      (one GPU) the filters that reduce to first-order passes (comb_filter at 64 and 16
+                   rows, cspline, diag_state_space): ms per step and fraction of the copy bandwidth.
 
 Multi-GPU (launched by torchrun): the headline ``value`` is the batch-sharded job, every rank
 running the full per-GPU workload on its own rows (weak scaling, no data-path collective).  The
@@ -780,6 +782,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     if world == 1:
         if not args.no_configs:
             line["configs"] = run_configs(dev, args, main_entry)
+            line["callers"] = callers_entries(dev, max(3, min(args.steps, 10)), args.warmup)
         if rank == 0:
             base, _ = cpu_reference_run(steps=3, warmup=1, sample_T=1 << 18)
             line["cpu_baseline"] = base
@@ -1026,12 +1029,8 @@ def run_complex_poles(args):
                     {"dtype": "c128" if args.f64 else "c64"})
 
 
-def run_callers(args):
-    """Secondary lines for the callers that are pure first-order passes (one per invocation):
-    --comb-filter   y[t] = x[t] - a y[t-1000], B = 64, T = 2^22, fp32, fwd+bwd (grads a, x);
-    --cubic-spline  cspline coefficients (parallel form), B = 64, T = 2^22, fp32, fwd+bwd (grad x);
-    --diag-ssm      4th-order real system with complex poles through diag_state_space (B (M,), C (M,)),
-                    B = 64, T = 2^20, fp32, fwd+bwd (grads x, L)."""
+def caller_case(dev, kind: str, Bc: int):
+    """(step, workload name, algorithmic bytes per sample, samples per row) of a caller workload."""
     import math
 
     import torch
@@ -1039,18 +1038,15 @@ def run_callers(args):
     import philtorch_b200 as ptb
     from philtorch_b200.lti.interp import cspline
 
-    dev = torch.device("cuda", 0)
-    torch.cuda.set_device(dev)
     g = torch.Generator(device=dev).manual_seed(SEED_LPV + 2)
-    Bc = args.rows if args.rows != B else 64
-    if args.comb_filter:
+    if kind == "comb":
         Tc, delay = 1 << 22, 1000
         a = (torch.rand(Bc, device=dev, generator=g) * 1.8 - 0.9).requires_grad_()
         x = torch.randn(Bc, Tc, device=dev, generator=g).requires_grad_()
         gy = torch.randn(Bc, Tc, device=dev, generator=g)
         step = lambda: torch.autograd.grad(ptb.lti.comb_filter(a, delay, x), (a, x), gy)   # noqa: E731
         name, alg = f"comb_filter delay={delay} fwd+bwd (grads a, x), fp32, B={Bc}, T=2^22", 8 + 12
-    elif args.cubic_spline:
+    elif kind == "cspline":
         Tc = 1 << 22
         x = torch.randn(Bc, Tc, device=dev, generator=g).requires_grad_()
         gy = torch.randn(Bc, Tc, device=dev, generator=g)
@@ -1072,6 +1068,44 @@ def run_callers(args):
         step = lambda: torch.autograd.grad(ptb.lti.diag_state_space(x, L=L, V=V, B=Bm, C=Cm), (x, L), gy)   # noqa: E731
         name, alg = f"diag_state_space M={M} (complex pole pairs, B (M,), C (M,)) fwd+bwd (grads x, L), fp32, " \
                     f"B={Bc}, T=2^20", 8 + 8
+    return step, name, alg, Tc
+
+
+def callers_entries(dev, steps: int, warmup: int):
+    """The callers that are first-order passes, for the main line: time and fraction of the copy
+    bandwidth each (their parity is the GPU tests' business: oracle, golden vectors, scipy)."""
+    out = {}
+    for key, kind, rows in (("comb_filter", "comb", 64), ("comb_filter_16_rows", "comb", 16), ("cspline", "cspline", 64),
+                            ("diag_state_space", "diag_ssm", 64)):
+        try:
+            step, name, alg, Tc = caller_case(dev, kind, rows)
+            ms = _time_steps(step, steps, warmup, dev)
+            out[key] = _entry(name, "public API + autograd.grad", rows * Tc, ms, alg, None)
+            del step
+        except Exception as e:   # keep the headline line alive
+            out[key] = {"error": f"{type(e).__name__}: {e}"[:300]}
+        _free()
+    return out
+
+
+def run_callers(args):
+    """Secondary lines for the callers that are pure first-order passes (one per invocation):
+    --comb-filter   y[t] = x[t] - a y[t-1000], B = 64, T = 2^22, fp32, fwd+bwd (grads a, x);
+    --cubic-spline  cspline coefficients (parallel form), B = 64, T = 2^22, fp32, fwd+bwd (grad x);
+    --diag-ssm      4th-order real system with complex poles through diag_state_space (B (M,), C (M,)),
+                    B = 64, T = 2^20, fp32, fwd+bwd (grads x, L)."""
+    import math
+
+    import torch
+
+    import philtorch_b200 as ptb
+    from philtorch_b200.lti.interp import cspline
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    Bc = args.rows if args.rows != B else 64
+    kind = "comb" if args.comb_filter else ("cspline" if args.cubic_spline else "diag_ssm")
+    step, name, alg, Tc = caller_case(dev, kind, Bc)
     ms = _timed(step, args, dev)
     ptb.check_errors(dev)
     _secondary_line(args, name, Bc * Tc, ms, alg, {})
