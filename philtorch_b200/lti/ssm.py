@@ -211,9 +211,11 @@ def _eigen_basis(L: Optional[Tensor], V: Optional[Tensor], Vinv: Optional[Tensor
             V = torch.cat([torch.ones_like(rest[..., :1, 0]), rest[..., 0]], dim=-1).mT
             Vinv = torch.linalg.inv(V)
     elif V is None:
-        V = torch.linalg.inv(Vinv)
+        V = torch.linalg.inv_ex(Vinv).inverse
     elif Vinv is None:
-        Vinv = torch.linalg.inv(V)
+        # inv_ex: no error check, hence no device synchronisation per call (a singular V gives
+        # non-finite outputs where torch.linalg.inv, which the reference calls, raises)
+        Vinv = torch.linalg.inv_ex(V).inverse
     return L, V, Vinv, M
 
 
