@@ -40,6 +40,11 @@ template <class R_> struct RealOf<Cx<R_>> { using R = R_; static constexpr int N
 #define PTB_FOLTI_BWD_STAGES 3
 #define PTB_FOLTI_BWD_CTAS 1
 #endif
+// the reverse pass fused with its combination stages two inputs per tile and writes over one of them
+#ifndef PTB_FOFUSE_CH
+#define PTB_FOFUSE_CH PTB_FOLTI_BWD_CH
+#define PTB_FOFUSE_STAGES PTB_FOLTI_BWD_STAGES
+#endif
 template <class S, bool LPV, class G = S> struct FoFwdSel { using type = FoFwd<S, PTB_FO_FWD_CH, PTB_FO_FWD_STAGES, PTB_FO_FWD_CTAS, 1, true>; };
 template <class S> struct FoFwdSel<S, false, S> { using type = FoFwd<S, PTB_FOLTI_FWD_CH, PTB_FOLTI_FWD_STAGES, PTB_FOLTI_FWD_CTAS, 1, false>; };
 template <class S, bool LPV, class G = S> struct FoBwdSel { using type = FoBwd<S, PTB_FO_BWD_CH, PTB_FO_BWD_STAGES, PTB_FO_BWD_CTAS, 1, true>; };
@@ -147,7 +152,7 @@ template <class S>
 static int fo_reverse_fused(int64_t B, int64_t T, const void* a, int a_batched, const void* x, const void* second,
                             const void* g_in, double scale, void* out, void* first_state, void* ws, int64_t wsb,
                             uint32_t* status, cudaStream_t st) {
-  using P = FoBwd<S, PTB_FOLTI_BWD_CH, PTB_FOLTI_BWD_STAGES, PTB_FOLTI_BWD_CTAS, 1, false, true>;
+  using P = FoBwd<S, PTB_FOFUSE_CH, PTB_FOFUSE_STAGES, PTB_FOLTI_BWD_CTAS, 1, false, true>;
   typename P::Params p;
   p.a = static_cast<const S*>(a);
   p.a_row_stride = a_batched ? 1 : 0;

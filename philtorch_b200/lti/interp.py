@@ -36,6 +36,78 @@ def _anticausal(x: Tensor, pole: Tensor, end: Tensor) -> Tensor:
     return ReverseLTIRecurrence.apply(pole.expand(rows), end.expand(rows).contiguous(), x)
 
 
+SEGMENT_TARGET_ROWS = 256    # rows from which the scan kernels run at full rate (fewer, longer rows: -15 % at 64)
+SEGMENT_MIN_LENGTH = 1 << 14
+
+_CONSTANTS: dict = {}
+
+
+def _constants(device, dtype, terms: int):
+    """(pole as a 1-element tensor, POLE**k for k < terms, the same reversed, POLE**(k+1)), made once
+    per device, dtype and length (never kept when made while a CUDA graph is being captured)."""
+    key = (device, dtype, terms)
+    hit = _CONSTANTS.get(key)
+    if hit is not None:
+        return hit
+    r = torch.full((1,), POLE, device=device, dtype=dtype)
+    pw = r.pow(torch.arange(terms, device=device, dtype=dtype))
+    made = (r, pw, pw.flip(0).contiguous(), pw * POLE)
+    if not (device.type == "cuda" and torch.cuda.is_current_stream_capturing()):
+        _CONSTANTS[key] = made
+    return made
+
+
+def _segments(rows: int, length: int, itemsize: int) -> int:
+    """Pieces each row is cut into so that the kernels see about SEGMENT_TARGET_ROWS rows: a power of
+    two that divides the length into pieces of whole 16-byte units, none shorter than
+    SEGMENT_MIN_LENGTH.  1 = rows stay whole."""
+    S = 1
+    unit = 16 // itemsize
+    while (rows * S < SEGMENT_TARGET_ROWS and length % (2 * S) == 0
+           and (length // (2 * S)) % unit == 0 and length // (2 * S) >= max(SEGMENT_MIN_LENGTH, MIRROR_TERMS)):
+        S *= 2
+    return S
+
+
+def _causal_kernel(a: Tensor, start: Tensor, x: Tensor) -> Tensor:
+    return torch.ops.philtorch_b200.lti_recur(a, start, x)
+
+
+def _reverse_fused_kernel(a: Tensor, x: Tensor, second: Tensor, g_in: Tensor, need_first: bool):
+    return torch.ops.philtorch_b200.lti_recur_reverse_fused(a, x, second, g_in, GAIN, need_first)
+
+
+def _two_pass(x: Tensor, start: Tensor, end_of, transposed: bool):
+    """The causal recurrence over x, then the reverse-time recurrence fused with the combination
+    ``GAIN (h + g - x)``; returns the combination and the state that leaves the reverse pass at t = 0.
+
+    ``start`` (B,) is the causal state before the first sample; ``end_of(h_last)`` gives the state of
+    the reverse pass beyond the last sample, times the pole, from the causal pass's last output.
+    Few long rows are cut into pieces that the kernels treat as rows of their own: the pole is a
+    constant whose powers vanish (exactly, in floating point) within MIRROR_TERMS samples, so the state
+    entering a piece is the power sum over the MIRROR_TERMS samples next to it, in the causal pass
+    those before it and in the reverse pass those after it.  No sample is read or written twice."""
+    B, T = x.shape
+    terms = min(T, MIRROR_TERMS)
+    r, _, pw_rev, pw_pole = _constants(x.device, x.dtype, terms)
+    S = _segments(B, T, x.element_size())
+    if S == 1:
+        h = _causal_kernel(r, start, x)
+        out, first = _reverse_fused_kernel(r, x, h, end_of(h[:, -1]), transposed)
+        return out, (first if transposed else None)
+    L = T // S
+    rows = x.view(B * S, L)
+    # two matrix-vector products over strided views (no copies): every piece's last samples give the
+    # causal state entering the next piece, its first samples the reverse state entering the previous one
+    tails = (rows[:, L - terms:] @ pw_rev).view(B, S)
+    heads = (rows[:, :terms] @ pw_pole).view(B, S)
+    starts = torch.cat([start.unsqueeze(1), tails[:, :-1]], 1)
+    h = _causal_kernel(r, starts.view(-1), rows)
+    ends = torch.cat([heads[:, 1:], end_of(h.view(B, T)[:, -1]).unsqueeze(1)], 1)
+    out, first = _reverse_fused_kernel(r, rows, h, ends.view(-1), transposed)
+    return out.view(B, T), (first.view(B, S)[:, 0] if transposed else None)
+
+
 class _ParallelFormCoefficients(torch.autograd.Function):
     """The partial-fraction evaluation as two kernel passes per direction: the causal recurrence,
     then the reverse-time recurrence that also forms ``k (h + g - x)`` on its way out (20 B per
@@ -44,15 +116,17 @@ class _ParallelFormCoefficients(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x: Tensor, scipy_padding: bool) -> Tensor:
-        ops = torch.ops.philtorch_b200
-        r = torch.full((1,), POLE, device=x.device, dtype=x.dtype)
         off = 0 if scipy_padding else 1
         terms = min(x.shape[-1] - off, MIRROR_TERMS)
-        pw = r.pow(torch.arange(terms, device=x.device, dtype=x.dtype))
+        x = x.contiguous()
+        pw = _constants(x.device, x.dtype, terms)[1]
         start = x[:, off:off + terms] @ pw
-        h = ops.lti_recur(r, start, x)
-        end = h[:, -1] if scipy_padding else (h[:, -1] - x[:, -1]) / POLE
-        out, _ = ops.lti_recur_reverse_fused(r, x, h, end * POLE, GAIN, False)
+        if scipy_padding:
+            end_of = lambda h_last: h_last * POLE
+        else:
+            x_last = x[:, -1]
+            end_of = lambda h_last: h_last - x_last          # ((h - x) / POLE) * POLE
+        out, _ = _two_pass(x, start, end_of, False)
         ctx.scipy_padding = scipy_padding
         ctx.save_for_backward(x)
         return out
@@ -67,33 +141,37 @@ class _ParallelFormCoefficients(torch.autograd.Function):
                 (gx,) = torch.autograd.grad(_coefficients(xr, True, sp, fused=False), xr, grad_out,
                                             create_graph=True)
             return gx, None
-        ops = torch.ops.philtorch_b200
         G = grad_out.contiguous()
-        r = torch.full((1,), POLE, device=G.device, dtype=G.dtype)
         off = 0 if sp else 1
         terms = min(G.shape[-1] - off, MIRROR_TERMS)
-        pw = r.pow(torch.arange(terms, device=G.device, dtype=G.dtype))
-        q = ops.lti_recur(r, torch.zeros_like(G[:, 0]), G)          # transpose of the reverse-time pass
-        e_bar = q[:, -1] * POLE                                      # gradient of its end state
-        g_in = e_bar if sp else e_bar / POLE                         # ... which enters the causal pass at its last sample
-        gx, s_bar = ops.lti_recur_reverse_fused(r, G, q, g_in, GAIN, True)   # transpose of the causal pass + combine
-        gx[:, off:off + terms] += (GAIN * s_bar).unsqueeze(1) * pw   # the mirror sum that starts the causal pass
+        pw = _constants(G.device, G.dtype, terms)[1]
+        # transpose of the reverse-time pass (a causal pass from zero), whose last value times the pole
+        # is the gradient of the forward end state; that enters the transposed causal pass at its last
+        # sample (scaled by 1 / POLE without scipy's padding)
+        last = []
+        def end_of(q_last):
+            last.append(q_last)
+            return q_last * POLE if sp else q_last
+        gx, s_bar = _two_pass(G, torch.zeros_like(G[:, 0]), end_of, True)
+        # the mirror sum that starts the causal pass, and (reflect padding) the last sample's part in the end state
+        gx[:, off:off + terms].addcmul_(s_bar.unsqueeze(1), pw, value=GAIN)
         if not sp:
-            gx[:, -1] -= GAIN * e_bar / POLE
+            gx[:, -1].sub_(last[0], alpha=GAIN)
         return gx, None
 
 
 def _coefficients(x: Tensor, parallel_form: bool, scipy_padding: bool, fused: bool = True) -> Tensor:
     """philtorch/lti/interp.py:23-57.  The signal is continued by mirroring: with the sample at the
     border repeated (scipy's cspline1d) or not (torch's 'reflect' padding)."""
-    r = torch.tensor(POLE, device=x.device, dtype=x.dtype)
-    # state of the causal recurrence at t = -1: the geometric sum over the mirrored past, of which
-    # only the first terms are non-zero in floating point
     if parallel_form and fused and x.dim() == 2 and x.shape[-1] >= 2:
         return _ParallelFormCoefficients.apply(x, scipy_padding)
+    # state of the causal recurrence at t = -1: the geometric sum over the mirrored past, of which
+    # only the first terms are non-zero in floating point
     past = x if scipy_padding else x[..., 1:]
     terms = min(past.shape[-1], MIRROR_TERMS)
-    start = past[..., :terms] @ r.pow(torch.arange(terms, device=x.device, dtype=x.dtype))
+    r, pw = _constants(x.device, x.dtype, terms)[:2]   # filled on the device: no host-to-device copy
+    r = r[0]
+    start = past[..., :terms] @ pw
     h = _causal(x, r, start)
 
     if parallel_form:

@@ -69,6 +69,44 @@ def test_spline_boundaries(cpu_kernels, parallel_form, scipy_padding):
     assert rel_err(c, g["c_" + key]) <= 1e-12
 
 
+@pytest.mark.parametrize("scipy_padding", [True, False])
+def test_spline_row_pieces(cpu_kernels, monkeypatch, scipy_padding):
+    """Few long rows are cut into pieces whose entering states are power sums over the neighbouring
+    samples: with the two kernel passes replaced by the oracle, values equal the whole-row
+    composite evaluation and the gradient is the transposed map (float64, so the truncated sums are exact)."""
+    from philtorch_b200.lti import interp
+
+    def causal(a, start, x):
+        return cport.lti_recur(a.expand(x.shape[0]).contiguous(), start.contiguous(), x.contiguous())
+
+    def reverse_fused(a, x, second, g_in, need_first):
+        rows = x.shape[0]
+        a_rows = a.expand(rows).contiguous()
+        # g[t] = x[t] + a g[t+1], g[T-1] = x[T-1] + g_in: the forward oracle over the flipped signal
+        g = cport.lti_recur(a_rows, (g_in / a_rows).contiguous(), x.flip(1).contiguous()).flip(1)
+        return interp.GAIN * (g + second - x), (a_rows * g[:, 0] if need_first else x.new_empty(0))
+
+    monkeypatch.setattr(interp, "_causal_kernel", causal)
+    monkeypatch.setattr(interp, "_reverse_fused_kernel", reverse_fused)
+    monkeypatch.setattr(interp, "SEGMENT_MIN_LENGTH", 2048)
+    gen = torch.Generator().manual_seed(11)
+    x0 = torch.randn(3, 1 << 14, generator=gen, dtype=torch.float64)
+    gy = torch.randn(3, 1 << 14, generator=gen, dtype=torch.float64)
+    assert interp._segments(3, 1 << 14, 8) == 8
+    assert interp._segments(3, (1 << 14) + 2, 8) == 1 and interp._segments(300, 1 << 14, 8) == 1
+    x = x0.clone().requires_grad_()
+    c = interp._coefficients(x, True, scipy_padding, fused=True)
+    (gx,) = torch.autograd.grad(c, x, gy)
+    assert rel_err(c.detach(), interp._coefficients(x0, True, scipy_padding, fused=False)) <= 1e-12
+    # the map is linear, c = M x, so the gradient M^T gy satisfies <gy, M u> = <M^T gy, u> for any u
+    # (the stand-ins are not differentiable, the composite form gives no gradient to compare with)
+    for seed in (1, 2):
+        u = torch.randn(3, 1 << 14, generator=torch.Generator().manual_seed(seed), dtype=torch.float64)
+        lhs = (gy * interp._coefficients(u, True, scipy_padding, fused=False)).sum()
+        rhs = (gx * u).sum()
+        assert abs(lhs - rhs) <= 1e-10 * (gy.norm() * u.norm())
+
+
 def test_diag_state_space_basis(cpu_kernels):
     from philtorch_b200.lti import diag_state_space
     g = load_golden("diag_ssm_matrix_f64")

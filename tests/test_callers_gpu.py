@@ -194,6 +194,32 @@ def test_cspline_forms_agree(dtype, n, scipy_padding, comb_route):
     assert rel_err(res[0][1], res[1][1]) <= 10 * tol(dtype)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+@pytest.mark.parametrize("scipy_padding", [True, False])
+def test_cspline_row_pieces(dtype, scipy_padding, comb_route):
+    """Few long rows (3 x 2^18) run as 16 pieces per row whose entering states are power sums over the
+    neighbouring samples: against the oracle's whole-row evaluation, and values and gradients against
+    the cascaded form, which runs whole rows on other kernels."""
+    if comb_route != "folded_scan":
+        pytest.skip("independent of the comb route")
+    from philtorch_b200.lti import interp
+    rows, n = 3, 1 << 18
+    assert interp._segments(rows, n, torch.empty((), dtype=dtype).element_size()) == 16
+    gen = torch.Generator().manual_seed(17)
+    x0 = torch.randn(rows, n, generator=gen, dtype=torch.float64).to(dtype)
+    gy = torch.randn(rows, n, generator=gen, dtype=torch.float64).to(dtype).to(DEV)
+    res = []
+    for pfe in (True, False):
+        x = x0.to(DEV).requires_grad_()
+        c = cspline(x, parallel_form=pfe, scipy_padding=scipy_padding)
+        res.append((c.detach(), torch.autograd.grad(c, x, gy)[0]))
+    ptb.check_errors()
+    ref = torch.from_numpy(callers.cspline(x0.double().numpy(), scipy_padding))
+    assert rel_err(res[0][0], ref) <= tol(dtype)
+    assert rel_err(res[0][0], res[1][0]) <= 10 * tol(dtype)
+    assert rel_err(res[0][1], res[1][1]) <= 10 * tol(dtype)
+
+
 def test_comb_large_signal_routes_agree(comb_route, monkeypatch):
     """A signal of benchmark proportions (16 rows x 2^20 samples, delay 1000: 1048 steps of 1000
     phases, a ragged tail of 576 samples): the default kernel choice against the folded scan, outputs
