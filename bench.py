@@ -365,8 +365,8 @@ def config3(dev, steps, warmup, rows=512, shard=0, parity=True, graph=False):
 
     def chained():
         u = x
-        for k in range(K):
-            u = ptb.lti.lfilter(b[k], a[k], u)
+        for bk, ak in zip(b, a):          # iterating a tensor unbinds it: one stack in the backward pass
+            u = ptb.lti.lfilter(bk, ak, u)
         return u
 
     def fused():
@@ -874,8 +874,8 @@ def run_sos_cascade(args):
 
     def chained():
         u = x
-        for k in range(K):
-            u = ptb.lti.lfilter(b[k], a[k], u)
+        for bk, ak in zip(b, a):
+            u = ptb.lti.lfilter(bk, ak, u)
         return torch.autograd.grad(u, (b, a, x), gy)
 
     def timed(fn):

@@ -316,6 +316,12 @@ def matrix_recurrence_scalar_input(A: Tensor, zi: Tensor, x: Tensor, lpv: bool) 
     return _ScalarInputMatrixRecurrence.apply(A, zi, x, lpv)
 
 
+def _defined(*pairs):
+    """(outputs, their gradients) without the pairs whose gradient is undefined."""
+    kept = [(o, g) for o, g in pairs if g is not None]
+    return [o for o, _ in kept], [g for _, g in kept]
+
+
 class BiquadTDF2(Function):
     """One transposed-direct-form-II second-order section, (b, a, zi, x) -> (y, zf)."""
 
@@ -328,6 +334,7 @@ class BiquadTDF2(Function):
         b, a, zi, x = inputs
         y, _ = output
         ctx.has_zi = zi is not None
+        ctx.set_materialize_grads(False)   # an unused zf arrives as None, not as a zero tensor to fill and read
         ctx.save_for_backward(b, a, x, y, *([zi] if zi is not None else []))
 
     @staticmethod
@@ -341,8 +348,8 @@ class BiquadTDF2(Function):
             with torch.enable_grad():
                 y2, zf2 = _biquad_reference_form(b, a, zi, x)
                 ins = [t for t, n in ((b, need_b), (a, need_a), (zi, need_zi), (x, need_x)) if n]
-                gs = list(torch.autograd.grad([y2, zf2], ins, [grad_y, grad_zf], create_graph=True,
-                                              allow_unused=True))
+                outs, gouts = _defined((y2, grad_y), (zf2, grad_zf))
+                gs = list(torch.autograd.grad(outs, ins, gouts, create_graph=True, allow_unused=True))
             out = []
             for n in (need_b, need_a, need_zi, need_x):
                 out.append(gs.pop(0) if n else None)
@@ -425,6 +432,7 @@ class ModalBank(Function):
     def forward(ctx: Any, x: Tensor, lam: Tensor, gain: Tensor, coef: Tensor, d: Optional[Tensor], w0: Tensor):
         y, wf, chk = _ops.modal_bank(x, lam, gain, coef, d, w0)
         ctx.has_d = d is not None
+        ctx.set_materialize_grads(False)
         ctx.save_for_backward(x, lam, gain, coef, chk, *([d] if d is not None else []))
         return y, wf
 
@@ -474,6 +482,7 @@ class SOSCascade(Function):
         need_coef = ctx.needs_input_grad[0] or ctx.needs_input_grad[1]
         y, mid, zf = _ops.sos_cascade(b, a, zi, x, need_coef)
         ctx.has_zi = zi is not None
+        ctx.set_materialize_grads(False)
         ctx.save_for_backward(b, a, x, mid, y, *([zi] if zi is not None else []))
         return y, zf
 
@@ -491,8 +500,8 @@ class SOSCascade(Function):
                     u, zf_k = BiquadTDF2.apply(b[k], a[k], None if zi is None else zi[k], u)
                     zfs.append(zf_k)
                 ins = [t for t, n in ((b, need_b), (a, need_a), (zi, need_zi), (x, need_x)) if n]
-                gs = list(torch.autograd.grad([u, torch.stack(zfs)], ins, [grad_y, grad_zf], create_graph=True,
-                                              allow_unused=True))
+                outs, gouts = _defined((u, grad_y), (torch.stack(zfs), grad_zf))
+                gs = list(torch.autograd.grad(outs, ins, gouts, create_graph=True, allow_unused=True))
             out = []
             for n in (need_b, need_a, need_zi, need_x):
                 out.append(gs.pop(0) if n else None)
@@ -516,6 +525,7 @@ class LPVBiquad(Function):
         y, hp, zf = fwd(b, a, zi, x, need)
         ctx.has_zi = zi is not None
         ctx.form = form
+        ctx.set_materialize_grads(False)
         ctx.save_for_backward(b, a, x, hp)
         return y, zf
 

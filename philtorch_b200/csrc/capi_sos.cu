@@ -95,7 +95,9 @@ static int chain_fwd_cfg(int64_t B, int64_t T, const void* b, const void* a, int
   if (ntiles >= 0xFFFFFFFEll || B >= 0xFFFFFFFFll) return PTB_ERR_TOO_LARGE;
   const WsLayout l = ws_layout(ntiles, C::SLOT_WORDS, 0);
   if (!ws || (reinterpret_cast<uintptr_t>(ws) & 255u) || wsb < tb + l.total) return PTB_ERR_WORKSPACE;
-  chain_setup_kernel<S, C, false><<<(unsigned)((rows * K + 127) / 128), 128, 0, st>>>(
+  // one warp per block: a thread writes its ~150 table entries with a stride of a table row, and the
+  // load/store units of few SMs serialised those (13.5 us with 128-thread blocks at 512 threads)
+  chain_setup_kernel<S, C, false><<<(unsigned)((rows * K + 31) / 32), 32, 0, st>>>(
       static_cast<const S*>(b), rows * 3, coef_batched ? 3 : 0, static_cast<const S*>(a), rows * 2,
       coef_batched ? 2 : 0, static_cast<S*>(ws), rows);
   PTB_CUDA(cudaGetLastError());
@@ -266,7 +268,7 @@ static int chain_bwd_cfg(int64_t B, int64_t T, const void* b, const void* a, int
   if (!ws || (reinterpret_cast<uintptr_t>(ws) & 255u) || wsb < tb + l.total) return PTB_ERR_WORKSPACE;
   const bool want_coef = grad_b != nullptr || grad_a != nullptr;
   if (want_coef && (!x || !mid || !y)) return PTB_ERR_ARG;
-  chain_setup_kernel<S, C, true><<<(unsigned)((rows * K + 127) / 128), 128, 0, st>>>(
+  chain_setup_kernel<S, C, true><<<(unsigned)((rows * K + 31) / 32), 32, 0, st>>>(
       static_cast<const S*>(b), rows * 3, coef_batched ? 3 : 0, static_cast<const S*>(a), rows * 2,
       coef_batched ? 2 : 0, static_cast<S*>(ws), rows);
   PTB_CUDA(cudaGetLastError());

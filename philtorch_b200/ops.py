@@ -534,8 +534,10 @@ def _biquad_tdf2_bwd(b, a, x, y, gy, gzf, need_coef, need_zi):
     b_c, a_c, x_c, y_c, gy_c, gzf_c = b.contiguous(), a.contiguous(), x.contiguous(), y.contiguous(), \
         gy.contiguous(), _opt(gzf)
     gx = torch.empty_like(x_c)
-    gb = torch.zeros_like(b_c) if need_coef else b.new_empty(0)
-    ga = torch.zeros_like(a_c) if need_coef else a.new_empty(0)
+    # the reduction that ends the launch writes every entry: zeros only when nothing is launched
+    fresh = torch.empty_like if (B and T) else torch.zeros_like
+    gb = fresh(b_c) if need_coef else b.new_empty(0)
+    ga = fresh(a_c) if need_coef else a.new_empty(0)
     gzi = x.new_empty(B, 2) if need_zi else x.new_empty(0)
     if B and T:
         _lib.call(lib.ptb_biquad_tdf2_bwd, dev, B, T, _lib.dtype_code(x), B, T, ptr(b_c), ptr(a_c),
@@ -907,8 +909,10 @@ def _sos_cascade_bwd(b, a, x, mid, y, gy, gzf, need_coef, need_zi):
     if need_coef and mid.numel() != (K - 1) * B * T:
         raise RuntimeError("coefficient gradients need the intermediate section outputs (keep_mid=True)")
     gx = torch.empty_like(x_c)
-    gb = torch.zeros_like(b_c) if need_coef else b.new_empty(0)
-    ga = torch.zeros_like(a_c) if need_coef else a.new_empty(0)
+    # the reduction that ends the launch writes every entry: zeros only when nothing is launched
+    fresh = torch.empty_like if (B and T) else torch.zeros_like
+    gb = fresh(b_c) if need_coef else b.new_empty(0)
+    ga = fresh(a_c) if need_coef else a.new_empty(0)
     gzi = x.new_empty(K, B, 2) if need_zi else x.new_empty(0)
     if B and T:
         code = _lib.dtype_code(x)
