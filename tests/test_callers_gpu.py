@@ -163,6 +163,26 @@ def test_cubic_spline_sizes(dtype, m, scipy_padding):
 
 
 @pytest.mark.parametrize("scipy_padding", [True, False])
+def test_cubic_spline_long_rows(scipy_padding):
+    """Two rows of 2^17 samples (the prefilter cuts them into pieces), upsampled by 3, with the gradient
+    checked through the adjoint identity <gy, S u> = <S^T gy, u> of the linear map S."""
+    n, m = 1 << 17, 3
+    gen = torch.Generator().manual_seed(23)
+    x0 = torch.randn(2, n, generator=gen, dtype=torch.float64)
+    x = x0.to(DEV).requires_grad_()
+    y = cubic_spline(x, m, scipy_padding=scipy_padding)
+    ref = torch.from_numpy(callers.cubic_spline(x0.numpy(), m, scipy_padding))
+    assert rel_err(y.detach(), ref) <= tol(torch.float64)
+    gy = torch.randn(y.shape, generator=gen, dtype=torch.float64).to(DEV)
+    (gx,) = torch.autograd.grad(y, x, gy)
+    u = torch.randn(2, n, generator=gen, dtype=torch.float64)
+    lhs = (gy.cpu() * torch.from_numpy(callers.cubic_spline(u.numpy(), m, scipy_padding))).sum()
+    rhs = (gx.cpu() * u).sum()
+    ptb.check_errors()
+    assert abs(lhs - rhs) <= 1e-9 * float(gy.norm() * u.norm())
+
+
+@pytest.mark.parametrize("scipy_padding", [True, False])
 @pytest.mark.parametrize("pfe", [True, False])
 def test_cspline_gradcheck(scipy_padding, pfe, comb_route):
     if comb_route != "folded_scan":
