@@ -73,19 +73,7 @@ static int bank_bwd(BankParams<R> p, cudaStream_t st) {
   PTB_CUDA(cudaGetLastError());
   bank_fold_kernel<R, true><<<(unsigned)((p.rows * p.M * 32 + 127) / 128), 128, 0, st>>>(p, C::TILE);
   PTB_CUDA(cudaGetLastError());
-  constexpr int smem = MMAX * C::SPT * kBankNT * (int)sizeof(Cx<R>);   // the tile's forward states
-  static bool attr_set[kMaxDevices] = {};
-  int dev = 0;
-  PTB_CUDA(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= kMaxDevices) return PTB_ERR_ARG;
-  {
-    std::lock_guard<std::mutex> init_lock(init_mutex());
-    if (!attr_set[dev]) {
-      PTB_CUDA(cudaFuncSetAttribute(bank_backward_kernel<R, MMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-      attr_set[dev] = true;
-    }
-  }
-  bank_backward_kernel<R, MMAX><<<grid, kBankNT, smem, st>>>(p);
+  bank_backward_kernel<R, MMAX><<<grid, kBankNT, 0, st>>>(p);
   PTB_CUDA(cudaGetLastError());
   return PTB_OK;
 }

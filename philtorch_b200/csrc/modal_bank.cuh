@@ -390,18 +390,41 @@ __global__ void __launch_bounds__(kBankNT, 4) bank_forward_kernel(const BankPara
 }
 
 // ---- step C adjoint ---------------------------------------------------------------------------------
+// Neither the forward nor the adjoint modes are stepped sample by sample.  Inside a thread (S = SPT
+// samples x_j, gy_j; h = w[tb-1], the forward modes entering the thread; rin = r[tb+S], the adjoint
+// modes entering it from the right; l = lam, a = conj(lam)):
+//   W_j = w[tb+j-1] = l^j h + gain sum_{k<j} l^(j-1-k) x_k
+//   R_j = r[tb+j+1] = a^(S-1-j) rin + conj(coef) sum_{i>j} a^(i-j-1) gy_i
+// With the REAL cross-correlation of the thread's samples, C[n] = sum_j x_j gy_(j+n) (the same for every
+// mode), and per mode four real-times-complex dot products and two sums over C,
+//   SX = sum_j a^(S-1-j) x_j     U = sum_k (S-1-k) a^(S-2-k) x_k     SG = sum_j a^j gy_j     V = sum_i i a^(i-1) gy_i
+//   Q  = sum_{n>=1} a^(n-1) C[n]                                    Q2 = sum_{n>=2} (n-1) a^(n-2) C[n]
+// the thread's outputs and sums are
+//   grad_x_j  = d gy_j + sum_{i>j} K[i-j-1] gy_i + Re sum_m conj(gain l^(S-1-j)) rin      (K as in the forward kernel)
+//   grad_gain = sum_j R_j x_j        = rin SX + conj(coef) Q
+//   grad_coef = sum_j gy_j conj(W_j) = conj(h) SG + conj(gain) Q
+//   grad_lam  = sum_j R_j conj(W_j)  = S a^(S-1) rin conj(h) + rin conj(gain) U + conj(coef) conj(h) V + conj(coef gain) Q2
+//   grad_d    = C[0]
+// and the aggregates the two scans over the threads start from are gain conj(SX) and conj(coef) SG.
+// (Stepping both sets of modes and keeping the forward ones in 64 KB of shared memory took about four
+// times the instructions.)  The gradient of the final modes enters at sample N-1: the one thread that
+// owns it adds the terms of dR_j = a^(jN-j) g_wf, j <= jN = N-1-tb, from the same tables.
 template <class R, int MMAX>
 __global__ void __launch_bounds__(kBankNT, sizeof(R) == 4 ? 3 : 1) bank_backward_kernel(const BankParams<R> p) {
   using C = BankCfg<R, MMAX>;
   constexpr int SPT = C::SPT;
+  constexpr int LS = SPT + 1;   // stride of the power tables
   constexpr int NSUM = 6 * MMAX + 1;
   __shared__ Cx<R> pw[(C::NPOW + 1) * MMAX];
   __shared__ Cx<R> pwa[(C::NPOW + 1) * MMAX];
   __shared__ Cx<R> sm_w[kBankNW * MMAX];
   __shared__ Cx<R> sm_c[6 * MMAX];   // lam, gain, coef, forward / adjoint state entering the tile, r[N]
   __shared__ R sm_red[kBankNW * NSUM];
-  __shared__ Cx<R> lp[MMAX * (SPT + 1)], lpa[MMAX * (SPT + 1)];
+  __shared__ Cx<R> lp[MMAX * LS], lpa[MMAX * LS];   // l^k, a^k, k = 0..SPT
   __shared__ Cx<R> wt[MMAX * SPT], wta[MMAX * SPT];
+  __shared__ Cx<R> dta[MMAX * LS];                  // k a^(k-1)
+  __shared__ Cx<R> gl[MMAX * SPT];                  // gain l^k
+  __shared__ R kern[SPT];                           // K[n] = Re sum_m coef l^n gain
   const int64_t runs = (p.ntiles + p.run - 1) / p.run;
   const int64_t row = blockIdx.x / runs, tile0 = (blockIdx.x % runs) * p.run;
   bank_powers<R, MMAX, false>(p, row, pw);
@@ -416,11 +439,27 @@ __global__ void __launch_bounds__(kBankNT, sizeof(R) == 4 ? 3 : 1) bank_backward
     sm_c[2 * MMAX + m] = on ? p.coef[row * p.M + m] : Cx<R>(R(0));
     sm_c[5 * MMAX + m] = (on && p.g_wf) ? p.g_wf[row * p.M + m] : Cx<R>(R(0));
   }
+  if (threadIdx.x < MMAX * LS) {
+    const int k = threadIdx.x % LS;
+    const Cx<R> prev = k > 0 ? lpa[threadIdx.x - 1] : Cx<R>(R(0));
+    dta[threadIdx.x] = Cx<R>((R)k * prev.re, (R)k * prev.im);
+  }
+  if (threadIdx.x < MMAX * SPT) {
+    const int m = threadIdx.x / SPT, k = threadIdx.x % SPT;
+    gl[threadIdx.x] = m < p.M ? p.gain[row * p.M + m] * lp[m * LS + k] : Cx<R>(R(0));
+  }
+  __syncthreads();
+  if (threadIdx.x < SPT) {
+    R a = R(0);
+    for (int m = 0; m < p.M; ++m) {
+      const Cx<R> c = p.coef[row * p.M + m], g = gl[m * SPT + threadIdx.x];
+      a += c.re * g.re - c.im * g.im;
+    }
+    kern[threadIdx.x] = a;
+  }
   const bool vec = bank_vec_ok<R>(p.x, p.gy, p.y, p.N);
   const R dd = p.d ? __ldg(p.d + row) : R(0);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  extern __shared__ __align__(16) unsigned char bank_dyn_smem[];
-  Cx<R>* wprev = reinterpret_cast<Cx<R>*>(bank_dyn_smem);
   for (int64_t tile = tile0; tile < tile0 + p.run && tile < p.ntiles; ++tile) {
   if (threadIdx.x < MMAX) {
     const int m = threadIdx.x;
@@ -434,49 +473,37 @@ __global__ void __launch_bounds__(kBankNT, sizeof(R) == 4 ? 3 : 1) bank_backward
   R xv[SPT], gv[SPT];
   bank_load<R, SPT>(p.x + row * p.N, p.N, t0, threadIdx.x, vec, xv);
   bank_load<R, SPT>(p.gy + row * p.N, p.N, t0, threadIdx.x, vec, gv);
+  const bool own = p.N - 1 >= tb && p.N - 1 < tb + SPT;   // this thread holds the row's last sample
+  const int jn = own ? (int)(p.N - 1 - tb) : 0;
 
-  // (1) forward states w[t-1] at this thread's samples, recomputed from the tile's checkpoint
-  Cx<R> s[MMAX], exc[MMAX], h[MMAX];
+  // (1) forward modes entering this thread, from the tile's checkpoint
+  Cx<R> sx[MMAX], sg[MMAX], s[MMAX], exc[MMAX], h[MMAX];
 #pragma unroll
   for (int m = 0; m < MMAX; ++m) {
-    Cx<R> a(R(0));
+    Cx<R> a(R(0)), b(R(0));
 #pragma unroll
-    for (int j = 0; j < SPT; ++j) cfma_r(a, wt[m * SPT + j], xv[j]);
-    s[m] = a;
+    for (int j = 0; j < SPT; ++j) {
+      cfma_r(a, lpa[m * LS + SPT - 1 - j], xv[j]);
+      cfma_r(b, lpa[m * LS + j], gv[j]);
+    }
+    sx[m] = a;
+    sg[m] = b;
+    s[m] = sm_c[MMAX + m] * cj(a);
   }
   bank_scan<R, MMAX>(s, pw, sm_w, exc);
   __syncthreads();
   bank_thread_state<R, MMAX>(sm_c + 3 * MMAX, exc, pw, sm_w, h);
-  // kept in shared memory, [mode][sample][thread]: consecutive threads hit consecutive 8- or 16-byte
-  // words, and the registers stay free for the adjoint part
-#pragma unroll
-  for (int j = 0; j < SPT; ++j)
-#pragma unroll
-    for (int m = 0; m < MMAX; ++m) {
-      wprev[(m * SPT + j) * kBankNT + threadIdx.x] = h[m];
-      h[m] = sm_c[m] * h[m];
-      cfma_r(h[m], sm_c[MMAX + m], xv[j]);
-    }
   __syncthreads();   // sm_w is reused by the adjoint scan
 
-  // (2) adjoint states: the scan runs over the threads in DESCENDING time, i.e. the thread that
+  // (2) adjoint modes: the scan runs over the threads in DESCENDING time, i.e. the thread that
   // holds the tile's last samples comes first: exchange roles through a mirrored thread index
   // (thread i plays scan position NT-1-i by shuffling with mirrored lanes and warps).
-  Cx<R> sa[MMAX];
-#pragma unroll
-  for (int m = 0; m < MMAX; ++m) {
-    Cx<R> a(R(0));
-#pragma unroll
-    for (int j = 0; j < SPT; ++j) cfma_r(a, wta[m * SPT + j], gv[j]);
-    if (p.N - 1 >= tb && p.N - 1 < tb + SPT)               // r[N] enters above sample N-1
-      a = a + lpa[m * (SPT + 1) + (int)(p.N - tb)] * sm_c[5 * MMAX + m];
-    sa[m] = a;
-  }
-  // mirrored inclusive scan: lane L takes contributions of lanes L+1.. (later in time) first
   Cx<R> rin[MMAX];
 #pragma unroll
   for (int m = 0; m < MMAX; ++m) {
-    Cx<R> a = sa[m];
+    Cx<R> a = cj(sm_c[2 * MMAX + m]) * sg[m];
+    if (own) a = a + lpa[m * LS + jn + 1] * sm_c[5 * MMAX + m];   // r[N] enters above sample N-1
+    // mirrored inclusive scan: lane L takes contributions of lanes L+1.. (later in time) first
 #pragma unroll
     for (int d = 0; d < 5; ++d) {
       const Cx<R> o = shfl_down_s(a, 1 << d);
@@ -496,41 +523,96 @@ __global__ void __launch_bounds__(kBankNT, sizeof(R) == 4 ? 3 : 1) bank_backward
     rin[m] = bank_lane_power<R, MMAX>(pwa, m, 31 - lane) * z + rin[m];   // r[t+1] of the thread's last sample
   }
 
-  // (3) the thread's samples in descending time
-  Cx<R> g_gain[MMAX], g_lam[MMAX], g_coef[MMAX];
-#pragma unroll
-  for (int m = 0; m < MMAX; ++m) { g_gain[m] = Cx<R>(R(0)); g_lam[m] = Cx<R>(R(0)); g_coef[m] = Cx<R>(R(0)); }
-  R g_d = R(0);
+  // (3) grad_x: a short real convolution of gy plus the decaying incoming adjoint modes
   R gxv[SPT];
 #pragma unroll
-  for (int j = SPT - 1; j >= 0; --j) {
+  for (int j = 0; j < SPT; ++j) {
     R acc = dd * gv[j];
-    Cx<R> acc2(R(0), R(0));   // sum over the modes of (g.re r.re, g.im r.im): its two halves add up to Re(conj(gain) r[t+1])
+#pragma unroll
+    for (int i = j + 1; i < SPT; ++i) acc += kern[i - j - 1] * gv[i];
+    if constexpr (std::is_same<R, float>::value) {
+      float2 acc2 = make_float2(0.f, 0.f);
+#pragma unroll
+      for (int m = 0; m < MMAX; ++m) {
+        const Cx<R> g = gl[m * SPT + SPT - 1 - j];
+        acc2 = __ffma2_rn(make_float2(g.re, g.im), make_float2(rin[m].re, rin[m].im), acc2);
+      }
+      acc += acc2.x + acc2.y;
+    } else {
+#pragma unroll
+      for (int m = 0; m < MMAX; ++m) {
+        const Cx<R> g = gl[m * SPT + SPT - 1 - j];
+        acc += g.re * rin[m].re + g.im * rin[m].im;
+      }
+    }
+    gxv[j] = acc;
+  }
+
+  // (4) the thread's sums
+  Cx<R> g_gain[MMAX], g_lam[MMAX], g_coef[MMAX];
+  R g_d = R(0);
+  if (p.need) {
+    R cr[SPT];   // C[n]
+#pragma unroll
+    for (int n = 0; n < SPT; ++n) {
+      R a = R(0);
+#pragma unroll
+      for (int j = 0; j + n < SPT; ++j) a += xv[j] * gv[j + n];
+      cr[n] = a;
+    }
+    g_d = cr[0];
 #pragma unroll
     for (int m = 0; m < MMAX; ++m) {
-      if (tb + j == p.N - 1) rin[m] = rin[m] + sm_c[5 * MMAX + m];
-      const Cx<R> r1 = rin[m];                                // r[t+1]
-      const Cx<R> g = sm_c[MMAX + m];
-      if constexpr (std::is_same<R, float>::value) {
-        const float2 t = __ffma2_rn(make_float2(g.re, g.im), make_float2(r1.re, r1.im), make_float2(acc2.re, acc2.im));
-        acc2.re = t.x;
-        acc2.im = t.y;
-      } else {
-        acc += g.re * r1.re + g.im * r1.im;                   // Re(conj(gain) r[t+1])
+      Cx<R> u(R(0)), v(R(0)), q(R(0)), q2(R(0));
+#pragma unroll
+      for (int j = 0; j < SPT; ++j) {
+        cfma_r(u, dta[m * LS + SPT - 1 - j], xv[j]);
+        cfma_r(v, dta[m * LS + j], gv[j]);
       }
-      const Cx<R> wc = cj(wprev[(m * SPT + j) * kBankNT + threadIdx.x]);
-      if (p.need & 1) cfma_r(g_gain[m], r1, xv[j]);
-      if (p.need & 2) g_lam[m] += r1 * wc;
-      if (p.need & 4) cfma_r(g_coef[m], wc, gv[j]);
-      rin[m] = cj(sm_c[m]) * r1;                                            // r[t]
-      cfma_r(rin[m], cj(sm_c[2 * MMAX + m]), gv[j]);
+#pragma unroll
+      for (int n = 1; n < SPT; ++n) {
+        cfma_r(q, lpa[m * LS + n - 1], cr[n]);
+        if (n >= 2) cfma_r(q2, dta[m * LS + n - 1], cr[n]);
+      }
+      const Cx<R> gb = cj(sm_c[MMAX + m]), cb = cj(sm_c[2 * MMAX + m]), hb = cj(h[m]), r = rin[m];
+      const Cx<R> ap = lpa[m * LS + SPT - 1];
+      g_gain[m] = r * sx[m] + cb * q;
+      g_coef[m] = hb * sg[m] + gb * q;
+      const Cx<R> rh = r * hb;
+      g_lam[m] = Cx<R>((R)SPT * ap.re, (R)SPT * ap.im) * rh + (r * gb) * u + (cb * hb) * v + (cb * gb) * q2;
     }
-    g_d += gv[j] * xv[j];
-    gxv[j] = acc + (acc2.re + acc2.im);
+  } else {
+#pragma unroll
+    for (int m = 0; m < MMAX; ++m) { g_gain[m] = Cx<R>(R(0)); g_lam[m] = Cx<R>(R(0)); g_coef[m] = Cx<R>(R(0)); }
+  }
+  if (own && p.g_wf) {   // one thread per row: the terms of r[N], which enters at sample jn
+#pragma unroll
+    for (int m = 0; m < MMAX; ++m) {
+      const Cx<R> G = sm_c[5 * MMAX + m];
+      Cx<R> ax(R(0)), ad(R(0));   // sum_{j<=jn} a^(jn-j) x_j,  sum_{k<jn} (jn-k) a^(jn-k-1) x_k
+#pragma unroll
+      for (int j = 0; j < SPT; ++j) {
+        if (j <= jn) {
+          const Cx<R> g = gl[m * SPT + jn - j];
+          gxv[j] += g.re * G.re + g.im * G.im;
+          cfma_r(ax, lpa[m * LS + jn - j], xv[j]);
+          cfma_r(ad, dta[m * LS + jn - j], xv[j]);
+        }
+      }
+      const Cx<R> an = lpa[m * LS + jn];
+      g_gain[m] = g_gain[m] + G * ax;
+      g_lam[m] = g_lam[m] + G * (Cx<R>((R)(jn + 1) * an.re, (R)(jn + 1) * an.im) * cj(h[m]) + cj(sm_c[MMAX + m]) * ad);
+    }
   }
   bank_store<R, SPT>(p.y + row * p.N, p.N, tb, vec, gxv);
+#pragma unroll
+  for (int m = 0; m < MMAX; ++m) {
+    if (!(p.need & 1)) g_gain[m] = Cx<R>(R(0));
+    if (!(p.need & 2)) g_lam[m] = Cx<R>(R(0));
+    if (!(p.need & 4)) g_coef[m] = Cx<R>(R(0));
+  }
 
-  // (4) sums of the tile: warp shuffles, then the warps' results through shared memory
+  // (5) sums of the tile: warp shuffles, then the warps' results through shared memory
   R sums[NSUM];
 #pragma unroll
   for (int m = 0; m < MMAX; ++m) {
