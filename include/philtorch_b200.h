@@ -480,7 +480,8 @@ int ptb_modal_mix_bwd(int dtype, int64_t rows, int64_t M, int64_t N, const void*
  * tile, which the adjoint needs (keep it until then).  wf (may be NULL): the modes after the last
  * sample.  Adjoint (gy real (rows, N); g_wf optional gradient of wf): grad_x (rows, N), grad_w0
  * (rows, M); `partial` receives (rows, tiles, 6 M + 1) reals per tile: {grad_gain, grad_lam, grad_coef}
- * as interleaved complex (M each) followed by grad_d -- the caller sums them over the tiles; `need`
+ * as interleaved complex (M each) followed by grad_d -- the caller sums them over the tiles (a run of
+ * consecutive tiles may store its sums with its last tile and zeros with the others); `need`
  * selects the parameter sums that are computed (bit 0 grad_gain, bit 1 grad_lam, bit 2 grad_coef); chk for
  * the adjoint is a second scratch array of the same size as the forward one (fwd_chk). */
 int64_t ptb_modal_bank_tiles(int64_t M, int64_t N);

@@ -57,7 +57,7 @@ struct BankParams {
   const Cx<R>* fwd_chk;    // adjoint: the forward direction's checkpoints
   R* y;                    // (rows, N)   forward: y; adjoint: grad_x
   Cx<R>* wf;               // (rows, M)   forward: final modes; adjoint: grad_w0
-  R* partial;              // adjoint: (rows, ntiles, 6 M + 1) sums of the tile
+  R* partial;              // adjoint: (rows, ntiles, 6 M + 1) sums; a run's sums are stored with its last tile, zeros elsewhere
   int64_t run;             // consecutive tiles of a row handled by one CTA (the per-row set-up is paid once)
   int need;                // adjoint: sums wanted: 1 grad_gain, 2 grad_lam, 4 grad_coef (skipped ones are zero)
 };
@@ -291,18 +291,24 @@ __global__ void bank_fold_kernel(const BankParams<R> p, int tile_len) {
   if (ADJ && p.wf && lane == 0) p.wf[idx] = Cx<R>((R)st.re, (R)st.im);
 }
 
+// lanep[m][lane] = lam^(SPT * lane), once per CTA: what a thread multiplies the state entering its warp by
+template <class R, int MMAX>
+__device__ __forceinline__ void bank_lane_table(const Cx<R>* pw, Cx<R>* lanep) {
+  for (int i = threadIdx.x; i < MMAX * 32; i += kBankNT) lanep[i] = bank_lane_power<R, MMAX>(pw, i >> 5, i & 31);
+}
+
 // State entering this thread, given the state entering the tile (z_tile), the scan's exclusive
 // offsets and the warps' totals.
 template <class R, int MMAX>
 __device__ __forceinline__ void bank_thread_state(const Cx<R>* z_tile, const Cx<R>* exc, const Cx<R>* pw,
-                                                  const Cx<R>* sm_w, Cx<R>* h) {
+                                                  const Cx<R>* sm_w, const Cx<R>* lanep, Cx<R>* h) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
   for (int m = 0; m < MMAX; ++m) {
     const Cx<R> p32 = pw[5 * MMAX + m];
     Cx<R> z = z_tile[m];
     for (int w = 0; w < warp; ++w) z = p32 * z + sm_w[w * MMAX + m];
-    h[m] = bank_lane_power<R, MMAX>(pw, m, lane) * z + exc[m];
+    h[m] = lanep[m * 32 + lane] * z + exc[m];
   }
 }
 
@@ -321,11 +327,13 @@ __global__ void __launch_bounds__(kBankNT, 4) bank_forward_kernel(const BankPara
   __shared__ Cx<R> cl[MMAX * SPT];   // coef_m lam_m^j
   __shared__ Cx<R> zt[MMAX];         // the modes entering the tile
   __shared__ R kern[SPT];
+  __shared__ Cx<R> lanep[MMAX * 32];
   const int64_t runs = (p.ntiles + p.run - 1) / p.run;
   const int64_t row = blockIdx.x / runs, tile0 = (blockIdx.x % runs) * p.run;
   const bool vec = bank_vec_ok<R>(p.x, p.y, p.y, p.N);
   bank_powers<R, MMAX, false>(p, row, pw);
-  bank_tables<R, MMAX, SPT, false>(p, row, lp, wt);
+  bank_tables<R, MMAX, SPT, false>(p, row, lp, wt);   // (a barrier inside: pw is complete after it)
+  bank_lane_table<R, MMAX>(pw, lanep);
   if (threadIdx.x < MMAX * SPT) {
     const int m = threadIdx.x / SPT, j = threadIdx.x % SPT;
     cl[threadIdx.x] = m < p.M ? p.coef[row * p.M + m] * lp[m * (SPT + 1) + j] : Cx<R>(R(0));
@@ -357,7 +365,7 @@ __global__ void __launch_bounds__(kBankNT, 4) bank_forward_kernel(const BankPara
     Cx<R> exc[MMAX], h[MMAX];
     bank_scan<R, MMAX>(s, pw, sm_w, exc);
     __syncthreads();   // also publishes kern (first tile) and zt
-    bank_thread_state<R, MMAX>(zt, exc, pw, sm_w, h);
+    bank_thread_state<R, MMAX>(zt, exc, pw, sm_w, lanep, h);
     const int64_t tb = t0 + (int64_t)threadIdx.x * SPT;
     R out[SPT];
 #pragma unroll
@@ -425,12 +433,15 @@ __global__ void __launch_bounds__(kBankNT, sizeof(R) == 4 ? 3 : 1) bank_backward
   __shared__ Cx<R> dta[MMAX * LS];                  // k a^(k-1)
   __shared__ Cx<R> gl[MMAX * SPT];                  // gain l^k
   __shared__ R kern[SPT];                           // K[n] = Re sum_m coef l^n gain
+  __shared__ Cx<R> lanep[MMAX * 32], lanepa[MMAX * 32];   // l^(SPT lane), a^(SPT lane)
   const int64_t runs = (p.ntiles + p.run - 1) / p.run;
   const int64_t row = blockIdx.x / runs, tile0 = (blockIdx.x % runs) * p.run;
   bank_powers<R, MMAX, false>(p, row, pw);
   bank_powers<R, MMAX, true>(p, row, pwa);
-  bank_tables<R, MMAX, SPT, false>(p, row, lp, wt);
+  bank_tables<R, MMAX, SPT, false>(p, row, lp, wt);    // (barriers inside: pw and pwa are complete after them)
   bank_tables<R, MMAX, SPT, true>(p, row, lpa, wta);
+  bank_lane_table<R, MMAX>(pw, lanep);
+  bank_lane_table<R, MMAX>(pwa, lanepa);
   if (threadIdx.x < MMAX) {
     const int m = threadIdx.x;
     const bool on = m < p.M;
@@ -460,6 +471,10 @@ __global__ void __launch_bounds__(kBankNT, sizeof(R) == 4 ? 3 : 1) bank_backward
   const bool vec = bank_vec_ok<R>(p.x, p.gy, p.y, p.N);
   const R dd = p.d ? __ldg(p.d + row) : R(0);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  Cx<R> g_gain[MMAX], g_lam[MMAX], g_coef[MMAX];
+#pragma unroll
+  for (int m = 0; m < MMAX; ++m) { g_gain[m] = Cx<R>(R(0)); g_lam[m] = Cx<R>(R(0)); g_coef[m] = Cx<R>(R(0)); }
+  R g_d = R(0);
   for (int64_t tile = tile0; tile < tile0 + p.run && tile < p.ntiles; ++tile) {
   if (threadIdx.x < MMAX) {
     const int m = threadIdx.x;
@@ -492,7 +507,7 @@ __global__ void __launch_bounds__(kBankNT, sizeof(R) == 4 ? 3 : 1) bank_backward
   }
   bank_scan<R, MMAX>(s, pw, sm_w, exc);
   __syncthreads();
-  bank_thread_state<R, MMAX>(sm_c + 3 * MMAX, exc, pw, sm_w, h);
+  bank_thread_state<R, MMAX>(sm_c + 3 * MMAX, exc, pw, sm_w, lanep, h);
   __syncthreads();   // sm_w is reused by the adjoint scan
 
   // (2) adjoint modes: the scan runs over the threads in DESCENDING time, i.e. the thread that
@@ -520,7 +535,7 @@ __global__ void __launch_bounds__(kBankNT, sizeof(R) == 4 ? 3 : 1) bank_backward
     const Cx<R> p32 = pwa[5 * MMAX + m];
     Cx<R> z = sm_c[4 * MMAX + m];                 // adjoint state entering the tile from the right
     for (int w = kBankNW - 1; w > warp; --w) z = p32 * z + sm_w[w * MMAX + m];
-    rin[m] = bank_lane_power<R, MMAX>(pwa, m, 31 - lane) * z + rin[m];   // r[t+1] of the thread's last sample
+    rin[m] = lanepa[m * 32 + 31 - lane] * z + rin[m];   // r[t+1] of the thread's last sample
   }
 
   // (3) grad_x: a short real convolution of gy plus the decaying incoming adjoint modes
@@ -548,9 +563,7 @@ __global__ void __launch_bounds__(kBankNT, sizeof(R) == 4 ? 3 : 1) bank_backward
     gxv[j] = acc;
   }
 
-  // (4) the thread's sums
-  Cx<R> g_gain[MMAX], g_lam[MMAX], g_coef[MMAX];
-  R g_d = R(0);
+  // (4) the thread's sums, accumulated over the tiles of the run
   if (p.need) {
     R cr[SPT];   // C[n]
 #pragma unroll
@@ -560,7 +573,7 @@ __global__ void __launch_bounds__(kBankNT, sizeof(R) == 4 ? 3 : 1) bank_backward
       for (int j = 0; j + n < SPT; ++j) a += xv[j] * gv[j + n];
       cr[n] = a;
     }
-    g_d = cr[0];
+    g_d += cr[0];
 #pragma unroll
     for (int m = 0; m < MMAX; ++m) {
       Cx<R> u(R(0)), v(R(0)), q(R(0)), q2(R(0));
@@ -576,14 +589,11 @@ __global__ void __launch_bounds__(kBankNT, sizeof(R) == 4 ? 3 : 1) bank_backward
       }
       const Cx<R> gb = cj(sm_c[MMAX + m]), cb = cj(sm_c[2 * MMAX + m]), hb = cj(h[m]), r = rin[m];
       const Cx<R> ap = lpa[m * LS + SPT - 1];
-      g_gain[m] = r * sx[m] + cb * q;
-      g_coef[m] = hb * sg[m] + gb * q;
+      g_gain[m] = g_gain[m] + (r * sx[m] + cb * q);
+      g_coef[m] = g_coef[m] + (hb * sg[m] + gb * q);
       const Cx<R> rh = r * hb;
-      g_lam[m] = Cx<R>((R)SPT * ap.re, (R)SPT * ap.im) * rh + (r * gb) * u + (cb * hb) * v + (cb * gb) * q2;
+      g_lam[m] = g_lam[m] + (Cx<R>((R)SPT * ap.re, (R)SPT * ap.im) * rh + (r * gb) * u + (cb * hb) * v + (cb * gb) * q2);
     }
-  } else {
-#pragma unroll
-    for (int m = 0; m < MMAX; ++m) { g_gain[m] = Cx<R>(R(0)); g_lam[m] = Cx<R>(R(0)); g_coef[m] = Cx<R>(R(0)); }
   }
   if (own && p.g_wf) {   // one thread per row: the terms of r[N], which enters at sample jn
 #pragma unroll
@@ -605,14 +615,21 @@ __global__ void __launch_bounds__(kBankNT, sizeof(R) == 4 ? 3 : 1) bank_backward
     }
   }
   bank_store<R, SPT>(p.y + row * p.N, p.N, tb, vec, gxv);
+
+  // (5) sums of the run, stored with its last tile (the slots of its other tiles hold zeros): warp
+  // shuffles, then the warps' results through shared memory
+  const bool last_of_run = tile + 1 == tile0 + p.run || tile + 1 == p.ntiles;
+  if (!last_of_run) {
+    if (threadIdx.x < 6 * p.M + 1) p.partial[(row * p.ntiles + tile) * (6 * p.M + 1) + threadIdx.x] = R(0);
+    __syncthreads();   // the shared scratch is rewritten by the next tile
+    continue;
+  }
 #pragma unroll
   for (int m = 0; m < MMAX; ++m) {
     if (!(p.need & 1)) g_gain[m] = Cx<R>(R(0));
     if (!(p.need & 2)) g_lam[m] = Cx<R>(R(0));
     if (!(p.need & 4)) g_coef[m] = Cx<R>(R(0));
   }
-
-  // (5) sums of the tile: warp shuffles, then the warps' results through shared memory
   R sums[NSUM];
 #pragma unroll
   for (int m = 0; m < MMAX; ++m) {
