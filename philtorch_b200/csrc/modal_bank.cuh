@@ -324,7 +324,7 @@ __global__ void __launch_bounds__(kBankNT, 4) bank_forward_kernel(const BankPara
   __shared__ Cx<R> sm_w[kBankNW * MMAX];
   __shared__ Cx<R> lp[MMAX * (SPT + 1)];
   __shared__ Cx<R> wt[MMAX * SPT];
-  __shared__ Cx<R> cl[MMAX * SPT];   // coef_m lam_m^j
+  __shared__ Cx<R> cl[MMAX * SPT];   // conj(coef_m lam_m^j): Re(coef lam^j h) = cl.re h.re + cl.im h.im, one packed multiply-add
   __shared__ Cx<R> zt[MMAX];         // the modes entering the tile
   __shared__ R kern[SPT];
   __shared__ Cx<R> lanep[MMAX * 32];
@@ -336,14 +336,14 @@ __global__ void __launch_bounds__(kBankNT, 4) bank_forward_kernel(const BankPara
   bank_lane_table<R, MMAX>(pw, lanep);
   if (threadIdx.x < MMAX * SPT) {
     const int m = threadIdx.x / SPT, j = threadIdx.x % SPT;
-    cl[threadIdx.x] = m < p.M ? p.coef[row * p.M + m] * lp[m * (SPT + 1) + j] : Cx<R>(R(0));
+    cl[threadIdx.x] = m < p.M ? cj(p.coef[row * p.M + m] * lp[m * (SPT + 1) + j]) : Cx<R>(R(0));
   }
   __syncthreads();
   if (threadIdx.x < SPT) {   // K[n] = Re sum_m (coef lam^n) gain
     R a = R(0);
     for (int m = 0; m < p.M; ++m) {
       const Cx<R> c = cl[m * SPT + threadIdx.x], g = p.gain[row * p.M + m];
-      a += c.re * g.re - c.im * g.im;
+      a += c.re * g.re + c.im * g.im;
     }
     kern[threadIdx.x] = a;
   }
@@ -373,10 +373,20 @@ __global__ void __launch_bounds__(kBankNT, 4) bank_forward_kernel(const BankPara
       R acc = dd * v[j];
 #pragma unroll
       for (int i = 0; i < j; ++i) acc += kern[j - 1 - i] * v[i];
+      if constexpr (std::is_same<R, float>::value) {
+        float2 acc2 = make_float2(0.f, 0.f);
 #pragma unroll
-      for (int m = 0; m < MMAX; ++m) {
-        const Cx<R> c = cl[m * SPT + j];
-        acc += c.re * h[m].re - c.im * h[m].im;
+        for (int m = 0; m < MMAX; ++m) {
+          const Cx<R> c = cl[m * SPT + j];
+          acc2 = __ffma2_rn(make_float2(c.re, c.im), make_float2(h[m].re, h[m].im), acc2);
+        }
+        acc += acc2.x + acc2.y;
+      } else {
+#pragma unroll
+        for (int m = 0; m < MMAX; ++m) {
+          const Cx<R> c = cl[m * SPT + j];
+          acc += c.re * h[m].re + c.im * h[m].im;
+        }
       }
       out[j] = acc;
     }
