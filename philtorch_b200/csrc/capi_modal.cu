@@ -45,6 +45,9 @@ static int modal_drive(int64_t rows, int64_t M, int64_t N, const void* x, const 
 // ---- fused bank of modes (modal_bank.cuh) -------------------------------------------------------------
 // tiles of a row that one CTA takes in a row (the per-row tables are then built once per run): as many
 // as leave about eight CTAs per SM
+#ifndef PTB_BANK_AGG_RUN_DIV
+#define PTB_BANK_AGG_RUN_DIV 4
+#endif
 static int64_t bank_run_length(int64_t rows, int64_t ntiles) {
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -56,7 +59,9 @@ template <class R, int MMAX>
 static int bank_fwd(BankParams<R> p, cudaStream_t st) {
   using C = BankCfg<R, MMAX>;
   const unsigned grid = (unsigned)(p.rows * ((p.ntiles + p.run - 1) / p.run));
-  bank_aggregate_kernel<R, MMAX, false><<<grid, kBankNT, 0, st>>>(p);
+  BankParams<R> pa = p;   // the aggregate pass keeps few registers: shorter runs, more CTAs per SM
+  pa.run = std::max<int64_t>(1, p.run / PTB_BANK_AGG_RUN_DIV);
+  bank_aggregate_kernel<R, MMAX, false><<<(unsigned)(p.rows * ((p.ntiles + pa.run - 1) / pa.run)), kBankNT, 0, st>>>(pa);
   PTB_CUDA(cudaGetLastError());
   bank_fold_kernel<R, false><<<(unsigned)((p.rows * p.M * 32 + 127) / 128), 128, 0, st>>>(p, C::TILE);
   PTB_CUDA(cudaGetLastError());
@@ -69,7 +74,9 @@ template <class R, int MMAX>
 static int bank_bwd(BankParams<R> p, cudaStream_t st) {
   using C = BankCfg<R, MMAX>;
   const unsigned grid = (unsigned)(p.rows * ((p.ntiles + p.run - 1) / p.run));
-  bank_aggregate_kernel<R, MMAX, true><<<grid, kBankNT, 0, st>>>(p);
+  BankParams<R> pa = p;
+  pa.run = std::max<int64_t>(1, p.run / PTB_BANK_AGG_RUN_DIV);
+  bank_aggregate_kernel<R, MMAX, true><<<(unsigned)(p.rows * ((p.ntiles + pa.run - 1) / pa.run)), kBankNT, 0, st>>>(pa);
   PTB_CUDA(cudaGetLastError());
   bank_fold_kernel<R, true><<<(unsigned)((p.rows * p.M * 32 + 127) / 128), 128, 0, st>>>(p, C::TILE);
   PTB_CUDA(cudaGetLastError());

@@ -198,6 +198,12 @@ __device__ __forceinline__ Cx<R> bank_lane_power(const Cx<R>* pw, int m, int lan
   return r;
 }
 
+// lanep[m][lane] = lam^(SPT * lane), once per CTA: what a thread multiplies the state entering its warp by
+template <class R, int MMAX>
+__device__ __forceinline__ void bank_lane_table(const Cx<R>* pw, Cx<R>* lanep) {
+  for (int i = threadIdx.x; i < MMAX * 32; i += kBankNT) lanep[i] = bank_lane_power<R, MMAX>(pw, i >> 5, i & 31);
+}
+
 // ---- step A: tile aggregates (forward: x with gain; adjoint: gy with conj(coef), reversed time) ----
 template <class R, int MMAX, bool ADJ>
 __global__ void __launch_bounds__(kBankNT) bank_aggregate_kernel(const BankParams<R> p) {
@@ -207,6 +213,7 @@ __global__ void __launch_bounds__(kBankNT) bank_aggregate_kernel(const BankParam
   __shared__ Cx<R> sm_w[kBankNW * MMAX];
   __shared__ Cx<R> lp[MMAX * (SPT + 1)];
   __shared__ Cx<R> wt[MMAX * SPT];
+  __shared__ Cx<R> lanep[MMAX * 32];
   const int64_t runs = (p.ntiles + p.run - 1) / p.run;
   const int64_t row = blockIdx.x / runs, tile0 = (blockIdx.x % runs) * p.run;
   // thread order along the scan: forward = ascending time, adjoint = descending time
@@ -214,8 +221,10 @@ __global__ void __launch_bounds__(kBankNT) bank_aggregate_kernel(const BankParam
   const R* src = ADJ ? p.gy : p.x;
   const bool vec = bank_vec_ok<R>(src, src, src, p.N);
   bank_powers<R, MMAX, ADJ>(p, row, pw);
-  bank_tables<R, MMAX, SPT, ADJ>(p, row, lp, wt);
+  bank_tables<R, MMAX, SPT, ADJ>(p, row, lp, wt);   // (a barrier inside: pw is complete after it)
+  bank_lane_table<R, MMAX>(pw, lanep);
   __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int64_t tile = tile0; tile < tile0 + p.run && tile < p.ntiles; ++tile) {
     const int64_t t0 = tile * C::TILE;
     R v[SPT];
@@ -231,8 +240,15 @@ __global__ void __launch_bounds__(kBankNT) bank_aggregate_kernel(const BankParam
         a = a + lp[m * (SPT + 1) + (int)(p.N - tb)] * p.g_wf[row * p.M + m];
       s[m] = a;
     }
-    Cx<R> exc[MMAX];
-    bank_scan<R, MMAX>(s, pw, sm_w, exc);
+    // only the totals are wanted: every thread's offset times the power that carries it to the end of
+    // its warp, then a plain sum over the lanes (a scan would cost twice the shuffles)
+#pragma unroll
+    for (int m = 0; m < MMAX; ++m) {
+      Cx<R> a = lanep[m * 32 + 31 - lane] * s[m];
+#pragma unroll
+      for (int d = 16; d > 0; d >>= 1) a = a + shfl_down_s(a, d);
+      if (lane == 0) sm_w[warp * MMAX + m] = a;
+    }
     __syncthreads();
     if (threadIdx.x < MMAX && threadIdx.x < p.M) {
       const int m = threadIdx.x;
@@ -289,12 +305,6 @@ __global__ void bank_fold_kernel(const BankParams<R> p, int tile_len) {
   }
   // the state after the whole (zero-padded) row; only the adjoint uses it: r[0] = grad_w0
   if (ADJ && p.wf && lane == 0) p.wf[idx] = Cx<R>((R)st.re, (R)st.im);
-}
-
-// lanep[m][lane] = lam^(SPT * lane), once per CTA: what a thread multiplies the state entering its warp by
-template <class R, int MMAX>
-__device__ __forceinline__ void bank_lane_table(const Cx<R>* pw, Cx<R>* lanep) {
-  for (int i = threadIdx.x; i < MMAX * 32; i += kBankNT) lanep[i] = bank_lane_power<R, MMAX>(pw, i >> 5, i & 31);
 }
 
 // State entering this thread, given the state entering the tile (z_tile), the scan's exclusive
