@@ -285,11 +285,15 @@ __global__ void bank_fold_kernel(const BankParams<R> p, int tile_len) {
   Cx<double> st(0.0, 0.0);
   if (!ADJ && p.w0) { const Cx<R> z = p.w0[idx]; st = Cx<double>((double)z.re, (double)z.im); }
   Cx<R>* c = p.chk + row * p.ntiles * p.M + m;
+  // the aggregates of the next 32 tiles are fetched while this step's scan runs
+  Cx<R> ahead(R(0));
+  if (lane < p.ntiles) ahead = c[(ADJ ? p.ntiles - 1 - lane : lane) * p.M];
   for (int64_t k0 = 0; k0 < p.ntiles; k0 += 32) {
     const int64_t k = k0 + lane;
     const int64_t tile = ADJ ? p.ntiles - 1 - k : k;       // the adjoint walks the tiles from the last one
-    Cx<double> a(0.0, 0.0);
-    if (k < p.ntiles) { const Cx<R> g = c[tile * p.M]; a = Cx<double>((double)g.re, (double)g.im); }
+    Cx<double> a((double)ahead.re, (double)ahead.im);
+    ahead = Cx<R>(R(0));
+    if (k + 32 < p.ntiles) ahead = c[(ADJ ? p.ntiles - 1 - (k + 32) : k + 32) * p.M];
 #pragma unroll
     for (int d = 0; d < 5; ++d) {
       const Cx<double> o = shfl_up_s(a, 1 << d);
