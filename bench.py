@@ -1081,6 +1081,9 @@ def callers_entries(dev, steps: int, warmup: int):
             step, name, alg, Tc = caller_case(dev, kind, rows)
             ms = _time_steps(step, steps, warmup, dev)
             out[key] = _entry(name, "public API + autograd.grad", rows * Tc, ms, alg, None)
+            if kind == "diag_ssm":
+                out[key]["note"] = ("bound by instruction issue, not by HBM: four complex modes per sample are "
+                                    "scanned in registers while x is read and y written once per pass")
             del step
         except Exception as e:   # keep the headline line alive
             out[key] = {"error": f"{type(e).__name__}: {e}"[:300]}
