@@ -57,10 +57,18 @@ template <class S> struct FoBwdSel<S, false, S> { using type = FoBwd<S, PTB_FOLT
 #define PTB_FOH_BWD_CH 5       // 10240-sample tiles, 20 KB per array (3 units: 0.481 ms, 5 units: 0.404 ms)
 #define PTB_FOH_BWD_STAGES 3
 #endif
-template <bool LPV> struct FoFwdSel<float, LPV, __half> { using type = FoFwd<float, LPV ? PTB_FOH_FWD_CH : PTB_FOH_FWD_CH + 2, PTB_FOH_FWD_STAGES, 1, 1, LPV, __half>; };
-template <bool LPV> struct FoFwdSel<float, LPV, __nv_bfloat16> { using type = FoFwd<float, LPV ? PTB_FOH_FWD_CH : PTB_FOH_FWD_CH + 2, PTB_FOH_FWD_STAGES, 1, 1, LPV, __nv_bfloat16>; };
-template <bool LPV> struct FoBwdSel<float, LPV, __half> { using type = FoBwd<float, LPV ? PTB_FOH_BWD_CH : PTB_FOH_BWD_CH + 2, PTB_FOH_BWD_STAGES, 1, 1, LPV, false, __half>; };
-template <bool LPV> struct FoBwdSel<float, LPV, __nv_bfloat16> { using type = FoBwd<float, LPV ? PTB_FOH_BWD_CH : PTB_FOH_BWD_CH + 2, PTB_FOH_BWD_STAGES, 1, 1, LPV, false, __nv_bfloat16>; };
+// time-invariant coefficients: one staged array less per tile (forward, B=256, T=2^20, float16: 9 units x 3
+// stages 0.227 ms, 13 x 3 0.201 ms, 15 x 3 0.198 ms, 17 x 3 0.199 ms; backward: 9 x 3 no better than 7 x 3)
+#ifndef PTB_FOH_LTI_FWD_CH
+#define PTB_FOH_LTI_FWD_CH 15
+#define PTB_FOH_LTI_FWD_STAGES 3
+#define PTB_FOH_LTI_BWD_CH (PTB_FOH_BWD_CH + 2)
+#define PTB_FOH_LTI_BWD_STAGES PTB_FOH_BWD_STAGES
+#endif
+template <bool LPV> struct FoFwdSel<float, LPV, __half> { using type = FoFwd<float, LPV ? PTB_FOH_FWD_CH : PTB_FOH_LTI_FWD_CH, LPV ? PTB_FOH_FWD_STAGES : PTB_FOH_LTI_FWD_STAGES, 1, 1, LPV, __half>; };
+template <bool LPV> struct FoFwdSel<float, LPV, __nv_bfloat16> { using type = FoFwd<float, LPV ? PTB_FOH_FWD_CH : PTB_FOH_LTI_FWD_CH, LPV ? PTB_FOH_FWD_STAGES : PTB_FOH_LTI_FWD_STAGES, 1, 1, LPV, __nv_bfloat16>; };
+template <bool LPV> struct FoBwdSel<float, LPV, __half> { using type = FoBwd<float, LPV ? PTB_FOH_BWD_CH : PTB_FOH_LTI_BWD_CH, LPV ? PTB_FOH_BWD_STAGES : PTB_FOH_LTI_BWD_STAGES, 1, 1, LPV, false, __half>; };
+template <bool LPV> struct FoBwdSel<float, LPV, __nv_bfloat16> { using type = FoBwd<float, LPV ? PTB_FOH_BWD_CH : PTB_FOH_LTI_BWD_CH, LPV ? PTB_FOH_BWD_STAGES : PTB_FOH_LTI_BWD_STAGES, 1, 1, LPV, false, __nv_bfloat16>; };
 template <class S, bool LPV, class G = S> using FoFwdP = typename FoFwdSel<S, LPV, G>::type;
 template <class S, bool LPV, class G = S> using FoBwdP = typename FoBwdSel<S, LPV, G>::type;
 
